@@ -1,0 +1,126 @@
+"""In-tree build of the native libraries.
+
+* ``libovb_cuda.so``  - sm_100a kernels (nvcc, C ABI, loaded with ctypes)
+* ``_ovcore*.so``     - native core: graph IR, IR v11 reader/writer, passes, CPU reference
+                        executor, runtime and scheduler (g++ + pybind11)
+
+Both are written next to the sources inside the package so that a checkout is
+self-contained: nothing is installed into site-packages and no JIT cache is used.
+Run ``python -m openvino_b200.build`` to (re)build; imports trigger a build only when
+a library is missing or older than its sources.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB = PKG / "lib"
+OBJ = PKG / "build"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-unused-function", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _stale(target: Path, sources: list[Path]) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(s.stat().st_mtime > t for s in sources)
+
+
+def _run(cmd: list[str]) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout[-4000:], r.stderr[-8000:]))
+
+
+def cuda_sources() -> list[Path]:
+    return sorted((CSRC / "cuda").glob("*.cu"))
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every .cu under csrc/cuda for sm_100a and link libovb_cuda.so."""
+    LIB.mkdir(exist_ok=True)
+    OBJ.mkdir(exist_ok=True)
+    target = LIB / "libovb_cuda.so"
+    srcs = cuda_sources()
+    hdrs = sorted((CSRC / "cuda").glob("*.cuh")) + sorted((CSRC / "cuda").glob("*.h"))
+    if not force and not _stale(target, srcs + hdrs):
+        return target
+    nvcc = _nvcc()
+
+    def compile_one(src: Path) -> Path:
+        obj = OBJ / (src.stem + ".o")
+        if force or _stale(obj, [src] + hdrs):
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
+            if verbose:
+                cmd.insert(1, "-Xptxas")
+                cmd.insert(2, "-v")
+            _run(cmd)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+        objs = list(ex.map(compile_one, srcs))
+    _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-cudart", "static"])
+    return target
+
+
+def core_sources() -> list[Path]:
+    return sorted((CSRC / "core").glob("*.cpp"))
+
+
+def build_core(force: bool = False) -> Path | None:
+    """Compile the native core into a CPython extension module (pybind11)."""
+    srcs = core_sources()
+    if not srcs:
+        return None
+    import pybind11
+
+    LIB.mkdir(exist_ok=True)
+    OBJ.mkdir(exist_ok=True)
+    ext = sysconfig.get_config_var("EXT_SUFFIX")
+    target = PKG / ("_ovcore" + ext)
+    hdrs = sorted((CSRC / "core").glob("*.hpp")) + sorted((CSRC / "core").glob("*.h"))
+    if not force and not _stale(target, srcs + hdrs):
+        return target
+    cxx = os.environ.get("CXX", "g++")
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(CSRC / "core")]
+
+    def compile_one(src: Path) -> Path:
+        obj = OBJ / ("core_" + src.stem + ".o")
+        if force or _stale(obj, [src] + hdrs):
+            _run([cxx, *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(compile_one, srcs))
+    _run([cxx, "-shared", "-o", str(target), *map(str, objs), "-pthread"])
+    return target
+
+
+def build_all(force: bool = False) -> None:
+    build_cuda(force)
+    build_core(force)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv)
+    print("built:", [p.name for p in LIB.glob("*.so")] + [p.name for p in PKG.glob("_ovcore*.so")])

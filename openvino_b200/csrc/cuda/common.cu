@@ -1,0 +1,94 @@
+#include <cudaTypedefs.h>
+#include <stdarg.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ovb {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+static int* g_status[64] = {nullptr};
+static std::mutex g_status_mu;
+
+int* status_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_status_mu);
+    if (g_status[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
+        cudaMemset(p, 0, 256);
+        g_status[dev] = p;
+    }
+    return g_status[dev];
+}
+
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+static int load_encode() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || fn == nullptr) {
+        set_error("cuTensorMapEncodeTiled entry point not available: %s", cudaGetErrorString(e));
+        return ERR_TMAP;
+    }
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    return 0;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t rows,
+                 uint64_t cols, uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+    if (int rc = load_encode()) return rc;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (pitch_bytes & 15) != 0) {
+        set_error("TMA operand must be 16-byte aligned with a 16-byte multiple row pitch (base %p pitch %llu)", base,
+                  (unsigned long long)pitch_bytes);
+        return ERR_BAD_ARG;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(out, dtype, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with %d (rows %llu cols %llu pitch %llu box %ux%u elem %d)", (int)r,
+                  (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes, box_rows, box_cols,
+                  elem_bytes);
+        return ERR_TMAP;
+    }
+    return 0;
+}
+
+}  // namespace ovb
+
+extern "C" {
+
+int ovb_version(void) { return 100; }
+
+const char* ovb_last_error(void) { return ovb::g_err; }
+
+int* ovb_status_ptr(void) { return ovb::status_word(); }
+
+int ovb_status_read(ovb_stream_t stream) {
+    int* p = ovb::status_word();
+    if (!p) return -1;
+    int v = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+    if (v != 0) cudaMemsetAsync(p, 0, sizeof(int), s);
+    return v;
+}
+}

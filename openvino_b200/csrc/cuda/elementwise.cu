@@ -1,0 +1,452 @@
+// Bandwidth-bound kernels of the LLM / encoder paths: RMSNorm (+residual), LayerNorm, SwiGLU
+// gating, embedding gather, greedy sampling (argmax), RoPE fused with the paged KV-cache write,
+// int4 weight re-packing.
+//
+// Reference counterparts (OpenCL / JIT, Intel-only): rms_gpu_bfyx_opt.cl, rope_opt.cl,
+// swiglu_gpu_opt.cl, pa_kv_cache_update_ref.cl, mvn_gpu_*.cl; math as in
+// src/core/reference/include/openvino/reference/rms_norm.hpp.
+#include <math_constants.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ovb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (threadIdx.x < THREADS / 32) ? red[threadIdx.x] : 0.f;
+    if (warp == 0) {
+        t = warp_sum(t);
+        if (lane == 0) red[0] = t;
+    }
+    __syncthreads();
+    return red[0];
+}
+
+union Pack8 {
+    uint4 u;
+    __nv_bfloat16 b[8];
+    __half h[8];
+};
+
+// ------------------------------------------------------------------------------------ RMSNorm
+// One CTA per row; cols % 8 == 0. Row is kept in registers (up to 8 vectors per thread).
+template <int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+               const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ y,
+               __nv_bfloat16* __restrict__ residual_out, int cols, float eps) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int nvec = cols >> 3;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * cols);
+    const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + row * cols) : nullptr;
+    float vals[MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        if (v < nvec) {
+            Pack8 a;
+            a.u = xr[v];
+            if (rr) {
+                Pack8 b;
+                b.u = rr[v];
+                Pack8 o;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // the residual stream is stored in bf16: round before normalising, as the stored value is
+                    // what the next layer reads
+                    o.b[j] = __float2bfloat16_rn(__bfloat162float(a.b[j]) + __bfloat162float(b.b[j]));
+                    vals[i][j] = __bfloat162float(o.b[j]);
+                }
+                if (residual_out) reinterpret_cast<uint4*>(residual_out + row * cols)[v] = o.u;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) vals[i][j] = __bfloat162float(a.b[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+        }
+    }
+    const float tot = block_sum<THREADS>(ss, red);
+    const float inv = rsqrtf(tot / float(cols) + eps);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        if (v < nvec) {
+            Pack8 g, o;
+            g.u = reinterpret_cast<const uint4*>(gamma)[v];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o.b[j] = __float2bfloat16_rn(vals[i][j] * inv * __bfloat162float(g.b[j]));
+            reinterpret_cast<uint4*>(y + row * cols)[v] = o.u;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ LayerNorm
+template <class E, int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS)
+layernorm_kernel(const E* __restrict__ x, const E* __restrict__ residual, const E* __restrict__ gamma,
+                 const E* __restrict__ beta, E* __restrict__ y, int cols, float eps) {
+    __shared__ float red[32];
+    const size_t row = blockIdx.x;
+    const int nvec = cols >> 3;
+    float vals[MAXV][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        if (v < nvec) {
+            uint4 a = reinterpret_cast<const uint4*>(x + row * cols)[v];
+            const E* ae = reinterpret_cast<const E*>(&a);
+            uint4 b = make_uint4(0, 0, 0, 0);
+            if (residual) b = reinterpret_cast<const uint4*>(residual + row * cols)[v];
+            const E* be = reinterpret_cast<const E*>(&b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                vals[i][j] = float(ae[j]) + (residual ? float(be[j]) : 0.f);
+                s += vals[i][j];
+            }
+        }
+    }
+    const float mean = block_sum<THREADS>(s, red) / float(cols);
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        if (v < nvec) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float d = vals[i][j] - mean;
+                sq += d * d;
+            }
+        }
+    }
+    const float var = block_sum<THREADS>(sq, red) / float(cols);
+    const float inv = rsqrtf(var + eps);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        if (v < nvec) {
+            uint4 g = reinterpret_cast<const uint4*>(gamma)[v];
+            uint4 bt = reinterpret_cast<const uint4*>(beta)[v];
+            const E* ge = reinterpret_cast<const E*>(&g);
+            const E* bte = reinterpret_cast<const E*>(&bt);
+            uint4 o;
+            E* oe = reinterpret_cast<E*>(&o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) oe[j] = E((vals[i][j] - mean) * inv * float(ge[j]) + float(bte[j]));
+            reinterpret_cast<uint4*>(y + row * cols)[v] = o;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ SwiGLU gate
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int F) {
+    const int fv = F >> 3;
+    const size_t total = (size_t)rows * fv;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / fv;
+        const int c = int(i - r * fv);
+        Pack8 g, u, o;
+        g.u = reinterpret_cast<const uint4*>(gu + r * 2 * F)[c];
+        u.u = reinterpret_cast<const uint4*>(gu + r * 2 * F + F)[c];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float gv = __bfloat162float(g.b[j]);
+            const float s = gv / (1.0f + __expf(-gv));
+            o.b[j] = __float2bfloat16_rn(s * __bfloat162float(u.b[j]));
+        }
+        reinterpret_cast<uint4*>(out + r * F)[c] = o.u;
+    }
+}
+
+__global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                           __nv_bfloat16* __restrict__ out, size_t nvec) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+        Pack8 x, y, o;
+        x.u = reinterpret_cast<const uint4*>(a)[i];
+        y.u = reinterpret_cast<const uint4*>(b)[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.b[j] = __float2bfloat16_rn(__bfloat162float(x.b[j]) + __bfloat162float(y.b[j]));
+        reinterpret_cast<uint4*>(out)[i] = o.u;
+    }
+}
+
+// ------------------------------------------------------------------------------------ embedding
+__global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* __restrict__ table,
+                                 uint4* __restrict__ out, int rows, int vec_per_row, int vocab) {
+    const size_t total = (size_t)rows * vec_per_row;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / vec_per_row;
+        const int c = int(i - r * vec_per_row);
+        int64_t id = ids[r];
+        if (id < 0 || id >= vocab) id = 0;   // out-of-range ids read row 0 instead of faulting
+        out[i] = table[(size_t)id * vec_per_row + c];
+    }
+}
+
+// ------------------------------------------------------------------------------------ argmax
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int vocab, int64_t* __restrict__ out_ids,
+              float* __restrict__ out_max) {
+    __shared__ float sv[THREADS / 32];
+    __shared__ int si[THREADS / 32];
+    const size_t row = blockIdx.x;
+    const __nv_bfloat16* lr = logits + row * ld;
+    float best = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    const int nvec = vocab >> 3;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(lr) & 15) == 0);
+    if (aligned) {
+        for (int v = threadIdx.x; v < nvec; v += THREADS) {
+            Pack8 a;
+            a.u = reinterpret_cast<const uint4*>(lr)[v];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = __bfloat162float(a.b[j]);
+                if (f > best) { best = f; bi = v * 8 + j; }
+            }
+        }
+        for (int i = nvec * 8 + threadIdx.x; i < vocab; i += THREADS) {
+            const float f = __bfloat162float(lr[i]);
+            if (f > best) { best = f; bi = i; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < vocab; i += THREADS) {
+            const float f = __bfloat162float(lr[i]);
+            if (f > best) { best = f; bi = i; }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < THREADS / 32 ? sv[lane] : -CUDART_INF_F;
+        bi = lane < THREADS / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) {
+            out_ids[row] = bi == 0x7fffffff ? 0 : bi;
+            if (out_max) out_max[row] = best;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ RoPE + KV write
+// One CTA per token. q rotated in place; k rotated and written to the cache; v copied to the cache.
+// Cache layout [num_blocks, Hkv, block_size, D].
+__global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache,
+                                     __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D, float log2_theta,
+                                     int block_size) {
+    const int t = blockIdx.x;
+    const int half = D >> 1;
+    const float pos = float(positions[t]);
+    const int slot = slot_map[t];
+    const int blk = slot / block_size, off = slot - blk * block_size;
+    __nv_bfloat16* row = qkv + (size_t)t * (Hq + 2 * Hkv) * D;
+    const int pairs_q = Hq * half, pairs_k = Hkv * half;
+    for (int i = threadIdx.x; i < pairs_q + pairs_k; i += blockDim.x) {
+        const bool is_k = i >= pairs_q;
+        const int j = is_k ? i - pairs_q : i;
+        const int h = j / half, d = j - h * half;
+        const float inv_freq = exp2f(-log2_theta * (2.0f * float(d) / float(D)));
+        float sn, cs;
+        sincosf(pos * inv_freq, &sn, &cs);
+        __nv_bfloat16* p = row + (size_t)(is_k ? Hq + h : h) * D;
+        const float x1 = __bfloat162float(p[d]), x2 = __bfloat162float(p[d + half]);
+        const __nv_bfloat16 o1 = __float2bfloat16_rn(x1 * cs - x2 * sn);
+        const __nv_bfloat16 o2 = __float2bfloat16_rn(x2 * cs + x1 * sn);
+        if (is_k) {
+            if (slot >= 0) {
+                __nv_bfloat16* c = k_cache + (((size_t)blk * Hkv + h) * block_size + off) * D;
+                c[d] = o1;
+                c[d + half] = o2;
+            }
+        } else {
+            p[d] = o1;
+            p[d + half] = o2;
+        }
+    }
+    if (slot >= 0) {
+        const __nv_bfloat16* v = row + (size_t)(Hq + Hkv) * D;
+        for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
+            const int h = i / D, d = i - h * D;
+            v_cache[(((size_t)blk * Hkv + h) * block_size + off) * D + d] = v[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ int4 re-pack
+// IR layout: byte b of a row holds element 2b in its low nibble and 2b+1 in its high nibble.
+// Plugin layout: every aligned group of 8 elements e0..e7 becomes one u32 with nibble j (j<4) = e[2j]
+// and nibble j+4 = e[2j+1], so that one mask per shifted copy yields a pair of adjacent elements.
+__global__ void pack_u4_kernel(const uint32_t* __restrict__ w_ir, uint32_t* __restrict__ w_out, size_t nwords) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nwords; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t x = w_ir[i];   // nibble k = element k
+        uint32_t o = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            o |= ((x >> (8 * j)) & 0xF) << (4 * j);            // e[2j]   -> nibble j
+            o |= ((x >> (8 * j + 4)) & 0xF) << (4 * j + 16);   // e[2j+1] -> nibble j+4
+        }
+        w_out[i] = o;
+    }
+}
+// scales_ir [N, G] fp16 -> [G, N] bf16;  zps -> [G, N] bf16 holding bias + zp
+__global__ void pack_scale_zp_kernel(const __half* __restrict__ scales_ir, const uint8_t* __restrict__ zps_ir,
+                                     int zp_is_u8, __nv_bfloat16* __restrict__ scales_out,
+                                     __nv_bfloat16* __restrict__ zps_out, int N, int G, float zp_bias,
+                                     float zp_default) {
+    const size_t total = (size_t)N * G;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / G;
+        const int g = int(i - n * G);
+        scales_out[(size_t)g * N + n] = __float2bfloat16_rn(__half2float(scales_ir[i]));
+        float z = zp_default;
+        if (zps_ir) {
+            if (zp_is_u8) z = float(zps_ir[i]);
+            else z = float((zps_ir[i >> 1] >> ((i & 1) * 4)) & 0xF);
+        }
+        zps_out[(size_t)g * N + n] = __float2bfloat16_rn(zp_bias + z);
+    }
+}
+
+static inline int grid_for(size_t n, int threads) {
+    size_t g = (n + threads - 1) / threads;
+    if (g > 148 * 16) g = 148 * 16;
+    if (g < 1) g = 1;
+    return int(g);
+}
+
+}  // namespace ovb
+
+extern "C" {
+using namespace ovb;
+
+int ovb_rmsnorm(const void* x, const void* residual, const void* gamma, void* y, void* residual_out, int rows,
+                int cols, float eps, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(x && gamma && y && rows > 0, "ovb_rmsnorm: null operand");
+    OVB_REQUIRE(cols % 8 == 0 && cols <= 256 * 8 * 8, "ovb_rmsnorm: cols=%d must be a multiple of 8 and <= 16384", cols);
+    auto X = (const __nv_bfloat16*)x;
+    auto R = (const __nv_bfloat16*)residual;
+    auto G = (const __nv_bfloat16*)gamma;
+    auto Y = (__nv_bfloat16*)y;
+    auto RO = (__nv_bfloat16*)residual_out;
+    const int nvec = cols / 8;
+    if (nvec <= 256) rmsnorm_kernel<256, 1><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
+    else if (nvec <= 512) rmsnorm_kernel<256, 2><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
+    else if (nvec <= 1024) rmsnorm_kernel<256, 4><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
+    else rmsnorm_kernel<256, 8><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* y, int rows,
+                  int cols, float eps, int is_f16, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(x && gamma && beta && y && rows > 0, "ovb_layernorm: null operand");
+    OVB_REQUIRE(cols % 8 == 0 && cols <= 256 * 8 * 4, "ovb_layernorm: cols=%d must be a multiple of 8 and <= 8192", cols);
+    if (is_f16)
+        layernorm_kernel<__half, 256, 4><<<rows, 256, 0, stream>>>((const __half*)x, (const __half*)residual,
+                                                                  (const __half*)gamma, (const __half*)beta, (__half*)y,
+                                                                  cols, eps);
+    else
+        layernorm_kernel<__nv_bfloat16, 256, 4><<<rows, 256, 0, stream>>>(
+            (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)gamma,
+            (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, cols, eps);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(gu && out && rows > 0 && F % 8 == 0, "ovb_silu_mul: bad arguments");
+    const size_t total = (size_t)rows * (F / 8);
+    silu_mul_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(a && b && out && n % 8 == 0, "ovb_add: n must be a multiple of 8");
+    add_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                         (__nv_bfloat16*)out, (size_t)n / 8);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_embedding(const int64_t* ids, const void* table, void* out, int rows, int cols, int vocab,
+                  ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(ids && table && out && rows > 0 && cols % 8 == 0, "ovb_embedding: bad arguments");
+    const size_t total = (size_t)rows * (cols / 8);
+    embedding_kernel<<<grid_for(total, 256), 256, 0, stream>>>(ids, (const uint4*)table, (uint4*)out, rows, cols / 8,
+                                                               vocab);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_argmax(const void* logits, int ld, int rows, int vocab, int64_t* out_ids, float* out_max,
+               ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0, "ovb_argmax: bad arguments");
+    argmax_kernel<1024><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, out_ids, out_max);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void* k_cache, void* v_cache, int T,
+                      int Hq, int Hkv, int D, float theta, int block_size, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(qkv && positions && slot_map && k_cache && v_cache && T > 0, "ovb_rope_kv_write: null operand");
+    OVB_REQUIRE(D % 2 == 0, "ovb_rope_kv_write: head size must be even");
+    rope_kv_write_kernel<<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
+                                                (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int zp_is_u8, void* w_out,
+                void* scales_out, void* zps_out, int N, int K, int group_size, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(w_ir && scales_ir && w_out && scales_out && zps_out, "ovb_pack_u4: null operand");
+    OVB_REQUIRE(K % 8 == 0 && group_size > 0 && K % group_size == 0, "ovb_pack_u4: bad K/group_size");
+    const size_t nwords = (size_t)N * K / 8;
+    pack_u4_kernel<<<grid_for(nwords, 256), 256, 0, stream>>>((const uint32_t*)w_ir, (uint32_t*)w_out, nwords);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    const int G = K / group_size;
+    pack_scale_zp_kernel<<<grid_for((size_t)N * G, 256), 256, 0, stream>>>(
+        (const __half*)scales_ir, (const uint8_t*)zps_ir, zp_is_u8, (__nv_bfloat16*)scales_out, (__nv_bfloat16*)zps_out,
+        N, G, 16.0f, 8.0f);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // extern "C"

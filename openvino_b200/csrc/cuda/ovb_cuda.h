@@ -1,0 +1,148 @@
+// C ABI of the sm_100a kernel library (libovb_cuda.so). Every entry point takes raw device
+// pointers plus a CUDA stream and returns 0 on success or a negative error code; device-side
+// problems (a wait that ran out, a failed argument check) are reported through the status
+// word returned by ovb_status_ptr()/ovb_status_read().
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* ovb_stream_t;
+
+// ---------------------------------------------------------------------------------------------
+// Library / device
+int ovb_version(void);
+// Device status word of the current device (allocated on first use, 4 bytes of device memory).
+int* ovb_status_ptr(void);
+// Copy the status word to the host (synchronises the stream) and reset it to 0.
+int ovb_status_read(ovb_stream_t stream);
+const char* ovb_last_error(void);
+
+// ---------------------------------------------------------------------------------------------
+// GEMM family:  out[T, N] = epilogue( X[T, K] * dequant(W[N, K])^T )
+// Weights sit on the 128-row M side of tcgen05.mma (weight-stationary "swap-AB"), tokens on
+// the N side, so the same kernel serves decode (T <= 64) and prefill (T in the thousands).
+enum {
+    OVB_W_BF16 = 0,   // W is bf16 [N, K]
+    OVB_W_U4 = 1,     // W is packed u4 in the plugin layout made by ovb_pack_u4 (N x K/2 bytes)
+    OVB_W_U8 = 2,     // W is u8 [N, K]
+    OVB_W_F16 = 3,    // W and X are fp16 (BERT path)
+};
+enum {
+    OVB_ACT_NONE = 0,
+    OVB_ACT_GELU_ERF = 1,
+    OVB_ACT_RELU = 2,
+    OVB_ACT_SILU = 3,
+    OVB_ACT_SWIGLU = 4,   // dual GEMM: rows [0,N) of W are "gate", rows [N,2N) are "up"; out = silu(g)*u
+    OVB_ACT_GELU_TANH = 5,
+};
+
+typedef struct {
+    const void* x;        // [T, K] bf16/fp16, row pitch ldx elements
+    const void* w;        // see OVB_W_*
+    void* out;            // [T, N] bf16/fp16 (or fp32 when out_f32), row pitch ldo elements
+    const void* bias;     // [N] same type as x, or NULL
+    const void* residual; // [T, N] same type as out (16-bit only), row pitch ldr, or NULL
+    const void* scales;   // u4/u8: [K/group, N] bf16 (transposed, plugin layout)
+    const void* zps;      // u4: [K/group, N] bf16 holding 16+zp;  u8: [K/group, N] bf16 holding zp
+    float* ws;            // split-K workspace (fp32), may be NULL when splits == 1
+    int* counters;        // split-K tile counters (zero-initialised, self-resetting), may be NULL
+    int64_t ws_bytes;     // capacity of ws
+    int T, N, K;
+    int ldx, ldo, ldr;
+    int group_size;       // quantisation group along K (multiple of 64)
+    int wmode;            // OVB_W_*
+    int act;              // OVB_ACT_*
+    int out_f32;          // 1: fp32 output
+    int splits;           // 0 = choose automatically
+    int block_t;          // 0 = choose automatically (16/32/64/128/256)
+    // Tensor-parallel fused all-reduce epilogue (0 ranks = off): see ovb_comm_* below.
+    void* comm;           // communicator handle or NULL
+} ovb_gemm_args;
+
+int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream);
+// Bytes of split-K workspace / number of counters that ovb_gemm may need for the given problem.
+int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act);
+int ovb_gemm_num_counters(void);
+
+// Re-pack IR-layout u4 weights (LSB-first nibbles, [N, K]) into the plugin layout read by the
+// dequantising GEMM, and build transposed bf16 scale / biased zero-point tables.
+//   w_ir    : [N, K/2] bytes         scales_ir: [N, G] fp16     zps_ir: [N, G/2..] packed u4 or NULL (zp = 8)
+int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int zp_is_u8, void* w_out,
+                void* scales_out, void* zps_out, int N, int K, int group_size, ovb_stream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Normalisation / elementwise
+// y = rmsnorm(x (+ residual)) * gamma ;  if residual_out != NULL it receives x + residual.
+int ovb_rmsnorm(const void* x, const void* residual, const void* gamma, void* y, void* residual_out, int rows,
+                int cols, float eps, ovb_stream_t stream);
+int ovb_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* y, int rows,
+                  int cols, float eps, int is_f16, ovb_stream_t stream);
+// out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
+int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
+int ovb_embedding(const int64_t* ids, const void* table, void* out, int rows, int cols, int vocab,
+                  ovb_stream_t stream);
+// Greedy sampling: out_ids[r] = argmax_v logits[r, v] (first index on ties); optional out_max.
+int ovb_argmax(const void* logits, int ld, int rows, int vocab, int64_t* out_ids, float* out_max,
+               ovb_stream_t stream);
+int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream);
+
+// RoPE (half-rotate, LLaMA style) applied in place to q and k inside a fused qkv buffer, then
+// k/v rows are scattered into the paged cache.
+//   qkv       : [T, (Hq + 2*Hkv) * D] bf16
+//   positions : [T] int32 absolute position of each token
+//   slot_map  : [T] int32 physical slot (block * block_size + offset) of each token
+//   k_cache/v_cache : [num_blocks, block_size, Hkv, D] bf16
+int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void* k_cache, void* v_cache, int T,
+                      int Hq, int Hkv, int D, float theta, int block_size, ovb_stream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Paged attention. Cache layout [num_blocks, block_size, Hkv, D]; ragged batch described like the
+// PagedAttentionExtension op: past_lens[B], subsequence_begins[B+1], block_indices[...],
+// block_indices_begins[B+1].
+typedef struct {
+    const void* q;            // [T, Hq*D] (row pitch ldq elements)
+    void* out;                // [T, Hq*D] contiguous
+    const void* k_cache;
+    const void* v_cache;
+    const int* past_lens;
+    const int* subsequence_begins;
+    const int* block_indices;
+    const int* block_indices_begins;
+    float* scratch;           // decode split-KV partials (see ovb_pa_scratch_bytes) or NULL
+    int B, T, Hq, Hkv, D;
+    int ldq;
+    int block_size;
+    int max_context_len;
+    int max_q_len;            // longest subsequence in the batch (1 = pure decode)
+    int sliding_window;       // 0 = off
+    float scale;
+} ovb_pa_args;
+int ovb_paged_attention(const ovb_pa_args* a, ovb_stream_t stream);
+int64_t ovb_pa_scratch_bytes(int B, int Hq, int D, int max_context_len);
+
+// Dense (non-paged) bidirectional attention for encoder models: q,k,v [B, S, H, D] fp16/bf16.
+int ovb_sdpa_dense(const void* q, const void* k, const void* v, void* out, int B, int S, int H, int D, int ld,
+                   float scale, int is_f16, int causal, ovb_stream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel communicator over NVLink peer memory (one process per GPU; buffers exchanged
+// as CUDA IPC handles by the Python side).
+typedef struct {
+    int rank, world;
+    void* peer_buf[8];     // staging buffer of every rank (this rank's own included), same size each
+    int* peer_flags[8];    // flag words of every rank
+    int64_t buf_bytes;
+    int64_t nflags;
+    int epoch;             // bumped by every collective call (host side)
+} ovb_comm;
+
+// In-place all-reduce of a bf16 tensor [rows, cols] held in `data` on every rank.
+int ovb_allreduce_bf16(ovb_comm* c, void* data, int64_t n, ovb_stream_t stream);
+// Fused: out = rmsnorm(allreduce(x) + residual) etc. is done by the GEMM epilogue; see ovb_gemm.comm.
+
+#ifdef __cplusplus
+}
+#endif

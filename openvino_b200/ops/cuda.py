@@ -1,0 +1,312 @@
+"""ctypes front-end of ``libovb_cuda.so`` (the hand-written sm_100a kernel library).
+
+Tensors are ``torch.Tensor`` objects used as typed device buffers: torch supplies the
+allocator and the CUDA stream, every computation below runs in this repository's own kernels.
+There is no eager/PyTorch fallback: if the library cannot be loaded, calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+import os
+import threading
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_PKG = Path(__file__).resolve().parent.parent
+_LIB_PATH = _PKG / "lib" / "libovb_cuda.so"
+
+W_BF16, W_U4, W_U8, W_F16 = 0, 1, 2, 3
+ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_SWIGLU, ACT_GELU_TANH = 0, 1, 2, 3, 4, 5
+
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument seen on device",
+                4: "local flag wait timed out"}
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("out", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p),
+        ("scales", C.c_void_p), ("zps", C.c_void_p), ("ws", C.c_void_p), ("counters", C.c_void_p),
+        ("ws_bytes", C.c_int64),
+        ("T", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("ldx", C.c_int), ("ldo", C.c_int), ("ldr", C.c_int),
+        ("group_size", C.c_int), ("wmode", C.c_int), ("act", C.c_int), ("out_f32", C.c_int),
+        ("splits", C.c_int), ("block_t", C.c_int),
+        ("comm", C.c_void_p),
+    ]
+
+
+class PaArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("out", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("past_lens", C.c_void_p), ("subsequence_begins", C.c_void_p), ("block_indices", C.c_void_p),
+        ("block_indices_begins", C.c_void_p), ("scratch", C.c_void_p),
+        ("B", C.c_int), ("T", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("D", C.c_int),
+        ("ldq", C.c_int), ("block_size", C.c_int), ("max_context_len", C.c_int), ("max_q_len", C.c_int),
+        ("sliding_window", C.c_int), ("scale", C.c_float),
+    ]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+def lib():
+    """Load (building first if the sources are newer) and return the kernel library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not _LIB_PATH.exists() or os.environ.get("OVB_REBUILD") == "1":
+            from .. import build as _build
+            _build.build_cuda()
+        if not _LIB_PATH.exists():
+            raise KernelLibraryError("libovb_cuda.so is missing and could not be built: %s" % _LIB_PATH)
+        l = C.CDLL(str(_LIB_PATH))
+        l.ovb_last_error.restype = C.c_char_p
+        l.ovb_status_ptr.restype = C.c_void_p
+        l.ovb_gemm_ws_bytes.restype = C.c_int64
+        l.ovb_pa_scratch_bytes.restype = C.c_int64
+        l.ovb_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+        l.ovb_paged_attention.argtypes = [C.POINTER(PaArgs), C.c_void_p]
+        l.ovb_status_read.argtypes = [C.c_void_p]
+        _lib = l
+    return _lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelLibraryError("%s failed (%d): %s" % (what, rc, lib().ovb_last_error().decode()))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def read_status() -> int:
+    """Device status word: 0 = ok. Synchronises the current stream and clears the word."""
+    return int(lib().ovb_status_read(C.c_void_p(_stream())))
+
+
+def check_status(what: str = "kernel") -> None:
+    s = read_status()
+    if s != 0:
+        raise KernelLibraryError("%s reported device status %d (%s)" % (what, s, STATUS_NAMES.get(s, "?")))
+
+
+# ------------------------------------------------------------------------------------------ workspace
+class Workspace:
+    """Scratch memory shared by the kernels of one device/stream: split-K partials + counters,
+    decode-attention split-KV partials. Allocated once, reused by every call (calls that overlap on
+    the GPU must use different workspaces)."""
+
+    def __init__(self, device, gemm_bytes: int = 64 << 20, pa_bytes: int = 64 << 20):
+        self.device = device
+        self.gemm_ws = torch.empty(gemm_bytes // 4, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(int(lib().ovb_gemm_num_counters()), dtype=torch.int32, device=device)
+        self.pa_scratch = torch.empty(pa_bytes // 4, dtype=torch.float32, device=device)
+
+
+_default_ws: dict = {}
+
+
+def default_workspace(device) -> Workspace:
+    key = torch.device(device).index or 0
+    if key not in _default_ws:
+        _default_ws[key] = Workspace(torch.device("cuda", key))
+    return _default_ws[key]
+
+
+# ------------------------------------------------------------------------------------------ weights
+class PackedWeight:
+    """A FullyConnected weight in the layout the GEMM kernel reads.
+
+    mode W_BF16/W_F16: ``w`` is [N, K] 16-bit.  mode W_U4: ``w`` is the re-packed nibble stream
+    [N, K/2] u8, ``scales``/``zps`` are [K/group, N] bf16 (zps hold 16 + zero_point).
+    mode W_U8: ``w`` [N, K] u8, ``zps`` hold the zero point itself.
+    """
+
+    def __init__(self, mode, w, N, K, scales=None, zps=None, group_size=0, bias=None):
+        self.mode, self.w, self.N, self.K = mode, w, N, K
+        self.scales, self.zps, self.group_size, self.bias = scales, zps, group_size, bias
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, bias=None) -> "PackedWeight":
+        assert w.dim() == 2 and w.dtype in (torch.bfloat16, torch.float16)
+        mode = W_BF16 if w.dtype == torch.bfloat16 else W_F16
+        return PackedWeight(mode, w.contiguous(), w.shape[0], w.shape[1], bias=bias)
+
+    @staticmethod
+    def from_ir_u4(w_ir: torch.Tensor, scales_ir: torch.Tensor, zps_ir: Optional[torch.Tensor], N: int, K: int,
+                   group_size: int, zp_is_u8: bool = False, bias=None) -> "PackedWeight":
+        """w_ir: uint8 [N*K/2] LSB-first nibbles (IR layout); scales_ir fp16 [N, G]; zps_ir packed u4 [N*G/2]
+        (or uint8 [N, G] when zp_is_u8) or None for the symmetric i4-style offset 8."""
+        dev = w_ir.device
+        G = K // group_size
+        w_out = torch.empty(N * K // 2, dtype=torch.uint8, device=dev)
+        s_out = torch.empty(G * N, dtype=torch.bfloat16, device=dev)
+        z_out = torch.empty(G * N, dtype=torch.bfloat16, device=dev)
+        rc = lib().ovb_pack_u4(C.c_void_p(w_ir.data_ptr()), C.c_void_p(scales_ir.data_ptr()),
+                               C.c_void_p(_ptr(zps_ir)), C.c_int(1 if zp_is_u8 else 0), C.c_void_p(w_out.data_ptr()),
+                               C.c_void_p(s_out.data_ptr()), C.c_void_p(z_out.data_ptr()), C.c_int(N), C.c_int(K),
+                               C.c_int(group_size), C.c_void_p(_stream()))
+        _check(rc, "ovb_pack_u4")
+        return PackedWeight(W_U4, w_out, N, K, s_out, z_out, group_size, bias)
+
+    @staticmethod
+    def from_ir_u8(w_ir: torch.Tensor, scales_ir: torch.Tensor, zps_ir: Optional[torch.Tensor], N: int, K: int,
+                   group_size: int, bias=None) -> "PackedWeight":
+        G = K // group_size
+        s = scales_ir.reshape(N, G).float().t().contiguous().to(torch.bfloat16)
+        if zps_ir is None:
+            z = torch.full((G, N), 128.0, dtype=torch.bfloat16, device=w_ir.device)
+        else:
+            z = zps_ir.reshape(N, G).float().t().contiguous().to(torch.bfloat16)
+        return PackedWeight(W_U8, w_ir.contiguous(), N, K, s.reshape(-1), z.reshape(-1), group_size, bias)
+
+
+# ------------------------------------------------------------------------------------------ ops
+def gemm(x: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+         act: int = ACT_NONE, out_f32: bool = False, ws: Optional[Workspace] = None, splits: int = 0,
+         block_t: int = 0) -> torch.Tensor:
+    """out[T, N] = act(x[T, K] @ dequant(W)^T + bias) + residual  on the tcgen05 GEMM."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    T, K = x.shape
+    assert K == w.K, (K, w.K)
+    if out is None:
+        out = torch.empty((T, w.N), dtype=torch.float32 if out_f32 else x.dtype, device=x.device)
+    if ws is None:
+        ws = default_workspace(x.device)
+    a = GemmArgs()
+    a.x, a.w, a.out = x.data_ptr(), w.w.data_ptr(), out.data_ptr()
+    a.bias = _ptr(w.bias)
+    a.residual = _ptr(residual)
+    a.scales, a.zps = _ptr(w.scales), _ptr(w.zps)
+    a.ws, a.counters, a.ws_bytes = ws.gemm_ws.data_ptr(), ws.counters.data_ptr(), ws.gemm_ws.numel() * 4
+    a.T, a.N, a.K = T, w.N, K
+    a.ldx, a.ldo = x.stride(0), out.stride(0)
+    a.ldr = residual.stride(0) if residual is not None else 0
+    a.group_size = w.group_size
+    a.wmode, a.act, a.out_f32 = w.mode, act, 1 if out_f32 else 0
+    a.splits, a.block_t = splits, block_t
+    a.comm = None
+    _check(lib().ovb_gemm(C.byref(a), C.c_void_p(_stream())), "ovb_gemm")
+    return out
+
+
+def rmsnorm(x, gamma, eps, residual=None, out=None, residual_out=None):
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _check(lib().ovb_rmsnorm(C.c_void_p(x.data_ptr()), C.c_void_p(_ptr(residual)), C.c_void_p(gamma.data_ptr()),
+                             C.c_void_p(out.data_ptr()), C.c_void_p(_ptr(residual_out)), C.c_int(rows), C.c_int(cols),
+                             C.c_float(eps), C.c_void_p(_stream())), "ovb_rmsnorm")
+    return out
+
+
+def layernorm(x, gamma, beta, eps, residual=None, out=None):
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _check(lib().ovb_layernorm(C.c_void_p(x.data_ptr()), C.c_void_p(_ptr(residual)), C.c_void_p(gamma.data_ptr()),
+                               C.c_void_p(beta.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(rows), C.c_int(cols),
+                               C.c_float(eps), C.c_int(1 if x.dtype == torch.float16 else 0), C.c_void_p(_stream())),
+           "ovb_layernorm")
+    return out
+
+
+def silu_mul(gu, out=None):
+    rows, F2 = gu.shape
+    F = F2 // 2
+    if out is None:
+        out = torch.empty((rows, F), dtype=gu.dtype, device=gu.device)
+    _check(lib().ovb_silu_mul(C.c_void_p(gu.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(rows), C.c_int(F),
+                              C.c_void_p(_stream())), "ovb_silu_mul")
+    return out
+
+
+def add(a, b, out=None):
+    if out is None:
+        out = torch.empty_like(a)
+    _check(lib().ovb_add(C.c_void_p(a.data_ptr()), C.c_void_p(b.data_ptr()), C.c_void_p(out.data_ptr()),
+                         C.c_int64(a.numel()), C.c_void_p(_stream())), "ovb_add")
+    return out
+
+
+def embedding(ids, table, out=None):
+    rows = ids.numel()
+    vocab, cols = table.shape
+    if out is None:
+        out = torch.empty((rows, cols), dtype=table.dtype, device=table.device)
+    _check(lib().ovb_embedding(C.c_void_p(ids.data_ptr()), C.c_void_p(table.data_ptr()), C.c_void_p(out.data_ptr()),
+                               C.c_int(rows), C.c_int(cols), C.c_int(vocab), C.c_void_p(_stream())), "ovb_embedding")
+    return out
+
+
+def argmax(logits, out=None, out_max=None):
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _check(lib().ovb_argmax(C.c_void_p(logits.data_ptr()), C.c_int(logits.stride(0)), C.c_int(rows), C.c_int(vocab),
+                            C.c_void_p(out.data_ptr()), C.c_void_p(_ptr(out_max)), C.c_void_p(_stream())), "ovb_argmax")
+    return out
+
+
+def rope_kv_write(qkv, positions, slot_map, k_cache, v_cache, Hq, Hkv, D, theta, block_size):
+    T = qkv.shape[0]
+    _check(lib().ovb_rope_kv_write(C.c_void_p(qkv.data_ptr()), C.c_void_p(positions.data_ptr()),
+                                   C.c_void_p(slot_map.data_ptr()), C.c_void_p(k_cache.data_ptr()),
+                                   C.c_void_p(v_cache.data_ptr()), C.c_int(T), C.c_int(Hq), C.c_int(Hkv), C.c_int(D),
+                                   C.c_float(theta), C.c_int(block_size), C.c_void_p(_stream())), "ovb_rope_kv_write")
+
+
+def paged_attention(q, k_cache, v_cache, past_lens, subsequence_begins, block_indices, block_indices_begins, Hq, Hkv, D,
+                    scale=None, max_context_len=0, max_q_len=0, sliding_window=0, block_size=16, out=None, ws=None):
+    """q: [T, >=Hq*D] (row pitch = q.stride(0)); caches [num_blocks, Hkv, block_size, D]."""
+    T = q.shape[0]
+    B = past_lens.numel()
+    if out is None:
+        out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+    if ws is None:
+        ws = default_workspace(q.device)
+    a = PaArgs()
+    a.q, a.out, a.k_cache, a.v_cache = q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    a.past_lens, a.subsequence_begins = past_lens.data_ptr(), subsequence_begins.data_ptr()
+    a.block_indices, a.block_indices_begins = block_indices.data_ptr(), block_indices_begins.data_ptr()
+    need = int(lib().ovb_pa_scratch_bytes(C.c_int(B), C.c_int(Hq), C.c_int(D), C.c_int(max_context_len)))
+    a.scratch = ws.pa_scratch.data_ptr() if need <= ws.pa_scratch.numel() * 4 else None
+    a.B, a.T, a.Hq, a.Hkv, a.D = B, T, Hq, Hkv, D
+    a.ldq = q.stride(0)
+    a.block_size, a.max_context_len, a.max_q_len = block_size, max_context_len, max_q_len
+    a.sliding_window = sliding_window
+    a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    _check(lib().ovb_paged_attention(C.byref(a), C.c_void_p(_stream())), "ovb_paged_attention")
+    return out
+
+
+def sdpa_dense(q, k, v, B, S, H, D, ld, scale=None, causal=False, out=None):
+    """q/k/v: views into [B*S, ld] buffers (head h at column h*D); out [B*S, H*D]."""
+    if out is None:
+        out = torch.empty((B * S, H * D), dtype=q.dtype, device=q.device)
+    sc = scale if scale is not None else 1.0 / math.sqrt(D)
+    _check(lib().ovb_sdpa_dense(C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()), C.c_void_p(v.data_ptr()),
+                                C.c_void_p(out.data_ptr()), C.c_int(B), C.c_int(S), C.c_int(H), C.c_int(D), C.c_int(ld),
+                                C.c_float(sc), C.c_int(1 if q.dtype == torch.float16 else 0), C.c_int(1 if causal else 0),
+                                C.c_void_p(_stream())), "ovb_sdpa_dense")
+    return out

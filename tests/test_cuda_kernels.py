@@ -1,0 +1,271 @@
+"""Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from openvino_b200.ops import cuda as k
+    k.lib()
+    return k
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (16, 256, 256), (64, 4096, 4096), (100, 384, 1024), (300, 512, 448),
+                                   (2048, 1024, 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_dense(ops, T, N, K, dtype):
+    torch.manual_seed(0)
+    x = torch.randn(T, K, device="cuda", dtype=dtype)
+    w = (torch.randn(N, K, device="cuda") * 0.05).to(dtype)
+    bias = torch.randn(N, device="cuda").to(dtype)
+    res = torch.randn(T, N, device="cuda").to(dtype)
+    pw = ops.PackedWeight.from_dense(w, bias)
+    y = ops.gemm(x, pw, residual=res)
+    ops.check_status("gemm")
+    ref = x.float() @ w.float().t() + bias.float() + res.float()
+    assert _rel_err(y, ref) < 1e-2
+    # activation epilogue, fp32 output
+    y2 = ops.gemm(x, ops.PackedWeight.from_dense(w), act=ops.ACT_GELU_ERF, out_f32=True)
+    ref2 = torch.nn.functional.gelu(x.float() @ w.float().t())
+    assert _rel_err(y2, ref2) < 1e-2
+    ops.check_status("gemm")
+
+
+@pytest.mark.parametrize("T,N,K,splits", [(4, 256, 512, 1), (64, 512, 4096, 4), (64, 4096, 14336, 0), (33, 384, 1024, 8),
+                                          (512, 1024, 1024, 1), (1000, 256, 2048, 1)])
+def test_gemm_u4(ops, T, N, K, splits):
+    from openvino_b200.utils import quant
+    torch.manual_seed(1)
+    gs = 128
+    w = torch.randn(N, K, device="cuda") * 0.05
+    q, s, z = quant.quantize_u4_asym(w, gs)
+    wdq = quant.dequantize_u4(q, s, z, gs)
+    pw = ops.PackedWeight.from_ir_u4(quant.pack_u4(q), s, quant.pack_u4(z), N, K, gs)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    y = ops.gemm(x, pw, splits=splits)
+    ops.check_status("gemm_u4")
+    ref = x.float() @ wdq.t()
+    assert _rel_err(y, ref) < 1.5e-2
+    # run twice: identical bits (split-K reduction order is fixed)
+    y2 = ops.gemm(x, pw, splits=splits)
+    assert torch.equal(y, y2)
+
+
+def test_gemm_u8(ops):
+    from openvino_b200.utils import quant
+    torch.manual_seed(2)
+    T, N, K, gs = 48, 256, 1024, 128
+    w = torch.randn(N, K, device="cuda") * 0.05
+    q, s, z = quant.quantize_u8_asym(w, gs)
+    wdq = ((q.float().reshape(N, K // gs, gs) - z.float().unsqueeze(-1)) * s.float().unsqueeze(-1)).reshape(N, K)
+    pw = ops.PackedWeight.from_ir_u8(q, s, z, N, K, gs)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    y = ops.gemm(x, pw)
+    ops.check_status("gemm_u8")
+    assert _rel_err(y, x.float() @ wdq.t()) < 1.5e-2
+
+
+@pytest.mark.parametrize("rows,cols", [(3, 128), (64, 4096), (17, 8192), (5, 14336)])
+def test_rmsnorm(ops, rows, cols):
+    torch.manual_seed(3)
+    x = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(rows, cols, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(cols, device="cuda", dtype=torch.bfloat16)
+    y = ops.rmsnorm(x, g, 1e-5)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()
+    assert _rel_err(y, ref) < 5e-3
+    ro = torch.empty_like(x)
+    y2 = ops.rmsnorm(x, g, 1e-5, residual=r, residual_out=ro)
+    h = (x.float() + r.float()).to(torch.bfloat16).float()
+    ref2 = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()
+    assert _rel_err(y2, ref2) < 5e-3
+    assert _rel_err(ro, h) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_layernorm(ops, dtype):
+    torch.manual_seed(4)
+    x = torch.randn(33, 1024, device="cuda", dtype=dtype)
+    r = torch.randn(33, 1024, device="cuda", dtype=dtype)
+    g = torch.randn(1024, device="cuda", dtype=dtype)
+    b = torch.randn(1024, device="cuda", dtype=dtype)
+    y = ops.layernorm(x, g, b, 1e-12, residual=r)
+    ref = torch.nn.functional.layer_norm(x.float() + r.float(), (1024,), g.float(), b.float(), 1e-12)
+    assert _rel_err(y, ref) < 5e-3
+
+
+def test_silu_mul_embedding_argmax_add(ops):
+    torch.manual_seed(5)
+    gu = torch.randn(37, 2 * 1024, device="cuda", dtype=torch.bfloat16)
+    y = ops.silu_mul(gu)
+    ref = torch.nn.functional.silu(gu[:, :1024].float()) * gu[:, 1024:].float()
+    assert _rel_err(y, ref) < 5e-3
+    table = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 1000, (77,), device="cuda")
+    assert torch.equal(ops.embedding(ids, table), table[ids])
+    logits = torch.randn(9, 128256, device="cuda", dtype=torch.bfloat16)
+    am = ops.argmax(logits)
+    ref_max = logits.float().max(dim=-1).values
+    assert torch.equal(logits.float().gather(1, am[:, None])[:, 0], ref_max)
+    # first index on ties
+    logits[:, 5] = 100.0
+    logits[:, 77] = 100.0
+    assert torch.equal(ops.argmax(logits), torch.full((9,), 5, device="cuda"))
+    a = torch.randn(64, 512, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(64, 512, device="cuda", dtype=torch.bfloat16)
+    assert _rel_err(ops.add(a, b), a.float() + b.float()) < 5e-3
+
+
+def _rope_ref(x, pos, theta):
+    # x [T, H, D] float; half-rotate (LLaMA) convention
+    T, H, D = x.shape
+    inv = theta ** (-torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D)
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2 = x[..., : D // 2], x[..., D // 2:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+def _make_paged_batch(q_lens, past_lens, block_size, device, shuffle=True):
+    """Block tables for a ragged batch; returns descriptors and total block count."""
+    B = len(q_lens)
+    nblocks = [(p + q + block_size - 1) // block_size for p, q in zip(past_lens, q_lens)]
+    total = sum(nblocks)
+    perm = torch.randperm(total) if shuffle else torch.arange(total)
+    block_indices = perm.to(torch.int32)
+    bib = [0]
+    for n in nblocks:
+        bib.append(bib[-1] + n)
+    sb = [0]
+    for q in q_lens:
+        sb.append(sb[-1] + q)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    return to(past_lens), to(sb), block_indices.to(device), to(bib), total
+
+
+def _attn_ref(q, k_all, v_all, q_lens, past_lens, Hq, Hkv, D, scale, window=0):
+    """q [T, Hq, D] fp32; k_all/v_all: list per sequence of [ctx, Hkv, D] fp32."""
+    outs = []
+    t = 0
+    G = Hq // Hkv
+    for b, (ql, pl) in enumerate(zip(q_lens, past_lens)):
+        qb = q[t:t + ql]                                  # [ql, Hq, D]
+        kb = k_all[b].repeat_interleave(G, dim=1)         # [ctx, Hq, D]
+        vb = v_all[b].repeat_interleave(G, dim=1)
+        s = torch.einsum("qhd,khd->hqk", qb, kb) * scale
+        ctx = pl + ql
+        qpos = pl + torch.arange(ql, device=q.device)
+        kpos = torch.arange(ctx, device=q.device)
+        mask = kpos[None, :] <= qpos[:, None]
+        if window > 0:
+            mask &= kpos[None, :] > (qpos[:, None] - window)
+        s = s.masked_fill(~mask[None], float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        outs.append(torch.einsum("hqk,khd->qhd", p, vb))
+        t += ql
+    return torch.cat(outs, dim=0)
+
+
+@pytest.mark.parametrize("q_lens,past_lens,Hq,Hkv", [
+    ([5], [0], 4, 1),
+    ([40, 17, 128], [0, 3, 70], 8, 2),
+    ([1, 1, 1, 1], [0, 15, 16, 300], 8, 2),            # decode
+    ([1] * 7, [5, 1000, 77, 256, 31, 32, 511], 32, 8),  # decode, GQA 4
+    ([200, 1], [56, 9], 32, 8),                         # mixed
+])
+def test_rope_kv_write_and_paged_attention(ops, q_lens, past_lens, Hq, Hkv):
+    torch.manual_seed(6)
+    D, bs, theta = 128, 16, 500000.0
+    dev = "cuda"
+    pl_t, sb_t, bi_t, bib_t, total_blocks = _make_paged_batch(q_lens, past_lens, bs, dev)
+    T = sum(q_lens)
+    k_cache = torch.zeros(total_blocks, Hkv, bs, D, device=dev, dtype=torch.bfloat16)
+    v_cache = torch.zeros_like(k_cache)
+    # history: fill the cache with past tokens through the same write kernel
+    k_hist, v_hist = [], []
+    for b, pl in enumerate(past_lens):
+        kh = torch.randn(pl, Hkv, D, device=dev).to(torch.bfloat16)
+        vh = torch.randn(pl, Hkv, D, device=dev).to(torch.bfloat16)
+        k_hist.append(kh)
+        v_hist.append(vh)
+        blocks = bi_t[bib_t[b]:bib_t[b + 1]].long()
+        for j in range(pl):
+            k_cache[blocks[j // bs], :, j % bs] = kh[j]
+            v_cache[blocks[j // bs], :, j % bs] = vh[j]
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev).to(torch.bfloat16)
+    positions, slots = [], []
+    for b, (ql, pl) in enumerate(zip(q_lens, past_lens)):
+        blocks = bi_t[bib_t[b]:bib_t[b + 1]].long().tolist()
+        for j in range(pl, pl + ql):
+            positions.append(j)
+            slots.append(blocks[j // bs] * bs + j % bs)
+    positions = torch.tensor(positions, dtype=torch.int32, device=dev)
+    slots = torch.tensor(slots, dtype=torch.int32, device=dev)
+    qkv0 = qkv.clone()
+    ops.rope_kv_write(qkv, positions, slots, k_cache, v_cache, Hq, Hkv, D, theta, bs)
+    q_ref = _rope_ref(qkv0[:, : Hq * D].float().reshape(T, Hq, D), positions, theta)
+    k_new = _rope_ref(qkv0[:, Hq * D:(Hq + Hkv) * D].float().reshape(T, Hkv, D), positions, theta)
+    v_new = qkv0[:, (Hq + Hkv) * D:].float().reshape(T, Hkv, D)
+    assert _rel_err(qkv[:, : Hq * D].reshape(T, Hq, D), q_ref) < 5e-3
+    # gather cache rows of the new tokens
+    kc = k_cache.permute(0, 2, 1, 3).reshape(-1, Hkv, D)[slots.long()]
+    vc = v_cache.permute(0, 2, 1, 3).reshape(-1, Hkv, D)[slots.long()]
+    assert _rel_err(kc, k_new) < 5e-3
+    assert torch.equal(vc.float(), v_new)
+
+    scale = 1.0 / math.sqrt(D)
+    out = ops.paged_attention(qkv, k_cache, v_cache, pl_t, sb_t, bi_t, bib_t, Hq, Hkv, D, scale=scale,
+                              max_context_len=max(p + q for p, q in zip(past_lens, q_lens)), max_q_len=max(q_lens))
+    ops.check_status("paged_attention")
+    k_all, v_all = [], []
+    t = 0
+    for b, ql in enumerate(q_lens):
+        k_all.append(torch.cat([k_hist[b].float(), kc[t:t + ql].float()], dim=0))
+        v_all.append(torch.cat([v_hist[b].float(), vc[t:t + ql].float()], dim=0))
+        t += ql
+    ref = _attn_ref(qkv[:, : Hq * D].float().reshape(T, Hq, D), k_all, v_all, q_lens, past_lens, Hq, Hkv, D, scale)
+    assert _rel_err(out.reshape(T, Hq, D), ref) < 1e-2
+
+
+def test_paged_attention_sliding_window(ops):
+    torch.manual_seed(7)
+    Hq, Hkv, D, bs = 8, 2, 128, 16
+    for q_lens, past_lens in ([[90], [40]], [[1, 1], [200, 37]]):
+        pl_t, sb_t, bi_t, bib_t, total_blocks = _make_paged_batch(q_lens, past_lens, bs, "cuda")
+        T = sum(q_lens)
+        k_cache = torch.randn(total_blocks, Hkv, bs, D, device="cuda").to(torch.bfloat16)
+        v_cache = torch.randn(total_blocks, Hkv, bs, D, device="cuda").to(torch.bfloat16)
+        q = torch.randn(T, Hq * D, device="cuda").to(torch.bfloat16)
+        out = ops.paged_attention(q, k_cache, v_cache, pl_t, sb_t, bi_t, bib_t, Hq, Hkv, D,
+                                  max_context_len=max(p + q_ for p, q_ in zip(past_lens, q_lens)),
+                                  max_q_len=max(q_lens), sliding_window=32)
+        k_all, v_all = [], []
+        for b in range(len(q_lens)):
+            blocks = bi_t[bib_t[b]:bib_t[b + 1]].long()
+            ctx = past_lens[b] + q_lens[b]
+            k_all.append(k_cache[blocks].permute(0, 2, 1, 3).reshape(-1, Hkv, D)[:ctx].float())
+            v_all.append(v_cache[blocks].permute(0, 2, 1, 3).reshape(-1, Hkv, D)[:ctx].float())
+        ref = _attn_ref(q.float().reshape(T, Hq, D), k_all, v_all, q_lens, past_lens, Hq, Hkv, D, 1 / math.sqrt(D), 32)
+        assert _rel_err(out.reshape(T, Hq, D), ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.bfloat16, 128)])
+def test_sdpa_dense(ops, dtype, D):
+    torch.manual_seed(8)
+    B, S, H = 3, 200, 4
+    qkv = torch.randn(B * S, 3 * H * D, device="cuda").to(dtype)
+    q, k, v = qkv[:, : H * D], qkv[:, H * D: 2 * H * D], qkv[:, 2 * H * D:]
+    out = ops.sdpa_dense(q, k, v, B, S, H, D, ld=3 * H * D)
+    qf, kf, vf = [t.float().reshape(B, S, H, D).transpose(1, 2) for t in (q, k, v)]
+    ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf).transpose(1, 2).reshape(B * S, H * D)
+    assert _rel_err(out, ref) < 1e-2
