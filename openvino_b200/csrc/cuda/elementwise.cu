@@ -186,7 +186,8 @@ __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloa
 }
 
 // ------------------------------------------------------------------------------------ embedding
-__global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* __restrict__ table,
+template <class IdT>
+__global__ void embedding_kernel(const IdT* __restrict__ ids, const uint4* __restrict__ table,
                                  uint4* __restrict__ out, int rows, int vec_per_row, int vocab) {
     const size_t total = (size_t)rows * vec_per_row;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -198,10 +199,32 @@ __global__ void embedding_kernel(const int64_t* __restrict__ ids, const uint4* _
     }
 }
 
+// ------------------------------------------------------------------------------------ token feedback
+// Steps can be chained on the device without a host round trip: a token position whose tok_src is
+// >= 0 takes its id from last_token[tok_src] (the token sampled for that request by an earlier step)
+// instead of the id uploaded by the host; after sampling, sequence i's token goes to
+// last_token[tok_dst[i]] (tok_dst < 0: the step ended inside the prompt, nothing to record).
+__global__ void resolve_ids_kernel(int* __restrict__ ids, const int* __restrict__ tok_src,
+                                   const int* __restrict__ last_token, int T) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < T) {
+        const int s = tok_src[t];
+        if (s >= 0) ids[t] = last_token[s];
+    }
+}
+__global__ void scatter_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_dst,
+                                      int* __restrict__ last_token, int B) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) {
+        const int d = tok_dst[i];
+        if (d >= 0) last_token[d] = tokens[i];
+    }
+}
+
 // ------------------------------------------------------------------------------------ argmax
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
-argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int vocab, int64_t* __restrict__ out_ids,
+argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int vocab, void* __restrict__ out_ids, int ids_i32,
               float* __restrict__ out_max) {
     __shared__ float sv[THREADS / 32];
     __shared__ int si[THREADS / 32];
@@ -250,7 +273,9 @@ argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int vocab, int64
             if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
         }
         if (lane == 0) {
-            out_ids[row] = bi == 0x7fffffff ? 0 : bi;
+            const int res = bi == 0x7fffffff ? 0 : bi;
+            if (ids_i32) reinterpret_cast<int*>(out_ids)[row] = res;
+            else reinterpret_cast<int64_t*>(out_ids)[row] = res;
             if (out_max) out_max[row] = best;
         }
     }
@@ -305,19 +330,37 @@ __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int*
 // IR layout: byte b of a row holds element 2b in its low nibble and 2b+1 in its high nibble.
 // Plugin layout: every aligned group of 8 elements e0..e7 becomes one u32 with nibble j (j<4) = e[2j]
 // and nibble j+4 = e[2j+1], so that one mask per shifted copy yields a pair of adjacent elements.
-__global__ void pack_u4_kernel(const uint32_t* __restrict__ w_ir, uint32_t* __restrict__ w_out, size_t nwords) {
+// The words are also re-ordered so that the 128 x 64 block of one (weight tile, k-block) pair is one
+// contiguous 4 KB chunk: word index ((tile * KB + kb) * 128 + row) * 8 + w.
+__global__ void pack_u4_kernel(const uint32_t* __restrict__ w_ir, uint32_t* __restrict__ w_out, size_t nwords, int K) {
+    const int wpr = K / 8;          // words per row
+    const int KB = K / 64;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nwords; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t x = w_ir[i];   // nibble k = element k
+        const size_t n = i / wpr;
+        const int kw = int(i - n * wpr);
+        const size_t dst = ((((n >> 7) * KB + (kw >> 3)) << 7) + (n & 127)) * 8 + (kw & 7);
         uint32_t o = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             o |= ((x >> (8 * j)) & 0xF) << (4 * j);            // e[2j]   -> nibble j
             o |= ((x >> (8 * j + 4)) & 0xF) << (4 * j + 16);   // e[2j+1] -> nibble j+4
         }
-        w_out[i] = o;
+        w_out[dst] = o;
     }
 }
-// scales_ir [N, G] fp16 -> [G, N] bf16;  zps -> [G, N] bf16 holding bias + zp
+__global__ void pack_w16_kernel(const uint4* __restrict__ w, uint4* __restrict__ w_out, size_t npieces, int K) {
+    const int ppr = K / 8;          // 16-byte pieces per row
+    const int KB = K / 64;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < npieces; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / ppr;
+        const int pc = int(i - n * ppr);
+        const int kb = pc >> 3, c = pc & 7, r = int(n & 127);
+        const size_t dst = ((((n >> 7) * KB + kb) << 7) + r) * 8 + (c ^ (r & 7));
+        w_out[dst] = w[i];
+    }
+}
+// scales_ir [N, G] fp16 + zero points -> [G, N] pairs (bf16 scale, bf16 bias + zp); zps_out (optional) [G, N]
 __global__ void pack_scale_zp_kernel(const __half* __restrict__ scales_ir, const uint8_t* __restrict__ zps_ir,
                                      int zp_is_u8, __nv_bfloat16* __restrict__ scales_out,
                                      __nv_bfloat16* __restrict__ zps_out, int N, int G, float zp_bias,
@@ -326,13 +369,14 @@ __global__ void pack_scale_zp_kernel(const __half* __restrict__ scales_ir, const
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t n = i / G;
         const int g = int(i - n * G);
-        scales_out[(size_t)g * N + n] = __float2bfloat16_rn(__half2float(scales_ir[i]));
+        scales_out[((size_t)g * N + n) * 2] = __float2bfloat16_rn(__half2float(scales_ir[i]));
         float z = zp_default;
         if (zps_ir) {
             if (zp_is_u8) z = float(zps_ir[i]);
             else z = float((zps_ir[i >> 1] >> ((i & 1) * 4)) & 0xF);
         }
-        zps_out[(size_t)g * N + n] = __float2bfloat16_rn(zp_bias + z);
+        scales_out[((size_t)g * N + n) * 2 + 1] = __float2bfloat16_rn(zp_bias + z);
+        if (zps_out) zps_out[(size_t)g * N + n] = __float2bfloat16_rn(zp_bias + z);
     }
 }
 
@@ -402,22 +446,42 @@ int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t str
     return 0;
 }
 
-int ovb_embedding(const int64_t* ids, const void* table, void* out, int rows, int cols, int vocab,
+int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, int rows, int cols, int vocab,
                   ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(ids && table && out && rows > 0 && cols % 8 == 0, "ovb_embedding: bad arguments");
     const size_t total = (size_t)rows * (cols / 8);
-    embedding_kernel<<<grid_for(total, 256), 256, 0, stream>>>(ids, (const uint4*)table, (uint4*)out, rows, cols / 8,
-                                                               vocab);
+    if (ids_i32)
+        embedding_kernel<int><<<grid_for(total, 256), 256, 0, stream>>>((const int*)ids, (const uint4*)table, (uint4*)out,
+                                                                        rows, cols / 8, vocab);
+    else
+        embedding_kernel<int64_t><<<grid_for(total, 256), 256, 0, stream>>>((const int64_t*)ids, (const uint4*)table,
+                                                                            (uint4*)out, rows, cols / 8, vocab);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
 
-int ovb_argmax(const void* logits, int ld, int rows, int vocab, int64_t* out_ids, float* out_max,
+int ovb_resolve_ids(int* ids, const int* tok_src, const int* last_token, int T, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(ids && tok_src && last_token && T > 0, "ovb_resolve_ids: bad arguments");
+    resolve_ids_kernel<<<(T + 255) / 256, 256, 0, stream>>>(ids, tok_src, last_token, T);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_scatter_tokens(const int* tokens, const int* tok_dst, int* last_token, int B, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(tokens && tok_dst && last_token && B > 0, "ovb_scatter_tokens: bad arguments");
+    scatter_tokens_kernel<<<(B + 255) / 256, 256, 0, stream>>>(tokens, tok_dst, last_token, B);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_argmax(const void* logits, int ld, int rows, int vocab, void* out_ids, int ids_i32, float* out_max,
                ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0, "ovb_argmax: bad arguments");
-    argmax_kernel<1024><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, out_ids, out_max);
+    argmax_kernel<1024><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, out_ids, ids_i32, out_max);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -433,13 +497,25 @@ int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void
     return 0;
 }
 
+int ovb_pack_w16(const void* w, void* w_out, int N, int K, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(w && w_out && N > 0 && K % 64 == 0, "ovb_pack_w16: K must be a multiple of 64");
+    OVB_CHECK_CUDA(cudaMemsetAsync(w_out, 0, (size_t)((N + 127) / 128) * 128 * K * 2, stream));
+    const size_t npieces = (size_t)N * K / 8;
+    pack_w16_kernel<<<grid_for(npieces, 256), 256, 0, stream>>>((const uint4*)w, (uint4*)w_out, npieces, K);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int zp_is_u8, void* w_out,
                 void* scales_out, void* zps_out, int N, int K, int group_size, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    OVB_REQUIRE(w_ir && scales_ir && w_out && scales_out && zps_out, "ovb_pack_u4: null operand");
-    OVB_REQUIRE(K % 8 == 0 && group_size > 0 && K % group_size == 0, "ovb_pack_u4: bad K/group_size");
+    OVB_REQUIRE(w_ir && scales_ir && w_out && scales_out, "ovb_pack_u4: null operand");
+    OVB_REQUIRE(K % 64 == 0 && group_size > 0 && K % group_size == 0, "ovb_pack_u4: K must be a multiple of 64 and of group_size");
     const size_t nwords = (size_t)N * K / 8;
-    pack_u4_kernel<<<grid_for(nwords, 256), 256, 0, stream>>>((const uint32_t*)w_ir, (uint32_t*)w_out, nwords);
+    // w_out holds ceil(N/128)*128 rows; rows beyond N stay zero
+    OVB_CHECK_CUDA(cudaMemsetAsync(w_out, 0, (size_t)((N + 127) / 128) * 128 * (K / 2), stream));
+    pack_u4_kernel<<<grid_for(nwords, 256), 256, 0, stream>>>((const uint32_t*)w_ir, (uint32_t*)w_out, nwords, K);
     OVB_CHECK_CUDA(cudaGetLastError());
     const int G = K / group_size;
     pack_scale_zp_kernel<<<grid_for((size_t)N * G, 256), 256, 0, stream>>>(

@@ -8,16 +8,21 @@
 // Design (Blackwell-first, not a translation):
 //  * The 128 weight rows of a tile sit on the M side of tcgen05.mma, the tokens on the N side
 //    (16..256). The accumulator [128 x BT] fp32 lives in TMEM.
-//  * warp 0 = TMA producer (cp.async.bulk.tensor, 128-byte swizzle), warp 1 = MMA issuer (one
-//    elected lane), warps 2..9 = weight dequantisation during the main loop, then the epilogue
-//    (tcgen05.ld -> registers -> global).
-//  * Quantised weights are fetched packed (4 KB per 128x64 tile for u4), expanded to bf16 by the
-//    dequant warps straight into the swizzled K-major layout that the MMA descriptor expects,
-//    made visible to the async proxy with fence.proxy.async, and handed over through an mbarrier.
+//  * warp 0 = producer (one lane): TMA tensor loads of the token tile (128-byte swizzle) and 1-D bulk
+//    copies of the weight chunks; warp 1 = MMA issuer (one lane); warps 2..9 = weight dequantisation
+//    during the main loop, then the epilogue.
+//  * Weights are constants, so the plugin stores them tile-contiguously: every (128-row tile, 64-column
+//    k-block) pair is ONE chunk (u4: 4 KB packed; bf16: 16 KB already in the swizzled smem order), which
+//    a single bulk copy fetches with full DRAM locality.
+//  * Quantised weights use two rings: a deep ring of packed chunks that the producer fills far ahead
+//    of use (HBM latency hidden), and a short ring of MMA stages (token tile + expanded bf16 weight
+//    tile). Each MMA stage is owned by one or two dequant warps, so several k-blocks are expanded at the
+//    same time; a stage is handed to the MMA through an mbarrier after fence.proxy.async.
 //  * Small-T problems (decode) are split along K so that every SM streams weights; the last CTA
 //    to arrive at a tile reduces the fp32 partials in a fixed order (bitwise reproducible).
-#include <map>
-#include <mutex>
+//  * Epilogue: TMEM -> registers -> (bias, activation) -> 16-bit tile in shared memory -> coalesced
+//    16-byte stores (residual added on the way out).
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -27,26 +32,31 @@ namespace ovb {
 constexpr int TILE_N = 128;      // weight rows per CTA (MMA M)
 constexpr int TILE_K = 64;       // bf16 elements per k-block = one 128-byte swizzle span
 constexpr int NUM_DQ_WARPS = 8;  // dequant + epilogue warps
+constexpr int DQ_THREADS = NUM_DQ_WARPS * 32;
 constexpr int GEMM_THREADS = (2 + NUM_DQ_WARPS) * 32;
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 8;    // MMA stages
+constexpr int MAX_PSLOTS = 16;   // packed-weight ring slots
+constexpr int kBandN = 16;       // weight tiles per rasterisation band
 
 struct GemmKParams {
     void* out;
     const void* bias;
     const void* residual;
-    const __nv_bfloat16* scales;
-    const __nv_bfloat16* zps;
+    const uint32_t* sz;       // [K/group, N] pairs (bf16 scale, bf16 biased zero point)
     float* ws;
     int* counters;
     int* status;
+    const uint8_t* w_tiled;   // non-null: weights in the tile-contiguous plugin layout (1-D bulk copies)
     int T, N, K;
     int ldo, ldr;
     int group_size;
     int act;
     int out_f32;
     int splits;
-    int stages;
+    int stages;               // MMA stages
+    int pslots;               // packed ring slots (quantised modes)
     int kblocks_per_split;
+    int debug;                // tuning aid (OVB_GEMM_DEBUG): 1 skip token-tile loads, 2 skip dequant math, 4 skip packed loads
 };
 
 template <bool F16>
@@ -101,6 +111,27 @@ __device__ __forceinline__ uint4 dequant_u4x8(uint32_t x, __nv_bfloat162 zz, __n
     return make_uint4(t[0], t[1], t[2], t[3]);
 }
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 template <int BT, int WMODE, bool F16>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmKParams p) {
@@ -109,43 +140,68 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     constexpr int X_BYTES = BT * 128;
     constexpr int W_BYTES = TILE_N * 128;
     constexpr int WQ_BYTES = (WMODE == OVB_W_U4) ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
-    constexpr int STAGE_BYTES = X_BYTES + W_BYTES + ((WQ_BYTES + 1023) / 1024) * 1024;
+    constexpr int ROW_PKT = WQ_BYTES / TILE_N;          // packed bytes per row and k-block
+    constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
     constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int stages = p.stages;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + stages * STAGE_BYTES);
-    uint64_t* full_tma = bars;                  // [stages] TMA bytes landed
-    uint64_t* full_dq = bars + MAX_STAGES;      // [stages] dequantised tile written
-    uint64_t* empty = bars + 2 * MAX_STAGES;    // [stages] MMAs that read the stage retired
-    uint64_t* acc_full = bars + 3 * MAX_STAGES; // accumulator complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * MAX_STAGES + 1);
+    const int pslots = p.pslots;
+    uint8_t* pring = smem + stages * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + pslots * WQ_BYTES);
+    uint64_t* full_x = bars;                         // [stages] token tile (and bf16 weight chunk) landed
+    uint64_t* full_dq = bars + MAX_STAGES;           // [stages] expanded weight tile written
+    uint64_t* empty = bars + 2 * MAX_STAGES;         // [stages] MMAs that read the stage retired
+    uint64_t* p_full = bars + 3 * MAX_STAGES;        // [pslots] packed chunk landed
+    uint64_t* p_empty = p_full + MAX_PSLOTS;         // [pslots] packed chunk consumed
+    uint64_t* acc_full = p_empty + MAX_PSLOTS;       // accumulator complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TILE_N;
-    const int t0 = blockIdx.y * BT;
+    // Tile order: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so the
+    // CTAs that are resident together share a few weight tiles and a few token tiles in L2.
+    int n_tile, t_tile;
+    {
+        const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
+        const int tiles_t = (p.T + BT - 1) / BT;
+        const int band_sz = kBandN * tiles_t;
+        const int band = blockIdx.x / band_sz;
+        const int r = blockIdx.x - band * band_sz;
+        const int in_band = min(kBandN, tiles_n - band * kBandN);
+        t_tile = r / in_band;
+        n_tile = band * kBandN + (r - t_tile * in_band);
+    }
+    const int n0 = n_tile * TILE_N;
+    const int t0 = t_tile * BT;
     const int split = blockIdx.z;
     const int total_kb = (p.K + TILE_K - 1) / TILE_K;
     const int kb_begin = split * p.kblocks_per_split;
     const int kb_end = min(total_kb, kb_begin + p.kblocks_per_split);
     const int num_kb = max(0, kb_end - kb_begin);
+    // dequant warps per MMA stage: with few stages two warps share one k-block (64 rows each)
+    const int wps = (stages <= NUM_DQ_WARPS / 2) ? 2 : 1;
 
+    const long long t_kernel0 = clock64();
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
-            mbar_init(&full_tma[s], 1);
-            mbar_init(&full_dq[s], NUM_DQ_WARPS);
+            mbar_init(&full_x[s], 1);
+            mbar_init(&full_dq[s], wps);
             mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < pslots; ++s) {
+            mbar_init(&p_full[s], 1);
+            mbar_init(&p_empty[s], wps);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         *last_flag = 0;
         mbar_fence_init();
-        tma_prefetch_desc(&tmW);
         tma_prefetch_desc(&tmX);
+        if (!QUANT && p.w_tiled == nullptr) tma_prefetch_desc(&tmW);
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -156,117 +212,235 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    const bool prof = (p.debug & 16) && blockIdx.x == 0 && blockIdx.z == 0 && p.ws != nullptr;
+    long long* prof_out = reinterpret_cast<long long*>(p.ws);
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ producer
         if (lane == 0) {
-            uint32_t phase = 0;
-            int s = 0;
-            for (int i = 0; i < num_kb; ++i) {
-                if (!mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status)) break;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                const int kb = kb_begin + i;
-                mbar_arrive_expect_tx(&full_tma[s], X_BYTES + (QUANT ? WQ_BYTES : W_BYTES));
-                tma_load_2d(st, &tmX, &full_tma[s], kb * TILE_K, t0);
-                if (WMODE == OVB_W_U4) {
-                    tma_load_2d(st + X_BYTES + W_BYTES, &tmW, &full_tma[s], kb * (TILE_K / 2), n0);
-                } else if (WMODE == OVB_W_U8) {
-                    tma_load_2d(st + X_BYTES + W_BYTES, &tmW, &full_tma[s], kb * TILE_K, n0);
-                } else {
-                    tma_load_2d(st + X_BYTES, &tmW, &full_tma[s], kb * TILE_K, n0);
+            if (QUANT) {
+                // Event loop over two cursors: packed weight chunks run ahead by up to `pslots` k-blocks,
+                // token tiles by up to `stages`. test_wait does not block, so neither stream holds up the other.
+                // running (slot, parity) counters: no divisions in this latency-bound single-lane loop
+                int iw = 0, ix = 0;
+                int wslot = 0, xs = 0;
+                uint32_t wpar = 1, xpar = 1;          // parity to wait for on the "empty" barriers
+                uint32_t idle = 0;
+                long long n_idle = 0;
+                const long long tb = clock64();
+                const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * total_kb + kb_begin) * WQ_BYTES;
+                int xk = kb_begin * TILE_K;
+                uint32_t wdst = smem_u32(pring), xdst = smem_u32(smem);
+                const bool skip_w = (p.debug & 4) != 0, skip_x = (p.debug & 1) != 0;
+                while (iw < num_kb || ix < num_kb) {
+                    bool progress = false;
+                    if (iw < num_kb && mbar_test(&p_empty[wslot], wpar)) {
+                        if (skip_w) {
+                            mbar_arrive(&p_full[wslot]);
+                        } else {
+                            mbar_arrive_expect_tx(&p_full[wslot], WQ_BYTES);
+                            if (WMODE == OVB_W_U4) {
+                                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                             ::"r"(wdst), "l"(wsrc), "r"(WQ_BYTES), "r"(smem_u32(&p_full[wslot])) : "memory");
+                            } else {
+                                tma_load_2d(pring + wslot * WQ_BYTES, &tmW, &p_full[wslot], (kb_begin + iw) * TILE_K, n0);
+                            }
+                        }
+                        ++iw;
+                        wsrc += WQ_BYTES;
+                        wdst += WQ_BYTES;
+                        if (++wslot == pslots) { wslot = 0; wpar ^= 1; wdst = smem_u32(pring); }
+                        progress = true;
+                    }
+                    if (ix < num_kb && mbar_test(&empty[xs], xpar)) {
+                        if (skip_x) {
+                            mbar_arrive(&full_x[xs]);
+                        } else {
+                            mbar_arrive_expect_tx(&full_x[xs], X_BYTES);
+                            asm volatile(
+                                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                                ::"r"(xdst), "l"(reinterpret_cast<uint64_t>(&tmX)), "r"(smem_u32(&full_x[xs])), "r"(xk), "r"(t0)
+                                : "memory");
+                        }
+                        ++ix;
+                        xk += TILE_K;
+                        xdst += STAGE_BYTES;
+                        if (++xs == stages) { xs = 0; xpar ^= 1; xdst = smem_u32(smem); }
+                        progress = true;
+                    }
+                    if (progress) {
+                        idle = 0;
+                    } else if (++n_idle, ++idle > (1u << 26) || ((idle & 1023u) == 0 && *abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; report_status(p.status, STATUS_MBAR_TIMEOUT); }
+                        break;
+                    }
                 }
-                if (++s == stages) { s = 0; phase ^= 1; }
+                if (prof) { prof_out[16] = clock64() - tb; prof_out[17] = n_idle; }
+            } else {
+                uint32_t phase = 0;
+                int s = 0;
+                for (int i = 0; i < num_kb; ++i) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status)) break;
+                    uint8_t* st = smem + s * STAGE_BYTES;
+                    const int kb = kb_begin + i;
+                    mbar_arrive_expect_tx(&full_x[s], X_BYTES + W_BYTES);
+                    tma_load_2d(st, &tmX, &full_x[s], kb * TILE_K, t0);
+                    if (p.w_tiled != nullptr)
+                        bulk_load_1d(st + X_BYTES, p.w_tiled + ((size_t)n_tile * total_kb + kb) * W_BYTES, W_BYTES, &full_x[s]);
+                    else
+                        tma_load_2d(st + X_BYTES, &tmW, &full_x[s], kb * TILE_K, n0);
+                    if (++s == stages) { s = 0; phase ^= 1; }
+                }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
+        // Only lane 0 waits and issues; lanes 1..31 park at the __syncwarp below (no polling).
         constexpr uint32_t idesc = umma_idesc_f16(TILE_N, BT, !F16);
-        uint32_t phase = 0;
-        int s = 0;
-        for (int i = 0; i < num_kb; ++i) {
-            bool ok = mbar_wait(&full_tma[s], phase, abort_flag, p.status);
-            if (ok && QUANT) ok = mbar_wait(&full_dq[s], phase, abort_flag, p.status);
-            if (!ok) break;
-            tc_fence_after_sync();
-            if (lane == 0) {
-                const uint32_t xa = smem_u32(smem + s * STAGE_BYTES);
-                const uint32_t wa = xa + X_BYTES;
+        const uint64_t desc0 = umma_desc_k_sw128(smem_u32(smem), 1024);
+        if (lane == 0) {
+            uint32_t phase = 0;
+            int s = 0;
+            long long t_x = 0, t_dq = 0, t_issue = 0;
+            const long long t_begin = clock64();
+            for (int i = 0; i < num_kb; ++i) {
+                const long long c0 = clock64();
+                bool ok = mbar_wait(&full_x[s], phase, abort_flag, p.status);
+                const long long c1 = clock64();
+                if (ok && QUANT) ok = mbar_wait(&full_dq[s], phase, abort_flag, p.status);
+                const long long c2 = clock64();
+                t_x += c1 - c0; t_dq += c2 - c1;
+                if (!ok) break;
+                tc_fence_after_sync();
+                // descriptors differ only in the 16-byte-unit start address (low 14 bits, no carry out here)
+                const uint64_t db0 = desc0 + (uint64_t)((s * STAGE_BYTES) >> 4);
+                const uint64_t da0 = db0 + (uint64_t)(X_BYTES >> 4);
 #pragma unroll
                 for (int k = 0; k < TILE_K / 16; ++k) {
-                    const uint64_t da = umma_desc_k_sw128(wa + k * 32, 1024);
-                    const uint64_t db = umma_desc_k_sw128(xa + k * 32, 1024);
-                    umma_f16_ss(tmem_base, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    if (p.debug & 8) break;
+                    umma_f16_ss(tmem_base, da0 + 2 * k, db0 + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty[s]);
+                t_issue += clock64() - c2;
+                if (++s == stages) { s = 0; phase ^= 1; }
             }
-            __syncwarp();
-            if (++s == stages) { s = 0; phase ^= 1; }
+            umma_commit(acc_full);
+            if (prof) {
+                prof_out[0] = clock64() - t_begin; prof_out[1] = t_x; prof_out[2] = t_dq; prof_out[3] = t_issue;
+                prof_out[4] = num_kb;
+            }
         }
-        if (lane == 0) umma_commit(acc_full);
         __syncwarp();
     } else {
         // ------------------------------------------------------------ dequant warps, then epilogue
         const int dq_tid = threadIdx.x - 64;  // 0..255
         if (QUANT) {
-            const int r = dq_tid >> 1;       // weight row inside the tile
-            const int half = dq_tid & 1;     // which 32-element half of the 64-wide k-block
-            const int n = n0 + r;
+            // Warp pair/single (dw / wps) owns MMA stage d and expands k-blocks d, d+stages, ... of it.
+            // One owner per stage keeps every parity wait at most one phase ahead of its barrier
+            // (pslots >= 2 * stages gives the same guarantee for the packed ring).
+            const int dw = warp - 2;
+            const int d = dw / wps;
+            const int sub = dw - d * wps;
+            const int rows_per_warp = TILE_N / wps;     // 128 or 64
+            const int iters = rows_per_warp / 16;       // 16 rows per pass of 32 lanes x 16 bytes
+            const int row0 = sub * rows_per_warp;
             const int G = p.K / p.group_size;
-            uint32_t phase = 0;
-            int s = 0;
-            int cur_g = -1;
-            __nv_bfloat162 ss = __floats2bfloat162_rn(0.f, 0.f), zz = ss;
-            for (int i = 0; i < num_kb; ++i) {
-                const int kb = kb_begin + i;
+            const int half = lane & 1;
+            // (scale, zero point) pairs of this lane's rows; the pairs of the warp's NEXT k-block are fetched
+            // at the start of the current one so that their latency hides behind the expansion work
+            uint32_t cur[8], nx1[8], nx2[8];
+            auto load_scales = [&](int kb, uint32_t* dst) {
                 const int g = (kb * TILE_K) / p.group_size;
-                if (g != cur_g) {
-                    cur_g = g;
-                    __nv_bfloat16 sv = __float2bfloat16_rn(0.f), zv = sv;
-                    if (n < p.N && g < G) {
-                        sv = p.scales[(size_t)g * p.N + n];
-                        zv = p.zps[(size_t)g * p.N + n];
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    if (it < iters) {
+                        const int n = n0 + row0 + it * 16 + (lane >> 1);
+                        dst[it] = (n < p.N && g < G) ? __ldg(p.sz + (size_t)g * p.N + n) : 0u;
                     }
-                    ss = __halves2bfloat162(sv, sv);
-                    zz = __halves2bfloat162(zv, zv);
                 }
-                bool ok = mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status);
-                if (ok) ok = mbar_wait(&full_tma[s], phase, abort_flag, p.status);
+            };
+            int i = d < stages ? d : num_kb;
+            uint32_t phase = 0;
+            // this warp's k-blocks are `stages` apart; their scale pairs are cold in HBM, so they are fetched
+            // two of the warp's iterations ahead
+            if (i < num_kb) load_scales(kb_begin + i, nx1);
+            if (i + stages < num_kb) load_scales(kb_begin + i + stages, nx2);
+            int slot = i;                       // i < stages <= pslots
+            uint32_t ppar = 0;
+            long long t_pf = 0, t_em = 0, t_work = 0;
+            const long long tb = clock64();
+            for (; i < num_kb; i += stages) {
+                const long long c0 = clock64();
+                long long c1 = c0;
+                // lane 0 polls, the warp barrier hands the observation on to the other lanes
+                int ok = 0;
+                if (lane == 0) {
+                    if (mbar_wait(&p_full[slot], ppar, abort_flag, p.status)) {
+                        c1 = clock64();
+                        ok = mbar_wait(&empty[d], phase ^ 1, abort_flag, p.status) ? 1 : 0;
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                const long long c2 = clock64();
+                t_pf += c1 - c0; t_em += c2 - c1;
                 if (!ok) break;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                uint8_t* wdst = st + X_BYTES + r * 128;
-                const uint8_t* wq = st + X_BYTES + W_BYTES;
-                if (WMODE == OVB_W_U4) {
-                    const uint4 pk = *reinterpret_cast<const uint4*>(wq + r * 32 + half * 16);
-                    const uint32_t xs[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int c = half * 4 + j;
-                        *reinterpret_cast<uint4*>(wdst + ((c ^ (r & 7)) << 4)) = dequant_u4x8(xs[j], zz, ss);
-                    }
-                } else {
-                    const float sf = __bfloat162float(__low2bfloat16(ss));
-                    const float zf = __bfloat162float(__low2bfloat16(zz));
+                for (int it = 0; it < 8; ++it) { cur[it] = nx1[it]; nx1[it] = nx2[it]; }
+                if (i + 2 * stages < num_kb) load_scales(kb_begin + i + 2 * stages, nx2);
+                const uint32_t wbase = smem_u32(smem + d * STAGE_BYTES + X_BYTES);
+                const uint8_t* wq = pring + slot * WQ_BYTES;
+                const uint32_t wq_a = smem_u32(wq);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint2 pk = *reinterpret_cast<const uint2*>(wq + r * 64 + half * 32 + j * 8);
-                        const uint32_t b[2] = {pk.x, pk.y};
-                        uint32_t o[4];
+                for (int it = 0; it < 8; ++it) {
+                    if (it < iters && !(p.debug & 2)) {
+                        const int r = row0 + it * 16 + (lane >> 1);
+                        const uint32_t wdst = wbase + r * 128;
+                        const __nv_bfloat162 szp = *reinterpret_cast<const __nv_bfloat162*>(&cur[it]);
+                        if (WMODE == OVB_W_U4) {
+                            const __nv_bfloat162 ss2 = __halves2bfloat162(__low2bfloat16(szp), __low2bfloat16(szp));
+                            const __nv_bfloat162 zz2 = __halves2bfloat162(__high2bfloat16(szp), __high2bfloat16(szp));
+                            const uint4 pk = lds128(wq_a + r * ROW_PKT + half * 16);
+                            const uint32_t xs[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const uint32_t w32 = b[e >> 1];
-                            const int sh = (e & 1) * 16;
-                            const float f0 = (float((w32 >> sh) & 0xFF) - zf) * sf;
-                            const float f1 = (float((w32 >> (sh + 8)) & 0xFF) - zf) * sf;
-                            o[e] = pack_bf16x2(f0, f1);
+                            for (int j = 0; j < 4; ++j) {
+                                const int c = half * 4 + j;
+                                sts128(wdst + ((c ^ (r & 7)) << 4), dequant_u4x8(xs[j], zz2, ss2));
+                            }
+                        } else {
+                            const float sf = __bfloat162float(__low2bfloat16(szp));
+                            const float zf = __bfloat162float(__high2bfloat16(szp));
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint2 pk = *reinterpret_cast<const uint2*>(wq + r * ROW_PKT + half * 32 + j * 8);
+                                const uint32_t b[2] = {pk.x, pk.y};
+                                uint32_t o[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const uint32_t w32 = b[e >> 1];
+                                    const int sh = (e & 1) * 16;
+                                    const float f0 = (float((w32 >> sh) & 0xFF) - zf) * sf;
+                                    const float f1 = (float((w32 >> (sh + 8)) & 0xFF) - zf) * sf;
+                                    o[e] = pack_bf16x2(f0, f1);
+                                }
+                                const int c = half * 4 + j;
+                                sts128(wdst + ((c ^ (r & 7)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+                            }
                         }
-                        const int c = half * 4 + j;
-                        *reinterpret_cast<uint4*>(wdst + ((c ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
-                fence_proxy_async_smem();
+                if (!(p.debug & 32)) fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full_dq[s]);
-                if (++s == stages) { s = 0; phase ^= 1; }
+                if (lane == 0) {
+                    mbar_arrive(&full_dq[d]);
+                    mbar_arrive(&p_empty[slot]);
+                }
+                phase ^= 1;
+                slot += stages;
+                if (slot >= pslots) { slot -= pslots; ppar ^= 1; }
+                t_work += clock64() - c2;
+            }
+            if (prof && dw == 0 && lane == 0) {
+                prof_out[8] = clock64() - tb; prof_out[9] = t_pf; prof_out[10] = t_em; prof_out[11] = t_work;
             }
         }
 
@@ -279,12 +453,23 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         constexpr int CHUNKS = (COLS_PER_WARP + 15) / 16;
         const int cbeg = (BT >= 32) ? colhalf * COLS_PER_WARP : 0;
         const bool active_warp = (BT >= 32) || (colhalf == 0);
-        const bool acc_ok = (num_kb > 0) ? mbar_wait(acc_full, 0, abort_flag, p.status) : true;
+        // one thread polls the accumulator barrier; the other 255 park at a hardware named barrier
+        if (dq_tid == 0 && num_kb > 0) mbar_wait(acc_full, 0, abort_flag, p.status);
+        asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+        const bool acc_ok = (*abort_flag == 0);
         tc_fence_after_sync();
 
         const float bias_v = (p.bias != nullptr && oc < p.N) ? to_float(reinterpret_cast<const E*>(p.bias)[oc]) : 0.f;
-        const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+        const int tile_id = blockIdx.x;
         float* ws_tile = p.ws ? p.ws + ((size_t)tile_id * p.splits) * (TILE_N * BT) : nullptr;
+        // Fast path: whole 128-row tile inside N, 16-bit output with 16-byte aligned rows. The tile is staged
+        // in shared memory as [token][128] (the pipeline stages are free by now) and written with 16-byte
+        // stores that cover 256 contiguous bytes per token row.
+        const bool fast = p.splits == 1 && !p.out_f32 && (n0 + TILE_N <= p.N) && (p.ldo % 8 == 0) &&
+                          ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
+                          (p.residual == nullptr || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
+        // fp32 staging keeps a single rounding (after the residual add): BT x 128 x 4 bytes <= 2 * STAGE_BYTES
+        float* stage_out = reinterpret_cast<float*>(smem);
 
         auto finish = [&](int col, float v) {
             const int tok = t0 + col;
@@ -311,7 +496,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0;
                 }
-                if (p.splits == 1) {
+                if (fast) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        stage_out[(c0 + j) * TILE_N + row] = apply_act(__uint_as_float(r[j]) + bias_v, p.act);
+                } else if (p.splits == 1) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) finish(c0 + j, __uint_as_float(r[j]));
                 } else {
@@ -321,22 +510,83 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
             }
         }
+        if (fast) {
+            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+            if (acc_ok) {
+                constexpr int PIECES = BT * (TILE_N / 8);     // 16-byte pieces in the tile
+                const int ntok = min(BT, p.T - t0);
+                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                    const int col = i >> 4, pc = i & 15;
+                    if (col < ntok) {
+                        const float4 f0 = *reinterpret_cast<const float4*>(stage_out + col * TILE_N + pc * 8);
+                        const float4 f1 = *reinterpret_cast<const float4*>(stage_out + col * TILE_N + pc * 8 + 4);
+                        float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                        const size_t tok = (size_t)(t0 + col);
+                        if (p.residual) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.residual) + tok * p.ldr + n0 + pc * 8);
+                            const E* re = reinterpret_cast<const E*>(&rr);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] += to_float(re[j]);
+                        }
+                        uint4 v;
+                        E* ve = reinterpret_cast<E*>(&v);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) ve[j] = from_float<E>(f[j]);
+                        *reinterpret_cast<uint4*>(reinterpret_cast<E*>(p.out) + tok * p.ldo + n0 + pc * 8) = v;
+                    }
+                }
+            }
+        }
         if (p.splits > 1) {
             // Last CTA to arrive at this tile sums the partials in split order.
             __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(NUM_DQ_WARPS * 32));
+            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
             if (dq_tid == 0) {
                 const int prev = atomicAdd(&p.counters[tile_id], 1);
                 *last_flag = (prev == p.splits - 1) ? 1 : 0;
                 if (prev == p.splits - 1) p.counters[tile_id] = 0;
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(NUM_DQ_WARPS * 32));
-            if (*last_flag && active_warp) {
+            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+            if (*last_flag) {
                 __threadfence();
-                for (int c = cbeg; c < cbeg + (BT >= 32 ? COLS_PER_WARP : BT); ++c) {
-                    float acc = 0.f;
-                    for (int z = 0; z < p.splits; ++z) acc += __ldcg(ws_tile + (size_t)z * (TILE_N * BT) + c * TILE_N + row);
-                    finish(c, acc);
+                // all 256 threads: float4 pieces of the [BT][128] partial tiles, every split in flight at once
+                constexpr int TOTAL4 = TILE_N * BT / 4;
+                for (int i4 = dq_tid; i4 < TOTAL4; i4 += DQ_THREADS) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int z = 0; z < p.splits; ++z) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(ws_tile + (size_t)z * (TILE_N * BT)) + i4);
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    const int e = i4 * 4;
+                    const int col = e / TILE_N, r4 = e % TILE_N;
+                    const int tok = t0 + col, oc4 = n0 + r4;
+                    if (tok < p.T) {
+                        float vv[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (oc4 + j < p.N) {
+                                float v = vv[j];
+                                if (p.bias) v += to_float(reinterpret_cast<const E*>(p.bias)[oc4 + j]);
+                                v = apply_act(v, p.act);
+                                if (p.residual) v += to_float(reinterpret_cast<const E*>(p.residual)[(size_t)tok * p.ldr + oc4 + j]);
+                                vv[j] = v;
+                            }
+                        }
+                        if (p.out_f32) {
+                            float* o = reinterpret_cast<float*>(p.out) + (size_t)tok * p.ldo + oc4;
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) if (oc4 + j < p.N) o[j] = vv[j];
+                        } else {
+                            E* o = reinterpret_cast<E*>(p.out) + (size_t)tok * p.ldo + oc4;
+                            if (oc4 + 3 < p.N && ((reinterpret_cast<uintptr_t>(o) & 7) == 0)) {
+                                E t4[4] = {from_float<E>(vv[0]), from_float<E>(vv[1]), from_float<E>(vv[2]), from_float<E>(vv[3])};
+                                *reinterpret_cast<uint2*>(o) = *reinterpret_cast<uint2*>(t4);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) if (oc4 + j < p.N) o[j] = from_float<E>(vv[j]);
+                            }
+                        }
+                    }
                 }
             }
         }
@@ -353,16 +603,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
+        if (prof && lane == 0) prof_out[24] = clock64() - t_kernel0;
     }
 }
 
 // --------------------------------------------------------------------------------------------- host
-static int stage_bytes(int bt, int wmode) {
-    int wq = wmode == OVB_W_U4 ? TILE_N * 32 : (wmode == OVB_W_U8 ? TILE_N * 64 : 0);
-    return bt * 128 + TILE_N * 128 + ((wq + 1023) / 1024) * 1024;
-}
-
-constexpr int kSmemBudget = 212 * 1024;
+constexpr int kSmemLimit = 227 * 1024;          // opt-in dynamic shared memory per CTA
+constexpr int kSmemBudget = kSmemLimit - 2560;  // minus alignment slack and the barrier block
 constexpr int kNumCounters = 4096;
 constexpr int kNumSMs = 148;
 
@@ -377,31 +624,68 @@ static int pick_block_t(int T) {
 static int pick_splits(int T, int N, int K, int bt) {
     const int tiles = ceil_div(N, TILE_N) * ceil_div(T, bt);
     const int total_kb = ceil_div(K, TILE_K);
-    if (tiles >= 120 || total_kb < 8) return 1;
-    int s = ceil_div(kNumSMs, tiles);
-    s = s < total_kb / 4 ? s : total_kb / 4;
-    if (s > 16) s = 16;
-    return s < 1 ? 1 : s;
+    if (tiles >= 2 * kNumSMs || total_kb < 8) return 1;
+    // pick the split count whose CTA count fills whole waves of SMs best (ties: fewer splits)
+    int best = 1;
+    double best_eff = 0.0;
+    const int max_s = total_kb / 4 < 16 ? total_kb / 4 : 16;
+    for (int s = 1; s <= max_s; ++s) {
+        const int ctas = tiles * s;
+        const int waves = ceil_div(ctas, kNumSMs);
+        if (waves > 4 && s > 1) break;
+        const double eff = double(ctas) / double(waves * kNumSMs);
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+// MMA stages and packed-ring slots that fit the shared-memory budget.
+static void pick_rings(int bt, int wmode, int* stages, int* pslots) {
+    const int stage = bt * 128 + TILE_N * 128;
+    const int wq = wmode == OVB_W_U4 ? TILE_N * 32 : (wmode == OVB_W_U8 ? TILE_N * 64 : 0);
+    if (wq == 0) {
+        int s = kSmemBudget / stage;
+        *stages = s > MAX_STAGES ? MAX_STAGES : (s < 2 ? 2 : s);
+        *pslots = 0;
+        return;
+    }
+    // quantised: pslots >= 2 * stages (see the kernel). Four MMA stages with two dequant warps each keep all
+    // eight warps expanding; the rest of the budget goes to the packed ring.
+    int s = 4;
+    while (s > 2 && (kSmemBudget - s * stage) / wq < 2 * s) --s;
+    int pmax = (kSmemBudget - s * stage) / wq;
+    if (pmax > MAX_PSLOTS) pmax = MAX_PSLOTS;
+    *stages = s;
+    *pslots = pmax;
 }
 
 template <int BT, int WMODE, bool F16>
 static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensorMap& tmX, GemmKParams& p,
                   cudaStream_t stream) {
-    const int sb = stage_bytes(BT, WMODE);
-    int stages = kSmemBudget / sb;
-    if (stages > MAX_STAGES) stages = MAX_STAGES;
-    if (stages < 2) stages = 2;
+    int stages = 2, pslots = 0;
+    pick_rings(BT, WMODE, &stages, &pslots);
+    if (const char* e = getenv("OVB_GEMM_STAGES")) {   // tuning aid
+        const int v = atoi(e);
+        if (v >= 2 && v <= stages) stages = v;
+    }
     p.stages = stages;
-    const int smem = stages * sb + 1024 + 512;
+    p.pslots = pslots;
+    if (const char* e = getenv("OVB_GEMM_DEBUG")) p.debug = atoi(e);
+    const int wq = WMODE == OVB_W_U4 ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
+    const int smem = stages * (BT * 128 + TILE_N * 128) + pslots * wq + 1024 + 1024;
     auto kern = gemm_ws_kernel<BT, WMODE, F16>;
     static uint64_t configured = 0;  // one bit per device
     int dev = 0;
     OVB_CHECK_CUDA(cudaGetDevice(&dev));
     if (!(configured & (1ull << dev))) {
-        OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
+        OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
         configured |= (1ull << dev);
     }
-    dim3 grid(ceil_div(a->N, TILE_N), ceil_div(a->T, BT), p.splits);
+    if (smem > kSmemLimit) {
+        set_error("ovb_gemm: internal error, %d bytes of shared memory requested", smem);
+        return ERR_TOO_LARGE;
+    }
+    dim3 grid(ceil_div(a->N, TILE_N) * ceil_div(a->T, BT), 1, p.splits);
     kern<<<grid, GEMM_THREADS, smem, stream>>>(tmW, tmX, p);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
@@ -445,7 +729,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     const bool f16 = a->wmode == OVB_W_F16;
     const bool quant = a->wmode == OVB_W_U4 || a->wmode == OVB_W_U8;
     if (quant) {
-        OVB_REQUIRE(a->scales && a->zps, "ovb_gemm: quantised weights need scales and zero points");
+        OVB_REQUIRE(a->scales, "ovb_gemm: quantised weights need the (scale, zero point) table");
         OVB_REQUIRE(a->group_size >= 64 && a->group_size % 64 == 0 && a->K % a->group_size == 0,
                     "ovb_gemm: group_size %d must be a multiple of 64 that divides K=%d", a->group_size, a->K);
         OVB_REQUIRE(a->K % 32 == 0, "ovb_gemm: K must be a multiple of 32 for packed weights");
@@ -467,8 +751,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.out = a->out;
     p.bias = a->bias;
     p.residual = a->residual;
-    p.scales = reinterpret_cast<const __nv_bfloat16*>(a->scales);
-    p.zps = reinterpret_cast<const __nv_bfloat16*>(a->zps);
+    p.sz = reinterpret_cast<const uint32_t*>(a->scales);
     p.ws = a->ws;
     p.counters = a->counters;
     p.status = status_word();
@@ -486,8 +769,11 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     const CUtensorMapDataType dt16 = f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     if (int rc = make_tmap_2d(&tmX, a->x, dt16, 2, a->T, a->K, (uint64_t)ldx * 2, bt, TILE_K, true)) return rc;
     int rc = 0;
-    if (a->wmode == OVB_W_U4) {
-        rc = make_tmap_2d(&tmW, a->w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->N, a->K / 2, (uint64_t)a->K / 2, TILE_N, 32, false);
+    if (a->wmode == OVB_W_U4 || (a->w_tiled && !quant)) {
+        OVB_REQUIRE(a->K % TILE_K == 0, "ovb_gemm: tile-packed weights need K to be a multiple of 64");
+        OVB_REQUIRE((reinterpret_cast<uintptr_t>(a->w) & 15) == 0, "ovb_gemm: packed weights must be 16-byte aligned");
+        p.w_tiled = reinterpret_cast<const uint8_t*>(a->w);
+        tmW = tmX;   // unused by the kernel in this mode
     } else if (a->wmode == OVB_W_U8) {
         rc = make_tmap_2d(&tmW, a->w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->N, a->K, (uint64_t)a->K, TILE_N, 64, false);
     } else {

@@ -45,8 +45,8 @@ typedef struct {
     void* out;            // [T, N] bf16/fp16 (or fp32 when out_f32), row pitch ldo elements
     const void* bias;     // [N] same type as x, or NULL
     const void* residual; // [T, N] same type as out (16-bit only), row pitch ldr, or NULL
-    const void* scales;   // u4/u8: [K/group, N] bf16 (transposed, plugin layout)
-    const void* zps;      // u4: [K/group, N] bf16 holding 16+zp;  u8: [K/group, N] bf16 holding zp
+    const void* scales;   // u4/u8: [K/group, N] pairs of bf16 (scale, zero point); u4 zero points are stored as 16+zp
+    const void* zps;      // unused (kept for layout compatibility)
     float* ws;            // split-K workspace (fp32), may be NULL when splits == 1
     int* counters;        // split-K tile counters (zero-initialised, self-resetting), may be NULL
     int64_t ws_bytes;     // capacity of ws
@@ -58,6 +58,7 @@ typedef struct {
     int out_f32;          // 1: fp32 output
     int splits;           // 0 = choose automatically
     int block_t;          // 0 = choose automatically (16/32/64/128/256)
+    int w_tiled;          // 16-bit weights are in the tile-contiguous layout made by ovb_pack_w16
     // Tensor-parallel fused all-reduce epilogue (0 ranks = off): see ovb_comm_* below.
     void* comm;           // communicator handle or NULL
 } ovb_gemm_args;
@@ -68,10 +69,16 @@ int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act);
 int ovb_gemm_num_counters(void);
 
 // Re-pack IR-layout u4 weights (LSB-first nibbles, [N, K]) into the plugin layout read by the
-// dequantising GEMM, and build transposed bf16 scale / biased zero-point tables.
+// dequantising GEMM, and build the transposed table of (bf16 scale, bf16 16+zero point) pairs.
 //   w_ir    : [N, K/2] bytes         scales_ir: [N, G] fp16     zps_ir: [N, G/2..] packed u4 or NULL (zp = 8)
+//   scales_out : [G, N, 2] bf16      zps_out: optional [G, N] bf16 (may be NULL)
 int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int zp_is_u8, void* w_out,
                 void* scales_out, void* zps_out, int N, int K, int group_size, ovb_stream_t stream);
+
+// Re-pack a 16-bit [N, K] row-major weight into the tile-contiguous layout: for every 128-row tile and
+// 64-column k-block one 16 KB chunk whose 16-byte pieces are already placed in the 128-byte swizzle
+// ((tile * K/64 + kb) * 128 + row) * 8 + (piece ^ (row & 7)). w_out holds ceil(N/128)*128 * K elements.
+int ovb_pack_w16(const void* w, void* w_out, int N, int K, ovb_stream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // Normalisation / elementwise
@@ -82,24 +89,28 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
                   int cols, float eps, int is_f16, ovb_stream_t stream);
 // out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
 int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
-int ovb_embedding(const int64_t* ids, const void* table, void* out, int rows, int cols, int vocab,
+// ids are int64 (ids_i32 == 0) or int32; ids outside [0, vocab) read row 0.
+int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, int rows, int cols, int vocab,
                   ovb_stream_t stream);
 // Greedy sampling: out_ids[r] = argmax_v logits[r, v] (first index on ties); optional out_max.
-int ovb_argmax(const void* logits, int ld, int rows, int vocab, int64_t* out_ids, float* out_max,
+int ovb_argmax(const void* logits, int ld, int rows, int vocab, void* out_ids, int ids_i32, float* out_max,
                ovb_stream_t stream);
 int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream);
+// Device-side token feedback between chained steps (see elementwise.cu).
+int ovb_resolve_ids(int* ids, const int* tok_src, const int* last_token, int T, ovb_stream_t stream);
+int ovb_scatter_tokens(const int* tokens, const int* tok_dst, int* last_token, int B, ovb_stream_t stream);
 
 // RoPE (half-rotate, LLaMA style) applied in place to q and k inside a fused qkv buffer, then
 // k/v rows are scattered into the paged cache.
 //   qkv       : [T, (Hq + 2*Hkv) * D] bf16
 //   positions : [T] int32 absolute position of each token
 //   slot_map  : [T] int32 physical slot (block * block_size + offset) of each token
-//   k_cache/v_cache : [num_blocks, block_size, Hkv, D] bf16
+//   k_cache/v_cache : [num_blocks, Hkv, block_size, D] bf16
 int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void* k_cache, void* v_cache, int T,
                       int Hq, int Hkv, int D, float theta, int block_size, ovb_stream_t stream);
 
 // ---------------------------------------------------------------------------------------------
-// Paged attention. Cache layout [num_blocks, block_size, Hkv, D]; ragged batch described like the
+// Paged attention. Cache layout [num_blocks, Hkv, block_size, D]; ragged batch described like the
 // PagedAttentionExtension op: past_lens[B], subsequence_begins[B+1], block_indices[...],
 // block_indices_begins[B+1].
 typedef struct {

@@ -59,15 +59,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait. `abort_flag` lives in shared memory: once any role gives up, every later
 // wait in the CTA returns at once so that all warps reach the tear-down barrier.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    if (*abort_flag) return false;
+// The fast path is a single try_wait: control lanes are latency bound, every extra instruction counts.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
     for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
     report_status(status, STATUS_MBAR_TIMEOUT);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status);
 }
 
 // ---------------------------------------------------------------- fences
@@ -98,6 +102,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
+}
+
+// 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion as bytes on `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM

@@ -33,7 +33,7 @@ class GemmArgs(C.Structure):
         ("T", C.c_int), ("N", C.c_int), ("K", C.c_int),
         ("ldx", C.c_int), ("ldo", C.c_int), ("ldr", C.c_int),
         ("group_size", C.c_int), ("wmode", C.c_int), ("act", C.c_int), ("out_f32", C.c_int),
-        ("splits", C.c_int), ("block_t", C.c_int),
+        ("splits", C.c_int), ("block_t", C.c_int), ("w_tiled", C.c_int),
         ("comm", C.c_void_p),
     ]
 
@@ -137,20 +137,30 @@ def default_workspace(device) -> Workspace:
 class PackedWeight:
     """A FullyConnected weight in the layout the GEMM kernel reads.
 
-    mode W_BF16/W_F16: ``w`` is [N, K] 16-bit.  mode W_U4: ``w`` is the re-packed nibble stream
-    [N, K/2] u8, ``scales``/``zps`` are [K/group, N] bf16 (zps hold 16 + zero_point).
-    mode W_U8: ``w`` [N, K] u8, ``zps`` hold the zero point itself.
+    mode W_BF16/W_F16: ``w`` is [N, K] 16-bit (optionally tile-packed).  mode W_U4: ``w`` is the tile-packed
+    nibble stream, ``scales`` is the [K/group, N, 2] bf16 table of (scale, 16 + zero_point) pairs.
+    mode W_U8: ``w`` [N, K] u8, the pairs hold the zero point itself.
     """
 
-    def __init__(self, mode, w, N, K, scales=None, zps=None, group_size=0, bias=None):
+    def __init__(self, mode, w, N, K, scales=None, zps=None, group_size=0, bias=None, tiled=False):
         self.mode, self.w, self.N, self.K = mode, w, N, K
         self.scales, self.zps, self.group_size, self.bias = scales, zps, group_size, bias
+        self.tiled = tiled
 
     @staticmethod
-    def from_dense(w: torch.Tensor, bias=None) -> "PackedWeight":
+    def from_dense(w: torch.Tensor, bias=None, tiled: bool = True) -> "PackedWeight":
+        """16-bit [N, K] weight. ``tiled`` re-packs it into tile-contiguous, pre-swizzled 16 KB chunks (one
+        bulk copy per k-block); K must then be a multiple of 64, otherwise the row-major form is kept."""
         assert w.dim() == 2 and w.dtype in (torch.bfloat16, torch.float16)
         mode = W_BF16 if w.dtype == torch.bfloat16 else W_F16
-        return PackedWeight(mode, w.contiguous(), w.shape[0], w.shape[1], bias=bias)
+        N, Kd = w.shape
+        w = w.contiguous()
+        if tiled and Kd % 64 == 0:
+            out = torch.empty(((N + 127) // 128) * 128 * Kd, dtype=w.dtype, device=w.device)
+            _check(lib().ovb_pack_w16(C.c_void_p(w.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(N), C.c_int(Kd),
+                                      C.c_void_p(_stream())), "ovb_pack_w16")
+            return PackedWeight(mode, out, N, Kd, bias=bias, tiled=True)
+        return PackedWeight(mode, w, N, Kd, bias=bias)
 
     @staticmethod
     def from_ir_u4(w_ir: torch.Tensor, scales_ir: torch.Tensor, zps_ir: Optional[torch.Tensor], N: int, K: int,
@@ -159,15 +169,14 @@ class PackedWeight:
         (or uint8 [N, G] when zp_is_u8) or None for the symmetric i4-style offset 8."""
         dev = w_ir.device
         G = K // group_size
-        w_out = torch.empty(N * K // 2, dtype=torch.uint8, device=dev)
-        s_out = torch.empty(G * N, dtype=torch.bfloat16, device=dev)
-        z_out = torch.empty(G * N, dtype=torch.bfloat16, device=dev)
+        w_out = torch.empty(((N + 127) // 128) * 128 * K // 2, dtype=torch.uint8, device=dev)
+        s_out = torch.empty(G * N * 2, dtype=torch.bfloat16, device=dev)
         rc = lib().ovb_pack_u4(C.c_void_p(w_ir.data_ptr()), C.c_void_p(scales_ir.data_ptr()),
                                C.c_void_p(_ptr(zps_ir)), C.c_int(1 if zp_is_u8 else 0), C.c_void_p(w_out.data_ptr()),
-                               C.c_void_p(s_out.data_ptr()), C.c_void_p(z_out.data_ptr()), C.c_int(N), C.c_int(K),
+                               C.c_void_p(s_out.data_ptr()), C.c_void_p(None), C.c_int(N), C.c_int(K),
                                C.c_int(group_size), C.c_void_p(_stream()))
         _check(rc, "ovb_pack_u4")
-        return PackedWeight(W_U4, w_out, N, K, s_out, z_out, group_size, bias)
+        return PackedWeight(W_U4, w_out, N, K, s_out, None, group_size, bias)
 
     @staticmethod
     def from_ir_u8(w_ir: torch.Tensor, scales_ir: torch.Tensor, zps_ir: Optional[torch.Tensor], N: int, K: int,
@@ -178,7 +187,8 @@ class PackedWeight:
             z = torch.full((G, N), 128.0, dtype=torch.bfloat16, device=w_ir.device)
         else:
             z = zps_ir.reshape(N, G).float().t().contiguous().to(torch.bfloat16)
-        return PackedWeight(W_U8, w_ir.contiguous(), N, K, s.reshape(-1), z.reshape(-1), group_size, bias)
+        sz = torch.stack([s, z], dim=-1).contiguous()      # [G, N, 2] pairs
+        return PackedWeight(W_U8, w_ir.contiguous(), N, K, sz.reshape(-1), None, group_size, bias)
 
 
 # ------------------------------------------------------------------------------------------ ops
@@ -205,6 +215,7 @@ def gemm(x: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None, r
     a.group_size = w.group_size
     a.wmode, a.act, a.out_f32 = w.mode, act, 1 if out_f32 else 0
     a.splits, a.block_t = splits, block_t
+    a.w_tiled = 1 if (w.tiled and w.mode in (W_BF16, W_F16)) else 0
     a.comm = None
     _check(lib().ovb_gemm(C.byref(a), C.c_void_p(_stream())), "ovb_gemm")
     return out
@@ -254,7 +265,8 @@ def embedding(ids, table, out=None):
     vocab, cols = table.shape
     if out is None:
         out = torch.empty((rows, cols), dtype=table.dtype, device=table.device)
-    _check(lib().ovb_embedding(C.c_void_p(ids.data_ptr()), C.c_void_p(table.data_ptr()), C.c_void_p(out.data_ptr()),
+    _check(lib().ovb_embedding(C.c_void_p(ids.data_ptr()), C.c_int(1 if ids.dtype == torch.int32 else 0),
+                               C.c_void_p(table.data_ptr()), C.c_void_p(out.data_ptr()),
                                C.c_int(rows), C.c_int(cols), C.c_int(vocab), C.c_void_p(_stream())), "ovb_embedding")
     return out
 
@@ -264,8 +276,21 @@ def argmax(logits, out=None, out_max=None):
     if out is None:
         out = torch.empty(rows, dtype=torch.int64, device=logits.device)
     _check(lib().ovb_argmax(C.c_void_p(logits.data_ptr()), C.c_int(logits.stride(0)), C.c_int(rows), C.c_int(vocab),
-                            C.c_void_p(out.data_ptr()), C.c_void_p(_ptr(out_max)), C.c_void_p(_stream())), "ovb_argmax")
+                            C.c_void_p(out.data_ptr()), C.c_int(1 if out.dtype == torch.int32 else 0),
+                            C.c_void_p(_ptr(out_max)), C.c_void_p(_stream())), "ovb_argmax")
     return out
+
+
+def resolve_ids(ids, tok_src, last_token):
+    _check(lib().ovb_resolve_ids(C.c_void_p(ids.data_ptr()), C.c_void_p(tok_src.data_ptr()),
+                                 C.c_void_p(last_token.data_ptr()), C.c_int(ids.numel()), C.c_void_p(_stream())),
+           "ovb_resolve_ids")
+
+
+def scatter_tokens(tokens, tok_dst, last_token):
+    _check(lib().ovb_scatter_tokens(C.c_void_p(tokens.data_ptr()), C.c_void_p(tok_dst.data_ptr()),
+                                    C.c_void_p(last_token.data_ptr()), C.c_int(tokens.numel()), C.c_void_p(_stream())),
+           "ovb_scatter_tokens")
 
 
 def rope_kv_write(qkv, positions, slot_map, k_cache, v_cache, Hq, Hkv, D, theta, block_size):
