@@ -1,1 +1,36 @@
+"""openvino_b200: an inference framework for NVIDIA B200 (sm_100a) with the OpenVINO programming model.
 
+Public API in one place, named as in ``import openvino as ov``: ``Core``, ``Model``, ``Tensor``, ``Type``,
+``PartialShape``, ``convert_model``, ``save_model``, ``compile_model`` and the sub-modules ``opset``,
+``properties``, ``preprocess``, ``passes``, ``frontend``, ``runtime``, ``genai``.
+"""
+try:
+    from . import _ovcore   # noqa: F401
+except ImportError:   # first import of a fresh checkout: compile the native core in-tree
+    from .build import build_core as _build_core
+    _build_core()
+    from . import _ovcore   # noqa: F401
+
+from ._types import Dimension, PartialShape, Shape, Type, get_element_type   # noqa: F401
+from ._tensor import Tensor   # noqa: F401
+from ._graph import Input, Model, Node, Output, RTMap   # noqa: F401
+from . import opset   # noqa: F401
+from . import opset as opset1, opset as opset2, opset as opset3, opset as opset4, opset as opset5, opset as opset6   # noqa: F401,E401
+from . import opset as opset7, opset as opset8, opset as opset9, opset as opset10, opset as opset11, opset as opset12   # noqa: F401,E401
+from . import opset as opset13, opset as opset14, opset as opset15, opset as opset16   # noqa: F401,E401
+from . import properties   # noqa: F401
+from . import passes   # noqa: F401
+from . import preprocess   # noqa: F401
+from .preprocess import Layout, layout_helpers   # noqa: F401
+from .frontend import FrontEndManager, convert_model, read_model, save_model, serialize   # noqa: F401
+from .runtime.core import (AsyncInferQueue, CompiledModel, Core, InferRequest, OVDict, ProfilingInfo, VariableState, Version,   # noqa: F401
+                           __version__, compile_model)
+
+__all__ = ["AsyncInferQueue", "CompiledModel", "Core", "Dimension", "FrontEndManager", "InferRequest", "Input", "Layout", "Model", "Node",
+           "OVDict", "Output", "PartialShape", "ProfilingInfo", "RTMap", "Shape", "Tensor", "Type", "VariableState", "Version", "compile_model",
+           "convert_model", "get_element_type", "layout_helpers", "opset", "passes", "preprocess", "properties", "read_model", "save_model",
+           "serialize"]
+
+
+def get_version() -> str:
+    return __version__

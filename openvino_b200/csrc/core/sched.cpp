@@ -1,0 +1,170 @@
+#include "sched.hpp"
+
+#include <algorithm>
+#include <stdexcept>
+
+namespace ovc {
+
+Scheduler::Scheduler(const SchedulerConfig& cfg) : cfg_(cfg) {
+    for (int64_t i = 0; i < cfg.num_kv_blocks; ++i) free_.push_back((int32_t)i);
+    for (int64_t i = 0; i < cfg.max_num_seqs * 4; ++i) free_slots_.push_back(i);
+}
+
+SeqPtr Scheduler::add(int64_t request_id, std::vector<int32_t> prompt, int64_t max_new_tokens, int32_t eos, bool ignore_eos) {
+    if (prompt.empty()) throw std::invalid_argument("a request needs at least one prompt token");
+    auto s = std::make_shared<SeqState>();
+    s->request_id = request_id;
+    s->prompt = std::move(prompt);
+    s->max_new_tokens = max_new_tokens;
+    s->eos_token_id = eos;
+    s->ignore_eos = ignore_eos;
+    waiting_.push_back(s);
+    return s;
+}
+
+bool Scheduler::grow(SeqState& s, int64_t new_len) {
+    const int64_t need = (new_len + cfg_.block_size - 1) / cfg_.block_size - (int64_t)s.blocks.size();
+    if (need <= 0) return true;
+    if (need > (int64_t)free_.size()) return false;
+    for (int64_t i = 0; i < need; ++i) { s.blocks.push_back(free_.front()); free_.pop_front(); }
+    return true;
+}
+void Scheduler::release(SeqState& s) {
+    for (auto b : s.blocks) free_.push_back(b);
+    s.blocks.clear();
+}
+bool Scheduler::preempt_one(const SeqState* keep) {
+    for (auto it = running_.rbegin(); it != running_.rend(); ++it) {
+        SeqPtr v = *it;
+        if (v.get() == keep || v->blocks.empty()) continue;
+        release(*v);
+        v->num_computed = 0;
+        running_.erase(std::next(it).base());
+        waiting_.push_front(v);
+        ++preemptions_;
+        return true;
+    }
+    return false;
+}
+void Scheduler::finish(const SeqPtr& s) {
+    if (s->finished) return;
+    s->finished = true;
+    release(*s);
+    running_.erase(std::remove(running_.begin(), running_.end(), s), running_.end());
+    if (s->slot >= 0) { free_slots_.push_back(s->slot); s->slot = -1; }
+}
+
+bool Scheduler::schedule(ScheduledStep& out) {
+    out = ScheduledStep();
+    int64_t budget = cfg_.max_num_batched_tokens;
+    auto pending = [](const SeqState& s) { return s.total_len() - s.num_computed; };
+    std::vector<SeqPtr> prefill_running, decode_running;
+    for (auto& s : running_) (pending(*s) > 1 ? prefill_running : decode_running).push_back(s);
+    const bool want_prefill = !prefill_running.empty() || !waiting_.empty();
+    auto in_running = [&](const SeqPtr& s) { return std::find(running_.begin(), running_.end(), s) != running_.end(); };
+
+    if (!decode_running.empty() && (cfg_.dynamic_split_fuse || !want_prefill)) {
+        for (auto& s : decode_running) {
+            if (budget <= 0 || (int64_t)out.seqs.size() >= cfg_.max_num_seqs) break;
+            if (!in_running(s)) continue;   // preempted by an earlier sequence of this loop
+            while (!grow(*s, s->total_len())) if (!preempt_one(s.get())) break;
+            if ((s->total_len() + cfg_.block_size - 1) / cfg_.block_size > (int64_t)s->blocks.size() || !in_running(s)) continue;
+            out.seqs.push_back(s);
+            out.num_new.push_back(1);
+            --budget;
+        }
+    }
+    if (want_prefill && (cfg_.dynamic_split_fuse || out.seqs.empty())) {
+        std::vector<SeqPtr> cands = prefill_running;
+        while (!waiting_.empty() && (int64_t)running_.size() + (int64_t)(cands.size() - prefill_running.size()) < cfg_.max_num_seqs) {
+            cands.push_back(waiting_.front());
+            waiting_.pop_front();
+        }
+        std::vector<SeqPtr> back;
+        for (auto& s : cands) {
+            const bool was_running = in_running(s);
+            if (budget <= 0 || (int64_t)out.seqs.size() >= cfg_.max_num_seqs) { if (!was_running) back.push_back(s); continue; }
+            const int64_t n = std::min(budget, s->total_len() - s->num_computed);
+            if (n <= 0 || !grow(*s, s->num_computed + n)) { if (!was_running) back.push_back(s); continue; }
+            if (!was_running) {
+                running_.push_back(s);
+                if (s->slot < 0) { s->slot = free_slots_.front(); free_slots_.pop_front(); }
+            }
+            out.seqs.push_back(s);
+            out.num_new.push_back(n);
+            budget -= n;
+        }
+        for (auto it = back.rbegin(); it != back.rend(); ++it) waiting_.push_front(*it);
+    }
+    if (out.seqs.empty()) return false;
+    for (size_t i = 0; i < out.seqs.size(); ++i) {
+        out.T += out.num_new[i];
+        out.max_q_len = std::max(out.max_q_len, out.num_new[i]);
+        out.max_ctx = std::max(out.max_ctx, out.seqs[i]->num_computed + out.num_new[i]);
+    }
+    return true;
+}
+
+void Scheduler::fill(const ScheduledStep& st, int32_t* d, const DescLayout& lay, bool host_ids) const {
+    const int64_t bs = cfg_.block_size;
+    int64_t t = 0, nb = 0;
+    if ((int64_t)st.seqs.size() > lay.Bcap || st.T > lay.Tcap) throw std::length_error("step does not fit the descriptor buffer");
+    d[lay.subsequence_begins] = 0;
+    d[lay.block_indices_begins] = 0;
+    for (size_t i = 0; i < st.seqs.size(); ++i) {
+        const SeqState& s = *st.seqs[i];
+        const int64_t n = st.num_new[i], c0 = s.num_computed;
+        for (int64_t j = 0; j < n; ++j) {
+            const int64_t pos = c0 + j;
+            d[lay.ids + t + j] = s.token_at(pos);
+            d[lay.positions + t + j] = (int32_t)pos;
+            d[lay.slot_map + t + j] = s.blocks[(size_t)(pos / bs)] * (int32_t)bs + (int32_t)(pos % bs);
+            d[lay.tok_src + t + j] = -1;
+        }
+        const bool ends_on_last = c0 + n == s.total_len();
+        if (!host_ids && !s.generated.empty() && ends_on_last) d[lay.tok_src + t + n - 1] = (int32_t)s.slot;
+        d[lay.tok_dst + (int64_t)i] = ends_on_last ? (int32_t)s.slot : -1;
+        d[lay.past_lens + (int64_t)i] = (int32_t)c0;
+        d[lay.logit_idx + (int64_t)i] = (int32_t)(t + n - 1);
+        const int64_t k = (c0 + n + bs - 1) / bs;
+        if (nb + k > lay.blocks_cap) throw std::length_error("block table does not fit the descriptor buffer");
+        for (int64_t j = 0; j < k; ++j) d[lay.block_indices + nb + j] = s.blocks[(size_t)j];
+        nb += k;
+        t += n;
+        d[lay.subsequence_begins + (int64_t)i + 1] = (int32_t)t;
+        d[lay.block_indices_begins + (int64_t)i + 1] = (int32_t)nb;
+    }
+}
+
+std::vector<Produced> Scheduler::commit(const ScheduledStep& st, const int32_t* tokens) {
+    std::vector<Produced> produced;
+    for (size_t i = 0; i < st.seqs.size(); ++i) {
+        const SeqPtr& s = st.seqs[i];
+        s->num_computed += st.num_new[i];
+        if (s->num_computed >= s->total_len() && !s->finished) {
+            s->generated.push_back(tokens ? tokens[i] : -1);
+            produced.push_back({s, (int64_t)s->generated.size() - 1, (int64_t)i});
+            if ((int64_t)s->generated.size() >= s->max_new_tokens) finish(s);
+        }
+    }
+    if (tokens) check_eos(produced);
+    return produced;
+}
+
+void Scheduler::patch(const std::vector<Produced>& produced, const int32_t* tokens) {
+    for (auto& p : produced)
+        if (p.gen_index < (int64_t)p.seq->generated.size()) p.seq->generated[(size_t)p.gen_index] = tokens[p.row];
+    check_eos(produced);
+}
+
+void Scheduler::check_eos(const std::vector<Produced>& produced) {
+    for (auto& p : produced) {
+        SeqState& s = *p.seq;
+        if (s.ignore_eos || p.gen_index >= (int64_t)s.generated.size() || s.generated[(size_t)p.gen_index] != s.eos_token_id) continue;
+        s.generated.resize((size_t)p.gen_index + 1);   // tokens sampled by steps launched before the EOS was seen are dropped
+        s.num_computed = std::min(s.num_computed, s.total_len());
+        finish(p.seq);
+    }
+}
+
+}  // namespace ovc

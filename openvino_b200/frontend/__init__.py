@@ -1,1 +1,197 @@
+"""Model input/output: ``read_model``, ``convert_model``, ``save_model``, ``serialize`` and the frontend registry.
 
+``FrontEndManager`` resolves a frontend by name or by inspecting the model ("ir", "onnx", "pytorch"), the way
+ov::frontend::FrontEndManager does (src/frontends/common/src/manager.cpp:28-276); ``read_model`` and
+``convert_model`` are the two entry points built on it (src/inference/src/model_reader.cpp:230,
+tools/ovc/openvino/tools/ovc/convert.py). ``save_model`` compresses fp32 weights to fp16 by default
+(src/core/src/graph_util.cpp:388-418), ``serialize`` writes the graph as it is.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, List, Optional
+
+import numpy as np
+
+from .. import _ovcore as _c
+from .._graph import Model
+from .._tensor import Tensor
+
+
+class FrontEnd:
+    name = ""
+
+    def supported(self, model) -> bool:
+        return False
+
+    def load(self, model, weights=None):
+        """-> an input model handle that ``convert`` accepts."""
+        return (model, weights)
+
+    def convert(self, input_model) -> Model:
+        raise NotImplementedError
+
+    def __repr__(self):
+        return "<FrontEnd '%s'>" % self.name
+
+
+class IRFrontEnd(FrontEnd):
+    """IR v10/v11 xml + bin (src/frontends/ir/src/frontend.cpp:31, ir_deserializer.cpp)."""
+
+    name = "ir"
+
+    def supported(self, model) -> bool:
+        if isinstance(model, (str, os.PathLike)):
+            s = str(model)
+            if s.lower().endswith(".xml"):
+                return True
+            return s.lstrip().startswith("<?xml") or s.lstrip().startswith("<net")
+        if isinstance(model, (bytes, bytearray)):
+            head = bytes(model[:64]).lstrip()
+            return head.startswith(b"<?xml") or head.startswith(b"<net")
+        return False
+
+    def convert(self, input_model) -> Model:
+        model, weights = input_model
+        if isinstance(model, (bytes, bytearray)):
+            model = bytes(model).decode()
+        model = str(model)
+        if model.lstrip().startswith("<"):
+            w = None
+            if weights is not None:
+                if isinstance(weights, Tensor):
+                    w = np.ascontiguousarray(weights.data).reshape(-1).view(np.uint8)
+                elif isinstance(weights, (bytes, bytearray, memoryview)):
+                    w = np.frombuffer(weights, dtype=np.uint8)
+                elif isinstance(weights, np.ndarray):
+                    w = np.ascontiguousarray(weights).reshape(-1).view(np.uint8)
+                else:
+                    with open(weights, "rb") as f:
+                        w = np.frombuffer(f.read(), dtype=np.uint8)
+            return Model._wrap(_c.deserialize(model, w))
+        if not os.path.exists(model):
+            raise RuntimeError("Model file %s cannot be opened!" % model)
+        bin_path = str(weights) if weights is not None else ""
+        return Model._wrap(_c.read_model_files(model, bin_path))
+
+
+class PyTorchFrontEnd(FrontEnd):
+    name = "pytorch"
+
+    def supported(self, model) -> bool:
+        try:
+            import torch
+        except ImportError:
+            return False
+        return isinstance(model, torch.nn.Module) or (hasattr(model, "graph_signature") and hasattr(model, "graph"))
+
+    def convert(self, input_model) -> Model:
+        from . import pytorch
+        model, kwargs = input_model
+        return pytorch.convert(model, **(kwargs or {}))
+
+
+class OnnxFrontEnd(FrontEnd):
+    name = "onnx"
+
+    def supported(self, model) -> bool:
+        if isinstance(model, (str, os.PathLike)):
+            return str(model).lower().endswith(".onnx")
+        return False
+
+    def convert(self, input_model) -> Model:
+        from . import onnx
+        model, _ = input_model
+        return onnx.convert(model)
+
+
+class FrontEndManager:
+    def __init__(self):
+        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd()}
+
+    def get_available_front_ends(self) -> List[str]:
+        return list(self._frontends)
+
+    def register_front_end(self, name: str, frontend: FrontEnd) -> None:
+        self._frontends[name] = frontend
+
+    def load_by_framework(self, framework: str) -> FrontEnd:
+        if framework not in self._frontends:
+            raise RuntimeError("frontend '%s' is not available" % framework)
+        return self._frontends[framework]
+
+    def load_by_model(self, model) -> Optional[FrontEnd]:
+        for fe in self._frontends.values():
+            if fe.supported(model):
+                return fe
+        return None
+
+
+_manager = FrontEndManager()
+
+
+def read_model(model, weights=None, extensions=None) -> Model:
+    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor) or an ``.onnx`` file."""
+    if isinstance(model, Model):
+        return model
+    if hasattr(model, "read"):
+        model = model.read()
+    fe = _manager.load_by_model(model)
+    if fe is None:
+        raise RuntimeError("Unable to read the model: %s. Please check that the model format is supported (IR xml, ONNX) and the file exists"
+                           % (str(model)[:200],))
+    return fe.convert(fe.load(model, weights))
+
+
+def convert_model(input_model, input=None, output=None, example_input=None, extension=None, verbose=False, share_weights=True, **kwargs) -> Model:
+    """Convert a framework model (a ``torch.nn.Module`` / ``ExportedProgram``, or a model file path) to a ``Model``.
+
+    ``input``: shapes to give the inputs (list in input order, ``{name: shape}`` or ``[(name, shape[, type])]``);
+    ``output``: names of the values to keep as model outputs; ``example_input``: sample inputs for tracing.
+    """
+    if isinstance(input_model, Model):
+        model = input_model
+    elif _manager._frontends["pytorch"].supported(input_model):
+        model = _manager._frontends["pytorch"].convert((input_model, dict(example_input=example_input, input=input, share_weights=share_weights, **kwargs)))
+    else:
+        model = read_model(input_model)
+        if input is not None:
+            from .pytorch import _input_shapes
+            shapes = _input_shapes(input)
+            keys = list(input.keys()) if isinstance(input, dict) else [it[0] if isinstance(it, tuple) and isinstance(it[0], str) else i for i, it in enumerate(input)]
+            model.reshape({k: s for k, s in zip(keys, shapes)})
+    if output:
+        names = [output] if isinstance(output, str) else list(output)
+        keep = []
+        for nm in names:
+            found = None
+            for n in model.get_ops():
+                for o in n.outputs():
+                    if nm in o.get_names() or n.get_friendly_name() == nm:
+                        found = o
+                        break
+                if found:
+                    break
+            if found is None:
+                raise RuntimeError("convert_model: no value named '%s'" % nm)
+            keep.append(found)
+        model = Model(keep, model.get_parameters(), model.get_friendly_name())
+    return model
+
+
+def serialize(model: Model, xml_path: str, bin_path: str = "", version: str = "UNSPECIFIED") -> None:
+    """Write the model as IR (no weight compression)."""
+    v = {"UNSPECIFIED": 11, "IR_V10": 10, "IR_V11": 11}.get(str(version), 11)
+    _c.save_model_files(model._m, str(xml_path), str(bin_path or ""), v)
+
+
+def save_model(model: Model, output_model: str, compress_to_fp16: bool = True) -> None:
+    """Write the model as IR; fp32 weights are stored as fp16 followed by a Convert unless ``compress_to_fp16=False``."""
+    m = model
+    if compress_to_fp16:
+        m = model.clone()
+        _c.compress_model_to_f16(m._m)
+    out = str(output_model)
+    if not out.lower().endswith(".xml"):
+        raise RuntimeError("save_model: the output path must end with .xml")
+    _c.save_model_files(m._m, out, "", 11)

@@ -1,1 +1,434 @@
+"""Graph passes: ``Manager``, ``ModelPass``, ``MatcherPass``/``Matcher`` with pattern nodes, and the named passes.
 
+Python face of the native pass infrastructure. Reference API: ``openvino.passes``
+(src/bindings/python/src/pyopenvino/graph/passes/{manager,model_pass,matcher_pass,pattern_ops,transformations}.cpp);
+the machinery it fronts: ov::pass::Manager::run_passes (src/core/src/pass/manager.cpp:323), GraphRewrite
+(src/core/src/pass/graph_rewrite.cpp:73-292) and the pattern Matcher (src/core/src/pattern/matcher.cpp:108-242).
+"""
+from __future__ import annotations
+
+from typing import Callable, Iterable, List, Optional, Sequence, Union
+
+from .. import _ovcore as _c
+from .._graph import Model, Node, Output
+
+
+class PassBase:
+    def __init__(self, name: Optional[str] = None):
+        self._name = name or type(self).__name__
+
+    def get_name(self) -> str:
+        return self._name
+
+    def set_name(self, name: str) -> None:
+        self._name = name
+
+    def _native(self):
+        raise NotImplementedError
+
+
+class ModelPass(PassBase):
+    """Sub-class and implement ``run_on_model(model) -> bool`` (True when the graph was changed)."""
+
+    def run_on_model(self, model: Model) -> bool:
+        raise NotImplementedError
+
+    def _native(self):
+        return _c.make_python_pass(self.get_name(), lambda core_model: bool(self.run_on_model(Model._wrap(core_model))))
+
+
+class _NamedPass(PassBase):
+    """A pass implemented natively, addressed by name with options."""
+
+    native_name = ""
+
+    def __init__(self, **options):
+        super().__init__(self.native_name or type(self).__name__)
+        self._options = options
+
+    def _native(self):
+        return _c.make_pass(self.native_name or type(self).__name__, self._options)
+
+    def run_on_model(self, model: Model) -> bool:
+        return self._native().run_on_model(model._m)
+
+
+class ConstantFolding(_NamedPass):
+    native_name = "ConstantFolding"
+
+
+class NopElimination(_NamedPass):
+    native_name = "NopElimination"
+
+
+class BatchNormDecomposition(_NamedPass):
+    native_name = "BatchNormDecomposition"
+
+
+class Validate(_NamedPass):
+    native_name = "Validate"
+
+
+class InitNodeInfo(_NamedPass):
+    native_name = "InitNodeInfo"
+
+
+class FusedNamesCleanup(_NamedPass):
+    native_name = "FusedNamesCleanup"
+
+
+class ConvertFP32ToFP16(_NamedPass):
+    native_name = "ConvertFP32ToFP16"
+
+
+class CompressFloatConstants(_NamedPass):
+    native_name = "CompressFloatConstants"
+
+
+class MOCTransformations(_NamedPass):
+    native_name = "MOCTransformations"
+
+
+class RMSFusion(_NamedPass):
+    native_name = "RMSFusion"
+
+
+class RoPEFusion(_NamedPass):
+    native_name = "RoPEFusion"
+
+
+class GLUFusion(_NamedPass):
+    native_name = "GLUFusion"
+
+
+class SDPAFusion(_NamedPass):
+    native_name = "SDPAFusion"
+
+
+class FuseMOEExperts(_NamedPass):
+    native_name = "FuseMOEExperts"
+
+
+class ConvertMatMulToFullyConnected(_NamedPass):
+    native_name = "ConvertMatMulToFullyConnected"
+
+
+class ConvertFullyConnectedToFullyConnectedCompressed(_NamedPass):
+    native_name = "ConvertFullyConnectedToFullyConnectedCompressed"
+
+
+class StatefulToStateless(_NamedPass):
+    native_name = "StatefulToStateless"
+
+
+class SDPAToPagedAttention(_NamedPass):
+    native_name = "SDPAToPagedAttention"
+
+    def __init__(self, use_block_indices_inputs=False, use_score_outputs=False, allow_score_aggregation=False, allow_cache_rotation=False,
+                 allow_xattention=False, allow_adaptive_rkv=False, allow_qq_bias=False):
+        super().__init__(use_block_indices_inputs=use_block_indices_inputs, use_score_outputs=use_score_outputs,
+                         allow_score_aggregation=allow_score_aggregation, allow_cache_rotation=allow_cache_rotation,
+                         allow_xattention=allow_xattention, allow_adaptive_rkv=allow_adaptive_rkv, allow_qq_bias=allow_qq_bias)
+
+
+class ConvertPrecision(_NamedPass):
+    """``ConvertPrecision(from_type, to_type)``: re-types parameters, constants and operations."""
+
+    native_name = "ConvertPrecision"
+
+    def __init__(self, from_type="f32", to_type="f16", keep_precision_sensitive_in_fp32: bool = True):
+        super().__init__(**{"from": str(from_type), "to": str(to_type), "keep_precision_sensitive_in_fp32": keep_precision_sensitive_in_fp32})
+
+
+class CompressWeights(_NamedPass):
+    native_name = "CompressWeights"
+
+    def __init__(self, mode: str = "int4_asym", group_size: int = 128, ratio: float = 1.0, all_layers: bool = False):
+        super().__init__(mode=mode, group_size=group_size, ratio=ratio, all_layers=all_layers)
+
+
+class MakeStateful(ModelPass):
+    """Turn (Parameter, Result) pairs into ReadValue/Assign. Pairs are tensor names or nodes."""
+
+    def __init__(self, pairs):
+        super().__init__("MakeStateful")
+        items = pairs.items() if isinstance(pairs, dict) else pairs
+        self._pairs = []
+        for p, r in items:
+            pn = p if isinstance(p, str) else (sorted(p.output(0).get_names()) or [p.get_friendly_name()])[0]
+            rn = r if isinstance(r, str) else (sorted(r.input_value(0).get_names()) or [r.get_friendly_name()])[0]
+            self._pairs.append((pn, rn))
+
+    def run_on_model(self, model: Model) -> bool:
+        return _c.make_stateful(model._m, self._pairs)
+
+
+class LowLatency2(ModelPass):
+    """Unrolls single-iteration TensorIterator/Loop state: back-edge pairs become ReadValue/Assign outside the body
+    when the iteration count is 1 (src/common/transformations/src/transformations/control_flow/unroll_tensor_iterator.cpp,
+    src/core/src/pass/low_latency.cpp)."""
+
+    def __init__(self, use_const_initializer: bool = True):
+        super().__init__("LowLatency2")
+        self.use_const_initializer = use_const_initializer
+
+    def run_on_model(self, model: Model) -> bool:
+        return False   # no recurrent bodies with back edges survive conversion in this framework's frontends
+
+
+class Serialize(ModelPass):
+    def __init__(self, path_to_xml: str, path_to_bin: str = "", version: str = "UNSPECIFIED"):
+        super().__init__("Serialize")
+        self.xml, self.bin, self.version = path_to_xml, path_to_bin, version
+
+    def run_on_model(self, model: Model) -> bool:
+        from ..frontend import serialize
+        serialize(model, self.xml, self.bin, self.version)
+        return False
+
+
+class VisualizeTree(ModelPass):
+    """Writes the graph in Graphviz dot format."""
+
+    def __init__(self, file_name: str = "model.dot"):
+        super().__init__("VisualizeTree")
+        self.file_name = file_name
+
+    def run_on_model(self, model: Model) -> bool:
+        lines = ["digraph model {", "  node [shape=box, fontsize=10];"]
+        ids = {}
+        for i, n in enumerate(model.get_ops()):
+            ids[n] = "n%d" % i
+            shapes = ", ".join(n.get_output_partial_shape(k).to_string() for k in range(n.get_output_size()))
+            lines.append('  n%d [label="%s\\n%s\\n%s"];' % (i, n.get_friendly_name().replace('"', "'"), n.get_type_name(), shapes))
+        for n in model.get_ops():
+            for k in range(n.get_input_size()):
+                src = n.input_value(k).get_node()
+                lines.append("  %s -> %s;" % (ids[src], ids[n]))
+        lines.append("}")
+        with open(self.file_name, "w") as f:
+            f.write("\n".join(lines))
+        return False
+
+
+# ------------------------------------------------------------------------------------------------ patterns
+class _Pattern:
+    def __init__(self, native):
+        self._p = native
+
+    def output(self, i: int = 0) -> "_Pattern":
+        return self
+
+
+def _pred(pred):
+    if pred is None:
+        return None
+    return lambda pair: bool(pred(Output(pair[0], pair[1])))
+
+
+def _types(t) -> List[str]:
+    items = t if isinstance(t, (list, tuple)) else [t]
+    return [str(x).split(".")[-1] if not str(x).startswith("opset") else str(x).split(".")[-1] for x in items]
+
+
+def _pins(inputs) -> list:
+    return [i._p if isinstance(i, _Pattern) else i for i in (inputs or [])]
+
+
+class AnyInput(_Pattern):
+    def __init__(self, predicate: Optional[Callable[[Output], bool]] = None):
+        super().__init__(_c.pattern_any(_pred(predicate)))
+
+
+class WrapType(_Pattern):
+    """Matches a node of one of the given types (``"opset13.Relu"`` or ``"Relu"``) whose inputs match ``inputs``."""
+
+    def __init__(self, type_names, inputs=None, predicate=None):
+        if callable(inputs) and predicate is None:
+            inputs, predicate = None, inputs
+        if isinstance(inputs, _Pattern):
+            inputs = [inputs]
+        super().__init__(_c.pattern_type(_types(type_names), _pins(inputs), _pred(predicate)))
+
+
+class Optional(_Pattern):   # noqa: A001 - name fixed by the API it mirrors
+    """Matches the node when present, otherwise matches its first input pattern directly."""
+
+    def __init__(self, type_names, inputs=None, predicate=None):
+        if isinstance(inputs, _Pattern):
+            inputs = [inputs]
+        super().__init__(_c.pattern_optional(_types(type_names), _pins(inputs), _pred(predicate)))
+
+
+class Or(_Pattern):
+    def __init__(self, alternatives: Sequence[_Pattern]):
+        super().__init__(_c.pattern_or(_pins(alternatives)))
+
+
+def any_input(predicate=None) -> AnyInput:
+    return AnyInput(predicate)
+
+
+def wrap_type(type_names, inputs=None, predicate=None) -> WrapType:
+    return WrapType(type_names, inputs, predicate)
+
+
+# predicates (src/core/include/openvino/pass/pattern/op/pattern.hpp)
+def consumers_count(n: int):
+    return lambda o: len(o.get_target_inputs()) == n
+
+
+def has_static_shape():
+    return lambda o: o.get_partial_shape().is_static
+
+
+def has_static_rank():
+    return lambda o: o.get_partial_shape().rank.is_static
+
+
+def has_static_dim(i: int):
+    return lambda o: o.get_partial_shape().rank.is_static and len(o.get_partial_shape()) > i and o.get_partial_shape()[i].is_static
+
+
+def rank_equals(r: int):
+    return lambda o: o.get_partial_shape().rank.is_static and len(o.get_partial_shape()) == r
+
+
+def type_matches(t):
+    return lambda o: o.get_element_type() == t
+
+
+def type_matches_any(ts):
+    return lambda o: any(o.get_element_type() == t for t in ts)
+
+
+class Matcher:
+    """Matches a pattern against a graph value; after a successful ``match`` gives the pattern -> value map."""
+
+    def __init__(self, pattern: _Pattern, name: str = ""):
+        self._pattern = pattern
+        self._m = _c.Matcher(pattern._p, name)
+
+    @classmethod
+    def _wrap(cls, native) -> "Matcher":
+        m = cls.__new__(cls)
+        m._m, m._pattern = native, None
+        return m
+
+    def get_name(self) -> str:
+        return self._m.name
+
+    def match(self, value) -> bool:
+        from .._graph import as_output
+        return self._m.match(as_output(value)._core())
+
+    def get_match_root(self) -> Node:
+        return Node(self._m.get_match_root())
+
+    def get_match_value(self) -> Output:
+        n, i = self._m.get_match_value()
+        return Output(n, i)
+
+    def get_match_nodes(self) -> List[Node]:
+        return [Node(n) for n in self._m.get_matched_nodes()]
+
+    def get_pattern_value_map(self) -> "_PatternMap":
+        return _PatternMap(self._m)
+
+
+class _PatternMap:
+    def __init__(self, native_matcher):
+        self._m = native_matcher
+
+    def __contains__(self, p: _Pattern) -> bool:
+        return self._m.has(p._p)
+
+    def __getitem__(self, p: _Pattern) -> Output:
+        n, i = self._m.at(p._p)
+        return Output(n, i)
+
+
+class MatcherPass(PassBase):
+    """``MatcherPass(matcher, callback)`` or sub-class calling ``register_matcher(matcher, callback)``.
+    ``callback(matcher) -> bool`` may rewrite the graph around the match root."""
+
+    def __init__(self, matcher: Optional[Matcher] = None, callback: Optional[Callable[[Matcher], bool]] = None):
+        super().__init__()
+        self._matcher, self._callback = matcher, callback
+        self._new_nodes: List[Node] = []
+
+    def register_matcher(self, matcher: Matcher, callback: Callable[[Matcher], bool]) -> None:
+        self._matcher, self._callback = matcher, callback
+        if matcher.get_name():
+            self.set_name(matcher.get_name())
+
+    def register_new_node(self, node: Node) -> Node:
+        self._new_nodes.append(node)
+        return node
+
+    def _native(self):
+        if self._matcher is None:
+            raise RuntimeError("MatcherPass has no matcher registered")
+        cb = self._callback
+        return _c.make_matcher_pass(self.get_name(), self._matcher._pattern._p, lambda native: bool(cb(Matcher._wrap(native))))
+
+    def run_on_model(self, model: Model) -> bool:
+        return self._native().run_on_model(model._m)
+
+
+class GraphRewrite(PassBase):
+    """Runs several matcher passes over the graph."""
+
+    def __init__(self, passes: Iterable[MatcherPass] = ()):
+        super().__init__()
+        self._passes = list(passes)
+
+    def add_matcher(self, p: MatcherPass) -> MatcherPass:
+        self._passes.append(p)
+        return p
+
+    def _native(self):
+        natives = [p._native() for p in self._passes]
+        return _c.make_python_pass(self.get_name(), lambda core_model: any([n.run_on_model(core_model) for n in natives]))
+
+
+BackwardGraphRewrite = GraphRewrite
+
+
+class Manager:
+    """Ordered list of passes; ``run_passes(model)`` applies them and re-validates the graph in between."""
+
+    def __init__(self):
+        self._pm = _c.PassManager()
+        self._passes: List[PassBase] = []
+
+    def register_pass(self, p, *args, **kwargs) -> PassBase:
+        if isinstance(p, type):
+            p = p(*args, **kwargs)
+        if isinstance(p, str):
+            native, wrapper = _c.make_pass(p, kwargs), None
+        else:
+            native, wrapper = p._native(), p
+        self._pm.add(native)
+        self._passes.append(wrapper)
+        return wrapper
+
+    def set_per_pass_validation(self, new_state: bool) -> None:
+        self._pm.validate_after_each = bool(new_state)
+
+    def disable(self, name: str) -> None:
+        self._pm.disable(name)
+
+    def enable(self, name: str) -> None:
+        self._pm.enable(name)
+
+    def run_passes(self, model: Model) -> bool:
+        return self._pm.run(model._m)
+
+    def get_timings(self):
+        """[(pass name, milliseconds, changed)] of the last run."""
+        return list(self._pm.timings())
+
+
+def available_passes() -> List[str]:
+    return list(_c.available_passes())
