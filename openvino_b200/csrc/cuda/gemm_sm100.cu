@@ -56,8 +56,19 @@ struct GemmKParams {
     int stages;               // MMA stages
     int pslots;               // packed ring slots (quantised modes)
     int kblocks_per_split;
-    int debug;                // tuning aid (OVB_GEMM_DEBUG): 1 skip token-tile loads, 2 skip dequant math, 4 skip packed loads
+    // Tensor-parallel all-reduce fused into the epilogue (world <= 1: off). Every rank runs the same launch;
+    // heap[r] is the symmetric heap of rank r mapped into this process (heap[rank] is local memory).
+    int world, rank;
+    int comm_mode;            // 1: one-shot (every rank gets every partial), 2: two-shot (tile owners reduce and broadcast)
+    int parity;               // one-shot staging buffer to use (consecutive fused calls alternate)
+    uint8_t* heap[8];
+    long long stage_off;      // staging area of the chosen mode (one-shot: of the chosen parity), offset in the heap
+    long long flags_off;      // this call site's flags: [tile][world + 1] int32, offset in the heap
+    long long out_off;        // `out` as an offset in the heap (two-shot owners write it on every rank)
+    const int* epoch;         // device word holding the current step number (local memory)
 };
+
+constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 us apart
 
 template <bool F16>
 struct Elem {
@@ -185,7 +196,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // dequant warps per MMA stage: with few stages two warps share one k-block (64 rows each)
     const int wps = (stages <= NUM_DQ_WARPS / 2) ? 2 : 1;
 
-    const long long t_kernel0 = clock64();
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(&full_x[s], 1);
@@ -212,8 +222,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const bool prof = (p.debug & 16) && blockIdx.x == 0 && blockIdx.z == 0 && p.ws != nullptr;
-    long long* prof_out = reinterpret_cast<long long*>(p.ws);
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
@@ -225,25 +233,18 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 int wslot = 0, xs = 0;
                 uint32_t wpar = 1, xpar = 1;          // parity to wait for on the "empty" barriers
                 uint32_t idle = 0;
-                long long n_idle = 0;
-                const long long tb = clock64();
                 const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * total_kb + kb_begin) * WQ_BYTES;
                 int xk = kb_begin * TILE_K;
                 uint32_t wdst = smem_u32(pring), xdst = smem_u32(smem);
-                const bool skip_w = (p.debug & 4) != 0, skip_x = (p.debug & 1) != 0;
                 while (iw < num_kb || ix < num_kb) {
                     bool progress = false;
                     if (iw < num_kb && mbar_test(&p_empty[wslot], wpar)) {
-                        if (skip_w) {
-                            mbar_arrive(&p_full[wslot]);
+                        mbar_arrive_expect_tx(&p_full[wslot], WQ_BYTES);
+                        if (WMODE == OVB_W_U4) {
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                         ::"r"(wdst), "l"(wsrc), "r"(WQ_BYTES), "r"(smem_u32(&p_full[wslot])) : "memory");
                         } else {
-                            mbar_arrive_expect_tx(&p_full[wslot], WQ_BYTES);
-                            if (WMODE == OVB_W_U4) {
-                                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                             ::"r"(wdst), "l"(wsrc), "r"(WQ_BYTES), "r"(smem_u32(&p_full[wslot])) : "memory");
-                            } else {
-                                tma_load_2d(pring + wslot * WQ_BYTES, &tmW, &p_full[wslot], (kb_begin + iw) * TILE_K, n0);
-                            }
+                            tma_load_2d(pring + wslot * WQ_BYTES, &tmW, &p_full[wslot], (kb_begin + iw) * TILE_K, n0);
                         }
                         ++iw;
                         wsrc += WQ_BYTES;
@@ -252,15 +253,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         progress = true;
                     }
                     if (ix < num_kb && mbar_test(&empty[xs], xpar)) {
-                        if (skip_x) {
-                            mbar_arrive(&full_x[xs]);
-                        } else {
-                            mbar_arrive_expect_tx(&full_x[xs], X_BYTES);
-                            asm volatile(
-                                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                                ::"r"(xdst), "l"(reinterpret_cast<uint64_t>(&tmX)), "r"(smem_u32(&full_x[xs])), "r"(xk), "r"(t0)
-                                : "memory");
-                        }
+                        mbar_arrive_expect_tx(&full_x[xs], X_BYTES);
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                            ::"r"(xdst), "l"(reinterpret_cast<uint64_t>(&tmX)), "r"(smem_u32(&full_x[xs])), "r"(xk), "r"(t0)
+                            : "memory");
                         ++ix;
                         xk += TILE_K;
                         xdst += STAGE_BYTES;
@@ -269,12 +266,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     }
                     if (progress) {
                         idle = 0;
-                    } else if (++n_idle, ++idle > (1u << 26) || ((idle & 1023u) == 0 && *abort_flag)) {
+                    } else if (++idle > (1u << 26) || ((idle & 1023u) == 0 && *abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; report_status(p.status, STATUS_MBAR_TIMEOUT); }
                         break;
                     }
                 }
-                if (prof) { prof_out[16] = clock64() - tb; prof_out[17] = n_idle; }
             } else {
                 uint32_t phase = 0;
                 int s = 0;
@@ -301,15 +297,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (lane == 0) {
             uint32_t phase = 0;
             int s = 0;
-            long long t_x = 0, t_dq = 0, t_issue = 0;
-            const long long t_begin = clock64();
             for (int i = 0; i < num_kb; ++i) {
-                const long long c0 = clock64();
                 bool ok = mbar_wait(&full_x[s], phase, abort_flag, p.status);
-                const long long c1 = clock64();
                 if (ok && QUANT) ok = mbar_wait(&full_dq[s], phase, abort_flag, p.status);
-                const long long c2 = clock64();
-                t_x += c1 - c0; t_dq += c2 - c1;
                 if (!ok) break;
                 tc_fence_after_sync();
                 // descriptors differ only in the 16-byte-unit start address (low 14 bits, no carry out here)
@@ -317,18 +307,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const uint64_t da0 = db0 + (uint64_t)(X_BYTES >> 4);
 #pragma unroll
                 for (int k = 0; k < TILE_K / 16; ++k) {
-                    if (p.debug & 8) break;
                     umma_f16_ss(tmem_base, da0 + 2 * k, db0 + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty[s]);
-                t_issue += clock64() - c2;
                 if (++s == stages) { s = 0; phase ^= 1; }
             }
             umma_commit(acc_full);
-            if (prof) {
-                prof_out[0] = clock64() - t_begin; prof_out[1] = t_x; prof_out[2] = t_dq; prof_out[3] = t_issue;
-                prof_out[4] = num_kb;
-            }
         }
         __syncwarp();
     } else {
@@ -367,22 +351,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (i + stages < num_kb) load_scales(kb_begin + i + stages, nx2);
             int slot = i;                       // i < stages <= pslots
             uint32_t ppar = 0;
-            long long t_pf = 0, t_em = 0, t_work = 0;
-            const long long tb = clock64();
             for (; i < num_kb; i += stages) {
-                const long long c0 = clock64();
-                long long c1 = c0;
                 // lane 0 polls, the warp barrier hands the observation on to the other lanes
                 int ok = 0;
                 if (lane == 0) {
-                    if (mbar_wait(&p_full[slot], ppar, abort_flag, p.status)) {
-                        c1 = clock64();
+                    if (mbar_wait(&p_full[slot], ppar, abort_flag, p.status))
                         ok = mbar_wait(&empty[d], phase ^ 1, abort_flag, p.status) ? 1 : 0;
-                    }
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                const long long c2 = clock64();
-                t_pf += c1 - c0; t_em += c2 - c1;
                 if (!ok) break;
 #pragma unroll
                 for (int it = 0; it < 8; ++it) { cur[it] = nx1[it]; nx1[it] = nx2[it]; }
@@ -392,7 +368,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const uint32_t wq_a = smem_u32(wq);
 #pragma unroll
                 for (int it = 0; it < 8; ++it) {
-                    if (it < iters && !(p.debug & 2)) {
+                    if (it < iters) {
                         const int r = row0 + it * 16 + (lane >> 1);
                         const uint32_t wdst = wbase + r * 128;
                         const __nv_bfloat162 szp = *reinterpret_cast<const __nv_bfloat162*>(&cur[it]);
@@ -428,7 +404,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         }
                     }
                 }
-                if (!(p.debug & 32)) fence_proxy_async_smem();
+                fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&full_dq[d]);
@@ -437,10 +413,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 phase ^= 1;
                 slot += stages;
                 if (slot >= pslots) { slot -= pslots; ppar ^= 1; }
-                t_work += clock64() - c2;
-            }
-            if (prof && dw == 0 && lane == 0) {
-                prof_out[8] = clock64() - tb; prof_out[9] = t_pf; prof_out[10] = t_em; prof_out[11] = t_work;
             }
         }
 
@@ -465,11 +437,128 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // Fast path: whole 128-row tile inside N, 16-bit output with 16-byte aligned rows. The tile is staged
         // in shared memory as [token][128] (the pipeline stages are free by now) and written with 16-byte
         // stores that cover 256 contiguous bytes per token row.
-        const bool fast = p.splits == 1 && !p.out_f32 && (n0 + TILE_N <= p.N) && (p.ldo % 8 == 0) &&
+        const bool fast = p.world <= 1 && p.splits == 1 && !p.out_f32 && (n0 + TILE_N <= p.N) && (p.ldo % 8 == 0) &&
                           ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) &&
                           (p.residual == nullptr || ((p.ldr % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.residual) & 15) == 0)));
         // fp32 staging keeps a single rounding (after the residual add): BT x 128 x 4 bytes <= 2 * STAGE_BYTES
         float* stage_out = reinterpret_cast<float*>(smem);
+
+        // ---- tensor-parallel: the fp32 partial tile in stage_out is summed over the ranks (see GemmKParams)
+        const bool comm = p.world > 1;
+        auto comm_epilogue = [&]() {
+            const int ntok = min(BT, p.T - t0);
+            const int epoch = __ldcg(p.epoch);
+            constexpr int PIECES = BT * (TILE_N / 8);               // 16-byte pieces of the bf16 tile
+            constexpr size_t SLOT = (size_t)BT * TILE_N * 2;        // bytes of one bf16 tile
+            const int tiles = gridDim.x;
+            const int W = p.world;
+            auto flags_of = [&](int r) { return reinterpret_cast<int*>(p.heap[r] + p.flags_off) + (size_t)tile_id * (W + 1); };
+            int* my_flags = flags_of(p.rank);
+            auto wait_flag = [&](const int* f) {
+                for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+                    if (ld_acquire_sys(f) >= epoch) return;
+                    if ((i & 255u) == 255u && *abort_flag) return;
+                    __nanosleep(200);
+                }
+                report_status(p.status, STATUS_PEER_TIMEOUT);
+                *abort_flag = 1;
+            };
+            auto partial_piece = [&](int col, int pc) {
+                const float4 f0 = *reinterpret_cast<const float4*>(stage_out + col * TILE_N + pc * 8);
+                const float4 f1 = *reinterpret_cast<const float4*>(stage_out + col * TILE_N + pc * 8 + 4);
+                return make_uint4(pack_bf16x2(f0.x, f0.y), pack_bf16x2(f0.z, f0.w), pack_bf16x2(f1.x, f1.y), pack_bf16x2(f1.z, f1.w));
+            };
+            // sum of the W bf16 partials of one piece (rank order, so every rank gets the same bits) + bias + residual
+            auto reduced_piece = [&](const uint8_t* slots, size_t slot_stride, int col, int pc) {
+                float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int r = 0; r < W; ++r) {
+                    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(slots + (size_t)r * slot_stride + ((size_t)col * TILE_N + pc * 8) * 2));
+                    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] += __bfloat162float(e[j]);
+                }
+                const size_t tok = (size_t)(t0 + col);
+                if (p.bias) {
+                    const uint4 bb = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.bias) + n0 + pc * 8);
+                    const E* be = reinterpret_cast<const E*>(&bb);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] += to_float(be[j]);
+                }
+                if (p.residual) {
+                    const uint4 rr = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.residual) + tok * p.ldr + n0 + pc * 8);
+                    const E* re = reinterpret_cast<const E*>(&rr);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) f[j] += to_float(re[j]);
+                }
+                uint4 v;
+                E* ve = reinterpret_cast<E*>(&v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ve[j] = from_float<E>(f[j]);
+                return v;
+            };
+            if (p.comm_mode == 1) {
+                // one-shot: push the partial to every rank, then every rank reduces the tile for itself
+                const size_t slot = (size_t)p.stage_off + ((size_t)p.rank * tiles + tile_id) * SLOT;
+                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                    const int col = i >> 4, pc = i & 15;
+                    if (col < ntok) {
+                        const uint4 v = partial_piece(col, pc);
+                        for (int r = 0; r < W; ++r)
+                            *reinterpret_cast<uint4*>(p.heap[r] + slot + ((size_t)col * TILE_N + pc * 8) * 2) = v;
+                    }
+                }
+                __threadfence_system();
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (dq_tid < W) {
+                    st_release_sys(flags_of(dq_tid) + p.rank, epoch);
+                    wait_flag(my_flags + dq_tid);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (*abort_flag == 0) {
+                    const uint8_t* slots = p.heap[p.rank] + p.stage_off + (size_t)tile_id * SLOT;
+                    for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                        const int col = i >> 4, pc = i & 15;
+                        if (col < ntok)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<E*>(p.out) + (size_t)(t0 + col) * p.ldo + n0 + pc * 8) =
+                                reduced_piece(slots, (size_t)tiles * SLOT, col, pc);
+                    }
+                }
+            } else {
+                // two-shot: the owner of the tile (tile_id mod W) collects the partials, reduces, and writes the
+                // finished tile into `out` on every rank; nobody leaves before its copy of the tile is final
+                const int owner = tile_id % W, own_idx = tile_id / W, own_cap = (tiles + W - 1) / W;
+                const size_t slot = (size_t)p.stage_off + ((size_t)p.rank * own_cap + own_idx) * SLOT;
+                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                    const int col = i >> 4, pc = i & 15;
+                    if (col < ntok)
+                        *reinterpret_cast<uint4*>(p.heap[owner] + slot + ((size_t)col * TILE_N + pc * 8) * 2) = partial_piece(col, pc);
+                }
+                __threadfence_system();
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (dq_tid == 0) st_release_sys(flags_of(owner) + p.rank, epoch);
+                if (p.rank == owner) {
+                    if (dq_tid < W) wait_flag(my_flags + dq_tid);
+                    asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                    const bool good = (*abort_flag == 0);
+                    if (good) {
+                        const uint8_t* slots = p.heap[p.rank] + p.stage_off + (size_t)own_idx * SLOT;
+                        for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                            const int col = i >> 4, pc = i & 15;
+                            if (col < ntok) {
+                                const uint4 v = reduced_piece(slots, (size_t)own_cap * SLOT, col, pc);
+                                const size_t off = (size_t)p.out_off + ((size_t)(t0 + col) * p.ldo + n0 + pc * 8) * 2;
+                                for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(p.heap[r] + off) = v;
+                            }
+                        }
+                    }
+                    __threadfence_system();
+                    asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                    if (good && dq_tid < W) st_release_sys(flags_of(dq_tid) + W, epoch);
+                }
+                if (dq_tid == 0) wait_flag(my_flags + W);
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+            }
+        };
 
         auto finish = [&](int col, float v) {
             const int tok = t0 + col;
@@ -496,7 +585,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 16; ++j) r[j] = 0;
                 }
-                if (fast) {
+                if (comm && p.splits == 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage_out[(c0 + j) * TILE_N + row] = __uint_as_float(r[j]);
+                } else if (fast) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         stage_out[(c0 + j) * TILE_N + row] = apply_act(__uint_as_float(r[j]) + bias_v, p.act);
@@ -510,7 +602,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
             }
         }
-        if (fast) {
+        if (comm && p.splits == 1) {
+            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+            if (acc_ok) comm_epilogue();   // acc_ok is uniform over the epilogue threads
+        } else if (fast) {
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
             if (acc_ok) {
                 constexpr int PIECES = BT * (TILE_N / 8);     // 16-byte pieces in the tile
@@ -547,7 +642,20 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (prev == p.splits - 1) p.counters[tile_id] = 0;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-            if (*last_flag) {
+            if (*last_flag && comm) {
+                __threadfence();
+                constexpr int TOTAL4 = TILE_N * BT / 4;
+                for (int i4 = dq_tid; i4 < TOTAL4; i4 += DQ_THREADS) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int z = 0; z < p.splits; ++z) {
+                        const float4 v = __ldcg(reinterpret_cast<const float4*>(ws_tile + (size_t)z * (TILE_N * BT)) + i4);
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    reinterpret_cast<float4*>(stage_out)[i4] = acc;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (*abort_flag == 0) comm_epilogue();
+            } else if (*last_flag) {
                 __threadfence();
                 // all 256 threads: float4 pieces of the [BT][128] partial tiles, every split in flight at once
                 constexpr int TOTAL4 = TILE_N * BT / 4;
@@ -603,7 +711,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLS);
-        if (prof && lane == 0) prof_out[24] = clock64() - t_kernel0;
     }
 }
 
@@ -664,13 +771,8 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
                   cudaStream_t stream) {
     int stages = 2, pslots = 0;
     pick_rings(BT, WMODE, &stages, &pslots);
-    if (const char* e = getenv("OVB_GEMM_STAGES")) {   // tuning aid
-        const int v = atoi(e);
-        if (v >= 2 && v <= stages) stages = v;
-    }
     p.stages = stages;
     p.pslots = pslots;
-    if (const char* e = getenv("OVB_GEMM_DEBUG")) p.debug = atoi(e);
     const int wq = WMODE == OVB_W_U4 ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
     const int smem = stages * (BT * 128 + TILE_N * 128) + pslots * wq + 1024 + 1024;
     auto kern = gemm_ws_kernel<BT, WMODE, F16>;
@@ -763,6 +865,39 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.out_f32 = a->out_f32;
     p.splits = splits;
     p.kblocks_per_split = ceil_div(total_kb, splits);
+    if (a->comm != nullptr && static_cast<const ovb_comm*>(a->comm)->world > 1) {
+        const ovb_comm* c = static_cast<const ovb_comm*>(a->comm);
+        OVB_REQUIRE(c->world <= 8 && c->rank >= 0 && c->rank < c->world, "ovb_gemm: bad communicator (rank %d of %d)", c->rank, c->world);
+        OVB_REQUIRE(!f16 && !a->out_f32 && a->act == OVB_ACT_NONE, "ovb_gemm: the fused all-reduce needs a bf16 output and no activation");
+        OVB_REQUIRE(a->N % TILE_N == 0 && p.ldo % 8 == 0 && p.ldr % 8 == 0 && (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 &&
+                        (reinterpret_cast<uintptr_t>(a->residual) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->bias) & 15) == 0,
+                    "ovb_gemm: the fused all-reduce needs N %% 128 == 0 and 16-byte aligned rows");
+        const int mode = c->mode ? c->mode : (a->T <= 128 ? 1 : 2);
+        const int64_t slot = (int64_t)bt * TILE_N * 2;
+        const int64_t need = mode == 1 ? c->world * tiles * slot : c->world * ((tiles + c->world - 1) / c->world) * slot;
+        OVB_REQUIRE(need <= (mode == 1 ? c->stage1_bytes : c->stage2_bytes),
+                    "ovb_gemm: the communicator's staging area (%lld bytes) is too small for T=%d N=%d (%lld bytes)",
+                    (long long)(mode == 1 ? c->stage1_bytes : c->stage2_bytes), a->T, a->N, (long long)need);
+        OVB_REQUIRE(tiles * (c->world + 1) <= c->flags_per_site && c->site >= 0 && c->site < c->num_sites,
+                    "ovb_gemm: communicator flag area too small (%lld tiles) or bad call site %d", (long long)tiles, c->site);
+        p.world = c->world;
+        p.rank = c->rank;
+        p.comm_mode = mode;
+        p.parity = c->site & 1;
+        for (int r = 0; r < c->world; ++r) {
+            OVB_REQUIRE(c->heap[r] != nullptr, "ovb_gemm: communicator heap of rank %d is not mapped", r);
+            p.heap[r] = static_cast<uint8_t*>(c->heap[r]);
+        }
+        p.stage_off = mode == 1 ? c->stage1_off + (int64_t)p.parity * c->stage1_bytes : c->stage2_off;
+        p.flags_off = c->flags_off + (int64_t)c->site * c->flags_per_site * 4;
+        p.epoch = reinterpret_cast<const int*>(p.heap[c->rank] + c->epoch_off);
+        if (mode == 2) {
+            const int64_t off = static_cast<uint8_t*>(a->out) - p.heap[c->rank];
+            OVB_REQUIRE(off >= 0 && off + ((int64_t)(a->T - 1) * p.ldo + a->N) * 2 <= c->heap_bytes,
+                        "ovb_gemm: with the two-shot all-reduce the output must live in the communicator's symmetric heap");
+            p.out_off = off;
+        }
+    }
 
     CUtensorMap tmW, tmX;
     const int ldx = a->ldx ? a->ldx : a->K;

@@ -59,8 +59,8 @@ typedef struct {
     int splits;           // 0 = choose automatically
     int block_t;          // 0 = choose automatically (16/32/64/128/256)
     int w_tiled;          // 16-bit weights are in the tile-contiguous layout made by ovb_pack_w16
-    // Tensor-parallel fused all-reduce epilogue (0 ranks = off): see ovb_comm_* below.
-    void* comm;           // communicator handle or NULL
+    // Tensor-parallel: out = residual + sum over ranks of (x * W^T), reduced inside the epilogue (see ovb_comm below).
+    void* comm;           // const ovb_comm* or NULL
 } ovb_gemm_args;
 
 int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream);
@@ -139,20 +139,39 @@ int ovb_sdpa_dense(const void* q, const void* k, const void* v, void* out, int B
                    float scale, int is_f16, int causal, ovb_stream_t stream);
 
 // ---------------------------------------------------------------------------------------------
-// Tensor-parallel communicator over NVLink peer memory (one process per GPU; buffers exchanged
-// as CUDA IPC handles by the Python side).
+// Tensor-parallel communicator over NVLink peer memory: one process per GPU; every rank owns a "symmetric heap"
+// (one device allocation with the same layout on every rank) that all ranks map through CUDA IPC handles.
+// The Python side (openvino_b200/parallel/comm.py) allocates, exchanges and maps the heaps and fills this struct.
+//
+// Layout inside the heap (byte offsets, identical on every rank):
+//   epoch_off    one int32: the step number, bumped by ovb_comm_step_begin at the start of every step
+//   flags_off    num_sites x flags_per_site int32, zero at start; a flag holds the step number of its last signal
+//   stage1_off   2 x stage1_bytes: one-shot staging (two buffers used alternately by consecutive fused calls)
+//   stage2_off   stage2_bytes: two-shot staging
+//   the rest     tensors handed out by the Python side (residual streams that peers write into)
 typedef struct {
     int rank, world;
-    void* peer_buf[8];     // staging buffer of every rank (this rank's own included), same size each
-    int* peer_flags[8];    // flag words of every rank
-    int64_t buf_bytes;
-    int64_t nflags;
-    int epoch;             // bumped by every collective call (host side)
+    void* heap[8];
+    int64_t heap_bytes;
+    int64_t epoch_off, flags_off, flags_per_site, stage1_off, stage1_bytes, stage2_off, stage2_bytes;
+    int num_sites;
+    int site;      // call site of this collective inside the step (every site has its own flags)
+    int mode;      // 0: choose by size, 1: one-shot, 2: two-shot
 } ovb_comm;
 
-// In-place all-reduce of a bf16 tensor [rows, cols] held in `data` on every rank.
-int ovb_allreduce_bf16(ovb_comm* c, void* data, int64_t n, ovb_stream_t stream);
-// Fused: out = rmsnorm(allreduce(x) + residual) etc. is done by the GEMM epilogue; see ovb_gemm.comm.
+// Symmetric-heap plumbing (no kernels): allocate zeroed device memory, export / open / close CUDA IPC handles.
+int ovb_comm_alloc(int64_t bytes, void** ptr);
+int ovb_comm_free(void* ptr);
+int ovb_comm_export(void* ptr, void* handle64);          // writes the 64-byte IPC handle
+int ovb_comm_open(const void* handle64, void** ptr);     // maps a peer's heap
+int ovb_comm_close(void* ptr);
+// epoch += 1 on this rank (a one-thread kernel; first kernel of every step, also inside CUDA graphs).
+int ovb_comm_step_begin(const ovb_comm* c, ovb_stream_t stream);
+// Greedy sampling over vocabulary shards: every rank holds its shard's best (value, local index) per row;
+// afterwards ids[row] is the global argmax on every rank (lowest index on ties). rows <= 1024.
+int ovb_comm_argmax_combine(const ovb_comm* c, int* ids, const float* max_vals, int rows, int shard_size, ovb_stream_t stream);
+// In-place sum of a bf16 tensor of n elements that lives at the same heap offset on every rank (n % 8 == 0).
+int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -194,8 +194,10 @@ class PackedWeight:
 # ------------------------------------------------------------------------------------------ ops
 def gemm(x: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
          act: int = ACT_NONE, out_f32: bool = False, ws: Optional[Workspace] = None, splits: int = 0,
-         block_t: int = 0) -> torch.Tensor:
-    """out[T, N] = act(x[T, K] @ dequant(W)^T + bias) + residual  on the tcgen05 GEMM."""
+         block_t: int = 0, comm=None) -> torch.Tensor:
+    """out[T, N] = act(x[T, K] @ dequant(W)^T + bias) + residual  on the tcgen05 GEMM.
+
+    ``comm`` (a ``parallel.comm.CommStruct``): sum the product over the tensor-parallel ranks inside the epilogue."""
     assert x.dim() == 2 and x.stride(1) == 1
     T, K = x.shape
     assert K == w.K, (K, w.K)
@@ -216,7 +218,7 @@ def gemm(x: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None, r
     a.wmode, a.act, a.out_f32 = w.mode, act, 1 if out_f32 else 0
     a.splits, a.block_t = splits, block_t
     a.w_tiled = 1 if (w.tiled and w.mode in (W_BF16, W_F16)) else 0
-    a.comm = None
+    a.comm = C.addressof(comm) if comm is not None else None
     _check(lib().ovb_gemm(C.byref(a), C.c_void_p(_stream())), "ovb_gemm")
     return out
 

@@ -1,0 +1,188 @@
+"""Tensor-parallel communicator: one process per GPU, peers reach each other's memory over NVLink.
+
+Every rank owns a *symmetric heap*: one device allocation with the same layout on all ranks, exported as a CUDA
+IPC handle and mapped by every peer (handles travel through ``torch.distributed``; NCCL or gloo only carry the
+64-byte handles, never tensor data). The kernels of the library then read and write peers' heaps directly:
+
+* ``gemm_allreduce``  - the row-parallel GEMM with the all-reduce (+ residual add) fused into its epilogue:
+  tiles are pushed to peers as soon as they leave the tensor core, tile by tile (ovb_gemm with ``comm``).
+* ``argmax_combine``  - greedy sampling over vocabulary shards.
+* ``all_reduce``      - small bf16 tensors that live in the heap.
+
+Heap layout (byte offsets are the same on every rank): step counter, flag words per call site, one-shot staging
+(two alternating buffers), two-shot staging, then tensors handed out by ``alloc`` (the residual streams).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+
+from ..ops import cuda as K
+
+MAX_RANKS = 8
+ARGMAX_ROWS_CAP = 1024
+
+
+class CommStruct(C.Structure):
+    """Mirror of ``ovb_comm`` (csrc/cuda/ovb_cuda.h)."""
+
+    _fields_ = [
+        ("rank", C.c_int), ("world", C.c_int),
+        ("heap", C.c_void_p * MAX_RANKS),
+        ("heap_bytes", C.c_int64),
+        ("epoch_off", C.c_int64), ("flags_off", C.c_int64), ("flags_per_site", C.c_int64),
+        ("stage1_off", C.c_int64), ("stage1_bytes", C.c_int64), ("stage2_off", C.c_int64), ("stage2_bytes", C.c_int64),
+        ("num_sites", C.c_int), ("site", C.c_int), ("mode", C.c_int),
+    ]
+
+
+def _round_up(v: int, a: int) -> int:
+    return (v + a - 1) // a * a
+
+
+class HeapLayout:
+    """Offsets of the fixed areas inside the symmetric heap; pure arithmetic, shared by every rank."""
+
+    def __init__(self, world: int, hidden: int, max_tokens: int, num_sites: int, tensor_bytes: int):
+        self.world, self.hidden, self.max_tokens, self.num_sites = world, hidden, max_tokens, num_sites
+        tiles_max = (hidden // 128) * ((max_tokens + 255) // 256 + 1)
+        self.flags_per_site = max(tiles_max * (world + 1), 64 + 2 * world * ARGMAX_ROWS_CAP * 2)
+        self.epoch_off = 0
+        self.flags_off = 256
+        off = self.flags_off + num_sites * self.flags_per_site * 4
+        self.stage1_off = _round_up(off, 1024)
+        self.stage1_bytes = _round_up(world * 128 * hidden * 2, 1024)            # one-shot: T <= 128
+        self.stage2_off = self.stage1_off + 2 * self.stage1_bytes
+        # two-shot: every tile has one owner; rounding the tiles per owner up costs at most `world` extra tiles
+        self.stage2_bytes = _round_up((_round_up(max_tokens, 256) * hidden + world * 256 * 128) * 2, 1024)
+        self.tensors_off = _round_up(self.stage2_off + self.stage2_bytes, 1024)
+        self.heap_bytes = self.tensors_off + _round_up(tensor_bytes, 1024)
+
+
+class PeerCommunicator:
+    def __init__(self, rank: int, world: int, device, group=None):
+        assert 1 <= world <= MAX_RANKS
+        self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
+        self.layout: Optional[HeapLayout] = None
+        self._base = 0
+        self._peer_ptrs: List[int] = []
+        self._bump = 0
+        self._structs = {}
+        self._keep = []
+
+    # ------------------------------------------------------------------ set-up (collective)
+    def setup(self, hidden: int, max_tokens: int, num_layers: int, tensor_bytes: int) -> None:
+        """Allocate this rank's heap, exchange IPC handles, map every peer. Call on all ranks with equal arguments."""
+        import torch.distributed as dist
+        num_sites = 2 * num_layers + 2          # two fused GEMMs per layer, argmax, generic all-reduce
+        self.layout = HeapLayout(self.world, hidden, max_tokens, num_sites, tensor_bytes)
+        lib = K.lib()
+        self._declare(lib)
+        with torch.cuda.device(self.device):
+            base = C.c_void_p()
+            K._check(lib.ovb_comm_alloc(C.c_int64(self.layout.heap_bytes), C.byref(base)), "ovb_comm_alloc")
+            self._base = base.value
+            handle = (C.c_ubyte * 64)()
+            K._check(lib.ovb_comm_export(C.c_void_p(self._base), handle), "ovb_comm_export")
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=self.group)
+            self._peer_ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self._peer_ptrs.append(self._base)
+                    continue
+                buf = (C.c_ubyte * 64).from_buffer_copy(handles[r])
+                p = C.c_void_p()
+                K._check(lib.ovb_comm_open(buf, C.byref(p)), "ovb_comm_open")
+                self._peer_ptrs.append(p.value)
+        self._bump = self.layout.tensors_off
+        dist.barrier(group=self.group)
+
+    @staticmethod
+    def _declare(lib) -> None:
+        lib.ovb_comm_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p)]
+        lib.ovb_comm_export.argtypes = [C.c_void_p, C.c_void_p]
+        lib.ovb_comm_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        lib.ovb_comm_close.argtypes = [C.c_void_p]
+        lib.ovb_comm_free.argtypes = [C.c_void_p]
+        lib.ovb_comm_step_begin.argtypes = [C.POINTER(CommStruct), C.c_void_p]
+        lib.ovb_comm_argmax_combine.argtypes = [C.POINTER(CommStruct), C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        lib.ovb_comm_allreduce_bf16.argtypes = [C.POINTER(CommStruct), C.c_void_p, C.c_int64, C.c_void_p]
+
+    def close(self) -> None:
+        if not self._base:
+            return
+        lib = K.lib()
+        torch.cuda.synchronize(self.device)
+        for r, p in enumerate(self._peer_ptrs):
+            if r != self.rank and p:
+                lib.ovb_comm_close(C.c_void_p(p))
+        lib.ovb_comm_free(C.c_void_p(self._base))
+        self._base, self._peer_ptrs = 0, []
+
+    # ------------------------------------------------------------------ heap tensors
+    def alloc(self, shape, dtype=torch.bfloat16) -> torch.Tensor:
+        """A tensor inside the symmetric heap (same offset on every rank when every rank allocates in the same order)."""
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        off = _round_up(self._bump, 256)
+        if off + nbytes > self.layout.heap_bytes:
+            raise RuntimeError("symmetric heap exhausted: %d bytes wanted at offset %d of %d" % (nbytes, off, self.layout.heap_bytes))
+        self._bump = off + nbytes
+        t = _wrap_device_memory(self._base + off, nbytes, self.device).view(dtype).reshape(tuple(shape))
+        self._keep.append(t)
+        return t
+
+    def in_heap(self, t: torch.Tensor) -> bool:
+        return self._base <= t.data_ptr() < self._base + self.layout.heap_bytes
+
+    # ------------------------------------------------------------------ collectives
+    def struct(self, site: int, mode: int = 0) -> CommStruct:
+        key = (site, mode)
+        s = self._structs.get(key)
+        if s is None:
+            L = self.layout
+            s = CommStruct()
+            s.rank, s.world = self.rank, self.world
+            for r in range(self.world):
+                s.heap[r] = self._peer_ptrs[r]
+            s.heap_bytes = L.heap_bytes
+            s.epoch_off, s.flags_off, s.flags_per_site = L.epoch_off, L.flags_off, L.flags_per_site
+            s.stage1_off, s.stage1_bytes, s.stage2_off, s.stage2_bytes = L.stage1_off, L.stage1_bytes, L.stage2_off, L.stage2_bytes
+            s.num_sites, s.site, s.mode = L.num_sites, site, mode
+            self._structs[key] = s
+        return s
+
+    def step_begin(self) -> None:
+        K._check(K.lib().ovb_comm_step_begin(C.byref(self.struct(0)), C.c_void_p(K._stream())), "ovb_comm_step_begin")
+
+    def gemm_allreduce(self, x: torch.Tensor, w: "K.PackedWeight", h: torch.Tensor, ws, site: int, mode: int = 0) -> None:
+        """h += sum over ranks of x @ W_shard^T (h replicated, must live in the heap)."""
+        K.gemm(x, w, out=h, residual=h, ws=ws, comm=self.struct(site, mode))
+
+    def argmax_combine(self, ids: torch.Tensor, max_vals: torch.Tensor, shard_size: int) -> None:
+        site = self.layout.num_sites - 2
+        K._check(K.lib().ovb_comm_argmax_combine(C.byref(self.struct(site)), C.c_void_p(ids.data_ptr()), C.c_void_p(max_vals.data_ptr()),
+                                                 C.c_int(ids.numel()), C.c_int(shard_size), C.c_void_p(K._stream())), "ovb_comm_argmax_combine")
+
+    def all_reduce(self, t: torch.Tensor) -> None:
+        assert t.dtype == torch.bfloat16 and t.is_contiguous() and self.in_heap(t)
+        site = self.layout.num_sites - 1
+        K._check(K.lib().ovb_comm_allreduce_bf16(C.byref(self.struct(site)), C.c_void_p(t.data_ptr()), C.c_int64(t.numel()),
+                                                 C.c_void_p(K._stream())), "ovb_comm_allreduce_bf16")
+
+
+class _DeviceMemory:
+    """Exposes raw device memory through ``__cuda_array_interface__`` so that torch can view it without a copy."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+def _wrap_device_memory(ptr: int, nbytes: int, device) -> torch.Tensor:
+    with torch.cuda.device(device):
+        return torch.as_tensor(_DeviceMemory(ptr, nbytes), device=device)

@@ -140,7 +140,7 @@ class StepBuffers:
     The host fills a pinned mirror and uploads it with ONE copy per step.
     """
 
-    def __init__(self, cfg: LlmConfig, Tcap: int, Bcap: int, max_blocks_per_seq: int, device, tp_size: int = 1):
+    def __init__(self, cfg: LlmConfig, Tcap: int, Bcap: int, max_blocks_per_seq: int, device, tp_size: int = 1, comm=None):
         self.Tcap, self.Bcap, self.max_blocks = Tcap, Bcap, max_blocks_per_seq
         sizes = [("ids", Tcap), ("positions", Tcap), ("slot_map", Tcap), ("tok_src", Tcap), ("tok_dst", Bcap),
                  ("logit_idx", Bcap), ("past_lens", Bcap),
@@ -158,7 +158,8 @@ class StepBuffers:
         H, D = cfg.hidden_size, cfg.head_dim
         hq, hkv, ffn = cfg.num_heads // tp_size, cfg.num_kv_heads // tp_size, cfg.ffn_size // tp_size
         bf = dict(dtype=torch.bfloat16, device=device)
-        self.h = torch.empty((Tcap, H), **bf)
+        # with tensor parallelism the residual stream lives in the communicator's symmetric heap: peers write into it
+        self.h = comm.alloc((Tcap, H)) if comm is not None else torch.empty((Tcap, H), **bf)
         self.x = torch.empty((Tcap, H), **bf)
         self.qkv = torch.empty((Tcap, (hq + 2 * hkv) * D), **bf)
         self.attn = torch.empty((Tcap, hq * D), **bf)
@@ -209,8 +210,12 @@ class CudaLlmExecutor:
                         for _ in range(cfg.num_layers)]
         self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
         self.ws = K.Workspace(self.device)
-        self.prefill = StepBuffers(cfg, max_batch_tokens, max_seqs, max_blocks_per_seq, self.device, self.tp_size)
-        self.decode = StepBuffers(cfg, max_seqs, max_seqs, max_blocks_per_seq, self.device, self.tp_size)
+        if self.tp_size > 1:
+            if comm is None:
+                raise ValueError("tensor-parallel weights need a communicator")
+            comm.setup(cfg.hidden_size, max_batch_tokens, cfg.num_layers, tensor_bytes=(max_batch_tokens + max_seqs + 2) * cfg.hidden_size * 2 + 4096)
+        self.prefill = StepBuffers(cfg, max_batch_tokens, max_seqs, max_blocks_per_seq, self.device, self.tp_size, comm if self.tp_size > 1 else None)
+        self.decode = StepBuffers(cfg, max_seqs, max_seqs, max_blocks_per_seq, self.device, self.tp_size, comm if self.tp_size > 1 else None)
         # token sampled last for every request slot (device-side feedback between chained steps)
         self.last_token = torch.zeros(max(max_seqs, 1) * 4, dtype=torch.int32, device=self.device)
         self._graphs = {}
@@ -224,9 +229,12 @@ class CudaLlmExecutor:
         ids = sb.view("ids")[:T]
         positions, slot_map = sb.view("positions"), sb.view("slot_map")
         h, x, qkv, attn, gu, act = sb.h[:T], sb.x[:T], sb.qkv[:T], sb.attn[:T], sb.gu[:T], sb.act[:T]
+        n = 3
+        if self.tp_size > 1:
+            self.comm.step_begin()
+            n += 1
         K.resolve_ids(ids, sb.view("tok_src")[:T], self.last_token)
         K.embedding(ids, w.embed, out=h)
-        n = 3
         for l, lw in enumerate(w.layers):
             K.rmsnorm(h, lw.norm1, cfg.rms_eps, out=x)
             K.gemm(x, lw.qkv, out=qkv, ws=ws)
@@ -237,11 +245,11 @@ class CudaLlmExecutor:
                               sb.view("block_indices_begins")[:B + 1], self.hq, self.hkv, D,
                               max_context_len=shp.max_ctx, max_q_len=shp.max_q_len, sliding_window=cfg.sliding_window,
                               block_size=self.block_size, out=attn, ws=ws)
-            self._row_parallel(attn, lw.o, h)
+            self._row_parallel(attn, lw.o, h, 2 * l)
             K.rmsnorm(h, lw.norm2, cfg.rms_eps, out=x)
             K.gemm(x, lw.gate_up, out=gu, ws=ws)
             K.silu_mul(gu, out=act)
-            self._row_parallel(act, lw.down, h)
+            self._row_parallel(act, lw.down, h, 2 * l + 1)
             n += 9
         # logits only for the last token of every sequence
         last_h, last_x = sb.last_h[:B], sb.last_x[:B]
@@ -252,12 +260,12 @@ class CudaLlmExecutor:
         self._sample(sb, B)
         self.kernel_launches += n + 5
 
-    def _row_parallel(self, x: torch.Tensor, wt: K.PackedWeight, h: torch.Tensor) -> None:
+    def _row_parallel(self, x: torch.Tensor, wt: K.PackedWeight, h: torch.Tensor, site: int) -> None:
         """h += x @ W^T summed over tensor-parallel ranks (h is the replicated residual stream)."""
         if self.tp_size == 1:
             K.gemm(x, wt, out=h, residual=h, ws=self.ws)
         else:
-            self.comm.gemm_allreduce(x, wt, h, self.ws)
+            self.comm.gemm_allreduce(x, wt, h, self.ws, site)
 
     def _sample(self, sb: StepBuffers, B: int) -> None:
         if self.tp_size == 1:

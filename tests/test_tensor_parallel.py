@@ -1,0 +1,47 @@
+"""Tensor parallelism: heap layout arithmetic on CPU; the fused GEMM + all-reduce and the TP model on 2 GPUs."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from openvino_b200.parallel.comm import CommStruct, HeapLayout
+
+
+def test_heap_layout_is_disjoint_and_large_enough():
+    for world, hidden, tokens, layers in ((2, 4096, 8192, 32), (8, 4096, 8192, 32), (4, 8192, 4096, 80), (2, 256, 256, 2)):
+        L = HeapLayout(world, hidden, tokens, 2 * layers + 2, tensor_bytes=tokens * hidden * 2)
+        areas = [(L.epoch_off, 4), (L.flags_off, L.num_sites * L.flags_per_site * 4), (L.stage1_off, 2 * L.stage1_bytes),
+                 (L.stage2_off, L.stage2_bytes), (L.tensors_off, L.heap_bytes - L.tensors_off)]
+        for (a, n), (b, _) in zip(areas, areas[1:]):
+            assert a + n <= b
+        assert L.heap_bytes - L.tensors_off >= tokens * hidden * 2
+        # one-shot: T <= 128 -> one token tile per weight tile
+        tiles = hidden // 128
+        assert world * tiles * 128 * 128 * 2 <= L.stage1_bytes
+        # two-shot: worst case T = tokens with 256-token tiles
+        t_tiles = (tokens + 255) // 256
+        total = tiles * t_tiles
+        assert world * ((total + world - 1) // world) * 256 * 128 * 2 <= L.stage2_bytes
+        assert total * (world + 1) <= L.flags_per_site
+        for off in (L.stage1_off, L.stage2_off, L.tensors_off):
+            assert off % 256 == 0
+
+
+def test_comm_struct_matches_the_c_layout():
+    # int rank, world; void* heap[8]; int64 x 8; int x 3 (+ padding to 8)
+    assert C.sizeof(CommStruct) == 8 + 64 + 8 * 8 + 16
+    assert CommStruct.heap.offset == 8 and CommStruct.heap_bytes.offset == 72 and CommStruct.num_sites.offset == 136
+
+
+@pytest.mark.gpu
+def test_tensor_parallel_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tp_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29671", worker], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])

@@ -1,0 +1,135 @@
+"""Worker of the tensor-parallel GPU tests: run as ``python -m torch.distributed.run --nproc-per-node N tests/tp_worker.py``.
+
+Checks, on N GPUs of one node: the GEMM with fused all-reduce (one-shot, two-shot, with and without split-K)
+against an fp32 reference of the full product; the sharded argmax; a small-tensor all-reduce; and that a
+tensor-parallel tiny Llama generates the tokens of the single-GPU model. Prints ``TP_WORKER_OK`` on rank 0.
+"""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=dev)
+    from openvino_b200.ops import cuda as K
+    from openvino_b200.parallel.comm import PeerCommunicator
+
+    H = 1024
+    comm = PeerCommunicator(rank, world, dev)
+    comm.setup(hidden=H, max_tokens=1024, num_layers=4, tensor_bytes=(1024 + 64) * H * 2 + 4096)
+    ws = K.Workspace(dev)
+    h_big = comm.alloc((1024, H))
+    site = 0
+    failures = []
+    # (T, K per rank, forced mode, forced splits)
+    cases = [(8, 256, 0, 0), (64, 512, 1, 1), (64, 1792, 1, 4), (128, 256, 2, 1), (300, 512, 0, 0), (1000, 256, 2, 0), (40, 1024, 2, 2)]
+    for T, Kr, mode, splits in cases:
+        g = torch.Generator(device="cpu").manual_seed(1000 + T + Kr)
+        x_full = torch.randn(T, Kr * world, generator=g)
+        w_full = torch.randn(H, Kr * world, generator=g) * 0.05
+        res = torch.randn(T, H, generator=g)
+        x = x_full[:, rank * Kr:(rank + 1) * Kr].to(dev, torch.bfloat16).contiguous()
+        w = w_full[:, rank * Kr:(rank + 1) * Kr].to(dev, torch.bfloat16).contiguous()
+        pw = K.PackedWeight.from_dense(w)
+        h = h_big[:T]
+        h.copy_(res.to(dev, torch.bfloat16))
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.step_begin()
+        K.gemm(x, pw, out=h, residual=h, ws=ws, splits=splits, comm=comm.struct(site, mode))
+        torch.cuda.synchronize()
+        K.check_status("fused gemm T=%d" % T)
+        ref = x_full.to(torch.bfloat16).float() @ w_full.to(torch.bfloat16).float().t() + res.to(torch.bfloat16).float()
+        err = ((h.float().cpu() - ref).norm() / ref.norm()).item()
+        # every rank must hold the same bits
+        gathered = [torch.empty_like(h) for _ in range(world)]
+        dist.all_gather(gathered, h.contiguous())
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+        if err > 1.5e-2 or not same:
+            failures.append(("gemm", T, Kr, mode, splits, err, same))
+        site = (site + 1) % 8
+
+    # sharded argmax
+    comm.step_begin()
+    rows, shard = 37, 500
+    vals = torch.randn(rows, device=dev)
+    ids = torch.randint(0, shard, (rows,), device=dev, dtype=torch.int32)
+    all_vals = [torch.empty_like(vals) for _ in range(world)]
+    all_ids = [torch.empty_like(ids) for _ in range(world)]
+    dist.all_gather(all_vals, vals)
+    dist.all_gather(all_ids, ids)
+    comm.argmax_combine(ids, vals, shard)
+    torch.cuda.synchronize()
+    K.check_status("argmax_combine")
+    sv = torch.stack(all_vals)
+    best = sv.argmax(0)
+    want = torch.stack(all_ids).gather(0, best[None].long())[0] + best.int() * shard
+    if not torch.equal(ids, want.int()):
+        failures.append(("argmax", ids.tolist(), want.tolist()))
+
+    # small all-reduce
+    comm.step_begin()
+    t = comm.alloc((4096,))
+    t.copy_(torch.full((4096,), float(rank + 1), device=dev, dtype=torch.bfloat16))
+    torch.cuda.synchronize()
+    dist.barrier()
+    comm.all_reduce(t)
+    torch.cuda.synchronize()
+    K.check_status("all_reduce")
+    if not torch.equal(t.float(), torch.full((4096,), float(world * (world + 1) // 2), device=dev)):
+        failures.append(("all_reduce", t[:4].tolist()))
+
+    # end to end: the tensor-parallel model generates what the single-GPU model generates
+    from openvino_b200.genai.pipeline import ContinuousBatchingPipeline, GenerationConfig
+    from openvino_b200.genai.scheduler import SchedulerConfig
+    from openvino_b200.models import llama
+    from openvino_b200.models.llm_config import TINY_LLAMA
+    from openvino_b200.runtime.cuda_llm import CudaLlmExecutor, LlmWeights
+    cfg = TINY_LLAMA.with_(num_heads=8, num_kv_heads=world if world > 2 else 2, ffn_size=1024)
+    state = llama.random_float_state(cfg, seed=3)
+    gprompts = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gprompts).tolist() for n in (150, 9, 33)]
+    gen = GenerationConfig(max_new_tokens=8, ignore_eos=True)
+    sc = SchedulerConfig(max_num_batched_tokens=256, max_num_seqs=4, num_kv_blocks=64, block_size=16, max_blocks_per_seq=12)
+    tp_comm = PeerCommunicator(rank, world, dev)
+    ex = CudaLlmExecutor(cfg, LlmWeights.from_float(cfg, state, dev, tp_rank=rank, tp_size=world), num_kv_blocks=64, block_size=16,
+                         max_batch_tokens=256, max_seqs=4, max_blocks_per_seq=12, device=dev, comm=tp_comm)
+    got = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, gen)]
+    K.check_status("tp generate")
+    ex1 = CudaLlmExecutor(cfg, LlmWeights.from_float(cfg, state, dev), num_kv_blocks=64, block_size=16, max_batch_tokens=256,
+                          max_seqs=4, max_blocks_per_seq=12, device=dev)
+    want1 = [r.tokens for r in ContinuousBatchingPipeline(ex1, sc).generate(prompts, gen)]
+    agree = sum(int(a == b) for g_, w_ in zip(got, want1) for a, b in zip(g_, w_))
+    total = sum(len(w_) for w_ in want1)
+    if agree < total - 3:     # bf16 partial sums may flip a near-tie late in a sequence
+        failures.append(("generate", got, want1))
+    obj = [None] * world
+    dist.all_gather_object(obj, got)
+    if any(o != obj[0] for o in obj):
+        failures.append(("ranks disagree", obj))
+
+    all_fail = [None] * world
+    dist.all_gather_object(all_fail, failures)
+    torch.cuda.synchronize()
+    dist.barrier()
+    tp_comm.close()
+    comm.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        if any(all_fail):
+            print("TP_WORKER_FAILED", all_fail)
+            sys.exit(1)
+        print("TP_WORKER_OK", "tokens agree %d/%d" % (agree, total))
+
+
+if __name__ == "__main__":
+    main()
