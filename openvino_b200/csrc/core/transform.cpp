@@ -8,7 +8,6 @@
 // src/core/src/pass/{make_stateful,stateful_to_stateless}.cpp; the weight-compression algorithm itself
 // lives outside the reference tree (NNCF) - this file emits the IR pattern that
 // pattern_blocks/compressed_weights_block.cpp:17-75 recognises.
-#include <regex>
 
 #include "pass.hpp"
 
@@ -376,15 +375,24 @@ bool stateful_to_stateless(const ModelPtr& m) {
         if (n->type == "ReadValue") reads[n->attr_str("variable_id")] = n;
         if (n->type == "Assign") assigns[n->attr_str("variable_id")] = n;
     }
-    static const std::regex re("(past_key_values\\.[0-9]+\\.(key|value))(present\\.[0-9]+\\.(key|value))");
+    // "past_key_values.3.keypresent.3.key" -> ("past_key_values.3.key", "present.3.key"); plain string search on purpose:
+    // std::regex must not be used in this module (its template code clashes with the copy exported by libtorch).
+    auto split_kv_name = [](const std::string& id, std::string& in_name, std::string& out_name) {
+        if (id.rfind("past_key_values.", 0) != 0) return false;
+        const size_t pos = id.find("present.");
+        if (pos == std::string::npos || pos == 0) return false;
+        in_name = id.substr(0, pos);
+        out_name = id.substr(pos);
+        return true;
+    };
     for (auto& kv : reads) {
         auto it = assigns.find(kv.first);
         if (it == assigns.end()) continue;
         std::string in_name = kv.first + "_in", out_name = kv.first + "_out";
-        std::smatch mm;
-        if (std::regex_match(kv.first, mm, re)) { in_name = mm[1]; out_name = mm[3]; }
+        split_kv_name(kv.first, in_name, out_name);
         NodePtr rv = kv.second, as = it->second;
         auto p = make_parameter(rv->outs[0].et, rv->outs[0].shape, in_name);
+
         replace_output(rv->output(0), p->output(0));
         auto r = make_result(as->input(0));
         r->name = out_name;

@@ -1,0 +1,165 @@
+"""``Model`` builders for the benchmark architectures, written the way exporters write them.
+
+``build_llama`` emits the stateful decoder that optimum-style exports of Llama-family models contain: inputs
+``input_ids`` / ``attention_mask`` / ``position_ids`` / ``beam_idx``, per-layer ReadValue -> Gather(beam_idx) ->
+Concat -> Assign KV state, decomposed RMSNorm and half-rotate RoPE, ScaledDotProductAttention with a causal mask,
+gate/up/down MLP, and (optionally) int4/int8 group-compressed weights as Constant(u4) -> Convert -> Subtract(zp) ->
+Multiply(scale) -> Reshape. The graph-level fusions and the SDPA -> PagedAttention rewrite are tested on it, and the
+CUDA device turns it into its LLM program.
+
+The same topology is described by the reference's GGUF builder (src/frontends/gguf/src/builder/blocks/attention.cpp:51-250,
+blocks/ffn.cpp, arch/decoder_builder.cpp).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from .. import opset as ops
+from .._graph import Model, Node, Output, constant, parameter, result
+from .._tensor import Tensor
+from .._types import PartialShape, Type
+from ..utils import quant
+from .llm_config import LlmConfig
+
+
+def _f32(t: torch.Tensor) -> np.ndarray:
+    return t.detach().float().cpu().numpy()
+
+
+def _i64(v) -> Node:
+    return constant(np.array(v, dtype=np.int64))
+
+
+def _linear_weight(name: str, w: torch.Tensor, cfg: LlmConfig, compress: Optional[str]) -> Output:
+    """[N, K] weight as an fp32 value: plain Constant, or the decompression sub-graph of a compressed one."""
+    if compress is None:
+        return constant(_f32(w), name=name).output(0)
+    N, Kd = w.shape
+    g = cfg.group_size
+    G = Kd // g
+    if compress == "int4":
+        q, s, z = quant.quantize_u4_asym(w.float(), g)            # q [N, K] uint8 values 0..15, s/z [N, G]
+        qt = Tensor(q.reshape(N, G, g).cpu().numpy().astype(np.float32)).astype(Type.u4)
+        zt = Tensor(z.reshape(N, G, 1).cpu().numpy().astype(np.float32)).astype(Type.u4)
+    elif compress == "int8":
+        q, s, z = quant.quantize_u8_asym(w.float(), g)
+        qt = Tensor(q.reshape(N, G, g).cpu().numpy().astype(np.uint8))
+        zt = Tensor(z.reshape(N, G, 1).cpu().numpy().astype(np.uint8))
+    else:
+        raise ValueError("compress must be None, 'int4' or 'int8'")
+    wq = constant(qt, name=name + "/compressed")
+    zp = constant(zt, name=name + "/zero_point")
+    sc = constant(s.reshape(N, G, 1).cpu().numpy().astype(np.float16), name=name + "/scale")
+    x = ops.subtract(ops.convert(wq, "f16"), ops.convert(zp, "f16"))
+    x = ops.multiply(x, sc)
+    x = ops.reshape(x, _i64([N, Kd]), False)
+    return ops.convert(x, "f32", name=name + "/decompressed").output(0)
+
+
+def _rms(x: Output, gamma: np.ndarray, eps: float, name: str) -> Output:
+    sq = ops.power(x, np.float32(2.0))
+    var = ops.reduce_mean(sq, _i64([-1]), True)
+    inv = ops.divide(np.float32(1.0), ops.sqrt(ops.add(var, np.float32(eps))))
+    return ops.multiply(ops.multiply(x, inv), constant(gamma, name=name + ".weight"), name=name).output(0)
+
+
+def _rope(x: Output, cos: Output, sin: Output, D: int) -> Output:
+    """x [B, H, L, D]; cos/sin [B, 1, L, D]: x * cos + rotate_half(x) * sin."""
+    lo = ops.slice(x, _i64([0]), _i64([D // 2]), _i64([1]), _i64([3]))
+    hi = ops.slice(x, _i64([D // 2]), _i64([D]), _i64([1]), _i64([3]))
+    rot = ops.concat([ops.negative(hi).output(0), lo.output(0)], 3)
+    return ops.add(ops.multiply(x, cos), ops.multiply(rot, sin)).output(0)
+
+
+def build_llama(cfg: LlmConfig, state: Dict[str, torch.Tensor], compress: Optional[str] = None, stateful: bool = True) -> Model:
+    """Stateful decoder ``Model`` with fp32 activations. ``compress``: None | "int4" | "int8" (group-wise, asymmetric)."""
+    H, D, Hq, Hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    input_ids = parameter(PartialShape([-1, -1]), "i64", "input_ids")
+    attention_mask = parameter(PartialShape([-1, -1]), "i64", "attention_mask")
+    position_ids = parameter(PartialShape([-1, -1]), "i64", "position_ids")
+    beam_idx = parameter(PartialShape([-1]), "i32", "beam_idx")
+    for p in (input_ids, attention_mask, position_ids, beam_idx):
+        p.output(0).set_names({p.get_friendly_name()})
+
+    embed = constant(_f32(state["embed_tokens"]), name="model.embed_tokens.weight")
+    h = ops.gather(embed, input_ids, _i64(0), name="embed").output(0)             # [B, L, H]
+
+    # rotary tables from position ids: [B, L] -> cos/sin [B, 1, L, D]
+    inv_freq = (cfg.rope_theta ** (-np.arange(0, D, 2, dtype=np.float32) / D)).astype(np.float32)
+    pos = ops.convert(ops.unsqueeze(position_ids, _i64([2])), "f32")               # [B, L, 1]
+    ang = ops.multiply(pos, constant(inv_freq.reshape(1, 1, -1)))                  # [B, L, D/2]
+    ang = ops.concat([ang.output(0), ang.output(0)], 2)
+    cos = ops.unsqueeze(ops.cos(ang), _i64([1])).output(0)
+    sin = ops.unsqueeze(ops.sin(ang), _i64([1])).output(0)
+
+    # additive causal + padding mask [B, 1, L, S]: position of key j must be <= position of query i and mask[j] == 1
+    shape_ids = ops.shape_of(input_ids)
+    L = ops.gather(shape_ids, _i64([1]), _i64(0))
+    S = ops.gather(ops.shape_of(attention_mask), _i64([1]), _i64(0))
+    past = ops.subtract(S, L)
+    q_pos = ops.add(ops.range(_i64(0), ops.squeeze(L), _i64(1), "i64"), ops.squeeze(past))
+    k_pos = ops.range(_i64(0), ops.squeeze(S), _i64(1), "i64")
+    causal = ops.less_equal(ops.unsqueeze(k_pos, _i64([0])), ops.unsqueeze(q_pos, _i64([1])))   # [L, S]
+    pad_ok = ops.unsqueeze(ops.not_equal(attention_mask, _i64(0)), _i64([1, 2]))                # [B, 1, 1, S]
+    allowed = ops.logical_and(ops.unsqueeze(causal, _i64([0, 1])), pad_ok)
+    mask = ops.select(allowed, np.float32(0.0), np.float32(-65504.0), name="attention_bias").output(0)
+
+    batch = ops.gather(shape_ids, _i64([0]), _i64(0))
+    sinks = []
+    for l in range(cfg.num_layers):
+        p = "layers.%d." % l
+        n = "model.layers.%d." % l
+        x = _rms(h, _f32(state[p + "input_layernorm"]), cfg.rms_eps, n + "input_layernorm")
+
+        def proj(name, inp, key):
+            return ops.matmul(inp, _linear_weight(n + name + ".weight", state[p + key], cfg, compress), False, True, name=n + name).output(0)
+
+        def heads(t: Output, nh: int) -> Output:   # [B, L, nh*D] -> [B, nh, L, D]
+            r = ops.reshape(t, _i64([0, 0, nh, D]), True)
+            return ops.transpose(r, _i64([0, 2, 1, 3])).output(0)
+
+        q = _rope(heads(proj("self_attn.q_proj", x, "q_proj"), Hq), cos, sin, D)
+        k = _rope(heads(proj("self_attn.k_proj", x, "k_proj"), Hkv), cos, sin, D)
+        v = heads(proj("self_attn.v_proj", x, "v_proj"), Hkv)
+
+        if stateful:
+            init_shape = ops.concat([batch.output(0), _i64([Hkv, 0, D]).output(0)], 0)
+            k_init = ops.broadcast(np.float32(0.0), init_shape)
+            v_init = ops.broadcast(np.float32(0.0), init_shape)
+            kid, vid = "past_key_values.%d.keypresent.%d.key" % (l, l), "past_key_values.%d.valuepresent.%d.value" % (l, l)
+            k_past = ops.gather(ops.read_value(k_init, kid, "f32", PartialShape([-1, Hkv, -1, D])), beam_idx, _i64(0))
+            v_past = ops.gather(ops.read_value(v_init, vid, "f32", PartialShape([-1, Hkv, -1, D])), beam_idx, _i64(0))
+            k_all = ops.concat([k_past.output(0), k], 2, name=n + "self_attn.k_cache")
+            v_all = ops.concat([v_past.output(0), v], 2, name=n + "self_attn.v_cache")
+            sinks += [ops.assign(k_all, kid), ops.assign(v_all, vid)]
+            k_use, v_use = k_all.output(0), v_all.output(0)
+        else:
+            k_use, v_use = k, v
+        if Hq != Hkv:   # grouped-query attention: repeat every KV head Hq / Hkv times
+            G = Hq // Hkv
+
+            def expand(t: Output) -> Output:
+                u = ops.unsqueeze(t, _i64([2]))                                             # [B, Hkv, 1, S, D]
+                bshape = ops.concat([batch.output(0), _i64([Hkv, G]).output(0), ops.gather(ops.shape_of(t), _i64([2]), _i64(0)).output(0),
+                                     _i64([D]).output(0)], 0)
+                b = ops.broadcast(u, bshape)
+                return ops.reshape(b, _i64([0, Hq, -1, D]), True).output(0)
+            k_use, v_use = expand(k_use), expand(v_use)
+        attn = ops.scaled_dot_product_attention(q, k_use, v_use, mask, name=n + "self_attn.sdpa")
+        a = ops.reshape(ops.transpose(attn, _i64([0, 2, 1, 3])), _i64([0, 0, Hq * D]), True)
+        h = ops.add(h, proj("self_attn.o_proj", a, "o_proj")).output(0)
+
+        x = _rms(h, _f32(state[p + "post_attention_layernorm"]), cfg.rms_eps, n + "post_attention_layernorm")
+        gate = ops.swish(proj("mlp.gate_proj", x, "gate_proj"))
+        up = proj("mlp.up_proj", x, "up_proj")
+        h = ops.add(h, proj("mlp.down_proj", ops.multiply(gate, up), "down_proj")).output(0)
+
+    x = _rms(h, _f32(state["norm"]), cfg.rms_eps, "model.norm")
+    logits = ops.matmul(x, _linear_weight("lm_head.weight", state["lm_head"], cfg, compress), False, True, name="lm_head")
+    logits.output(0).set_names({"logits"})
+    m = Model([result(logits, "logits")], [input_ids, attention_mask, position_ids, beam_idx], cfg.name, sinks)
+    m.set_rt_info("llama", ["model_info", "architecture"])
+    return m

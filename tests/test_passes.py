@@ -1,0 +1,265 @@
+"""Graph passes: infrastructure (Manager, MatcherPass, patterns from Python) and the named transformations,
+checked structurally and by comparing evaluation before and after (the reference's TransformationTestsF pattern,
+src/tests/test_utils/common_test_utils/include/common_test_utils/ov_test_utils.hpp)."""
+from collections import Counter
+
+import numpy as np
+import pytest
+import torch
+
+import openvino_b200 as ov
+from openvino_b200 import Model, PartialShape, Tensor, Type
+from openvino_b200 import _offline_transformations as offline
+from openvino_b200 import opset as ops
+from openvino_b200 import passes
+from openvino_b200.models import llama
+from openvino_b200.models.llm_config import TINY_LLAMA
+from openvino_b200.models.ov_builders import build_llama
+
+CFG = TINY_LLAMA.with_(vocab_size=128, hidden_size=128, num_heads=4, num_kv_heads=2, head_dim=64, ffn_size=256, group_size=64, num_layers=2)
+
+
+def types(m):
+    return Counter(n.get_type_name() for n in m.get_ops())
+
+
+def infer(m, *arrays):
+    return ov.compile_model(m, "CPU")(list(arrays))
+
+
+def test_constant_folding_and_nop_elimination():
+    x = ops.parameter([2, 3], "f32")
+    c = ops.add(ops.constant(np.ones((2, 3), np.float32)), ops.multiply(np.float32(2), np.float32(3)))
+    y = ops.add(x, c)
+    y = ops.reshape(y, [2, 3], False)            # no-op reshape
+    y = ops.convert(y, "f32")                    # no-op convert
+    y = ops.transpose(y, [0, 1])                 # identity transpose
+    m = Model([y], [x], "cf")
+    before = infer(m, np.zeros((2, 3), np.float32))[0]
+    pm = passes.Manager()
+    pm.register_pass(passes.ConstantFolding())
+    pm.register_pass("NopElimination")
+    assert pm.run_passes(m)
+    t = types(m)
+    assert t["Add"] == 1 and t["Multiply"] == 0 and t["Reshape"] == 0 and t["Convert"] == 0 and t["Transpose"] == 0
+    np.testing.assert_array_equal(infer(m, np.zeros((2, 3), np.float32))[0], before)
+    assert [name for name, ms, changed in pm.get_timings()] == ["ConstantFolding", "NopElimination"]
+
+
+def test_python_matcher_pass_rewrites_graph():
+    x = ops.parameter([4], "f32")
+    y = ops.relu(ops.add(x, np.float32(1)))
+    m = Model([ops.exp(y)], [x], "mp")
+    add_p = passes.WrapType("opset1.Add", [passes.AnyInput(), passes.WrapType("Constant")])
+    relu_p = passes.WrapType("Relu", [add_p], passes.consumers_count(1))
+    seen = []
+
+    def callback(matcher):
+        root = matcher.get_match_root()
+        pmap = matcher.get_pattern_value_map()
+        assert add_p in pmap and pmap[relu_p].get_node() == root
+        seen.append(root.get_type_name())
+        new = ops.sigmoid(pmap[add_p])
+        root.output(0).replace(new.output(0))
+        return True
+    p = passes.MatcherPass(passes.Matcher(relu_p, "ReluToSigmoid"), callback)
+    pm = passes.Manager()
+    pm.register_pass(p)
+    assert pm.run_passes(m) and seen == ["Relu"]
+    assert types(m)["Relu"] == 0 and types(m)["Sigmoid"] == 1
+    v = np.array([0.0, 1.0, -1.0, 2.0], np.float32)
+    np.testing.assert_allclose(infer(m, v)[0], np.exp(1 / (1 + np.exp(-(v + 1)))), rtol=1e-6)
+
+
+def test_matcher_or_optional_and_predicates():
+    x = ops.parameter([2, 2], "f32")
+    a = ops.relu(ops.convert(x, "f32"))
+    b = ops.sigmoid(x)
+    pat = passes.Or([passes.WrapType("Relu", [passes.Optional("Convert", [passes.AnyInput()])]), passes.WrapType("Tanh")])
+    mt = passes.Matcher(pat, "m")
+    assert mt.match(a.output(0)) and not mt.match(b.output(0))
+    assert passes.Matcher(passes.WrapType("Relu", [passes.AnyInput(passes.rank_equals(3))])).match(a.output(0)) is False
+    assert passes.Matcher(passes.AnyInput(passes.type_matches(Type.f32))).match(b.output(0))
+
+
+def test_custom_model_pass_and_disable():
+    class Count(passes.ModelPass):
+        def __init__(self):
+            super().__init__("Count")
+            self.n = 0
+
+        def run_on_model(self, model):
+            self.n = len(model.get_ops())
+            return False
+    x = ops.parameter([1], "f32")
+    m = Model([ops.add(x, ops.multiply(np.float32(2), np.float32(3)))], [x], "c")
+    cnt = Count()
+    pm = passes.Manager()
+    pm.register_pass("ConstantFolding")
+    pm.register_pass(cnt)
+    pm.disable("ConstantFolding")
+    assert pm.run_passes(m) is False and cnt.n == 6 and types(m)["Multiply"] == 1
+    pm.enable("ConstantFolding")
+    assert pm.run_passes(m) and cnt.n == 4
+
+
+def test_batch_norm_decomposition_and_fp16_compression():
+    rng = np.random.default_rng(0)
+    x = ops.parameter([1, 4, 5, 5], "f32")
+    g, b, mu, var = (rng.uniform(0.5, 1.5, 4).astype(np.float32) for _ in range(4))
+    y = ops.batch_norm_inference(ops.convolution(x, rng.standard_normal((4, 4, 3, 3)).astype(np.float32), [1, 1], [1, 1], [1, 1], [1, 1]), g, b, mu, var, 1e-5)
+    m = Model([y], [x], "bn")
+    inp = rng.standard_normal((1, 4, 5, 5)).astype(np.float32)
+    before = infer(m, inp)[0]
+    offline.apply_moc_transformations(m)
+    assert types(m)["BatchNormInference"] == 0
+    np.testing.assert_allclose(infer(m, inp)[0], before, rtol=1e-4, atol=1e-5)
+    offline.compress_model_transformation(m)
+    consts = [n for n in m.get_ops() if n.get_type_name() == "Constant" and n.get_output_shape(0) == [4, 4, 3, 3]]
+    assert consts and consts[0].get_output_element_type(0) == Type.f16
+    conv = [n for n in m.get_ops() if n.get_type_name() == "Convert"][0]
+    assert "decompression" in " ".join(conv.rt_info.keys()).lower()
+    np.testing.assert_allclose(infer(m, inp)[0], before, rtol=2e-2, atol=2e-2)
+
+
+def test_convert_precision():
+    x = ops.parameter([2, 2], "f32")
+    m = Model([ops.add(x, np.ones((2, 2), np.float32))], [x], "p")
+    passes.ConvertPrecision("f32", "f16").run_on_model(m)
+    assert m.input(0).get_element_type() == Type.f16 and m.output(0).get_element_type() == Type.f16
+
+
+def test_weight_compression_int4_and_int8():
+    rng = np.random.default_rng(1)
+    x = ops.parameter([3, 256], "f32")
+    w = rng.standard_normal((64, 256)).astype(np.float32)
+    m = Model([ops.matmul(x, w, False, True)], [x], "wc")
+    inp = rng.standard_normal((3, 256)).astype(np.float32)
+    ref = inp @ w.T
+    for mode, tol in (("int8_asym", 0.02), ("int4_asym", 0.15)):
+        c = m.clone()
+        assert passes.CompressWeights(mode=mode, group_size=64, all_layers=True).run_on_model(c)
+        lp = [n for n in c.get_ops() if n.get_type_name() == "Constant" and n.get_output_element_type(0) in (Type.u4, Type.u8)]
+        assert lp, mode
+        out = infer(c, inp)[0]
+        assert np.linalg.norm(out - ref) / np.linalg.norm(ref) < tol
+
+
+def test_make_stateful_and_back():
+    x = ops.parameter([1, 4], "f32", "x")
+    past = ops.parameter([1, 4], "f32", "past")
+    past.output(0).set_names({"past"})
+    s = ops.add(past, x)
+    s.output(0).set_names({"present"})
+    m = Model([ops.result(ops.relu(s), "out"), ops.result(s, "present")], [x, past], "st")
+    offline.apply_make_stateful_transformation(m, {"past": "present"})
+    t = types(m)
+    assert t["ReadValue"] == 1 and t["Assign"] == 1 and len(m.get_parameters()) == 1 and len(m.get_results()) == 1
+    assert [v.get_info().variable_id for v in m.get_variables()] == ["pastpresent"]
+    req = ov.compile_model(m, "CPU").create_infer_request()
+    one = np.ones((1, 4), np.float32)
+    assert (req.infer([one])[0] == 1).all() and (req.infer([one])[0] == 2).all()
+    offline.stateful_to_stateless_transformation(m)
+    t = types(m)
+    assert t["ReadValue"] == 0 and t["Assign"] == 0 and len(m.get_parameters()) == 2 and len(m.get_results()) == 2
+
+
+@pytest.fixture(scope="module")
+def llama_state():
+    return llama.random_float_state(CFG, seed=0, std=0.1)
+
+
+def run_stateful(m, ids):
+    req = ov.compile_model(m, "CPU").create_infer_request()
+    n = len(ids)
+    return req.infer({"input_ids": np.asarray(ids)[None], "attention_mask": np.ones((1, n), np.int64),
+                      "position_ids": np.arange(n)[None], "beam_idx": np.zeros(1, np.int32)})[0][0]
+
+
+def test_llm_fusions_keep_numerics(llama_state):
+    ids = list(range(3, 12))
+    ref = llama.reference_logits(CFG, llama_state, torch.tensor(ids)).numpy()
+    m = build_llama(CFG, llama_state)
+    np.testing.assert_allclose(run_stateful(m, ids), ref, rtol=1e-3, atol=1e-4)
+    pm = passes.Manager()
+    for name in ("RMSFusion", "RoPEFusion", "ConvertMatMulToFullyConnected"):
+        pm.register_pass(name)
+    pm.run_passes(m)
+    t = types(m)
+    assert t["RMS"] == 2 * CFG.num_layers + 1 and t["RoPE"] == 2 * CFG.num_layers and t["FullyConnected"] == 7 * CFG.num_layers + 1
+    assert t["Power"] == 0 and t["Sqrt"] == 0 and t["MatMul"] == 0
+    np.testing.assert_allclose(run_stateful(m, ids), ref, rtol=1e-3, atol=1e-4)
+
+
+def test_compressed_llm_becomes_fully_connected_compressed(llama_state):
+    ids = [5, 9, 1, 77, 30]
+    m = build_llama(CFG, llama_state, compress="int4")
+    eff = llama.effective_state(CFG, llama_state)
+    # the graph keeps norms and embeddings in fp32: compare against weights dequantised the same way
+    eff = {k: (v if v.dim() == 2 and not k.endswith("embed_tokens") else llama_state[k]) for k, v in eff.items()}
+    ref = llama.reference_logits(CFG, eff, torch.tensor(ids)).numpy()
+    before = run_stateful(m, ids)
+    np.testing.assert_allclose(before, ref, rtol=2e-2, atol=2e-2)
+    pm = passes.Manager()
+    for name in ("RMSFusion", "RoPEFusion", "ConvertMatMulToFullyConnected", "ConvertFullyConnectedToFullyConnectedCompressed"):
+        pm.register_pass(name)
+    pm.run_passes(m)
+    t = types(m)
+    assert t["FullyConnectedCompressed"] == 7 * CFG.num_layers + 1 and t["FullyConnected"] == 0
+    fc = [n for n in m.get_ops() if n.get_type_name() == "FullyConnectedCompressed"][0]
+    assert fc.input_value(1).get_element_type() == Type.u4
+    # the unfused graph rounds (q - zp) * scale to fp16 before the product, the fused op keeps fp32
+    np.testing.assert_allclose(run_stateful(m, ids), before, rtol=1e-2, atol=1e-2)
+
+
+def test_sdpa_to_paged_attention(llama_state):
+    m = build_llama(CFG, llama_state)
+    offline.paged_attention_transformation(m)
+    t = types(m)
+    assert t["PagedAttentionExtension"] == CFG.num_layers and t["ScaledDotProductAttention"] == 0
+    assert t["ReadValue"] == 0 and t["Assign"] == 0 and not m.get_sinks()
+    names = {p.get_friendly_name() for p in m.get_parameters()}
+    assert {"input_ids", "position_ids", "past_lens", "subsequence_begins", "block_indices", "block_indices_begins", "max_context_len",
+            "key_cache.0", "value_cache.0", "key_cache.1", "value_cache.1"} <= names
+    assert "beam_idx" not in names and "attention_mask" not in names
+    pa = [n for n in m.get_ops() if n.get_type_name() == "PagedAttentionExtension"][0]
+    assert pa.get_input_size() == 28 and pa.get_output_size() == 3
+    assert m.input("input_ids").get_partial_shape().to_string() == "[?]"
+
+    # run two sequences as one ragged batch against block caches and compare with the dense reference
+    seqs = [[3, 7, 11, 19, 23], [2, 4, 6]]
+    bs, Hkv, D = 16, CFG.num_kv_heads, CFG.head_dim
+    caches = {}
+    for l in range(CFG.num_layers):
+        caches["key_cache.%d" % l] = np.zeros((4, Hkv, bs, D), np.float32)
+        caches["value_cache.%d" % l] = np.zeros((4, Hkv, bs, D), np.float32)
+    feed = {"input_ids": np.array(sum(seqs, []), np.int64), "position_ids": np.array([0, 1, 2, 3, 4, 0, 1, 2], np.int64),
+            "past_lens": np.array([0, 0], np.int32), "subsequence_begins": np.array([0, 5, 8], np.int32),
+            "block_indices": np.array([2, 0], np.int32), "block_indices_begins": np.array([0, 1, 2], np.int32),
+            "max_context_len": np.array(5, np.int32)}
+    feed.update(caches)
+    cm = ov.compile_model(m, "CPU")
+    logits = cm(feed)["logits"]
+    logits = logits.reshape(-1, CFG.vocab_size)
+    for s, (a, b) in zip(seqs, ((0, 5), (5, 8))):
+        ref = llama.reference_logits(CFG, llama_state, torch.tensor(s)).numpy()
+        np.testing.assert_allclose(logits[a:b], ref, rtol=1e-3, atol=1e-4)
+    # the caches were written in place: decode one more token of sequence 0 from the cache
+    assert np.abs(caches["key_cache.0"][2]).sum() > 0
+    feed2 = dict(feed, input_ids=np.array([29], np.int64), position_ids=np.array([5], np.int64), past_lens=np.array([5], np.int32),
+                 subsequence_begins=np.array([0, 1], np.int32), block_indices=np.array([2], np.int32),
+                 block_indices_begins=np.array([0, 1], np.int32), max_context_len=np.array(6, np.int32))
+    logits2 = cm(feed2)["logits"].reshape(-1, CFG.vocab_size)
+    ref2 = llama.reference_logits(CFG, llama_state, torch.tensor(seqs[0] + [29])).numpy()
+    np.testing.assert_allclose(logits2[0], ref2[-1], rtol=1e-3, atol=1e-4)
+
+
+def test_visualize_and_serialize_passes(tmp_path):
+    x = ops.parameter([1], "f32")
+    m = Model([ops.relu(x)], [x], "v")
+    pm = passes.Manager()
+    pm.register_pass(passes.VisualizeTree(str(tmp_path / "g.dot")))
+    pm.register_pass(passes.Serialize(str(tmp_path / "m.xml"), str(tmp_path / "m.bin")))
+    pm.run_passes(m)
+    assert "digraph" in open(tmp_path / "g.dot").read() and (tmp_path / "m.xml").exists()
+    assert "ConstantFolding" in passes.available_passes()
