@@ -1,0 +1,126 @@
+"""The "CUDA" device through the public API: compile, infer, precision hints, states, remote tensors, AUTO/HETERO."""
+import numpy as np
+import pytest
+import torch
+
+import openvino_b200 as ov
+from openvino_b200 import Model, Tensor, Type
+from openvino_b200 import opset as ops
+from openvino_b200 import properties as props
+from openvino_b200.models import llama
+from openvino_b200.models.llm_config import TINY_LLAMA
+from openvino_b200.models.ov_builders import build_llama
+from openvino_b200.models.torch_zoo import ResNet18, bert_tiny
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def core():
+    return ov.Core()
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-12)
+
+
+def test_device_is_listed_and_describes_itself(core):
+    assert any(d.startswith("CUDA") for d in core.available_devices)
+    assert "B200" in core.get_property("CUDA", props.device.full_name) or core.get_property("CUDA", props.device.full_name)
+    assert core.get_property("CUDA", props.device.architecture).startswith("sm_")
+    assert "INT4" in core.get_property("CUDA", props.device.capabilities)
+
+
+def test_resnet_fp32_and_fp16(core):
+    torch.manual_seed(0)
+    net = ResNet18(num_classes=10, width=16).eval()
+    x = torch.randn(4, 3, 64, 64)
+    with torch.no_grad():
+        want = net(x).numpy()
+    m = ov.convert_model(net, example_input=(x,))
+    out = core.compile_model(m, "CUDA")(x.numpy())[0]
+    assert rel(out, want) < 1e-3
+    out16 = core.compile_model(m, "CUDA", {props.hint.inference_precision: "f16"})(x.numpy())[0]
+    assert out16.dtype == np.float32 and rel(out16, want) < 3e-2
+    assert core.compile_model(m, "GPU").get_property(props.execution_devices) == ["CUDA.0"]
+
+
+def test_bert_fp16_uses_own_kernels(core):
+    torch.manual_seed(0)
+    net = bert_tiny().eval()
+    ids = torch.randint(0, 100, (2, 16))
+    mask = torch.ones(2, 16, dtype=torch.int64)
+    typ = torch.zeros(2, 16, dtype=torch.int64)
+    with torch.no_grad():
+        want = net(ids, mask, typ).numpy()
+    m = ov.convert_model(net, example_input=(ids, mask, typ))
+    cm = core.compile_model(m, "CUDA", {props.hint.inference_precision: "f16", props.enable_profiling: True})
+    req = cm.create_infer_request()
+    out = req.infer([ids.numpy(), mask.numpy(), typ.numpy()])[0]
+    assert rel(out, want) < 3e-2
+    prof = req.get_profiling_info()
+    assert any(p.node_type == "FullyConnected" for p in prof) and all(p.exec_type == "cuda" for p in prof)
+
+
+def test_stateful_llm_int4_on_device(core):
+    cfg = TINY_LLAMA.with_(vocab_size=256, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=128, ffn_size=512, group_size=128)
+    state = llama.random_float_state(cfg, seed=2, std=0.05)
+    m = build_llama(cfg, state, compress="int4")
+    cpu = core.compile_model(m, "CPU").create_infer_request()
+    gpu = core.compile_model(m, "CUDA", {props.hint.inference_precision: "bf16"}).create_infer_request()
+    feeds = [{"input_ids": np.array([[3, 9, 27, 5, 100, 7]], np.int64), "attention_mask": np.ones((1, 6), np.int64),
+              "position_ids": np.arange(6)[None], "beam_idx": np.zeros(1, np.int32)},
+             {"input_ids": np.array([[42]], np.int64), "attention_mask": np.ones((1, 7), np.int64),
+              "position_ids": np.array([[6]], np.int64), "beam_idx": np.zeros(1, np.int32)}]
+    for feed in feeds:
+        want, got = cpu.infer(feed)[0], gpu.infer(feed)[0]
+        assert rel(got, want) < 5e-2
+        assert (got[0, -1].argmax() == want[0, -1].argmax()) or rel(got, want) < 2e-2
+    st = gpu.query_state()
+    assert len(st) == 2 * cfg.num_layers and st[0].state.shape[2] == 7
+    gpu.reset_state()
+    assert rel(gpu.infer(feeds[0])[0], cpu.infer(feeds[0])[0]) < 1.0    # runs again from an empty state
+
+
+def test_remote_tensors_and_async(core):
+    x = ops.parameter([4, 8], "f32", "x")
+    m = Model([ops.relu(ops.add(x, np.float32(-0.5)))], [x], "r")
+    cm = core.compile_model(m, "CUDA", {props.num_streams: 2})
+    ctx = core.get_default_context("CUDA")
+    rin = ctx.create_tensor(Type.f32, [4, 8])
+    rout = ctx.create_tensor(Type.f32, [4, 8])
+    rin.torch().copy_(torch.arange(32, dtype=torch.float32).reshape(4, 8) / 16)
+    req = cm.create_infer_request()
+    req.set_input_tensor(rin)
+    req.set_output_tensor(rout)
+    req.infer()
+    assert req.get_output_tensor() is rout and rout.is_remote
+    np.testing.assert_allclose(rout.data, np.maximum(np.arange(32).reshape(4, 8) / 16 - 0.5, 0), rtol=1e-6)
+    q = ov.AsyncInferQueue(cm, 4)
+    got = {}
+    q.set_callback(lambda r, i: got.__setitem__(i, r.results[0].copy()))
+    xs = [np.full((4, 8), float(i), np.float32) for i in range(8)]
+    for i, a in enumerate(xs):
+        q.start_async({"x": a}, userdata=i)
+    q.wait_all()
+    for i, a in enumerate(xs):
+        np.testing.assert_allclose(got[i], np.maximum(a - 0.5, 0))
+    host = ctx.create_host_tensor(Type.f32, [4, 8])
+    assert host.data.shape == (4, 8)
+
+
+def test_auto_prefers_cuda_and_hetero_splits(core):
+    x = ops.parameter([2, 4], "f32", "x")
+    y = ops.selu(ops.relu(x), np.float32(1.5), np.float32(1.0), name="selu")      # Selu has no device implementation
+    m = Model([ops.add(y, np.float32(1), name="tail")], [x], "h")
+    assert core.compile_model(m, "AUTO").get_property(props.execution_devices)[0].startswith("CUDA")
+    q = core.query_model(m, "CUDA")
+    assert "selu" not in q and "tail" in q
+    cm = core.compile_model(m, "HETERO:CUDA,CPU")
+    assert [s.device for s in cm.subs] == ["CUDA", "CPU", "CUDA"]
+    a = np.array([[-1, 0.5, 2, -3], [1, 1, -1, 0]], np.float32)
+    r = np.maximum(a, 0)
+    np.testing.assert_allclose(cm(a)[0], np.where(r > 0, r, 1.5 * (np.exp(r) - 1)) + 1, rtol=1e-5)
+    # the device alone still runs the model: unsupported operations fall back to the host
+    np.testing.assert_allclose(core.compile_model(m, "CUDA")(a)[0], cm(a)[0], rtol=1e-5)
