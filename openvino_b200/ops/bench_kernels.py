@@ -1,0 +1,131 @@
+"""Kernel micro-benchmarks with roofline fractions: ``python -m openvino_b200.ops.bench_kernels <kernel> [options]``.
+
+Kernels: ``gemm`` (tcgen05 GEMM, bf16 or int4/int8 weights; ``--cublas`` adds the library GEMM for comparison),
+``attention`` (paged decode or prefill), ``rmsnorm``. Every timed launch is preceded by an L2 flush (a 256 MB write),
+timed with CUDA events on the launching stream after warm-up; the median is reported together with achieved
+bandwidth / throughput and, when ``MEASURED_PEAKS.json`` sits in the working directory, the fraction of the measured
+peaks. ``--iters`` small (3-5) gives a run suited to a profiler capture.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+
+def _peaks():
+    for path in ("MEASURED_PEAKS.json", os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")):
+        if os.path.exists(path):
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": d.get("hbm_gbs"), "bf16_tflops": d.get("bf16_tflops"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def timeit(fn, iters: int, warmup: int) -> float:
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def bench_gemm(a) -> dict:
+    from . import cuda as K
+    from ..utils import quant
+    T, N, Kd = a.T, a.N, a.K
+    x = torch.randn(T, Kd, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    if a.wmode == "bf16":
+        w = (torch.randn(N, Kd, device="cuda") * 0.02).to(torch.bfloat16)
+        pw = K.PackedWeight.from_dense(w)
+        wbytes = N * Kd * 2
+    else:
+        packed, s, z = quant.random_u4_weight(N, Kd, a.group, "cuda")
+        pw = K.PackedWeight.from_ir_u4(packed, s, quant.pack_u4(z), N, Kd, a.group)
+        wbytes = N * Kd // 2 + (N * Kd // a.group) * 4
+    ms = timeit(lambda: K.gemm(x, pw, out=out), a.iters, a.warmup)
+    K.check_status("gemm")
+    flops = 2.0 * T * N * Kd
+    bytes_ = wbytes + T * Kd * 2 + T * N * 2
+    r = {"kernel": "gemm_%s" % a.wmode, "T": T, "N": N, "K": Kd, "ms": ms, "tflops": flops / ms / 1e9, "gbs": bytes_ / ms / 1e6}
+    if a.cublas:
+        w16 = (torch.randn(N, Kd, device="cuda") * 0.02).to(torch.bfloat16)
+        r["cublas_bf16_ms"] = timeit(lambda: torch.matmul(x, w16.t(), out=out), a.iters, a.warmup)
+    return r
+
+
+def bench_attention(a) -> dict:
+    from . import cuda as K
+    B, Hq, Hkv, D, bs = a.B, a.Hq, a.Hkv, 128, 16
+    ctx, q_len = a.ctx, a.q_len
+    nblk = (ctx + bs - 1) // bs
+    total = B * nblk
+    kc = torch.randn(total, Hkv, bs, D, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(total, Hkv, bs, D, device="cuda").to(torch.bfloat16)
+    T = B * q_len
+    q = torch.randn(T, Hq * D, device="cuda").to(torch.bfloat16)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    past, sb = i32([ctx - q_len] * B), i32([i * q_len for i in range(B + 1)])
+    bi, bib = torch.randperm(total).to(torch.int32).cuda(), i32([i * nblk for i in range(B + 1)])
+    out = torch.empty(T, Hq * D, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: K.paged_attention(q, kc, vc, past, sb, bi, bib, Hq, Hkv, D, max_context_len=ctx, max_q_len=q_len, out=out), a.iters, a.warmup)
+    K.check_status("attention")
+    kv_bytes = 2 * B * ctx * Hkv * D * 2
+    flops = 4.0 * B * Hq * D * (q_len * (ctx - q_len) + q_len * (q_len + 1) / 2)
+    return {"kernel": "paged_attention", "B": B, "ctx": ctx, "q_len": q_len, "Hq": Hq, "Hkv": Hkv, "ms": ms, "gbs": (kv_bytes + 2 * T * Hq * D * 2) / ms / 1e6,
+            "tflops": flops / ms / 1e9}
+
+
+def bench_rmsnorm(a) -> dict:
+    from . import cuda as K
+    x = torch.randn(a.T, a.N, device="cuda").to(torch.bfloat16)
+    g = torch.ones(a.N, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+    ms = timeit(lambda: K.rmsnorm(x, g, 1e-5, out=out), a.iters, a.warmup)
+    return {"kernel": "rmsnorm", "rows": a.T, "cols": a.N, "ms": ms, "gbs": 2 * x.numel() * 2 / ms / 1e6}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm"])
+    ap.add_argument("--T", type=int, default=64)
+    ap.add_argument("--N", type=int, default=4096)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--wmode", default="u4", choices=["u4", "bf16"])
+    ap.add_argument("--group", type=int, default=128)
+    ap.add_argument("--cublas", action="store_true")
+    ap.add_argument("--B", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--q-len", dest="q_len", type=int, default=1)
+    ap.add_argument("--Hq", type=int, default=32)
+    ap.add_argument("--Hkv", type=int, default=8)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    r = {"gemm": bench_gemm, "attention": bench_attention, "rmsnorm": bench_rmsnorm}[a.kernel](a)
+    pk = _peaks()
+    if pk["hbm_gbs"]:
+        r["frac_of_%s_hbm" % pk["source"]] = r["gbs"] / pk["hbm_gbs"]
+    if pk["bf16_tflops"] and "tflops" in r:
+        r["frac_of_%s_bf16" % pk["source"]] = r["tflops"] / pk["bf16_tflops"]
+    print(json.dumps(r))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
