@@ -79,7 +79,10 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-cudart", "static"])
+    # only the C ABI is exported; everything else (C++ runtime templates, the static CUDA runtime) stays local
+    vers = OBJ / "ovb_cuda.map"
+    vers.write_text("{ global: ovb_*; local: *; };\n")
+    _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-cudart", "static", "-Xlinker", "--version-script=%s" % vers])
     return target
 
 
@@ -112,7 +115,12 @@ def build_core(force: bool = False) -> Path | None:
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, srcs))
-    _run([cxx, "-shared", "-o", str(target), *map(str, objs), "-pthread"])
+    # Export the module init function only and bind the module's own references locally. The C++ standard library
+    # templates instantiated in this module would otherwise be visible process-wide and get mixed with the copies
+    # inside other extension modules (PyTorch), which crashes whichever module is imported second.
+    vers = OBJ / "ovcore.map"
+    vers.write_text("{ global: PyInit__ovcore; local: *; };\n")
+    _run([cxx, "-shared", "-o", str(target), *map(str, objs), "-pthread", "-Wl,--version-script=%s" % vers, "-Wl,-Bsymbolic"])
     return target
 
 

@@ -752,10 +752,12 @@ def _prepare_fc(n: Node, ins, ctx: Ctx):
                     zp = torch.from_numpy(np.ascontiguousarray(zp_node.get_tensor_view().to_float32())).reshape(-1)
                     zp = (zp.expand(N * G) if zp.numel() == 1 else zp).reshape(N, G).to(torch.uint8).to(dev)
                 b16 = bias.to(torch.bfloat16) if bias is not None and bias.numel() == N else None
+                sc16 = scales.to(torch.float16).contiguous().to(dev)
                 if et == "u4":
-                    st["packed"] = K.PackedWeight.from_ir_u4(wq.reshape(N, Kd // 2), scales.to(torch.float16).to(dev), zp, Kd // G, bias=b16)
+                    st["packed"] = K.PackedWeight.from_ir_u4(wq.reshape(-1), sc16, zp.contiguous() if zp is not None else None, N, Kd, Kd // G,
+                                                             zp_is_u8=True, bias=b16)
                 else:
-                    st["packed"] = K.PackedWeight.from_ir_u8(wq.reshape(N, Kd), scales.to(torch.float16).to(dev), zp, Kd // G, bias=b16)
+                    st["packed"] = K.PackedWeight.from_ir_u8(wq.reshape(N, Kd), sc16, zp, N, Kd, Kd // G, bias=b16)
     ctx.cache[id(n)] = st
     return st
 

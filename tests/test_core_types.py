@@ -106,3 +106,14 @@ def test_tensor_copy_to():
 
 def test_version():
     assert "b200" in ov.get_version()
+
+
+def test_import_order_with_torch_does_not_matter():
+    """The native core hides its C++ runtime symbols: importing it before PyTorch must not crash PyTorch."""
+    import subprocess
+    import sys
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for code in ("import openvino_b200, torch; print(torch.zeros(2).sum().item())", "import torch, openvino_b200; print(torch.zeros(2).sum().item())"):
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, timeout=300)
+        assert r.returncode == 0 and "0.0" in r.stdout, (r.returncode, r.stderr[-500:])
