@@ -331,7 +331,10 @@ __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int*
 // Plugin layout: every aligned group of 8 elements e0..e7 becomes one u32 with nibble j (j<4) = e[2j]
 // and nibble j+4 = e[2j+1], so that one mask per shifted copy yields a pair of adjacent elements.
 // The words are also re-ordered so that the 128 x 64 block of one (weight tile, k-block) pair is one
-// contiguous 4 KB chunk: word index ((tile * KB + kb) * 128 + row) * 8 + w.
+// contiguous chunk of 4608 bytes: 4 KB of nibbles split in two halves of k (0..31, 32..63) with 16 bytes per row in
+// each half (word (tile * KB + kb) * 1152 + khalf * 512 + row * 4 + w; a warp whose lanes are consecutive rows reads
+// consecutive 16-byte pieces, no bank conflicts), followed by the 128 (scale, 16 + zero point) bf16 pairs of the
+// chunk's rows for its quantisation group (word ... + 1024 + row), so that ONE bulk copy brings all a k-block needs.
 __global__ void pack_u4_kernel(const uint32_t* __restrict__ w_ir, uint32_t* __restrict__ w_out, size_t nwords, int K) {
     const int wpr = K / 8;          // words per row
     const int KB = K / 64;
@@ -339,7 +342,7 @@ __global__ void pack_u4_kernel(const uint32_t* __restrict__ w_ir, uint32_t* __re
         const uint32_t x = w_ir[i];   // nibble k = element k
         const size_t n = i / wpr;
         const int kw = int(i - n * wpr);
-        const size_t dst = ((((n >> 7) * KB + (kw >> 3)) << 7) + (n & 127)) * 8 + (kw & 7);
+        const size_t dst = ((n >> 7) * KB + (kw >> 3)) * 1152 + (size_t)(((kw & 7) >> 2) * 512) + (n & 127) * 4 + (kw & 3);
         uint32_t o = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -347,6 +350,17 @@ __global__ void pack_u4_kernel(const uint32_t* __restrict__ w_ir, uint32_t* __re
             o |= ((x >> (8 * j + 4)) & 0xF) << (4 * j + 16);   // e[2j+1] -> nibble j+4
         }
         w_out[dst] = o;
+    }
+}
+// copies the pairs of table [G][N] into every chunk of the tiled u4 layout (see pack_u4_kernel)
+__global__ void embed_pairs_kernel(const uint32_t* __restrict__ table, uint32_t* __restrict__ w_out, int N, int KB, int kb_per_group,
+                                   size_t total) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int row = int(i & 127);
+        const size_t chunk = i >> 7;                 // tile * KB + kb
+        const int kb = int(chunk % KB);
+        const size_t n = (chunk / KB) * 128 + row;
+        w_out[chunk * 1152 + 1024 + row] = n < (size_t)N ? table[(size_t)(kb / kb_per_group) * N + n] : 0u;
     }
 }
 __global__ void pack_w16_kernel(const uint4* __restrict__ w, uint4* __restrict__ w_out, size_t npieces, int K) {
@@ -514,13 +528,18 @@ int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int
     OVB_REQUIRE(K % 64 == 0 && group_size > 0 && K % group_size == 0, "ovb_pack_u4: K must be a multiple of 64 and of group_size");
     const size_t nwords = (size_t)N * K / 8;
     // w_out holds ceil(N/128)*128 rows; rows beyond N stay zero
-    OVB_CHECK_CUDA(cudaMemsetAsync(w_out, 0, (size_t)((N + 127) / 128) * 128 * (K / 2), stream));
+    OVB_REQUIRE(group_size % 64 == 0, "ovb_pack_u4: group_size must be a multiple of 64");
+    const size_t chunks = (size_t)((N + 127) / 128) * (K / 64);
+    OVB_CHECK_CUDA(cudaMemsetAsync(w_out, 0, chunks * 4608, stream));
     pack_u4_kernel<<<grid_for(nwords, 256), 256, 0, stream>>>((const uint32_t*)w_ir, (uint32_t*)w_out, nwords, K);
     OVB_CHECK_CUDA(cudaGetLastError());
     const int G = K / group_size;
     pack_scale_zp_kernel<<<grid_for((size_t)N * G, 256), 256, 0, stream>>>(
         (const __half*)scales_ir, (const uint8_t*)zps_ir, zp_is_u8, (__nv_bfloat16*)scales_out, (__nv_bfloat16*)zps_out,
         N, G, 16.0f, 8.0f);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    embed_pairs_kernel<<<grid_for(chunks * 128, 256), 256, 0, stream>>>((const uint32_t*)scales_out, (uint32_t*)w_out, N, K / 64,
+                                                                        group_size / 64, chunks * 128);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -33,7 +33,8 @@ constexpr int TILE_N = 128;      // weight rows per CTA (MMA M)
 constexpr int TILE_K = 64;       // bf16 elements per k-block = one 128-byte swizzle span
 constexpr int NUM_DQ_WARPS = 8;  // dequant + epilogue warps
 constexpr int DQ_THREADS = NUM_DQ_WARPS * 32;
-constexpr int GEMM_THREADS = (2 + NUM_DQ_WARPS) * 32;
+constexpr int GEMM_THREADS = (3 + NUM_DQ_WARPS) * 32;   // producer, MMA issuer, 8 dequant/epilogue warps, token-tile producer (quantised modes)
+constexpr int X_PRODUCER_WARP = 2 + NUM_DQ_WARPS;
 constexpr int MAX_STAGES = 8;    // MMA stages
 constexpr int MAX_PSLOTS = 16;   // packed-weight ring slots
 constexpr int kBandN = 16;       // weight tiles per rasterisation band
@@ -69,6 +70,14 @@ struct GemmKParams {
 };
 
 constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 us apart
+
+// Tuning aid, compiled out unless the file is built with -DOVB_GEMM_TRACE: CTA 0 writes cycle counts of its control
+// lanes (waits vs. issue) into the split-K workspace. TR(x) keeps the statements out of normal builds entirely.
+#ifdef OVB_GEMM_TRACE
+#define TR(...) __VA_ARGS__
+#else
+#define TR(...)
+#endif
 
 template <bool F16>
 struct Elem {
@@ -131,36 +140,42 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
+// Quantised stages cover two k-blocks (128 elements of K) except for 256-token tiles, whose token tile alone is 32 KB
+// per k-block: every barrier round trip between the producers, the dequant warps and the MMA issuer then moves twice
+// the data, which halves the per-byte cost of the control chain.
+constexpr int kblocks_per_stage(int bt, int wmode) { return (wmode == OVB_W_U4 || wmode == OVB_W_U8) && bt < 256 ? 2 : 1; }
+
+// Decode-sized quantised problems run two CTAs per SM: one CTA's control chain (barrier round trips between the
+// producer, the dequant warps and the MMA issuer) is latency bound, a second resident CTA fills the gaps.
+constexpr bool two_ctas(int bt, int wmode) { return bt <= 64 && (wmode == OVB_W_U4 || wmode == OVB_W_U8); }
 
 template <int BT, int WMODE, bool F16>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, two_ctas(BT, WMODE) ? 2 : 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmKParams p) {
     using E = typename Elem<F16>::type;
     constexpr bool QUANT = (WMODE == OVB_W_U4 || WMODE == OVB_W_U8);
+    constexpr int KPS = kblocks_per_stage(BT, WMODE);   // k-blocks per pipeline stage (see STAGE_BYTES)
     constexpr int X_BYTES = BT * 128;
     constexpr int W_BYTES = TILE_N * 128;
     constexpr int WQ_BYTES = (WMODE == OVB_W_U4) ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
     constexpr int ROW_PKT = WQ_BYTES / TILE_N;          // packed bytes per row and k-block
-    constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
-    constexpr int TMEM_COLS = BT < 32 ? 32 : BT;
+    constexpr int SZ_BYTES = QUANT ? TILE_N * 4 : 0;    // (scale, zero point) pairs of the tile's rows for one k-block
+    constexpr int WQ_SLOT = WQ_BYTES + SZ_BYTES;        // one k-block in the ring: packed chunk, then its pairs
+    constexpr int RING_SLOT = KPS * WQ_SLOT;            // one ring slot = the k-blocks of one stage
+    // Quantised weights never touch shared memory in expanded form: the dequant warps write the bf16 tile straight
+    // into tensor memory (tcgen05.st) and the MMA takes its A operand from there, so a stage holds the token tile only.
+    constexpr int STAGE_BYTES = QUANT ? KPS * X_BYTES : X_BYTES + W_BYTES;
+    constexpr int ACC_COLS = BT < 32 ? 32 : BT;
+    constexpr int A_COLS = KPS * 32;                             // 128 rows x 64 bf16 = 32 columns of 32 bits per k-block
+    // accumulator + stages of A: 4 stages (256 columns, two CTAs per SM) for small tiles, up to 8 stages otherwise
+    constexpr int TMEM_COLS = !QUANT ? ACC_COLS : (two_ctas(BT, WMODE) ? 256 : 512);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int stages = p.stages;
     const int pslots = p.pslots;
     uint8_t* pring = smem + stages * STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + pslots * WQ_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + pslots * RING_SLOT);
     uint64_t* full_x = bars;                         // [stages] token tile (and bf16 weight chunk) landed
     uint64_t* full_dq = bars + MAX_STAGES;           // [stages] expanded weight tile written
     uint64_t* empty = bars + 2 * MAX_STAGES;         // [stages] MMAs that read the stage retired
@@ -173,6 +188,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    TR(long long tr_k0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_k0));)
     // Tile order: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so the
     // CTAs that are resident together share a few weight tiles and a few token tiles in L2.
     int n_tile, t_tile;
@@ -193,18 +209,18 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int kb_begin = split * p.kblocks_per_split;
     const int kb_end = min(total_kb, kb_begin + p.kblocks_per_split);
     const int num_kb = max(0, kb_end - kb_begin);
+    const int num_it = (num_kb + KPS - 1) / KPS;         // stage iterations of the main loop
     // dequant warps per MMA stage: with few stages two warps share one k-block (64 rows each)
-    const int wps = (stages <= NUM_DQ_WARPS / 2) ? 2 : 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(&full_x[s], 1);
-            mbar_init(&full_dq[s], wps);
+            mbar_init(&full_dq[s], NUM_DQ_WARPS);
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < pslots; ++s) {
             mbar_init(&p_full[s], 1);
-            mbar_init(&p_empty[s], wps);
+            mbar_init(&p_empty[s], NUM_DQ_WARPS);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
@@ -221,56 +237,52 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    TR(if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+           reinterpret_cast<long long*>(p.ws)[24] = t - tr_k0; })
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             if (QUANT) {
-                // Event loop over two cursors: packed weight chunks run ahead by up to `pslots` k-blocks,
-                // token tiles by up to `stages`. test_wait does not block, so neither stream holds up the other.
-                // running (slot, parity) counters: no divisions in this latency-bound single-lane loop
-                int iw = 0, ix = 0;
-                int wslot = 0, xs = 0;
-                uint32_t wpar = 1, xpar = 1;          // parity to wait for on the "empty" barriers
-                uint32_t idle = 0;
-                const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * total_kb + kb_begin) * WQ_BYTES;
-                int xk = kb_begin * TILE_K;
-                uint32_t wdst = smem_u32(pring), xdst = smem_u32(smem);
-                while (iw < num_kb || ix < num_kb) {
-                    bool progress = false;
-                    if (iw < num_kb && mbar_test(&p_empty[wslot], wpar)) {
-                        mbar_arrive_expect_tx(&p_full[wslot], WQ_BYTES);
-                        if (WMODE == OVB_W_U4) {
+                // Weight producer: one ring slot per k-block, requested up to `pslots` k-blocks ahead of use. A u4 slot is
+                // ONE bulk copy: the packed chunk and the (scale, zero point) pairs of its rows are stored together.
+                // (Every instruction of this single-lane loop is on the critical path of the whole CTA: no divisions,
+                // running pointers only. The token tiles have a producer lane of their own in warp X_PRODUCER_WARP.)
+                int wslot = 0;
+                uint32_t wpar = 1;                    // parity to wait for on the "empty" barriers
+                TR(long long tr_t0 = clock64(); long long tr_w = 0;)
+                const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * total_kb + kb_begin) * (WMODE == OVB_W_U4 ? WQ_SLOT : WQ_BYTES);
+                uint32_t wdst = smem_u32(pring);
+                // u8: pairs come from the [group][N] table with a second copy
+                const int kpg = p.group_size / TILE_K;
+                int gk = kb_begin % kpg;
+                const uint32_t* zsrc = p.sz + (size_t)(kb_begin / kpg) * p.N + n0;
+                int kcoord = kb_begin * TILE_K;
+                for (int iw = 0; iw < num_it; ++iw) {
+                    if (!mbar_wait(&p_empty[wslot], wpar, abort_flag, p.status)) break;
+                    TR(const long long tr_a = clock64();)
+                    const int nk = min(KPS, num_kb - iw * KPS);
+                    mbar_arrive_expect_tx(&p_full[wslot], nk * WQ_SLOT);
+                    if (WMODE == OVB_W_U4) {
+                        // consecutive k-blocks of a tile are consecutive chunks in memory: one copy brings the whole stage
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(wdst), "l"(wsrc), "r"(nk * WQ_SLOT), "r"(smem_u32(&p_full[wslot])) : "memory");
+                        wsrc += KPS * WQ_SLOT;
+                    } else {
+                        for (int t = 0; t < nk; ++t) {
+                            tma_load_2d(pring + wslot * RING_SLOT + t * WQ_SLOT, &tmW, &p_full[wslot], kcoord, n0);
                             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                         ::"r"(wdst), "l"(wsrc), "r"(WQ_BYTES), "r"(smem_u32(&p_full[wslot])) : "memory");
-                        } else {
-                            tma_load_2d(pring + wslot * WQ_BYTES, &tmW, &p_full[wslot], (kb_begin + iw) * TILE_K, n0);
+                                         ::"r"(wdst + t * WQ_SLOT + WQ_BYTES), "l"(zsrc), "r"(SZ_BYTES), "r"(smem_u32(&p_full[wslot])) : "memory");
+                            kcoord += TILE_K;
+                            if (++gk == kpg) { gk = 0; zsrc += p.N; }
                         }
-                        ++iw;
-                        wsrc += WQ_BYTES;
-                        wdst += WQ_BYTES;
-                        if (++wslot == pslots) { wslot = 0; wpar ^= 1; wdst = smem_u32(pring); }
-                        progress = true;
                     }
-                    if (ix < num_kb && mbar_test(&empty[xs], xpar)) {
-                        mbar_arrive_expect_tx(&full_x[xs], X_BYTES);
-                        asm volatile(
-                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                            ::"r"(xdst), "l"(reinterpret_cast<uint64_t>(&tmX)), "r"(smem_u32(&full_x[xs])), "r"(xk), "r"(t0)
-                            : "memory");
-                        ++ix;
-                        xk += TILE_K;
-                        xdst += STAGE_BYTES;
-                        if (++xs == stages) { xs = 0; xpar ^= 1; xdst = smem_u32(smem); }
-                        progress = true;
-                    }
-                    if (progress) {
-                        idle = 0;
-                    } else if (++idle > (1u << 26) || ((idle & 1023u) == 0 && *abort_flag)) {
-                        if (!*abort_flag) { *abort_flag = 1; report_status(p.status, STATUS_MBAR_TIMEOUT); }
-                        break;
-                    }
+                    wdst += RING_SLOT;
+                    if (++wslot == pslots) { wslot = 0; wpar ^= 1; wdst = smem_u32(pring); }
+                    TR(tr_w += clock64() - tr_a;)
                 }
+                TR(if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
+                       o[0] = clock64() - tr_t0; o[1] = tr_w; o[4] = num_kb; })
             } else {
                 uint32_t phase = 0;
                 int s = 0;
@@ -289,131 +301,164 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
         }
         __syncwarp();
+    } else if (warp == X_PRODUCER_WARP) {
+        // ------------------------------------------------------------ token-tile producer (quantised modes only)
+        if (QUANT && lane == 0) {
+            uint32_t xpar = 1;
+            int xs = 0;
+            int xk = kb_begin * TILE_K;
+            uint32_t xdst = smem_u32(smem);
+            TR(long long tr_t0 = clock64(); long long tr_x = 0;)
+            for (int ix = 0; ix < num_it; ++ix) {
+                if (!mbar_wait(&empty[xs], xpar, abort_flag, p.status)) break;
+                TR(const long long tr_c = clock64();)
+                const int nk = min(KPS, num_kb - ix * KPS);
+                mbar_arrive_expect_tx(&full_x[xs], nk * X_BYTES);
+                for (int t = 0; t < nk; ++t) {
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                        ::"r"(xdst + t * X_BYTES), "l"(reinterpret_cast<uint64_t>(&tmX)), "r"(smem_u32(&full_x[xs])), "r"(xk), "r"(t0)
+                        : "memory");
+                    xk += TILE_K;
+                }
+                xdst += STAGE_BYTES;
+                if (++xs == stages) { xs = 0; xpar ^= 1; xdst = smem_u32(smem); }
+                TR(tr_x += clock64() - tr_c;)
+            }
+            TR(if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
+                   o[2] = tr_x; o[3] = clock64() - tr_t0; })
+        }
+        __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        // Only lane 0 waits and issues; lanes 1..31 park at the __syncwarp below (no polling).
+        // The whole warp runs the loop with warp-uniform control flow and elect.sync picks the lane that issues:
+        // descriptors then live in uniform registers and the four MMAs of a k-block issue back to back (a loop under
+        // `if (lane == 0)` costs about twice the cycles per k-block on the issuing thread).
         constexpr uint32_t idesc = umma_idesc_f16(TILE_N, BT, !F16);
         const uint64_t desc0 = umma_desc_k_sw128(smem_u32(smem), 1024);
-        if (lane == 0) {
+        {
             uint32_t phase = 0;
             int s = 0;
-            for (int i = 0; i < num_kb; ++i) {
-                bool ok = mbar_wait(&full_x[s], phase, abort_flag, p.status);
-                if (ok && QUANT) ok = mbar_wait(&full_dq[s], phase, abort_flag, p.status);
+            TR(long long tr_t0 = clock64(), tr_wx = 0, tr_wd = 0, tr_is = 0;)
+            for (int i = 0; i < (QUANT ? num_it : num_kb); ++i) {
+                TR(const long long tr_a = clock64();)
+                int ok = 0;
+                if (lane == 0) {
+                    ok = mbar_wait(&full_x[s], phase, abort_flag, p.status) ? 1 : 0;
+                    TR(tr_wx += clock64() - tr_a;)
+                    if (ok && QUANT) ok = mbar_wait(&full_dq[s], phase, abort_flag, p.status) ? 1 : 0;
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                TR(const long long tr_c = clock64(); tr_wd += tr_c - tr_a;)
                 if (!ok) break;
                 tc_fence_after_sync();
                 // descriptors differ only in the 16-byte-unit start address (low 14 bits, no carry out here)
                 const uint64_t db0 = desc0 + (uint64_t)((s * STAGE_BYTES) >> 4);
-                const uint64_t da0 = db0 + (uint64_t)(X_BYTES >> 4);
+                const uint32_t acc_first = i > 0 ? 1u : 0u;
+                if (QUANT) {
+                    const uint32_t a0 = tmem_base + uint32_t(ACC_COLS + s * A_COLS);   // 8 columns per K=16 slice
+                    umma_f16_ts_elect(tmem_base, a0, db0, idesc, acc_first);
 #pragma unroll
-                for (int k = 0; k < TILE_K / 16; ++k) {
-                    umma_f16_ss(tmem_base, da0 + 2 * k, db0 + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 1; k < TILE_K / 16; ++k) umma_f16_ts_elect(tmem_base, a0 + 8 * k, db0 + 2 * k, idesc, 1u);
+                    if (KPS == 2 && num_kb - i * KPS > 1) {                            // second k-block of the stage
+                        const uint64_t db1 = db0 + (uint64_t)(X_BYTES >> 4);
+#pragma unroll
+                        for (int k = 0; k < TILE_K / 16; ++k) umma_f16_ts_elect(tmem_base, a0 + 32 + 8 * k, db1 + 2 * k, idesc, 1u);
+                    }
+                } else {
+                    const uint64_t da0 = db0 + (uint64_t)(X_BYTES >> 4);
+                    umma_f16_ss_elect(tmem_base, da0, db0, idesc, acc_first);
+#pragma unroll
+                    for (int k = 1; k < TILE_K / 16; ++k) umma_f16_ss_elect(tmem_base, da0 + 2 * k, db0 + 2 * k, idesc, 1u);
                 }
-                umma_commit(&empty[s]);
+                umma_commit_elect(&empty[s]);
+                TR(tr_is += clock64() - tr_c;)
                 if (++s == stages) { s = 0; phase ^= 1; }
             }
-            umma_commit(acc_full);
+            umma_commit_elect(acc_full);
+            TR(if (lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                   reinterpret_cast<long long*>(p.ws)[25] = t - tr_k0; })
+            TR(if (lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
+                   o[8] = clock64() - tr_t0; o[9] = tr_wx; o[10] = tr_wd - tr_wx; o[11] = tr_is; })
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------ dequant warps, then epilogue
         const int dq_tid = threadIdx.x - 64;  // 0..255
         if (QUANT) {
-            // Warp pair/single (dw / wps) owns MMA stage d and expands k-blocks d, d+stages, ... of it.
-            // One owner per stage keeps every parity wait at most one phase ahead of its barrier
-            // (pslots >= 2 * stages gives the same guarantee for the packed ring).
-            const int dw = warp - 2;
-            const int d = dw / wps;
-            const int sub = dw - d * wps;
-            const int rows_per_warp = TILE_N / wps;     // 128 or 64
-            const int iters = rows_per_warp / 16;       // 16 rows per pass of 32 lanes x 16 bytes
-            const int row0 = sub * rows_per_warp;
-            const int G = p.K / p.group_size;
-            const int half = lane & 1;
-            // (scale, zero point) pairs of this lane's rows; the pairs of the warp's NEXT k-block are fetched
-            // at the start of the current one so that their latency hides behind the expansion work
-            uint32_t cur[8], nx1[8], nx2[8];
-            auto load_scales = [&](int kb, uint32_t* dst) {
-                const int g = (kb * TILE_K) / p.group_size;
-#pragma unroll
-                for (int it = 0; it < 8; ++it) {
-                    if (it < iters) {
-                        const int n = n0 + row0 + it * 16 + (lane >> 1);
-                        dst[it] = (n < p.N && g < G) ? __ldg(p.sz + (size_t)g * p.N + n) : 0u;
+            // Two groups of four warps: group g expands k-block g of every stage. Inside a group a warp owns the 32 rows of
+            // its TMEM lane quarter; a thread expands the 64 values of one row and writes them to tensor memory as 32
+            // columns of bf16 pairs (two tcgen05.st).
+            const int grp = (warp - 2) >> 2;
+            const int qd = warp & 3;                    // TMEM lane quarter this warp may access
+            const int row = qd * 32 + lane;
+            const bool row_ok = (n0 + row) < p.N;
+            int slot = 0, st = 0;
+            uint32_t ppar = 0, phase = 0;
+            const uint32_t a_lane = tmem_base + (uint32_t(qd * 32) << 16) + uint32_t(ACC_COLS + (KPS == 2 ? grp * 32 : 0));
+            TR(long long tr_t0 = clock64(), tr_wp = 0, tr_we = 0, tr_wk = 0;)
+            for (int i = 0; i < num_it; ++i) {
+                // lane 0 polls, the shuffle hands the observation on to the other lanes
+                int ok = 0;
+                TR(const long long tr_a = clock64(); long long tr_b = tr_a;)
+                if (lane == 0) {
+                    if (mbar_wait(&p_full[slot], ppar, abort_flag, p.status)) {
+                        TR(tr_b = clock64();)
+                        ok = mbar_wait(&empty[st], phase ^ 1, abort_flag, p.status) ? 1 : 0;
                     }
                 }
-            };
-            int i = d < stages ? d : num_kb;
-            uint32_t phase = 0;
-            // this warp's k-blocks are `stages` apart; their scale pairs are cold in HBM, so they are fetched
-            // two of the warp's iterations ahead
-            if (i < num_kb) load_scales(kb_begin + i, nx1);
-            if (i + stages < num_kb) load_scales(kb_begin + i + stages, nx2);
-            int slot = i;                       // i < stages <= pslots
-            uint32_t ppar = 0;
-            for (; i < num_kb; i += stages) {
-                // lane 0 polls, the warp barrier hands the observation on to the other lanes
-                int ok = 0;
-                if (lane == 0) {
-                    if (mbar_wait(&p_full[slot], ppar, abort_flag, p.status))
-                        ok = mbar_wait(&empty[d], phase ^ 1, abort_flag, p.status) ? 1 : 0;
-                }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
+                TR(const long long tr_c = clock64(); tr_wp += tr_b - tr_a; tr_we += tr_c - tr_b;)
                 if (!ok) break;
+                // KPS == 2: group g expands k-block g of the stage; KPS == 1: the groups take alternate stages
+                const uint32_t slot_a = smem_u32(pring + slot * RING_SLOT + (KPS == 2 ? grp * WQ_SLOT : 0));
+                if (KPS == 2 ? (i * KPS + grp < num_kb) : ((i & 1) == grp)) {
+                uint32_t cur;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(cur) : "r"(slot_a + WQ_BYTES + row * 4));
+                if (!row_ok) cur = 0u;          // rows past N: scale 0
+                const __nv_bfloat162 szp = *reinterpret_cast<const __nv_bfloat162*>(&cur);
+                uint32_t r[32];
+                if (WMODE == OVB_W_U4) {
+                    const __nv_bfloat162 ss2 = __halves2bfloat162(__low2bfloat16(szp), __low2bfloat16(szp));
+                    const __nv_bfloat162 zz2 = __halves2bfloat162(__high2bfloat16(szp), __high2bfloat16(szp));
+                    const uint4 pk0 = lds128(slot_a + row * 16), pk1 = lds128(slot_a + TILE_N * 16 + row * 16);
+                    const uint32_t xs[8] = {pk0.x, pk0.y, pk0.z, pk0.w, pk1.x, pk1.y, pk1.z, pk1.w};
 #pragma unroll
-                for (int it = 0; it < 8; ++it) { cur[it] = nx1[it]; nx1[it] = nx2[it]; }
-                if (i + 2 * stages < num_kb) load_scales(kb_begin + i + 2 * stages, nx2);
-                const uint32_t wbase = smem_u32(smem + d * STAGE_BYTES + X_BYTES);
-                const uint8_t* wq = pring + slot * WQ_BYTES;
-                const uint32_t wq_a = smem_u32(wq);
+                    for (int j = 0; j < 8; ++j) {
+                        const uint4 e = dequant_u4x8(xs[j], zz2, ss2);
+                        r[4 * j] = e.x; r[4 * j + 1] = e.y; r[4 * j + 2] = e.z; r[4 * j + 3] = e.w;
+                    }
+                } else {
+                    const float sf = __bfloat162float(__low2bfloat16(szp));
+                    const float zf = __bfloat162float(__high2bfloat16(szp));
 #pragma unroll
-                for (int it = 0; it < 8; ++it) {
-                    if (it < iters) {
-                        const int r = row0 + it * 16 + (lane >> 1);
-                        const uint32_t wdst = wbase + r * 128;
-                        const __nv_bfloat162 szp = *reinterpret_cast<const __nv_bfloat162*>(&cur[it]);
-                        if (WMODE == OVB_W_U4) {
-                            const __nv_bfloat162 ss2 = __halves2bfloat162(__low2bfloat16(szp), __low2bfloat16(szp));
-                            const __nv_bfloat162 zz2 = __halves2bfloat162(__high2bfloat16(szp), __high2bfloat16(szp));
-                            const uint4 pk = lds128(wq_a + r * ROW_PKT + half * 16);
-                            const uint32_t xs[4] = {pk.x, pk.y, pk.z, pk.w};
+                    for (int h = 0; h < 4; ++h) {
+                        const uint4 pk = lds128(slot_a + row * ROW_PKT + h * 16);
+                        const uint32_t b[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int c = half * 4 + j;
-                                sts128(wdst + ((c ^ (r & 7)) << 4), dequant_u4x8(xs[j], zz2, ss2));
-                            }
-                        } else {
-                            const float sf = __bfloat162float(__low2bfloat16(szp));
-                            const float zf = __bfloat162float(__high2bfloat16(szp));
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint2 pk = *reinterpret_cast<const uint2*>(wq + r * ROW_PKT + half * 32 + j * 8);
-                                const uint32_t b[2] = {pk.x, pk.y};
-                                uint32_t o[4];
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const uint32_t w32 = b[e >> 1];
-                                    const int sh = (e & 1) * 16;
-                                    const float f0 = (float((w32 >> sh) & 0xFF) - zf) * sf;
-                                    const float f1 = (float((w32 >> (sh + 8)) & 0xFF) - zf) * sf;
-                                    o[e] = pack_bf16x2(f0, f1);
-                                }
-                                const int c = half * 4 + j;
-                                sts128(wdst + ((c ^ (r & 7)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
-                            }
+                        for (int e = 0; e < 8; ++e) {
+                            const uint32_t w32 = b[e >> 1];
+                            const int sh = (e & 1) * 16;
+                            r[h * 8 + e] = pack_bf16x2((float((w32 >> sh) & 0xFF) - zf) * sf, (float((w32 >> (sh + 8)) & 0xFF) - zf) * sf);
                         }
                     }
                 }
-                fence_proxy_async_smem();
+                tmem_st_x16(a_lane + uint32_t(st * A_COLS), r);
+                tmem_st_x16(a_lane + uint32_t(st * A_COLS + 16), r + 16);
+                tmem_st_wait();
+                }
+                tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&full_dq[d]);
+                    mbar_arrive(&full_dq[st]);
                     mbar_arrive(&p_empty[slot]);
                 }
-                phase ^= 1;
-                slot += stages;
-                if (slot >= pslots) { slot -= pslots; ppar ^= 1; }
+                if (++st == stages) { st = 0; phase ^= 1; }
+                if (++slot == pslots) { slot = 0; ppar ^= 1; }
+                TR(tr_wk += clock64() - tr_c;)
             }
+            TR(if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
+                   o[16] = clock64() - tr_t0; o[17] = tr_wp; o[18] = tr_we; o[19] = tr_wk; })
         }
 
         // -------- epilogue: warp (w % 4) owns TMEM lanes 32*(w%4) .. +31; two warps share a quarter
@@ -703,6 +748,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // ---------------------------------------------------------------- tear-down
     tc_fence_before_sync();
     __syncthreads();
+    TR(if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+           reinterpret_cast<long long*>(p.ws)[26] = t - tr_k0; })
     if (*abort_flag) {
         // Give copies that are still in flight time to land before the CTA's shared memory is reused.
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -728,20 +775,27 @@ static int pick_block_t(int T) {
     return 256;
 }
 
-static int pick_splits(int T, int N, int K, int bt) {
+static int pick_splits(int T, int N, int K, int bt, int wmode) {
+    // Split-K trades idle SMs against extra traffic: every split writes an fp32 partial tile that the last CTA of the
+    // tile reads back. Estimate the time of every candidate with a small model (all constants in microseconds,
+    // measured on B200 with the decode shapes of an 8B model) and take the cheapest.
     const int tiles = ceil_div(N, TILE_N) * ceil_div(T, bt);
     const int total_kb = ceil_div(K, TILE_K);
-    if (tiles >= 2 * kNumSMs || total_kb < 8) return 1;
-    // pick the split count whose CTA count fills whole waves of SMs best (ties: fewer splits)
+    const int slots = two_ctas(bt, wmode) ? 2 * kNumSMs : kNumSMs;        // CTAs resident at a time
+    if (tiles >= slots || total_kb < 8) return 1;
+    const double t_kb = (wmode == OVB_W_U4 || wmode == OVB_W_U8) ? 0.36 : 0.12 + 0.0028 * bt;   // one k-block in one CTA
+    const double t_cta = 6.0;                                              // set-up, pipeline fill, epilogue of a CTA
+    const double partial_us_per_mb = 0.45;                                 // write + read of partials through L2/HBM
     int best = 1;
-    double best_eff = 0.0;
+    double best_t = 1e30;
     const int max_s = total_kb / 4 < 16 ? total_kb / 4 : 16;
     for (int s = 1; s <= max_s; ++s) {
         const int ctas = tiles * s;
-        const int waves = ceil_div(ctas, kNumSMs);
-        if (waves > 4 && s > 1) break;
-        const double eff = double(ctas) / double(waves * kNumSMs);
-        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+        const int waves = ceil_div(ctas, slots);
+        const bool shared_sm = two_ctas(bt, wmode) && ctas > kNumSMs;      // two CTAs on an SM slow each other down
+        double t = waves * (ceil_div(total_kb, s) * t_kb * (shared_sm ? 1.25 : 1.0) + t_cta);
+        if (s > 1) t += 2.0 * s * double(T) * N * 4.0 / 1e6 * partial_us_per_mb;
+        if (t < best_t - 0.25) { best_t = t; best = s; }
     }
     return best;
 }
@@ -756,11 +810,21 @@ static void pick_rings(int bt, int wmode, int* stages, int* pslots) {
         *pslots = 0;
         return;
     }
-    // quantised: pslots >= 2 * stages (see the kernel). Four MMA stages with two dequant warps each keep all
-    // eight warps expanding; the rest of the budget goes to the packed ring.
-    int s = 4;
-    while (s > 2 && (kSmemBudget - s * stage) / wq < 2 * s) --s;
-    int pmax = (kSmemBudget - s * stage) / wq;
+    // quantised: a stage is the token tile only (the expanded weights live in tensor memory); four stages, the rest of
+    // the budget goes to the packed ring so that weight chunks are requested far ahead of use
+    // a quantised stage covers kps k-blocks: token tiles of kps x 64 K-elements, ring slots of kps chunks, kps x 32 TMEM columns of A
+    const int kps = kblocks_per_stage(bt, wmode);
+    const int xstage = kps * bt * 128;
+    const int slot = kps * (wq + TILE_N * 4);  // packed chunks + (scale, zero point) pairs
+    int s, budget;
+    if (two_ctas(bt, wmode)) {               // two CTAs share the SM: half the shared memory, 256 TMEM columns each
+        s = 3;                               // accumulator (<= 64 columns) + 3 x 64 columns of A
+        budget = (kSmemLimit - 2 * 1024) / 2 - 2560;
+    } else {
+        s = 4;                               // accumulator + 4 x 64 (or 4 x 32) columns of A fit the 512 TMEM columns
+        budget = kSmemBudget;
+    }
+    int pmax = (budget - s * xstage) / slot;
     if (pmax > MAX_PSLOTS) pmax = MAX_PSLOTS;
     *stages = s;
     *pslots = pmax;
@@ -774,13 +838,15 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     p.stages = stages;
     p.pslots = pslots;
     const int wq = WMODE == OVB_W_U4 ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
-    const int smem = stages * (BT * 128 + TILE_N * 128) + pslots * wq + 1024 + 1024;
+    const int kps = kblocks_per_stage(BT, WMODE);
+    const int smem = stages * (wq ? kps * BT * 128 : BT * 128 + TILE_N * 128) + pslots * (wq ? kps * (wq + TILE_N * 4) : 0) + 1024 + 1024;
     auto kern = gemm_ws_kernel<BT, WMODE, F16>;
     static uint64_t configured = 0;  // one bit per device
     int dev = 0;
     OVB_CHECK_CUDA(cudaGetDevice(&dev));
     if (!(configured & (1ull << dev))) {
         OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+        OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         configured |= (1ull << dev);
     }
     if (smem > kSmemLimit) {
@@ -816,7 +882,7 @@ int ovb_gemm_num_counters(void) { return ovb::kNumCounters; }
 int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act) {
     (void)act;
     const int bt = ovb::pick_block_t(T);
-    const int splits = ovb::pick_splits(T, N, K, bt);
+    const int splits = ovb::pick_splits(T, N, K, bt, OVB_W_U4);
     if (splits == 1) return 0;
     const int64_t tiles = (int64_t)ovb::ceil_div(N, ovb::TILE_N) * ovb::ceil_div(T, bt);
     return tiles * splits * ovb::TILE_N * bt * (int64_t)sizeof(float);
@@ -835,11 +901,13 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         OVB_REQUIRE(a->group_size >= 64 && a->group_size % 64 == 0 && a->K % a->group_size == 0,
                     "ovb_gemm: group_size %d must be a multiple of 64 that divides K=%d", a->group_size, a->K);
         OVB_REQUIRE(a->K % 32 == 0, "ovb_gemm: K must be a multiple of 32 for packed weights");
+        OVB_REQUIRE(a->N % 4 == 0 && (reinterpret_cast<uintptr_t>(a->scales) & 15) == 0,
+                    "ovb_gemm: quantised weights need N %% 4 == 0 and a 16-byte aligned (scale, zero point) table");
     }
     OVB_REQUIRE(a->act != OVB_ACT_SWIGLU, "ovb_gemm: SWIGLU epilogue is provided by ovb_silu_mul");
 
     const int bt = a->block_t ? a->block_t : pick_block_t(a->T);
-    int splits = a->splits ? a->splits : pick_splits(a->T, a->N, a->K, bt);
+    int splits = a->splits ? a->splits : pick_splits(a->T, a->N, a->K, bt, a->wmode);
     const int total_kb = ceil_div(a->K, TILE_K);
     if (splits > total_kb) splits = total_kb;
     const int64_t tiles = (int64_t)ceil_div(a->N, TILE_N) * ceil_div(a->T, bt);

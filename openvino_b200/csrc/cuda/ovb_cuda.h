@@ -26,7 +26,7 @@ const char* ovb_last_error(void);
 // the N side, so the same kernel serves decode (T <= 64) and prefill (T in the thousands).
 enum {
     OVB_W_BF16 = 0,   // W is bf16 [N, K]
-    OVB_W_U4 = 1,     // W is packed u4 in the plugin layout made by ovb_pack_u4 (N x K/2 bytes)
+    OVB_W_U4 = 1,     // W is packed u4 in the plugin layout made by ovb_pack_u4 (4608-byte chunks, see below)
     OVB_W_U8 = 2,     // W is u8 [N, K]
     OVB_W_F16 = 3,    // W and X are fp16 (BERT path)
 };
@@ -71,6 +71,7 @@ int ovb_gemm_num_counters(void);
 // Re-pack IR-layout u4 weights (LSB-first nibbles, [N, K]) into the plugin layout read by the
 // dequantising GEMM, and build the transposed table of (bf16 scale, bf16 16+zero point) pairs.
 //   w_ir    : [N, K/2] bytes         scales_ir: [N, G] fp16     zps_ir: [N, G/2..] packed u4 or NULL (zp = 8)
+//   w_out      : ceil(N/128) * (K/64) chunks of 4608 bytes (4 KB of nibbles + the 128 rows' bf16 pairs)
 //   scales_out : [G, N, 2] bf16      zps_out: optional [G, N] bf16 (may be NULL)
 int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int zp_is_u8, void* w_out,
                 void* scales_out, void* zps_out, int N, int K, int group_size, ovb_stream_t stream);

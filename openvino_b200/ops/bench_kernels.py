@@ -1,7 +1,7 @@
 """Kernel micro-benchmarks with roofline fractions: ``python -m openvino_b200.ops.bench_kernels <kernel> [options]``.
 
 Kernels: ``gemm`` (tcgen05 GEMM, bf16 or int4/int8 weights; ``--cublas`` adds the library GEMM for comparison),
-``attention`` (paged decode or prefill), ``rmsnorm``. Every timed launch is preceded by an L2 flush (a 256 MB write),
+``attention`` (paged decode or prefill), ``rmsnorm``. Every timed launch is preceded by an L2 flush (a 256 MB read),
 timed with CUDA events on the launching stream after warm-up; the median is reported together with achieved
 bandwidth / throughput and, when ``MEASURED_PEAKS.json`` sits in the working directory, the fraction of the measured
 peaks. ``--iters`` small (3-5) gives a run suited to a profiler capture.
@@ -26,21 +26,24 @@ def _peaks():
 
 
 def timeit(fn, iters: int, warmup: int) -> float:
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    """Median device time of ``fn`` in ms. The whole sequence (L2 flush, event, launch, event) x iters is queued without
+    host synchronisation in between, so the GPU never waits for the host and an interval holds kernel time only."""
+    # the flush READS 256 MB: the L2 ends up full of clean lines of another buffer (a flush that writes leaves dirty
+    # lines whose write-back would be charged to the kernel under test)
+    flush = torch.zeros(64 << 20, dtype=torch.int32, device="cuda")
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    times = []
+    events = []
     for _ in range(iters):
-        flush.zero_()
+        flush.sum()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
         s.record()
         fn()
         e.record()
-        torch.cuda.synchronize()
-        times.append(s.elapsed_time(e))
-    times.sort()
+        events.append((s, e))
+    torch.cuda.synchronize()
+    times = sorted(s.elapsed_time(e) for s, e in events)
     return times[len(times) // 2]
 
 

@@ -169,8 +169,9 @@ class PackedWeight:
         (or uint8 [N, G] when zp_is_u8) or None for the symmetric i4-style offset 8."""
         dev = w_ir.device
         G = K // group_size
-        w_out = torch.empty(((N + 127) // 128) * 128 * K // 2, dtype=torch.uint8, device=dev)
-        s_out = torch.empty(G * N * 2, dtype=torch.bfloat16, device=dev)
+        w_out = torch.empty(((N + 127) // 128) * (K // 64) * 4608, dtype=torch.uint8, device=dev)
+        # the kernel copies the pairs of 128 rows at a time: keep 128 pairs of slack behind the table
+        s_out = torch.zeros(G * N * 2 + 256, dtype=torch.bfloat16, device=dev)
         rc = lib().ovb_pack_u4(C.c_void_p(w_ir.data_ptr()), C.c_void_p(scales_ir.data_ptr()),
                                C.c_void_p(_ptr(zps_ir)), C.c_int(1 if zp_is_u8 else 0), C.c_void_p(w_out.data_ptr()),
                                C.c_void_p(s_out.data_ptr()), C.c_void_p(None), C.c_int(N), C.c_int(K),
@@ -188,7 +189,8 @@ class PackedWeight:
         else:
             z = zps_ir.reshape(N, G).float().t().contiguous().to(torch.bfloat16)
         sz = torch.stack([s, z], dim=-1).contiguous()      # [G, N, 2] pairs
-        return PackedWeight(W_U8, w_ir.contiguous(), N, K, sz.reshape(-1), None, group_size, bias)
+        sz = torch.cat([sz.reshape(-1), torch.zeros(256, dtype=sz.dtype, device=sz.device)])   # slack for 128-row copies
+        return PackedWeight(W_U8, w_ir.contiguous(), N, K, sz, None, group_size, bias)
 
 
 # ------------------------------------------------------------------------------------------ ops
