@@ -173,6 +173,60 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
     }
 }
 
+// ------------------------------------------------------------------------------------ mixture of experts
+// Router: softmax over the E expert logits of a token, keep the top k, renormalise them to sum 1 (Mixtral rule).
+// Output: dense [T, E] fp32 routing weights (0 for experts that were not selected). One thread per token, E <= 64.
+__global__ void moe_route_topk_kernel(const float* __restrict__ logits, float* __restrict__ weights, int T, int E, int k) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    float v[64];
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) { v[e] = logits[(size_t)t * E + e]; mx = fmaxf(mx, v[e]); }
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) { v[e] = __expf(v[e] - mx); sum += v[e]; }
+    unsigned long long picked = 0ull;
+    float top_sum = 0.f;
+    for (int j = 0; j < k; ++j) {
+        int best = -1;
+        float bv = -1.f;
+        for (int e = 0; e < E; ++e)
+            if (!((picked >> e) & 1ull) && v[e] > bv) { bv = v[e]; best = e; }      // first index wins ties
+        picked |= 1ull << best;
+        top_sum += bv;
+    }
+    (void)sum;   // the softmax denominator cancels in the renormalisation
+    for (int e = 0; e < E; ++e) weights[(size_t)t * E + e] = ((picked >> e) & 1ull) ? v[e] / top_sum : 0.f;
+}
+
+// act[t, e*F + f] = silu(gu[t, e*2F + f]) * gu[t, e*2F + F + f] * w[t, e0 + e] for the `nloc` local experts of a rank.
+// A token that is not routed to an expert gets zeros there, so the stacked down projection sums exactly the routed experts.
+__global__ void moe_silu_mul_scale_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                          int rows, int F, int nloc, int E, int e0) {
+    const int fv = F >> 3;
+    const size_t total = (size_t)rows * nloc * fv;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / ((size_t)nloc * fv);
+        const int rem = int(i - r * (size_t)nloc * fv);
+        const int e = rem / fv, c = rem - e * fv;
+        const float scale = w[r * E + e0 + e];
+        Pack8 o;
+        if (scale == 0.f) {
+            o.u = make_uint4(0u, 0u, 0u, 0u);
+        } else {
+            Pack8 g, u;
+            const __nv_bfloat16* base = gu + (r * nloc + e) * 2 * (size_t)F;
+            g.u = reinterpret_cast<const uint4*>(base)[c];
+            u.u = reinterpret_cast<const uint4*>(base + F)[c];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float gv = __bfloat162float(g.b[j]);
+                o.b[j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * __bfloat162float(u.b[j]) * scale);
+            }
+        }
+        reinterpret_cast<uint4*>(out + (r * nloc + e) * (size_t)F)[c] = o.u;
+    }
+}
+
 __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                            __nv_bfloat16* __restrict__ out, size_t nvec) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
@@ -447,6 +501,23 @@ int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream
     OVB_REQUIRE(gu && out && rows > 0 && F % 8 == 0, "ovb_silu_mul: bad arguments");
     const size_t total = (size_t)rows * (F / 8);
     silu_mul_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_moe_route_topk(const float* logits, float* weights, int T, int E, int k, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(logits && weights && T > 0 && E > 0 && E <= 64 && k > 0 && k <= E, "ovb_moe_route_topk: need 1 <= k <= E <= 64");
+    moe_route_topk_kernel<<<(T + 127) / 128, 128, 0, stream>>>(logits, weights, T, E, k);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_moe_silu_mul_scale(const void* gu, const float* weights, void* out, int rows, int F, int nloc, int E, int e0, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(gu && weights && out && rows > 0 && F % 8 == 0 && nloc > 0 && e0 >= 0 && e0 + nloc <= E, "ovb_moe_silu_mul_scale: bad arguments");
+    const size_t total = (size_t)rows * nloc * (F / 8);
+    moe_silu_mul_scale_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, weights, (__nv_bfloat16*)out, rows, F, nloc, E, e0);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -97,6 +97,11 @@ int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, in
 int ovb_argmax(const void* logits, int ld, int rows, int vocab, void* out_ids, int ids_i32, float* out_max,
                ovb_stream_t stream);
 int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream);
+// Mixture of experts. Router: softmax over E logits per token, top-k kept and renormalised; weights is dense [T, E] fp32.
+int ovb_moe_route_topk(const float* logits, float* weights, int T, int E, int k, ovb_stream_t stream);
+// SwiGLU of the `nloc` local experts [e0, e0 + nloc) stacked along the feature axis, scaled by the routing weight:
+// gu [rows, nloc * 2F] (gate block then up block per expert) -> out [rows, nloc * F]; rows not routed to an expert get zeros.
+int ovb_moe_silu_mul_scale(const void* gu, const float* weights, void* out, int rows, int F, int nloc, int E, int e0, ovb_stream_t stream);
 // Device-side token feedback between chained steps (see elementwise.cu).
 int ovb_resolve_ids(int* ids, const int* tok_src, const int* last_token, int T, ovb_stream_t stream);
 int ovb_scatter_tokens(const int* tokens, const int* tok_dst, int* last_token, int B, ovb_stream_t stream);

@@ -25,9 +25,16 @@ def random_float_state(cfg: LlmConfig, seed: int = 0, device="cpu", std: float =
         st[p + "k_proj"] = rn(cfg.num_kv_heads * D, H)
         st[p + "v_proj"] = rn(cfg.num_kv_heads * D, H)
         st[p + "o_proj"] = rn(H, cfg.num_heads * D)
-        st[p + "gate_proj"] = rn(cfg.ffn_size, H)
-        st[p + "up_proj"] = rn(cfg.ffn_size, H)
-        st[p + "down_proj"] = rn(H, cfg.ffn_size)
+        if cfg.num_experts:
+            st[p + "router"] = rn(cfg.num_experts, H) * 10.0     # spread the routing logits so that the top-k is well separated
+            for e in range(cfg.num_experts):
+                st[p + "experts.%d.gate_proj" % e] = rn(cfg.ffn_size, H)
+                st[p + "experts.%d.up_proj" % e] = rn(cfg.ffn_size, H)
+                st[p + "experts.%d.down_proj" % e] = rn(H, cfg.ffn_size)
+        else:
+            st[p + "gate_proj"] = rn(cfg.ffn_size, H)
+            st[p + "up_proj"] = rn(cfg.ffn_size, H)
+            st[p + "down_proj"] = rn(H, cfg.ffn_size)
     return st
 
 
@@ -37,7 +44,7 @@ def effective_state(cfg: LlmConfig, state: Dict[str, torch.Tensor]) -> Dict[str,
     from ..utils import quant
     out = {}
     for k, v in state.items():
-        if v.dim() == 2 and not k.endswith("embed_tokens"):
+        if v.dim() == 2 and not k.endswith("embed_tokens") and not k.endswith("router"):
             if cfg.weight_format == "int4":
                 q, s, z = quant.quantize_u4_asym(v, cfg.group_size)
                 out[k] = quant.dequantize_u4(q, s, z, cfg.group_size)
@@ -88,8 +95,19 @@ def reference_logits(cfg: LlmConfig, state: Dict[str, torch.Tensor], ids: torch.
         a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(S, Hq * D)
         h = h + a @ state[p + "o_proj"].t()
         x = _rms(h, state[p + "post_attention_layernorm"], cfg.rms_eps)
-        g = torch.nn.functional.silu(x @ state[p + "gate_proj"].t()) * (x @ state[p + "up_proj"].t())
-        h = h + g @ state[p + "down_proj"].t()
+        if cfg.num_experts:
+            probs = torch.softmax(x @ state[p + "router"].t(), -1)
+            top_v, top_i = probs.topk(cfg.experts_top_k, -1)
+            top_v = top_v / top_v.sum(-1, keepdim=True)
+            y = torch.zeros_like(h)
+            for e in range(cfg.num_experts):
+                w_e = (top_v * (top_i == e)).sum(-1, keepdim=True)          # routing weight of expert e per token (0 if not chosen)
+                g = torch.nn.functional.silu(x @ state[p + "experts.%d.gate_proj" % e].t()) * (x @ state[p + "experts.%d.up_proj" % e].t())
+                y = y + w_e * (g @ state[p + "experts.%d.down_proj" % e].t())
+            h = h + y
+        else:
+            g = torch.nn.functional.silu(x @ state[p + "gate_proj"].t()) * (x @ state[p + "up_proj"].t())
+            h = h + g @ state[p + "down_proj"].t()
     return _rms(h, state["norm"], cfg.rms_eps) @ state["lm_head"].t()
 
 

@@ -256,6 +256,26 @@ def silu_mul(gu, out=None):
     return out
 
 
+def moe_route_topk(logits: torch.Tensor, k: int, out=None) -> torch.Tensor:
+    """logits [T, E] fp32 -> dense routing weights [T, E] fp32 (softmax, top-k, renormalised)."""
+    T, E = logits.shape
+    if out is None:
+        out = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    _check(lib().ovb_moe_route_topk(C.c_void_p(logits.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(T), C.c_int(E), C.c_int(k),
+                                    C.c_void_p(_stream())), "ovb_moe_route_topk")
+    return out
+
+
+def moe_silu_mul_scale(gu: torch.Tensor, weights: torch.Tensor, F: int, nloc: int, e0: int, out=None) -> torch.Tensor:
+    rows = gu.shape[0]
+    E = weights.shape[1]
+    if out is None:
+        out = torch.empty((rows, nloc * F), dtype=gu.dtype, device=gu.device)
+    _check(lib().ovb_moe_silu_mul_scale(C.c_void_p(gu.data_ptr()), C.c_void_p(weights.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(rows),
+                                        C.c_int(F), C.c_int(nloc), C.c_int(E), C.c_int(e0), C.c_void_p(_stream())), "ovb_moe_silu_mul_scale")
+    return out
+
+
 def add(a, b, out=None):
     if out is None:
         out = torch.empty_like(a)

@@ -30,10 +30,8 @@ class LayerWeights:
     norm2: torch.Tensor
     gate_up: Optional[K.PackedWeight] = None
     down: Optional[K.PackedWeight] = None
-    # MoE
+    # MoE: router [E, H]; gate_up / down hold the rank's local experts stacked ([nloc * 2F, H] and [H, nloc * F])
     router: Optional[K.PackedWeight] = None
-    experts_gate_up: List[K.PackedWeight] = field(default_factory=list)
-    experts_down: List[K.PackedWeight] = field(default_factory=list)
 
 
 @dataclass
@@ -95,7 +93,15 @@ class LlmWeights:
                 lw.gate_up = LlmWeights._random_packed(2 * ffn, H, cfg, device, s + 3)
                 lw.down = LlmWeights._random_packed(H, ffn, cfg, device, s + 4)
             else:
-                raise NotImplementedError("MoE weights are built by runtime.cuda_moe")
+                # expert parallel: a rank holds whole experts (nloc of them), attention stays tensor parallel
+                assert cfg.num_experts % tp_size == 0, "the number of experts must be a multiple of the number of ranks"
+                nloc = cfg.num_experts // tp_size
+                gr = torch.Generator(device=device)
+                gr.manual_seed(seed * 100003 + l * 97 + 5)       # the router is replicated: same seed on every rank
+                router = (torch.randn((cfg.num_experts, H), device=device, generator=gr) * 0.02).to(torch.bfloat16)
+                lw.router = K.PackedWeight.from_dense(router)
+                lw.gate_up = LlmWeights._random_packed(nloc * 2 * cfg.ffn_size, H, cfg, device, s + 3)
+                lw.down = LlmWeights._random_packed(H, nloc * cfg.ffn_size, cfg, device, s + 4)
             layers.append(lw)
         lm_head = LlmWeights._random_packed(vshard, H, cfg, device, seed * 100003 + 7 + tp_rank)
         return LlmWeights(embed, layers, ones(), lm_head, tp_rank, tp_size)
@@ -115,10 +121,19 @@ class LlmWeights:
             k = state[p + "k_proj"][r * hkv * D:(r + 1) * hkv * D]
             v = state[p + "v_proj"][r * hkv * D:(r + 1) * hkv * D]
             o = state[p + "o_proj"][:, r * hq * D:(r + 1) * hq * D]
-            gate = state[p + "gate_proj"][r * ffn:(r + 1) * ffn]
-            up = state[p + "up_proj"][r * ffn:(r + 1) * ffn]
-            down = state[p + "down_proj"][:, r * ffn:(r + 1) * ffn]
-            layers.append(LayerWeights(
+            router = None
+            if cfg.num_experts:
+                nloc = cfg.num_experts // tp_size
+                local = range(r * nloc, (r + 1) * nloc)
+                gu = torch.cat([torch.cat([state[p + "experts.%d.gate_proj" % e], state[p + "experts.%d.up_proj" % e]], 0) for e in local], 0)
+                down = torch.cat([state[p + "experts.%d.down_proj" % e] for e in local], 1)
+                gate, up = gu, gu[:0]
+                router = K.PackedWeight.from_dense(dev(state[p + "router"]).to(torch.bfloat16).contiguous())
+            else:
+                gate = state[p + "gate_proj"][r * ffn:(r + 1) * ffn]
+                up = state[p + "up_proj"][r * ffn:(r + 1) * ffn]
+                down = state[p + "down_proj"][:, r * ffn:(r + 1) * ffn]
+            layers.append(LayerWeights(router=router,
                 norm1=dev(state[p + "input_layernorm"]).to(torch.bfloat16),
                 qkv=LlmWeights._pack(dev(torch.cat([q, k, v], 0)).contiguous(), cfg),
                 o=LlmWeights._pack(dev(o).contiguous(), cfg),
@@ -163,8 +178,15 @@ class StepBuffers:
         self.x = torch.empty((Tcap, H), **bf)
         self.qkv = torch.empty((Tcap, (hq + 2 * hkv) * D), **bf)
         self.attn = torch.empty((Tcap, hq * D), **bf)
-        self.gu = torch.empty((Tcap, 2 * ffn), **bf)
-        self.act = torch.empty((Tcap, ffn), **bf)
+        if cfg.num_experts:
+            nloc = cfg.num_experts // tp_size
+            self.gu = torch.empty((Tcap, nloc * 2 * cfg.ffn_size), **bf)
+            self.act = torch.empty((Tcap, nloc * cfg.ffn_size), **bf)
+            self.router_logits = torch.empty((Tcap, cfg.num_experts), dtype=torch.float32, device=device)
+            self.route = torch.empty((Tcap, cfg.num_experts), dtype=torch.float32, device=device)
+        else:
+            self.gu = torch.empty((Tcap, 2 * ffn), **bf)
+            self.act = torch.empty((Tcap, ffn), **bf)
         self.last_h = torch.empty((Bcap, H), **bf)
         self.last_x = torch.empty((Bcap, H), **bf)
         self.logits = torch.empty((Bcap, cfg.vocab_size // tp_size), **bf)
@@ -247,8 +269,19 @@ class CudaLlmExecutor:
                               block_size=self.block_size, out=attn, ws=ws)
             self._row_parallel(attn, lw.o, h, 2 * l)
             K.rmsnorm(h, lw.norm2, cfg.rms_eps, out=x)
-            K.gemm(x, lw.gate_up, out=gu, ws=ws)
-            K.silu_mul(gu, out=act)
+            if cfg.num_experts:
+                # every rank holds all tokens (the residual stream is replicated), so "dispatch" is free: a rank runs its
+                # experts on the tokens routed to them (others contribute zeros) and the row-parallel down projection
+                # with its fused all-reduce is the "combine"
+                nloc = cfg.num_experts // self.tp_size
+                K.gemm(x, lw.router, out=sb.router_logits[:T], out_f32=True, ws=ws)
+                K.moe_route_topk(sb.router_logits[:T], cfg.experts_top_k, out=sb.route[:T])
+                K.gemm(x, lw.gate_up, out=gu, ws=ws)
+                K.moe_silu_mul_scale(gu, sb.route[:T], cfg.ffn_size, nloc, self.tp_rank * nloc, out=act)
+                n += 2
+            else:
+                K.gemm(x, lw.gate_up, out=gu, ws=ws)
+                K.silu_mul(gu, out=act)
             self._row_parallel(act, lw.down, h, 2 * l + 1)
             n += 9
         # logits only for the last token of every sequence

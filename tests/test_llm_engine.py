@@ -5,16 +5,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("fmt", ["bf16", "int4"])
+@pytest.mark.parametrize("fmt", ["bf16", "int4", "moe"])
 def test_tiny_llama_generate_matches_reference(fmt):
     from openvino_b200.genai.pipeline import ContinuousBatchingPipeline, GenerationConfig
     from openvino_b200.genai.scheduler import SchedulerConfig
     from openvino_b200.models import llama
-    from openvino_b200.models.llm_config import TINY_LLAMA
+    from openvino_b200.models.llm_config import TINY_LLAMA, TINY_MOE
     from openvino_b200.ops import cuda as K
     from openvino_b200.runtime.cuda_llm import CudaLlmExecutor, LlmWeights, StepShape
 
-    cfg = TINY_LLAMA.with_(weight_format=fmt)
+    cfg = TINY_MOE if fmt == "moe" else TINY_LLAMA.with_(weight_format=fmt)
     state = llama.random_float_state(cfg, seed=3, std=0.05)
     eff = {k: v.cuda() for k, v in llama.effective_state(cfg, state).items()}
     w = LlmWeights.from_float(cfg, state, "cuda")

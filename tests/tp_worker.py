@@ -117,18 +117,35 @@ def main():
     if any(o != obj[0] for o in obj):
         failures.append(("ranks disagree", obj))
 
+    # mixture of experts: experts sharded over the ranks (expert parallel), attention tensor parallel
+    from openvino_b200.models.llm_config import TINY_MOE
+    mcfg = TINY_MOE.with_(num_heads=8, num_kv_heads=world if world > 2 else 2, num_experts=4 if world <= 4 else 8)
+    mstate = llama.random_float_state(mcfg, seed=4)
+    moe_comm = PeerCommunicator(rank, world, dev)
+    mex = CudaLlmExecutor(mcfg, LlmWeights.from_float(mcfg, mstate, dev, tp_rank=rank, tp_size=world), num_kv_blocks=64, block_size=16,
+                          max_batch_tokens=256, max_seqs=4, max_blocks_per_seq=12, device=dev, comm=moe_comm)
+    mgot = [r.tokens for r in ContinuousBatchingPipeline(mex, sc).generate(prompts, gen)]
+    K.check_status("moe tp generate")
+    mex1 = CudaLlmExecutor(mcfg, LlmWeights.from_float(mcfg, mstate, dev), num_kv_blocks=64, block_size=16, max_batch_tokens=256,
+                           max_seqs=4, max_blocks_per_seq=12, device=dev)
+    mwant = [r.tokens for r in ContinuousBatchingPipeline(mex1, sc).generate(prompts, gen)]
+    magree = sum(int(a == b) for g_, w_ in zip(mgot, mwant) for a, b in zip(g_, w_))
+    if magree < total - 4:
+        failures.append(("moe generate", mgot, mwant))
+
     all_fail = [None] * world
     dist.all_gather_object(all_fail, failures)
     torch.cuda.synchronize()
     dist.barrier()
     tp_comm.close()
+    moe_comm.close()
     comm.close()
     dist.destroy_process_group()
     if rank == 0:
         if any(all_fail):
             print("TP_WORKER_FAILED", all_fail)
             sys.exit(1)
-        print("TP_WORKER_OK", "tokens agree %d/%d" % (agree, total))
+        print("TP_WORKER_OK", "tokens agree %d/%d, moe %d/%d" % (agree, total, magree, total))
 
 
 if __name__ == "__main__":
