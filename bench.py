@@ -91,10 +91,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--model", default="llama-3-8b")
-    ap.add_argument("--requests", type=int, default=64)
-    ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--model", default="llama-3-8b",
+                    help="llama-3-8b (headline) | llama-3-70b | mixtral-8x7b | tiny-llama | tiny-moe (serving); bert-large | resnet18 (graph API)")
+    ap.add_argument("--requests", type=int, default=0, help="concurrent requests (default: the benchmark's number for the model)")
+    ap.add_argument("--prompt-len", type=int, default=0)
+    ap.add_argument("--output-len", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result is then marked invalid)")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
@@ -111,10 +112,103 @@ def reference_arm(args):
     return 0
 
 
+SERVING_DEFAULTS = {"mixtral-8x7b": (128, 512, 128), "tiny-moe": (16, 128, 32), "tiny-llama": (16, 128, 32)}   # requests, prompt, output
+
+
+def graph_api_bench(args):
+    """Secondary configurations that run through convert_model / compile_model / InferRequest.
+
+    resnet18   : the plumbing configuration (fp32, batch 1, "CPU" device): convert -> save -> read -> compile -> infer,
+                 checked against eager PyTorch; reports latency.
+    bert-large : encoder, fp16, batch 64 x sequence 384 on the "CUDA" device; with N GPUs every rank serves its own replica
+                 (data parallel), the value is the sum over ranks.
+    """
+    import tempfile
+    import numpy as np
+    import torch
+    import openvino_b200 as ov
+    from openvino_b200 import properties as props
+    from openvino_b200.models import torch_zoo
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    core = ov.Core()
+    if args.model == "resnet18":
+        torch.manual_seed(0)
+        net = torch_zoo.ResNet18().eval()
+        for m in net.modules():
+            if isinstance(m, (torch.nn.Conv2d, torch.nn.Linear)):
+                torch.nn.init.kaiming_normal_(m.weight)
+        x = torch.randn(1, 3, 224, 224)
+        with torch.no_grad():
+            want = net(x).numpy()
+        d = tempfile.mkdtemp()
+        model = ov.convert_model(net, example_input=(x,))
+        ov.save_model(model, os.path.join(d, "resnet18.xml"), compress_to_fp16=False)
+        cm = core.compile_model(core.read_model(os.path.join(d, "resnet18.xml")), "CPU")
+        req = cm.create_infer_request()
+        for _ in range(args.warmup):
+            req.infer([x.numpy()])
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            out = req.infer([x.numpy()])[0]
+        ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        err = float(np.abs(out - want).max() / max(np.abs(want).max(), 1e-9))
+        print(json.dumps({"metric": "latency", "value": ms, "unit": "ms", "n_gpus": 0, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": ms, "higher_is_better": False, "dtype": "fp32", "data": "synthetic N(0,1) image, Kaiming-normal weights",
+                          "config": {"model": "resnet18", "device": "CPU", "batch": 1, "path": "convert_model -> save_model -> read_model -> compile_model -> InferRequest"},
+                          "max_rel_error_vs_torch": err, "logits_equal": err < 1e-3}))
+        return 0
+    # bert-large
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.manual_seed(0)
+    net = torch_zoo.bert_large().eval()
+    for prm in net.parameters():
+        torch.nn.init.normal_(prm, 0.0, 0.02) if prm.dim() > 1 else None
+    B, S = 64, 384
+    ids = torch.randint(0, 30522, (B, S))
+    mask = torch.ones(B, S, dtype=torch.int64)
+    typ = torch.zeros(B, S, dtype=torch.int64)
+    model = ov.convert_model(net, example_input=(ids, mask, typ))
+    cm = core.compile_model(model, "CUDA.%d" % local_rank, {props.hint.inference_precision: "f16"})
+    req = cm.create_infer_request()
+    feed = [ids.numpy(), mask.numpy(), typ.numpy()]
+    for _ in range(args.warmup):
+        req.infer(feed)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        req.infer(feed)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    t = torch.tensor([wall], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.destroy_process_group()
+    wall = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "sequences/s", "value": world * B * args.steps / wall, "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": wall * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak", "dtype": "fp16",
+                          "data": "synthetic: uniform token ids, all-ones mask, N(0,0.02) weights",
+                          "config": {"model": "bert-large", "batch_per_gpu": B, "seq_len": S, "parallelism": "dp%d" % world, "device": "CUDA",
+                                     "timing": "end to end through InferRequest.infer (host inputs in, host output out)"}}))
+    return 0
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.model in ("resnet18", "bert-large"):
+        return graph_api_bench(args)
+    dr, dp, do = SERVING_DEFAULTS.get(args.model, (64, 1024, 256))
+    args.requests, args.prompt_len, args.output_len = args.requests or dr, args.prompt_len or dp, args.output_len or do
 
     import torch
     import torch.distributed as dist
@@ -229,10 +323,12 @@ def main():
         line = {
             "metric": "output tokens/s", "value": value, "unit": "output tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16 activations, int4 (u4 g128 asym) weights",
+            "scaling": "strong", "vs_baseline": (value / PUBLISHED_TOK_S) if cfg.name == "llama-3-8b" else None,
+            "dtype": "bf16 activations, %s weights" % {"int4": "int4 (u4 g128 asym)", "int8": "int8 (u8 g128 asym)"}.get(cfg.weight_format, cfg.weight_format),
             "data": "synthetic: uniform random prompt ids, random-init weights", "impl": "ours",
             "config": {"model": cfg.name + ("" if not args.layers else "-DEBUG-%dlayers" % args.layers),
-                       "global_batch": R, "seq_len": P, "output_len": O, "parallelism": "tp%d" % world,
+                       "global_batch": R, "seq_len": P, "output_len": O,
+                       "parallelism": ("tp%d" % world) if not cfg.num_experts else ("attention tp%d, experts ep%d" % (world, world)),
                        "kv_block_size": bs, "step": "one serving pass over all requests",
                        "l2": "working set (weights + KV cache) far larger than L2; no flush needed",
                        "published_baseline": "OVMS Meta-Llama-3-8B-Instruct FP16 on Xeon 8580: 1151.94 tok/s"},
