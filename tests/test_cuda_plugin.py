@@ -124,3 +124,28 @@ def test_auto_prefers_cuda_and_hetero_splits(core):
     np.testing.assert_allclose(cm(a)[0], np.where(r > 0, r, 1.5 * (np.exp(r) - 1)) + 1, rtol=1e-5)
     # the device alone still runs the model: unsupported operations fall back to the host
     np.testing.assert_allclose(core.compile_model(m, "CUDA")(a)[0], cm(a)[0], rtol=1e-5)
+
+
+def test_llm_pipeline_from_ir_directory(tmp_path):
+    """IR on disk -> graph analysis -> serving program: tokens must follow the fp32 reference of the same weights."""
+    from openvino_b200.genai import ByteTokenizer, GenerationConfig, LLMPipeline
+    cfg = TINY_LLAMA.with_(vocab_size=320, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=128, ffn_size=512, group_size=128)
+    state = llama.random_float_state(cfg, seed=7, std=0.05)
+    m = build_llama(cfg, state, compress="int4")
+    ov.save_model(m, str(tmp_path / "openvino_model.xml"))
+    pipe = LLMPipeline(str(tmp_path), "CUDA", tokenizer=ByteTokenizer(), max_num_seqs=4, max_num_batched_tokens=256, max_model_len=128)
+    got_cfg = pipe.config
+    assert (got_cfg.num_layers, got_cfg.num_heads, got_cfg.num_kv_heads, got_cfg.head_dim, got_cfg.ffn_size, got_cfg.weight_format) == \
+           (cfg.num_layers, 4, 2, 128, 512, "int4")
+    assert abs(got_cfg.rope_theta - cfg.rope_theta) / cfg.rope_theta < 1e-3
+    prompts = [[5, 17, 200, 31, 8], [300, 2, 2, 9]]
+    outs = pipe.generate(prompts, GenerationConfig(max_new_tokens=5))
+    eff = llama.effective_state(cfg, state)
+    for p, o in zip(prompts, outs):
+        seq = p + o
+        logits = llama.reference_logits(cfg, eff, torch.tensor(seq[:-1]))
+        for i, tok in enumerate(o):
+            row = logits[len(p) - 1 + i]
+            assert row[tok] >= row.max() - 0.05 * row.abs().max()
+    text = pipe.generate("hi", max_new_tokens=3)
+    assert isinstance(text, str)
