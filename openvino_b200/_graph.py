@@ -457,7 +457,10 @@ def constant(value, dtype=None, name: Optional[str] = None, shared_memory: bool 
             t = t.astype(dtype)
     else:
         try:
-            import torch
+            import sys
+            torch = sys.modules.get("torch")
+            if torch is None:
+                raise ImportError
             if isinstance(value, torch.Tensor):
                 value = Tensor(value.detach().cpu(), shared_memory=shared_memory)
         except ImportError:

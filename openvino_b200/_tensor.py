@@ -7,6 +7,7 @@ views, ``data`` as a numpy view, settable ``shape``, ``copy_to`` / ``copy_from``
 """
 from __future__ import annotations
 
+import sys
 from typing import Optional, Sequence
 
 import numpy as np
@@ -41,7 +42,9 @@ class Tensor:
                 self._data = self._alloc(n)
             return
         try:
-            import torch
+            torch = sys.modules.get("torch")      # a torch tensor can only arrive if the caller imported torch already
+            if torch is None:
+                raise ImportError
             if isinstance(array, torch.Tensor):
                 if array.is_cuda:
                     self._torch = array

@@ -96,6 +96,10 @@ int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, in
 // Greedy sampling: out_ids[r] = argmax_v logits[r, v] (first index on ties); optional out_max.
 int ovb_argmax(const void* logits, int ld, int rows, int vocab, void* out_ids, int ids_i32, float* out_max,
                ovb_stream_t stream);
+// Stochastic sampling (sampling.cu): temperature, top-k, top-p; deterministic for a (seed, *step, row) triple.
+int ovb_sample(const void* logits, int ld, int rows, int vocab, float temperature, int top_k, float top_p, uint64_t seed,
+               const int* step, int* out_ids, ovb_stream_t stream);
+int ovb_bump(int* counter, ovb_stream_t stream);     // *counter += 1 on the device
 int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream);
 // Mixture of experts. Router: softmax over E logits per token, top-k kept and renormalised; weights is dense [T, E] fp32.
 int ovb_moe_route_topk(const float* logits, float* weights, int T, int E, int k, ovb_stream_t stream);

@@ -22,7 +22,11 @@ class GenerationConfig:
     max_new_tokens: int = 128
     eos_token_id: int = -1
     ignore_eos: bool = True
-    do_sample: bool = False   # greedy only for now
+    do_sample: bool = False       # False: greedy. True: multinomial with the transforms below (whole pipeline, not per request)
+    temperature: float = 1.0
+    top_k: int = 0                # 0 = off
+    top_p: float = 1.0            # 1 = off
+    rng_seed: int = 0
 
 
 @dataclass
@@ -164,6 +168,10 @@ class ContinuousBatchingPipeline:
         """Serve all prompts to completion. ``lookahead`` steps may be in flight on the GPU while the host
         schedules the next one (the newest token of a sequence is fed back on the device), so host work
         overlaps GPU work; 0 = fully synchronous."""
+        if gen.do_sample:
+            self.ex.set_sampling(gen.temperature, gen.top_k, gen.top_p, gen.rng_seed)
+        else:
+            self.ex.set_sampling(0.0)
         rids = [self.add_request(p, gen) for p in prompts]
         inflight = []
         while self.has_non_finished_requests() or inflight:

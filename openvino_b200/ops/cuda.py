@@ -256,6 +256,22 @@ def silu_mul(gu, out=None):
     return out
 
 
+def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0, seed: int = 0, step: Optional[torch.Tensor] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Draw one token per row of bf16 ``logits`` [rows, V]; ``step``: device int32 word mixed into the random stream."""
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(lib().ovb_sample(C.c_void_p(logits.data_ptr()), C.c_int(logits.stride(0)), C.c_int(rows), C.c_int(V), C.c_float(temperature),
+                            C.c_int(top_k), C.c_float(top_p), C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), C.c_void_p(_ptr(step)),
+                            C.c_void_p(out.data_ptr()), C.c_void_p(_stream())), "ovb_sample")
+    return out
+
+
+def bump(counter: torch.Tensor) -> None:
+    _check(lib().ovb_bump(C.c_void_p(counter.data_ptr()), C.c_void_p(_stream())), "ovb_bump")
+
+
 def moe_route_topk(logits: torch.Tensor, k: int, out=None) -> torch.Tensor:
     """logits [T, E] fp32 -> dense routing weights [T, E] fp32 (softmax, top-k, renormalised)."""
     T, E = logits.shape

@@ -242,6 +242,18 @@ class CudaLlmExecutor:
         self.last_token = torch.zeros(max(max_seqs, 1) * 4, dtype=torch.int32, device=self.device)
         self._graphs = {}
         self.kernel_launches = 0
+        # sampling: None = greedy; (temperature, top_k, top_p, seed) = stochastic (single-rank only). The step word is
+        # bumped on the device before every draw, so replays of a captured decode graph keep drawing fresh numbers.
+        self.sampling = None
+        self.sample_step = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
+        new = None if temperature <= 0 else (float(temperature), int(top_k), float(top_p), int(seed))
+        if new is not None and self.tp_size > 1:
+            raise NotImplementedError("stochastic sampling over vocabulary shards is not implemented: use greedy decoding with tensor parallelism")
+        if new != self.sampling:
+            self._graphs.clear()       # captured decode graphs embed the sampling kernel
+        self.sampling = new
 
     # -- one forward pass over the buffers of `sb`
     def _forward(self, sb: StepBuffers, shp: StepShape) -> None:
@@ -301,7 +313,12 @@ class CudaLlmExecutor:
             self.comm.gemm_allreduce(x, wt, h, self.ws, site)
 
     def _sample(self, sb: StepBuffers, B: int) -> None:
-        if self.tp_size == 1:
+        if self.sampling is not None:
+            temp, top_k, top_p, seed = self.sampling
+            K.bump(self.sample_step)
+            K.sample(sb.logits[:B], temp, top_k, top_p, seed, self.sample_step, out=sb.tokens[:B])
+            self.kernel_launches += 1
+        elif self.tp_size == 1:
             K.argmax(sb.logits[:B], out=sb.tokens[:B])
         else:
             K.argmax(sb.logits[:B], out=sb.tokens[:B], out_max=sb.logit_max[:B])

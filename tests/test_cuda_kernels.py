@@ -269,3 +269,41 @@ def test_sdpa_dense(ops, dtype, D):
     qf, kf, vf = [t.float().reshape(B, S, H, D).transpose(1, 2) for t in (q, k, v)]
     ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf).transpose(1, 2).reshape(B * S, H * D)
     assert _rel_err(out, ref) < 1e-2
+
+
+def test_sampling_kernel(ops):
+    torch.manual_seed(11)
+    V = 1000
+    logits = (torch.randn(6, V, device="cuda") * 2).to(torch.bfloat16)
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    greedy = logits.float().argmax(-1).int()
+    # top_k = 1 and a tiny nucleus both reduce to the argmax
+    assert torch.equal(ops.sample(logits, 1.0, top_k=1, seed=3, step=step), greedy)
+    assert torch.equal(ops.sample(logits, 1.0, top_p=1e-4, seed=4, step=step), greedy)
+    assert torch.equal(ops.sample(logits, 0.01, seed=5, step=step), greedy)
+    # the same (seed, step) repeats, another step differs somewhere
+    a = ops.sample(logits, 1.0, seed=7, step=step)
+    b = ops.sample(logits, 1.0, seed=7, step=step)
+    assert torch.equal(a, b)
+    draws = []
+    for _ in range(40):
+        ops.bump(step)
+        draws.append(ops.sample(logits, 1.0, top_k=5, seed=7, step=step))
+    draws = torch.stack(draws)
+    top5 = logits.float().topk(5, -1).indices
+    assert all(int(draws[i, r]) in top5[r].tolist() for i in range(40) for r in range(6))
+    assert len({tuple(d.tolist()) for d in draws}) > 5
+    # frequencies follow the softmax: small vocabulary, many draws
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, -30.0, 0.5, 0.5, 1.5]], device="cuda").to(torch.bfloat16).repeat(512, 1)
+    counts = torch.zeros(8)
+    for _ in range(8):
+        ops.bump(step)
+        counts += torch.bincount(ops.sample(small, 1.0, seed=9, step=step).cpu().long(), minlength=8).float()
+    want = torch.softmax(small[0].float().cpu(), -1)
+    assert (counts / counts.sum() - want).abs().max() < 0.03
+    # nucleus: with top_p = 0.5 only the most likely tokens whose mass reaches 0.5 can appear
+    ops.bump(step)
+    nuc = ops.sample(small, 1.0, top_p=0.5, seed=10, step=step).cpu()
+    order = want.argsort(descending=True)
+    keep = order[: int((want[order].cumsum(0) < 0.5).sum()) + 1].tolist()
+    assert set(nuc.tolist()) <= set(keep)
