@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const __nv_bfloa
     float z = 0.f;
     for (int v = v0; v < v1; ++v) z += __expf((__bfloat162float(l[v]) - mx) * inv_temp);
     z = block_reduce(z, sh, false);
-    // bisection on the threshold: invariant  keep(lo) is acceptable (enough mass, maybe too many), keep(hi) is too small
+    // bisection on the threshold: keep(lo) is never smaller than the wanted set, keep(hi) may be
     float lo = mn, hi = mx;
     const bool restrict_k = top_k > 0 && top_k < V, restrict_p = top_p < 1.f;
     if (restrict_k || restrict_p) {
@@ -69,8 +69,9 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const __nv_bfloa
             }
             cnt = block_reduce(cnt, sh, false);
             mass = block_reduce(mass, sh, false);
-            // raising the threshold to mid is allowed while the kept set still satisfies every active rule's lower bound
-            const bool enough = (!restrict_p || mass >= top_p * z) && (!restrict_k || cnt >= (float)top_k);
+            // t* = max(t_k, t_p): the threshold may rise to mid while at least one active rule still holds there
+            // (t_k = largest t with count(>= t) >= k, t_p = largest t with mass(>= t) >= p)
+            const bool enough = (restrict_p && mass >= top_p * z) || (restrict_k && cnt >= (float)top_k);
             if (enough) lo = mid; else hi = mid;
         }
     }

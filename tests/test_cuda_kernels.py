@@ -290,8 +290,9 @@ def test_sampling_kernel(ops):
         ops.bump(step)
         draws.append(ops.sample(logits, 1.0, top_k=5, seed=7, step=step))
     draws = torch.stack(draws)
-    top5 = logits.float().topk(5, -1).indices
-    assert all(int(draws[i, r]) in top5[r].tolist() for i in range(40) for r in range(6))
+    fifth = logits.float().topk(5, -1).values[:, -1]           # ties with the 5th value stay in the kept set
+    picked = torch.gather(logits.float(), 1, draws.t().long())  # [rows, draws]
+    assert (picked >= fifth[:, None]).all()
     assert len({tuple(d.tolist()) for d in draws}) > 5
     # frequencies follow the softmax: small vocabulary, many draws
     small = torch.tensor([[2.0, 1.0, 0.0, -1.0, -30.0, 0.5, 0.5, 1.5]], device="cuda").to(torch.bfloat16).repeat(512, 1)
