@@ -105,9 +105,23 @@ class OnnxFrontEnd(FrontEnd):
         return onnx.convert(model)
 
 
+class GgufFrontEnd(FrontEnd):
+    name = "gguf"
+
+    def supported(self, model) -> bool:
+        if isinstance(model, (str, os.PathLike)) and str(model).lower().endswith(".gguf"):
+            return True
+        return False
+
+    def convert(self, input_model) -> Model:
+        from . import gguf
+        model, _ = input_model
+        return gguf.convert(str(model))
+
+
 class FrontEndManager:
     def __init__(self):
-        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd()}
+        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "gguf": GgufFrontEnd()}
 
     def get_available_front_ends(self) -> List[str]:
         return list(self._frontends)
@@ -131,7 +145,7 @@ _manager = FrontEndManager()
 
 
 def read_model(model, weights=None, extensions=None) -> Model:
-    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor) or an ``.onnx`` file."""
+    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor), a ``.gguf`` or an ``.onnx`` file."""
     if isinstance(model, Model):
         return model
     if hasattr(model, "read"):
