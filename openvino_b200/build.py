@@ -3,6 +3,7 @@
 * ``libovb_cuda.so``  - sm_100a kernels (nvcc, C ABI, loaded with ctypes)
 * ``_ovcore*.so``     - native core: graph IR, IR v11 reader/writer, passes, CPU reference
                         executor, runtime and scheduler (g++ + pybind11)
+* ``libopenvino_b200_c.so`` - the same core behind the C API (no Python dependency)
 
 Both are written next to the sources inside the package so that a checkout is
 self-contained: nothing is installed into site-packages and no JIT cache is used.
@@ -124,9 +125,39 @@ def build_core(force: bool = False) -> Path | None:
     return target
 
 
+def build_capi(force: bool = False) -> Path | None:
+    """Link the native core (without the Python bindings) and the C API into ``lib/libopenvino_b200_c.so``."""
+    capi = sorted((CSRC / "capi").glob("*.cpp"))
+    if not capi:
+        return None
+    LIB.mkdir(exist_ok=True)
+    OBJ.mkdir(exist_ok=True)
+    target = LIB / "libopenvino_b200_c.so"
+    core = [s for s in core_sources() if s.stem != "bind"]
+    hdrs = sorted((CSRC / "core").glob("*.hpp")) + sorted((PKG / "include").rglob("*.h"))
+    if not force and not _stale(target, capi + core + hdrs):
+        return target
+    cxx = os.environ.get("CXX", "g++")
+    inc = ["-I", str(CSRC / "core")]
+
+    def compile_one(src: Path) -> Path:
+        obj = OBJ / ("capi_" + src.stem + ".o")
+        if force or _stale(obj, [src] + hdrs):
+            _run([cxx, *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(compile_one, capi + core))
+    vers = OBJ / "ovcapi.map"
+    vers.write_text("{ global: ov_*; local: *; };\n")
+    _run([cxx, "-shared", "-o", str(target), *map(str, objs), "-pthread", "-Wl,--version-script=%s" % vers, "-Wl,-Bsymbolic"])
+    return target
+
+
 def build_all(force: bool = False) -> None:
     build_cuda(force)
     build_core(force)
+    build_capi(force)
 
 
 if __name__ == "__main__":
