@@ -22,9 +22,8 @@ def apply_low_latency_transformation(model: Model, use_const_initializer: bool =
 
 
 def apply_pruning_transformation(model: Model) -> None:
-    """Removes channels whose weights are entirely zero is not part of this framework's offline passes; the call
-    validates the graph and leaves it unchanged so that scripts written for the reference keep working."""
-    model.validate_nodes_and_infer_types()
+    from .passes.pruning import Pruning
+    Pruning().run_on_model(model)
 
 
 def apply_make_stateful_transformation(model: Model, param_res_names) -> None:
@@ -36,9 +35,8 @@ def compress_model_transformation(model: Model) -> None:
 
 
 def compress_quantize_weights_transformation(model: Model) -> None:
-    m = _passes.Manager()
-    m.register_pass("ConstantFolding")
-    m.run_passes(model)
+    from .passes.low_precision import CompressQuantizeWeights
+    CompressQuantizeWeights().run_on_model(model)
 
 
 def convert_sequence_to_tensor_iterator_transformation(model: Model) -> None:
