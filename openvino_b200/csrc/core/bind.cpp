@@ -8,6 +8,7 @@
 #include "ir.hpp"
 #include "pass.hpp"
 #include "runtime.hpp"
+#include "sysconf.hpp"
 #include "sched.hpp"
 
 namespace py = pybind11;
@@ -483,6 +484,24 @@ PYBIND11_MODULE(_ovcore, mod) {
     }, py::arg("model"), py::arg("options") = py::dict());
     mod.def("make_stateful", &make_stateful);
     mod.def("stateful_to_stateless", &stateful_to_stateless);
+
+    // ------------------------------------------------------------------ host topology
+    py::class_<CpuTopology>(mod, "CpuTopology")
+        .def_readonly("sockets", &CpuTopology::sockets)
+        .def_readonly("numa_nodes", &CpuTopology::numa_nodes)
+        .def_readonly("cores", &CpuTopology::cores)
+        .def_readonly("processors", &CpuTopology::processors)
+        .def_readonly("proc_type_table", &CpuTopology::proc_type_table)
+        .def_readonly("cpu_mapping_table", &CpuTopology::cpu_mapping_table)
+        .def_readonly("flags", &CpuTopology::flags)
+        .def("has", &CpuTopology::has);
+    mod.def("read_cpu_topology", &read_cpu_topology, py::arg("root") = "/");
+    mod.def("host_cpu_topology", []() { return host_cpu_topology(); });
+    mod.def("parse_cpu_list", &parse_cpu_list);
+    mod.def("plan_streams", [](const CpuTopology& t, const std::string& hint, int streams, int threads) {
+        const StreamsPlan p = plan_streams(t, hint, streams, threads);
+        return py::make_tuple(p.num_streams, p.threads_per_stream);
+    }, py::arg("topology"), py::arg("hint") = "LATENCY", py::arg("num_streams") = 0, py::arg("num_threads") = 0);
     mod.def("compress_weights", &compress_weights, py::arg("model"), py::arg("mode") = "int4_asym", py::arg("group_size") = 128,
             py::arg("ratio") = 1.0, py::arg("all_layers") = false);
     mod.def("compress_model_to_f16", &compress_model_to_f16);

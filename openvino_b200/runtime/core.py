@@ -813,7 +813,9 @@ class CpuPlugin(Plugin):
         rm = model.clone()
         _c.run_moc_transformations(rm._m, True)
         if str(cfg.get(props.hint.performance_mode)) == "THROUGHPUT" and props.num_streams not in config and props.num_streams not in self.config:
-            cfg[props.num_streams] = max(1, min(8, (os.cpu_count() or 2) // 2))
+            # stream count from the host topology (physical cores, NUMA nodes), as the reference CPU device does
+            streams, _ = _c.plan_streams(_c.host_cpu_topology(), "THROUGHPUT", 0, int(cfg.get(props.inference_num_threads, 0) or 0))
+            cfg[props.num_streams] = max(1, min(16, streams))
         return CpuCompiledModel(self, model, cfg, rm)
 
     def query_model(self, model: Model, config: dict) -> Dict[str, str]:
