@@ -380,6 +380,42 @@ __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int*
     }
 }
 
+// Vector form for head sizes that are multiples of 4: one warp per (token, head), a lane rotates two adjacent pairs
+// (bf16x2 loads and stores); the grid covers every head of every token, so a decode step of a few dozen tokens still
+// fills the machine.
+__global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                                         const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache,
+                                         __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D, float log2_theta,
+                                         int block_size) {
+    const int t = blockIdx.x;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (h >= Hq + 2 * Hkv) return;
+    const int half = D >> 1;
+    const int slot = slot_map[t];
+    const int blk = slot / block_size, off = slot - blk * block_size;
+    __nv_bfloat16* p = qkv + ((size_t)t * (Hq + 2 * Hkv) + h) * D;
+    if (h >= Hq + Hkv) {                       // value head: copy to the cache
+        if (slot < 0) return;
+        __nv_bfloat16* c = v_cache + (((size_t)blk * Hkv + (h - Hq - Hkv)) * block_size + off) * D;
+        for (int d = lane * 2; d < D; d += 64) *reinterpret_cast<uint32_t*>(c + d) = *reinterpret_cast<const uint32_t*>(p + d);
+        return;
+    }
+    const bool is_k = h >= Hq;
+    if (is_k && slot < 0) return;
+    __nv_bfloat16* dst = is_k ? k_cache + (((size_t)blk * Hkv + (h - Hq)) * block_size + off) * D : p;
+    const float pos = float(positions[t]);
+    for (int d = lane * 2; d < half; d += 64) {
+        float s0, c0, s1, c1;
+        sincosf(pos * exp2f(-log2_theta * (2.0f * float(d) / float(D))), &s0, &c0);
+        sincosf(pos * exp2f(-log2_theta * (2.0f * float(d + 1) / float(D))), &s1, &c1);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + d));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + d + half));
+        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+        *reinterpret_cast<__nv_bfloat162*>(dst + d + half) = __floats2bfloat162_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+    }
+}
+
 // ------------------------------------------------------------------------------------ int4 re-pack
 // IR layout: byte b of a row holds element 2b in its low nibble and 2b+1 in its high nibble.
 // Plugin layout: every aligned group of 8 elements e0..e7 becomes one u32 with nibble j (j<4) = e[2j]
@@ -576,8 +612,15 @@ int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(qkv && positions && slot_map && k_cache && v_cache && T > 0, "ovb_rope_kv_write: null operand");
     OVB_REQUIRE(D % 2 == 0, "ovb_rope_kv_write: head size must be even");
-    rope_kv_write_kernel<<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
-                                                (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
+    if (D % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 3) == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 3) == 0 &&
+        (reinterpret_cast<uintptr_t>(v_cache) & 3) == 0) {
+        const int heads = Hq + 2 * Hkv;
+        rope_kv_write_vec_kernel<<<dim3(T, (heads + 3) / 4), 128, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
+                                                                                (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
+    } else {
+        rope_kv_write_kernel<<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
+                                                    (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
+    }
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

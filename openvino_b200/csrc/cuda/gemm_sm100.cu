@@ -18,8 +18,10 @@
 //    of use (HBM latency hidden), and a short ring of MMA stages (token tile + expanded bf16 weight
 //    tile). Each MMA stage is owned by one or two dequant warps, so several k-blocks are expanded at the
 //    same time; a stage is handed to the MMA through an mbarrier after fence.proxy.async.
-//  * Small-T problems (decode) are split along K so that every SM streams weights; the last CTA
-//    to arrive at a tile reduces the fp32 partials in a fixed order (bitwise reproducible).
+//  * Small-T problems (decode) are split along K so that every SM streams weights. The splits of a tile form a
+//    thread-block cluster: every CTA leaves its fp32 partial tile in its own shared memory, and after a cluster
+//    barrier each CTA sums one slice of the tile over all partials through distributed shared memory, in split
+//    order (bitwise reproducible), and writes that slice of the output. No partial ever goes to global memory.
 //  * Epilogue: TMEM -> registers -> (bias, activation) -> 16-bit tile in shared memory -> coalesced
 //    16-byte stores (residual added on the way out).
 #include <stdlib.h>
@@ -75,6 +77,9 @@ constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 u
 // lanes (waits vs. issue) into the split-K workspace. TR(x) keeps the statements out of normal builds entirely.
 #ifdef OVB_GEMM_TRACE
 #define TR(...) __VA_ARGS__
+__device__ long long g_cta_trace[16384 * 4];   // per CTA: start, last MMA issued, end (globaltimer ns), SM id
+__device__ long long g_it_trace[64 * 8];         // CTA 0, per iteration: clock64 at the control lanes' hand-over points
+#define TRI(i, k) if (blockIdx.x == 0 && blockIdx.z == 0 && (i) < 64) g_it_trace[(i) * 8 + (k)] = clock64();
 #else
 #define TR(...)
 #endif
@@ -140,24 +145,39 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+constexpr bool is_quant(int wmode) { return wmode == OVB_W_U4 || wmode == OVB_W_U8 || wmode == OVB_W_F8; }
+constexpr int wq_bytes(int wmode) { return wmode == OVB_W_U4 ? TILE_N * 32 : ((wmode == OVB_W_U8 || wmode == OVB_W_F8) ? TILE_N * 64 : 0); }
+
+// Four fp8 e4m3 bytes -> four bf16 (two words), each scaled: an e4m3 byte placed at bits 4..10 (sign at 15) of a bf16
+// reads as value * 2^-120 (sub-normals included), and the per-block scale in `ss` already carries the 2^120.
+__device__ __forceinline__ void dequant_f8x4(uint32_t w, __nv_bfloat162 ss, uint32_t& lo, uint32_t& hi) {
+    const uint32_t y0 = __byte_perm(w, 0u, 0x4140), y1 = __byte_perm(w, 0u, 0x4342);
+    uint32_t t0 = ((y0 << 8) & 0x80008000u) | ((y0 << 4) & 0x07F007F0u);
+    uint32_t t1 = ((y1 << 8) & 0x80008000u) | ((y1 << 4) & 0x07F007F0u);
+    __nv_bfloat162 v0 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&t0), ss);
+    __nv_bfloat162 v1 = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&t1), ss);
+    lo = *reinterpret_cast<uint32_t*>(&v0);
+    hi = *reinterpret_cast<uint32_t*>(&v1);
+}
+
 // Quantised stages cover two k-blocks (128 elements of K) except for 256-token tiles, whose token tile alone is 32 KB
 // per k-block: every barrier round trip between the producers, the dequant warps and the MMA issuer then moves twice
 // the data, which halves the per-byte cost of the control chain.
-constexpr int kblocks_per_stage(int bt, int wmode) { return (wmode == OVB_W_U4 || wmode == OVB_W_U8) && bt < 256 ? 2 : 1; }
+constexpr int kblocks_per_stage(int bt, int wmode) { return is_quant(wmode) && bt < 256 ? 2 : 1; }
 
 // Decode-sized quantised problems run two CTAs per SM: one CTA's control chain (barrier round trips between the
 // producer, the dequant warps and the MMA issuer) is latency bound, a second resident CTA fills the gaps.
-constexpr bool two_ctas(int bt, int wmode) { return bt <= 64 && (wmode == OVB_W_U4 || wmode == OVB_W_U8); }
+constexpr bool two_ctas(int bt, int wmode) { return bt <= 64 && is_quant(wmode); }
 
 template <int BT, int WMODE, bool F16>
 __global__ void __launch_bounds__(GEMM_THREADS, two_ctas(BT, WMODE) ? 2 : 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmKParams p) {
     using E = typename Elem<F16>::type;
-    constexpr bool QUANT = (WMODE == OVB_W_U4 || WMODE == OVB_W_U8);
+    constexpr bool QUANT = is_quant(WMODE);
     constexpr int KPS = kblocks_per_stage(BT, WMODE);   // k-blocks per pipeline stage (see STAGE_BYTES)
     constexpr int X_BYTES = BT * 128;
     constexpr int W_BYTES = TILE_N * 128;
-    constexpr int WQ_BYTES = (WMODE == OVB_W_U4) ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
+    constexpr int WQ_BYTES = wq_bytes(WMODE);
     constexpr int ROW_PKT = WQ_BYTES / TILE_N;          // packed bytes per row and k-block
     constexpr int SZ_BYTES = QUANT ? TILE_N * 4 : 0;    // (scale, zero point) pairs of the tile's rows for one k-block
     constexpr int WQ_SLOT = WQ_BYTES + SZ_BYTES;        // one k-block in the ring: packed chunk, then its pairs
@@ -176,8 +196,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int pslots = p.pslots;
     uint8_t* pring = smem + stages * STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(pring + pslots * RING_SLOT);
-    uint64_t* full_x = bars;                         // [stages] token tile (and bf16 weight chunk) landed
-    uint64_t* full_dq = bars + MAX_STAGES;           // [stages] expanded weight tile written
+    uint64_t* full_x = bars;                         // [stages] token tile landed and (quantised modes) weight tile expanded into TMEM
     uint64_t* empty = bars + 2 * MAX_STAGES;         // [stages] MMAs that read the stage retired
     uint64_t* p_full = bars + 3 * MAX_STAGES;        // [pslots] packed chunk landed
     uint64_t* p_empty = p_full + MAX_PSLOTS;         // [pslots] packed chunk consumed
@@ -189,6 +208,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     TR(long long tr_k0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_k0));)
+    TR(const int tr_cta = (blockIdx.z * gridDim.x + blockIdx.x) & 16383;
+       if (threadIdx.x == 0) { uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_cta_trace[tr_cta * 4] = tr_k0; g_cta_trace[tr_cta * 4 + 3] = sm; })
     // Tile order: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so the
     // CTAs that are resident together share a few weight tiles and a few token tiles in L2.
     int n_tile, t_tile;
@@ -204,7 +225,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
     const int n0 = n_tile * TILE_N;
     const int t0 = t_tile * BT;
-    const int split = blockIdx.z;
+    const int split = p.splits > 1 ? (int)cluster_ctarank() : 0;   // the splits of a tile are one cluster along z
     const int total_kb = (p.K + TILE_K - 1) / TILE_K;
     const int kb_begin = split * p.kblocks_per_split;
     const int kb_end = min(total_kb, kb_begin + p.kblocks_per_split);
@@ -214,8 +235,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
-            mbar_init(&full_x[s], 1);
-            mbar_init(&full_dq[s], NUM_DQ_WARPS);
+            mbar_init(&full_x[s], QUANT ? 1 + NUM_DQ_WARPS : 1);   // producer's expect_tx arrival (+ one arrival per dequant warp)
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < pslots; ++s) {
@@ -260,7 +280,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 int kcoord = kb_begin * TILE_K;
                 for (int iw = 0; iw < num_it; ++iw) {
                     if (!mbar_wait(&p_empty[wslot], wpar, abort_flag, p.status)) break;
-                    TR(const long long tr_a = clock64();)
+                    TR(const long long tr_a = clock64(); TRI(iw, 7))
                     const int nk = min(KPS, num_kb - iw * KPS);
                     mbar_arrive_expect_tx(&p_full[wslot], nk * WQ_SLOT);
                     if (WMODE == OVB_W_U4) {
@@ -311,7 +331,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             TR(long long tr_t0 = clock64(); long long tr_x = 0;)
             for (int ix = 0; ix < num_it; ++ix) {
                 if (!mbar_wait(&empty[xs], xpar, abort_flag, p.status)) break;
-                TR(const long long tr_c = clock64();)
+                TR(const long long tr_c = clock64(); TRI(ix, 6))
                 const int nk = min(KPS, num_kb - ix * KPS);
                 mbar_arrive_expect_tx(&full_x[xs], nk * X_BYTES);
                 for (int t = 0; t < nk; ++t) {
@@ -342,14 +362,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             TR(long long tr_t0 = clock64(), tr_wx = 0, tr_wd = 0, tr_is = 0;)
             for (int i = 0; i < (QUANT ? num_it : num_kb); ++i) {
                 TR(const long long tr_a = clock64();)
-                int ok = 0;
-                if (lane == 0) {
-                    ok = mbar_wait(&full_x[s], phase, abort_flag, p.status) ? 1 : 0;
-                    TR(tr_wx += clock64() - tr_a;)
-                    if (ok && QUANT) ok = mbar_wait(&full_dq[s], phase, abort_flag, p.status) ? 1 : 0;
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                TR(const long long tr_c = clock64(); tr_wd += tr_c - tr_a;)
+                // every lane polls the same barrier word (no divergence, no shuffle): one wait per stage covers both the
+                // token tile and the expanded weights
+                const bool ok = mbar_wait(&full_x[s], phase, abort_flag, p.status);
+                TR(const long long tr_c = clock64(); tr_wx += tr_c - tr_a; tr_wd += tr_c - tr_a; if (lane == 0) { TRI(i, 0) TRI(i, 1) })
                 if (!ok) break;
                 tc_fence_after_sync();
                 // descriptors differ only in the 16-byte-unit start address (low 14 bits, no carry out here)
@@ -372,12 +388,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     for (int k = 1; k < TILE_K / 16; ++k) umma_f16_ss_elect(tmem_base, da0 + 2 * k, db0 + 2 * k, idesc, 1u);
                 }
                 umma_commit_elect(&empty[s]);
-                TR(tr_is += clock64() - tr_c;)
+                TR(tr_is += clock64() - tr_c; if (lane == 0) { TRI(i, 2) })
                 if (++s == stages) { s = 0; phase ^= 1; }
             }
             umma_commit_elect(acc_full);
-            TR(if (lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-                   reinterpret_cast<long long*>(p.ws)[25] = t - tr_k0; })
+            TR(if (lane == 0) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_cta_trace[tr_cta * 4 + 1] = t;
+                   if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) reinterpret_cast<long long*>(p.ws)[25] = t - tr_k0; })
             TR(if (lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
                    o[8] = clock64() - tr_t0; o[9] = tr_wx; o[10] = tr_wd - tr_wx; o[11] = tr_is; })
         }
@@ -398,17 +414,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const uint32_t a_lane = tmem_base + (uint32_t(qd * 32) << 16) + uint32_t(ACC_COLS + (KPS == 2 ? grp * 32 : 0));
             TR(long long tr_t0 = clock64(), tr_wp = 0, tr_we = 0, tr_wk = 0;)
             for (int i = 0; i < num_it; ++i) {
-                // lane 0 polls, the shuffle hands the observation on to the other lanes
-                int ok = 0;
+                // every lane polls (same word, same answer): no divergence and no shuffle on the way to the work
                 TR(const long long tr_a = clock64(); long long tr_b = tr_a;)
-                if (lane == 0) {
-                    if (mbar_wait(&p_full[slot], ppar, abort_flag, p.status)) {
-                        TR(tr_b = clock64();)
-                        ok = mbar_wait(&empty[st], phase ^ 1, abort_flag, p.status) ? 1 : 0;
-                    }
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                TR(const long long tr_c = clock64(); tr_wp += tr_b - tr_a; tr_we += tr_c - tr_b;)
+                bool ok = mbar_wait(&p_full[slot], ppar, abort_flag, p.status);
+                TR(tr_b = clock64(); if (warp == 2 && lane == 0) { TRI(i, 3) })
+                ok = ok && mbar_wait(&empty[st], phase ^ 1, abort_flag, p.status);
+                TR(const long long tr_c = clock64(); tr_wp += tr_b - tr_a; tr_we += tr_c - tr_b; if (warp == 2 && lane == 0) { TRI(i, 4) })
                 if (!ok) break;
                 // KPS == 2: group g expands k-block g of the stage; KPS == 1: the groups take alternate stages
                 const uint32_t slot_a = smem_u32(pring + slot * RING_SLOT + (KPS == 2 ? grp * WQ_SLOT : 0));
@@ -425,8 +436,23 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     const uint32_t xs[8] = {pk0.x, pk0.y, pk0.z, pk0.w, pk1.x, pk1.y, pk1.z, pk1.w};
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
+#ifdef OVB_GEMM_TRACE_NO_ALU   // tuning experiment: how fast is the control chain without the expansion arithmetic
+                        r[4 * j] = xs[j]; r[4 * j + 1] = xs[j]; r[4 * j + 2] = xs[j]; r[4 * j + 3] = xs[j];
+                        (void)zz2; (void)ss2;
+#else
                         const uint4 e = dequant_u4x8(xs[j], zz2, ss2);
                         r[4 * j] = e.x; r[4 * j + 1] = e.y; r[4 * j + 2] = e.z; r[4 * j + 3] = e.w;
+#endif
+                    }
+                } else if (WMODE == OVB_W_F8) {
+                    const __nv_bfloat162 ss2 = __halves2bfloat162(__low2bfloat16(szp), __low2bfloat16(szp));
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const uint4 pk = lds128(slot_a + row * ROW_PKT + h * 16);
+                        dequant_f8x4(pk.x, ss2, r[h * 8 + 0], r[h * 8 + 1]);
+                        dequant_f8x4(pk.y, ss2, r[h * 8 + 2], r[h * 8 + 3]);
+                        dequant_f8x4(pk.z, ss2, r[h * 8 + 4], r[h * 8 + 5]);
+                        dequant_f8x4(pk.w, ss2, r[h * 8 + 6], r[h * 8 + 7]);
                     }
                 } else {
                     const float sf = __bfloat162float(__low2bfloat16(szp));
@@ -449,8 +475,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
                 tc_fence_before_sync();
                 __syncwarp();
+                TR(if (warp == 2 && lane == 0) { TRI(i, 5) })
                 if (lane == 0) {
-                    mbar_arrive(&full_dq[st]);
+                    mbar_arrive(&full_x[st]);
                     mbar_arrive(&p_empty[slot]);
                 }
                 if (++st == stages) { st = 0; phase ^= 1; }
@@ -478,7 +505,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
         const float bias_v = (p.bias != nullptr && oc < p.N) ? to_float(reinterpret_cast<const E*>(p.bias)[oc]) : 0.f;
         const int tile_id = blockIdx.x;
-        float* ws_tile = p.ws ? p.ws + ((size_t)tile_id * p.splits) * (TILE_N * BT) : nullptr;
         // Fast path: whole 128-row tile inside N, 16-bit output with 16-byte aligned rows. The tile is staged
         // in shared memory as [token][128] (the pipeline stages are free by now) and written with 16-byte
         // stores that cover 256 contiguous bytes per token row.
@@ -641,9 +667,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
                     for (int j = 0; j < 16; ++j) finish(c0 + j, __uint_as_float(r[j]));
                 } else {
-                    float* dst = ws_tile + (size_t)split * (TILE_N * BT);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) dst[(c0 + j) * TILE_N + row] = __uint_as_float(r[j]);
+                    for (int j = 0; j < 16; ++j) stage_out[(c0 + j) * TILE_N + row] = __uint_as_float(r[j]);
                 }
             }
         }
@@ -678,36 +703,36 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
         }
         if (p.splits > 1) {
-            // Last CTA to arrive at this tile sums the partials in split order.
-            __threadfence();
-            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-            if (dq_tid == 0) {
-                const int prev = atomicAdd(&p.counters[tile_id], 1);
-                *last_flag = (prev == p.splits - 1) ? 1 : 0;
-                if (prev == p.splits - 1) p.counters[tile_id] = 0;
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-            if (*last_flag && comm) {
-                __threadfence();
-                constexpr int TOTAL4 = TILE_N * BT / 4;
-                for (int i4 = dq_tid; i4 < TOTAL4; i4 += DQ_THREADS) {
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int z = 0; z < p.splits; ++z) {
-                        const float4 v = __ldcg(reinterpret_cast<const float4*>(ws_tile + (size_t)z * (TILE_N * BT)) + i4);
-                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            // Every CTA of the cluster (one per split) holds its fp32 partial tile in `stage_out`. After the first cluster
+            // barrier CTA r sums slice r of the tile over all partials (split order) and writes that part of the output;
+            // the second barrier keeps every partial alive until all peers have read it. With the fused all-reduce the
+            // whole tile is summed by CTA 0 (in place), which then runs the communication epilogue on it.
+            cluster_arrive();
+            cluster_wait();
+            constexpr int TOTAL4 = TILE_N * BT / 4;
+            const uint32_t S = (uint32_t)p.splits;
+            const uint32_t base = smem_u32(stage_out);
+            const bool ok_all = (*abort_flag == 0);
+            if (ok_all && comm) {
+                if (split == 0) {
+                    for (int i4 = dq_tid; i4 < TOTAL4; i4 += DQ_THREADS) {
+                        float4 acc = reinterpret_cast<float4*>(stage_out)[i4];
+#pragma unroll 4
+                        for (uint32_t z = 1; z < S; ++z) {
+                            const float4 v = ld_dsmem_f4(dsmem_addr(base + (uint32_t)i4 * 16u, z));
+                            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                        }
+                        reinterpret_cast<float4*>(stage_out)[i4] = acc;
                     }
-                    reinterpret_cast<float4*>(stage_out)[i4] = acc;
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (*abort_flag == 0) comm_epilogue();
-            } else if (*last_flag) {
-                __threadfence();
-                // all 256 threads: float4 pieces of the [BT][128] partial tiles, every split in flight at once
-                constexpr int TOTAL4 = TILE_N * BT / 4;
-                for (int i4 = dq_tid; i4 < TOTAL4; i4 += DQ_THREADS) {
+            } else if (ok_all) {
+                const int per = (TOTAL4 + (int)S - 1) / (int)S;
+                const int i_end = min(TOTAL4, (split + 1) * per);
+                for (int i4 = split * per + dq_tid; i4 < i_end; i4 += DQ_THREADS) {
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int z = 0; z < p.splits; ++z) {
-                        const float4 v = __ldcg(reinterpret_cast<const float4*>(ws_tile + (size_t)z * (TILE_N * BT)) + i4);
+#pragma unroll 4
+                    for (uint32_t z = 0; z < S; ++z) {
+                        const float4 v = ld_dsmem_f4(dsmem_addr(base + (uint32_t)i4 * 16u, z));
                         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                     }
                     const int e = i4 * 4;
@@ -742,14 +767,28 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     }
                 }
             }
+            cluster_arrive();
+            cluster_wait();
+            if (comm && split == 0) {
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (*abort_flag == 0) comm_epilogue();
+            }
         }
+    }
+    // The producer and MMA warps take part in the two cluster barriers of the split-K reduction (a cluster barrier
+    // counts every thread of every CTA).
+    if (p.splits > 1 && (warp < 2 || warp == X_PRODUCER_WARP)) {
+        cluster_arrive();
+        cluster_wait();
+        cluster_arrive();
+        cluster_wait();
     }
 
     // ---------------------------------------------------------------- tear-down
     tc_fence_before_sync();
     __syncthreads();
-    TR(if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-           reinterpret_cast<long long*>(p.ws)[26] = t - tr_k0; })
+    TR(if (threadIdx.x == 0) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_cta_trace[tr_cta * 4 + 2] = t;
+           if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) reinterpret_cast<long long*>(p.ws)[26] = t - tr_k0; })
     if (*abort_flag) {
         // Give copies that are still in flight time to land before the CTA's shared memory is reused.
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -775,26 +814,29 @@ static int pick_block_t(int T) {
     return 256;
 }
 
-static int pick_splits(int T, int N, int K, int bt, int wmode) {
-    // Split-K trades idle SMs against extra traffic: every split writes an fp32 partial tile that the last CTA of the
-    // tile reads back. Estimate the time of every candidate with a small model (all constants in microseconds,
-    // measured on B200 with the decode shapes of an 8B model) and take the cheapest.
+constexpr int kMaxSplits = 8;   // portable cluster size
+
+// Split-K trades idle SMs against the cost of the cluster reduction (two cluster barriers and one pass over the partial
+// tiles through distributed shared memory). Estimate the time of every candidate with a small model (all constants in
+// microseconds, measured on B200 with the decode shapes of an 8B model) and take the cheapest. `resident[s]` is the
+// number of CTAs of a launch with clusters of s that the device holds at a time (clusters are placed inside one GPC, so
+// it is not simply a multiple of the SM count).
+static int pick_splits(int T, int N, int K, int bt, int wmode, const int* resident) {
     const int tiles = ceil_div(N, TILE_N) * ceil_div(T, bt);
     const int total_kb = ceil_div(K, TILE_K);
-    const int slots = two_ctas(bt, wmode) ? 2 * kNumSMs : kNumSMs;        // CTAs resident at a time
-    if (tiles >= slots || total_kb < 8) return 1;
-    const double t_kb = (wmode == OVB_W_U4 || wmode == OVB_W_U8) ? 0.36 : 0.12 + 0.0028 * bt;   // one k-block in one CTA
+    if (tiles >= resident[1] || total_kb < 8) return 1;
+    const double t_kb = is_quant(wmode) ? 0.36 : 0.12 + 0.0028 * bt;   // one k-block in one CTA
     const double t_cta = 6.0;                                              // set-up, pipeline fill, epilogue of a CTA
-    const double partial_us_per_mb = 0.45;                                 // write + read of partials through L2/HBM
     int best = 1;
     double best_t = 1e30;
-    const int max_s = total_kb / 4 < 16 ? total_kb / 4 : 16;
+    const int max_s = total_kb / 4 < kMaxSplits ? total_kb / 4 : kMaxSplits;
     for (int s = 1; s <= max_s; ++s) {
+        if (resident[s] <= 0) continue;
         const int ctas = tiles * s;
-        const int waves = ceil_div(ctas, slots);
+        const int waves = ceil_div(ctas, resident[s]);
         const bool shared_sm = two_ctas(bt, wmode) && ctas > kNumSMs;      // two CTAs on an SM slow each other down
         double t = waves * (ceil_div(total_kb, s) * t_kb * (shared_sm ? 1.25 : 1.0) + t_cta);
-        if (s > 1) t += 2.0 * s * double(T) * N * 4.0 / 1e6 * partial_us_per_mb;
+        if (s > 1) t += 2.5;                                               // cluster barriers + the slice reduction
         if (t < best_t - 0.25) { best_t = t; best = s; }
     }
     return best;
@@ -803,7 +845,7 @@ static int pick_splits(int T, int N, int K, int bt, int wmode) {
 // MMA stages and packed-ring slots that fit the shared-memory budget.
 static void pick_rings(int bt, int wmode, int* stages, int* pslots) {
     const int stage = bt * 128 + TILE_N * 128;
-    const int wq = wmode == OVB_W_U4 ? TILE_N * 32 : (wmode == OVB_W_U8 ? TILE_N * 64 : 0);
+    const int wq = wq_bytes(wmode);
     if (wq == 0) {
         int s = kSmemBudget / stage;
         *stages = s > MAX_STAGES ? MAX_STAGES : (s < 2 ? 2 : s);
@@ -821,7 +863,10 @@ static void pick_rings(int bt, int wmode, int* stages, int* pslots) {
         s = 3;                               // accumulator (<= 64 columns) + 3 x 64 columns of A
         budget = (kSmemLimit - 2 * 1024) / 2 - 2560;
     } else {
-        s = 4;                               // accumulator + 4 x 64 (or 4 x 32) columns of A fit the 512 TMEM columns
+        // Large token tiles come from L2 with a latency of a microsecond or two under load: the token ring has to cover
+        // it (a 256-token stage is consumed in ~0.3 us), the packed-weight ring keeps what is left. The accumulator and
+        // s x 32 (64 for two-k-block stages) columns of A fit the 512 TMEM columns.
+        s = bt >= 256 ? 6 : (bt >= 128 ? 5 : 4);
         budget = kSmemBudget;
     }
     int pmax = (budget - s * xstage) / slot;
@@ -837,7 +882,7 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     pick_rings(BT, WMODE, &stages, &pslots);
     p.stages = stages;
     p.pslots = pslots;
-    const int wq = WMODE == OVB_W_U4 ? TILE_N * 32 : (WMODE == OVB_W_U8 ? TILE_N * 64 : 0);
+    const int wq = wq_bytes(WMODE);
     const int kps = kblocks_per_stage(BT, WMODE);
     const int smem = stages * (wq ? kps * BT * 128 : BT * 128 + TILE_N * 128) + pslots * (wq ? kps * (wq + TILE_N * 4) : 0) + 1024 + 1024;
     auto kern = gemm_ws_kernel<BT, WMODE, F16>;
@@ -853,8 +898,46 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
         set_error("ovb_gemm: internal error, %d bytes of shared memory requested", smem);
         return ERR_TOO_LARGE;
     }
+    // the splits of a tile are one thread-block cluster (reduction through distributed shared memory)
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 1;
+    attr.val.clusterDim.y = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    // CTAs resident at a time for every cluster size, asked of the driver once per kernel variant
+    static int resident[kMaxSplits + 1] = {-1};
+    if (resident[0] < 0) {
+        resident[1] = (two_ctas(BT, WMODE) ? 2 : 1) * kNumSMs;
+        for (int sz = 2; sz <= kMaxSplits; ++sz) {
+            int n = 0;
+            cfg.gridDim = dim3(sz * 64, 1, sz);
+            attr.val.clusterDim.z = sz;
+            resident[sz] = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess ? n * sz : 0;
+        }
+        (void)cudaGetLastError();
+        resident[0] = 0;
+    }
+    if (p.splits == 0) p.splits = pick_splits(a->T, a->N, a->K, BT, WMODE, resident);
+    TR(static int said = 0; if (!said++) { printf("gemm<%d,%d>: resident CTAs by cluster size:", BT, WMODE);
+       for (int sz = 1; sz <= kMaxSplits; ++sz) printf(" %d", resident[sz]); printf(" | T=%d N=%d K=%d -> splits %d\n", a->T, a->N, a->K, p.splits); })
+    const int total_kb = ceil_div(a->K, TILE_K);
+    if (p.splits > total_kb) p.splits = total_kb;
+    if (p.splits > kMaxSplits) p.splits = kMaxSplits;
+    p.kblocks_per_split = ceil_div(total_kb, p.splits);
     dim3 grid(ceil_div(a->N, TILE_N) * ceil_div(a->T, BT), 1, p.splits);
-    kern<<<grid, GEMM_THREADS, smem, stream>>>(tmW, tmX, p);
+    if (p.splits > 1) {
+        cfg.gridDim = grid;
+        attr.val.clusterDim.z = p.splits;
+        OVB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
+    } else {
+        kern<<<grid, GEMM_THREADS, smem, stream>>>(tmW, tmX, p);
+    }
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -877,15 +960,19 @@ static int dispatch_bt(int bt, const ovb_gemm_args* a, const CUtensorMap& tmW, c
 
 extern "C" {
 
+#ifdef OVB_GEMM_TRACE
+int ovb_gemm_trace_read(long long* host, int n_ctas) {
+    return (int)cudaMemcpyFromSymbol(host, ovb::g_cta_trace, sizeof(long long) * 4 * n_ctas);
+}
+int ovb_gemm_trace_iters(long long* host) { return (int)cudaMemcpyFromSymbol(host, ovb::g_it_trace, sizeof(long long) * 64 * 8); }
+#endif
+
 int ovb_gemm_num_counters(void) { return ovb::kNumCounters; }
 
 int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act) {
-    (void)act;
-    const int bt = ovb::pick_block_t(T);
-    const int splits = ovb::pick_splits(T, N, K, bt, OVB_W_U4);
-    if (splits == 1) return 0;
-    const int64_t tiles = (int64_t)ovb::ceil_div(N, ovb::TILE_N) * ovb::ceil_div(T, bt);
-    return tiles * splits * ovb::TILE_N * bt * (int64_t)sizeof(float);
+    // split-K partials stay in shared memory (cluster reduction): no global workspace is needed any more
+    (void)T; (void)N; (void)K; (void)act;
+    return 0;
 }
 
 int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
@@ -895,7 +982,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     OVB_REQUIRE(a->T > 0 && a->N > 0 && a->K > 0, "ovb_gemm: empty problem T=%d N=%d K=%d", a->T, a->N, a->K);
     OVB_REQUIRE(a->K % 8 == 0 && a->ldx % 8 == 0, "ovb_gemm: K and ldx must be multiples of 8 (TMA 16-byte rule)");
     const bool f16 = a->wmode == OVB_W_F16;
-    const bool quant = a->wmode == OVB_W_U4 || a->wmode == OVB_W_U8;
+    const bool quant = is_quant(a->wmode);
     if (quant) {
         OVB_REQUIRE(a->scales, "ovb_gemm: quantised weights need the (scale, zero point) table");
         OVB_REQUIRE(a->group_size >= 64 && a->group_size % 64 == 0 && a->K % a->group_size == 0,
@@ -907,14 +994,8 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     OVB_REQUIRE(a->act != OVB_ACT_SWIGLU, "ovb_gemm: SWIGLU epilogue is provided by ovb_silu_mul");
 
     const int bt = a->block_t ? a->block_t : pick_block_t(a->T);
-    int splits = a->splits ? a->splits : pick_splits(a->T, a->N, a->K, bt, a->wmode);
-    const int total_kb = ceil_div(a->K, TILE_K);
-    if (splits > total_kb) splits = total_kb;
+    const int splits = a->splits;   // 0: chosen at launch, where the kernel variant and its cluster occupancy are known
     const int64_t tiles = (int64_t)ceil_div(a->N, TILE_N) * ceil_div(a->T, bt);
-    if (splits > 1) {
-        const int64_t need = tiles * splits * TILE_N * bt * (int64_t)sizeof(float);
-        if (!a->ws || !a->counters || a->ws_bytes < need || tiles > kNumCounters) splits = 1;
-    }
 
     GemmKParams p;
     memset(&p, 0, sizeof(p));
@@ -932,7 +1013,6 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.act = a->act;
     p.out_f32 = a->out_f32;
     p.splits = splits;
-    p.kblocks_per_split = ceil_div(total_kb, splits);
     if (a->comm != nullptr && static_cast<const ovb_comm*>(a->comm)->world > 1) {
         const ovb_comm* c = static_cast<const ovb_comm*>(a->comm);
         OVB_REQUIRE(c->world <= 8 && c->rank >= 0 && c->rank < c->world, "ovb_gemm: bad communicator (rank %d of %d)", c->rank, c->world);
@@ -977,7 +1057,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         OVB_REQUIRE((reinterpret_cast<uintptr_t>(a->w) & 15) == 0, "ovb_gemm: packed weights must be 16-byte aligned");
         p.w_tiled = reinterpret_cast<const uint8_t*>(a->w);
         tmW = tmX;   // unused by the kernel in this mode
-    } else if (a->wmode == OVB_W_U8) {
+    } else if (a->wmode == OVB_W_U8 || a->wmode == OVB_W_F8) {
         rc = make_tmap_2d(&tmW, a->w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->N, a->K, (uint64_t)a->K, TILE_N, 64, false);
     } else {
         rc = make_tmap_2d(&tmW, a->w, dt16, 2, a->N, a->K, (uint64_t)a->K * 2, TILE_N, TILE_K, true);
@@ -989,6 +1069,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         case OVB_W_F16: return dispatch_bt<OVB_W_BF16, true>(bt, a, tmW, tmX, p, stream);
         case OVB_W_U4: return dispatch_bt<OVB_W_U4, false>(bt, a, tmW, tmX, p, stream);
         case OVB_W_U8: return dispatch_bt<OVB_W_U8, false>(bt, a, tmW, tmX, p, stream);
+        case OVB_W_F8: return dispatch_bt<OVB_W_F8, false>(bt, a, tmW, tmX, p, stream);
     }
     set_error("ovb_gemm: unknown wmode %d", a->wmode);
     return ERR_BAD_ARG;

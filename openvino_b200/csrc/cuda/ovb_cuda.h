@@ -29,6 +29,7 @@ enum {
     OVB_W_U4 = 1,     // W is packed u4 in the plugin layout made by ovb_pack_u4 (4608-byte chunks, see below)
     OVB_W_U8 = 2,     // W is u8 [N, K]
     OVB_W_F16 = 3,    // W and X are fp16 (BERT path)
+    OVB_W_F8 = 4,     // W is fp8 e4m3 [N, K]; the (scale, -) pair table carries the block scale of every (k-group, row) times 2^120
 };
 enum {
     OVB_ACT_NONE = 0,

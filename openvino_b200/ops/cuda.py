@@ -18,7 +18,7 @@ import torch
 _PKG = Path(__file__).resolve().parent.parent
 _LIB_PATH = _PKG / "lib" / "libovb_cuda.so"
 
-W_BF16, W_U4, W_U8, W_F16 = 0, 1, 2, 3
+W_BF16, W_U4, W_U8, W_F16, W_F8 = 0, 1, 2, 3, 4
 ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_SWIGLU, ACT_GELU_TANH = 0, 1, 2, 3, 4, 5
 
 STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument seen on device",
@@ -191,6 +191,22 @@ class PackedWeight:
         sz = torch.stack([s, z], dim=-1).contiguous()      # [G, N, 2] pairs
         sz = torch.cat([sz.reshape(-1), torch.zeros(256, dtype=sz.dtype, device=sz.device)])   # slack for 128-row copies
         return PackedWeight(W_U8, w_ir.contiguous(), N, K, sz, None, group_size, bias)
+
+    @staticmethod
+    def from_f8_block(w8: torch.Tensor, block_scales: torch.Tensor, N: int, K: int, block: int = 128, bias=None) -> "PackedWeight":
+        """fp8 e4m3 weight [N, K] (uint8 or float8 storage) with one fp32 scale per ``block`` x ``block`` tile
+        (``block_scales`` [ceil(N/block), K/block]): dequantised weight = fp8 value * scale of its tile.
+        The kernel reads the scales as a (k-group, row) table of bf16 values that already carry the 2^120 exponent
+        shift of its byte-to-bf16 conversion."""
+        assert block == 128 and K % block == 0
+        w8 = w8.view(torch.uint8).reshape(N, K).contiguous()
+        G = K // block
+        s = block_scales.float().reshape(-1, G)                                     # [N/128, G]
+        per_row = s.repeat_interleave(block, dim=0)[:N]                             # [N, G]
+        scaled = (per_row.t().contiguous() * float(2.0 ** 120)).to(torch.bfloat16)  # [G, N]
+        sz = torch.stack([scaled, torch.zeros_like(scaled)], dim=-1).contiguous()
+        sz = torch.cat([sz.reshape(-1), torch.zeros(256, dtype=sz.dtype, device=sz.device)])   # slack for 128-row copies
+        return PackedWeight(W_F8, w8, N, K, sz, None, block, bias)
 
 
 # ------------------------------------------------------------------------------------------ ops

@@ -53,6 +53,9 @@ class LlmWeights:
         if cfg.weight_format == "int8":
             q, s, z = quant.quantize_u8_asym(w, cfg.group_size)
             return K.PackedWeight.from_ir_u8(q, s, z, N, Kd, cfg.group_size)
+        if cfg.weight_format == "fp8" and Kd % 128 == 0:
+            q, s = quant.quantize_f8_block(w, 128)
+            return K.PackedWeight.from_f8_block(q, s, N, Kd, 128)
         return K.PackedWeight.from_dense(w.to(torch.bfloat16))
 
     @staticmethod
@@ -62,6 +65,13 @@ class LlmWeights:
             return K.PackedWeight.from_ir_u4(packed, s, quant.pack_u4(z), N, Kd, cfg.group_size)
         g = torch.Generator(device=device)
         g.manual_seed(seed)
+        if cfg.weight_format == "fp8" and Kd % 128 == 0:
+            # random e4m3 bytes (NaN encodings excluded) with one scale per 128 x 128 tile, values of a few hundredths
+            b = torch.randint(0, 256, (N, Kd), device=device, generator=g, dtype=torch.int32)
+            mag = torch.clamp(b & 0x7F, max=0x5E)                    # |value| <= 28
+            w8 = ((b & 0x80) | mag).to(torch.uint8)
+            scales = torch.full(((N + 127) // 128, Kd // 128), 2.0 ** -9, dtype=torch.float32, device=device)
+            return K.PackedWeight.from_f8_block(w8, scales, N, Kd, 128)
         w = (torch.randn((N, Kd), device=device, generator=g, dtype=torch.float32) * 0.02)
         if cfg.weight_format == "int8":
             q, s, z = quant.quantize_u8_asym(w, cfg.group_size)

@@ -71,3 +71,27 @@ def random_u4_weight(N: int, K: int, group_size: int, device, seed: int = 0, std
     # uniform 0..15 has std ~4.6
     scale = (torch.rand((N, G), device=device, generator=g) * 0.5 + 0.75) * (std / 4.6)
     return packed, scale.to(torch.float16), zp
+
+
+def quantize_f8_block(w: torch.Tensor, block: int = 128):
+    """Float [N, K] -> (fp8 e4m3 values [N, K] as uint8, fp32 scales [ceil(N/block), K/block]); every block x block tile
+    is scaled so that its largest magnitude maps to 448 (the e4m3 maximum). Scales are rounded to bf16 precision so that
+    kernels which apply them in bf16 reproduce them exactly."""
+    N, K = w.shape
+    assert K % block == 0
+    nb = (N + block - 1) // block
+    pad = nb * block - N
+    wf = torch.nn.functional.pad(w.float(), (0, 0, 0, pad)) if pad else w.float()
+    tiles = wf.reshape(nb, block, K // block, block)
+    amax = tiles.abs().amax(dim=(1, 3)).clamp_min(1e-12)                 # [nb, K/block]
+    scale = (amax / 448.0).to(torch.bfloat16).float()
+    q = (tiles / scale[:, None, :, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    q = q.reshape(nb * block, K)[:N].contiguous()
+    return q.view(torch.uint8), scale
+
+
+def dequantize_f8_block(q: torch.Tensor, scale: torch.Tensor, block: int = 128) -> torch.Tensor:
+    N, K = q.shape
+    w = q.view(torch.float8_e4m3fn).float()
+    s = scale.repeat_interleave(block, dim=0)[:N].repeat_interleave(block, dim=1)
+    return w * s

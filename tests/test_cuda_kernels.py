@@ -74,6 +74,23 @@ def test_gemm_u8(ops):
     assert _rel_err(y, x.float() @ wdq.t()) < 1.5e-2
 
 
+@pytest.mark.parametrize("T,N,K", [(48, 256, 1024), (300, 384, 512), (7, 1000, 256)])
+def test_gemm_f8_block_scaled(ops, T, N, K):
+    """fp8 e4m3 weights with one fp32 scale per 128 x 128 tile (weight-only: activations stay bf16)."""
+    from openvino_b200.utils import quant
+    torch.manual_seed(4)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    w[0, :16] = 1e-5          # lands in the fp8 sub-normal range of its tile
+    q, s = quant.quantize_f8_block(w, 128)
+    wdq = quant.dequantize_f8_block(q, s, 128)
+    assert _rel_err(wdq, w) < 5e-2
+    pw = ops.PackedWeight.from_f8_block(q, s, N, K, 128)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    y = ops.gemm(x, pw)
+    ops.check_status("gemm_f8")
+    assert _rel_err(y, x.float() @ wdq.t()) < 1e-2
+
+
 @pytest.mark.parametrize("rows,cols", [(3, 128), (64, 4096), (17, 8192), (5, 14336)])
 def test_rmsnorm(ops, rows, cols):
     torch.manual_seed(3)
