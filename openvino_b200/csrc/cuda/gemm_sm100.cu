@@ -33,10 +33,12 @@ namespace ovb {
 
 constexpr int TILE_N = 128;      // weight rows per CTA (MMA M)
 constexpr int TILE_K = 64;       // bf16 elements per k-block = one 128-byte swizzle span
-constexpr int NUM_DQ_WARPS = 8;  // dequant + epilogue warps
-constexpr int DQ_THREADS = NUM_DQ_WARPS * 32;
-constexpr int GEMM_THREADS = (3 + NUM_DQ_WARPS) * 32;   // producer, MMA issuer, 8 dequant/epilogue warps, token-tile producer (quantised modes)
-constexpr int X_PRODUCER_WARP = 2 + NUM_DQ_WARPS;
+// Warp roles: warp 0 weight producer, warp 1 MMA issuer, warps 2 .. 2+NDQ-1 dequantisation and epilogue, the last warp
+// token-tile producer (quantised modes). The kernel is written for NDQ = 8 or 16; measurements on B200 favour 8 with two
+// CTAs per SM for decode-sized quantised problems: the MMA-issuing warp, not the expansion arithmetic, is what limits
+// a CTA there (its instructions issue several times slower while the dequant warps run), and two CTAs bring two issuers.
+constexpr int num_dq_warps(int bt, int wmode) { (void)bt; (void)wmode; return 8; }
+constexpr int gemm_threads(int bt, int wmode) { return (3 + num_dq_warps(bt, wmode)) * 32; }
 constexpr int MAX_STAGES = 8;    // MMA stages
 constexpr int MAX_PSLOTS = 16;   // packed-weight ring slots
 constexpr int kBandN = 16;       // weight tiles per rasterisation band
@@ -165,12 +167,13 @@ __device__ __forceinline__ void dequant_f8x4(uint32_t w, __nv_bfloat162 ss, uint
 // the data, which halves the per-byte cost of the control chain.
 constexpr int kblocks_per_stage(int bt, int wmode) { return is_quant(wmode) && bt < 256 ? 2 : 1; }
 
-// Decode-sized quantised problems run two CTAs per SM: one CTA's control chain (barrier round trips between the
-// producer, the dequant warps and the MMA issuer) is latency bound, a second resident CTA fills the gaps.
-constexpr bool two_ctas(int bt, int wmode) { return bt <= 64 && is_quant(wmode); }
+// Decode-sized quantised problems run two CTAs per SM (half the shared memory and 256 TMEM columns each): one CTA's
+// control chain (barrier round trips between the producers, the dequant warps and the MMA issuer) is latency bound, a
+// second resident CTA fills the gaps.
+constexpr bool two_ctas(int bt, int wmode) { return bt <= 64 && is_quant(wmode) && num_dq_warps(bt, wmode) == 8; }
 
 template <int BT, int WMODE, bool F16>
-__global__ void __launch_bounds__(GEMM_THREADS, two_ctas(BT, WMODE) ? 2 : 1)
+__global__ void __launch_bounds__(gemm_threads(BT, WMODE), two_ctas(BT, WMODE) ? 2 : 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmKParams p) {
     using E = typename Elem<F16>::type;
     constexpr bool QUANT = is_quant(WMODE);
@@ -187,8 +190,16 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     constexpr int STAGE_BYTES = QUANT ? KPS * X_BYTES : X_BYTES + W_BYTES;
     constexpr int ACC_COLS = BT < 32 ? 32 : BT;
     constexpr int A_COLS = KPS * 32;                             // 128 rows x 64 bf16 = 32 columns of 32 bits per k-block
-    // accumulator + stages of A: 4 stages (256 columns, two CTAs per SM) for small tiles, up to 8 stages otherwise
-    constexpr int TMEM_COLS = !QUANT ? ACC_COLS : (two_ctas(BT, WMODE) ? 256 : 512);
+    constexpr int TMEM_COLS = !QUANT ? ACC_COLS : (two_ctas(BT, WMODE) ? 256 : 512);   // accumulator + the stages of A
+    constexpr int NDQ = num_dq_warps(BT, WMODE);
+    constexpr int DQ_THREADS = NDQ * 32;
+    constexpr int X_PRODUCER_WARP = 2 + NDQ;
+    // A group of four dequant warps (one per TMEM lane quarter) expands one k-block. A stage of KPS k-blocks is served by
+    // KPS groups; with more groups than that the sets of groups take alternate iterations, so that one set expands stage
+    // i + 1 while the MMAs of stage i still wait for the other.
+    constexpr int GPS = KPS;
+    constexpr int SETS = (NDQ / 4) / GPS;
+    static_assert(SETS >= 1 && SETS * GPS * 4 == NDQ, "dequant warps must form whole sets of groups");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -235,12 +246,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
-            mbar_init(&full_x[s], QUANT ? 1 + NUM_DQ_WARPS : 1);   // producer's expect_tx arrival (+ one arrival per dequant warp)
+            mbar_init(&full_x[s], QUANT ? 1 + 4 * GPS : 1);   // producer's expect_tx arrival (+ one arrival per dequant warp of the stage)
             mbar_init(&empty[s], 1);
         }
         for (int s = 0; s < pslots; ++s) {
             mbar_init(&p_full[s], 1);
-            mbar_init(&p_empty[s], NUM_DQ_WARPS);
+            mbar_init(&p_empty[s], 4 * GPS);
         }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
@@ -402,18 +413,19 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // ------------------------------------------------------------ dequant warps, then epilogue
         const int dq_tid = threadIdx.x - 64;  // 0..255
         if (QUANT) {
-            // Two groups of four warps: group g expands k-block g of every stage. Inside a group a warp owns the 32 rows of
-            // its TMEM lane quarter; a thread expands the 64 values of one row and writes them to tensor memory as 32
-            // columns of bf16 pairs (two tcgen05.st).
+            // Group g belongs to set g / GPS and expands k-block g % GPS of the stages that its set serves. Inside a group a
+            // warp owns the 32 rows of its TMEM lane quarter; a thread expands the 64 values of one row and writes them to
+            // tensor memory as 32 columns of bf16 pairs (two tcgen05.st).
             const int grp = (warp - 2) >> 2;
+            const int set = grp / GPS, kin = grp % GPS;
             const int qd = warp & 3;                    // TMEM lane quarter this warp may access
             const int row = qd * 32 + lane;
             const bool row_ok = (n0 + row) < p.N;
-            int slot = 0, st = 0;
+            int slot = set, st = set;                   // ring lengths are multiples of SETS (host side): an entry has one owner set
             uint32_t ppar = 0, phase = 0;
-            const uint32_t a_lane = tmem_base + (uint32_t(qd * 32) << 16) + uint32_t(ACC_COLS + (KPS == 2 ? grp * 32 : 0));
+            const uint32_t a_lane = tmem_base + (uint32_t(qd * 32) << 16) + uint32_t(ACC_COLS + kin * 32);
             TR(long long tr_t0 = clock64(), tr_wp = 0, tr_we = 0, tr_wk = 0;)
-            for (int i = 0; i < num_it; ++i) {
+            for (int i = set; i < num_it; i += SETS) {
                 // every lane polls (same word, same answer): no divergence and no shuffle on the way to the work
                 TR(const long long tr_a = clock64(); long long tr_b = tr_a;)
                 bool ok = mbar_wait(&p_full[slot], ppar, abort_flag, p.status);
@@ -421,9 +433,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 ok = ok && mbar_wait(&empty[st], phase ^ 1, abort_flag, p.status);
                 TR(const long long tr_c = clock64(); tr_wp += tr_b - tr_a; tr_we += tr_c - tr_b; if (warp == 2 && lane == 0) { TRI(i, 4) })
                 if (!ok) break;
-                // KPS == 2: group g expands k-block g of the stage; KPS == 1: the groups take alternate stages
-                const uint32_t slot_a = smem_u32(pring + slot * RING_SLOT + (KPS == 2 ? grp * WQ_SLOT : 0));
-                if (KPS == 2 ? (i * KPS + grp < num_kb) : ((i & 1) == grp)) {
+                const uint32_t slot_a = smem_u32(pring + slot * RING_SLOT + kin * WQ_SLOT);
+                if (i * KPS + kin < num_kb) {
                 uint32_t cur;
                 asm volatile("ld.shared.u32 %0, [%1];" : "=r"(cur) : "r"(slot_a + WQ_BYTES + row * 4));
                 if (!row_ok) cur = 0u;          // rows past N: scale 0
@@ -480,8 +491,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     mbar_arrive(&full_x[st]);
                     mbar_arrive(&p_empty[slot]);
                 }
-                if (++st == stages) { st = 0; phase ^= 1; }
-                if (++slot == pslots) { slot = 0; ppar ^= 1; }
+                st += SETS;
+                if (st >= stages) { st -= stages; phase ^= 1; }
+                slot += SETS;
+                if (slot >= pslots) { slot -= pslots; ppar ^= 1; }
                 TR(tr_wk += clock64() - tr_c;)
             }
             TR(if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
@@ -490,13 +503,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
         // -------- epilogue: warp (w % 4) owns TMEM lanes 32*(w%4) .. +31; two warps share a quarter
         const int q = warp & 3;
-        const int colhalf = (warp - 2) >> 2;  // 0 or 1
+        const int colpart = (warp - 2) >> 2;  // which slice of the token columns this warp drains
         const int row = q * 32 + lane;
         const int oc = n0 + row;
-        constexpr int COLS_PER_WARP = BT / 2;            // BT >= 32 -> multiple of 16
-        constexpr int CHUNKS = (COLS_PER_WARP + 15) / 16;
-        const int cbeg = (BT >= 32) ? colhalf * COLS_PER_WARP : 0;
-        const bool active_warp = (BT >= 32) || (colhalf == 0);
+        constexpr int PARTS = (NDQ / 4) < (BT / 16) ? (NDQ / 4) : (BT / 16);   // column slices, 16 columns at least
+        constexpr int COLS_PER_WARP = BT / PARTS;
+        constexpr int CHUNKS = COLS_PER_WARP / 16;
+        const int cbeg = colpart * COLS_PER_WARP;
+        const bool active_warp = colpart < PARTS;
         // one thread polls the accumulator barrier; the other 255 park at a hardware named barrier
         if (dq_tid == 0 && num_kb > 0) mbar_wait(acc_full, 0, abort_flag, p.status);
         asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
@@ -834,7 +848,7 @@ static int pick_splits(int T, int N, int K, int bt, int wmode, const int* reside
         if (resident[s] <= 0) continue;
         const int ctas = tiles * s;
         const int waves = ceil_div(ctas, resident[s]);
-        const bool shared_sm = two_ctas(bt, wmode) && ctas > kNumSMs;      // two CTAs on an SM slow each other down
+        const bool shared_sm = two_ctas(bt, wmode) && s == 1 && ctas > kNumSMs;   // two CTAs on an SM slow each other down
         double t = waves * (ceil_div(total_kb, s) * t_kb * (shared_sm ? 1.25 : 1.0) + t_cta);
         if (s > 1) t += 2.5;                                               // cluster barriers + the slice reduction
         if (t < best_t - 0.25) { best_t = t; best = s; }
@@ -858,19 +872,24 @@ static void pick_rings(int bt, int wmode, int* stages, int* pslots) {
     const int kps = kblocks_per_stage(bt, wmode);
     const int xstage = kps * bt * 128;
     const int slot = kps * (wq + TILE_N * 4);  // packed chunks + (scale, zero point) pairs
-    int s, budget;
+    // Large token tiles come from L2 with a latency of a microsecond or two under load: the token ring has to cover it
+    // (a 256-token stage is consumed in ~0.3 us); decode-sized tiles take seven stages so that the dequant sets run well
+    // ahead of the MMAs. The packed-weight ring keeps what is left. The accumulator and s x 32 (64 for two-k-block
+    // stages) columns of A fit the 512 TMEM columns.
+    // Both rings are walked by `sets` sets of dequant groups that take alternate iterations: their lengths are multiples
+    // of `sets`, so that a ring entry always belongs to the same set (a waiter on an mbarrier phase parity must never be
+    // two phases ahead of the barrier, which a set that sees only every other use of an entry could be).
+    const int sets = (num_dq_warps(bt, wmode) / 4) / kps;
+    int s = bt >= 256 ? 6 : (bt >= 128 ? 5 : 6);
+    int budget = kSmemBudget;
     if (two_ctas(bt, wmode)) {               // two CTAs share the SM: half the shared memory, 256 TMEM columns each
         s = 3;                               // accumulator (<= 64 columns) + 3 x 64 columns of A
         budget = (kSmemLimit - 2 * 1024) / 2 - 2560;
-    } else {
-        // Large token tiles come from L2 with a latency of a microsecond or two under load: the token ring has to cover
-        // it (a 256-token stage is consumed in ~0.3 us), the packed-weight ring keeps what is left. The accumulator and
-        // s x 32 (64 for two-k-block stages) columns of A fit the 512 TMEM columns.
-        s = bt >= 256 ? 6 : (bt >= 128 ? 5 : 4);
-        budget = kSmemBudget;
     }
+    s -= s % sets;
     int pmax = (budget - s * xstage) / slot;
     if (pmax > MAX_PSLOTS) pmax = MAX_PSLOTS;
+    pmax -= pmax % sets;
     *stages = s;
     *pslots = pmax;
 }
@@ -901,7 +920,7 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     // the splits of a tile are one thread-block cluster (reduction through distributed shared memory)
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.blockDim = dim3(gemm_threads(BT, WMODE), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr;
@@ -936,7 +955,7 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
         attr.val.clusterDim.z = p.splits;
         OVB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
     } else {
-        kern<<<grid, GEMM_THREADS, smem, stream>>>(tmW, tmX, p);
+        kern<<<grid, gemm_threads(BT, WMODE), smem, stream>>>(tmW, tmX, p);
     }
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
