@@ -60,10 +60,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. `abort_flag` lives in shared memory: once any role gives up, every later
 // wait in the CTA returns at once so that all warps reach the tear-down barrier.
 // The fast path is a single try_wait: control lanes are latency bound, every extra instruction counts.
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or the hint (nanoseconds)
+// runs out, instead of coming back after the default short time slice. A waiting warp then costs next to no issue slots,
+// which the dequantisation warps of the same scheduler need.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+constexpr uint32_t kMbarSuspendNs = 20000;            // per try_wait
+constexpr long long kMbarTimeoutNs = 2000000000ll;    // give up after two seconds
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
     for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if (mbar_try_wait_hint(bar, parity, kMbarSuspendNs)) return true;
+        if (*abort_flag) return false;
+        if ((i & 15u) == 15u) {
+            long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            if (t - t0 > kMbarTimeoutNs) break;
+        }
     }
     *abort_flag = 1;
     report_status(status, STATUS_MBAR_TIMEOUT);
