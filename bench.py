@@ -112,7 +112,7 @@ def reference_arm(args):
     return 0
 
 
-SERVING_DEFAULTS = {"mixtral-8x7b": (128, 512, 128), "tiny-moe": (16, 128, 32), "tiny-llama": (16, 128, 32)}   # requests, prompt, output
+SERVING_DEFAULTS = {"mixtral-8x7b": (128, 512, 128), "llama-3-70b": (32, 2048, 512), "tiny-moe": (16, 128, 32), "tiny-llama": (16, 128, 32)}   # requests, prompt, output
 
 
 def graph_api_bench(args):

@@ -868,9 +868,22 @@ class Core:
             mod, _, attr = plugin.partition(":")
             import importlib
             plugin = getattr(importlib.import_module(mod), attr or "Plugin")
+        config = dict(config or {})
+        alias = config.pop("PROXY_CONFIGURATION_ALIAS", None)
+        fallback = config.pop("PROXY_CONFIGURATION_FALLBACK", None)
+        config.pop("PROXY_CONFIGURATION_PRIORITY", None)
         self._factories[device_name] = plugin
+        if alias:
+            # the plugin stays reachable under its own name; `alias` becomes (or extends) a proxy device in front of it
+            from .policy_plugins import register_proxy
+            register_proxy(self, alias, [device_name] + ([fallback] if fallback else []))
         if config:
             self._get_plugin(device_name).set_property(props.normalize(config))
+
+    def register_proxy(self, alias: str, devices) -> None:
+        """Expose the plugins ``devices`` (fallback order) under the single device name ``alias``."""
+        from .policy_plugins import register_proxy
+        register_proxy(self, alias, list(devices))
 
     def unload_plugin(self, device_name: str) -> None:
         name = _DEVICE_ALIASES.get(device_name, device_name)

@@ -500,6 +500,113 @@ class BatchPlugin(Plugin):
         return self.core.query_model(model, dev, {})
 
 
+class ProxyPlugin(Plugin):
+    """One device name in front of several plugins, with a fallback order.
+
+    The proxy numbers the devices of its plugins consecutively ("GPU.0", "GPU.1" may belong to different plugins),
+    forwards every call to the plugin that owns the addressed device and, when that plugin cannot compile the model,
+    tries the remaining plugins in order. Role of src/plugins/proxy/src/plugin.cpp (alias / fallback / priority
+    configuration of src/plugins/proxy/dev_api/openvino/proxy/properties.hpp).
+    """
+
+    description = "proxy"
+
+    def __init__(self, core, alias: str, order: List[str]):
+        super().__init__(core)
+        self.device_name = alias
+        self.order = list(order)
+
+    def add_fallback(self, device: str, priority: Optional[int] = None) -> None:
+        if device not in self.order:
+            self.order.insert(len(self.order) if priority is None else max(0, min(priority, len(self.order))), device)
+
+    def _devices(self) -> List[tuple]:
+        out = []
+        for name in self.order:
+            try:
+                ids = self.core._get_plugin(name).available_device_ids()
+            except Exception:
+                continue
+            out += [(name, i) for i in ids]
+        return out
+
+    def available_device_ids(self) -> List[str]:
+        return [str(i) for i in range(len(self._devices()))]
+
+    def _target(self, config: dict) -> List[tuple]:
+        """(plugin, device id) candidates: the addressed device first, then one device of every later plugin."""
+        devs = self._devices()
+        if not devs:
+            raise RuntimeError("[%s] none of the devices behind the proxy is available: %s" % (self.device_name, self.order))
+        idx = int(str(config.get(props.device.id, self.config.get(props.device.id, "")) or 0))
+        if idx >= len(devs):
+            raise RuntimeError("[%s] no device with id %d (have %d)" % (self.device_name, idx, len(devs)))
+        first = devs[idx]
+        rest = []
+        for name in self.order[self.order.index(first[0]) + 1:]:
+            cand = [d for d in devs if d[0] == name]
+            if cand:
+                rest.append(cand[0])
+        return [first] + rest
+
+    def supported_properties(self) -> List[str]:
+        return super().supported_properties() + ["PROXY_FALLBACK_ORDER"]
+
+    def get_property(self, name: str, arguments: Optional[dict] = None):
+        if name == "PROXY_FALLBACK_ORDER":
+            return list(self.order)
+        if name in (props.supported_properties, props.available_devices):
+            return super().get_property(name, arguments)
+        plugin, dev_id = self._target(dict(arguments or {}))[0]
+        args = dict(arguments or {})
+        args[props.device.id] = dev_id
+        return self.core._get_plugin(plugin).get_property(name, args)
+
+    def set_property(self, config: dict) -> None:
+        for k, v in config.items():
+            if k == props.device.id:
+                self.config[k] = v
+                continue
+            for name in self.order:
+                try:
+                    self.core._get_plugin(name).set_property({k: v})
+                except RuntimeError:
+                    pass
+
+    def compile_model(self, model: Model, config: dict):
+        errors = []
+        cfg = {k: v for k, v in config.items() if k != props.device.id}
+        for plugin, dev_id in self._target(config):
+            try:
+                sub = dict(cfg)
+                if dev_id not in ("", None):
+                    sub[props.device.id] = dev_id
+                return self.core._get_plugin(plugin).compile_model(model, sub)
+            except Exception as e:          # the next plugin in the fallback order gets its chance
+                errors.append("%s: %s" % (plugin, e))
+        raise RuntimeError("[%s] no plugin behind the proxy could compile the model: %s" % (self.device_name, "; ".join(errors)))
+
+    def query_model(self, model, config):
+        plugin, _ = self._target(config)[0]
+        return {k: self.device_name for k in self.core._get_plugin(plugin).query_model(model, {}).keys()}
+
+    def import_model(self, blob, config):
+        plugin, _ = self._target(config)[0]
+        return self.core._get_plugin(plugin).import_model(blob, config)
+
+
+def register_proxy(core, alias: str, devices: List[str]) -> ProxyPlugin:
+    """Put ``devices`` (plugin names, highest priority first) behind the device name ``alias``."""
+    existing = core._plugins.get(alias)
+    if isinstance(existing, ProxyPlugin):
+        for d in devices:
+            existing.add_fallback(d)
+        return existing
+    core._factories[alias] = lambda c, a=alias, d=list(devices): ProxyPlugin(c, a, d)
+    core._plugins.pop(alias, None)
+    return core._get_plugin(alias)
+
+
 def register(core) -> None:
     core.register_plugin_factory("AUTO", AutoPlugin)
     core.register_plugin_factory("MULTI", MultiPlugin)

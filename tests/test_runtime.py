@@ -336,6 +336,39 @@ def test_auto_falls_back_when_a_device_fails(core):
     assert cm.get_property(props.execution_devices) == ["FLAKY", "CPU"]
 
 
+def test_proxy_device_aliases_plugins_with_fallback(core):
+    class Broken(Plugin):
+        device_name = "LOWLEVEL_A"
+
+        def compile_model(self, model, config):
+            raise RuntimeError("driver too old")
+
+        def query_model(self, model, config):
+            return {}
+
+    class TwoDevices(CpuPlugin):
+        device_name = "LOWLEVEL_B"
+
+        def available_device_ids(self):
+            return ["0", "1"]
+
+    # two low-level plugins behind one name; the second is the fallback of the first
+    core.register_plugin(Broken, "LOWLEVEL_A", {"PROXY_CONFIGURATION_ALIAS": "ACCEL"})
+    core.register_plugin(TwoDevices, "LOWLEVEL_B", {"PROXY_CONFIGURATION_ALIAS": "ACCEL"})
+    assert core.get_property("ACCEL", "PROXY_FALLBACK_ORDER") == ["LOWLEVEL_A", "LOWLEVEL_B"]
+    assert core.get_property("ACCEL", props.available_devices) == ["0", "1", "2"]
+    x = np.ones((1, 16), np.float32)
+    cm = core.compile_model(mlp(), "ACCEL")          # device 0 belongs to the broken plugin: falls back
+    np.testing.assert_allclose(cm(x)[0], ref(x), rtol=1e-5)
+    cm = core.compile_model(mlp(), "ACCEL.2")        # third device = second device of the second plugin
+    np.testing.assert_allclose(cm(x)[0], ref(x), rtol=1e-5)
+    with pytest.raises(RuntimeError, match="no device with id 5"):
+        core.compile_model(mlp(), "ACCEL.5")
+    core.register_proxy("ONLY_BROKEN", ["LOWLEVEL_A"])
+    with pytest.raises(RuntimeError, match="driver too old"):
+        core.compile_model(mlp(), "ONLY_BROKEN")
+
+
 def test_hetero_splits_by_supported_ops(core):
     class NoRelu(CpuPlugin):
         device_name = "NORELU"
