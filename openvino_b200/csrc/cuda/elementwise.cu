@@ -416,6 +416,37 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
     }
 }
 
+// ------------------------------------------------------------------------------------ im2col (convolution as GEMM)
+// cols[t][k] for t = (b, ho, wo) and k = (c * kh + r) * kw + s is x[b][c][ho*sh - pt + r*dh][wo*sw - pl + s*dw] (zero outside
+// the image and for k >= C*kh*kw): the [T, Kpad] operand of out[T, O] = cols x W[O, Kpad]^T on the tcgen05 GEMM. A thread
+// fills one 16-byte piece (8 consecutive k of one output position); the 16-bit payload is copied as it is (bf16 or fp16).
+__global__ void im2col_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ cols, int B, int C, int H, int W, int kh, int kw,
+                              int sh, int sw, int pt, int pl, int dh, int dw, int Ho, int Wo, int Kd, int Kpad) {
+    const int pieces = Kpad >> 3;
+    const size_t total = (size_t)B * Ho * Wo * pieces;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int pc = int(i % pieces);
+        const size_t t = i / pieces;
+        const int wo = int(t % Wo);
+        const int ho = int((t / Wo) % Ho);
+        const int b = int(t / ((size_t)Wo * Ho));
+        uint16_t v[8];
+        int k = pc * 8;
+        int s_ = k % kw, r = (k / kw) % kh, c = k / (kw * kh);
+#pragma unroll
+        for (int j = 0; j < 8; ++j, ++k) {
+            uint16_t val = 0;
+            if (k < Kd) {
+                const int hi = ho * sh - pt + r * dh, wi = wo * sw - pl + s_ * dw;
+                if (hi >= 0 && hi < H && wi >= 0 && wi < W) val = x[(((size_t)b * C + c) * H + hi) * W + wi];
+            }
+            v[j] = val;
+            if (++s_ == kw) { s_ = 0; if (++r == kh) { r = 0; ++c; } }
+        }
+        *reinterpret_cast<uint4*>(cols + t * Kpad + pc * 8) = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
 // ------------------------------------------------------------------------------------ int4 re-pack
 // IR layout: byte b of a row holds element 2b in its low nibble and 2b+1 in its high nibble.
 // Plugin layout: every aligned group of 8 elements e0..e7 becomes one u32 with nibble j (j<4) = e[2j]
@@ -621,6 +652,19 @@ int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void
         rope_kv_write_kernel<<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
                                                     (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
     }
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_im2col(const void* x, void* cols, int B, int C, int H, int W, int kh, int kw, int sh, int sw, int pt, int pl, int dh, int dw,
+               int Ho, int Wo, int Kpad, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(x && cols && B > 0 && C > 0 && Ho > 0 && Wo > 0, "ovb_im2col: null operand or empty problem");
+    OVB_REQUIRE(Kpad % 8 == 0 && Kpad >= C * kh * kw, "ovb_im2col: Kpad must be a multiple of 8 that covers C*kh*kw");
+    OVB_REQUIRE((reinterpret_cast<uintptr_t>(cols) & 15) == 0, "ovb_im2col: output must be 16-byte aligned");
+    const size_t total = (size_t)B * Ho * Wo * (Kpad / 8);
+    im2col_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const uint16_t*)x, (uint16_t*)cols, B, C, H, W, kh, kw, sh, sw, pt, pl, dh, dw,
+                                                            Ho, Wo, C * kh * kw, Kpad);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -91,6 +91,9 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
                   int cols, float eps, int is_f16, ovb_stream_t stream);
 // out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
 int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
+/* Convolution operand for the GEMM: 16-bit NCHW image -> cols [B*Ho*Wo, Kpad], k = (c*kh + r)*kw + s, zero padded. */
+int ovb_im2col(const void* x, void* cols, int B, int C, int H, int W, int kh, int kw, int sh, int sw, int pt, int pl, int dh, int dw,
+               int Ho, int Wo, int Kpad, ovb_stream_t stream);
 // ids are int64 (ids_i32 == 0) or int32; ids outside [0, vocab) read row 0.
 int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, int rows, int cols, int vocab,
                   ovb_stream_t stream);

@@ -272,6 +272,33 @@ def silu_mul(gu, out=None):
     return out
 
 
+def conv2d(x: torch.Tensor, w: "PackedWeight", kernel, strides, pads_begin, pads_end, dilations, act: int = ACT_NONE) -> torch.Tensor:
+    """2-D convolution of a 16-bit NCHW tensor as im2col + tcgen05 GEMM; ``w`` packs the filters as [O, Kpad] with
+    k = (c*kh + r)*kw + s (``pack_conv_weight``). Returns NCHW (a permuted view of the GEMM's [B*Ho*Wo, O] output)."""
+    B, Cin, H, W = x.shape
+    kh, kw = kernel
+    Ho = (H + pads_begin[0] + pads_end[0] - dilations[0] * (kh - 1) - 1) // strides[0] + 1
+    Wo = (W + pads_begin[1] + pads_end[1] - dilations[1] * (kw - 1) - 1) // strides[1] + 1
+    x = x.contiguous()
+    cols = torch.empty((B * Ho * Wo, w.K), dtype=x.dtype, device=x.device)
+    _check(lib().ovb_im2col(C.c_void_p(x.data_ptr()), C.c_void_p(cols.data_ptr()), C.c_int(B), C.c_int(Cin), C.c_int(H), C.c_int(W),
+                            C.c_int(kh), C.c_int(kw), C.c_int(strides[0]), C.c_int(strides[1]), C.c_int(pads_begin[0]), C.c_int(pads_begin[1]),
+                            C.c_int(dilations[0]), C.c_int(dilations[1]), C.c_int(Ho), C.c_int(Wo), C.c_int(w.K), C.c_void_p(_stream())), "ovb_im2col")
+    out = gemm(cols, w, act=act)
+    return out.view(B, Ho, Wo, w.N).permute(0, 3, 1, 2)
+
+
+def pack_conv_weight(w: torch.Tensor, bias=None) -> "PackedWeight":
+    """[O, C, kh, kw] 16-bit filters -> GEMM weight [O, Kpad], Kpad = C*kh*kw rounded up to 64."""
+    O = w.shape[0]
+    flat = w.reshape(O, -1)
+    Kd = flat.shape[1]
+    Kpad = (Kd + 63) // 64 * 64
+    if Kpad != Kd:
+        flat = torch.nn.functional.pad(flat, (0, Kpad - Kd))
+    return PackedWeight.from_dense(flat.contiguous(), bias=bias)
+
+
 def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0, seed: int = 0, step: Optional[torch.Tensor] = None,
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Draw one token per row of bf16 ``logits`` [rows, V]; ``step``: device int32 word mixed into the random stream."""

@@ -587,6 +587,22 @@ def _conv(x, w, at, groups):
 @op("Convolution")
 def _convolution(n, ins, ctx):
     x, w = _same_device(ctx, ins)
+    # 16-bit 2-D convolutions with constant filters run as im2col + the tcgen05 GEMM (filters packed once)
+    if ctx.K is not None and ctx.on_gpu and x.is_cuda and x.dim() == 4 and x.dtype in (torch.float16, torch.bfloat16) and x.shape[0] * x.shape[2] * x.shape[3] > 0:
+        st = ctx.cache.get(id(n))
+        if st is None:
+            st = {"packed": None}
+            src = n.input_value(1).get_node()
+            if src.get_type_name() == "Convert":
+                src = src.input_value(0).get_node()
+            if src.get_type_name() == "Constant":
+                st["packed"] = ctx.K.pack_conv_weight(w.to(x.dtype))
+            ctx.cache[id(n)] = st
+        if st["packed"] is not None:
+            at = n.get_attributes()
+            kernel = list(w.shape[2:])
+            pb, pe = _auto_pad(x, kernel, at["strides"], at["dilations"], at["pads_begin"], at["pads_end"], at["auto_pad"])
+            return [ctx.K.conv2d(x, st["packed"], kernel, at["strides"], pb, pe, at["dilations"])]
     return [_conv(x, w, n.get_attributes(), 1)]
 
 

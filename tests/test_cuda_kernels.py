@@ -91,6 +91,20 @@ def test_gemm_f8_block_scaled(ops, T, N, K):
     assert _rel_err(y, x.float() @ wdq.t()) < 1e-2
 
 
+@pytest.mark.parametrize("B,C,H,W,O,k,stride,pad,dil", [(2, 3, 32, 32, 64, 7, 2, 3, 1), (1, 64, 14, 14, 128, 3, 1, 1, 1),
+                                                        (3, 32, 9, 11, 48, 3, 2, 1, 1), (2, 16, 8, 8, 32, 1, 1, 0, 1), (1, 8, 12, 12, 16, 3, 1, 2, 2)])
+def test_conv2d_im2col_gemm(ops, B, C, H, W, O, k, stride, pad, dil):
+    torch.manual_seed(5)
+    x = torch.randn(B, C, H, W, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(O, C, k, k, device="cuda") * 0.1).to(torch.bfloat16)
+    pw = ops.pack_conv_weight(w)
+    y = ops.conv2d(x, pw, [k, k], [stride, stride], [pad, pad], [pad, pad], [dil, dil])
+    ops.check_status("conv2d")
+    ref = torch.nn.functional.conv2d(x.float(), w.float(), None, stride, pad, dil)
+    assert list(y.shape) == list(ref.shape)
+    assert _rel_err(y, ref) < 1e-2
+
+
 @pytest.mark.parametrize("rows,cols", [(3, 128), (64, 4096), (17, 8192), (5, 14336)])
 def test_rmsnorm(ops, rows, cols):
     torch.manual_seed(3)
