@@ -14,6 +14,7 @@ except ImportError:   # first import of a fresh checkout: compile the native cor
 from ._types import Dimension, PartialShape, Shape, Type, get_element_type   # noqa: F401
 from ._tensor import Tensor   # noqa: F401
 from ._graph import Input, Model, Node, Output, RTMap   # noqa: F401
+from ._op_base import DiscreteTypeInfo, Op, register_op   # noqa: F401
 from . import opset   # noqa: F401
 from . import opset as opset1, opset as opset2, opset as opset3, opset as opset4, opset as opset5, opset as opset6   # noqa: F401,E401
 from . import opset as opset7, opset as opset8, opset as opset9, opset as opset10, opset as opset11, opset as opset12   # noqa: F401,E401

@@ -279,6 +279,49 @@ PYBIND11_MODULE(_ovcore, mod) {
         for (auto kv : attrs) a.emplace_back(py::cast<std::string>(py::str(kv.first)), py_to_attr(kv.second));
         return make_node(type, version, outs_from_py(inputs), a, infer);
     }, py::arg("type"), py::arg("version"), py::arg("inputs"), py::arg("attrs") = py::dict(), py::arg("infer") = true);
+    // Operations defined in Python: `infer(node) -> [(element type name, partial shape), ...]` and, optionally,
+    // `evaluate(node, [(array, type, shape), ...]) -> [(array, type name), ...]`. The callables live for the whole process.
+    mod.def("register_custom_op", [](const std::string& type, const std::string& version, py::object infer, py::object eval, const py::dict& attrs) {
+        auto* infer_p = new py::object(std::move(infer));
+        auto* eval_p = eval.is_none() ? nullptr : new py::object(std::move(eval));
+        OpSchema s;
+        s.type = type;
+        s.version = version;
+        for (auto kv : attrs) {      // name -> default value: gives the IR reader the kind of every attribute
+            AttrSpec a;
+            a.name = py::cast<std::string>(py::str(kv.first));
+            a.def = py_to_attr(kv.second);
+            a.kind = a.def.kind;
+            s.attrs.push_back(a);
+        }
+        s.infer = [infer_p](Node& n) {
+            py::gil_scoped_acquire g;
+            py::list outs = py::cast<py::list>((*infer_p)(n.shared_from_this()));
+            n.set_num_outputs(outs.size());
+            size_t i = 0;
+            for (auto o : outs) {
+                auto t = py::cast<py::tuple>(o);
+                n.set_output(i++, et_from_name(py::cast<std::string>(t[0])), pshape_from_py(t[1]));
+            }
+        };
+        if (eval_p)
+            s.eval = [eval_p](const Node& n, const std::vector<Tensor>& in, std::vector<Tensor>& out, EvalContext&) {
+                py::gil_scoped_acquire g;
+                py::list pin;
+                for (auto& t : in) pin.append(PyTensor::pack(t));
+                py::object r = (*eval_p)(const_cast<Node&>(n).shared_from_this(), pin);
+                if (r.is_none()) return false;
+                out.clear();
+                for (auto o : py::cast<py::list>(r)) {
+                    auto t = py::cast<py::tuple>(o);
+                    py::array arr = py::cast<py::array>(t[0]);
+                    std::vector<int64_t> shape(arr.shape(), arr.shape() + arr.ndim());
+                    out.push_back(tensor_from_array(arr, py::cast<std::string>(t[1]), shape, false));
+                }
+                return true;
+            };
+        OpRegistry::get().add(std::move(s));
+    }, py::arg("type"), py::arg("version"), py::arg("infer"), py::arg("evaluate") = py::none(), py::arg("attrs") = py::dict());
     mod.def("make_constant", [](py::array arr, const std::string& et, std::vector<int64_t> shape, bool share) {
         return make_constant(tensor_from_array(arr, et, shape, share));
     }, py::arg("array"), py::arg("element_type"), py::arg("shape"), py::arg("share") = false);
