@@ -174,7 +174,9 @@ def graph_api_bench(args):
     mask = torch.ones(B, S, dtype=torch.int64)
     typ = torch.zeros(B, S, dtype=torch.int64)
     model = ov.convert_model(net, example_input=(ids, mask, typ))
-    cm = core.compile_model(model, "CUDA.%d" % local_rank, {props.hint.inference_precision: "f16"})
+    # more than one GPU: tensor parallel, every rank compiles its shard of the one model and all ranks serve the same batch
+    cm = core.compile_model(model, "CUDA.%d" % local_rank, {props.hint.inference_precision: "f16",
+                                                            props.hint.model_distribution_policy: "TENSOR_PARALLEL" if world > 1 else ""})
     req = cm.create_infer_request()
     feed = [ids.numpy(), mask.numpy(), typ.numpy()]
     for _ in range(args.warmup):
@@ -193,10 +195,10 @@ def graph_api_bench(args):
         dist.destroy_process_group()
     wall = float(t.item())
     if rank == 0:
-        print(json.dumps({"metric": "sequences/s", "value": world * B * args.steps / wall, "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
-                          "warmup": args.warmup, "ms_per_step": wall * 1e3 / args.steps, "higher_is_better": True, "scaling": "weak", "dtype": "fp16",
+        print(json.dumps({"metric": "sequences/s", "value": B * args.steps / wall, "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": wall * 1e3 / args.steps, "higher_is_better": True, "scaling": "strong", "dtype": "fp16",
                           "data": "synthetic: uniform token ids, all-ones mask, N(0,0.02) weights",
-                          "config": {"model": "bert-large", "batch_per_gpu": B, "seq_len": S, "parallelism": "dp%d" % world, "device": "CUDA",
+                          "config": {"model": "bert-large", "global_batch": B, "seq_len": S, "parallelism": "tp%d" % world, "device": "CUDA",
                                      "timing": "end to end through InferRequest.infer (host inputs in, host output out)"}}))
     return 0
 

@@ -105,6 +105,18 @@ class OnnxFrontEnd(FrontEnd):
         return onnx.convert(model)
 
 
+class TensorFlowFrontEnd(FrontEnd):
+    name = "tf"
+
+    def supported(self, model) -> bool:
+        return isinstance(model, (str, os.PathLike)) and str(model).lower().endswith(".pb")
+
+    def convert(self, input_model) -> Model:
+        from . import tensorflow
+        model, _ = input_model
+        return tensorflow.convert(model)
+
+
 class GgufFrontEnd(FrontEnd):
     name = "gguf"
 
@@ -121,7 +133,7 @@ class GgufFrontEnd(FrontEnd):
 
 class FrontEndManager:
     def __init__(self):
-        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "gguf": GgufFrontEnd()}
+        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "tf": TensorFlowFrontEnd(), "gguf": GgufFrontEnd()}
 
     def get_available_front_ends(self) -> List[str]:
         return list(self._frontends)
@@ -145,7 +157,7 @@ _manager = FrontEndManager()
 
 
 def read_model(model, weights=None, extensions=None) -> Model:
-    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor), a ``.gguf`` or an ``.onnx`` file."""
+    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor), an ``.onnx``, a frozen TensorFlow ``.pb`` or a ``.gguf`` file."""
     if isinstance(model, Model):
         return model
     if hasattr(model, "read"):

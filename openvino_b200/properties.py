@@ -128,6 +128,7 @@ hint = _Namespace(
     allow_auto_batching=_Prop("ALLOW_AUTO_BATCHING"),
     dynamic_quantization_group_size=_Prop("DYNAMIC_QUANTIZATION_GROUP_SIZE"),
     kv_cache_precision=_Prop("KV_CACHE_PRECISION"),
+    model_distribution_policy=_Prop("MODEL_DISTRIBUTION_POLICY"),
     activations_scale_factor=_Prop("ACTIVATIONS_SCALE_FACTOR"),
     model=_Prop("MODEL_PTR"),
     PerformanceMode=PerformanceMode, ExecutionMode=ExecutionMode, Priority=Priority, SchedulingCoreType=SchedulingCoreType,

@@ -818,6 +818,15 @@ def _fc(n, ins, ctx):
     return [out]
 
 
+@op("AllReduce")
+def _all_reduce(n, ins, ctx):
+    x = ins[0]
+    if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+        x = x.contiguous().clone() if not ctx.on_gpu else x.contiguous()
+        torch.distributed.all_reduce(x)
+    return [x]
+
+
 @op("Einsum")
 def _einsum(n, ins, ctx):
     return [torch.einsum(n.get_attribute("equation"), *_same_device(ctx, ins))]
@@ -1206,7 +1215,7 @@ class CudaPlugin(Plugin):
     def supported_properties(self):
         return super().supported_properties() + [props.cuda.use_cuda_graphs, props.cuda.tensor_parallel_size, props.device.uuid,
                                                  props.device.architecture, props.device.type, props.optimal_batch_size,
-                                                 props.hint.kv_cache_precision]
+                                                 props.hint.kv_cache_precision, props.hint.model_distribution_policy]
 
     def default_config(self):
         d = super().default_config()
@@ -1256,8 +1265,15 @@ class CudaPlugin(Plugin):
         if str(cfg.get(props.hint.performance_mode)) == "THROUGHPUT" and props.num_streams not in config and props.num_streams not in self.config:
             cfg[props.num_streams] = 2
         dev = self._device(cfg)
+        rm = self.transform(model)
+        policy = str(cfg.get(props.hint.model_distribution_policy, "") or "")
+        if "TENSOR_PARALLEL" in policy and torch.distributed.is_available() and torch.distributed.is_initialized() \
+                and torch.distributed.get_world_size() > 1:
+            # one process per GPU: this rank compiles its own shard of the model (attention heads and MLP columns)
+            from ..parallel.graph_tp import tensor_parallel_partition
+            tensor_parallel_partition(rm, torch.distributed.get_rank(), torch.distributed.get_world_size())
         with torch.cuda.device(dev):
-            return CudaCompiledModel(self, model, cfg, self.transform(model), dev, _PRECISIONS[prec])
+            return CudaCompiledModel(self, model, cfg, rm, dev, _PRECISIONS[prec])
 
     def query_model(self, model: Model, config: dict) -> Dict[str, str]:
         rm = self.transform(model)

@@ -1,0 +1,17 @@
+"""Tensor-parallel partitioning of a generic graph, verified with gloo ranks on the CPU device."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_bert_shards_reproduce_the_full_model(world):
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+           "--master-port", str(29800 + world), os.path.join(HERE, "graph_tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "GRAPH_TP_OK world=%d" % world in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])
