@@ -7,6 +7,8 @@
 // src/core/reference/include/openvino/reference/rms_norm.hpp.
 #include <math_constants.h>
 
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -416,6 +418,45 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
     }
 }
 
+// ------------------------------------------------------------------------------------ fp8 activation quantisation
+// Per token and group of 128 channels: scale = amax / 448, q = x / scale as e4m3 (round to nearest even, saturating).
+// One warp per (token, group); a lane holds four channels. Role of the reference's dynamic_quantize_gpu_opt
+// (src/plugins/intel_gpu/src/kernel_selector/cl_kernels/dynamic_quantize_gpu_opt.cl:82) with fp8 instead of int8 output.
+__global__ void act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales, int rows, int cols) {
+    const int groups = cols / 128;
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= rows * groups) return;
+    const int r = warp / groups, g = warp - r * groups;
+    const __nv_bfloat16* src = x + (size_t)r * cols + g * 128 + lane * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), p1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    float v[4] = {__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1)};
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.f ? amax / 448.0f : 1.0f;
+    const float inv = 1.0f / scale;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(v[j] * inv, __NV_SATFINITE, __NV_E4M3);
+        packed |= uint32_t(b) << (8 * j);
+    }
+    *reinterpret_cast<uint32_t*>(q + (size_t)r * cols + g * 128 + lane * 4) = packed;
+    if (lane == 0) scales[(size_t)r * groups + g] = scale;
+}
+
+// ------------------------------------------------------------------------------------ KV-cache block copy
+// Copies whole cache blocks src[i] -> dst[i] for the key and the value cache (fork of a sequence, swap after a
+// preemption, beam reordering). One CTA per (pair, cache); 16-byte pieces. Role of pa_kv_cache_reorder_ref.cl.
+__global__ void kv_block_copy_kernel(uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, const int* __restrict__ src,
+                                     const int* __restrict__ dst, size_t pieces_per_block) {
+    uint4* cache = blockIdx.y == 0 ? k_cache : v_cache;
+    const size_t s = (size_t)src[blockIdx.x] * pieces_per_block, d = (size_t)dst[blockIdx.x] * pieces_per_block;
+    if (s == d) return;
+    for (size_t i = threadIdx.x; i < pieces_per_block; i += blockDim.x) cache[d + i] = cache[s + i];
+}
+
 // ------------------------------------------------------------------------------------ im2col (convolution as GEMM)
 // cols[t][k] for t = (b, ho, wo) and k = (c * kh + r) * kw + s is x[b][c][ho*sh - pt + r*dh][wo*sw - pl + s*dw] (zero outside
 // the image and for k >= C*kh*kw): the [T, Kpad] operand of out[T, O] = cols x W[O, Kpad]^T on the tcgen05 GEMM. A thread
@@ -652,6 +693,28 @@ int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void
         rope_kv_write_kernel<<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
                                                     (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
     }
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_act_quant_fp8(const void* x, void* q, float* scales, int rows, int cols, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(x && q && scales && rows > 0, "ovb_act_quant_fp8: null operand");
+    OVB_REQUIRE(cols % 128 == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0,
+                "ovb_act_quant_fp8: the channel count must be a multiple of 128 and the rows 8-byte aligned");
+    const size_t warps = (size_t)rows * (cols / 128);
+    act_quant_fp8_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)q, scales, rows, cols);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_kv_block_copy(void* k_cache, void* v_cache, const int* src_blocks, const int* dst_blocks, int num_pairs, int64_t block_bytes,
+                      ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(k_cache && v_cache && src_blocks && dst_blocks, "ovb_kv_block_copy: null operand");
+    OVB_REQUIRE(block_bytes > 0 && block_bytes % 16 == 0, "ovb_kv_block_copy: a block must be a multiple of 16 bytes");
+    if (num_pairs <= 0) return 0;
+    kv_block_copy_kernel<<<dim3(num_pairs, 2), 256, 0, stream>>>((uint4*)k_cache, (uint4*)v_cache, src_blocks, dst_blocks, (size_t)block_bytes / 16);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -91,6 +91,11 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
                   int cols, float eps, int is_f16, ovb_stream_t stream);
 // out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
 int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
+/* bf16 [rows, cols] -> fp8 e4m3 bytes with one fp32 scale per row and group of 128 channels (scales [rows, cols/128]). */
+int ovb_act_quant_fp8(const void* x, void* q, float* scales, int rows, int cols, ovb_stream_t stream);
+/* Copy cache blocks src_blocks[i] -> dst_blocks[i] in the key and the value cache (block_bytes per block and cache). */
+int ovb_kv_block_copy(void* k_cache, void* v_cache, const int* src_blocks, const int* dst_blocks, int num_pairs, int64_t block_bytes,
+                      ovb_stream_t stream);
 /* Convolution operand for the GEMM: 16-bit NCHW image -> cols [B*Ho*Wo, Kpad], k = (c*kh + r)*kw + s, zero padded. */
 int ovb_im2col(const void* x, void* cols, int B, int C, int H, int W, int kh, int kw, int sh, int sw, int pt, int pl, int dh, int dw,
                int Ho, int Wo, int Kpad, ovb_stream_t stream);

@@ -272,6 +272,33 @@ def silu_mul(gu, out=None):
     return out
 
 
+def act_quant_fp8(x: torch.Tensor):
+    """bf16 [rows, cols] -> (e4m3 bytes [rows, cols] uint8, fp32 scales [rows, cols / 128]); x ~ q * scale per group of 128."""
+    rows, cols = x.shape
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    s = torch.empty((rows, cols // 128), dtype=torch.float32, device=x.device)
+    _check(lib().ovb_act_quant_fp8(C.c_void_p(x.data_ptr()), C.c_void_p(q.data_ptr()), C.c_void_p(s.data_ptr()), C.c_int(rows), C.c_int(cols),
+                                   C.c_void_p(_stream())), "ovb_act_quant_fp8")
+    return q, s
+
+
+def kv_block_copy(k_cache: torch.Tensor, v_cache: torch.Tensor, src_blocks: torch.Tensor, dst_blocks: torch.Tensor) -> None:
+    """Copy whole blocks (first dimension of the caches) src -> dst in both caches; int32 block lists on the device."""
+    n = int(src_blocks.numel())
+    block_bytes = k_cache[0].numel() * k_cache.element_size()
+    _check(lib().ovb_kv_block_copy(C.c_void_p(k_cache.data_ptr()), C.c_void_p(v_cache.data_ptr()), C.c_void_p(src_blocks.data_ptr()),
+                                   C.c_void_p(dst_blocks.data_ptr()), C.c_int(n), C.c_int64(block_bytes), C.c_void_p(_stream())), "ovb_kv_block_copy")
+
+
+def lora_apply(x: torch.Tensor, a: "PackedWeight", b: "PackedWeight", y: torch.Tensor, alpha: float = 1.0) -> torch.Tensor:
+    """y + alpha * (x @ A^T) @ B^T with both products on the tcgen05 GEMM (A [r, K], B [N, r] packed with ``from_dense``);
+    the second GEMM adds ``y`` in its epilogue. Role of the reference's lora_{ref,opt}.cl kernels."""
+    h = gemm(x, a)
+    if alpha != 1.0:
+        h = h * alpha
+    return gemm(h, b, residual=y)
+
+
 def conv2d(x: torch.Tensor, w: "PackedWeight", kernel, strides, pads_begin, pads_end, dilations, act: int = ACT_NONE) -> torch.Tensor:
     """2-D convolution of a 16-bit NCHW tensor as im2col + tcgen05 GEMM; ``w`` packs the filters as [O, Kpad] with
     k = (c*kh + r)*kw + s (``pack_conv_weight``). Returns NCHW (a permuted view of the GEMM's [B*Ho*Wo, O] output)."""

@@ -105,6 +105,41 @@ def test_conv2d_im2col_gemm(ops, B, C, H, W, O, k, stride, pad, dil):
     assert _rel_err(y, ref) < 1e-2
 
 
+def test_act_quant_fp8_groups_of_128(ops):
+    torch.manual_seed(6)
+    x = (torch.randn(37, 512, device="cuda") * torch.logspace(-2, 1, 512, device="cuda")).to(torch.bfloat16)
+    q, s = ops.act_quant_fp8(x)
+    ops.check_status("act_quant_fp8")
+    xf = x.float().reshape(37, 4, 128)
+    want_s = xf.abs().amax(-1) / 448.0
+    assert torch.allclose(s, want_s, rtol=1e-6)
+    deq = q.view(torch.float8_e4m3fn).float().reshape(37, 4, 128) * s.unsqueeze(-1)
+    assert _rel_err(deq, xf) < 4e-2                       # e4m3: 3 mantissa bits
+    ref_q = (xf / want_s.unsqueeze(-1)).to(torch.float8_e4m3fn).view(torch.uint8).reshape(37, 512)
+    assert (q == ref_q).float().mean() > 0.999
+
+
+def test_kv_block_copy_and_lora(ops):
+    torch.manual_seed(7)
+    k = torch.randn(12, 8, 16, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(12, 8, 16, 128, device="cuda", dtype=torch.bfloat16)
+    k0, v0 = k.clone(), v.clone()
+    src = torch.tensor([1, 5, 7], dtype=torch.int32, device="cuda")
+    dst = torch.tensor([2, 9, 7], dtype=torch.int32, device="cuda")
+    ops.kv_block_copy(k, v, src, dst)
+    ops.check_status("kv_block_copy")
+    want_k, want_v = k0.clone(), v0.clone()
+    want_k[dst.long()], want_v[dst.long()] = k0[src.long()], v0[src.long()]
+    assert torch.equal(k, want_k) and torch.equal(v, want_v)
+    x = torch.randn(40, 256, device="cuda", dtype=torch.bfloat16)
+    a = (torch.randn(64, 256, device="cuda") * 0.05).to(torch.bfloat16)
+    b = (torch.randn(384, 64, device="cuda") * 0.05).to(torch.bfloat16)
+    y = torch.randn(40, 384, device="cuda", dtype=torch.bfloat16)
+    out = ops.lora_apply(x, ops.PackedWeight.from_dense(a), ops.PackedWeight.from_dense(b), y, alpha=0.5)
+    ref = y.float() + 0.5 * (x.float() @ a.float().t()) @ b.float().t()
+    assert _rel_err(out, ref) < 1e-2
+
+
 @pytest.mark.parametrize("rows,cols", [(3, 128), (64, 4096), (17, 8192), (5, 14336)])
 def test_rmsnorm(ops, rows, cols):
     torch.manual_seed(3)
