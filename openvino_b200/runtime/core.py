@@ -599,7 +599,12 @@ class InferRequest:
         self._bind(inputs, share_inputs)
         self._cancel_requested = False
         self._req.infer()
-        return self.results
+        res = self.results
+        if not share_outputs and getattr(self, "_pinned_out", None):
+            # the device keeps its results in request-owned staging memory that the next inference overwrites:
+            # without share_outputs the caller gets arrays of its own
+            res = OVDict(self._cm._outputs, [np.array(a, copy=True) if isinstance(a, np.ndarray) else a for a in res.to_tuple()])
+        return res
 
     def start_async(self, inputs=None, userdata=None, share_inputs: bool = False) -> None:
         self._bind(inputs, share_inputs)

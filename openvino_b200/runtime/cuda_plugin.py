@@ -742,7 +742,9 @@ def _prepare_fc(n: Node, ins, ctx: Ctx):
         return st
     K = ctx.K
     t = n.get_type_name()
-    st = {"packed": None}
+    st = {"packed": None, "act": n.get_rt_info().get("fused_activation")}
+    if st["act"] is not None:
+        st["act"] = str(st["act"])
     w_node = n.input_value(1).get_node()
     if K is not None and w_node.get_type_name() == "Constant":
         bias = None
@@ -807,15 +809,38 @@ def _fc(n, ins, ctx):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        out = ctx.K.gemm(x2, pw)
+        act = st.get("act")
+        fused = act is not None and not (has_bias and pw.bias is None)      # the epilogue order is bias, then activation
+        out = ctx.K.gemm(x2, pw, act=_GEMM_ACTS[act] if fused else 0)
         if has_bias and pw.bias is None:
             out = out + ins[2].to(out.device, out.dtype)
+        if act is not None and not fused:
+            out = _TORCH_ACTS[act](out)
         return [out.reshape(list(x.shape[:-1]) + [pw.N])]
     w = _dequant_weight(n, ins, ctx) if n.get_type_name() == "FullyConnectedCompressed" else ins[1]
     out = torch.matmul(x, w.to(x.device, x.dtype).t())
     if has_bias:
         out = out + ins[2].to(out.device, out.dtype)
+    if st.get("act") is not None:
+        out = _TORCH_ACTS[st["act"]](out)
     return [out]
+
+
+_GEMM_ACTS = {"gelu_erf": 1, "relu": 2, "silu": 3, "gelu_tanh": 5}
+_TORCH_ACTS = {"gelu_erf": F.gelu, "relu": F.relu, "silu": F.silu, "gelu_tanh": lambda t: F.gelu(t, approximate="tanh")}
+
+
+@op("LayerNormFused")
+def _layer_norm_fused(n, ins, ctx):
+    x, g, b = ins[0], ins[1], ins[2]
+    eps = float(n.get_attribute("eps"))
+    if ctx.K is not None and x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.shape[-1] % 8 == 0:
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        out = ctx.K.layernorm(x2, g.to(x.device, x.dtype).contiguous(), b.to(x.device, x.dtype).contiguous(), eps)
+        return [out.reshape(x.shape)]
+    return [F.layer_norm(x, [x.shape[-1]], g.to(x.device, x.dtype), b.to(x.device, x.dtype), eps)]
 
 
 @op("AllReduce")
@@ -1148,6 +1173,7 @@ class CudaCompiledModel(CompiledModel):
             else:
                 outs = program.run([to_device(t) for t in ins], prof)
                 res = self._finish(outs, req)
+                torch.cuda.current_stream(self.device).synchronize()
             if prof is not None:
                 req._profile = [ProfilingInfo(name, typ, "cuda", (ev[0].elapsed_time(ev[1]) * 1e3) if ev else 0.0) for name, typ, ev in prof]
             return res
@@ -1164,11 +1190,22 @@ class CudaCompiledModel(CompiledModel):
                 user.torch().copy_(o)
                 res.append(user)
                 continue
-            host = o.detach().to("cpu")
-            if host.dtype == torch.bfloat16:
-                res.append(Tensor(host.contiguous()))
+            # results land in pinned host memory owned by the request (re-used by its next inference): the copy runs at
+            # full PCIe rate and without a staging pass; the caller synchronises the stream before handing them out
+            o = o.detach()
+            if o.is_cuda:
+                pinned = req.__dict__.setdefault("_pinned_out", {})
+                host = pinned.get(i)
+                if host is None or host.shape != o.shape or host.dtype != o.dtype:
+                    host = torch.empty(o.shape, dtype=o.dtype, pin_memory=True)
+                    pinned[i] = host
+                host.copy_(o, non_blocking=True)
             else:
-                res.append(Tensor(host.contiguous().numpy(), shared_memory=True))
+                host = o.contiguous()
+            if host.dtype == torch.bfloat16:
+                res.append(Tensor(host))
+            else:
+                res.append(Tensor(host.numpy(), shared_memory=True))
         return res
 
     def _variables(self, request: InferRequest) -> List[VariableState]:
@@ -1255,6 +1292,8 @@ class CudaPlugin(Plugin):
         rm = model.clone()
         _c.run_moc_transformations(rm._m, True)
         _c.run_llm_fusions(rm._m)
+        from . import cuda_fusions
+        cuda_fusions.run(rm)
         return rm
 
     def compile_model(self, model: Model, config: dict) -> CompiledModel:

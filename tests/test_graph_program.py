@@ -20,6 +20,8 @@ def both(m: Model, arrays, transform=True, rtol=1e-4, atol=1e-4):
     if transform:
         _c.run_moc_transformations(rm._m, True)
         _c.run_llm_fusions(rm._m)
+        from openvino_b200.runtime import cuda_fusions
+        cuda_fusions.run(rm)          # bias / activation into FullyConnected, LayerNorm as one operation
     prog = GraphProgram(rm, "cpu")
     got = prog.run([torch.from_numpy(np.ascontiguousarray(a)) for a in arrays])
     assert len(got) == len(want)
@@ -38,6 +40,13 @@ def test_resnet_and_bert_graphs():
     mask = torch.ones(2, 10, dtype=torch.int64)
     mask[0, 7:] = 0
     m = ov.convert_model(bert, example_input=(ids, mask, torch.zeros(2, 10, dtype=torch.int64)))
+    fused = m.clone()
+    _c.run_moc_transformations(fused._m, True)
+    _c.run_llm_fusions(fused._m)
+    from openvino_b200.runtime import cuda_fusions
+    assert cuda_fusions.run(fused) >= 12
+    types = [n.get_type_name() for n in fused.get_ops()]
+    assert "LayerNormFused" in types and "MVN" not in types and "Gelu" not in types
     both(m, [ids.numpy(), mask.numpy(), np.zeros((2, 10), np.int64)], rtol=1e-3, atol=1e-3)
 
 
