@@ -108,6 +108,11 @@ int ovb_argmax(const void* logits, int ld, int rows, int vocab, void* out_ids, i
 // Stochastic sampling (sampling.cu): temperature, top-k, top-p; deterministic for a (seed, *step, row) triple.
 int ovb_sample(const void* logits, int ld, int rows, int vocab, float temperature, int top_k, float top_p, uint64_t seed,
                const int* step, int* out_ids, ovb_stream_t stream);
+/* Temperature sampling over a vocabulary shard: perturbed arg-max (Gumbel-max) of logits[:, 0..vocab) whose tokens have the
+   global indices vocab_offset + i; out_ids are local indices, out_max the perturbed maxima (for the arg-max exchange of
+   tensor-parallel ranks). With vocab_offset = 0 and the whole vocabulary it is a complete sampler. */
+int ovb_sample_gumbel(const void* logits, int ld, int rows, int vocab, int vocab_offset, float temperature, uint64_t seed, const int* step,
+                      int* out_ids, float* out_max, ovb_stream_t stream);
 int ovb_bump(int* counter, ovb_stream_t stream);     // *counter += 1 on the device
 int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream);
 // Mixture of experts. Router: softmax over E logits per token, top-k kept and renormalised; weights is dense [T, E] fp32.

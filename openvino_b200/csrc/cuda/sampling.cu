@@ -115,6 +115,56 @@ __global__ void bump_kernel(int* p) { *p += 1; }
 }  // namespace ovb
 
 extern "C" {
+namespace ovb {
+
+// Sampling over vocabulary shards without gathering the logits (Gumbel-max): argmax_i(logit_i / T + G_i) with
+// G_i = -log(-log(u_i)) is a draw from softmax(logits / T) when the u_i are independent uniforms. u_i depends on the seed,
+// the step word, the row and the GLOBAL token index only, so every tensor-parallel rank perturbs its own shard, reduces
+// it to (best value, local index), and the usual arg-max exchange between the ranks picks the token.
+__global__ void __launch_bounds__(kSampleThreads) gumbel_argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int V, int vocab_offset,
+                                                                       float inv_temp, uint64_t seed, const int* __restrict__ step_ptr,
+                                                                       int* __restrict__ out_ids, float* __restrict__ out_max) {
+    __shared__ float sv[kSampleThreads / 32];
+    __shared__ int si[kSampleThreads / 32];
+    const int row = blockIdx.x;
+    const __nv_bfloat16* lr = logits + (size_t)row * ld;
+    const uint64_t base = mix64(seed ^ mix64(((uint64_t)(step_ptr ? *step_ptr : 0) << 20) ^ (uint64_t)row));
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += kSampleThreads) {
+        const uint64_t h = mix64(base ^ ((uint64_t)(uint32_t)(vocab_offset + i) * 0xD1B54A32D192ED03ull));
+        const float u = ((float)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);     // (0, 1)
+        const float g = -__logf(-__logf(u));
+        const float f = __bfloat162float(lr[i]) * inv_temp + g;
+        if (f > best) { best = f; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < kSampleThreads / 32 ? sv[lane] : -INFINITY;
+        bi = lane < kSampleThreads / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (lane == 0) {
+            out_ids[row] = bi == 0x7fffffff ? 0 : bi;
+            if (out_max) out_max[row] = best;
+        }
+    }
+}
+
+}  // namespace ovb
+
 using namespace ovb;
 
 // out_ids[row] ~ softmax(logits[row] / temperature) restricted to the top_k most likely tokens and to the smallest
@@ -126,6 +176,16 @@ int ovb_sample(const void* logits, int ld, int rows, int vocab, float temperatur
     OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0 && temperature > 0.f, "ovb_sample: bad arguments (temperature must be > 0)");
     sample_kernel<<<rows, kSampleThreads, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, 1.0f / temperature, top_k,
                                                        top_p <= 0.f ? 1e-6f : top_p, seed, step, out_ids);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_sample_gumbel(const void* logits, int ld, int rows, int vocab, int vocab_offset, float temperature, uint64_t seed, const int* step,
+                      int* out_ids, float* out_max, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0 && temperature > 0.f, "ovb_sample_gumbel: bad arguments (temperature must be > 0)");
+    gumbel_argmax_kernel<<<rows, kSampleThreads, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, vocab_offset, 1.0f / temperature, seed, step,
+                                                              out_ids, out_max);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -299,6 +299,19 @@ def lora_apply(x: torch.Tensor, a: "PackedWeight", b: "PackedWeight", y: torch.T
     return gemm(h, b, residual=y)
 
 
+def sample_gumbel(logits: torch.Tensor, temperature: float, seed: int = 0, step: Optional[torch.Tensor] = None, vocab_offset: int = 0,
+                  out: Optional[torch.Tensor] = None, out_max: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Temperature sampling by perturbed arg-max over bf16 ``logits`` [rows, V] (a vocabulary shard starting at
+    ``vocab_offset``); returns local token indices (int32) and, in ``out_max``, the perturbed maxima."""
+    rows, V = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(lib().ovb_sample_gumbel(C.c_void_p(logits.data_ptr()), C.c_int(logits.stride(0)), C.c_int(rows), C.c_int(V), C.c_int(vocab_offset),
+                                   C.c_float(temperature), C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), C.c_void_p(_ptr(step)),
+                                   C.c_void_p(out.data_ptr()), C.c_void_p(_ptr(out_max)), C.c_void_p(_stream())), "ovb_sample_gumbel")
+    return out
+
+
 def conv2d(x: torch.Tensor, w: "PackedWeight", kernel, strides, pads_begin, pads_end, dilations, act: int = ACT_NONE) -> torch.Tensor:
     """2-D convolution of a 16-bit NCHW tensor as im2col + tcgen05 GEMM; ``w`` packs the filters as [O, Kpad] with
     k = (c*kh + r)*kw + s (``pack_conv_weight``). Returns NCHW (a permuted view of the GEMM's [B*Ho*Wo, O] output)."""

@@ -259,8 +259,9 @@ class CudaLlmExecutor:
 
     def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
         new = None if temperature <= 0 else (float(temperature), int(top_k), float(top_p), int(seed))
-        if new is not None and self.tp_size > 1:
-            raise NotImplementedError("stochastic sampling over vocabulary shards is not implemented: use greedy decoding with tensor parallelism")
+        if new is not None and self.tp_size > 1 and (top_k > 0 or top_p < 1.0):
+            raise NotImplementedError("top-k / top-p over vocabulary shards is not implemented: with tensor parallelism use greedy "
+                                      "decoding or plain temperature sampling")
         if new != self.sampling:
             self._graphs.clear()       # captured decode graphs embed the sampling kernel
         self.sampling = new
@@ -326,7 +327,15 @@ class CudaLlmExecutor:
         if self.sampling is not None:
             temp, top_k, top_p, seed = self.sampling
             K.bump(self.sample_step)
-            K.sample(sb.logits[:B], temp, top_k, top_p, seed, self.sample_step, out=sb.tokens[:B])
+            if self.tp_size > 1:
+                # every rank perturbs its vocabulary shard with noise that depends on the global token index, then the
+                # ranks exchange (best value, index): a draw from the full softmax without gathering the logits
+                shard = self.cfg.vocab_size // self.tp_size
+                K.sample_gumbel(sb.logits[:B], temp, seed, self.sample_step, vocab_offset=self.w.tp_rank * shard, out=sb.tokens[:B],
+                                out_max=sb.logit_max[:B])
+                self.comm.argmax_combine(sb.tokens[:B], sb.logit_max[:B], shard)
+            else:
+                K.sample(sb.logits[:B], temp, top_k, top_p, seed, self.sample_step, out=sb.tokens[:B])
             self.kernel_launches += 1
         elif self.tp_size == 1:
             K.argmax(sb.logits[:B], out=sb.tokens[:B])

@@ -105,6 +105,33 @@ def test_conv2d_im2col_gemm(ops, B, C, H, W, O, k, stride, pad, dil):
     assert _rel_err(y, ref) < 1e-2
 
 
+def test_gumbel_sampling_matches_softmax_and_shards_agree(ops):
+    torch.manual_seed(8)
+    V = 512
+    logits = (torch.randn(1, V, device="cuda") * 2.0).to(torch.bfloat16)
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rows = logits.expand(4096, V).contiguous()
+    counts = torch.zeros(V, device="cuda")
+    for it in range(8):
+        step.fill_(it)
+        ids = ops.sample_gumbel(rows, 0.8, seed=11, step=step)
+        counts += torch.bincount(ids.long(), minlength=V).float()
+    ops.check_status("sample_gumbel")
+    p = torch.softmax(logits.float()[0] / 0.8, -1)
+    freq = counts / counts.sum()
+    top = torch.topk(p, 20).indices
+    assert (freq[top] - p[top]).abs().max() < 0.01 and (freq - p).abs().sum() < 0.12
+    # two vocabulary shards with global indices give the full-vocabulary draw
+    x = (torch.randn(32, V, device="cuda") * 3.0).to(torch.bfloat16)
+    full_max = torch.empty(32, device="cuda")
+    full = ops.sample_gumbel(x, 1.3, seed=5, step=step, out_max=full_max)
+    m0, m1 = torch.empty(32, device="cuda"), torch.empty(32, device="cuda")
+    i0 = ops.sample_gumbel(x[:, :256].contiguous(), 1.3, seed=5, step=step, vocab_offset=0, out_max=m0)
+    i1 = ops.sample_gumbel(x[:, 256:].contiguous(), 1.3, seed=5, step=step, vocab_offset=256, out_max=m1)
+    merged = torch.where(m0 >= m1, i0, i1 + 256)
+    assert torch.equal(merged, full) and torch.equal(torch.maximum(m0, m1), full_max)
+
+
 def test_act_quant_fp8_groups_of_128(ops):
     torch.manual_seed(6)
     x = (torch.randn(37, 512, device="cuda") * torch.logspace(-2, 1, 512, device="cuda")).to(torch.bfloat16)

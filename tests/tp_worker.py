@@ -117,6 +117,18 @@ def main():
     if any(o != obj[0] for o in obj):
         failures.append(("ranks disagree", obj))
 
+    # temperature sampling over vocabulary shards (perturbed arg-max + exchange): every rank draws the same tokens, and
+    # another seed draws other tokens
+    sgen = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.5, rng_seed=7)
+    s1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, sgen)]
+    K.check_status("tp sampling")
+    sobj = [None] * world
+    dist.all_gather_object(sobj, s1)
+    sgen2 = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.5, rng_seed=8)
+    s2 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, sgen2)]
+    if any(o != sobj[0] for o in sobj) or s1 == s2 or s1 == got:
+        failures.append(("tp sampling", sobj, s2))
+
     # mixture of experts: experts sharded over the ranks (expert parallel), attention tensor parallel
     from openvino_b200.models.llm_config import TINY_MOE
     mcfg = TINY_MOE.with_(num_heads=8, num_kv_heads=world if world > 2 else 2, num_experts=4 if world <= 4 else 8)
