@@ -90,6 +90,15 @@ bool unary(Ins in, Outs out, FR fr, FI fi) {
             Tensor r(ET::f64, x.shape);
             for (int64_t i = 0; i < n; ++i) r.ptr<double>()[i] = fr(x.ptr<double>()[i]);
             out[0] = r;
+        } else if (x.et == ET::f32) {
+            // fp32 in, fp32 out: no staging copies, large tensors are split over threads
+            Tensor r(ET::f32, x.shape);
+            const float* p = x.ptr<float>();
+            float* q = r.ptr<float>();
+            parallel_for(n, n >= (1 << 16) ? 0 : 1, [&](int64_t i0, int64_t i1) {
+                for (int64_t i = i0; i < i1; ++i) q[i] = float(fr(double(p[i])));
+            });
+            out[0] = r;
         } else {
             auto v = to_f32(x);
             for (auto& e : v) e = float(fr(double(e)));
@@ -121,6 +130,21 @@ bool binary(const Node& n, Ins in, Outs out, FR fr, FI fi) {
             std::vector<double> vo((size_t)shape_size(os));
             broadcast_apply(os, sa, sb, va.data(), vb.data(), vo.data(), fr);
             out[0] = from_f64(cet, os, vo);
+        } else if (a.et == ET::f32 && b.et == ET::f32 && (n.outs[0].et == ET::f32 || n.outs[0].et == ET::dynamic)) {
+            // fp32 operands: straight from the tensors' memory into the result
+            Tensor r(ET::f32, os);
+            const float* pa = a.ptr<float>();
+            const float* pb = b.ptr<float>();
+            float* po = r.ptr<float>();
+            const int64_t total = shape_size(os);
+            if (a.shape == b.shape) {
+                parallel_for(total, total >= (1 << 16) ? 0 : 1, [&](int64_t i0, int64_t i1) {
+                    for (int64_t i = i0; i < i1; ++i) po[i] = float(fr(pa[i], pb[i]));
+                });
+            } else {
+                broadcast_apply(os, sa, sb, pa, pb, po, [&](float x, float y) { return float(fr(x, y)); });
+            }
+            out[0] = r;
         } else {
             auto va = to_f32(a), vb = to_f32(b);
             std::vector<float> vo((size_t)shape_size(os));
@@ -198,26 +222,68 @@ bool reduce(const Node& n, Ins in, Outs out, double init, Acc acc, Fin fin) {
     return true;
 }
 
-// C[M,N] (+)= A[M,K] * B[K,N] (row-major, fp32) with simple cache blocking; rows are split over threads
-void sgemm(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int threads, bool accumulate = false) {
-    parallel_for(M, threads, [&](int64_t m0, int64_t m1) {
-        const int64_t KB = 256, NB = 512;
-        for (int64_t m = m0; m < m1; ++m) if (!accumulate) std::fill(C + m * N, C + (m + 1) * N, 0.f);
-        for (int64_t k0 = 0; k0 < K; k0 += KB) {
-            const int64_t k1 = std::min(K, k0 + KB);
-            for (int64_t n0 = 0; n0 < N; n0 += NB) {
-                const int64_t n1 = std::min(N, n0 + NB);
-                for (int64_t m = m0; m < m1; ++m) {
-                    float* c = C + m * N;
-                    for (int64_t k = k0; k < k1; ++k) {
-                        const float a = A[m * K + k];
-                        const float* b = B + k * N;
-                        for (int64_t nn = n0; nn < n1; ++nn) c[nn] += a * b[nn];
-                    }
-                }
+// Inner block of the fp32 GEMM: rows [m0, m1) x columns [n0, n1) += A[:, k0:k1] * B[k0:k1, :]. Four rows share every load
+// of a B row, the column loop is unit stride so that the compiler vectorises it; the function is cloned for AVX-512, AVX2
+// and baseline x86-64 and the loader picks the clone that the machine supports.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define OVC_SIMD_CLONES __attribute__((target_clones("arch=x86-64-v4", "arch=x86-64-v3", "default"), optimize("O3")))
+#else
+#define OVC_SIMD_CLONES
+#endif
+OVC_SIMD_CLONES
+void sgemm_block(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int64_t N, int64_t K, int64_t m0, int64_t m1,
+                 int64_t k0, int64_t k1, int64_t n0, int64_t n1) {
+    int64_t m = m0;
+    for (; m + 4 <= m1; m += 4) {
+        float* __restrict__ c0 = C + m * N;
+        float* __restrict__ c1 = c0 + N;
+        float* __restrict__ c2 = c1 + N;
+        float* __restrict__ c3 = c2 + N;
+        for (int64_t k = k0; k < k1; ++k) {
+            const float a0 = A[m * K + k], a1 = A[(m + 1) * K + k], a2 = A[(m + 2) * K + k], a3 = A[(m + 3) * K + k];
+            const float* __restrict__ b = B + k * N;
+            for (int64_t nn = n0; nn < n1; ++nn) {
+                const float bv = b[nn];
+                c0[nn] += a0 * bv;
+                c1[nn] += a1 * bv;
+                c2[nn] += a2 * bv;
+                c3[nn] += a3 * bv;
             }
         }
-    });
+    }
+    for (; m < m1; ++m) {
+        float* __restrict__ c = C + m * N;
+        for (int64_t k = k0; k < k1; ++k) {
+            const float a = A[m * K + k];
+            const float* __restrict__ b = B + k * N;
+            for (int64_t nn = n0; nn < n1; ++nn) c[nn] += a * b[nn];
+        }
+    }
+}
+
+// C[M,N] (+)= A[M,K] * B[K,N] (row-major, fp32): cache blocking over K and N (the B block stays in L2), the work is split
+// over threads along M, or along N when there are fewer rows than threads
+void sgemm(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int threads, bool accumulate = false) {
+    if (threads <= 0) threads = (int)std::max(1u, std::thread::hardware_concurrency());
+    const int64_t KB = 128, NB = 256;
+    if (M >= 4 * threads || N < 64 * threads) {
+        parallel_for((M + 3) / 4, threads, [&](int64_t q0, int64_t q1) {
+            const int64_t m0 = q0 * 4, m1 = std::min(M, q1 * 4);
+            for (int64_t m = m0; m < m1; ++m) if (!accumulate) std::fill(C + m * N, C + (m + 1) * N, 0.f);
+            for (int64_t k0 = 0; k0 < K; k0 += KB)
+                for (int64_t n0 = 0; n0 < N; n0 += NB)
+                    sgemm_block(A, B, C, N, K, m0, m1, k0, std::min(K, k0 + KB), n0, std::min(N, n0 + NB));
+        });
+    } else {
+        const int64_t nblocks = (N + NB - 1) / NB;
+        parallel_for(nblocks, threads, [&](int64_t b0, int64_t b1) {
+            for (int64_t nb = b0; nb < b1; ++nb) {
+                const int64_t n0 = nb * NB, n1 = std::min(N, n0 + NB);
+                if (!accumulate) for (int64_t m = 0; m < M; ++m) std::fill(C + m * N + n0, C + m * N + n1, 0.f);
+                for (int64_t k0 = 0; k0 < K; k0 += KB) sgemm_block(A, B, C, N, K, 0, M, k0, std::min(K, k0 + KB), n0, n1);
+            }
+        });
+    }
 }
 // C[M,N] = A[M,K] * B[N,K]^T
 void sgemm_nt(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int threads) {
@@ -318,13 +384,28 @@ bool eval_conv(const Node& n, Ins in, Outs out, EvalContext& ctx, bool group) {
     auto pad3v = [&](std::vector<int64_t> s, int64_t v) { while (s.size() < 3) s.insert(s.begin(), v); return s; };
     const auto S = pad3v(st, 1), D = pad3v(dil, 1), PB = pad3v(pb, 0);
     const int64_t ksz = Kk[0] * Kk[1] * Kk[2], osz = O[0] * O[1] * O[2], isz = I[0] * I[1] * I[2];
-    auto vx = to_f32(X), vw = to_f32(W);
-    std::vector<float> vo((size_t)(N * G * Cout_g * osz));
+    // fp32 tensors are read and written in place; other types go through fp32 copies
+    std::vector<float> vx_c, vw_c, vo_c;
+    if (X.et != ET::f32) vx_c = to_f32(X);
+    if (W.et != ET::f32) vw_c = to_f32(W);
+    const float* vx_p = X.et == ET::f32 ? X.ptr<float>() : vx_c.data();
+    const float* vw_p = W.et == ET::f32 ? W.ptr<float>() : vw_c.data();
+    Shape os = {N, G * Cout_g};
+    os.insert(os.end(), osp.begin(), osp.end());
+    Tensor result;
+    float* vo_p;
+    if (X.et == ET::f32) {
+        result = Tensor(ET::f32, os);
+        vo_p = result.ptr<float>();
+    } else {
+        vo_c.resize((size_t)(N * G * Cout_g * osz));
+        vo_p = vo_c.data();
+    }
     const int64_t Kdim = Cin_g * ksz;
     std::vector<float> col((size_t)(Kdim * osz));
     for (int64_t b = 0; b < N; ++b) {
         for (int64_t g = 0; g < G; ++g) {
-            const float* xg = vx.data() + (b * Cin + g * Cin_g) * isz;
+            const float* xg = vx_p + (b * Cin + g * Cin_g) * isz;
             parallel_for(Kdim, ctx.num_threads, [&](int64_t r0, int64_t r1) {
                 for (int64_t r = r0; r < r1; ++r) {
                     const int64_t c = r / ksz, kk = r % ksz;
@@ -344,12 +425,10 @@ bool eval_conv(const Node& n, Ins in, Outs out, EvalContext& ctx, bool group) {
                     }
                 }
             });
-            sgemm(vw.data() + g * Cout_g * Kdim, col.data(), vo.data() + (b * G + g) * Cout_g * osz, Cout_g, osz, Kdim, ctx.num_threads);
+            sgemm(vw_p + g * Cout_g * Kdim, col.data(), vo_p + (b * G + g) * Cout_g * osz, Cout_g, osz, Kdim, ctx.num_threads);
         }
     }
-    Shape os = {N, G * Cout_g};
-    os.insert(os.end(), osp.begin(), osp.end());
-    out[0] = from_f32(X.et, os, vo);
+    out[0] = X.et == ET::f32 ? result : from_f32(X.et, os, vo_c);
     return true;
 }
 
