@@ -164,16 +164,60 @@ class MakeStateful(ModelPass):
 
 
 class LowLatency2(ModelPass):
-    """Unrolls single-iteration TensorIterator/Loop state: back-edge pairs become ReadValue/Assign outside the body
-    when the iteration count is 1 (src/common/transformations/src/transformations/control_flow/unroll_tensor_iterator.cpp,
-    src/core/src/pass/low_latency.cpp)."""
+    """Turns the back edges of TensorIterator / Loop nodes into model state: the initial value of every merged input is
+    read through ``ReadValue`` and the value after the last iteration is stored with ``Assign``, so a recurrent network
+    that is fed one chunk of the sequence per inference carries its hidden state from one call to the next
+    (``reset_state`` starts a new sequence). With ``use_const_initializer`` the ReadValue starts from zeros of the
+    initial value's shape instead of the original initial-value sub-graph. Reference: src/core/src/pass/low_latency.cpp."""
 
     def __init__(self, use_const_initializer: bool = True):
         super().__init__("LowLatency2")
         self.use_const_initializer = use_const_initializer
 
     def run_on_model(self, model: Model) -> bool:
-        return False   # no recurrent bodies with back edges survive conversion in this framework's frontends
+        import numpy as np
+        from .. import opset as ops
+        changed = False
+        sinks = []
+        for n in model.get_ordered_ops():
+            if n.get_type_name() not in ("TensorIterator", "Loop"):
+                continue
+            at = n.get_attributes()
+            back = list(at.get("back_edges") or [])
+            if not back:
+                continue
+            in_map = list(at.get("input_map") or [])
+            out_map = list(at.get("output_map") or [])
+            for k in range(0, len(back), 2):
+                ridx, pidx = int(back[k]), int(back[k + 1])
+                port = next((int(in_map[j]) for j in range(0, len(in_map), 3) if int(in_map[j + 1]) == pidx and int(in_map[j + 2]) < 0), None)
+                if port is None:
+                    continue
+                init = n.input_value(port)
+                var_id = "%s/variable_%d" % (n.get_friendly_name(), k // 2)
+                if any(s_.get_type_name() == "Assign" and s_.get_attributes().get("variable_id") == var_id for s_ in model.get_sinks()):
+                    continue                                     # already converted
+                ps = init.get_partial_shape()
+                if self.use_const_initializer and ps.is_static:
+                    zeros = np.zeros(list(ps.to_shape()), dtype=init.get_element_type().to_dtype())
+                    start = ops.constant(zeros).output(0)
+                else:
+                    start = init
+                rv = ops.read_value(start, variable_id=var_id, variable_type=init.get_element_type().name, variable_shape=ps)
+                n.input(port).replace_source_output(rv.output(0))
+                # node output that carries the value of the last iteration (added when the model does not expose it)
+                j = next((q // 2 for q in range(0, len(out_map), 2) if int(out_map[q]) == ridx and int(out_map[q + 1]) < 0), None)
+                if j is None:
+                    out_map += [ridx, -1]
+                    n.set_attribute("output_map", [int(v) for v in out_map])
+                    n.validate()
+                    j = len(out_map) // 2 - 1
+                sinks.append(ops.assign(n.output(j), variable_id=var_id))
+                changed = True
+        if changed:
+            model.add_sinks(sinks)
+            model.validate_nodes_and_infer_types()
+        return changed
 
 
 class Serialize(ModelPass):

@@ -263,3 +263,37 @@ def test_visualize_and_serialize_passes(tmp_path):
     pm.run_passes(m)
     assert "digraph" in open(tmp_path / "g.dot").read() and (tmp_path / "m.xml").exists()
     assert "ConstantFolding" in passes.available_passes()
+
+
+def test_low_latency2_makes_recurrent_state_persistent():
+    """A TensorIterator with a back edge accumulates over the sequence; after LowLatency2 the accumulator is model state
+    that survives between inferences until reset_state."""
+    import openvino_b200 as ov
+    from openvino_b200 import opset as ops
+    from openvino_b200.passes import LowLatency2
+    xt = ops.parameter([1, 1, 4], "f32", "xt")
+    h = ops.parameter([1, 4], "f32", "h")
+    hn = ops.add(h, ops.squeeze(xt, np.array([1], dtype=np.int64)))
+    body = ov.Model([ops.result(hn)], [xt, h], "body")
+    x = ops.parameter([1, 3, 4], "f32", "x")
+    h0 = ops.constant(np.full((1, 4), 10.0, np.float32))
+    ti = ops.tensor_iterator()
+    ti.set_body(body)
+    ti.set_sliced_input(xt, x, axis=1)
+    ti.set_merged_input(h, h0, body.get_results()[0])
+    out_idx = ti.get_iter_value(body.get_results()[0])
+    node = ti.build()
+    m = ov.Model([ops.result(node.output(out_idx))], [x], "rnn")
+    data = np.arange(12, dtype=np.float32).reshape(1, 3, 4)
+    np.testing.assert_allclose(ov.compile_model(m.clone(), "CPU")(data)[0], 10.0 + data.sum(1))
+    assert LowLatency2(use_const_initializer=False).run_on_model(m)
+    types = [n.get_type_name() for n in m.get_ops()]
+    assert "ReadValue" in types and len(m.get_sinks()) == 1
+    req = ov.compile_model(m, "CPU").create_infer_request()
+    first = req.infer([data])[0].copy()
+    second = req.infer([data])[0].copy()
+    np.testing.assert_allclose(first, 10.0 + data.sum(1))
+    np.testing.assert_allclose(second, 10.0 + 2 * data.sum(1))          # the state carried over
+    req.reset_state()
+    np.testing.assert_allclose(req.infer([data])[0], 10.0 + data.sum(1))
+    assert not LowLatency2().run_on_model(m)                              # idempotent
