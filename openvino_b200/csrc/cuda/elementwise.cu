@@ -418,6 +418,76 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
     }
 }
 
+// ------------------------------------------------------------------------------------ MoE token grouping (prefill)
+// For every local expert: the indices of the tokens routed to it, in token order, and their number. One CTA per expert
+// walks the tokens in chunks of its size; positions come from a ballot / prefix sum, so the order is deterministic.
+__global__ void moe_group_kernel(const float* __restrict__ route, int T, int E, int e0, int* __restrict__ idx, int* __restrict__ counts, int idx_stride) {
+    const int e = blockIdx.x;
+    __shared__ int warp_sums[32];
+    __shared__ int base_s;
+    if (threadIdx.x == 0) base_s = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int t0 = 0; t0 < T; t0 += blockDim.x) {
+        const int t = t0 + threadIdx.x;
+        const bool hit = t < T && route[(size_t)t * E + e0 + e] != 0.f;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_sums[warp] = __popc(m);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_sums[w];
+        if (hit) idx[(size_t)e * idx_stride + base_s + before + __popc(m & ((1u << lane) - 1u))] = t;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < nwarps; ++w) tot += warp_sums[w];
+            base_s += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = base_s;
+}
+
+// act[i, f] = silu(gu[i, f]) * gu[i, F + f] * route[idx[i], e]  for the gathered rows of one expert
+__global__ void moe_silu_mul_rows_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route, const int* __restrict__ idx,
+                                         __nv_bfloat16* __restrict__ out, int rows, int F, int E, int e) {
+    const int fv = F >> 3;
+    const size_t total = (size_t)rows * fv;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / fv;
+        const int c = int(i - r * fv);
+        const float scale = route[(size_t)idx[r] * E + e];
+        Pack8 g, u, o;
+        const __nv_bfloat16* base = gu + r * 2 * (size_t)F;
+        g.u = reinterpret_cast<const uint4*>(base)[c];
+        u.u = reinterpret_cast<const uint4*>(base + F)[c];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float gv = __bfloat162float(g.b[j]);
+            o.b[j] = __float2bfloat16_rn(gv / (1.0f + __expf(-gv)) * __bfloat162float(u.b[j]) * scale);
+        }
+        reinterpret_cast<uint4*>(out + r * (size_t)F)[c] = o.u;
+    }
+}
+
+// dst[idx[i], :] += src[i, :]; the rows of one expert are distinct tokens, so no two threads touch the same element
+__global__ void moe_scatter_add_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx, __nv_bfloat16* __restrict__ dst,
+                                       int rows, int H, int ld_dst) {
+    const int hv = H >> 3;
+    const size_t total = (size_t)rows * hv;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / hv;
+        const int c = int(i - r * hv);
+        Pack8 a, b;
+        a.u = reinterpret_cast<const uint4*>(src + r * (size_t)H)[c];
+        uint4* d = reinterpret_cast<uint4*>(dst + (size_t)idx[r] * ld_dst) + c;
+        b.u = *d;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) b.b[j] = __float2bfloat16_rn(__bfloat162float(a.b[j]) + __bfloat162float(b.b[j]));
+        *d = b.u;
+    }
+}
+
 // ------------------------------------------------------------------------------------ fp8 activation quantisation
 // Per token and group of 128 channels: scale = amax / 448, q = x / scale as e4m3 (round to nearest even, saturating).
 // One warp per (token, group); a lane holds four channels. Role of the reference's dynamic_quantize_gpu_opt
@@ -626,6 +696,31 @@ int ovb_moe_silu_mul_scale(const void* gu, const float* weights, void* out, int 
     OVB_REQUIRE(gu && weights && out && rows > 0 && F % 8 == 0 && nloc > 0 && e0 >= 0 && e0 + nloc <= E, "ovb_moe_silu_mul_scale: bad arguments");
     const size_t total = (size_t)rows * nloc * (F / 8);
     moe_silu_mul_scale_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, weights, (__nv_bfloat16*)out, rows, F, nloc, E, e0);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_moe_group(const float* route, int T, int E, int e0, int nloc, int* idx, int idx_stride, int* counts, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(route && idx && counts && T > 0 && nloc > 0 && e0 >= 0 && e0 + nloc <= E && idx_stride >= T, "ovb_moe_group: bad arguments");
+    moe_group_kernel<<<nloc, 1024, 0, stream>>>(route, T, E, e0, idx, counts, idx_stride);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_moe_silu_mul_rows(const void* gu, const float* route, const int* idx, void* out, int rows, int F, int E, int e, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(gu && route && idx && out && rows > 0 && F % 8 == 0 && e >= 0 && e < E, "ovb_moe_silu_mul_rows: bad arguments");
+    moe_silu_mul_rows_kernel<<<grid_for((size_t)rows * (F / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, route, idx, (__nv_bfloat16*)out,
+                                                                                      rows, F, E, e);
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_moe_scatter_add(const void* src, const int* idx, void* dst, int rows, int H, int ld_dst, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(src && idx && dst && rows > 0 && H % 8 == 0 && ld_dst % 8 == 0, "ovb_moe_scatter_add: bad arguments");
+    moe_scatter_add_kernel<<<grid_for((size_t)rows * (H / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)src, idx, (__nv_bfloat16*)dst, rows, H, ld_dst);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

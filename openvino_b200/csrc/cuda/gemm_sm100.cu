@@ -61,6 +61,7 @@ struct GemmKParams {
     int stages;               // MMA stages
     int pslots;               // packed ring slots (quantised modes)
     int kblocks_per_split;
+    int w_kb_stride;          // chunks between consecutive weight tiles in memory (total k-blocks unless the weight is a window)
     // Tensor-parallel all-reduce fused into the epilogue (world <= 1: off). Every rank runs the same launch;
     // heap[r] is the symmetric heap of rank r mapped into this process (heap[rank] is local memory).
     int world, rank;
@@ -282,7 +283,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 int wslot = 0;
                 uint32_t wpar = 1;                    // parity to wait for on the "empty" barriers
                 TR(long long tr_t0 = clock64(); long long tr_w = 0;)
-                const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * total_kb + kb_begin) * (WMODE == OVB_W_U4 ? WQ_SLOT : WQ_BYTES);
+                const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * p.w_kb_stride + kb_begin) * (WMODE == OVB_W_U4 ? WQ_SLOT : WQ_BYTES);
                 uint32_t wdst = smem_u32(pring);
                 // u8: pairs come from the [group][N] table with a second copy
                 const int kpg = p.group_size / TILE_K;
@@ -324,7 +325,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     mbar_arrive_expect_tx(&full_x[s], X_BYTES + W_BYTES);
                     tma_load_2d(st, &tmX, &full_x[s], kb * TILE_K, t0);
                     if (p.w_tiled != nullptr)
-                        bulk_load_1d(st + X_BYTES, p.w_tiled + ((size_t)n_tile * total_kb + kb) * W_BYTES, W_BYTES, &full_x[s]);
+                        bulk_load_1d(st + X_BYTES, p.w_tiled + ((size_t)n_tile * p.w_kb_stride + kb) * W_BYTES, W_BYTES, &full_x[s]);
                     else
                         tma_load_2d(st + X_BYTES, &tmW, &full_x[s], kb * TILE_K, n0);
                     if (++s == stages) { s = 0; phase ^= 1; }
@@ -1032,6 +1033,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.act = a->act;
     p.out_f32 = a->out_f32;
     p.splits = splits;
+    p.w_kb_stride = a->w_kb_stride > 0 ? a->w_kb_stride : ceil_div(a->K, TILE_K);
     if (a->comm != nullptr && static_cast<const ovb_comm*>(a->comm)->world > 1) {
         const ovb_comm* c = static_cast<const ovb_comm*>(a->comm);
         OVB_REQUIRE(c->world <= 8 && c->rank >= 0 && c->rank < c->world, "ovb_gemm: bad communicator (rank %d of %d)", c->rank, c->world);

@@ -62,6 +62,9 @@ typedef struct {
     int w_tiled;          // 16-bit weights are in the tile-contiguous layout made by ovb_pack_w16
     // Tensor-parallel: out = residual + sum over ranks of (x * W^T), reduced inside the epilogue (see ovb_comm below).
     void* comm;           // const ovb_comm* or NULL
+    // Window into a larger tile-contiguous weight (experts stacked along N or K): chunks of one 128-row weight tile are
+    // w_kb_stride apart from the next tile's (0 = K / 64, the weight is exactly [N, K]); `w` points at the window's first chunk.
+    int w_kb_stride;
 } ovb_gemm_args;
 
 int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream);
@@ -91,6 +94,11 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
                   int cols, float eps, int is_f16, ovb_stream_t stream);
 // out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
 int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
+/* MoE prefill: token lists per local expert (idx[e * idx_stride + i], counts[e]) from the dense routing matrix route [T, E];
+   SwiGLU of an expert's gathered rows scaled by the routing weight; dst[idx[i]] += src[i]. */
+int ovb_moe_group(const float* route, int T, int E, int e0, int nloc, int* idx, int idx_stride, int* counts, ovb_stream_t stream);
+int ovb_moe_silu_mul_rows(const void* gu, const float* route, const int* idx, void* out, int rows, int F, int E, int e, ovb_stream_t stream);
+int ovb_moe_scatter_add(const void* src, const int* idx, void* dst, int rows, int H, int ld_dst, ovb_stream_t stream);
 /* bf16 [rows, cols] -> fp8 e4m3 bytes with one fp32 scale per row and group of 128 channels (scales [rows, cols/128]). */
 int ovb_act_quant_fp8(const void* x, void* q, float* scales, int rows, int cols, ovb_stream_t stream);
 /* Copy cache blocks src_blocks[i] -> dst_blocks[i] in the key and the value cache (block_bytes per block and cache). */

@@ -34,7 +34,7 @@ class GemmArgs(C.Structure):
         ("ldx", C.c_int), ("ldo", C.c_int), ("ldr", C.c_int),
         ("group_size", C.c_int), ("wmode", C.c_int), ("act", C.c_int), ("out_f32", C.c_int),
         ("splits", C.c_int), ("block_t", C.c_int), ("w_tiled", C.c_int),
-        ("comm", C.c_void_p),
+        ("comm", C.c_void_p), ("w_kb_stride", C.c_int),
     ]
 
 
@@ -142,10 +142,21 @@ class PackedWeight:
     mode W_U8: ``w`` [N, K] u8, the pairs hold the zero point itself.
     """
 
-    def __init__(self, mode, w, N, K, scales=None, zps=None, group_size=0, bias=None, tiled=False):
+    def __init__(self, mode, w, N, K, scales=None, zps=None, group_size=0, bias=None, tiled=False, kb_stride=0):
         self.mode, self.w, self.N, self.K = mode, w, N, K
         self.scales, self.zps, self.group_size, self.bias = scales, zps, group_size, bias
         self.tiled = tiled
+        self.kb_stride = kb_stride     # > 0: this weight is a window into a larger tile-packed one
+
+    def window(self, n0: int, n: int, k0: int = 0, k: Optional[int] = None) -> "PackedWeight":
+        """Rows [n0, n0 + n) and columns [k0, k0 + k) of a tile-packed 16-bit weight as a weight of its own (no copy):
+        one expert of a stack of experts. Offsets and sizes are multiples of the tile (128 rows, 64 columns)."""
+        k = self.K - k0 if k is None else k
+        assert self.tiled and self.mode in (W_BF16, W_F16) and self.bias is None
+        assert n0 % 128 == 0 and n % 128 == 0 and k0 % 64 == 0 and k % 64 == 0 and n0 + n <= self.N and k0 + k <= self.K
+        stride = self.kb_stride or self.K // 64
+        first_chunk = (n0 // 128) * stride + k0 // 64
+        return PackedWeight(self.mode, self.w[first_chunk * 8192:], n, k, tiled=True, kb_stride=stride)
 
     @staticmethod
     def from_dense(w: torch.Tensor, bias=None, tiled: bool = True) -> "PackedWeight":
@@ -235,6 +246,7 @@ def gemm(x: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None, r
     a.group_size = w.group_size
     a.wmode, a.act, a.out_f32 = w.mode, act, 1 if out_f32 else 0
     a.splits, a.block_t = splits, block_t
+    a.w_kb_stride = int(getattr(w, "kb_stride", 0) or 0)
     a.w_tiled = 1 if (w.tiled and w.mode in (W_BF16, W_F16)) else 0
     a.comm = C.addressof(comm) if comm is not None else None
     _check(lib().ovb_gemm(C.byref(a), C.c_void_p(_stream())), "ovb_gemm")
@@ -373,6 +385,26 @@ def moe_silu_mul_scale(gu: torch.Tensor, weights: torch.Tensor, F: int, nloc: in
     _check(lib().ovb_moe_silu_mul_scale(C.c_void_p(gu.data_ptr()), C.c_void_p(weights.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(rows),
                                         C.c_int(F), C.c_int(nloc), C.c_int(E), C.c_int(e0), C.c_void_p(_stream())), "ovb_moe_silu_mul_scale")
     return out
+
+
+def moe_group(route: torch.Tensor, e0: int, nloc: int, idx: torch.Tensor, counts: torch.Tensor) -> None:
+    """Token lists of the local experts e0 .. e0+nloc-1: idx [nloc, >=T] int32 (token order), counts [nloc] int32."""
+    T, E = route.shape
+    _check(lib().ovb_moe_group(C.c_void_p(route.data_ptr()), C.c_int(T), C.c_int(E), C.c_int(e0), C.c_int(nloc), C.c_void_p(idx.data_ptr()),
+                               C.c_int(idx.stride(0)), C.c_void_p(counts.data_ptr()), C.c_void_p(_stream())), "ovb_moe_group")
+
+
+def moe_silu_mul_rows(gu: torch.Tensor, route: torch.Tensor, idx: torch.Tensor, e: int, out: torch.Tensor) -> torch.Tensor:
+    rows, F2 = gu.shape
+    _check(lib().ovb_moe_silu_mul_rows(C.c_void_p(gu.data_ptr()), C.c_void_p(route.data_ptr()), C.c_void_p(idx.data_ptr()), C.c_void_p(out.data_ptr()),
+                                       C.c_int(rows), C.c_int(F2 // 2), C.c_int(route.shape[1]), C.c_int(e), C.c_void_p(_stream())), "ovb_moe_silu_mul_rows")
+    return out
+
+
+def moe_scatter_add(src: torch.Tensor, idx: torch.Tensor, dst: torch.Tensor) -> None:
+    rows, H = src.shape
+    _check(lib().ovb_moe_scatter_add(C.c_void_p(src.data_ptr()), C.c_void_p(idx.data_ptr()), C.c_void_p(dst.data_ptr()), C.c_int(rows), C.c_int(H),
+                                     C.c_int(dst.stride(0)), C.c_void_p(_stream())), "ovb_moe_scatter_add")
 
 
 def add(a, b, out=None):

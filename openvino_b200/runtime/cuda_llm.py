@@ -157,6 +157,10 @@ class LlmWeights:
 
 
 # ----------------------------------------------------------------------------------------- step buffers
+# Batches of at least this many tokens gather the tokens of every expert instead of running every expert on every token.
+MOE_GATHER_MIN_TOKENS = 1024
+
+
 class StepBuffers:
     """Static device buffers of one shape bucket: the packed int32 step descriptor plus activations.
 
@@ -194,6 +198,15 @@ class StepBuffers:
             self.act = torch.empty((Tcap, nloc * cfg.ffn_size), **bf)
             self.router_logits = torch.empty((Tcap, cfg.num_experts), dtype=torch.float32, device=device)
             self.route = torch.empty((Tcap, cfg.num_experts), dtype=torch.float32, device=device)
+            # prefill-sized batches run every expert on its own tokens only (gathered rows); see _moe_gathered
+            self.moe_gather = Tcap >= MOE_GATHER_MIN_TOKENS
+            if self.moe_gather:
+                self.xg = torch.empty((Tcap, H), **bf)
+                self.gug = torch.empty((Tcap, 2 * cfg.ffn_size), **bf)
+                self.actg = torch.empty((Tcap, cfg.ffn_size), **bf)
+                self.outg = torch.empty((Tcap, H), **bf)
+                self.moe_idx = torch.zeros((nloc, Tcap), dtype=torch.int32, device=device)
+                self.moe_counts = torch.zeros(nloc, dtype=torch.int32, device=device)
         else:
             self.gu = torch.empty((Tcap, 2 * ffn), **bf)
             self.act = torch.empty((Tcap, ffn), **bf)
@@ -251,6 +264,7 @@ class CudaLlmExecutor:
         # token sampled last for every request slot (device-side feedback between chained steps)
         self.last_token = torch.zeros(max(max_seqs, 1) * 4, dtype=torch.int32, device=self.device)
         self._graphs = {}
+        self._expert_windows = {}
         self.kernel_launches = 0
         # sampling: None = greedy; (temperature, top_k, top_p, seed) = stochastic (single-rank only). The step word is
         # bumped on the device before every draw, so replays of a captured decode graph keep drawing fresh numbers.
@@ -299,6 +313,11 @@ class CudaLlmExecutor:
                 nloc = cfg.num_experts // self.tp_size
                 K.gemm(x, lw.router, out=sb.router_logits[:T], out_f32=True, ws=ws)
                 K.moe_route_topk(sb.router_logits[:T], cfg.experts_top_k, out=sb.route[:T])
+                if (self.tp_size == 1 and getattr(sb, "moe_gather", False) and T >= MOE_GATHER_MIN_TOKENS and shp.max_q_len > 1
+                        and lw.gate_up.tiled and lw.gate_up.mode == K.W_BF16 and lw.down.tiled):
+                    n += self._moe_gathered(sb, l, T, x, h)
+                    n += 7
+                    continue
                 K.gemm(x, lw.gate_up, out=gu, ws=ws)
                 K.moe_silu_mul_scale(gu, sb.route[:T], cfg.ffn_size, nloc, self.tp_rank * nloc, out=act)
                 n += 2
@@ -315,6 +334,34 @@ class CudaLlmExecutor:
         K.gemm(last_x, w.lm_head, out=logits, ws=ws)
         self._sample(sb, B)
         self.kernel_launches += n + 5
+
+    def _moe_gathered(self, sb: StepBuffers, l: int, T: int, x: torch.Tensor, h: torch.Tensor) -> int:
+        """Experts on their own tokens only (prefill-sized batches): the routed tokens of every expert are listed on the
+        device, gathered, run through that expert's window of the stacked weights, and the weighted results are added
+        back into the residual stream. Top-2 of 8 experts does a quarter of the dense-masked work. One host read per
+        layer (the token counts) sizes the GEMMs. Returns the number of kernel launches."""
+        cfg = self.cfg
+        F, H, E = cfg.ffn_size, cfg.hidden_size, cfg.num_experts
+        wins = self._expert_windows.get(l)
+        if wins is None:
+            lw = self.w.layers[l]
+            wins = [(lw.gate_up.window(j * 2 * F, 2 * F), lw.down.window(0, H, j * F, F)) for j in range(E)]
+            self._expert_windows[l] = wins
+        K.moe_group(sb.route[:T], 0, E, sb.moe_idx, sb.moe_counts)
+        counts = sb.moe_counts.tolist()
+        launches = 1
+        for j, cnt in enumerate(counts):
+            if cnt == 0:
+                continue
+            idx = sb.moe_idx[j, :cnt]
+            xg, gug, actg, outg = sb.xg[:cnt], sb.gug[:cnt], sb.actg[:cnt], sb.outg[:cnt]
+            K.embedding(idx, x, out=xg)                                  # row gather
+            K.gemm(xg, wins[j][0], out=gug, ws=self.ws)
+            K.moe_silu_mul_rows(gug, sb.route[:T], idx, j, out=actg)
+            K.gemm(actg, wins[j][1], out=outg, ws=self.ws)
+            K.moe_scatter_add(outg, idx, h)
+            launches += 5
+        return launches
 
     def _row_parallel(self, x: torch.Tensor, wt: K.PackedWeight, h: torch.Tensor, site: int) -> None:
         """h += x @ W^T summed over tensor-parallel ranks (h is the replicated residual stream)."""

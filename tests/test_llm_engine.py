@@ -5,8 +5,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("fmt", ["bf16", "int4", "moe"])
-def test_tiny_llama_generate_matches_reference(fmt):
+@pytest.mark.parametrize("fmt", ["bf16", "int4", "moe", "moe-gather"])
+def test_tiny_llama_generate_matches_reference(fmt, monkeypatch):
     from openvino_b200.genai.pipeline import ContinuousBatchingPipeline, GenerationConfig
     from openvino_b200.genai.scheduler import SchedulerConfig
     from openvino_b200.models import llama
@@ -14,7 +14,11 @@ def test_tiny_llama_generate_matches_reference(fmt):
     from openvino_b200.ops import cuda as K
     from openvino_b200.runtime.cuda_llm import CudaLlmExecutor, LlmWeights, StepShape
 
-    cfg = TINY_MOE if fmt == "moe" else TINY_LLAMA.with_(weight_format=fmt)
+    if fmt == "moe-gather":
+        # prefill batches take the path that runs every expert on its own (gathered) tokens only
+        from openvino_b200.runtime import cuda_llm
+        monkeypatch.setattr(cuda_llm, "MOE_GATHER_MIN_TOKENS", 8)
+    cfg = TINY_MOE if fmt.startswith("moe") else TINY_LLAMA.with_(weight_format=fmt)
     state = llama.random_float_state(cfg, seed=3, std=0.05)
     eff = {k: v.cuda() for k, v in llama.effective_state(cfg, state).items()}
     w = LlmWeights.from_float(cfg, state, "cuda")
