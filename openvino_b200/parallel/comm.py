@@ -76,7 +76,7 @@ class PeerCommunicator:
     def setup(self, hidden: int, max_tokens: int, num_layers: int, tensor_bytes: int) -> None:
         """Allocate this rank's heap, exchange IPC handles, map every peer. Call on all ranks with equal arguments."""
         import torch.distributed as dist
-        num_sites = 2 * num_layers + 2          # two fused GEMMs per layer, argmax, generic all-reduce
+        num_sites = 2 * num_layers + 3          # two fused GEMMs per layer, argmax, two alternating all-reduce sites
         self.layout = HeapLayout(self.world, hidden, max_tokens, num_sites, tensor_bytes)
         lib = K.lib()
         self._declare(lib)
@@ -165,7 +165,7 @@ class PeerCommunicator:
         K.gemm(x, w, out=h, residual=h, ws=ws, comm=self.struct(site, mode))
 
     def argmax_combine(self, ids: torch.Tensor, max_vals: torch.Tensor, shard_size: int) -> None:
-        site = self.layout.num_sites - 2
+        site = self.layout.num_sites - 3
         K._check(K.lib().ovb_comm_argmax_combine(C.byref(self.struct(site)), C.c_void_p(ids.data_ptr()), C.c_void_p(max_vals.data_ptr()),
                                                  C.c_int(ids.numel()), C.c_int(shard_size), C.c_void_p(K._stream())), "ovb_comm_argmax_combine")
 
@@ -174,6 +174,28 @@ class PeerCommunicator:
         site = self.layout.num_sites - 1
         K._check(K.lib().ovb_comm_allreduce_bf16(C.byref(self.struct(site)), C.c_void_p(t.data_ptr()), C.c_int64(t.numel()),
                                                  C.c_void_p(K._stream())), "ovb_comm_allreduce_bf16")
+
+    def all_reduce_large(self, t: torch.Tensor) -> int:
+        """Sum a heap tensor of any size over the ranks, in pieces that fit the one-shot staging area. Every piece gets
+        a step number of its own (the flags of a call site hold step numbers) and the pieces alternate between two call
+        sites, i.e. between the two staging buffers: a rank that runs ahead writes into the buffer its peers are not
+        reading. A last bump keeps later users of the step number apart from these flags. Returns the launches made."""
+        assert t.dtype == torch.bfloat16 and t.is_contiguous() and self.in_heap(t)
+        L = self.layout
+        max_elems = (((L.stage1_bytes // self.world) & ~15) // 2) & ~7
+        flat = t.view(-1)
+        n, i, k = flat.numel(), 0, 0
+        lib = K.lib()
+        while i < n:
+            m = min(max_elems, n - i)
+            self.step_begin()
+            site = L.num_sites - 1 - (k & 1)
+            K._check(lib.ovb_comm_allreduce_bf16(C.byref(self.struct(site)), C.c_void_p(flat[i:i + m].data_ptr()), C.c_int64(m),
+                                                 C.c_void_p(K._stream())), "ovb_comm_allreduce_bf16")
+            i += m
+            k += 1
+        self.step_begin()
+        return 2 * k + 1
 
 
 class _DeviceMemory:

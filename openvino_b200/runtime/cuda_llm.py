@@ -205,6 +205,8 @@ class StepBuffers:
                 self.gug = torch.empty((Tcap, 2 * cfg.ffn_size), **bf)
                 self.actg = torch.empty((Tcap, cfg.ffn_size), **bf)
                 self.outg = torch.empty((Tcap, H), **bf)
+                # expert parallel: the local experts' contributions are summed over the ranks (symmetric heap)
+                self.moe_out = comm.alloc((Tcap, H)) if comm is not None else None
                 self.moe_idx = torch.zeros((nloc, Tcap), dtype=torch.int32, device=device)
                 self.moe_counts = torch.zeros(nloc, dtype=torch.int32, device=device)
         else:
@@ -258,7 +260,9 @@ class CudaLlmExecutor:
         if self.tp_size > 1:
             if comm is None:
                 raise ValueError("tensor-parallel weights need a communicator")
-            comm.setup(cfg.hidden_size, max_batch_tokens, cfg.num_layers, tensor_bytes=(max_batch_tokens + max_seqs + 2) * cfg.hidden_size * 2 + 4096)
+            moe_rows = max_batch_tokens + 1 if (cfg.num_experts and max_batch_tokens >= MOE_GATHER_MIN_TOKENS) else 0
+            comm.setup(cfg.hidden_size, max_batch_tokens, cfg.num_layers,
+                       tensor_bytes=(max_batch_tokens + max_seqs + 2 + moe_rows) * cfg.hidden_size * 2 + 8192)
         self.prefill = StepBuffers(cfg, max_batch_tokens, max_seqs, max_blocks_per_seq, self.device, self.tp_size, comm if self.tp_size > 1 else None)
         self.decode = StepBuffers(cfg, max_seqs, max_seqs, max_blocks_per_seq, self.device, self.tp_size, comm if self.tp_size > 1 else None)
         # token sampled last for every request slot (device-side feedback between chained steps)
@@ -313,7 +317,7 @@ class CudaLlmExecutor:
                 nloc = cfg.num_experts // self.tp_size
                 K.gemm(x, lw.router, out=sb.router_logits[:T], out_f32=True, ws=ws)
                 K.moe_route_topk(sb.router_logits[:T], cfg.experts_top_k, out=sb.route[:T])
-                if (self.tp_size == 1 and getattr(sb, "moe_gather", False) and T >= MOE_GATHER_MIN_TOKENS and shp.max_q_len > 1
+                if (getattr(sb, "moe_gather", False) and T >= MOE_GATHER_MIN_TOKENS and shp.max_q_len > 1
                         and lw.gate_up.tiled and lw.gate_up.mode == K.W_BF16 and lw.down.tiled):
                     n += self._moe_gathered(sb, l, T, x, h)
                     n += 7
@@ -341,15 +345,22 @@ class CudaLlmExecutor:
         back into the residual stream. Top-2 of 8 experts does a quarter of the dense-masked work. One host read per
         layer (the token counts) sizes the GEMMs. Returns the number of kernel launches."""
         cfg = self.cfg
-        F, H, E = cfg.ffn_size, cfg.hidden_size, cfg.num_experts
+        F, H = cfg.ffn_size, cfg.hidden_size
+        nloc = cfg.num_experts // self.tp_size
+        e0 = self.tp_rank * nloc
         wins = self._expert_windows.get(l)
         if wins is None:
             lw = self.w.layers[l]
-            wins = [(lw.gate_up.window(j * 2 * F, 2 * F), lw.down.window(0, H, j * F, F)) for j in range(E)]
+            wins = [(lw.gate_up.window(j * 2 * F, 2 * F), lw.down.window(0, H, j * F, F)) for j in range(nloc)]
             self._expert_windows[l] = wins
-        K.moe_group(sb.route[:T], 0, E, sb.moe_idx, sb.moe_counts)
+        K.moe_group(sb.route[:T], e0, nloc, sb.moe_idx, sb.moe_counts)
         counts = sb.moe_counts.tolist()
         launches = 1
+        # expert parallel: every rank adds its experts' results into a zeroed buffer, the buffers are summed over the ranks
+        dst = h
+        if self.tp_size > 1:
+            dst = sb.moe_out[:T]
+            dst.zero_()
         for j, cnt in enumerate(counts):
             if cnt == 0:
                 continue
@@ -357,10 +368,14 @@ class CudaLlmExecutor:
             xg, gug, actg, outg = sb.xg[:cnt], sb.gug[:cnt], sb.actg[:cnt], sb.outg[:cnt]
             K.embedding(idx, x, out=xg)                                  # row gather
             K.gemm(xg, wins[j][0], out=gug, ws=self.ws)
-            K.moe_silu_mul_rows(gug, sb.route[:T], idx, j, out=actg)
+            K.moe_silu_mul_rows(gug, sb.route[:T], idx, e0 + j, out=actg)
             K.gemm(actg, wins[j][1], out=outg, ws=self.ws)
-            K.moe_scatter_add(outg, idx, h)
+            K.moe_scatter_add(outg, idx, dst)
             launches += 5
+        if self.tp_size > 1:
+            launches += self.comm.all_reduce_large(dst)
+            K.add(h, dst, out=h)
+            launches += 2
         return launches
 
     def _row_parallel(self, x: torch.Tensor, wt: K.PackedWeight, h: torch.Tensor, site: int) -> None:

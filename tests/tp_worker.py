@@ -133,6 +133,10 @@ def main():
     from openvino_b200.models.llm_config import TINY_MOE
     mcfg = TINY_MOE.with_(num_heads=8, num_kv_heads=world if world > 2 else 2, num_experts=4 if world <= 4 else 8)
     mstate = llama.random_float_state(mcfg, seed=4)
+    # prefill steps take the gathered-token path (experts on their own tokens, contributions summed over the ranks in
+    # pieces), decode steps the dense-masked path with the fused all-reduce
+    from openvino_b200.runtime import cuda_llm
+    cuda_llm.MOE_GATHER_MIN_TOKENS = 8
     moe_comm = PeerCommunicator(rank, world, dev)
     mex = CudaLlmExecutor(mcfg, LlmWeights.from_float(mcfg, mstate, dev, tp_rank=rank, tp_size=world), num_kv_blocks=64, block_size=16,
                           max_batch_tokens=256, max_seqs=4, max_blocks_per_seq=12, device=dev, comm=moe_comm)
