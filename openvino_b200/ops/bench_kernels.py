@@ -1,7 +1,8 @@
 """Kernel micro-benchmarks with roofline fractions: ``python -m openvino_b200.ops.bench_kernels <kernel> [options]``.
 
 Kernels: ``gemm`` (tcgen05 GEMM, bf16 or int4/int8 weights; ``--cublas`` adds the library GEMM for comparison),
-``attention`` (paged decode or prefill), ``rmsnorm``. Every timed launch is preceded by an L2 flush (a 256 MB read),
+``attention`` (paged decode or prefill), ``rmsnorm``, ``rope`` (RoPE + KV-cache write), ``silu`` (SwiGLU gate),
+``sample`` (top-k / top-p and perturbed arg-max), ``conv`` (im2col + GEMM). Every timed launch is preceded by an L2 flush (a 256 MB read),
 timed with CUDA events on the launching stream after warm-up; the median is reported together with achieved
 bandwidth / throughput and, when ``MEASURED_PEAKS.json`` sits in the working directory, the fraction of the measured
 peaks. ``--iters`` small (3-5) gives a run suited to a profiler capture.
@@ -103,9 +104,55 @@ def bench_rmsnorm(a) -> dict:
     return {"kernel": "rmsnorm", "rows": a.T, "cols": a.N, "ms": ms, "gbs": 2 * x.numel() * 2 / ms / 1e6}
 
 
+def bench_rope(a) -> dict:
+    """RoPE of q/k in place + write of k/v into the paged cache for T tokens (Llama-3-8B head layout by default)."""
+    from . import cuda as K
+    T, Hq, Hkv, D, bs = a.T, a.Hq, a.Hkv, 128, 16
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").to(torch.bfloat16)
+    nblk = (T + bs - 1) // bs + 1
+    kc = torch.zeros(nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    pos = torch.arange(T, dtype=torch.int32, device="cuda") + 1000
+    slots = torch.arange(T, dtype=torch.int32, device="cuda")
+    ms = timeit(lambda: K.rope_kv_write(qkv, pos, slots, kc, vc, Hq, Hkv, D, 500000.0, bs), a.iters, a.warmup)
+    bytes_ = T * (Hq + Hkv) * D * 2 * 2 + T * Hkv * D * 2 * 2          # q, k read + written; v read + written
+    return {"kernel": "rope_kv_write", "T": T, "Hq": Hq, "Hkv": Hkv, "ms": ms, "gbs": bytes_ / ms / 1e6}
+
+
+def bench_silu(a) -> dict:
+    from . import cuda as K
+    gu = torch.randn(a.T, 2 * a.N, device="cuda").to(torch.bfloat16)
+    out = torch.empty(a.T, a.N, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: K.silu_mul(gu, out=out), a.iters, a.warmup)
+    return {"kernel": "silu_mul", "rows": a.T, "F": a.N, "ms": ms, "gbs": 3 * a.T * a.N * 2 / ms / 1e6}
+
+
+def bench_sample(a) -> dict:
+    from . import cuda as K
+    logits = (torch.randn(a.T, a.N, device="cuda") * 3).to(torch.bfloat16)
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty(a.T, dtype=torch.int32, device="cuda")
+    ms = timeit(lambda: K.sample(logits, 0.8, 50, 0.9, 1, step, out=out), a.iters, a.warmup)
+    ms_g = timeit(lambda: K.sample_gumbel(logits, 0.8, 1, step, out=out), a.iters, a.warmup)
+    return {"kernel": "sample(top-k 50, top-p 0.9)", "rows": a.T, "vocab": a.N, "ms": ms, "gbs": a.T * a.N * 2 / ms / 1e6, "gumbel_ms": ms_g}
+
+
+def bench_im2col(a) -> dict:
+    """3x3 stride-1 convolution operand of a B x C x H x W image (H = W = --K)."""
+    from . import cuda as K
+    B, Cc, H = a.B, a.N, a.K
+    x = torch.randn(B, Cc, H, H, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(Cc, Cc, 3, 3, device="cuda") * 0.05).to(torch.bfloat16)
+    pw = K.pack_conv_weight(w)
+    ms = timeit(lambda: K.conv2d(x, pw, [3, 3], [1, 1], [1, 1], [1, 1], [1, 1]), a.iters, a.warmup)
+    flops = 2.0 * B * H * H * Cc * Cc * 9
+    return {"kernel": "conv2d 3x3 (im2col + gemm)", "B": B, "C": Cc, "HW": H, "ms": ms, "tflops": flops / ms / 1e9,
+            "gbs": (B * H * H * pw.K * 2 * 2 + x.numel() * 2) / ms / 1e6}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "rope", "silu", "sample", "conv"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -120,7 +167,8 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
-    r = {"gemm": bench_gemm, "attention": bench_attention, "rmsnorm": bench_rmsnorm}[a.kernel](a)
+    r = {"gemm": bench_gemm, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "rope": bench_rope, "silu": bench_silu,
+         "sample": bench_sample, "conv": bench_im2col}[a.kernel](a)
     pk = _peaks()
     if pk["hbm_gbs"]:
         r["frac_of_%s_hbm" % pk["source"]] = r["gbs"] / pk["hbm_gbs"]
