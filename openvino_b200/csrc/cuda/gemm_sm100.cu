@@ -690,6 +690,26 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (comm && p.splits == 1) {
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
             if (acc_ok) comm_epilogue();   // acc_ok is uniform over the epilogue threads
+        } else if (fast && p.act == OVB_ACT_SWIGLU) {
+            // Gated MLP: the tile holds 64 "gate" rows followed by the 64 "up" rows of the same channels (the packer
+            // interleaves them per tile), so out[tok, 64 * tile + c] = silu(gate_c) * up_c needs this tile only.
+            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+            if (acc_ok) {
+                constexpr int PIECES = BT * (TILE_N / 16);    // 16-byte pieces of the 64 output channels
+                const int ntok = min(BT, p.T - t0);
+                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                    const int col = i >> 3, pc = i & 7;
+                    if (col < ntok) {
+                        const float* g = stage_out + col * TILE_N + pc * 8;
+                        const float* u = g + TILE_N / 2;
+                        uint4 v;
+                        E* ve = reinterpret_cast<E*>(&v);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) ve[j] = from_float<E>(g[j] / (1.0f + __expf(-g[j])) * u[j]);
+                        *reinterpret_cast<uint4*>(reinterpret_cast<E*>(p.out) + (size_t)(t0 + col) * p.ldo + n_tile * (TILE_N / 2) + pc * 8) = v;
+                    }
+                }
+            }
         } else if (fast) {
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
             if (acc_ok) {
@@ -1011,10 +1031,17 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         OVB_REQUIRE(a->N % 4 == 0 && (reinterpret_cast<uintptr_t>(a->scales) & 15) == 0,
                     "ovb_gemm: quantised weights need N %% 4 == 0 and a 16-byte aligned (scale, zero point) table");
     }
-    OVB_REQUIRE(a->act != OVB_ACT_SWIGLU, "ovb_gemm: SWIGLU epilogue is provided by ovb_silu_mul");
+    const bool swiglu = a->act == OVB_ACT_SWIGLU;
+    if (swiglu) {
+        // fused gated MLP: W rows are interleaved per 128-row tile (64 gate rows, then the 64 up rows of the same channels)
+        OVB_REQUIRE(a->N % TILE_N == 0 && !a->out_f32 && a->residual == nullptr && a->comm == nullptr && a->bias == nullptr,
+                    "ovb_gemm: the SWIGLU epilogue needs N %% 128 == 0, a 16-bit output and no bias / residual / communicator");
+        OVB_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && (a->ldo ? a->ldo : a->N / 2) % 8 == 0,
+                    "ovb_gemm: the SWIGLU epilogue needs a 16-byte aligned output with a row pitch that is a multiple of 8");
+    }
 
     const int bt = a->block_t ? a->block_t : pick_block_t(a->T);
-    const int splits = a->splits;   // 0: chosen at launch, where the kernel variant and its cluster occupancy are known
+    const int splits = swiglu ? 1 : a->splits;   // 0: chosen at launch, where the kernel variant and its cluster occupancy are known
     const int64_t tiles = (int64_t)ceil_div(a->N, TILE_N) * ceil_div(a->T, bt);
 
     GemmKParams p;
@@ -1027,7 +1054,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.counters = a->counters;
     p.status = status_word();
     p.T = a->T; p.N = a->N; p.K = a->K;
-    p.ldo = a->ldo ? a->ldo : a->N;
+    p.ldo = a->ldo ? a->ldo : (swiglu ? a->N / 2 : a->N);
     p.ldr = a->ldr ? a->ldr : a->N;
     p.group_size = quant ? a->group_size : a->K;
     p.act = a->act;

@@ -36,7 +36,8 @@ enum {
     OVB_ACT_GELU_ERF = 1,
     OVB_ACT_RELU = 2,
     OVB_ACT_SILU = 3,
-    OVB_ACT_SWIGLU = 4,   // dual GEMM: rows [0,N) of W are "gate", rows [N,2N) are "up"; out = silu(g)*u
+    OVB_ACT_SWIGLU = 4,   // gated MLP: every 128-row tile of W holds 64 "gate" rows, then the 64 "up" rows of the same channels;
+                          // out [T, N/2] = silu(gate) * up
     OVB_ACT_GELU_TANH = 5,
 };
 

@@ -231,7 +231,7 @@ def gemm(x: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None, r
     T, K = x.shape
     assert K == w.K, (K, w.K)
     if out is None:
-        out = torch.empty((T, w.N), dtype=torch.float32 if out_f32 else x.dtype, device=x.device)
+        out = torch.empty((T, w.N // 2 if act == ACT_SWIGLU else w.N), dtype=torch.float32 if out_f32 else x.dtype, device=x.device)
     if ws is None:
         ws = default_workspace(x.device)
     a = GemmArgs()
@@ -309,6 +309,14 @@ def lora_apply(x: torch.Tensor, a: "PackedWeight", b: "PackedWeight", y: torch.T
     if alpha != 1.0:
         h = h * alpha
     return gemm(h, b, residual=y)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[F, K] gate and up projections -> [2F, K] in the row order of the fused SwiGLU epilogue (``ACT_SWIGLU``): every
+    128-row tile holds 64 gate rows followed by the 64 up rows of the same channels. F must be a multiple of 64."""
+    F, Kd = gate.shape
+    assert up.shape == gate.shape and F % 64 == 0
+    return torch.stack([gate.reshape(F // 64, 64, Kd), up.reshape(F // 64, 64, Kd)], dim=1).reshape(2 * F, Kd)
 
 
 def sample_gumbel(logits: torch.Tensor, temperature: float, seed: int = 0, step: Optional[torch.Tensor] = None, vocab_offset: int = 0,

@@ -101,6 +101,7 @@ class LlmWeights:
                 norm2=ones())
             if cfg.num_experts == 0:
                 lw.gate_up = LlmWeights._random_packed(2 * ffn, H, cfg, device, s + 3)
+                lw.gate_up.swiglu = ffn % 64 == 0 and lw.gate_up.bias is None     # random rows: any row order is a valid interleaving
                 lw.down = LlmWeights._random_packed(H, ffn, cfg, device, s + 4)
             else:
                 # expert parallel: a rank holds whole experts (nloc of them), attention stays tensor parallel
@@ -143,6 +144,9 @@ class LlmWeights:
                 gate = state[p + "gate_proj"][r * ffn:(r + 1) * ffn]
                 up = state[p + "up_proj"][r * ffn:(r + 1) * ffn]
                 down = state[p + "down_proj"][:, r * ffn:(r + 1) * ffn]
+            fused_gate = cfg.num_experts == 0 and ffn % 64 == 0
+            if fused_gate:          # row order of the GEMM's fused SwiGLU epilogue
+                gate, up = K.interleave_gate_up(gate, up), gate[:0]
             layers.append(LayerWeights(router=router,
                 norm1=dev(state[p + "input_layernorm"]).to(torch.bfloat16),
                 qkv=LlmWeights._pack(dev(torch.cat([q, k, v], 0)).contiguous(), cfg),
@@ -150,6 +154,7 @@ class LlmWeights:
                 norm2=dev(state[p + "post_attention_layernorm"]).to(torch.bfloat16),
                 gate_up=LlmWeights._pack(dev(torch.cat([gate, up], 0)).contiguous(), cfg),
                 down=LlmWeights._pack(dev(down).contiguous(), cfg)))
+            layers[-1].gate_up.swiglu = fused_gate
         vshard = cfg.vocab_size // tp_size
         lm = state["lm_head"][r * vshard:(r + 1) * vshard]
         return LlmWeights(dev(state["embed_tokens"]).to(torch.bfloat16), layers, dev(state["norm"]).to(torch.bfloat16),
@@ -325,6 +330,9 @@ class CudaLlmExecutor:
                 K.gemm(x, lw.gate_up, out=gu, ws=ws)
                 K.moe_silu_mul_scale(gu, sb.route[:T], cfg.ffn_size, nloc, self.tp_rank * nloc, out=act)
                 n += 2
+            elif getattr(lw.gate_up, "swiglu", False):
+                K.gemm(x, lw.gate_up, out=act, act=K.ACT_SWIGLU, ws=ws)       # silu(gate) * up in the GEMM epilogue
+                n -= 1
             else:
                 K.gemm(x, lw.gate_up, out=gu, ws=ws)
                 K.silu_mul(gu, out=act)

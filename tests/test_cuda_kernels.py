@@ -105,6 +105,30 @@ def test_conv2d_im2col_gemm(ops, B, C, H, W, O, k, stride, pad, dil):
     assert _rel_err(y, ref) < 1e-2
 
 
+@pytest.mark.parametrize("T,wmode", [(48, "bf16"), (300, "bf16"), (64, "u4"), (1000, "u4")])
+def test_gemm_fused_swiglu(ops, T, wmode):
+    from openvino_b200.utils import quant
+    torch.manual_seed(9)
+    F, K = 384, 512
+    gate = torch.randn(F, K, device="cuda") * 0.05
+    up = torch.randn(F, K, device="cuda") * 0.05
+    w = ops.interleave_gate_up(gate, up)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    if wmode == "bf16":
+        pw = ops.PackedWeight.from_dense(w.to(torch.bfloat16))
+        gq, uq = gate.to(torch.bfloat16).float(), up.to(torch.bfloat16).float()
+    else:
+        q, s, z = quant.quantize_u4_asym(w, 128)
+        pw = ops.PackedWeight.from_ir_u4(quant.pack_u4(q), s, quant.pack_u4(z), 2 * F, K, 128)
+        wd = quant.dequantize_u4(q, s, z, 128).float().reshape(F // 64, 2, 64, K)
+        gq, uq = wd[:, 0].reshape(F, K), wd[:, 1].reshape(F, K)
+    y = ops.gemm(x, pw, act=ops.ACT_SWIGLU)
+    ops.check_status("gemm swiglu")
+    assert list(y.shape) == [T, F]
+    ref = torch.nn.functional.silu(x.float() @ gq.t()) * (x.float() @ uq.t())
+    assert _rel_err(y, ref) < 2e-2
+
+
 def test_gumbel_sampling_matches_softmax_and_shards_agree(ops):
     torch.manual_seed(8)
     V = 512
