@@ -62,7 +62,7 @@ def bench_gemm(a) -> dict:
         packed, s, z = quant.random_u4_weight(N, Kd, a.group, "cuda")
         pw = K.PackedWeight.from_ir_u4(packed, s, quant.pack_u4(z), N, Kd, a.group)
         wbytes = N * Kd // 2 + (N * Kd // a.group) * 4
-    ms = timeit(lambda: K.gemm(x, pw, out=out), a.iters, a.warmup)
+    ms = timeit(lambda: K.gemm(x, pw, out=out, block_t=a.block_t), a.iters, a.warmup)
     K.check_status("gemm")
     flops = 2.0 * T * N * Kd
     bytes_ = wbytes + T * Kd * 2 + T * N * 2
@@ -159,6 +159,7 @@ def main() -> int:
     ap.add_argument("--wmode", default="u4", choices=["u4", "bf16"])
     ap.add_argument("--group", type=int, default=128)
     ap.add_argument("--cublas", action="store_true")
+    ap.add_argument("--block-t", dest="block_t", type=int, default=0, help="token tile of the GEMM (0 = automatic)")
     ap.add_argument("--B", type=int, default=64)
     ap.add_argument("--ctx", type=int, default=1152)
     ap.add_argument("--q-len", dest="q_len", type=int, default=1)
