@@ -49,6 +49,22 @@ class PipelineMetrics:
     generated_tokens: int = 0
     preemptions: int = 0
 
+    def report(self, results=None, kv_blocks_total: int = 0, kv_blocks_free: int = 0) -> dict:
+        """Serving counters as one JSON-able dict; with the ``GenerationResult`` list of a ``generate`` call also the
+        time-to-first-token / time-per-output-token percentiles (milliseconds)."""
+        out = {k: getattr(self, k) for k in ("steps", "prefill_steps", "decode_steps", "h2d_bytes", "d2h_bytes", "scheduled_tokens",
+                                             "generated_tokens", "preemptions")}
+        if kv_blocks_total:
+            out["kv_block_utilisation"] = 1.0 - kv_blocks_free / float(kv_blocks_total)
+        if results:
+            import numpy as _np
+            ttft = _np.array([r.ttft_s for r in results]) * 1e3
+            tpot = _np.array([r.tpot_s for r in results if r.tpot_s > 0]) * 1e3
+            out["ttft_ms"] = {p: float(_np.percentile(ttft, q)) for p, q in (("p50", 50), ("p90", 90), ("p99", 99))}
+            if tpot.size:
+                out["tpot_ms"] = {p: float(_np.percentile(tpot, q)) for p, q in (("p50", 50), ("p90", 90), ("p99", 99))}
+        return out
+
 
 @dataclass
 class StepPlan:
@@ -57,6 +73,8 @@ class StepPlan:
     prompt_tokens: int
     output_tokens: int
 
+
+from ..utils import trace as _trace
 
 class ContinuousBatchingPipeline:
     def __init__(self, executor: CudaLlmExecutor, scheduler_config: SchedulerConfig):
@@ -99,7 +117,8 @@ class ContinuousBatchingPipeline:
         self.scheduler.fill(st, self._np_views[(id(sb), k)])
         self.metrics.h2d_bytes += ex.upload(sb, k)
         B = len(st.seqs)
-        ex.run(sb, StepShape(st.T, B, st.max_q_len, st.max_ctx))
+        with _trace.scope("ov::genai", "decode_step" if decode else "prefill_step"):
+            ex.run(sb, StepShape(st.T, B, st.max_q_len, st.max_ctx))
         ev = ex.download_tokens_async(sb, B, k)
         self.metrics.d2h_bytes += B * 4
         m = self.metrics

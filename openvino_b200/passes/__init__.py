@@ -467,7 +467,18 @@ class Manager:
         self._pm.enable(name)
 
     def run_passes(self, model: Model) -> bool:
-        return self._pm.run(model._m)
+        from ..utils import trace
+        with trace.scope("ov::pass", "Manager::run_passes"):
+            changed = self._pm.run(model._m)
+        if trace.enabled():
+            # one event per pass, laid end to end inside the manager's scope
+            import threading
+            import time
+            t = time.perf_counter_ns()
+            for name, ms, _ in reversed(list(self._pm.timings())):
+                t -= int(ms * 1e6)
+                trace._events.append(("ov::pass", str(name), t, int(ms * 1e6), threading.get_ident()))
+        return changed
 
     def get_timings(self):
         """[(pass name, milliseconds, changed)] of the last run."""

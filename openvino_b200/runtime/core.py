@@ -61,6 +61,8 @@ class ProfilingInfo:
 # ======================================================================================================
 # plugin interface
 # ======================================================================================================
+from ..utils import log as _log, trace as _trace
+
 class Plugin:
     """Device plugin interface (IPlugin): compile, query, import, properties."""
 
@@ -334,6 +336,18 @@ class CompiledModel:
             n.rt_info["execOrder"] = str(order)
             n.rt_info["primitiveType"] = "%s_%s" % (self.plugin.device_name.lower(), n.get_type_name().lower())
             n.rt_info["outputPrecisions"] = ",".join(str(n.get_output_element_type(i)) for i in range(n.get_output_size()))
+            n.rt_info["runtimePrecision"] = str(n.get_output_element_type(0)) if n.get_output_size() else ""
+            n.rt_info["originalLayersNames"] = str(n.rt_info.get("fused_names_0", n.get_friendly_name()))
+            n.rt_info["execTimeMcs"] = "not_executed"
+        # execution times of the most recent profiled inference (PERF_COUNT) of the default request
+        req = self._default_request
+        if req is not None:
+            times = {p.node_name: p.real_time for p in req.get_profiling_info()}
+            for n in m.get_ops():
+                t = times.get(n.get_friendly_name())
+                if t is not None:
+                    us = t.total_seconds() * 1e6 if hasattr(t, "total_seconds") else float(t)
+                    n.rt_info["execTimeMcs"] = str(int(round(us)))
         return m
 
     def get_property(self, name: str):
@@ -581,7 +595,8 @@ class InferRequest:
         if self._cancel_requested:
             raise _c.CancelledError("Infer Request was canceled")
         ins = [self.get_input_tensor(i) for i in range(len(self._in))]
-        outs = self._runner(self, ins)
+        with _trace.scope("ov::phases", "InferRequest::infer::%s" % self._cm.plugin.device_name):
+            outs = self._runner(self, ins)
         for i, t in enumerate(outs):
             if i in self._user_out:
                 dst = self._user_out[i]
@@ -939,6 +954,8 @@ class Core:
             cfg = props.normalize(device_or_config)
             for k, v in cfg.items():
                 self._core_config[k] = v
+                if k == props.log.level:
+                    _log.set_level(v)
             return
         name, dev_cfg = _parse_device(device_or_config)
         cfg = props.normalize(config)
@@ -962,7 +979,8 @@ class Core:
     # ---- reading
     def read_model(self, model, weights=None, config=None) -> Model:
         from ..frontend import read_model as _read
-        return _read(model, weights, self._extensions)
+        with _trace.scope("ov::ReadTime", "Core::read_model"):
+            return _read(model, weights, self._extensions)
 
     def add_extension(self, ext) -> None:
         self._extensions.append(ext)
@@ -994,9 +1012,14 @@ class Core:
             model = self.read_model(model, weights)
         cache_dir = self._cache_dir(plugin, cfg)
         cfg.pop(props.cache_dir, None)
-        if cache_dir and "EXPORT_IMPORT" in plugin.capabilities():
-            return self._compile_with_cache(plugin, model, cfg, cache_dir)
-        return plugin.compile_model(model, cfg)
+        with _trace.scope("ov::LoadTime", "Core::compile_model::%s" % dev):
+            if cache_dir and "EXPORT_IMPORT" in plugin.capabilities():
+                cm = self._compile_with_cache(plugin, model, cfg, cache_dir)
+                _log.info("core", "compiled '%s' for %s (%s)" % (model.get_friendly_name(), dev, "cache hit" if cm.loaded_from_cache else "cache miss"))
+                return cm
+            cm = plugin.compile_model(model, cfg)
+        _log.info("core", "compiled '%s' for %s" % (model.get_friendly_name(), dev))
+        return cm
 
     def _cache_key(self, plugin: Plugin, model: Model, cfg: dict) -> str:
         h = hashlib.sha256()
