@@ -32,6 +32,19 @@ __device__ __forceinline__ bool wait_flag_ge(const int* f, int epoch, int* statu
 
 __global__ void step_begin_kernel(int* epoch) { *epoch = *epoch + 1; }
 
+// One thread waits for *flag >= value with a caller-chosen poll budget; when the budget runs out the kernel records
+// STATUS_PEER_TIMEOUT in the status word and returns, so the context stays usable. The building block of the
+// failure-detection tests: a flag that nobody sets makes the wait run out.
+__global__ void wait_flag_kernel(const int* flag, int value, unsigned max_polls, int* status, int* result) {
+    bool ok = false;
+    for (unsigned i = 0; i < max_polls; ++i) {
+        if (ld_acquire_sys(flag) >= value) { ok = true; break; }
+        __nanosleep(200);
+    }
+    if (!ok) report_status(status, STATUS_PEER_TIMEOUT);
+    if (result) *result = ok ? 1 : 0;
+}
+
 struct CommK {
     int rank, world;
     uint8_t* heap[8];
@@ -175,6 +188,13 @@ int ovb_comm_step_begin(const ovb_comm* c, ovb_stream_t stream) {
     OVB_REQUIRE(c != nullptr && c->heap[c->rank] != nullptr, "ovb_comm_step_begin: bad communicator");
     step_begin_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<int*>(static_cast<uint8_t*>(c->heap[c->rank]) + c->epoch_off));
+    OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_comm_wait_flag(const int* flag, int value, unsigned max_polls, int* result, ovb_stream_t stream) {
+    OVB_REQUIRE(flag != nullptr && max_polls > 0 && max_polls <= (1u << 24), "ovb_comm_wait_flag: need a flag and 1 .. 2^24 polls");
+    wait_flag_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag, value, max_polls, status_word(), result);
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -202,6 +202,9 @@ int ovb_comm_close(void* ptr);
 int ovb_comm_step_begin(const ovb_comm* c, ovb_stream_t stream);
 // Greedy sampling over vocabulary shards: every rank holds its shard's best (value, local index) per row;
 // afterwards ids[row] is the global argmax on every rank (lowest index on ties). rows <= 1024.
+/* Wait on the device until *flag >= value, at most max_polls polls (~0.25 us apart); on time-out the status word gets the
+   peer-time-out code and *result (may be NULL) 0. Never blocks longer than max_polls allows. */
+int ovb_comm_wait_flag(const int* flag, int value, unsigned max_polls, int* result, ovb_stream_t stream);
 int ovb_comm_argmax_combine(const ovb_comm* c, int* ids, const float* max_vals, int rows, int shard_size, ovb_stream_t stream);
 // In-place sum of a bf16 tensor of n elements that lives at the same heap offset on every rank (n % 8 == 0).
 int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream_t stream);

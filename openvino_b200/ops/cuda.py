@@ -319,6 +319,12 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.reshape(F // 64, 64, Kd), up.reshape(F // 64, 64, Kd)], dim=1).reshape(2 * F, Kd)
 
 
+def wait_flag(flag: torch.Tensor, value: int, max_polls: int = 1 << 16, result: Optional[torch.Tensor] = None) -> None:
+    """Queue a bounded device-side wait for ``flag[0] >= value`` (int32 tensor); a time-out shows in the status word."""
+    _check(lib().ovb_comm_wait_flag(C.c_void_p(flag.data_ptr()), C.c_int(value), C.c_uint(max_polls), C.c_void_p(_ptr(result)),
+                                    C.c_void_p(_stream())), "ovb_comm_wait_flag")
+
+
 def sample_gumbel(logits: torch.Tensor, temperature: float, seed: int = 0, step: Optional[torch.Tensor] = None, vocab_offset: int = 0,
                   out: Optional[torch.Tensor] = None, out_max: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Temperature sampling by perturbed arg-max over bf16 ``logits`` [rows, V] (a vocabulary shard starting at

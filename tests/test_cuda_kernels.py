@@ -425,3 +425,19 @@ def test_sampling_kernel(ops):
     order = want.argsort(descending=True)
     keep = order[: int((want[order].cumsum(0) < 0.5).sum()) + 1].tolist()
     assert set(nuc.tolist()) <= set(keep)
+
+
+def test_bounded_wait_reports_a_timeout_and_the_context_survives(ops):
+    """Failure detection on the device: a wait on a flag that nobody sets runs out of polls, the status word says so,
+    and the next kernels run normally."""
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    ops.wait_flag(flag, 1, max_polls=20000, result=res)          # a few milliseconds
+    assert ops.read_status() == 2 and int(res.item()) == 0        # STATUS_PEER_TIMEOUT
+    assert ops.read_status() == 0                                 # reading clears the word
+    flag.fill_(3)
+    ops.wait_flag(flag, 3, max_polls=20000, result=res)
+    assert ops.read_status() == 0 and int(res.item()) == 1
+    x = torch.randn(4, 256, device="cuda", dtype=torch.bfloat16)
+    y = ops.rmsnorm(x, torch.ones(256, device="cuda", dtype=torch.bfloat16), 1e-5)
+    assert torch.isfinite(y.float()).all()
