@@ -67,6 +67,7 @@ struct GemmKParams {
     int world, rank;
     int comm_mode;            // 1: one-shot (every rank gets every partial), 2: two-shot (tile owners reduce and broadcast)
     int parity;               // one-shot staging buffer to use (consecutive fused calls alternate)
+    int site;                 // call site number (< 256): with the step number it makes the one-shot packets' tag unique
     uint8_t* heap[8];
     long long stage_off;      // staging area of the chosen mode (one-shot: of the chosen parity), offset in the heap
     long long flags_off;      // this call site's flags: [tile][world + 1] int32, offset in the heap
@@ -582,33 +583,82 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 for (int j = 0; j < 8; ++j) ve[j] = from_float<E>(f[j]);
                 return v;
             };
+            TR(long long tr_e0 = 0, tr_e1 = 0, tr_e2 = 0; if (dq_tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e0));)
             if (p.comm_mode == 1) {
-                // one-shot: push the partial to every rank, then every rank reduces the tile for itself
-                const size_t slot = (size_t)p.stage_off + ((size_t)p.rank * tiles + tile_id) * SLOT;
+                // One-shot with flag-carrying packets: every 16-byte store holds two (data word, step number) pairs, so the
+                // receiver sees data and "it has arrived" in the same 8-byte unit and needs neither a fence nor a flag
+                // round trip. A thread pushes its pieces of the bf16 partial to every peer, then polls the same pieces
+                // of every peer's partial in its own staging area and sums in rank order (identical bits on all ranks;
+                // its own partial is rounded to bf16 like the copies the peers receive).
+                constexpr size_t LL_SLOT = 2 * SLOT;
+                // two call sites share a staging buffer within a step, so the tag names the site as well as the step
+                const uint32_t tag = ((uint32_t)epoch << 8) | (uint32_t)(p.site & 255);
+                const size_t my_slot = (size_t)p.stage_off + ((size_t)p.rank * tiles + tile_id) * LL_SLOT;
                 for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
                     const int col = i >> 4, pc = i & 15;
                     if (col < ntok) {
                         const uint4 v = partial_piece(col, pc);
-                        for (int r = 0; r < W; ++r)
-                            *reinterpret_cast<uint4*>(p.heap[r] + slot + ((size_t)col * TILE_N + pc * 8) * 2) = v;
+                        const size_t off = my_slot + ((size_t)col * TILE_N + pc * 8) * 4;
+                        for (int r = 0; r < W; ++r) {
+                            if (r == p.rank) continue;
+                            st_volatile_v4(p.heap[r] + off, v.x, tag, v.y, tag);
+                            st_volatile_v4(p.heap[r] + off + 16, v.z, tag, v.w, tag);
+                        }
                     }
                 }
-                __threadfence_system();
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (dq_tid < W) {
-                    st_release_sys(flags_of(dq_tid) + p.rank, epoch);
-                    wait_flag(my_flags + dq_tid);
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (*abort_flag == 0) {
-                    const uint8_t* slots = p.heap[p.rank] + p.stage_off + (size_t)tile_id * SLOT;
-                    for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
-                        const int col = i >> 4, pc = i & 15;
-                        if (col < ntok)
-                            *reinterpret_cast<uint4*>(reinterpret_cast<E*>(p.out) + (size_t)(t0 + col) * p.ldo + n0 + pc * 8) =
-                                reduced_piece(slots, (size_t)tiles * SLOT, col, pc);
+                TR(if (dq_tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e1));)
+                bool ok_ll = true;
+                for (int i = dq_tid; i < PIECES && ok_ll; i += DQ_THREADS) {
+                    const int col = i >> 4, pc = i & 15;
+                    if (col >= ntok) continue;
+                    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    for (int r = 0; r < W && ok_ll; ++r) {
+                        uint4 v;
+                        if (r == p.rank) {
+                            v = partial_piece(col, pc);
+                        } else {
+                            const uint8_t* src = p.heap[p.rank] + p.stage_off + ((size_t)r * tiles + tile_id) * LL_SLOT + ((size_t)col * TILE_N + pc * 8) * 4;
+                            uint4 a, b;
+                            uint32_t spins = 0;
+                            for (;;) {
+                                a = ld_volatile_v4(src);
+                                b = ld_volatile_v4(src + 16);
+                                if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+                                if (++spins > kPeerSpinLimit || ((spins & 1023u) == 0 && *abort_flag)) { ok_ll = false; break; }
+                                if (spins > 64) __nanosleep(100);
+                            }
+                            v = make_uint4(a.x, a.z, b.x, b.z);
+                        }
+                        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) f[j] += __bfloat162float(e[j]);
                     }
+                    if (!ok_ll) break;
+                    const size_t tok = (size_t)(t0 + col);
+                    if (p.bias) {
+                        const uint4 bb = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.bias) + n0 + pc * 8);
+                        const E* be = reinterpret_cast<const E*>(&bb);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) f[j] += to_float(be[j]);
+                    }
+                    if (p.residual) {
+                        const uint4 rr = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.residual) + tok * p.ldr + n0 + pc * 8);
+                        const E* re = reinterpret_cast<const E*>(&rr);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) f[j] += to_float(re[j]);
+                    }
+                    uint4 o;
+                    E* oe = reinterpret_cast<E*>(&o);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) oe[j] = from_float<E>(f[j]);
+                    *reinterpret_cast<uint4*>(reinterpret_cast<E*>(p.out) + tok * p.ldo + n0 + pc * 8) = o;
                 }
+                if (!ok_ll) {
+                    report_status(p.status, STATUS_PEER_TIMEOUT);
+                    *abort_flag = 1;
+                }
+                TR(if (dq_tid == 0) { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e2));
+                       const int c_ = tile_id & 16383; g_cta_trace[c_ * 4 + 0] = tr_e0; g_cta_trace[c_ * 4 + 1] = tr_e1; g_cta_trace[c_ * 4 + 2] = tr_e2; })
             } else {
                 // two-shot: the owner of the tile (tile_id mod W) collects the partials, reduces, and writes the
                 // finished tile into `out` on every rank; nobody leaves before its copy of the tile is final
@@ -1070,16 +1120,19 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
                     "ovb_gemm: the fused all-reduce needs N %% 128 == 0 and 16-byte aligned rows");
         const int mode = c->mode ? c->mode : (a->T <= 128 ? 1 : 2);
         const int64_t slot = (int64_t)bt * TILE_N * 2;
-        const int64_t need = mode == 1 ? c->world * tiles * slot : c->world * ((tiles + c->world - 1) / c->world) * slot;
+        // one-shot staging holds flag-carrying packets: twice the bytes of the bf16 tiles
+        const int64_t need = mode == 1 ? 2 * c->world * tiles * slot : c->world * ((tiles + c->world - 1) / c->world) * slot;
         OVB_REQUIRE(need <= (mode == 1 ? c->stage1_bytes : c->stage2_bytes),
                     "ovb_gemm: the communicator's staging area (%lld bytes) is too small for T=%d N=%d (%lld bytes)",
                     (long long)(mode == 1 ? c->stage1_bytes : c->stage2_bytes), a->T, a->N, (long long)need);
         OVB_REQUIRE(tiles * (c->world + 1) <= c->flags_per_site && c->site >= 0 && c->site < c->num_sites,
                     "ovb_gemm: communicator flag area too small (%lld tiles) or bad call site %d", (long long)tiles, c->site);
+        OVB_REQUIRE(mode != 1 || c->num_sites <= 256, "ovb_gemm: the one-shot all-reduce tags packets with an 8-bit call site (%d sites)", c->num_sites);
         p.world = c->world;
         p.rank = c->rank;
         p.comm_mode = mode;
         p.parity = c->site & 1;
+        p.site = c->site;
         for (int r = 0; r < c->world; ++r) {
             OVB_REQUIRE(c->heap[r] != nullptr, "ovb_gemm: communicator heap of rank %d is not mapped", r);
             p.heap[r] = static_cast<uint8_t*>(c->heap[r]);

@@ -53,7 +53,7 @@ class HeapLayout:
         self.flags_off = 256
         off = self.flags_off + num_sites * self.flags_per_site * 4
         self.stage1_off = _round_up(off, 1024)
-        self.stage1_bytes = _round_up(world * 128 * hidden * 2, 1024)            # one-shot: T <= 128
+        self.stage1_bytes = _round_up(2 * world * 128 * hidden * 2, 1024)        # one-shot (T <= 128): flag-carrying packets, 2x the tile bytes
         self.stage2_off = self.stage1_off + 2 * self.stage1_bytes
         # two-shot: every tile has one owner; rounding the tiles per owner up costs at most `world` extra tiles
         self.stage2_bytes = _round_up((_round_up(max_tokens, 256) * hidden + world * 256 * 128) * 2, 1024)
