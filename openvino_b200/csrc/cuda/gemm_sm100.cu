@@ -73,6 +73,7 @@ struct GemmKParams {
     long long flags_off;      // this call site's flags: [tile][world + 1] int32, offset in the heap
     long long out_off;        // `out` as an offset in the heap (two-shot owners write it on every rank)
     const int* epoch;         // device word holding the current step number (local memory)
+    long long count_off;      // one int32 in the heap: CTAs of a two-shot launch that have finished their tile
 };
 
 constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 us apart
@@ -660,39 +661,95 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 TR(if (dq_tid == 0) { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e2));
                        const int c_ = tile_id & 16383; g_cta_trace[c_ * 4 + 0] = tr_e0; g_cta_trace[c_ * 4 + 1] = tr_e1; g_cta_trace[c_ * 4 + 2] = tr_e2; })
             } else {
-                // two-shot: the owner of the tile (tile_id mod W) collects the partials, reduces, and writes the
-                // finished tile into `out` on every rank; nobody leaves before its copy of the tile is final
+                // Two-shot: the owner of the tile (tile_id mod W) collects the partials, reduces, and writes the finished
+                // tile into `out` on every rank. The partials travel as flag-carrying packets, so a CTA that does not
+                // own its tile stores and leaves: no fence, no flag, no wait, and the SM goes on to the next tile. Only
+                // the last CTA of the launch to get here waits (bounded) until the owners on the other ranks have
+                // delivered every tile, which also tells it that they are done reading this rank's partials.
+                constexpr size_t LL_SLOT = 2 * SLOT;
+                const uint32_t tag = ((uint32_t)epoch << 8) | (uint32_t)(p.site & 255);
                 const int owner = tile_id % W, own_idx = tile_id / W, own_cap = (tiles + W - 1) / W;
-                const size_t slot = (size_t)p.stage_off + ((size_t)p.rank * own_cap + own_idx) * SLOT;
-                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
-                    const int col = i >> 4, pc = i & 15;
-                    if (col < ntok)
-                        *reinterpret_cast<uint4*>(p.heap[owner] + slot + ((size_t)col * TILE_N + pc * 8) * 2) = partial_piece(col, pc);
-                }
-                __threadfence_system();
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (dq_tid == 0) st_release_sys(flags_of(owner) + p.rank, epoch);
-                if (p.rank == owner) {
-                    if (dq_tid < W) wait_flag(my_flags + dq_tid);
-                    asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                    const bool good = (*abort_flag == 0);
-                    if (good) {
-                        const uint8_t* slots = p.heap[p.rank] + p.stage_off + (size_t)own_idx * SLOT;
-                        for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
-                            const int col = i >> 4, pc = i & 15;
-                            if (col < ntok) {
-                                const uint4 v = reduced_piece(slots, (size_t)own_cap * SLOT, col, pc);
-                                const size_t off = (size_t)p.out_off + ((size_t)(t0 + col) * p.ldo + n0 + pc * 8) * 2;
-                                for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(p.heap[r] + off) = v;
-                            }
+                if (p.rank != owner) {
+                    uint8_t* dst = p.heap[owner] + p.stage_off + ((size_t)p.rank * own_cap + own_idx) * LL_SLOT;
+                    for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                        const int col = i >> 4, pc = i & 15;
+                        if (col < ntok) {
+                            const uint4 v = partial_piece(col, pc);
+                            uint8_t* d = dst + ((size_t)col * TILE_N + pc * 8) * 4;
+                            st_volatile_v4(d, v.x, tag, v.y, tag);
+                            st_volatile_v4(d + 16, v.z, tag, v.w, tag);
                         }
+                    }
+                } else {
+                    bool ok_ll = true;
+                    for (int i = dq_tid; i < PIECES && ok_ll; i += DQ_THREADS) {
+                        const int col = i >> 4, pc = i & 15;
+                        if (col >= ntok) continue;
+                        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        for (int r = 0; r < W && ok_ll; ++r) {
+                            uint4 v;
+                            if (r == p.rank) {
+                                v = partial_piece(col, pc);
+                            } else {
+                                const uint8_t* src = p.heap[p.rank] + p.stage_off + ((size_t)r * own_cap + own_idx) * LL_SLOT + ((size_t)col * TILE_N + pc * 8) * 4;
+                                uint4 a, b;
+                                uint32_t spins = 0;
+                                for (;;) {
+                                    a = ld_volatile_v4(src);
+                                    b = ld_volatile_v4(src + 16);
+                                    if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+                                    if (++spins > kPeerSpinLimit || ((spins & 1023u) == 0 && *abort_flag)) { ok_ll = false; break; }
+                                    if (spins > 64) __nanosleep(100);
+                                }
+                                v = make_uint4(a.x, a.z, b.x, b.z);
+                            }
+                            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] += __bfloat162float(e[j]);
+                        }
+                        if (!ok_ll) break;
+                        const size_t tok = (size_t)(t0 + col);
+                        if (p.bias) {
+                            const uint4 bb = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.bias) + n0 + pc * 8);
+                            const E* be = reinterpret_cast<const E*>(&bb);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] += to_float(be[j]);
+                        }
+                        if (p.residual) {
+                            const uint4 rr = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.residual) + tok * p.ldr + n0 + pc * 8);
+                            const E* re = reinterpret_cast<const E*>(&rr);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] += to_float(re[j]);
+                        }
+                        uint4 o;
+                        E* oe = reinterpret_cast<E*>(&o);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) oe[j] = from_float<E>(f[j]);
+                        const size_t off = (size_t)p.out_off + (tok * p.ldo + n0 + pc * 8) * 2;
+                        for (int r = 0; r < W; ++r) *reinterpret_cast<uint4*>(p.heap[r] + off) = o;
+                    }
+                    if (!ok_ll) {
+                        report_status(p.status, STATUS_PEER_TIMEOUT);
+                        *abort_flag = 1;
                     }
                     __threadfence_system();
                     asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                    if (good && dq_tid < W) st_release_sys(flags_of(dq_tid) + W, epoch);
+                    if (*abort_flag == 0 && dq_tid < W && dq_tid != p.rank) st_release_sys(flags_of(dq_tid) + W, epoch);
                 }
-                if (dq_tid == 0) wait_flag(my_flags + W);
+                // the last CTA of this launch collects the "tile is final" flags of the tiles that peers own
+                int* done_count = reinterpret_cast<int*>(p.heap[p.rank] + p.count_off);
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (dq_tid == 0) {
+                    const int last = atomicAdd(done_count, 1) == tiles - 1;
+                    if (last) *done_count = 0;
+                    *last_flag = last;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (*last_flag) {
+                    int* base = reinterpret_cast<int*>(p.heap[p.rank] + p.flags_off);
+                    for (int t = dq_tid; t < tiles; t += DQ_THREADS)
+                        if (t % W != p.rank) wait_flag(base + (size_t)t * (W + 1) + W);
+                }
             }
         };
 
@@ -1120,8 +1177,8 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
                     "ovb_gemm: the fused all-reduce needs N %% 128 == 0 and 16-byte aligned rows");
         const int mode = c->mode ? c->mode : (a->T <= 128 ? 1 : 2);
         const int64_t slot = (int64_t)bt * TILE_N * 2;
-        // one-shot staging holds flag-carrying packets: twice the bytes of the bf16 tiles
-        const int64_t need = mode == 1 ? 2 * c->world * tiles * slot : c->world * ((tiles + c->world - 1) / c->world) * slot;
+        // the staging areas hold flag-carrying packets: twice the bytes of the bf16 tiles
+        const int64_t need = mode == 1 ? 2 * c->world * tiles * slot : 2 * c->world * ((tiles + c->world - 1) / c->world) * slot;
         OVB_REQUIRE(need <= (mode == 1 ? c->stage1_bytes : c->stage2_bytes),
                     "ovb_gemm: the communicator's staging area (%lld bytes) is too small for T=%d N=%d (%lld bytes)",
                     (long long)(mode == 1 ? c->stage1_bytes : c->stage2_bytes), a->T, a->N, (long long)need);
@@ -1140,6 +1197,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         p.stage_off = mode == 1 ? c->stage1_off + (int64_t)p.parity * c->stage1_bytes : c->stage2_off;
         p.flags_off = c->flags_off + (int64_t)c->site * c->flags_per_site * 4;
         p.epoch = reinterpret_cast<const int*>(p.heap[c->rank] + c->epoch_off);
+        p.count_off = c->epoch_off + 64;   // the first 256 bytes of the heap are reserved for such words
         if (mode == 2) {
             const int64_t off = static_cast<uint8_t*>(a->out) - p.heap[c->rank];
             OVB_REQUIRE(off >= 0 && off + ((int64_t)(a->T - 1) * p.ldo + a->N) * 2 <= c->heap_bytes,

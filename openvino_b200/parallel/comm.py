@@ -56,7 +56,7 @@ class HeapLayout:
         self.stage1_bytes = _round_up(2 * world * 128 * hidden * 2, 1024)        # one-shot (T <= 128): flag-carrying packets, 2x the tile bytes
         self.stage2_off = self.stage1_off + 2 * self.stage1_bytes
         # two-shot: every tile has one owner; rounding the tiles per owner up costs at most `world` extra tiles
-        self.stage2_bytes = _round_up((_round_up(max_tokens, 256) * hidden + world * 256 * 128) * 2, 1024)
+        self.stage2_bytes = _round_up(2 * (_round_up(max_tokens, 256) * hidden + world * 256 * 128) * 2, 1024)    # packets: 2x
         self.tensors_off = _round_up(self.stage2_off + self.stage2_bytes, 1024)
         self.heap_bytes = self.tensors_off + _round_up(tensor_bytes, 1024)
 
