@@ -267,24 +267,28 @@ class CudaLlmExecutor:
                 raise ValueError("tensor-parallel weights need a communicator")
             moe_rows = max_batch_tokens + 1 if (cfg.num_experts and max_batch_tokens >= MOE_GATHER_MIN_TOKENS) else 0
             comm.setup(cfg.hidden_size, max_batch_tokens, cfg.num_layers,
-                       tensor_bytes=(max_batch_tokens + max_seqs + 2 + moe_rows) * cfg.hidden_size * 2 + 8192)
+                       tensor_bytes=(max_batch_tokens + max_seqs + 2 + moe_rows) * cfg.hidden_size * 2 + 8192
+                       + max_seqs * cfg.vocab_size * 2 + 4096)
         self.prefill = StepBuffers(cfg, max_batch_tokens, max_seqs, max_blocks_per_seq, self.device, self.tp_size, comm if self.tp_size > 1 else None)
         self.decode = StepBuffers(cfg, max_seqs, max_seqs, max_blocks_per_seq, self.device, self.tp_size, comm if self.tp_size > 1 else None)
+        # top-k / top-p under tensor parallelism need the whole row: every rank places its vocabulary shard into a zeroed
+        # full-width buffer in the symmetric heap and the ranks sum the buffers (adding zeros is exact in bf16)
+        self.full_logits = comm.alloc((max(max_seqs, 1), cfg.vocab_size)) if self.tp_size > 1 else None
         # token sampled last for every request slot (device-side feedback between chained steps)
         self.last_token = torch.zeros(max(max_seqs, 1) * 4, dtype=torch.int32, device=self.device)
         self._graphs = {}
         self._expert_windows = {}
         self.kernel_launches = 0
-        # sampling: None = greedy; (temperature, top_k, top_p, seed) = stochastic (single-rank only). The step word is
+        # sampling: None = greedy; (temperature, top_k, top_p, seed) = stochastic. The step word is
         # bumped on the device before every draw, so replays of a captured decode graph keep drawing fresh numbers.
         self.sampling = None
         self.sample_step = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def set_sampling(self, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
         new = None if temperature <= 0 else (float(temperature), int(top_k), float(top_p), int(seed))
-        if new is not None and self.tp_size > 1 and (top_k > 0 or top_p < 1.0):
-            raise NotImplementedError("top-k / top-p over vocabulary shards is not implemented: with tensor parallelism use greedy "
-                                      "decoding or plain temperature sampling")
+        if new is not None and self.tp_size > 1 and (top_k > 0 or top_p < 1.0) and self.cfg.vocab_size % 8:
+            raise NotImplementedError("top-k / top-p with tensor parallelism gathers the logits in 16-byte pieces: the vocabulary "
+                                      "size must be a multiple of 8")
         if new != self.sampling:
             self._graphs.clear()       # captured decode graphs embed the sampling kernel
         self.sampling = new
@@ -397,7 +401,16 @@ class CudaLlmExecutor:
         if self.sampling is not None:
             temp, top_k, top_p, seed = self.sampling
             K.bump(self.sample_step)
-            if self.tp_size > 1:
+            if self.tp_size > 1 and (top_k > 0 or top_p < 1.0):
+                # truncated sampling needs the whole row: gather the shards (sum of zero-padded rows over the ranks), then
+                # every rank runs the same draw with the same seed and step, so all ranks get the same tokens
+                shard = self.cfg.vocab_size // self.tp_size
+                full = self.full_logits[:B]
+                full.zero_()
+                full[:, self.w.tp_rank * shard:(self.w.tp_rank + 1) * shard].copy_(sb.logits[:B])
+                self.kernel_launches += 2 + self.comm.all_reduce_large(full)
+                K.sample(full, temp, top_k, top_p, seed, self.sample_step, out=sb.tokens[:B])
+            elif self.tp_size > 1:
                 # every rank perturbs its vocabulary shard with noise that depends on the global token index, then the
                 # ranks exchange (best value, index): a draw from the full softmax without gathering the logits
                 shard = self.cfg.vocab_size // self.tp_size
