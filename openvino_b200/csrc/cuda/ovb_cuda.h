@@ -179,7 +179,8 @@ int ovb_sdpa_dense(const void* q, const void* k, const void* v, void* out, int B
 // Layout inside the heap (byte offsets, identical on every rank):
 //   epoch_off    one int32: the step number, bumped by ovb_comm_step_begin at the start of every step
 //   flags_off    num_sites x flags_per_site int32, zero at start; a flag holds the step number of its last signal
-//   stage1_off   2 x stage1_bytes: one-shot staging (two buffers used alternately by consecutive fused calls)
+//   stage1_off   2 x stage1_bytes: one-shot staging (two buffers used alternately by consecutive fused calls); sized for
+//                packets, i.e. twice the bytes of the bf16 tiles, like stage2
 //   stage2_off   stage2_bytes: two-shot staging
 //   the rest     tensors handed out by the Python side (residual streams that peers write into)
 typedef struct {
@@ -189,7 +190,9 @@ typedef struct {
     int64_t epoch_off, flags_off, flags_per_site, stage1_off, stage1_bytes, stage2_off, stage2_bytes;
     int num_sites;
     int site;      // call site of this collective inside the step (every site has its own flags)
-    int mode;      // 0: choose by size, 1: one-shot, 2: two-shot
+    int mode;      // 0: choose by size, 1: one-shot, 2: two-shot. How the partials travel (flag-carrying packets, or plain tiles with
+                   // a fence and arrival flags) is chosen from the world size; the environment variable OVB_COMM_PACKETS (bit 0:
+                   // one-shot, bit 1: two-shot) overrides it and must be the same on every rank.
 } ovb_comm;
 
 // Symmetric-heap plumbing (no kernels): allocate zeroed device memory, export / open / close CUDA IPC handles.
