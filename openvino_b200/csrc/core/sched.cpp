@@ -33,10 +33,12 @@ void Scheduler::release(SeqState& s) {
     for (auto b : s.blocks) free_.push_back(b);
     s.blocks.clear();
 }
-bool Scheduler::preempt_one(const SeqState* keep) {
+bool Scheduler::preempt_one(const SeqState* keep, const std::vector<SeqPtr>& scheduled) {
+    // youngest running sequence that is neither `keep` nor part of the step being built (its block table is in use)
     for (auto it = running_.rbegin(); it != running_.rend(); ++it) {
         SeqPtr v = *it;
         if (v.get() == keep || v->blocks.empty()) continue;
+        if (std::find(scheduled.begin(), scheduled.end(), v) != scheduled.end()) continue;
         release(*v);
         v->num_computed = 0;
         running_.erase(std::next(it).base());
@@ -58,25 +60,31 @@ bool Scheduler::schedule(ScheduledStep& out) {
     out = ScheduledStep();
     int64_t budget = cfg_.max_num_batched_tokens;
     auto pending = [](const SeqState& s) { return s.total_len() - s.num_computed; };
-    std::vector<SeqPtr> prefill_running, decode_running;
-    for (auto& s : running_) (pending(*s) > 1 ? prefill_running : decode_running).push_back(s);
-    const bool want_prefill = !prefill_running.empty() || !waiting_.empty();
     auto in_running = [&](const SeqPtr& s) { return std::find(running_.begin(), running_.end(), s) != running_.end(); };
-
-    if (!decode_running.empty() && (cfg_.dynamic_split_fuse || !want_prefill)) {
+    auto want_prefill = [&]() {
+        if (!waiting_.empty()) return true;
+        for (auto& s : running_) if (pending(*s) > 1) return true;
+        return false;
+    };
+    auto decode_phase = [&]() {
+        std::vector<SeqPtr> decode_running;
+        for (auto& s : running_) if (pending(*s) == 1) decode_running.push_back(s);
         for (auto& s : decode_running) {
             if (budget <= 0 || (int64_t)out.seqs.size() >= cfg_.max_num_seqs) break;
-            if (!in_running(s)) continue;   // preempted by an earlier sequence of this loop
-            while (!grow(*s, s->total_len())) if (!preempt_one(s.get())) break;
-            if ((s->total_len() + cfg_.block_size - 1) / cfg_.block_size > (int64_t)s->blocks.size() || !in_running(s)) continue;
+            if (!in_running(s)) continue;   // preempted on behalf of an earlier sequence of this loop
+            while (!grow(*s, s->total_len())) if (!preempt_one(s.get(), out.seqs)) break;
+            if ((s->total_len() + cfg_.block_size - 1) / cfg_.block_size > (int64_t)s->blocks.size()) continue;
             out.seqs.push_back(s);
             out.num_new.push_back(1);
             --budget;
         }
-    }
-    if (want_prefill && (cfg_.dynamic_split_fuse || out.seqs.empty())) {
-        std::vector<SeqPtr> cands = prefill_running;
-        while (!waiting_.empty() && (int64_t)running_.size() + (int64_t)(cands.size() - prefill_running.size()) < cfg_.max_num_seqs) {
+    };
+    auto prefill_phase = [&](bool may_preempt) {
+        // taken after the decode phase: a preemption there moves a mid-prefill sequence from running_ to waiting_
+        std::vector<SeqPtr> cands;
+        for (auto& s : running_) if (pending(*s) > 1) cands.push_back(s);
+        const size_t n_running_cands = cands.size();
+        while (!waiting_.empty() && (int64_t)running_.size() + (int64_t)(cands.size() - n_running_cands) < cfg_.max_num_seqs) {
             cands.push_back(waiting_.front());
             waiting_.pop_front();
         }
@@ -85,7 +93,10 @@ bool Scheduler::schedule(ScheduledStep& out) {
             const bool was_running = in_running(s);
             if (budget <= 0 || (int64_t)out.seqs.size() >= cfg_.max_num_seqs) { if (!was_running) back.push_back(s); continue; }
             const int64_t n = std::min(budget, s->total_len() - s->num_computed);
-            if (n <= 0 || !grow(*s, s->num_computed + n)) { if (!was_running) back.push_back(s); continue; }
+            bool ok = n > 0 && grow(*s, s->num_computed + n);
+            // last resort: the oldest candidate evicts younger sequences
+            while (n > 0 && !ok && may_preempt && out.seqs.empty() && preempt_one(s.get(), out.seqs)) ok = grow(*s, s->num_computed + n);
+            if (!ok) { if (!was_running) back.push_back(s); continue; }
             if (!was_running) {
                 running_.push_back(s);
                 if (s->slot < 0) { s->slot = free_slots_.front(); free_slots_.pop_front(); }
@@ -95,7 +106,15 @@ bool Scheduler::schedule(ScheduledStep& out) {
             budget -= n;
         }
         for (auto it = back.rbegin(); it != back.rend(); ++it) waiting_.push_front(*it);
+    };
+    if (cfg_.dynamic_split_fuse) {
+        decode_phase();
+        if (want_prefill()) prefill_phase(false);
+    } else {
+        if (want_prefill()) prefill_phase(false);
+        if (out.seqs.empty()) decode_phase();   // no prompt chunk fits: keep the running sequences going (they may preempt)
     }
+    if (out.seqs.empty() && want_prefill()) prefill_phase(true);
     if (out.seqs.empty()) return false;
     for (size_t i = 0; i < out.seqs.size(); ++i) {
         out.T += out.num_new[i];

@@ -82,7 +82,7 @@ public:
 private:
     bool grow(SeqState& s, int64_t new_len);
     void release(SeqState& s);
-    bool preempt_one(const SeqState* keep);
+    bool preempt_one(const SeqState* keep, const std::vector<SeqPtr>& scheduled);
     void finish(const SeqPtr& s);
     void check_eos(const std::vector<Produced>& produced);
     SchedulerConfig cfg_;

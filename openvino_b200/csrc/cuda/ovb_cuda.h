@@ -122,6 +122,8 @@ int ovb_sample(const void* logits, int ld, int rows, int vocab, float temperatur
    tensor-parallel ranks). With vocab_offset = 0 and the whole vocabulary it is a complete sampler. */
 int ovb_sample_gumbel(const void* logits, int ld, int rows, int vocab, int vocab_offset, float temperature, uint64_t seed, const int* step,
                       int* out_ids, float* out_max, ovb_stream_t stream);
+/* The uniform in (0, 1) that the perturbed arg-max derives from a 64-bit hash (runs on the host; largest value 1 - 2^-24). */
+float ovb_gumbel_uniform(uint64_t h);
 int ovb_bump(int* counter, ovb_stream_t stream);     // *counter += 1 on the device
 int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream);
 // Mixture of experts. Router: softmax over E logits per token, top-k kept and renormalised; weights is dense [T, E] fp32.

@@ -117,6 +117,13 @@ __global__ void bump_kernel(int* p) { *p += 1; }
 extern "C" {
 namespace ovb {
 
+// Uniform in the open interval (0, 1) from the top 23 bits of a hash: (k + 0.5) * 2^-23 with k < 2^23 needs 24 significant
+// bits, so the fp32 sum is exact and the largest value is 1 - 2^-24 (with 24 bits of k the sum k + 0.5 would round to 2^24
+// for k = 2^24 - 1, u would be exactly 1, and the Gumbel noise -log(-log(u)) would be +inf).
+__host__ __device__ __forceinline__ float gumbel_uniform(uint64_t h) {
+    return ((float)(h >> 41) + 0.5f) * (1.0f / 8388608.0f);
+}
+
 // Sampling over vocabulary shards without gathering the logits (Gumbel-max): argmax_i(logit_i / T + G_i) with
 // G_i = -log(-log(u_i)) is a draw from softmax(logits / T) when the u_i are independent uniforms. u_i depends on the seed,
 // the step word, the row and the GLOBAL token index only, so every tensor-parallel rank perturbs its own shard, reduces
@@ -133,7 +140,7 @@ __global__ void __launch_bounds__(kSampleThreads) gumbel_argmax_kernel(const __n
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += kSampleThreads) {
         const uint64_t h = mix64(base ^ ((uint64_t)(uint32_t)(vocab_offset + i) * 0xD1B54A32D192ED03ull));
-        const float u = ((float)(h >> 40) + 0.5f) * (1.0f / 16777216.0f);     // (0, 1)
+        const float u = gumbel_uniform(h);
         const float g = -__logf(-__logf(u));
         const float f = __bfloat162float(lr[i]) * inv_temp + g;
         if (f > best) { best = f; bi = i; }
@@ -189,6 +196,9 @@ int ovb_sample_gumbel(const void* logits, int ld, int rows, int vocab, int vocab
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
+
+// Host-side view of the hash -> uniform mapping of the Gumbel sampler (for tests of its range).
+float ovb_gumbel_uniform(uint64_t h) { return gumbel_uniform(h); }
 
 int ovb_bump(int* counter, ovb_stream_t stream_) {
     OVB_REQUIRE(counter != nullptr, "ovb_bump: null counter");

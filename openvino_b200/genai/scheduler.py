@@ -115,9 +115,11 @@ class Scheduler:
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 
-    def _preempt_one(self, keep: Sequence) -> bool:
+    def _preempt_one(self, keep: Sequence, scheduled: List[Sequence]) -> bool:
+        """Free the blocks of the youngest running sequence that is neither ``keep`` nor part of the step being
+        built (a sequence already scheduled keeps its blocks: the step's block table points at them)."""
         for victim in reversed(self.running):
-            if victim is not keep and victim.blocks:
+            if victim is not keep and victim.blocks and not any(victim is s for s in scheduled):
                 self.blocks.release(victim)
                 victim.num_computed = 0
                 self.running.remove(victim)
@@ -136,44 +138,68 @@ class Scheduler:
             # tokens that still have to pass through the model before the next token can be sampled
             return s.total_len - s.num_computed
 
-        # running sequences that still have prompt (or recomputation after preemption) to do
-        prefill_running = [s for s in self.running if pending(s) > 1]
-        decode_running = [s for s in self.running if pending(s) == 1]
-        want_prefill = bool(prefill_running or self.waiting)
-
-        if decode_running and (cfg.dynamic_split_fuse or not want_prefill):
-            for s in decode_running:
+        def decode_phase() -> None:
+            nonlocal budget
+            for s in [r for r in self.running if pending(r) == 1]:
                 if budget <= 0 or len(seqs) >= cfg.max_num_seqs:
                     break
+                if not any(s is r for r in self.running):
+                    continue                       # preempted on behalf of an earlier sequence of this loop
                 while not self.blocks.grow(s, s.total_len):
-                    if not self._preempt_one(s):
+                    if not self._preempt_one(s, seqs):
                         break
-                if self.blocks.blocks_needed(s, s.total_len) > 0 or s not in self.running:
+                if self.blocks.blocks_needed(s, s.total_len) > 0:
                     continue
                 seqs.append(s)
                 num_new.append(1)
                 budget -= 1
-        if want_prefill and (cfg.dynamic_split_fuse or not seqs):
-            cands = list(prefill_running)
-            while self.waiting and len(self.running) + (len(cands) - len(prefill_running)) < cfg.max_num_seqs:
+
+        def prefill_phase(may_preempt: bool) -> None:
+            nonlocal budget
+            # taken after the decode phase: a preemption there moves a mid-prefill sequence from `running` to `waiting`
+            cands = [s for s in self.running if pending(s) > 1]
+            n_running_cands = len(cands)
+            while self.waiting and len(self.running) + (len(cands) - n_running_cands) < cfg.max_num_seqs:
                 cands.append(self.waiting.popleft())
+            back: List[Sequence] = []
             for s in cands:
+                is_running = any(s is r for r in self.running)
                 if budget <= 0 or len(seqs) >= cfg.max_num_seqs:
-                    if s not in self.running:
-                        self.waiting.appendleft(s)
+                    if not is_running:
+                        back.append(s)
                     continue
                 n = min(budget, s.total_len - s.num_computed)
-                if n <= 0 or not self.blocks.grow(s, s.num_computed + n):
-                    if s not in self.running:
-                        self.waiting.appendleft(s)
+                ok = n > 0 and self.blocks.grow(s, s.num_computed + n)
+                while n > 0 and not ok and may_preempt and not seqs and self._preempt_one(s, seqs):
+                    ok = self.blocks.grow(s, s.num_computed + n)      # last resort: the oldest candidate evicts younger ones
+                if not ok:
+                    if not is_running:
+                        back.append(s)
                     continue
-                if s not in self.running:
+                if not is_running:
                     self.running.append(s)
                     if s.slot < 0:
                         s.slot = self._free_slots.popleft()
                 seqs.append(s)
                 num_new.append(n)
                 budget -= n
+            for s in reversed(back):               # keep the arrival order of what could not be placed
+                self.waiting.appendleft(s)
+
+        def want_prefill() -> bool:
+            return bool(self.waiting or any(pending(s) > 1 for s in self.running))
+
+        if cfg.dynamic_split_fuse:
+            decode_phase()
+            if want_prefill():
+                prefill_phase(False)
+        else:
+            if want_prefill():
+                prefill_phase(False)
+            if not seqs:
+                decode_phase()                     # no prompt chunk fits: keep the running sequences going (they may preempt)
+        if not seqs and want_prefill():
+            prefill_phase(True)
         if not seqs:
             return None
         T = sum(num_new)

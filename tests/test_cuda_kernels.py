@@ -156,6 +156,19 @@ def test_gumbel_sampling_matches_softmax_and_shards_agree(ops):
     assert torch.equal(merged, full) and torch.equal(torch.maximum(m0, m1), full_max)
 
 
+def test_gumbel_noise_stays_finite_on_a_large_flat_vocabulary(ops):
+    # 64 rows x 128256 tokens x 4 steps = 33M uniforms: with a 24-bit mapping about two of them would round to exactly 1
+    V = 128256
+    logits = torch.zeros(64, V, device="cuda", dtype=torch.bfloat16)
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out_max = torch.empty(64, device="cuda")
+    for it in range(4):
+        step.fill_(it)
+        ids = ops.sample_gumbel(logits, 1.0, seed=3, step=step, out_max=out_max)
+        assert torch.isfinite(out_max).all() and int(ids.min()) >= 0 and int(ids.max()) < V
+    ops.check_status("sample_gumbel")
+
+
 def test_act_quant_fp8_groups_of_128(ops):
     torch.manual_seed(6)
     x = (torch.randn(37, 512, device="cuda") * torch.logspace(-2, 1, 512, device="cuda")).to(torch.bfloat16)
