@@ -14,6 +14,8 @@
 // pages are fetched once per group.
 #include <math_constants.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -104,6 +106,7 @@ __device__ __forceinline__ const uint8_t* kv_row_ptr(const PaKParams& p, const v
 // (sequence, kv head); K/V tiles of 64 keys double-buffered with cp.async.
 template <int D, int G, bool PAGED, bool F16>
 __global__ void __launch_bounds__(256, 1) pa_prefill_kernel(PaKParams p) {
+    pdl_enter_attn();
     constexpr int BM = 128, BN = 64, TOK = BM / G, CH = D / 8;   // CH = 16-byte chunks per row
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -305,6 +308,7 @@ __global__ void __launch_bounds__(256, 1) pa_prefill_kernel(PaKParams p) {
 // pa_decode_combine_kernel finishes.
 template <int D, int G, int PAGE>
 __global__ void __launch_bounds__(128) pa_decode_kernel(PaKParams p) {
+    pdl_enter_attn();
     constexpr int CH = D / 8;
     constexpr int NST = 3;   // page stages per warp
     extern __shared__ uint8_t smem_raw[];
@@ -482,6 +486,7 @@ __global__ void __launch_bounds__(128) pa_decode_kernel(PaKParams p) {
 
 template <int D>
 __global__ void pa_decode_combine_kernel(PaKParams p) {
+    pdl_enter_attn();
     const int b = blockIdx.x, hq = blockIdx.y;
     const int tok = p.subsequence_begins[b];
     const float* base = p.scratch + (((size_t)b * p.Hq + hq) * p.nsplit) * (D + 2);
@@ -501,13 +506,25 @@ __global__ void pa_decode_combine_kernel(PaKParams p) {
 }
 
 // ------------------------------------------------------------------------------ host side
+// Opt a kernel variant in to `smem` bytes of dynamic shared memory, once per device (bit `device` of `configured`).
+static int set_smem_once(std::atomic<uint64_t>& configured, const void* kern, int smem) {
+    int dev = 0;
+    OVB_CHECK_CUDA(cudaGetDevice(&dev));
+    const uint64_t bit = 1ull << (dev & 63);
+    if (configured.load(std::memory_order_acquire) & bit) return 0;
+    OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured.fetch_or(bit, std::memory_order_release);
+    return 0;
+}
+
 template <int D, int G, bool PAGED, bool F16>
 static int launch_prefill(const PaKParams& p, int num_q_tiles, cudaStream_t stream) {
     const int smem = 128 * D * 2 + 4 * 64 * D * 2 + 128;
     auto kern = pa_prefill_kernel<D, G, PAGED, F16>;
-    OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    static std::atomic<uint64_t> configured{0};   // one bit per device: the attribute is set on first use only
+    if (int rc = set_smem_once(configured, reinterpret_cast<const void*>(kern), smem)) return rc;
     dim3 grid(num_q_tiles, p.Hkv);
-    kern<<<grid, 256, smem, stream>>>(p);
+    OVB_CHECK_CUDA(launch_pdl(kern, dim3(grid), dim3(256), smem, stream, p));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -517,12 +534,13 @@ static int launch_decode(const PaKParams& p, cudaStream_t stream) {
     constexpr int PAGE = 16;
     const int smem = 16 * D * 2 + 4 * (3 * 2 * PAGE * D * 2) + 4 * G * (D + 2) * 4 + 128;
     auto kern = pa_decode_kernel<D, G, PAGE>;
-    OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    static std::atomic<uint64_t> configured{0};
+    if (int rc = set_smem_once(configured, reinterpret_cast<const void*>(kern), smem)) return rc;
     dim3 grid(p.B, p.Hkv, p.nsplit);
-    kern<<<grid, 128, smem, stream>>>(p);
+    OVB_CHECK_CUDA(launch_pdl(kern, dim3(grid), dim3(128), smem, stream, p));
     OVB_CHECK_CUDA(cudaGetLastError());
     if (p.nsplit > 1) {
-        pa_decode_combine_kernel<D><<<dim3(p.B, p.Hq), 128, 0, stream>>>(p);
+        OVB_CHECK_CUDA(launch_pdl(pa_decode_combine_kernel<D>, dim3(p.B, p.Hq), dim3(128), 0, stream, p));
         OVB_CHECK_CUDA(cudaGetLastError());
     }
     return 0;

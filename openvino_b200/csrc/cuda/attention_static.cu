@@ -37,7 +37,14 @@ extern "C" int ovb_paged_attention_decode_static(const ovb_pa_args* a, ovb_strea
     OVB_REQUIRE(a->max_q_len == 1 && a->T == a->B,
                 "ovb_paged_attention_decode_static: decode batches only (one query token per sequence), got max_q_len %d, T %d, B %d",
                 a->max_q_len, a->T, a->B);
-    OVB_REQUIRE(a->B > 0 && a->Hq > 0 && a->D > 0, "ovb_paged_attention_decode_static: bad sizes");
+    OVB_REQUIRE(a->B > 0 && a->Hq > 0 && a->D > 0 && a->Hkv > 0 && a->Hq % a->Hkv == 0, "ovb_paged_attention_decode_static: bad sizes");
+    // Only the split-KV decode kernel uses the scratch; other shapes would be served by the ragged kernel, which needs none.
+    // Refuse them here, so that a caller never believes it runs the split path when it does not.
+    const int group = a->Hq / a->Hkv;
+    OVB_REQUIRE(a->D == 128 && a->block_size == 16 && (group == 1 || group == 2 || group == 4 || group == 8),
+                "ovb_paged_attention_decode_static: the split-KV decode kernel serves head size 128, block size 16 and 1, 2, 4 or 8 query "
+                "heads per KV head (got D %d, block size %d, %d heads per KV head); use ovb_paged_attention for other shapes",
+                a->D, a->block_size, group);
     const int64_t need = ovb_pa_scratch_bytes(a->B, a->Hq, a->D, a->max_context_len);
     if (need > (int64_t)OVB_PA_STATIC_SCRATCH_BYTES) {
         ovb::set_error("ovb_paged_attention_decode_static: this batch needs %lld bytes of scratch (B %d x Hq %d x D %d) but the static "

@@ -30,12 +30,14 @@ __device__ __forceinline__ bool wait_flag_ge(const int* f, int epoch, int* statu
     return false;
 }
 
-__global__ void step_begin_kernel(int* epoch) { *epoch = *epoch + 1; }
+__global__ void step_begin_kernel(int* epoch) {
+    pdl_enter(); *epoch = *epoch + 1; }
 
 // One thread waits for *flag >= value with a caller-chosen poll budget; when the budget runs out the kernel records
 // STATUS_PEER_TIMEOUT in the status word and returns, so the context stays usable. The building block of the
 // failure-detection tests: a flag that nobody sets makes the wait run out.
 __global__ void wait_flag_kernel(const int* flag, int value, unsigned max_polls, int* status, int* result) {
+    pdl_enter();
     bool ok = false;
     for (unsigned i = 0; i < max_polls; ++i) {
         if (ld_acquire_sys(flag) >= value) { ok = true; break; }
@@ -56,6 +58,7 @@ struct CommK {
 
 // One CTA; thread = row. Every rank pushes (max value, global index) of its shard to every rank, then picks.
 __global__ void argmax_combine_kernel(CommK c, int* ids, const float* max_vals, int rows, int shard_size) {
+    pdl_enter();
     const int epoch = __ldcg(c.epoch);
     const int W = c.world;
     const int row = threadIdx.x;
@@ -91,6 +94,7 @@ __global__ void argmax_combine_kernel(CommK c, int* ids, const float* max_vals, 
 
 // Small-tensor all-reduce (one-shot): CTA b owns pieces b, b + grid, ...; flags: one per (CTA, source rank).
 __global__ void allreduce_bf16_kernel(CommK c, long long data_off, long long npieces, long long rank_stride) {
+    pdl_enter();
     const int epoch = __ldcg(c.epoch);
     const int W = c.world;
     const uint4* mine = reinterpret_cast<const uint4*>(c.heap[c.rank] + data_off);
@@ -186,8 +190,8 @@ int ovb_comm_close(void* ptr) {
 
 int ovb_comm_step_begin(const ovb_comm* c, ovb_stream_t stream) {
     OVB_REQUIRE(c != nullptr && c->heap[c->rank] != nullptr, "ovb_comm_step_begin: bad communicator");
-    step_begin_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<int*>(static_cast<uint8_t*>(c->heap[c->rank]) + c->epoch_off));
+    OVB_CHECK_CUDA(launch_pdl(step_begin_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(stream), 
+        reinterpret_cast<int*>(static_cast<uint8_t*>(c->heap[c->rank]) + c->epoch_off)));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -205,7 +209,7 @@ int ovb_comm_argmax_combine(const ovb_comm* c, int* ids, const float* max_vals, 
     if (int rc = fill(c, &k, c ? c->site : 0)) return rc;
     OVB_REQUIRE(c->flags_per_site >= kArgmaxDataOff + 2 * c->world * kArgmaxRowsCap * 2, "ovb_comm_argmax_combine: flag area of a site is too small");
     const int threads = ((rows > c->world ? rows : c->world) + 31) / 32 * 32;
-    argmax_combine_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(k, ids, max_vals, rows, shard_size);
+    OVB_CHECK_CUDA(launch_pdl(argmax_combine_kernel, dim3(1), dim3(threads), 0, static_cast<cudaStream_t>(stream), k, ids, max_vals, rows, shard_size));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -222,7 +226,7 @@ int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream
     int grid = (int)((npieces + 255) / 256);
     if (grid > 148) grid = 148;
     OVB_REQUIRE((int64_t)grid * c->world <= c->flags_per_site, "ovb_comm_allreduce_bf16: flag area of a site is too small");
-    allreduce_bf16_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(k, off, npieces, rank_stride);
+    OVB_CHECK_CUDA(launch_pdl(allreduce_bf16_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), k, off, npieces, rank_stride));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

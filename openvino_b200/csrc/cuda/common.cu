@@ -1,5 +1,6 @@
 #include <cudaTypedefs.h>
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -30,6 +31,16 @@ int* status_word() {
         g_status[dev] = p;
     }
     return g_status[dev];
+}
+
+static int g_pdl = -1;   // -1: not decided yet (environment), 0 / 1
+
+bool pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* e = getenv("OVB_PDL");
+        g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl != 0;
 }
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -76,6 +87,12 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 extern "C" {
 
 int ovb_version(void) { return 100; }
+
+int ovb_set_pdl(int on) {
+    const int before = ovb::pdl_enabled() ? 1 : 0;
+    ovb::g_pdl = on ? 1 : 0;
+    return before;
+}
 
 const char* ovb_last_error(void) { return ovb::g_err; }
 

@@ -47,4 +47,42 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Programmatic dependent launch: kernels of a stream that call pdl_wait() (sm100_ptx.cuh) are launched with the
+// programmatic-stream-serialization attribute, so that the preamble of a kernel (barrier set-up, tensor-memory allocation,
+// the first weight fetches) runs under the tail of the kernel before it. Works inside stream capture (the edge becomes a
+// programmatic dependency of the graph). OVB_PDL=0 in the environment, or ovb_set_pdl(0), turns the attribute off.
+bool pdl_enabled();
+
+// Launch `kern` with the attribute (when enabled). Only for kernels whose every thread passes pdl_wait() before it touches
+// memory that an earlier kernel of the stream may write or still read.
+template <class... P, class... A>
+inline cudaError_t launch_pdl(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
+// Plain launch (fully ordered after the stream's earlier work). Kernels that write what a later GEMM reads as its
+// WEIGHT operand (the re-packing kernels) use this and never call pdl_trigger(): a GEMM fetches weights before its own
+// pdl_wait(), which is only sound while no kernel that may still be running writes them.
+template <class... P, class... A>
+inline cudaError_t launch_serial(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 }  // namespace ovb

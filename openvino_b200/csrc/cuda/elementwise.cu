@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(THREADS)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
                const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ y,
                __nv_bfloat16* __restrict__ residual_out, int cols, float eps) {
+    pdl_enter();
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int nvec = cols >> 3;
@@ -102,6 +103,7 @@ template <class E, int THREADS, int MAXV>
 __global__ void __launch_bounds__(THREADS)
 layernorm_kernel(const E* __restrict__ x, const E* __restrict__ residual, const E* __restrict__ gamma,
                  const E* __restrict__ beta, E* __restrict__ y, int cols, float eps) {
+    pdl_enter();
     __shared__ float red[32];
     const size_t row = blockIdx.x;
     const int nvec = cols >> 3;
@@ -157,6 +159,7 @@ layernorm_kernel(const E* __restrict__ x, const E* __restrict__ residual, const 
 
 // ------------------------------------------------------------------------------------ SwiGLU gate
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int F) {
+    pdl_enter();
     const int fv = F >> 3;
     const size_t total = (size_t)rows * fv;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -179,6 +182,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 // Router: softmax over the E expert logits of a token, keep the top k, renormalise them to sum 1 (Mixtral rule).
 // Output: dense [T, E] fp32 routing weights (0 for experts that were not selected). One thread per token, E <= 64.
 __global__ void moe_route_topk_kernel(const float* __restrict__ logits, float* __restrict__ weights, int T, int E, int k) {
+    pdl_enter();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
     float v[64];
@@ -204,6 +208,7 @@ __global__ void moe_route_topk_kernel(const float* __restrict__ logits, float* _
 // A token that is not routed to an expert gets zeros there, so the stacked down projection sums exactly the routed experts.
 __global__ void moe_silu_mul_scale_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ w, __nv_bfloat16* __restrict__ out,
                                           int rows, int F, int nloc, int E, int e0) {
+    pdl_enter();
     const int fv = F >> 3;
     const size_t total = (size_t)rows * nloc * fv;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -231,6 +236,7 @@ __global__ void moe_silu_mul_scale_kernel(const __nv_bfloat16* __restrict__ gu, 
 
 __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
                            __nv_bfloat16* __restrict__ out, size_t nvec) {
+    pdl_enter();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
         Pack8 x, y, o;
         x.u = reinterpret_cast<const uint4*>(a)[i];
@@ -245,6 +251,7 @@ __global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloa
 template <class IdT>
 __global__ void embedding_kernel(const IdT* __restrict__ ids, const uint4* __restrict__ table,
                                  uint4* __restrict__ out, int rows, int vec_per_row, int vocab) {
+    pdl_enter();
     const size_t total = (size_t)rows * vec_per_row;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / vec_per_row;
@@ -262,6 +269,7 @@ __global__ void embedding_kernel(const IdT* __restrict__ ids, const uint4* __res
 // last_token[tok_dst[i]] (tok_dst < 0: the step ended inside the prompt, nothing to record).
 __global__ void resolve_ids_kernel(int* __restrict__ ids, const int* __restrict__ tok_src,
                                    const int* __restrict__ last_token, int T) {
+    pdl_enter();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t < T) {
         const int s = tok_src[t];
@@ -270,6 +278,7 @@ __global__ void resolve_ids_kernel(int* __restrict__ ids, const int* __restrict_
 }
 __global__ void scatter_tokens_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_dst,
                                       int* __restrict__ last_token, int B) {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < B) {
         const int d = tok_dst[i];
@@ -282,6 +291,7 @@ template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int vocab, void* __restrict__ out_ids, int ids_i32,
               float* __restrict__ out_max) {
+    pdl_enter();
     __shared__ float sv[THREADS / 32];
     __shared__ int si[THREADS / 32];
     const size_t row = blockIdx.x;
@@ -344,6 +354,7 @@ __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int*
                                      const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache,
                                      __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D, float log2_theta,
                                      int block_size) {
+    pdl_enter();
     const int t = blockIdx.x;
     const int half = D >> 1;
     const float pos = float(positions[t]);
@@ -389,6 +400,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
                                          const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ k_cache,
                                          __nv_bfloat16* __restrict__ v_cache, int Hq, int Hkv, int D, float log2_theta,
                                          int block_size) {
+    pdl_enter();
     const int t = blockIdx.x;
     const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -422,6 +434,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
 // For every local expert: the indices of the tokens routed to it, in token order, and their number. One CTA per expert
 // walks the tokens in chunks of its size; positions come from a ballot / prefix sum, so the order is deterministic.
 __global__ void moe_group_kernel(const float* __restrict__ route, int T, int E, int e0, int* __restrict__ idx, int* __restrict__ counts, int idx_stride) {
+    pdl_enter();
     const int e = blockIdx.x;
     __shared__ int warp_sums[32];
     __shared__ int base_s;
@@ -451,6 +464,7 @@ __global__ void moe_group_kernel(const float* __restrict__ route, int T, int E, 
 // act[i, f] = silu(gu[i, f]) * gu[i, F + f] * route[idx[i], e]  for the gathered rows of one expert
 __global__ void moe_silu_mul_rows_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route, const int* __restrict__ idx,
                                          __nv_bfloat16* __restrict__ out, int rows, int F, int E, int e) {
+    pdl_enter();
     const int fv = F >> 3;
     const size_t total = (size_t)rows * fv;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -473,6 +487,7 @@ __global__ void moe_silu_mul_rows_kernel(const __nv_bfloat16* __restrict__ gu, c
 // dst[idx[i], :] += src[i, :]; the rows of one expert are distinct tokens, so no two threads touch the same element
 __global__ void moe_scatter_add_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx, __nv_bfloat16* __restrict__ dst,
                                        int rows, int H, int ld_dst) {
+    pdl_enter();
     const int hv = H >> 3;
     const size_t total = (size_t)rows * hv;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -493,6 +508,7 @@ __global__ void moe_scatter_add_kernel(const __nv_bfloat16* __restrict__ src, co
 // One warp per (token, group); a lane holds four channels. Role of the reference's dynamic_quantize_gpu_opt
 // (src/plugins/intel_gpu/src/kernel_selector/cl_kernels/dynamic_quantize_gpu_opt.cl:82) with fp8 instead of int8 output.
 __global__ void act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales, int rows, int cols) {
+    pdl_enter();
     const int groups = cols / 128;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= rows * groups) return;
@@ -521,6 +537,7 @@ __global__ void act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, uint8_
 // preemption, beam reordering). One CTA per (pair, cache); 16-byte pieces. Role of pa_kv_cache_reorder_ref.cl.
 __global__ void kv_block_copy_kernel(uint4* __restrict__ k_cache, uint4* __restrict__ v_cache, const int* __restrict__ src,
                                      const int* __restrict__ dst, size_t pieces_per_block) {
+    pdl_enter();
     uint4* cache = blockIdx.y == 0 ? k_cache : v_cache;
     const size_t s = (size_t)src[blockIdx.x] * pieces_per_block, d = (size_t)dst[blockIdx.x] * pieces_per_block;
     if (s == d) return;
@@ -533,6 +550,7 @@ __global__ void kv_block_copy_kernel(uint4* __restrict__ k_cache, uint4* __restr
 // fills one 16-byte piece (8 consecutive k of one output position); the 16-bit payload is copied as it is (bf16 or fp16).
 __global__ void im2col_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ cols, int B, int C, int H, int W, int kh, int kw,
                               int sh, int sw, int pt, int pl, int dh, int dw, int Ho, int Wo, int Kd, int Kpad) {
+    pdl_enter();
     const int pieces = Kpad >> 3;
     const size_t total = (size_t)B * Ho * Wo * pieces;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -649,10 +667,10 @@ int ovb_rmsnorm(const void* x, const void* residual, const void* gamma, void* y,
     auto Y = (__nv_bfloat16*)y;
     auto RO = (__nv_bfloat16*)residual_out;
     const int nvec = cols / 8;
-    if (nvec <= 256) rmsnorm_kernel<256, 1><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
-    else if (nvec <= 512) rmsnorm_kernel<256, 2><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
-    else if (nvec <= 1024) rmsnorm_kernel<256, 4><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
-    else rmsnorm_kernel<256, 8><<<rows, 256, 0, stream>>>(X, R, G, Y, RO, cols, eps);
+    if (nvec <= 256) OVB_CHECK_CUDA(launch_pdl(rmsnorm_kernel<256, 1>, dim3(rows), dim3(256), 0, stream, X, R, G, Y, RO, cols, eps));
+    else if (nvec <= 512) OVB_CHECK_CUDA(launch_pdl(rmsnorm_kernel<256, 2>, dim3(rows), dim3(256), 0, stream, X, R, G, Y, RO, cols, eps));
+    else if (nvec <= 1024) OVB_CHECK_CUDA(launch_pdl(rmsnorm_kernel<256, 4>, dim3(rows), dim3(256), 0, stream, X, R, G, Y, RO, cols, eps));
+    else OVB_CHECK_CUDA(launch_pdl(rmsnorm_kernel<256, 8>, dim3(rows), dim3(256), 0, stream, X, R, G, Y, RO, cols, eps));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -663,13 +681,13 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
     OVB_REQUIRE(x && gamma && beta && y && rows > 0, "ovb_layernorm: null operand");
     OVB_REQUIRE(cols % 8 == 0 && cols <= 256 * 8 * 4, "ovb_layernorm: cols=%d must be a multiple of 8 and <= 8192", cols);
     if (is_f16)
-        layernorm_kernel<__half, 256, 4><<<rows, 256, 0, stream>>>((const __half*)x, (const __half*)residual,
+        OVB_CHECK_CUDA(launch_pdl(layernorm_kernel<__half, 256, 4>, dim3(rows), dim3(256), 0, stream, (const __half*)x, (const __half*)residual,
                                                                   (const __half*)gamma, (const __half*)beta, (__half*)y,
-                                                                  cols, eps);
+                                                                  cols, eps));
     else
-        layernorm_kernel<__nv_bfloat16, 256, 4><<<rows, 256, 0, stream>>>(
+        OVB_CHECK_CUDA(launch_pdl(layernorm_kernel<__nv_bfloat16, 256, 4>, dim3(rows), dim3(256), 0, stream, 
             (const __nv_bfloat16*)x, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)gamma,
-            (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, cols, eps);
+            (const __nv_bfloat16*)beta, (__nv_bfloat16*)y, cols, eps));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -678,7 +696,7 @@ int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(gu && out && rows > 0 && F % 8 == 0, "ovb_silu_mul: bad arguments");
     const size_t total = (size_t)rows * (F / 8);
-    silu_mul_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F);
+    OVB_CHECK_CUDA(launch_pdl(silu_mul_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -686,7 +704,7 @@ int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream
 int ovb_moe_route_topk(const float* logits, float* weights, int T, int E, int k, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(logits && weights && T > 0 && E > 0 && E <= 64 && k > 0 && k <= E, "ovb_moe_route_topk: need 1 <= k <= E <= 64");
-    moe_route_topk_kernel<<<(T + 127) / 128, 128, 0, stream>>>(logits, weights, T, E, k);
+    OVB_CHECK_CUDA(launch_pdl(moe_route_topk_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, logits, weights, T, E, k));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -695,7 +713,7 @@ int ovb_moe_silu_mul_scale(const void* gu, const float* weights, void* out, int 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(gu && weights && out && rows > 0 && F % 8 == 0 && nloc > 0 && e0 >= 0 && e0 + nloc <= E, "ovb_moe_silu_mul_scale: bad arguments");
     const size_t total = (size_t)rows * nloc * (F / 8);
-    moe_silu_mul_scale_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, weights, (__nv_bfloat16*)out, rows, F, nloc, E, e0);
+    OVB_CHECK_CUDA(launch_pdl(moe_silu_mul_scale_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const __nv_bfloat16*)gu, weights, (__nv_bfloat16*)out, rows, F, nloc, E, e0));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -703,7 +721,7 @@ int ovb_moe_silu_mul_scale(const void* gu, const float* weights, void* out, int 
 int ovb_moe_group(const float* route, int T, int E, int e0, int nloc, int* idx, int idx_stride, int* counts, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(route && idx && counts && T > 0 && nloc > 0 && e0 >= 0 && e0 + nloc <= E && idx_stride >= T, "ovb_moe_group: bad arguments");
-    moe_group_kernel<<<nloc, 1024, 0, stream>>>(route, T, E, e0, idx, counts, idx_stride);
+    OVB_CHECK_CUDA(launch_pdl(moe_group_kernel, dim3(nloc), dim3(1024), 0, stream, route, T, E, e0, idx, counts, idx_stride));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -711,8 +729,8 @@ int ovb_moe_group(const float* route, int T, int E, int e0, int nloc, int* idx, 
 int ovb_moe_silu_mul_rows(const void* gu, const float* route, const int* idx, void* out, int rows, int F, int E, int e, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(gu && route && idx && out && rows > 0 && F % 8 == 0 && e >= 0 && e < E, "ovb_moe_silu_mul_rows: bad arguments");
-    moe_silu_mul_rows_kernel<<<grid_for((size_t)rows * (F / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)gu, route, idx, (__nv_bfloat16*)out,
-                                                                                      rows, F, E, e);
+    OVB_CHECK_CUDA(launch_pdl(moe_silu_mul_rows_kernel, dim3(grid_for((size_t)rows * (F / 8), 256)), dim3(256), 0, stream, (const __nv_bfloat16*)gu, route, idx, (__nv_bfloat16*)out,
+                                                                                      rows, F, E, e));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -720,7 +738,7 @@ int ovb_moe_silu_mul_rows(const void* gu, const float* route, const int* idx, vo
 int ovb_moe_scatter_add(const void* src, const int* idx, void* dst, int rows, int H, int ld_dst, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(src && idx && dst && rows > 0 && H % 8 == 0 && ld_dst % 8 == 0, "ovb_moe_scatter_add: bad arguments");
-    moe_scatter_add_kernel<<<grid_for((size_t)rows * (H / 8), 256), 256, 0, stream>>>((const __nv_bfloat16*)src, idx, (__nv_bfloat16*)dst, rows, H, ld_dst);
+    OVB_CHECK_CUDA(launch_pdl(moe_scatter_add_kernel, dim3(grid_for((size_t)rows * (H / 8), 256)), dim3(256), 0, stream, (const __nv_bfloat16*)src, idx, (__nv_bfloat16*)dst, rows, H, ld_dst));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -728,8 +746,8 @@ int ovb_moe_scatter_add(const void* src, const int* idx, void* dst, int rows, in
 int ovb_add(const void* a, const void* b, void* out, int64_t n, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(a && b && out && n % 8 == 0, "ovb_add: n must be a multiple of 8");
-    add_kernel<<<grid_for(n / 8, 256), 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
-                                                         (__nv_bfloat16*)out, (size_t)n / 8);
+    OVB_CHECK_CUDA(launch_pdl(add_kernel, dim3(grid_for(n / 8, 256)), dim3(256), 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+                                                         (__nv_bfloat16*)out, (size_t)n / 8));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -740,11 +758,11 @@ int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, in
     OVB_REQUIRE(ids && table && out && rows > 0 && cols % 8 == 0, "ovb_embedding: bad arguments");
     const size_t total = (size_t)rows * (cols / 8);
     if (ids_i32)
-        embedding_kernel<int><<<grid_for(total, 256), 256, 0, stream>>>((const int*)ids, (const uint4*)table, (uint4*)out,
-                                                                        rows, cols / 8, vocab);
+        OVB_CHECK_CUDA(launch_pdl(embedding_kernel<int>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const int*)ids, (const uint4*)table, (uint4*)out,
+                                                                        rows, cols / 8, vocab));
     else
-        embedding_kernel<int64_t><<<grid_for(total, 256), 256, 0, stream>>>((const int64_t*)ids, (const uint4*)table,
-                                                                            (uint4*)out, rows, cols / 8, vocab);
+        OVB_CHECK_CUDA(launch_pdl(embedding_kernel<int64_t>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const int64_t*)ids, (const uint4*)table,
+                                                                            (uint4*)out, rows, cols / 8, vocab));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -752,7 +770,7 @@ int ovb_embedding(const void* ids, int ids_i32, const void* table, void* out, in
 int ovb_resolve_ids(int* ids, const int* tok_src, const int* last_token, int T, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(ids && tok_src && last_token && T > 0, "ovb_resolve_ids: bad arguments");
-    resolve_ids_kernel<<<(T + 255) / 256, 256, 0, stream>>>(ids, tok_src, last_token, T);
+    OVB_CHECK_CUDA(launch_pdl(resolve_ids_kernel, dim3((T + 255) / 256), dim3(256), 0, stream, ids, tok_src, last_token, T));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -760,7 +778,7 @@ int ovb_resolve_ids(int* ids, const int* tok_src, const int* last_token, int T, 
 int ovb_scatter_tokens(const int* tokens, const int* tok_dst, int* last_token, int B, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(tokens && tok_dst && last_token && B > 0, "ovb_scatter_tokens: bad arguments");
-    scatter_tokens_kernel<<<(B + 255) / 256, 256, 0, stream>>>(tokens, tok_dst, last_token, B);
+    OVB_CHECK_CUDA(launch_pdl(scatter_tokens_kernel, dim3((B + 255) / 256), dim3(256), 0, stream, tokens, tok_dst, last_token, B));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -769,7 +787,7 @@ int ovb_argmax(const void* logits, int ld, int rows, int vocab, void* out_ids, i
                ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0, "ovb_argmax: bad arguments");
-    argmax_kernel<1024><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, out_ids, ids_i32, out_max);
+    OVB_CHECK_CUDA(launch_pdl(argmax_kernel<1024>, dim3(rows), dim3(1024), 0, stream, (const __nv_bfloat16*)logits, ld, vocab, out_ids, ids_i32, out_max));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -782,11 +800,11 @@ int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void
     if (D % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 3) == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 3) == 0 &&
         (reinterpret_cast<uintptr_t>(v_cache) & 3) == 0) {
         const int heads = Hq + 2 * Hkv;
-        rope_kv_write_vec_kernel<<<dim3(T, (heads + 3) / 4), 128, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
-                                                                                (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
+        OVB_CHECK_CUDA(launch_pdl(rope_kv_write_vec_kernel, dim3(T, (heads + 3) / 4), dim3(128), 0, stream, (__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
+                                                                                (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size));
     } else {
-        rope_kv_write_kernel<<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
-                                                    (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size);
+        OVB_CHECK_CUDA(launch_pdl(rope_kv_write_kernel, dim3(T), dim3(256), 0, stream, (__nv_bfloat16*)qkv, positions, slot_map, (__nv_bfloat16*)k_cache,
+                                                    (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size));
     }
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
@@ -798,7 +816,7 @@ int ovb_act_quant_fp8(const void* x, void* q, float* scales, int rows, int cols,
     OVB_REQUIRE(cols % 128 == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0,
                 "ovb_act_quant_fp8: the channel count must be a multiple of 128 and the rows 8-byte aligned");
     const size_t warps = (size_t)rows * (cols / 128);
-    act_quant_fp8_kernel<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)x, (uint8_t*)q, scales, rows, cols);
+    OVB_CHECK_CUDA(launch_pdl(act_quant_fp8_kernel, dim3((unsigned)((warps * 32 + 255) / 256)), dim3(256), 0, stream, (const __nv_bfloat16*)x, (uint8_t*)q, scales, rows, cols));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -809,7 +827,7 @@ int ovb_kv_block_copy(void* k_cache, void* v_cache, const int* src_blocks, const
     OVB_REQUIRE(k_cache && v_cache && src_blocks && dst_blocks, "ovb_kv_block_copy: null operand");
     OVB_REQUIRE(block_bytes > 0 && block_bytes % 16 == 0, "ovb_kv_block_copy: a block must be a multiple of 16 bytes");
     if (num_pairs <= 0) return 0;
-    kv_block_copy_kernel<<<dim3(num_pairs, 2), 256, 0, stream>>>((uint4*)k_cache, (uint4*)v_cache, src_blocks, dst_blocks, (size_t)block_bytes / 16);
+    OVB_CHECK_CUDA(launch_pdl(kv_block_copy_kernel, dim3(num_pairs, 2), dim3(256), 0, stream, (uint4*)k_cache, (uint4*)v_cache, src_blocks, dst_blocks, (size_t)block_bytes / 16));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -821,8 +839,8 @@ int ovb_im2col(const void* x, void* cols, int B, int C, int H, int W, int kh, in
     OVB_REQUIRE(Kpad % 8 == 0 && Kpad >= C * kh * kw, "ovb_im2col: Kpad must be a multiple of 8 that covers C*kh*kw");
     OVB_REQUIRE((reinterpret_cast<uintptr_t>(cols) & 15) == 0, "ovb_im2col: output must be 16-byte aligned");
     const size_t total = (size_t)B * Ho * Wo * (Kpad / 8);
-    im2col_kernel<<<grid_for(total, 256), 256, 0, stream>>>((const uint16_t*)x, (uint16_t*)cols, B, C, H, W, kh, kw, sh, sw, pt, pl, dh, dw,
-                                                            Ho, Wo, C * kh * kw, Kpad);
+    OVB_CHECK_CUDA(launch_pdl(im2col_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const uint16_t*)x, (uint16_t*)cols, B, C, H, W, kh, kw, sh, sw, pt, pl, dh, dw,
+                                                            Ho, Wo, C * kh * kw, Kpad));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -832,7 +850,7 @@ int ovb_pack_w16(const void* w, void* w_out, int N, int K, ovb_stream_t stream_)
     OVB_REQUIRE(w && w_out && N > 0 && K % 64 == 0, "ovb_pack_w16: K must be a multiple of 64");
     OVB_CHECK_CUDA(cudaMemsetAsync(w_out, 0, (size_t)((N + 127) / 128) * 128 * K * 2, stream));
     const size_t npieces = (size_t)N * K / 8;
-    pack_w16_kernel<<<grid_for(npieces, 256), 256, 0, stream>>>((const uint4*)w, (uint4*)w_out, npieces, K);
+    OVB_CHECK_CUDA(launch_serial(pack_w16_kernel, dim3(grid_for(npieces, 256)), dim3(256), 0, stream, (const uint4*)w, (uint4*)w_out, npieces, K));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -847,15 +865,15 @@ int ovb_pack_u4(const void* w_ir, const void* scales_ir, const void* zps_ir, int
     OVB_REQUIRE(group_size % 64 == 0, "ovb_pack_u4: group_size must be a multiple of 64");
     const size_t chunks = (size_t)((N + 127) / 128) * (K / 64);
     OVB_CHECK_CUDA(cudaMemsetAsync(w_out, 0, chunks * 4608, stream));
-    pack_u4_kernel<<<grid_for(nwords, 256), 256, 0, stream>>>((const uint32_t*)w_ir, (uint32_t*)w_out, nwords, K);
+    OVB_CHECK_CUDA(launch_serial(pack_u4_kernel, dim3(grid_for(nwords, 256)), dim3(256), 0, stream, (const uint32_t*)w_ir, (uint32_t*)w_out, nwords, K));
     OVB_CHECK_CUDA(cudaGetLastError());
     const int G = K / group_size;
-    pack_scale_zp_kernel<<<grid_for((size_t)N * G, 256), 256, 0, stream>>>(
+    OVB_CHECK_CUDA(launch_serial(pack_scale_zp_kernel, dim3(grid_for((size_t)N * G, 256)), dim3(256), 0, stream, 
         (const __half*)scales_ir, (const uint8_t*)zps_ir, zp_is_u8, (__nv_bfloat16*)scales_out, (__nv_bfloat16*)zps_out,
-        N, G, 16.0f, 8.0f);
+        N, G, 16.0f, 8.0f));
     OVB_CHECK_CUDA(cudaGetLastError());
-    embed_pairs_kernel<<<grid_for(chunks * 128, 256), 256, 0, stream>>>((const uint32_t*)scales_out, (uint32_t*)w_out, N, K / 64,
-                                                                        group_size / 64, chunks * 128);
+    OVB_CHECK_CUDA(launch_serial(embed_pairs_kernel, dim3(grid_for(chunks * 128, 256)), dim3(256), 0, stream, (const uint32_t*)scales_out, (uint32_t*)w_out, N, K / 64,
+                                                                        group_size / 64, chunks * 128));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

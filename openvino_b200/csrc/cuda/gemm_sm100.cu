@@ -26,6 +26,8 @@
 //    16-byte stores (residual added on the way out).
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -75,20 +77,13 @@ struct GemmKParams {
     long long out_off;        // `out` as an offset in the heap (two-shot owners write it on every rank)
     const int* epoch;         // device word holding the current step number (local memory)
     long long count_off;      // one int32 in the heap: CTAs of a two-shot launch that have finished their tile
+    // NVLink multicast (NVLS): multicast mapping of the symmetric heap (NULL: plain peer stores, protocols above) and this
+    // call site's barrier words, [tile][kNvlsFlagStride] int32, as an offset in the heap
+    uint8_t* mc;
+    long long nvls_flags_off;
 };
 
 constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 us apart
-
-// Tuning aid, compiled out unless the file is built with -DOVB_GEMM_TRACE: CTA 0 writes cycle counts of its control
-// lanes (waits vs. issue) into the split-K workspace. TR(x) keeps the statements out of normal builds entirely.
-#ifdef OVB_GEMM_TRACE
-#define TR(...) __VA_ARGS__
-__device__ long long g_cta_trace[16384 * 4];   // per CTA: start, last MMA issued, end (globaltimer ns), SM id
-__device__ long long g_it_trace[64 * 8];         // CTA 0, per iteration: clock64 at the control lanes' hand-over points
-#define TRI(i, k) if (blockIdx.x == 0 && blockIdx.z == 0 && (i) < 64) g_it_trace[(i) * 8 + (k)] = clock64();
-#else
-#define TR(...)
-#endif
 
 template <bool F16>
 struct Elem {
@@ -222,9 +217,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    TR(long long tr_k0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_k0));)
-    TR(const int tr_cta = (blockIdx.z * gridDim.x + blockIdx.x) & 16383;
-       if (threadIdx.x == 0) { uint32_t sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); g_cta_trace[tr_cta * 4] = tr_k0; g_cta_trace[tr_cta * 4 + 3] = sm; })
     // Tile order: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so the
     // CTAs that are resident together share a few weight tiles and a few token tiles in L2.
     int n_tile, t_tile;
@@ -272,8 +264,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    TR(if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-           reinterpret_cast<long long*>(p.ws)[24] = t - tr_k0; })
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
@@ -285,7 +275,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 // running pointers only. The token tiles have a producer lane of their own in warp X_PRODUCER_WARP.)
                 int wslot = 0;
                 uint32_t wpar = 1;                    // parity to wait for on the "empty" barriers
-                TR(long long tr_t0 = clock64(); long long tr_w = 0;)
                 const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * p.w_kb_stride + kb_begin) * (WMODE == OVB_W_U4 ? WQ_SLOT : WQ_BYTES);
                 uint32_t wdst = smem_u32(pring);
                 // u8: pairs come from the [group][N] table with a second copy
@@ -295,7 +284,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 int kcoord = kb_begin * TILE_K;
                 for (int iw = 0; iw < num_it; ++iw) {
                     if (!mbar_wait(&p_empty[wslot], wpar, abort_flag, p.status)) break;
-                    TR(const long long tr_a = clock64(); TRI(iw, 7))
                     const int nk = min(KPS, num_kb - iw * KPS);
                     mbar_arrive_expect_tx(&p_full[wslot], nk * WQ_SLOT);
                     if (WMODE == OVB_W_U4) {
@@ -314,25 +302,36 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     }
                     wdst += RING_SLOT;
                     if (++wslot == pslots) { wslot = 0; wpar ^= 1; wdst = smem_u32(pring); }
-                    TR(tr_w += clock64() - tr_a;)
                 }
-                TR(if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
-                       o[0] = clock64() - tr_t0; o[1] = tr_w; o[4] = num_kb; })
             } else {
-                uint32_t phase = 0;
-                int s = 0;
-                for (int i = 0; i < num_kb; ++i) {
-                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status)) break;
+                auto load_w = [&](int s, int kb) {
                     uint8_t* st = smem + s * STAGE_BYTES;
-                    const int kb = kb_begin + i;
-                    mbar_arrive_expect_tx(&full_x[s], X_BYTES + W_BYTES);
-                    tma_load_2d(st, &tmX, &full_x[s], kb * TILE_K, t0);
                     if (p.w_tiled != nullptr)
                         bulk_load_1d(st + X_BYTES, p.w_tiled + ((size_t)n_tile * p.w_kb_stride + kb) * W_BYTES, W_BYTES, &full_x[s]);
                     else
                         tma_load_2d(st + X_BYTES, &tmW, &full_x[s], kb * TILE_K, n0);
+                };
+                // Weights are constants: the first ring of weight tiles is requested before the kernel that produces
+                // the activations has finished (programmatic dependent launch); the token tiles follow after the wait.
+                const int pre = min(stages, num_kb);
+                for (int i = 0; i < pre; ++i) {
+                    mbar_arrive_expect_tx(&full_x[i], X_BYTES + W_BYTES);
+                    load_w(i, kb_begin + i);
+                }
+                pdl_wait();
+                if (OVB_PDL_GEMM == 2) pdl_trigger();
+                for (int i = 0; i < pre; ++i) tma_load_2d(smem + i * STAGE_BYTES, &tmX, &full_x[i], (kb_begin + i) * TILE_K, t0);
+                uint32_t phase = pre == stages ? 1 : 0;
+                int s = pre == stages ? 0 : pre;
+                for (int i = pre; i < num_kb; ++i) {
+                    if (!mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status)) break;
+                    const int kb = kb_begin + i;
+                    mbar_arrive_expect_tx(&full_x[s], X_BYTES + W_BYTES);
+                    tma_load_2d(smem + s * STAGE_BYTES, &tmX, &full_x[s], kb * TILE_K, t0);
+                    load_w(s, kb);
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
+                if (OVB_PDL_GEMM == 1) pdl_trigger();
             }
         }
         __syncwarp();
@@ -343,10 +342,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             int xs = 0;
             int xk = kb_begin * TILE_K;
             uint32_t xdst = smem_u32(smem);
-            TR(long long tr_t0 = clock64(); long long tr_x = 0;)
+            // the activations come from the kernel before this one; the weight producer (constants) does not wait
+            pdl_wait();
+            if (OVB_PDL_GEMM == 2) pdl_trigger();
             for (int ix = 0; ix < num_it; ++ix) {
                 if (!mbar_wait(&empty[xs], xpar, abort_flag, p.status)) break;
-                TR(const long long tr_c = clock64(); TRI(ix, 6))
                 const int nk = min(KPS, num_kb - ix * KPS);
                 mbar_arrive_expect_tx(&full_x[xs], nk * X_BYTES);
                 for (int t = 0; t < nk; ++t) {
@@ -358,10 +358,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
                 xdst += STAGE_BYTES;
                 if (++xs == stages) { xs = 0; xpar ^= 1; xdst = smem_u32(smem); }
-                TR(tr_x += clock64() - tr_c;)
             }
-            TR(if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
-                   o[2] = tr_x; o[3] = clock64() - tr_t0; })
+            if (OVB_PDL_GEMM == 1) pdl_trigger();
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -374,13 +372,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         {
             uint32_t phase = 0;
             int s = 0;
-            TR(long long tr_t0 = clock64(), tr_wx = 0, tr_wd = 0, tr_is = 0;)
             for (int i = 0; i < (QUANT ? num_it : num_kb); ++i) {
-                TR(const long long tr_a = clock64();)
                 // every lane polls the same barrier word (no divergence, no shuffle): one wait per stage covers both the
                 // token tile and the expanded weights
                 const bool ok = mbar_wait(&full_x[s], phase, abort_flag, p.status);
-                TR(const long long tr_c = clock64(); tr_wx += tr_c - tr_a; tr_wd += tr_c - tr_a; if (lane == 0) { TRI(i, 0) TRI(i, 1) })
                 if (!ok) break;
                 tc_fence_after_sync();
                 // descriptors differ only in the 16-byte-unit start address (low 14 bits, no carry out here)
@@ -403,14 +398,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     for (int k = 1; k < TILE_K / 16; ++k) umma_f16_ss_elect(tmem_base, da0 + 2 * k, db0 + 2 * k, idesc, 1u);
                 }
                 umma_commit_elect(&empty[s]);
-                TR(tr_is += clock64() - tr_c; if (lane == 0) { TRI(i, 2) })
                 if (++s == stages) { s = 0; phase ^= 1; }
             }
             umma_commit_elect(acc_full);
-            TR(if (lane == 0) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_cta_trace[tr_cta * 4 + 1] = t;
-                   if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) reinterpret_cast<long long*>(p.ws)[25] = t - tr_k0; })
-            TR(if (lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
-                   o[8] = clock64() - tr_t0; o[9] = tr_wx; o[10] = tr_wd - tr_wx; o[11] = tr_is; })
         }
         __syncwarp();
     } else {
@@ -428,14 +418,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             int slot = set, st = set;                   // ring lengths are multiples of SETS (host side): an entry has one owner set
             uint32_t ppar = 0, phase = 0;
             const uint32_t a_lane = tmem_base + (uint32_t(qd * 32) << 16) + uint32_t(ACC_COLS + kin * 32);
-            TR(long long tr_t0 = clock64(), tr_wp = 0, tr_we = 0, tr_wk = 0;)
             for (int i = set; i < num_it; i += SETS) {
                 // every lane polls (same word, same answer): no divergence and no shuffle on the way to the work
-                TR(const long long tr_a = clock64(); long long tr_b = tr_a;)
                 bool ok = mbar_wait(&p_full[slot], ppar, abort_flag, p.status);
-                TR(tr_b = clock64(); if (warp == 2 && lane == 0) { TRI(i, 3) })
                 ok = ok && mbar_wait(&empty[st], phase ^ 1, abort_flag, p.status);
-                TR(const long long tr_c = clock64(); tr_wp += tr_b - tr_a; tr_we += tr_c - tr_b; if (warp == 2 && lane == 0) { TRI(i, 4) })
                 if (!ok) break;
                 const uint32_t slot_a = smem_u32(pring + slot * RING_SLOT + kin * WQ_SLOT);
                 if (i * KPS + kin < num_kb) {
@@ -451,13 +437,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     const uint32_t xs[8] = {pk0.x, pk0.y, pk0.z, pk0.w, pk1.x, pk1.y, pk1.z, pk1.w};
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-#ifdef OVB_GEMM_TRACE_NO_ALU   // tuning experiment: how fast is the control chain without the expansion arithmetic
-                        r[4 * j] = xs[j]; r[4 * j + 1] = xs[j]; r[4 * j + 2] = xs[j]; r[4 * j + 3] = xs[j];
-                        (void)zz2; (void)ss2;
-#else
                         const uint4 e = dequant_u4x8(xs[j], zz2, ss2);
                         r[4 * j] = e.x; r[4 * j + 1] = e.y; r[4 * j + 2] = e.z; r[4 * j + 3] = e.w;
-#endif
                     }
                 } else if (WMODE == OVB_W_F8) {
                     const __nv_bfloat162 ss2 = __halves2bfloat162(__low2bfloat16(szp), __low2bfloat16(szp));
@@ -490,7 +471,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
                 tc_fence_before_sync();
                 __syncwarp();
-                TR(if (warp == 2 && lane == 0) { TRI(i, 5) })
                 if (lane == 0) {
                     mbar_arrive(&full_x[st]);
                     mbar_arrive(&p_empty[slot]);
@@ -499,10 +479,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (st >= stages) { st -= stages; phase ^= 1; }
                 slot += SETS;
                 if (slot >= pslots) { slot -= pslots; ppar ^= 1; }
-                TR(tr_wk += clock64() - tr_c;)
             }
-            TR(if (warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.z == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws);
-                   o[16] = clock64() - tr_t0; o[17] = tr_wp; o[18] = tr_we; o[19] = tr_wk; })
         }
 
         // -------- epilogue: warp (w % 4) owns TMEM lanes 32*(w%4) .. +31; two warps share a quarter
@@ -520,6 +497,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
         const bool acc_ok = (*abort_flag == 0);
         tc_fence_after_sync();
+        pdl_wait();   // the epilogue reads the residual and writes the output: both belong to the stream's earlier kernels until now
 
         const float bias_v = (p.bias != nullptr && oc < p.N) ? to_float(reinterpret_cast<const E*>(p.bias)[oc]) : 0.f;
         const int tile_id = blockIdx.x;
@@ -534,13 +512,73 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
         // ---- tensor-parallel: the fp32 partial tile in stage_out is summed over the ranks (see GemmKParams)
         const bool comm = p.world > 1;
-        auto comm_epilogue = [&]() {
+        auto comm_epilogue = [&](bool tile_ok) {
             const int ntok = min(BT, p.T - t0);
             const int epoch = __ldcg(p.epoch);
             constexpr int PIECES = BT * (TILE_N / 8);               // 16-byte pieces of the bf16 tile
             constexpr size_t SLOT = (size_t)BT * TILE_N * 2;        // bytes of one bf16 tile
             const int tiles = gridDim.x;
             const int W = p.world;
+            if (p.mc != nullptr) {
+                // In-switch all-reduce (NVLS). Every rank stores its bf16 partial tile in its OWN staging slot (rank 0 adds
+                // bias and residual first, so the switch's sum is the finished value and is rounded once), the ranks meet at
+                // the tile's barrier, then rank r fetches the sum over all ranks of its 1/W share of the tile with
+                // multimem.ld_reduce and writes it to `out` on every rank with multimem.st. A second barrier tells every
+                // rank that all shares have landed. Each piece is reduced exactly once, so all ranks hold the same bits.
+                // Traffic per rank and tile: one tile out (pulled by the switch), one tile in.
+                if (!tile_ok) return;
+                uint8_t* my_heap = p.heap[p.rank];
+                const size_t slot_off = (size_t)p.stage_off + (size_t)tile_id * SLOT;
+                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                    const int col = i >> 4, pc = i & 15;
+                    if (col >= ntok) continue;
+                    const float4 f0 = *reinterpret_cast<const float4*>(stage_out + col * TILE_N + pc * 8);
+                    const float4 f1 = *reinterpret_cast<const float4*>(stage_out + col * TILE_N + pc * 8 + 4);
+                    float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                    if (p.rank == 0) {
+                        const size_t tok = (size_t)(t0 + col);
+                        if (p.bias) {
+                            const uint4 bb = *reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.bias) + n0 + pc * 8);
+                            const E* be = reinterpret_cast<const E*>(&bb);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] += to_float(be[j]);
+                        }
+                        if (p.residual) {
+                            const uint4 rr = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const E*>(p.residual) + tok * p.ldr + n0 + pc * 8));
+                            const E* re = reinterpret_cast<const E*>(&rr);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) f[j] += to_float(re[j]);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(my_heap + slot_off + (size_t)i * 16) =
+                        make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+                }
+                fence_sys();
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride;
+                int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride;
+                if (dq_tid == 0 && !nvls_barrier(bar_local, bar_mc, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) {
+                    report_status(p.status, STATUS_PEER_TIMEOUT);
+                    *abort_flag = 1;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (*abort_flag) return;
+                const int per = PIECES / W;                             // PIECES is a multiple of 256, W of 2, 4 or 8
+                for (int i = p.rank * per + dq_tid; i < (p.rank + 1) * per; i += DQ_THREADS) {
+                    const int col = i >> 4, pc = i & 15;
+                    if (col >= ntok) continue;
+                    const uint4 v = multimem_ld_reduce_bf16x8(p.mc + slot_off + (size_t)i * 16);
+                    multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(t0 + col) * p.ldo + n0 + pc * 8) * 2, v);
+                }
+                fence_sys();
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                if (dq_tid == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) {
+                    report_status(p.status, STATUS_PEER_TIMEOUT);
+                    *abort_flag = 1;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                return;
+            }
             auto flags_of = [&](int r) { return reinterpret_cast<int*>(p.heap[r] + p.flags_off) + (size_t)tile_id * (W + 1); };
             int* my_flags = flags_of(p.rank);
             auto wait_flag = [&](const int* f) {
@@ -652,7 +690,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             constexpr size_t LL_SLOT = 2 * SLOT;
             // two call sites share a staging buffer within a step, so the tag names the site as well as the step
             const uint32_t tag = ((uint32_t)epoch << 8) | (uint32_t)(p.site & 255);
-            TR(long long tr_e0 = 0, tr_e1 = 0, tr_e2 = 0; if (dq_tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e0));)
+            if (!tile_ok && !(p.comm_mode == 2 && p.packets)) return;
             if (p.comm_mode == 1 && p.packets) {
                 // One-shot with flag-carrying packets: every 16-byte store holds two (data word, tag) pairs, so the
                 // receiver sees data and "it has arrived" in the same 8-byte unit and needs neither a fence nor a flag
@@ -672,7 +710,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         }
                     }
                 }
-                TR(if (dq_tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e1));)
                 const uint8_t* slots = p.heap[p.rank] + p.stage_off + (size_t)tile_id * LL_SLOT;
                 bool ok_ll = true;
                 for (int i = dq_tid; i < PIECES && ok_ll; i += DQ_THREADS) {
@@ -687,8 +724,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     report_status(p.status, STATUS_PEER_TIMEOUT);
                     *abort_flag = 1;
                 }
-                TR(if (dq_tid == 0) { asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tr_e2));
-                       const int c_ = tile_id & 16383; g_cta_trace[c_ * 4 + 0] = tr_e0; g_cta_trace[c_ * 4 + 1] = tr_e1; g_cta_trace[c_ * 4 + 2] = tr_e2; })
             } else if (p.comm_mode == 1) {
                     // one-shot: push the partial to every rank, then every rank reduces the tile for itself
                     const size_t slot = (size_t)p.stage_off + ((size_t)p.rank * tiles + tile_id) * SLOT;
@@ -717,6 +752,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         }
                     }
             } else if (p.packets) {
+                if (tile_ok) {
                 // Two-shot: the owner of the tile (tile_id mod W) collects the partials, reduces, and writes the finished
                 // tile into `out` on every rank. The partials travel as flag-carrying packets, so a CTA that does not
                 // own its tile stores and leaves: no fence, no flag, no wait, and the SM goes on to the next tile. Only
@@ -756,7 +792,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
                     if (*abort_flag == 0 && dq_tid < W && dq_tid != p.rank) st_release_sys(flags_of(dq_tid) + W, epoch);
                 }
-                // the last CTA of this launch collects the "tile is final" flags of the tiles that peers own
+                }
+                // The last CTA of this launch collects the "tile is final" flags of the tiles that peers own. Every CTA is
+                // counted, also one whose tile was given up (a wait that ran out): the counter must be back at zero when the
+                // launch ends, or later launches would never find their last CTA.
                 int* done_count = reinterpret_cast<int*>(p.heap[p.rank] + p.count_off);
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
                 if (dq_tid == 0) {
@@ -765,7 +804,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     *last_flag = last;
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (*last_flag) {
+                if (*last_flag && *abort_flag == 0) {
                     int* base = reinterpret_cast<int*>(p.heap[p.rank] + p.flags_off);
                     for (int t = dq_tid; t < tiles; t += DQ_THREADS)
                         if (t % W != p.rank) wait_flag(base + (size_t)t * (W + 1) + W);
@@ -850,7 +889,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         if (comm && p.splits == 1) {
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-            if (acc_ok) comm_epilogue();   // acc_ok is uniform over the epilogue threads
+            comm_epilogue(acc_ok);   // acc_ok is uniform over the epilogue threads
         } else if (fast && p.act == OVB_ACT_SWIGLU) {
             // Gated MLP: the tile holds 64 "gate" rows followed by the 64 "up" rows of the same channels (the packer
             // interleaves them per tile), so out[tok, 64 * tile + c] = silu(gate_c) * up_c needs this tile only.
@@ -967,7 +1006,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             cluster_wait();
             if (comm && split == 0) {
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (*abort_flag == 0) comm_epilogue();
+                comm_epilogue(*abort_flag == 0);
             }
         }
     }
@@ -983,8 +1022,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // ---------------------------------------------------------------- tear-down
     tc_fence_before_sync();
     __syncthreads();
-    TR(if (threadIdx.x == 0) { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); g_cta_trace[tr_cta * 4 + 2] = t;
-           if (blockIdx.x == 0 && blockIdx.z == 0 && p.ws) reinterpret_cast<long long*>(p.ws)[26] = t - tr_k0; })
     if (*abort_flag) {
         // Give copies that are still in flight time to land before the CTA's shared memory is reused.
         for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -1011,6 +1048,7 @@ static int pick_block_t(int T) {
 }
 
 constexpr int kMaxSplits = 8;   // portable cluster size
+static std::mutex g_launch_mu;   // first-use set-up of a kernel variant (function attributes, occupancy table)
 
 // Split-K trades idle SMs against the cost of the cluster reduction (two cluster barriers and one pass over the partial
 // tiles through distributed shared memory). Estimate the time of every candidate with a small model (all constants in
@@ -1087,13 +1125,16 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     const int kps = kblocks_per_stage(BT, WMODE);
     const int smem = stages * (wq ? kps * BT * 128 : BT * 128 + TILE_N * 128) + pslots * (wq ? kps * (wq + TILE_N * 4) : 0) + 1024 + 1024;
     auto kern = gemm_ws_kernel<BT, WMODE, F16>;
-    static uint64_t configured = 0;  // one bit per device
+    static uint64_t configured = 0;  // one bit per device, guarded by g_launch_mu
     int dev = 0;
     OVB_CHECK_CUDA(cudaGetDevice(&dev));
-    if (!(configured & (1ull << dev))) {
-        OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-        OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
-        configured |= (1ull << dev);
+    {
+        std::lock_guard<std::mutex> lk(g_launch_mu);
+        if (!(configured & (1ull << (dev & 63)))) {
+            OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+            OVB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+            configured |= (1ull << (dev & 63));
+        }
     }
     if (smem > kSmemLimit) {
         set_error("ovb_gemm: internal error, %d bytes of shared memory requested", smem);
@@ -1105,40 +1146,42 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     cfg.blockDim = dim3(gemm_threads(BT, WMODE), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 1;
-    attr.val.clusterDim.y = 1;
-    cfg.attrs = &attr;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
     cfg.numAttrs = 1;
     // CTAs resident at a time for every cluster size, asked of the driver once per kernel variant
     static int resident[kMaxSplits + 1] = {-1};
-    if (resident[0] < 0) {
-        resident[1] = (two_ctas(BT, WMODE) ? 2 : 1) * kNumSMs;
-        for (int sz = 2; sz <= kMaxSplits; ++sz) {
-            int n = 0;
-            cfg.gridDim = dim3(sz * 64, 1, sz);
-            attr.val.clusterDim.z = sz;
-            resident[sz] = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess ? n * sz : 0;
+    {
+        std::lock_guard<std::mutex> lk(g_launch_mu);
+        if (resident[0] < 0) {
+            resident[1] = (two_ctas(BT, WMODE) ? 2 : 1) * kNumSMs;
+            for (int sz = 2; sz <= kMaxSplits; ++sz) {
+                int n = 0;
+                cfg.gridDim = dim3(sz * 64, 1, sz);
+                attr[0].val.clusterDim.z = sz;
+                resident[sz] = cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess ? n * sz : 0;
+            }
+            (void)cudaGetLastError();
+            resident[0] = 0;
         }
-        (void)cudaGetLastError();
-        resident[0] = 0;
     }
     if (p.splits == 0) p.splits = pick_splits(a->T, a->N, a->K, BT, WMODE, resident);
-    TR(static int said = 0; if (!said++) { printf("gemm<%d,%d>: resident CTAs by cluster size:", BT, WMODE);
-       for (int sz = 1; sz <= kMaxSplits; ++sz) printf(" %d", resident[sz]); printf(" | T=%d N=%d K=%d -> splits %d\n", a->T, a->N, a->K, p.splits); })
     const int total_kb = ceil_div(a->K, TILE_K);
     if (p.splits > total_kb) p.splits = total_kb;
     if (p.splits > kMaxSplits) p.splits = kMaxSplits;
     p.kblocks_per_split = ceil_div(total_kb, p.splits);
-    dim3 grid(ceil_div(a->N, TILE_N) * ceil_div(a->T, BT), 1, p.splits);
-    if (p.splits > 1) {
-        cfg.gridDim = grid;
-        attr.val.clusterDim.z = p.splits;
-        OVB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
-    } else {
-        kern<<<grid, gemm_threads(BT, WMODE), smem, stream>>>(tmW, tmX, p);
-    }
+    cfg.gridDim = dim3(ceil_div(a->N, TILE_N) * ceil_div(a->T, BT), 1, p.splits);
+    attr[0].val.clusterDim.z = p.splits;
+    // programmatic dependent launch: set-up, tensor-memory allocation and the first weight fetches run under the tail of
+    // the kernel before this one (the kernel waits before it reads activations or writes anything)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    OVB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -1160,13 +1203,6 @@ static int dispatch_bt(int bt, const ovb_gemm_args* a, const CUtensorMap& tmW, c
 }  // namespace ovb
 
 extern "C" {
-
-#ifdef OVB_GEMM_TRACE
-int ovb_gemm_trace_read(long long* host, int n_ctas) {
-    return (int)cudaMemcpyFromSymbol(host, ovb::g_cta_trace, sizeof(long long) * 4 * n_ctas);
-}
-int ovb_gemm_trace_iters(long long* host) { return (int)cudaMemcpyFromSymbol(host, ovb::g_it_trace, sizeof(long long) * 64 * 8); }
-#endif
 
 int ovb_gemm_num_counters(void) { return ovb::kNumCounters; }
 
@@ -1267,11 +1303,19 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         p.flags_off = c->flags_off + (int64_t)c->site * c->flags_per_site * 4;
         p.epoch = reinterpret_cast<const int*>(p.heap[c->rank] + c->epoch_off);
         p.count_off = c->epoch_off + 64;   // the first 256 bytes of the heap are reserved for such words
+        const int64_t out_heap_off = static_cast<uint8_t*>(a->out) - p.heap[c->rank];
+        const bool out_in_heap = out_heap_off >= 0 && out_heap_off + ((int64_t)(a->T - 1) * p.ldo + a->N) * 2 <= c->heap_bytes;
         if (mode == 2) {
-            const int64_t off = static_cast<uint8_t*>(a->out) - p.heap[c->rank];
-            OVB_REQUIRE(off >= 0 && off + ((int64_t)(a->T - 1) * p.ldo + a->N) * 2 <= c->heap_bytes,
-                        "ovb_gemm: with the two-shot all-reduce the output must live in the communicator's symmetric heap");
-            p.out_off = off;
+            OVB_REQUIRE(out_in_heap, "ovb_gemm: with the two-shot all-reduce the output must live in the communicator's symmetric heap");
+            p.out_off = out_heap_off;
+        }
+        // In-switch reduction when the heap has a multicast mapping: plain bf16 tiles in the staging area of the mode (half of
+        // what the packets need), barrier words of the call site, output in the heap, 2, 4 or 8 ranks.
+        if (c->mc_base != nullptr && out_in_heap && (c->world == 2 || c->world == 4 || c->world == 8) &&
+            tiles * kNvlsFlagStride <= c->nvls_flags_per_site && tiles * slot <= (mode == 1 ? c->stage1_bytes : c->stage2_bytes)) {
+            p.mc = static_cast<uint8_t*>(c->mc_base);
+            p.nvls_flags_off = c->nvls_flags_off + (int64_t)c->site * c->nvls_flags_per_site * 4;
+            p.out_off = out_heap_off;
         }
     }
 

@@ -19,6 +19,9 @@ int* ovb_status_ptr(void);
 // Copy the status word to the host (synchronises the stream) and reset it to 0.
 int ovb_status_read(ovb_stream_t stream);
 const char* ovb_last_error(void);
+// Programmatic dependent launch of the library's kernels (on by default; OVB_PDL=0 in the environment turns it off):
+// a kernel's preamble overlaps the tail of the kernel before it in the stream. Returns the previous setting.
+int ovb_set_pdl(int on);
 
 // ---------------------------------------------------------------------------------------------
 // GEMM family:  out[T, N] = epilogue( X[T, K] * dequant(W[N, K])^T )
@@ -195,6 +198,12 @@ typedef struct {
     int mode;      // 0: choose by size, 1: one-shot, 2: two-shot. How the partials travel (flag-carrying packets, or plain tiles with
                    // a fence and arrival flags) is chosen from the world size; the environment variable OVB_COMM_PACKETS (bit 0:
                    // one-shot, bit 1: two-shot) overrides it and must be the same on every rank.
+    // NVLink multicast (NVLS). mc_base: the heap's multicast mapping (a store through it lands at the same offset of every
+    // rank's heap, multimem.ld_reduce through it returns the sum over the ranks), or NULL when the heap has none; then the
+    // peer-store protocols above are used. With a mapping the fused all-reduce and ovb_comm_allreduce_bf16 reduce inside the
+    // switch. nvls_flags_off: num_sites x nvls_flags_per_site int32 of barrier words (16 per tile / CTA), zero at start.
+    void* mc_base;
+    int64_t nvls_flags_off, nvls_flags_per_site;
 } ovb_comm;
 
 // Symmetric-heap plumbing (no kernels): allocate zeroed device memory, export / open / close CUDA IPC handles.

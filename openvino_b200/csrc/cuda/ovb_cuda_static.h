@@ -18,6 +18,9 @@
 //   * Decode batches only: one query token per sequence (a->max_q_len == 1, a->T == a->B); a->scratch is
 //     ignored. Everything else in ovb_pa_args means what it means for ovb_paged_attention(), and the result
 //     is the same.
+//   * Shapes: what the split-KV decode kernel serves, i.e. head size 128, cache block size 16 and 1, 2, 4 or 8
+//     query heads per KV head. Other shapes are refused with an error (ovb_paged_attention() runs them through
+//     a kernel that needs no scratch, so they need no entry point of their own).
 //   * Size limit: the call needs ovb_pa_scratch_bytes(B, Hq, D, max_context_len) bytes, which today is
 //     B * Hq * 32 * (D + 2) * 4. If that exceeds OVB_PA_STATIC_SCRATCH_BYTES the call launches nothing and
 //     returns a negative code; ovb_last_error() then names both numbers. With D = 128 the limit admits
@@ -25,6 +28,9 @@
 //   * First call on a device: it looks up the device address of the array (cudaGetSymbolAddress, with that
 //     device current) and remembers it per device. The look-up may make the runtime load this library's
 //     device code. Make that first call during start-up, before any stream capture begins on that device.
+//     The remembered address belongs to the device's current context: after cudaDeviceReset() on that device
+//     it is stale, and the library has no way to notice. A process that resets a device must not call this
+//     entry point on it again.
 //   * Every call on a device shares the one array, and the array keeps whatever the previous call left
 //     in it. No part of it has to start at zero: each call first writes every slot that it later reads.
 //     Two calls that can overlap on the device (different streams, or different host threads on the same

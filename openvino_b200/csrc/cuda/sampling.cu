@@ -6,6 +6,7 @@
 // (seed, step, row) triple always gives the same token. The role of openvino.genai's sampler
 // (multinomial / top-k / top-p transforms over logits), which the reference keeps outside its runtime repository.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 #include <cuda_bf16.h>
 
 namespace ovb {
@@ -43,6 +44,7 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int V, float inv_temp,
                                                                 int top_k, float top_p, uint64_t seed, const int* __restrict__ step_ptr,
                                                                 int* __restrict__ out_ids) {
+    pdl_enter();
     __shared__ float sh[33];
     __shared__ float scan[kSampleThreads];
     const int row = blockIdx.x;
@@ -110,7 +112,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const __nv_bfloa
     }
 }
 
-__global__ void bump_kernel(int* p) { *p += 1; }
+__global__ void bump_kernel(int* p) {
+    pdl_enter(); *p += 1; }
 
 }  // namespace ovb
 
@@ -131,6 +134,7 @@ __host__ __device__ __forceinline__ float gumbel_uniform(uint64_t h) {
 __global__ void __launch_bounds__(kSampleThreads) gumbel_argmax_kernel(const __nv_bfloat16* __restrict__ logits, int ld, int V, int vocab_offset,
                                                                        float inv_temp, uint64_t seed, const int* __restrict__ step_ptr,
                                                                        int* __restrict__ out_ids, float* __restrict__ out_max) {
+    pdl_enter();
     __shared__ float sv[kSampleThreads / 32];
     __shared__ int si[kSampleThreads / 32];
     const int row = blockIdx.x;
@@ -181,8 +185,8 @@ int ovb_sample(const void* logits, int ld, int rows, int vocab, float temperatur
                const int* step, int* out_ids, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0 && temperature > 0.f, "ovb_sample: bad arguments (temperature must be > 0)");
-    sample_kernel<<<rows, kSampleThreads, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, 1.0f / temperature, top_k,
-                                                       top_p <= 0.f ? 1e-6f : top_p, seed, step, out_ids);
+    OVB_CHECK_CUDA(launch_pdl(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, (const __nv_bfloat16*)logits, ld, vocab, 1.0f / temperature, top_k,
+                                                       top_p <= 0.f ? 1e-6f : top_p, seed, step, out_ids));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -191,8 +195,8 @@ int ovb_sample_gumbel(const void* logits, int ld, int rows, int vocab, int vocab
                       int* out_ids, float* out_max, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(logits && out_ids && rows > 0 && vocab > 0 && temperature > 0.f, "ovb_sample_gumbel: bad arguments (temperature must be > 0)");
-    gumbel_argmax_kernel<<<rows, kSampleThreads, 0, stream>>>((const __nv_bfloat16*)logits, ld, vocab, vocab_offset, 1.0f / temperature, seed, step,
-                                                              out_ids, out_max);
+    OVB_CHECK_CUDA(launch_pdl(gumbel_argmax_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, (const __nv_bfloat16*)logits, ld, vocab, vocab_offset, 1.0f / temperature, seed, step,
+                                                              out_ids, out_max));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -202,7 +206,7 @@ float ovb_gumbel_uniform(uint64_t h) { return gumbel_uniform(h); }
 
 int ovb_bump(int* counter, ovb_stream_t stream_) {
     OVB_REQUIRE(counter != nullptr, "ovb_bump: null counter");
-    bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(counter);
+    OVB_CHECK_CUDA(launch_pdl(bump_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(stream_), counter));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -16,7 +16,8 @@ from typing import Optional
 import torch
 
 _PKG = Path(__file__).resolve().parent.parent
-_LIB_PATH = _PKG / "lib" / "libovb_cuda.so"
+# OVB_CUDA_LIB names another build of the kernel library (a build with different compile-time tuning switches, say)
+_LIB_PATH = Path(os.environ["OVB_CUDA_LIB"]) if os.environ.get("OVB_CUDA_LIB") else _PKG / "lib" / "libovb_cuda.so"
 
 W_BF16, W_U4, W_U8, W_F16, W_F8 = 0, 1, 2, 3, 4
 ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_SWIGLU, ACT_GELU_TANH = 0, 1, 2, 3, 4, 5

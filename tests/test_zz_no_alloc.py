@@ -42,6 +42,24 @@ def _decode_batch(past_lens, Hq, Hkv, D, block_size, seed):
         B=B, Hq=Hq, Hkv=Hkv, D=D, block_size=block_size, max_context_len=max(past_lens) + 1)
 
 
+def _reference_decode(batch):
+    """Plain PyTorch fp32 decode attention over the paged cache (one query token per sequence)."""
+    B, Hq, Hkv, D, bs = batch["B"], batch["Hq"], batch["Hkv"], batch["D"], batch["block_size"]
+    q = batch["q"].float().view(B, Hq, D)
+    out = torch.empty(B, Hq, D, device="cuda")
+    begins = batch["block_indices_begins"].tolist()
+    for b in range(B):
+        n = int(batch["past_lens"][b]) + 1
+        blocks = batch["block_indices"][begins[b]:begins[b + 1]].long()
+        keys = batch["k_cache"][blocks].float().permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :n]
+        vals = batch["v_cache"][blocks].float().permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :n]
+        keys = keys.repeat_interleave(Hq // Hkv, 0)
+        vals = vals.repeat_interleave(Hq // Hkv, 0)
+        p = torch.softmax(torch.einsum("hd,hnd->hn", q[b], keys) / math.sqrt(D), -1)
+        out[b] = torch.einsum("hn,hnd->hd", p, vals)
+    return out.view(B, Hq * D)
+
+
 def _args(k, batch, out, scratch_ptr):
     a = k.PaArgs()
     a.q, a.out = batch["q"].data_ptr(), out.data_ptr()
@@ -88,6 +106,20 @@ def test_static_scratch_matches_caller_scratch_on_two_calls_in_a_row(k):
         torch.cuda.synchronize()
         assert want.float().abs().sum().item() > 0
         assert _rel_err(got, want) < 1e-2
+        assert _rel_err(got, _reference_decode(batch)) < 2e-2
+        # The point of the entry point: a call takes no device memory, neither from the driver nor from PyTorch's
+        # caching allocator. (The very first call on a device may load the library's device code; this one is later.)
+        out2 = torch.zeros_like(want)
+        args2 = _args(k, batch, out2, None)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        torch_before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+        rc = lib.ovb_paged_attention_decode_static(C.byref(args2), stream)
+        torch.cuda.synchronize()
+        assert rc == 0, lib.ovb_last_error()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == torch_before
+        assert torch.equal(out2, got)
 
 
 def test_batch_beyond_the_static_size_is_refused(k):
@@ -105,3 +137,8 @@ def test_batch_beyond_the_static_size_is_refused(k):
     a = _args(k, _decode_batch([3, 3], 8, 2, 128, 16, 4), out, None)
     a.max_q_len = 2
     assert lib.ovb_paged_attention_decode_static(C.byref(a), stream) < 0
+    # nor shapes that the split-KV decode kernel does not serve (they would never touch the scratch)
+    a = _args(k, _decode_batch([3, 3], 8, 2, 128, 16, 4), out, None)
+    a.block_size = 32
+    assert lib.ovb_paged_attention_decode_static(C.byref(a), stream) < 0
+    assert "block size" in lib.ovb_last_error().decode()
