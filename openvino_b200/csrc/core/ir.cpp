@@ -143,11 +143,12 @@ struct Writer {
         const uint8_t* p;
         size_t n;
         if (t.et == ET::string) {
-            // header: count, then (begin, end) offsets of every string, then the characters
+            // header: count, the begin offset of every string, the end of the last one; then the characters
+            // (src/core/src/runtime/string_aligned_buffer.cpp:19)
             const int32_t cnt = (int32_t)t.strings.size();
-            std::vector<int32_t> hdr{cnt};
+            std::vector<int32_t> hdr{cnt, 0};
             int32_t off = 0;
-            for (auto& s : t.strings) { hdr.push_back(off); off += (int32_t)s.size(); hdr.push_back(off); }
+            for (auto& s : t.strings) { off += (int32_t)s.size(); hdr.push_back(off); }
             packed.assign(reinterpret_cast<const char*>(hdr.data()), hdr.size() * 4);
             for (auto& s : t.strings) packed += s;
             p = reinterpret_cast<const uint8_t*>(packed.data());
@@ -373,13 +374,14 @@ struct Reader {
             OVC_CHECK(size >= 4, "string constant '" << lname << "' is truncated");
             int32_t cnt;
             std::memcpy(&cnt, p, 4);
-            OVC_CHECK(cnt >= 0 && (size_t)(1 + 2 * (size_t)cnt) * 4 <= size, "string constant '" << lname << "' has a bad header");
-            const char* chars = reinterpret_cast<const char*>(p) + (1 + 2 * (size_t)cnt) * 4;
-            const size_t chars_len = size - (1 + 2 * (size_t)cnt) * 4;
+            const size_t hdr_bytes = (2 + (size_t)(cnt < 0 ? 0 : cnt)) * 4;   // count, cnt begin offsets, the last end
+            OVC_CHECK(cnt >= 0 && hdr_bytes <= size, "string constant '" << lname << "' has a bad header");
+            const char* chars = reinterpret_cast<const char*>(p) + hdr_bytes;
+            const size_t chars_len = size - hdr_bytes;
             for (int32_t i = 0; i < cnt && (size_t)i < t.strings.size(); ++i) {
                 int32_t b, e;
-                std::memcpy(&b, p + 4 + 8 * (size_t)i, 4);
-                std::memcpy(&e, p + 8 + 8 * (size_t)i, 4);
+                std::memcpy(&b, p + 4 + 4 * (size_t)i, 4);
+                std::memcpy(&e, p + 8 + 4 * (size_t)i, 4);
                 OVC_CHECK(b >= 0 && e >= b && (size_t)e <= chars_len, "string constant '" << lname << "' has bad offsets");
                 t.strings[(size_t)i].assign(chars + b, chars + e);
             }

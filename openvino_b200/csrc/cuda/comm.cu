@@ -54,6 +54,8 @@ struct CommK {
     long long stage_off;
     const int* epoch;
     int* status;
+    uint8_t* mc;             // multicast mapping of the heap (NVLS) or NULL
+    long long nvls_flags_off;   // of the call site
 };
 
 // One CTA; thread = row. Every rank pushes (max value, global index) of its shard to every rank, then picks.
@@ -132,6 +134,34 @@ __global__ void allreduce_bf16_kernel(CommK c, long long data_off, long long npi
     }
 }
 
+// In-place all-reduce through the switch (NVLS): the ranks meet at a barrier (every rank's tensor is complete), rank r
+// fetches the sum over the ranks of its 1/W share of the 16-byte pieces (multimem.ld_reduce, fp32 accumulation) and writes
+// it back to every rank (multimem.st), and a second barrier tells every rank that all shares have landed. No staging: a
+// piece is read and rewritten by its one owner only. CTA b uses barrier b of the call site.
+__global__ void allreduce_nvls_kernel(CommK c, long long data_off, long long npieces) {
+    pdl_enter();
+    const int epoch = __ldcg(c.epoch);
+    const int W = c.world;
+    const int* bar_local = reinterpret_cast<const int*>(c.heap[c.rank] + c.nvls_flags_off) + (size_t)blockIdx.x * kNvlsFlagStride;
+    int* bar_mc = reinterpret_cast<int*>(c.mc + c.nvls_flags_off) + (size_t)blockIdx.x * kNvlsFlagStride;
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) ok_s = nvls_barrier(bar_local, bar_mc, c.rank, W, epoch, kSpinLimit, nullptr) ? 1 : 0;
+    __syncthreads();
+    if (!ok_s) {
+        if (threadIdx.x == 0) report_status(c.status, STATUS_PEER_TIMEOUT);
+        return;
+    }
+    const long long per = (npieces + W - 1) / W;
+    const long long begin = (long long)c.rank * per;
+    const long long end = begin + per < npieces ? begin + per : npieces;
+    uint8_t* base = c.mc + data_off;
+    for (long long i = begin + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < end; i += (long long)gridDim.x * blockDim.x)
+        multimem_st_b128(base + i * 16, multimem_ld_reduce_bf16x8(base + i * 16));
+    fence_sys();
+    __syncthreads();
+    if (threadIdx.x == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, c.rank, W, epoch, kSpinLimit, nullptr)) report_status(c.status, STATUS_PEER_TIMEOUT);
+}
+
 static int fill(const ovb_comm* c, CommK* k, int site) {
     OVB_REQUIRE(c != nullptr && c->world >= 1 && c->world <= 8 && c->rank >= 0 && c->rank < c->world, "bad communicator");
     OVB_REQUIRE(site >= 0 && site < c->num_sites, "communicator call site %d out of range (%d sites)", site, c->num_sites);
@@ -142,9 +172,12 @@ static int fill(const ovb_comm* c, CommK* k, int site) {
         k->heap[r] = static_cast<uint8_t*>(c->heap[r]);
     }
     k->flags_off = c->flags_off + (int64_t)site * c->flags_per_site * 4;
-    k->stage_off = c->stage1_off + (int64_t)(site & 1) * c->stage1_bytes;
+    k->stage_off = c->stage3_bytes > 0 ? c->stage3_off + (int64_t)(site & 1) * c->stage3_bytes
+                                       : c->stage1_off + (int64_t)(site & 1) * c->stage1_bytes;
     k->epoch = reinterpret_cast<const int*>(k->heap[c->rank] + c->epoch_off);
     k->status = status_word();
+    k->mc = static_cast<uint8_t*>(c->mc_base);
+    k->nvls_flags_off = c->nvls_flags_off + (int64_t)site * c->nvls_flags_per_site * 4;
     return 0;
 }
 
@@ -220,7 +253,17 @@ int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream
     if (int rc = fill(c, &k, c ? c->site : 0)) return rc;
     const int64_t off = static_cast<uint8_t*>(data) - k.heap[c->rank];
     OVB_REQUIRE(off >= 0 && off + n * 2 <= c->heap_bytes && off % 16 == 0, "ovb_comm_allreduce_bf16: the tensor must live in the symmetric heap, 16-byte aligned");
-    const int64_t rank_stride = (c->stage1_bytes / c->world) & ~int64_t(15);
+    if (k.mc != nullptr && (c->world == 2 || c->world == 4 || c->world == 8)) {
+        const int64_t npieces = n / 8;
+        int grid = (int)((npieces / c->world + 255) / 256);
+        if (grid < 1) grid = 1;
+        if (grid > 148) grid = 148;
+        if ((int64_t)grid * kNvlsFlagStride > c->nvls_flags_per_site) grid = (int)(c->nvls_flags_per_site / kNvlsFlagStride);
+        OVB_REQUIRE(grid >= 1, "ovb_comm_allreduce_bf16: no barrier words for the call site");
+        OVB_CHECK_CUDA(launch_pdl(allreduce_nvls_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), k, (long long)off, (long long)npieces));
+        return 0;
+    }
+    const int64_t rank_stride = ((c->stage3_bytes > 0 ? c->stage3_bytes : c->stage1_bytes) / c->world) & ~int64_t(15);
     OVB_REQUIRE(n * 2 <= rank_stride, "ovb_comm_allreduce_bf16: %lld bytes exceed the staging share of a rank (%lld)", (long long)(n * 2), (long long)rank_stride);
     const int64_t npieces = n / 8;
     int grid = (int)((npieces + 255) / 256);

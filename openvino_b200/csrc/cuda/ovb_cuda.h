@@ -204,6 +204,9 @@ typedef struct {
     // switch. nvls_flags_off: num_sites x nvls_flags_per_site int32 of barrier words (16 per tile / CTA), zero at start.
     void* mc_base;
     int64_t nvls_flags_off, nvls_flags_per_site;
+    // 2 x stage3_bytes of staging that only ovb_comm_allreduce_bf16 uses (alternating by call site), so that a rank running
+    // ahead into the next fused GEMM never writes a buffer that a peer's all-reduce still reads. 0: share the one-shot staging.
+    int64_t stage3_off, stage3_bytes;
 } ovb_comm;
 
 // Symmetric-heap plumbing (no kernels): allocate zeroed device memory, export / open / close CUDA IPC handles.

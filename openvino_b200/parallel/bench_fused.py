@@ -7,7 +7,8 @@ Shapes are the two row-parallel projections of a Llama-3-8B layer (attention out
 K = 14336 / N; int4 g128 weights, bf16 activations) at a decode batch (T = 64) and a prefill chunk (T = 8192). Every
 number is device time (CUDA events, max over ranks, median of the iterations; an L2-sized read precedes every launch).
 The roofline of a call is the slowest of: FLOPs / measured bf16 GEMM peak, weight bytes / measured HBM bandwidth, and the
-bytes a rank must send over NVLink / 770 GB/s (one-shot, T <= 128: (N-1) copies of the bf16 tile; two-shot: 2 (N-1)/N).
+bytes a rank must send over NVLink / 770 GB/s (one-shot, T <= 128: (N-1) copies of the bf16 tile; two-shot: 2 (N-1)/N;
+in-switch reduction: 1 + 1/N).
 Rank 0 prints one JSON line per shape.
 """
 from __future__ import annotations
@@ -94,14 +95,18 @@ def main() -> int:
         flops = 2.0 * T * H * Kd
         wbytes = H * Kd // 2 + (H * Kd // 128) * 4
         tile_bytes = T * H * 2
-        sent = (world - 1) * tile_bytes if T <= 128 else 2.0 * (world - 1) / world * tile_bytes
+        if comm.mc_ptr:
+            # in-switch reduction: the switch pulls this rank's partial tile once and the rank stores its 1/W share of the result
+            sent = (1.0 + 1.0 / world) * tile_bytes
+        else:
+            sent = (world - 1) * tile_bytes if T <= 128 else 2.0 * (world - 1) / world * tile_bytes
         t_compute = flops / (pk["bf16_tflops"] * 1e12) * 1e3
         t_hbm = (wbytes + T * Kd * 2 + 2 * tile_bytes) / (pk["hbm_gbs"] * 1e9) * 1e3
         t_link = sent / (link_gbs * 1e9) * 1e3
         roof = max(t_compute, t_hbm, t_link)
         if rank == 0:
             print(json.dumps({"kernel": "gemm_u4 + all-reduce (fused epilogue)", "n_gpus": world, "T": T, "N": H, "K_per_rank": Kd,
-                              "mode": "one-shot" if T <= 128 else "two-shot", "fused_ms": fused_ms, "gemm_then_nccl_ms": nccl_ms, "gemm_only_ms": gemm_ms,
+                              "mode": "in-switch (NVLS)" if comm.mc_ptr else ("one-shot" if T <= 128 else "two-shot"), "fused_ms": fused_ms, "gemm_then_nccl_ms": nccl_ms, "gemm_only_ms": gemm_ms,
                               "roofline_ms": roof, "bound": ["compute", "hbm", "nvlink"][[t_compute, t_hbm, t_link].index(roof)],
                               "fraction_of_roofline": roof / fused_ms, "peaks": pk["source"],
                               "nvlink_gbs_achieved": sent / fused_ms / 1e6}), flush=True)

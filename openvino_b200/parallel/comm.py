@@ -15,6 +15,7 @@ Heap layout (byte offsets are the same on every rank): step counter, flag words 
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List, Optional
 
 import torch
@@ -23,6 +24,7 @@ from ..ops import cuda as K
 
 MAX_RANKS = 8
 ARGMAX_ROWS_CAP = 1024
+NVLS_FLAG_STRIDE = 16      # kNvlsFlagStride of the kernels
 
 
 class CommStruct(C.Structure):
@@ -35,6 +37,8 @@ class CommStruct(C.Structure):
         ("epoch_off", C.c_int64), ("flags_off", C.c_int64), ("flags_per_site", C.c_int64),
         ("stage1_off", C.c_int64), ("stage1_bytes", C.c_int64), ("stage2_off", C.c_int64), ("stage2_bytes", C.c_int64),
         ("num_sites", C.c_int), ("site", C.c_int), ("mode", C.c_int),
+        ("mc_base", C.c_void_p), ("nvls_flags_off", C.c_int64), ("nvls_flags_per_site", C.c_int64),
+        ("stage3_off", C.c_int64), ("stage3_bytes", C.c_int64),
     ]
 
 
@@ -57,7 +61,13 @@ class HeapLayout:
         self.stage2_off = self.stage1_off + 2 * self.stage1_bytes
         # two-shot: every tile has one owner; rounding the tiles per owner up costs at most `world` extra tiles
         self.stage2_bytes = _round_up(2 * (_round_up(max_tokens, 256) * hidden + world * 256 * 128) * 2, 1024)    # packets: 2x
-        self.tensors_off = _round_up(self.stage2_off + self.stage2_bytes, 1024)
+        # staging of the stand-alone all-reduce (two alternating buffers of its own)
+        self.stage3_off = _round_up(self.stage2_off + self.stage2_bytes, 1024)
+        self.stage3_bytes = self.stage1_bytes
+        # barrier words of the in-switch (NVLS) collectives: 16 int32 per tile of a fused GEMM / CTA of an all-reduce
+        self.nvls_flags_per_site = max(tiles_max, 148) * NVLS_FLAG_STRIDE
+        self.nvls_flags_off = _round_up(self.stage3_off + 2 * self.stage3_bytes, 1024)
+        self.tensors_off = _round_up(self.nvls_flags_off + num_sites * self.nvls_flags_per_site * 4, 1024)
         self.heap_bytes = self.tensors_off + _round_up(tensor_bytes, 1024)
 
 
@@ -71,15 +81,63 @@ class PeerCommunicator:
         self._bump = 0
         self._structs = {}
         self._keep = []
+        self.mc_ptr = 0           # multicast mapping of the heap (NVLS), 0 = none
+        self._symm = None
 
     # ------------------------------------------------------------------ set-up (collective)
     def setup(self, hidden: int, max_tokens: int, num_layers: int, tensor_bytes: int) -> None:
-        """Allocate this rank's heap, exchange IPC handles, map every peer. Call on all ranks with equal arguments."""
+        """Allocate this rank's heap and map every peer's. Call on all ranks with equal arguments.
+
+        Two ways to get the heap. Preferred: ``torch.distributed._symmetric_memory`` (driver virtual-memory allocations
+        exchanged between the processes), which on an NVSwitch machine also binds the heaps to one NVLink multicast
+        object: ``mc_ptr`` then addresses all ranks' heaps at once and the collectives reduce inside the switch. Otherwise
+        (``OVB_NVLS=0`` or ``NCCL_NVLS_ENABLE=0`` in the environment, or the set-up failing on any rank): a plain device
+        allocation exported as a CUDA IPC handle, and the peer-store protocols. A job whose ranks may leave while others
+        keep running uses the second form: a rank must not die while its memory is bound to a multicast object."""
         import torch.distributed as dist
         num_sites = 2 * num_layers + 3          # two fused GEMMs per layer, argmax, two alternating all-reduce sites
         self.layout = HeapLayout(self.world, hidden, max_tokens, num_sites, tensor_bytes)
         lib = K.lib()
         self._declare(lib)
+        self.mc_ptr = 0
+        self._symm = None
+        want_nvls = os.environ.get("OVB_NVLS", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0" and self.world in (2, 4, 8)
+        if want_nvls:
+            ok, err = 1, ""
+            try:
+                self._setup_symmetric()
+            except Exception as e:            # noqa: BLE001 - any failure means "use the IPC heap", on every rank
+                ok, err = 0, "%s: %s" % (type(e).__name__, e)
+            flags = [None] * self.world
+            dist.all_gather_object(flags, (ok, err), group=self.group)
+            if not all(f[0] for f in flags):
+                self._symm, self._base, self._peer_ptrs, self.mc_ptr = None, 0, [], 0
+                from ..utils import log as _log
+                _log.warn("comm", "symmetric-memory heap unavailable (%s); using the CUDA IPC heap and peer stores"
+                          % "; ".join(f[1] for f in flags if not f[0])[:300])
+        if not self._base:
+            self._setup_ipc(lib)
+        self._bump = self.layout.tensors_off
+        dist.barrier(group=self.group)
+
+    def _setup_symmetric(self) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = self.group if self.group is not None else dist.group.WORLD
+        with torch.cuda.device(self.device):
+            t = symm.empty(self.layout.heap_bytes, dtype=torch.uint8, device=self.device)
+            t.zero_()
+            torch.cuda.synchronize(self.device)
+            hdl = symm.rendezvous(t, group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != t.data_ptr():
+            raise RuntimeError("unexpected symmetric-memory handle (%d pointers)" % len(ptrs))
+        self._symm = (t, hdl)               # keeps the allocation and the mappings alive
+        self._base, self._peer_ptrs = ptrs[self.rank], ptrs
+        self.mc_ptr = int(getattr(hdl, "multicast_ptr", 0) or 0)
+
+    def _setup_ipc(self, lib) -> None:
+        import torch.distributed as dist
         with torch.cuda.device(self.device):
             base = C.c_void_p()
             K._check(lib.ovb_comm_alloc(C.c_int64(self.layout.heap_bytes), C.byref(base)), "ovb_comm_alloc")
@@ -97,8 +155,6 @@ class PeerCommunicator:
                 p = C.c_void_p()
                 K._check(lib.ovb_comm_open(buf, C.byref(p)), "ovb_comm_open")
                 self._peer_ptrs.append(p.value)
-        self._bump = self.layout.tensors_off
-        dist.barrier(group=self.group)
 
     @staticmethod
     def _declare(lib) -> None:
@@ -116,6 +172,9 @@ class PeerCommunicator:
             return
         lib = K.lib()
         torch.cuda.synchronize(self.device)
+        if self._symm is not None:          # torch owns the allocation and the mappings
+            self._symm, self._base, self._peer_ptrs, self.mc_ptr = None, 0, [], 0
+            return
         for r, p in enumerate(self._peer_ptrs):
             if r != self.rank and p:
                 lib.ovb_comm_close(C.c_void_p(p))
@@ -154,6 +213,9 @@ class PeerCommunicator:
             s.epoch_off, s.flags_off, s.flags_per_site = L.epoch_off, L.flags_off, L.flags_per_site
             s.stage1_off, s.stage1_bytes, s.stage2_off, s.stage2_bytes = L.stage1_off, L.stage1_bytes, L.stage2_off, L.stage2_bytes
             s.num_sites, s.site, s.mode = L.num_sites, site, mode
+            s.mc_base = self.mc_ptr or None
+            s.nvls_flags_off, s.nvls_flags_per_site = L.nvls_flags_off, L.nvls_flags_per_site
+            s.stage3_off, s.stage3_bytes = L.stage3_off, L.stage3_bytes
             self._structs[key] = s
         return s
 
@@ -182,7 +244,12 @@ class PeerCommunicator:
         reading. A last bump keeps later users of the step number apart from these flags. Returns the launches made."""
         assert t.dtype == torch.bfloat16 and t.is_contiguous() and self.in_heap(t)
         L = self.layout
-        max_elems = (((L.stage1_bytes // self.world) & ~15) // 2) & ~7
+        if self.mc_ptr:
+            # in-switch reduction works in place on the heap tensor: no staging, so no pieces
+            self.step_begin()
+            self.all_reduce(t)
+            return 2
+        max_elems = (((L.stage3_bytes // self.world) & ~15) // 2) & ~7
         flat = t.view(-1)
         n, i, k = flat.numel(), 0, 0
         lib = K.lib()

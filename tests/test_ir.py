@@ -179,3 +179,58 @@ def test_read_from_memory_with_tensor_weights():
     assert r.get_output_partial_shape(0) == [1, 4, 8, 8]
     r2 = ov.Core().read_model(bytes(xml), bytes(weights))
     assert len(r2.get_ops()) == len(r.get_ops())
+
+
+# ---------------------------------------------------------------------------------------------- reference goldens
+_GOLDEN_DIR = "/root/reference/src/core/tests/models/ir"
+# files in that folder that the reference's own serializer wrote (IR v11, pugixml layout): they must come back byte for byte
+_WRITTEN_BY_SERIALIZER = ("dynamic_variable", "string_parameter", "const_string")
+
+
+def _goldens():
+    import glob
+    return sorted(glob.glob(os.path.join(_GOLDEN_DIR, "*.xml")))
+
+
+@pytest.mark.skipif(not os.path.isdir(_GOLDEN_DIR), reason="reference tree not present")
+def test_every_reference_golden_loads_and_reserialises_to_a_fixed_point(tmp_path):
+    core = ov.Core()
+    files = _goldens()
+    assert len(files) >= 20
+    for x in files:
+        m = core.read_model(x)
+        a_xml, a_bin = str(tmp_path / "a.xml"), str(tmp_path / "a.bin")
+        ov.serialize(m, a_xml, a_bin)
+        m2 = core.read_model(a_xml)
+        b_xml, b_bin = str(tmp_path / "b.xml"), str(tmp_path / "b.bin")
+        ov.serialize(m2, b_xml, b_bin)
+        assert open(a_xml, "rb").read() == open(b_xml, "rb").read(), x
+        assert open(a_bin, "rb").read() == open(b_bin, "rb").read(), x
+        assert len(m2.get_ops()) == len(m.get_ops())
+
+
+@pytest.mark.skipif(not os.path.isdir(_GOLDEN_DIR), reason="reference tree not present")
+@pytest.mark.parametrize("name", _WRITTEN_BY_SERIALIZER)
+def test_goldens_written_by_the_reference_serializer_come_back_byte_for_byte(tmp_path, name):
+    core = ov.Core()
+    src = os.path.join(_GOLDEN_DIR, name + ".xml")
+    m = core.read_model(src)
+    out_xml, out_bin = str(tmp_path / "o.xml"), str(tmp_path / "o.bin")
+    ov.serialize(m, out_xml, out_bin)
+    assert open(out_xml, "rb").read() == open(src, "rb").read()
+    src_bin = src[:-4] + ".bin"
+    if os.path.exists(src_bin):
+        assert open(out_bin, "rb").read() == open(src_bin, "rb").read()
+
+
+def test_string_constant_uses_the_packed_layout_of_the_reference(tmp_path):
+    # count, begin offsets, last end, characters (src/core/src/runtime/string_aligned_buffer.cpp:19)
+    import struct
+    c = ops.constant(np.array([["abc", ""], ["de", "f"]], dtype=object))
+    m = ov.Model([ops.result(c)], [], "strings")
+    ov.serialize(m, str(tmp_path / "s.xml"), str(tmp_path / "s.bin"))
+    raw = open(tmp_path / "s.bin", "rb").read()
+    assert struct.unpack("<6i", raw[:24]) == (4, 0, 3, 3, 5, 6) and raw[24:] == b"abcdef"
+    back = ov.Core().read_model(str(tmp_path / "s.xml"))
+    const = [n for n in back.get_ops() if n.get_type_name() == "Constant"][0]
+    assert [s.decode() if isinstance(s, bytes) else s for s in const.get_data().reshape(-1).tolist()] == ["abc", "", "de", "f"]

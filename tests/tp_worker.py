@@ -130,8 +130,7 @@ def main():
         failures.append(("tp sampling", sobj, s2))
 
     # top-k / top-p over vocabulary shards (the ranks gather full rows): ranks agree, and top_k = 1 is greedy decoding.
-    # Opt-in (OVB_TP_WORKER_TOPK=1) until this check has run on GPUs once.
-    if os.environ.get("OVB_TP_WORKER_TOPK") == "1":
+    if os.environ.get("OVB_TP_WORKER_TOPK", "1") == "1":
         kgen = GenerationConfig(max_new_tokens=8, ignore_eos=True, do_sample=True, temperature=1.3, top_k=1, rng_seed=3)
         k1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, kgen)]
         K.check_status("tp top-k sampling")
@@ -167,6 +166,7 @@ def main():
     dist.all_gather_object(all_fail, failures)
     torch.cuda.synchronize()
     dist.barrier()
+    nvls = int(bool(comm.mc_ptr))
     tp_comm.close()
     moe_comm.close()
     comm.close()
@@ -175,7 +175,7 @@ def main():
         if any(all_fail):
             print("TP_WORKER_FAILED", all_fail)
             sys.exit(1)
-        print("TP_WORKER_OK", "tokens agree %d/%d, moe %d/%d" % (agree, total, magree, total))
+        print("TP_WORKER_OK", "world=%d nvls=%d tokens agree %d/%d, moe %d/%d" % (world, nvls, agree, total, magree, total))
 
 
 if __name__ == "__main__":
