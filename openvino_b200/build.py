@@ -71,11 +71,15 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     def compile_one(src: Path) -> Path:
         obj = OBJ / (src.stem + ".o")
         if force or _stale(obj, [src] + hdrs):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
+            # ptxas reports registers, stack frame and spills of every kernel; the report is kept next to the object
+            # (build/<name>.ptxas.txt) so that a resource regression of a hot kernel shows up without a GPU
+            cmd = [nvcc, "-Xptxas", "-v", *NVCC_FLAGS, "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout[-4000:], r.stderr[-8000:]))
+            (OBJ / (src.stem + ".ptxas.txt")).write_text(r.stderr)
             if verbose:
-                cmd.insert(1, "-Xptxas")
-                cmd.insert(2, "-v")
-            _run(cmd)
+                print(r.stderr)
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
@@ -152,6 +156,21 @@ def build_capi(force: bool = False) -> Path | None:
     vers.write_text("{ global: ov_*; local: *; };\n")
     _run([cxx, "-shared", "-o", str(target), *map(str, objs), "-pthread", "-Wl,--version-script=%s" % vers, "-Wl,-Bsymbolic"])
     return target
+
+
+def kernel_resources(stem: str) -> dict:
+    """Per-kernel resource usage parsed from the ptxas report of ``csrc/cuda/<stem>.cu``:
+    ``{mangled name: {"registers", "stack", "spill_stores", "spill_loads"}}`` (empty when no report exists)."""
+    import re
+    path = OBJ / (stem + ".ptxas.txt")
+    if not path.exists():
+        return {}
+    out = {}
+    pat = re.compile(r"Compiling entry function '(\S+)' for 'sm_100a'.*?(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads"
+                     r".*?Used (\d+) registers", re.S)
+    for m in pat.finditer(path.read_text()):
+        out[m.group(1)] = {"stack": int(m.group(2)), "spill_stores": int(m.group(3)), "spill_loads": int(m.group(4)), "registers": int(m.group(5))}
+    return out
 
 
 def build_all(force: bool = False) -> None:

@@ -613,7 +613,8 @@ PYBIND11_MODULE(_ovcore, mod) {
         .def_readwrite("max_num_seqs", &SchedulerConfig::max_num_seqs)
         .def_readwrite("num_kv_blocks", &SchedulerConfig::num_kv_blocks)
         .def_readwrite("block_size", &SchedulerConfig::block_size)
-        .def_readwrite("dynamic_split_fuse", &SchedulerConfig::dynamic_split_fuse);
+        .def_readwrite("dynamic_split_fuse", &SchedulerConfig::dynamic_split_fuse)
+        .def_readwrite("enable_prefix_caching", &SchedulerConfig::enable_prefix_caching);
     py::class_<SeqState, SeqPtr>(mod, "SeqState")
         .def_readonly("request_id", &SeqState::request_id)
         .def_readonly("generated", &SeqState::generated)
@@ -621,6 +622,9 @@ PYBIND11_MODULE(_ovcore, mod) {
         .def_readonly("finished", &SeqState::finished)
         .def_readonly("slot", &SeqState::slot)
         .def_readonly("blocks", &SeqState::blocks)
+        .def_readonly("num_cached_tokens", &SeqState::num_cached_tokens)
+        .def("num_generated", [](SeqState& s) { return s.generated.size(); })
+        .def("generated_at", [](SeqState& s, size_t i) { return s.generated.at(i); })
         .def("prompt_len", [](SeqState& s) { return s.prompt.size(); })
         .def("total_len", &SeqState::total_len);
     py::class_<DescLayout>(mod, "DescLayout")
@@ -657,6 +661,8 @@ PYBIND11_MODULE(_ovcore, mod) {
         }, py::arg("step"), py::arg("tokens") = py::none())
         .def("patch", [](Scheduler& s, const std::vector<Produced>& p, py::array_t<int32_t> tokens) { s.patch(p, tokens.data()); })
         .def("num_free_blocks", &Scheduler::num_free_blocks)
+        .def("num_cached_blocks", &Scheduler::num_cached_blocks)
+        .def("prefix_hit_tokens", &Scheduler::prefix_hit_tokens)
         .def("num_preemptions", &Scheduler::num_preemptions)
         .def("num_running", &Scheduler::num_running)
         .def("num_waiting", &Scheduler::num_waiting);

@@ -16,7 +16,9 @@
 #include <deque>
 #include <map>
 #include <memory>
+#include <list>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 namespace ovc {
@@ -27,6 +29,9 @@ struct SchedulerConfig {
     int64_t num_kv_blocks = 0;
     int64_t block_size = 16;
     bool dynamic_split_fuse = false;
+    // Prefix caching: full blocks of prompt tokens are remembered by a hash of everything up to and including the block;
+    // a new request whose prompt starts with the same tokens shares those blocks and skips their computation.
+    bool enable_prefix_caching = false;
 };
 
 struct SeqState {
@@ -40,6 +45,8 @@ struct SeqState {
     std::vector<int32_t> blocks;
     bool finished = false;
     int64_t slot = -1;
+    std::vector<uint64_t> block_hashes;   // chain hash of every full prompt block (prefix caching)
+    int64_t num_cached_tokens = 0;        // prompt tokens whose KV came from shared blocks at the last admission
     int64_t total_len() const { return (int64_t)prompt.size() + (int64_t)generated.size(); }
     int32_t token_at(int64_t i) const { return i < (int64_t)prompt.size() ? prompt[(size_t)i] : generated[(size_t)(i - (int64_t)prompt.size())]; }
 };
@@ -74,7 +81,10 @@ public:
     void fill(const ScheduledStep& st, int32_t* desc, const DescLayout& lay, bool host_ids_for_generated = false) const;
     std::vector<Produced> commit(const ScheduledStep& st, const int32_t* tokens /* may be null */);
     void patch(const std::vector<Produced>& produced, const int32_t* tokens);
-    int64_t num_free_blocks() const { return (int64_t)free_.size(); }
+    // blocks that a sequence could be given right now: never used or invalidated ones plus cached ones that nobody holds
+    int64_t num_free_blocks() const { return (int64_t)free_.size() + (int64_t)evictable_.size(); }
+    int64_t num_cached_blocks() const { return (int64_t)by_hash_.size(); }
+    int64_t prefix_hit_tokens() const { return prefix_hit_tokens_; }
     int64_t num_preemptions() const { return preemptions_; }
     int64_t num_running() const { return (int64_t)running_.size(); }
     int64_t num_waiting() const { return (int64_t)waiting_.size(); }
@@ -85,7 +95,15 @@ private:
     bool preempt_one(const SeqState* keep, const std::vector<SeqPtr>& scheduled);
     void finish(const SeqPtr& s);
     void check_eos(const std::vector<Produced>& produced);
+    bool take_block(int32_t& out);
+    void match_prefix(SeqState& s);
+    void register_full_blocks(SeqState& s, int64_t before, int64_t after);
+    struct BlockMeta { int32_t ref = 0; bool hashed = false; uint64_t hash = 0; std::list<int32_t>::iterator lru; };
     SchedulerConfig cfg_;
+    std::vector<BlockMeta> meta_;
+    std::unordered_map<uint64_t, int32_t> by_hash_;   // chain hash -> block holding those tokens' KV
+    std::list<int32_t> evictable_;                     // cached blocks that no sequence holds, least recently released first
+    int64_t prefix_hit_tokens_ = 0;
     std::deque<int32_t> free_;
     std::deque<SeqPtr> waiting_;
     std::vector<SeqPtr> running_;

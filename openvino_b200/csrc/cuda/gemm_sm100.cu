@@ -70,6 +70,8 @@ struct GemmKParams {
     int comm_mode;            // 1: one-shot (every rank gets every partial), 2: two-shot (tile owners reduce and broadcast)
     int parity;               // one-shot staging buffer to use (consecutive fused calls alternate)
     int packets;              // 1: partials travel as flag-carrying packets; 0: plain tiles, a fence and arrival flags
+    int nvls;                 // reduce inside the switch (needs `mc`)
+    int twohop;               // one-shot sizes on more than two ranks: packets to the share's owner, reduced shares broadcast as packets
     int site;                 // call site number (< 256): with the step number it makes the one-shot packets' tag unique
     uint8_t* heap[8];
     long long stage_off;      // staging area of the chosen mode (one-shot: of the chosen parity), offset in the heap
@@ -519,7 +521,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             constexpr size_t SLOT = (size_t)BT * TILE_N * 2;        // bytes of one bf16 tile
             const int tiles = gridDim.x;
             const int W = p.world;
-            if (p.mc != nullptr) {
+            if (p.nvls) {
                 // In-switch all-reduce (NVLS). Every rank stores its bf16 partial tile in its OWN staging slot (rank 0 adds
                 // bias and residual first, so the switch's sum is the finished value and is rounded once), the ranks meet at
                 // the tile's barrier, then rank r fetches the sum over all ranks of its 1/W share of the tile with
@@ -553,7 +555,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     *reinterpret_cast<uint4*>(my_heap + slot_off + (size_t)i * 16) =
                         make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
                 }
-                fence_sys();
+                // (no fence here: the CTA barrier orders these stores before thread 0's release fence inside nvls_barrier)
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
                 const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride;
                 int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride;
@@ -564,13 +566,20 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
                 if (*abort_flag) return;
                 const int per = PIECES / W;                             // PIECES is a multiple of 256, W of 2, 4 or 8
-                for (int i = p.rank * per + dq_tid; i < (p.rank + 1) * per; i += DQ_THREADS) {
-                    const int col = i >> 4, pc = i & 15;
-                    if (col >= ntok) continue;
-                    const uint4 v = multimem_ld_reduce_bf16x8(p.mc + slot_off + (size_t)i * 16);
-                    multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(t0 + col) * p.ldo + n0 + pc * 8) * 2, v);
+                // all reducing loads of a thread are in flight together, then the stores (a load is a round trip to the switch)
+                constexpr int MAXP = (PIECES / 2 + DQ_THREADS - 1) / DQ_THREADS;
+                uint4 v[MAXP];
+#pragma unroll
+                for (int j = 0; j < MAXP; ++j) {
+                    const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
+                    if (k < per && (i >> 4) < ntok) v[j] = multimem_ld_reduce_bf16x8(p.mc + slot_off + (size_t)i * 16);
                 }
-                fence_sys();
+#pragma unroll
+                for (int j = 0; j < MAXP; ++j) {
+                    const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
+                    const int col = i >> 4, pc = i & 15;
+                    if (k < per && col < ntok) multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(t0 + col) * p.ldo + n0 + pc * 8) * 2, v[j]);
+                }
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
                 if (dq_tid == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) {
                     report_status(p.status, STATUS_PEER_TIMEOUT);
@@ -691,7 +700,80 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             // two call sites share a staging buffer within a step, so the tag names the site as well as the step
             const uint32_t tag = ((uint32_t)epoch << 8) | (uint32_t)(p.site & 255);
             if (!tile_ok && !(p.comm_mode == 2 && p.packets)) return;
-            if (p.comm_mode == 1 && p.packets) {
+            if (p.comm_mode == 1 && p.twohop) {
+                // Two hops of flag-carrying packets, no fence and no flag anywhere. Rank q owns the q-th share (PIECES / W
+                // consecutive 16-byte pieces) of every tile. Hop 1: every rank sends each piece of its bf16 partial to the
+                // piece's owner only. The owner polls the packets of its share, sums them in rank order, adds bias and
+                // residual, and (hop 2) sends the finished piece to every rank as a packet: one multimem.st through the switch
+                // when the heap has a multicast mapping, else one store per rank. Every rank then polls the finished pieces
+                // of the whole tile in its own memory and writes its own copy of `out`. Per rank and tile this moves
+                // (1 - 1/W) + 1 packet tiles in and, with multicast, (1 - 1/W) + 1/W out; pushing every partial to every
+                // rank moves W - 1 both ways. Each piece is summed once, by its owner: all ranks get the same bits.
+                const int share = PIECES / W;
+                const size_t hop1_bytes = (size_t)tiles * PIECES * 32;
+                uint8_t* mine = p.heap[p.rank] + p.stage_off;
+                for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
+                    const int col = i >> 4, owner = i / share;
+                    if (col >= ntok || owner == p.rank) continue;
+                    const uint4 v = partial_piece(col, i & 15);
+                    uint8_t* d = p.heap[owner] + p.stage_off + (((size_t)p.rank * tiles + tile_id) * share + (size_t)(i - owner * share)) * 32;
+                    st_volatile_v4(d, v.x, tag, v.y, tag);
+                    st_volatile_v4(d + 16, v.z, tag, v.w, tag);
+                }
+                bool ok_ll = true;
+                // packet_sum() adds (col * 128 + pc * 8) * 4 = i * 32 with i = rank * share + k to this base
+                const uint8_t* share_slots = mine + ((ptrdiff_t)tile_id - (ptrdiff_t)p.rank) * (ptrdiff_t)share * 32;
+                for (int k = dq_tid; k < share && ok_ll; k += DQ_THREADS) {
+                    const int i = p.rank * share + k, col = i >> 4, pc = i & 15;
+                    if (col >= ntok) continue;
+                    float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                    ok_ll = packet_sum(share_slots, (size_t)tiles * share * 32, col, pc, tag, f);
+                    if (!ok_ll) break;
+                    const uint4 o = finish_piece(f, col, pc);
+                    const size_t off = (size_t)p.stage_off + hop1_bytes + ((size_t)tile_id * PIECES + i) * 32;
+                    if (p.mc != nullptr) {
+                        multimem_st_b128(p.mc + off, make_uint4(o.x, tag, o.y, tag));
+                        multimem_st_b128(p.mc + off + 16, make_uint4(o.z, tag, o.w, tag));
+                    } else {
+                        for (int r = 0; r < W; ++r) {
+                            st_volatile_v4(p.heap[r] + off, o.x, tag, o.y, tag);
+                            st_volatile_v4(p.heap[r] + off + 16, o.z, tag, o.w, tag);
+                        }
+                    }
+                }
+                const uint8_t* done = mine + hop1_bytes + (size_t)tile_id * PIECES * 32;
+                for (int i0 = dq_tid; i0 < PIECES && ok_ll; i0 += 2 * DQ_THREADS) {
+                    // two pieces per round: their loads are in flight together
+                    uint4 a[2], b[2];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int i = i0 + j * DQ_THREADS;
+                        if (i < PIECES && (i >> 4) < ntok) {
+                            a[j] = ld_volatile_v4(done + (size_t)i * 32);
+                            b[j] = ld_volatile_v4(done + (size_t)i * 32 + 16);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        const int i = i0 + j * DQ_THREADS;
+                        if (i >= PIECES || (i >> 4) >= ntok) continue;
+                        uint32_t spins = 0;
+                        while (!(a[j].y == tag && a[j].w == tag && b[j].y == tag && b[j].w == tag)) {
+                            if (++spins > kPeerSpinLimit || ((spins & 1023u) == 0 && *abort_flag)) { ok_ll = false; break; }
+                            if (spins > 64) __nanosleep(100);
+                            a[j] = ld_volatile_v4(done + (size_t)i * 32);
+                            b[j] = ld_volatile_v4(done + (size_t)i * 32 + 16);
+                        }
+                        if (!ok_ll) break;
+                        *reinterpret_cast<uint4*>(reinterpret_cast<E*>(p.out) + (size_t)(t0 + (i >> 4)) * p.ldo + n0 + (i & 15) * 8) =
+                            make_uint4(a[j].x, a[j].z, b[j].x, b[j].z);
+                    }
+                }
+                if (!ok_ll) {
+                    report_status(p.status, STATUS_PEER_TIMEOUT);
+                    *abort_flag = 1;
+                }
+            } else if (p.comm_mode == 1 && p.packets) {
                 // One-shot with flag-carrying packets: every 16-byte store holds two (data word, tag) pairs, so the
                 // receiver sees data and "it has arrived" in the same 8-byte unit and needs neither a fence nor a flag
                 // round trip. A thread pushes its pieces of the bf16 partial to every peer, then polls the same pieces
@@ -887,9 +969,12 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 }
             }
         }
+        // The communication epilogue has ONE call site (below, after the split-K reduction): the compiler then inlines the
+        // lambda, and its by-reference captures stay in registers instead of a stack frame.
+        bool run_comm = false, comm_tile_ok = false;
         if (comm && p.splits == 1) {
-            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-            comm_epilogue(acc_ok);   // acc_ok is uniform over the epilogue threads
+            run_comm = true;
+            comm_tile_ok = acc_ok;   // acc_ok is uniform over the epilogue threads
         } else if (fast && p.act == OVB_ACT_SWIGLU) {
             // Gated MLP: the tile holds 64 "gate" rows followed by the 64 "up" rows of the same channels (the packer
             // interleaves them per tile), so out[tok, 64 * tile + c] = silu(gate_c) * up_c needs this tile only.
@@ -1005,9 +1090,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             cluster_arrive();
             cluster_wait();
             if (comm && split == 0) {
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                comm_epilogue(*abort_flag == 0);
+                run_comm = true;
+                comm_tile_ok = (*abort_flag == 0);
             }
+        }
+        if (run_comm) {
+            asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+            comm_epilogue(comm_tile_ok);
         }
     }
     // The producer and MMA warps take part in the two cluster barriers of the split-K reduction (a cluster barrier
@@ -1215,6 +1304,22 @@ int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act) {
 // Which protocol carries the partials of the fused all-reduce: flag-carrying packets (twice the bytes, no fence and no
 // flag round trip) or plain tiles with a fence and arrival flags. Every rank must choose alike, so the choice depends
 // on the world size and the mode only; OVB_COMM_PACKETS (bit 0: one-shot, bit 1: two-shot) overrides it for measurements.
+// Environment overrides for measurements (every rank must set them alike): OVB_COMM_TWOHOP = 0 / 1 forces the two-hop packet
+// protocol of the one-shot sizes off / on; OVB_COMM_NVLS_MODES is a bit mask of the modes (bit 0: T <= 128, bit 1: larger) that
+// reduce inside the switch when the heap has a multicast mapping.
+static int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+static int comm_twohop(int world) {
+    static const int env = env_int("OVB_COMM_TWOHOP", -1);
+    return env >= 0 ? env : (world > 2);
+}
+static int comm_nvls_modes() {
+    static const int env = env_int("OVB_COMM_NVLS_MODES", 2);
+    return env;
+}
+
 static int comm_packets(int world, int mode) {
     static const int env = [] {
         const char* e = getenv("OVB_COMM_PACKETS");
@@ -1311,9 +1416,13 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         }
         // In-switch reduction when the heap has a multicast mapping: plain bf16 tiles in the staging area of the mode (half of
         // what the packets need), barrier words of the call site, output in the heap, 2, 4 or 8 ranks.
-        if (c->mc_base != nullptr && out_in_heap && (c->world == 2 || c->world == 4 || c->world == 8) &&
+        if (mode == 1 && comm_twohop(c->world) && (bt * 16) % c->world == 0 && 2 * tiles * bt * 16 * 32 <= c->stage1_bytes) {
+            p.twohop = 1;
+            p.mc = static_cast<uint8_t*>(c->mc_base);   // NULL: hop 2 stores to every rank in turn
+        } else if (c->mc_base != nullptr && ((comm_nvls_modes() >> (mode - 1)) & 1) && out_in_heap && (c->world == 2 || c->world == 4 || c->world == 8) &&
             tiles * kNvlsFlagStride <= c->nvls_flags_per_site && tiles * slot <= (mode == 1 ? c->stage1_bytes : c->stage2_bytes)) {
             p.mc = static_cast<uint8_t*>(c->mc_base);
+            p.nvls = 1;
             p.nvls_flags_off = c->nvls_flags_off + (int64_t)c->site * c->nvls_flags_per_site * 4;
             p.out_off = out_heap_off;
         }

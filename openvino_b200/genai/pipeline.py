@@ -14,6 +14,7 @@ import numpy as np
 import torch
 
 from ..runtime.cuda_llm import CudaLlmExecutor, StepBuffers, StepShape
+from .native_scheduler import NativeScheduler, make_layout
 from .scheduler import ScheduledStep, Scheduler, SchedulerConfig, Sequence
 
 
@@ -80,7 +81,8 @@ class ContinuousBatchingPipeline:
     def __init__(self, executor: CudaLlmExecutor, scheduler_config: SchedulerConfig):
         self.ex = executor
         self.cfg = scheduler_config
-        self.scheduler = Scheduler(scheduler_config)
+        self.scheduler = self._make_scheduler(scheduler_config)
+        self._layouts = {id(sb): make_layout(sb.offsets, sb.Tcap, sb.Bcap, sb.max_blocks) for sb in (executor.prefill, executor.decode)}
         self._next_id = 0
         self._seqs: Dict[int, Sequence] = {}
         self.metrics = PipelineMetrics()
@@ -89,6 +91,21 @@ class ContinuousBatchingPipeline:
         for sb in (executor.prefill, executor.decode):
             for k in (0, 1):
                 self._np_views[(id(sb), k)] = {name: sb.view(name, host=k).numpy() for name in sb.offsets}
+
+    @staticmethod
+    def _make_scheduler(cfg: SchedulerConfig):
+        """The native scheduler unless the configuration asks for the Python one."""
+        if getattr(cfg, "use_native", True):
+            return NativeScheduler(cfg)
+        if getattr(cfg, "enable_prefix_caching", False):
+            raise ValueError("prefix caching is a feature of the native scheduler (use_native=True)")
+        return Scheduler(cfg)
+
+    def _fill(self, sched, st, sb, k: int) -> None:
+        if isinstance(sched, NativeScheduler):
+            sched.fill_flat(st, sb.desc_hosts[k].numpy(), self._layouts[id(sb)])
+        else:
+            sched.fill(st, self._np_views[(id(sb), k)])
 
     def add_request(self, prompt_ids, gen: GenerationConfig, request_id: Optional[int] = None) -> int:
         rid = self._next_id if request_id is None else request_id
@@ -114,7 +131,7 @@ class ContinuousBatchingPipeline:
         sb = ex.decode if decode else ex.prefill
         k = self._flip
         self._flip ^= 1
-        self.scheduler.fill(st, self._np_views[(id(sb), k)])
+        self._fill(self.scheduler, st, sb, k)
         self.metrics.h2d_bytes += ex.upload(sb, k)
         B = len(st.seqs)
         with _trace.scope("ov::genai", "decode_step" if decode else "prefill_step"):
@@ -134,7 +151,7 @@ class ContinuousBatchingPipeline:
         now = time.perf_counter()
         self.scheduler.patch(produced, toks)
         out = []
-        for s, gi, _ in produced:
+        for s, gi in ((p[0], p[1]) for p in produced):
             if gi < len(s.generated):
                 if gi == 0:
                     s.t_first = now
@@ -150,7 +167,7 @@ class ContinuousBatchingPipeline:
         descriptor on the device. ``run_plan`` then replays the steps without any host round trip: sampled
         tokens are fed back through the device-side last-token table."""
         assert gen.ignore_eos, "a plan needs output lengths that do not depend on token values"
-        sched = Scheduler(self.cfg)
+        sched = self._make_scheduler(self.cfg)
         for i, p in enumerate(prompts):
             sched.add(Sequence(i, np.asarray(p, dtype=np.int32), gen.max_new_tokens, gen.eos_token_id, True))
         ex = self.ex
@@ -163,8 +180,10 @@ class ContinuousBatchingPipeline:
             decode = st.max_q_len == 1 and len(st.seqs) <= ex.decode.Bcap
             sb = ex.decode if decode else ex.prefill
             arr = np.zeros(sb.desc_words, dtype=np.int32)
-            views = {name: arr[off:off + n] for name, (off, n) in sb.offsets.items()}
-            sched.fill(st, views)
+            if isinstance(sched, NativeScheduler):
+                sched.fill_flat(st, arr, self._layouts[id(sb)])
+            else:
+                sched.fill(st, {name: arr[off:off + n] for name, (off, n) in sb.offsets.items()})
             descs[id(sb)].append(torch.from_numpy(arr))
             steps.append((sb, len(descs[id(sb)]) - 1, StepShape(st.T, len(st.seqs), st.max_q_len, st.max_ctx)))
             sched.commit(st, None)
@@ -202,6 +221,8 @@ class ContinuousBatchingPipeline:
         out = []
         for rid in rids:
             s = self._seqs.pop(rid)
+            if isinstance(self.scheduler, NativeScheduler):
+                self.scheduler.forget(rid)
             n = len(s.generated)
             tpot = (s.t_tokens[-1] - s.t_first) / (n - 1) if n > 1 else 0.0
             out.append(GenerationResult(rid, list(s.generated), s.t_first - s.t_arrival, tpot, list(s.t_tokens)))

@@ -29,6 +29,8 @@ class SchedulerConfig:
     block_size: int = 16
     dynamic_split_fuse: bool = False
     max_blocks_per_seq: int = 0
+    enable_prefix_caching: bool = False   # native scheduler only: requests share the KV blocks of a common prompt prefix
+    use_native: bool = True               # csrc/core/sched.cpp; False: the Python scheduler of this module (same policy)
 
 
 @dataclass

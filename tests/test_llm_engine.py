@@ -71,3 +71,54 @@ def test_logits_close_to_reference():
     got = sb.logits[0].float()
     rel = ((got - ref).norm() / ref.norm()).item()
     assert rel < 3e-2, rel
+
+
+@pytest.mark.parametrize("native", [True, False])
+def test_python_and_native_scheduler_generate_the_same_tokens(native):
+    from openvino_b200.genai.pipeline import ContinuousBatchingPipeline, GenerationConfig
+    from openvino_b200.genai.scheduler import SchedulerConfig
+    from openvino_b200.models import llama
+    from openvino_b200.models.llm_config import TINY_LLAMA
+    from openvino_b200.ops import cuda as K
+    from openvino_b200.runtime.cuda_llm import CudaLlmExecutor, LlmWeights
+
+    cfg = TINY_LLAMA
+    state = llama.random_float_state(cfg, seed=9, std=0.05)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 9, 25)]
+    out = []
+    for use_native in (native, not native):
+        ex = CudaLlmExecutor(cfg, LlmWeights.from_float(cfg, state, "cuda"), num_kv_blocks=64, max_batch_tokens=128, max_seqs=4)
+        sc = SchedulerConfig(max_num_batched_tokens=32, max_num_seqs=4, num_kv_blocks=64, use_native=use_native)
+        out.append([r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, GenerationConfig(max_new_tokens=6), lookahead=1)])
+        K.check_status("generate")
+    assert out[0] == out[1]
+
+
+def test_prefix_caching_reuses_kv_blocks_and_keeps_the_tokens():
+    from openvino_b200.genai.pipeline import ContinuousBatchingPipeline, GenerationConfig
+    from openvino_b200.genai.scheduler import SchedulerConfig
+    from openvino_b200.models import llama
+    from openvino_b200.models.llm_config import TINY_LLAMA
+    from openvino_b200.ops import cuda as K
+    from openvino_b200.runtime.cuda_llm import CudaLlmExecutor, LlmWeights
+
+    cfg = TINY_LLAMA
+    state = llama.random_float_state(cfg, seed=11, std=0.05)
+    g = torch.Generator().manual_seed(4)
+    system = torch.randint(0, cfg.vocab_size, (70,), generator=g).tolist()          # shared "system prompt": four full blocks
+    prompts = [system + torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 11, 3)]
+    gen = GenerationConfig(max_new_tokens=5)
+    results = {}
+    for caching in (False, True):
+        ex = CudaLlmExecutor(cfg, LlmWeights.from_float(cfg, state, "cuda"), num_kv_blocks=64, max_batch_tokens=128, max_seqs=4)
+        sc = SchedulerConfig(max_num_batched_tokens=128, max_num_seqs=4, num_kv_blocks=64, enable_prefix_caching=caching)
+        pipe = ContinuousBatchingPipeline(ex, sc)
+        first = pipe.generate(prompts[:1], gen, lookahead=0)          # fills the cache
+        rest = pipe.generate(prompts[1:], gen, lookahead=0)           # later requests with the same prefix
+        K.check_status("prefix caching")
+        results[caching] = ([r.tokens for r in first + rest], pipe.metrics.scheduled_tokens,
+                            getattr(pipe.scheduler, "prefix_hit_tokens", 0))
+    assert results[True][0] == results[False][0]
+    assert results[True][2] == 2 * 64                                  # two later requests x four cached blocks of 16 tokens
+    assert results[True][1] == results[False][1] - 2 * 64
