@@ -158,6 +158,47 @@ def build_capi(force: bool = False) -> Path | None:
     return target
 
 
+SANITIZERS = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "undefined": ["-fsanitize=undefined", "-fno-sanitize-recover=undefined"],
+              "thread": ["-fsanitize=thread"]}
+
+
+def build_native_test(test_source: Path, sanitize: str = "", force: bool = False, core_subset=None) -> Path:
+    """Compile the native core and the C API together with one C++ test driver into a stand-alone executable, optionally
+    under a sanitizer (``address`` = ASan + UBSan, ``undefined``, ``thread``; the reference's switch for the same is
+    cmake/developer_package/compile_flags/sanitizer.cmake). Objects go to ``build/native_<sanitize>/``; nothing of the
+    regular build is touched. ``core_subset`` names the core translation units to link (default: all of them plus the C API).
+    ``python -m openvino_b200.build --sanitize=address tests/native/core_smoke.cpp`` does the same
+    from the command line."""
+    if sanitize and sanitize not in SANITIZERS:
+        raise ValueError("unknown sanitizer %r (choose from %s)" % (sanitize, ", ".join(SANITIZERS)))
+    test_source = Path(test_source).resolve()
+    out_dir = OBJ / ("native_" + (sanitize or "plain"))
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / (test_source.stem + ("" if core_subset is None else "." + "-".join(sorted(core_subset) or ["alone"])))
+    core = [s for s in core_sources() if s.stem != "bind"]
+    capi = sorted((CSRC / "capi").glob("*.cpp"))
+    if core_subset is not None:           # a driver that needs only some translation units (and no C API)
+        core, capi = [s for s in core if s.stem in set(core_subset)], []
+    hdrs = sorted((CSRC / "core").glob("*.hpp")) + sorted((PKG / "include").rglob("*.h")) + sorted((CSRC / "cuda").glob("comm_layout.h"))
+    if not force and not _stale(exe, core + capi + hdrs + [test_source]):
+        return exe
+    # the distribution's compiler knows where its sanitizer runtimes are; a compiler wrapper named by CXX may not
+    cxx = os.environ.get("OVB_NATIVE_TEST_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else os.environ.get("CXX", "g++"))
+    flags = ["-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", "-pthread", "-Wall", "-Wno-unused-function", *SANITIZERS.get(sanitize, [])]
+    inc = ["-I", str(CSRC / "core"), "-I", str(PKG / "include"), "-I", str(CSRC / "cuda")]
+
+    def compile_one(src: Path) -> Path:
+        obj = out_dir / (src.parent.name + "_" + src.stem + ".o")
+        if force or _stale(obj, [src] + hdrs):
+            _run([cxx, *flags, *inc, "-c", str(src), "-o", str(obj)])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(compile_one, core + capi + [test_source]))
+    _run([cxx, *flags, "-o", str(exe), *map(str, objs)])
+    return exe
+
+
 def kernel_resources(stem: str) -> dict:
     """Per-kernel resource usage parsed from the ptxas report of ``csrc/cuda/<stem>.cu``:
     ``{mangled name: {"registers", "stack", "spill_stores", "spill_loads"}}`` (empty when no report exists)."""
@@ -180,5 +221,10 @@ def build_all(force: bool = False) -> None:
 
 
 if __name__ == "__main__":
+    san = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--sanitize=")]
+    if san:
+        for src in [a for a in sys.argv[1:] if a.endswith(".cpp")]:
+            print("built:", build_native_test(Path(src), san[0], force="--force" in sys.argv))
+        sys.exit(0)
     build_all(force="--force" in sys.argv)
     print("built:", [p.name for p in LIB.glob("*.so")] + [p.name for p in PKG.glob("_ovcore*.so")])

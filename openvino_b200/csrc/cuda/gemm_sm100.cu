@@ -698,7 +698,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             };
             constexpr size_t LL_SLOT = 2 * SLOT;
             // two call sites share a staging buffer within a step, so the tag names the site as well as the step
-            const uint32_t tag = ((uint32_t)epoch << 8) | (uint32_t)(p.site & 255);
+            const uint32_t tag = packet_tag(epoch, p.site);
             if (!tile_ok && !(p.comm_mode == 2 && p.packets)) return;
             if (p.comm_mode == 1 && p.twohop) {
                 // Two hops of flag-carrying packets, no fence and no flag anywhere. Rank q owns the q-th share (PIECES / W
@@ -710,27 +710,26 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 // (1 - 1/W) + 1 packet tiles in and, with multicast, (1 - 1/W) + 1/W out; pushing every partial to every
                 // rank moves W - 1 both ways. Each piece is summed once, by its owner: all ranks get the same bits.
                 const int share = PIECES / W;
-                const size_t hop1_bytes = (size_t)tiles * PIECES * 32;
                 uint8_t* mine = p.heap[p.rank] + p.stage_off;
                 for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
-                    const int col = i >> 4, owner = i / share;
+                    const int col = i >> 4, owner = twohop_owner(i, share);
                     if (col >= ntok || owner == p.rank) continue;
                     const uint4 v = partial_piece(col, i & 15);
-                    uint8_t* d = p.heap[owner] + p.stage_off + (((size_t)p.rank * tiles + tile_id) * share + (size_t)(i - owner * share)) * 32;
+                    uint8_t* d = p.heap[owner] + p.stage_off + twohop_hop1_offset(p.rank, tiles, tile_id, share, i - owner * share);
                     st_volatile_v4(d, v.x, tag, v.y, tag);
                     st_volatile_v4(d + 16, v.z, tag, v.w, tag);
                 }
                 bool ok_ll = true;
                 // packet_sum() adds (col * 128 + pc * 8) * 4 = i * 32 with i = rank * share + k to this base
-                const uint8_t* share_slots = mine + ((ptrdiff_t)tile_id - (ptrdiff_t)p.rank) * (ptrdiff_t)share * 32;
+                const uint8_t* share_slots = mine + (ptrdiff_t)twohop_hop1_offset(0, tiles, tile_id, share, 0) - (ptrdiff_t)p.rank * share * kPacketBytes;
                 for (int k = dq_tid; k < share && ok_ll; k += DQ_THREADS) {
                     const int i = p.rank * share + k, col = i >> 4, pc = i & 15;
                     if (col >= ntok) continue;
                     float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    ok_ll = packet_sum(share_slots, (size_t)tiles * share * 32, col, pc, tag, f);
+                    ok_ll = packet_sum(share_slots, twohop_hop1_offset(1, tiles, 0, share, 0), col, pc, tag, f);
                     if (!ok_ll) break;
                     const uint4 o = finish_piece(f, col, pc);
-                    const size_t off = (size_t)p.stage_off + hop1_bytes + ((size_t)tile_id * PIECES + i) * 32;
+                    const size_t off = (size_t)p.stage_off + twohop_hop2_offset(tiles, PIECES, tile_id, i);
                     if (p.mc != nullptr) {
                         multimem_st_b128(p.mc + off, make_uint4(o.x, tag, o.y, tag));
                         multimem_st_b128(p.mc + off + 16, make_uint4(o.z, tag, o.w, tag));
@@ -741,7 +740,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         }
                     }
                 }
-                const uint8_t* done = mine + hop1_bytes + (size_t)tile_id * PIECES * 32;
+                const uint8_t* done = mine + twohop_hop2_offset(tiles, PIECES, tile_id, 0);
                 for (int i0 = dq_tid; i0 < PIECES && ok_ll; i0 += 2 * DQ_THREADS) {
                     // two pieces per round: their loads are in flight together
                     uint4 a[2], b[2];
@@ -1316,7 +1315,7 @@ static int comm_twohop(int world) {
     return env >= 0 ? env : (world > 2);
 }
 static int comm_nvls_modes() {
-    static const int env = env_int("OVB_COMM_NVLS_MODES", 2);
+    static const int env = env_int("OVB_COMM_NVLS_MODES", 0);
     return env;
 }
 

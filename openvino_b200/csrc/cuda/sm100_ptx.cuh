@@ -11,6 +11,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "comm_layout.h"
+
 namespace ovb {
 
 // Status codes written to the device status word (first error wins).
@@ -393,7 +395,6 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
     return v;
 }
 
-constexpr int kNvlsFlagStride = 16;   // int32 words per barrier: 8 "arrived" words (one per rank), then 8 "done" words
 
 // One thread of a CTA tells every rank "rank `rank` has reached step `epoch` at this barrier" (one multicast store) and
 // waits until the words of all `world` ranks say so. `local` / `mc` are the barrier's eight words in this rank's heap and
