@@ -13,9 +13,11 @@
 // accumulation. All the query heads of one KV group are stacked on the M side of the MMA, so K/V
 // pages are fetched once per group.
 #include <math_constants.h>
+#include <stdlib.h>
 
 #include <atomic>
 
+#include "attention.cuh"
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -66,28 +68,6 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
     return uint32_t(row * (D * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-struct PaKParams {
-    const void* q;
-    void* out;
-    const void* k_cache;
-    const void* v_cache;
-    const int* past_lens;
-    const int* subsequence_begins;
-    const int* block_indices;
-    const int* block_indices_begins;
-    float* scratch;
-    int B, T, Hq, Hkv;
-    int ldq;
-    int block_size;
-    int sliding_window;
-    int nsplit;
-    int keys_per_split;
-    float scale_log2;
-    // dense mode (no paging): k/v are [B, S, H, D] with token pitch ld_kv elements
-    int dense_S;
-    int ld_kv;
-    int causal;
-};
 
 // Address of key/value row `j` of sequence b, kv head h.
 template <int D, bool PAGED>
@@ -546,6 +526,15 @@ static int launch_decode(const PaKParams& p, cudaStream_t stream) {
     return 0;
 }
 
+// OVB_ATTN_TC=0 in the environment keeps prefill and dense attention on the mma.sync kernel (for comparisons).
+static bool use_tc_attention() {
+    static const bool on = [] {
+        const char* e = getenv("OVB_ATTN_TC");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
+}
+
 static int decode_nsplit(int B, int Hkv, int max_ctx) {
     // enough CTAs to fill the machine a few times over, at least 256 keys per split
     int by_len = (max_ctx + 255) / 256;
@@ -603,6 +592,11 @@ int ovb_paged_attention(const ovb_pa_args* a, ovb_stream_t stream_) {
     // ragged prefill / mixed: tiles of 128/G tokens per (sequence, kv head)
     const int tok_per_tile = 128 / G;
     const int num_q_tiles = a->T / tok_per_tile + a->B;   // upper bound of sum_b ceil(q_len_b / tok_per_tile)
+    // the tcgen05 kernel serves the common shapes; everything else (and OVB_ATTN_TC=0) runs on the mma.sync kernel below
+    if (use_tc_attention() && (G == 1 || G == 2 || G == 4 || G == 8)) {
+        const int rc = launch_prefill_tc(p, a->D, G, /*paged=*/true, /*f16=*/false, num_q_tiles, stream);
+        if (rc != ERR_UNSUPPORTED) return rc;
+    }
     if (a->D == 128) {
         switch (G) {
             case 1: return launch_prefill<128, 1, true, false>(p, num_q_tiles, stream);
@@ -633,6 +627,10 @@ int ovb_sdpa_dense(const void* q, const void* k, const void* v, void* out, int B
     p.scale_log2 = scale * 1.4426950408889634f;
     p.nsplit = 1;
     const int num_q_tiles = B * ((S + 127) / 128);
+    if (use_tc_attention()) {
+        const int rc = launch_prefill_tc(p, D, 1, /*paged=*/false, is_f16 != 0, num_q_tiles, stream);
+        if (rc != ERR_UNSUPPORTED) return rc;
+    }
     if (D == 64) return is_f16 ? launch_prefill<64, 1, false, true>(p, num_q_tiles, stream)
                                : launch_prefill<64, 1, false, false>(p, num_q_tiles, stream);
     if (D == 128) return is_f16 ? launch_prefill<128, 1, false, true>(p, num_q_tiles, stream)

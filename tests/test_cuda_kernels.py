@@ -312,6 +312,9 @@ def _attn_ref(q, k_all, v_all, q_lens, past_lens, Hq, Hkv, D, scale, window=0):
     ([1, 1, 1, 1], [0, 15, 16, 300], 8, 2),            # decode
     ([1] * 7, [5, 1000, 77, 256, 31, 32, 511], 32, 8),  # decode, GQA 4
     ([200, 1], [56, 9], 32, 8),                         # mixed
+    ([700, 130, 33], [330, 900, 0], 32, 8),             # long contexts: many key tiles per query tile, both stages reused
+    ([300, 520], [0, 64], 8, 8),                        # one query head per KV head
+    ([260], [100], 16, 2),                              # eight query heads per KV head
 ])
 def test_rope_kv_write_and_paged_attention(ops, q_lens, past_lens, Hq, Hkv):
     torch.manual_seed(6)
@@ -389,10 +392,11 @@ def test_paged_attention_sliding_window(ops):
         assert _rel_err(out.reshape(T, Hq, D), ref) < 1e-2
 
 
-@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.bfloat16, 128)])
-def test_sdpa_dense(ops, dtype, D):
+@pytest.mark.parametrize("S", [200, 384, 1000])
+@pytest.mark.parametrize("dtype,D", [(torch.float16, 64), (torch.bfloat16, 128), (torch.bfloat16, 64), (torch.float16, 128)])
+def test_sdpa_dense(ops, dtype, D, S):
     torch.manual_seed(8)
-    B, S, H = 3, 200, 4
+    B, H = 3, 4
     qkv = torch.randn(B * S, 3 * H * D, device="cuda").to(dtype)
     q, k, v = qkv[:, : H * D], qkv[:, H * D: 2 * H * D], qkv[:, 2 * H * D:]
     out = ops.sdpa_dense(q, k, v, B, S, H, D, ld=3 * H * D)
