@@ -12,6 +12,8 @@ namespace ovc {
 
 // Reference evaluation functions live in eval.cpp
 void register_eval_functions();
+// More operations, registered together with their reference evaluation (ops_ext.cpp)
+void register_ext_ops();
 
 namespace {
 
@@ -1124,6 +1126,7 @@ void register_all_ops() {
         r.alias("Gather", "opset8", "opset17");
 
         register_eval_functions();
+        register_ext_ops();
     });
 }
 

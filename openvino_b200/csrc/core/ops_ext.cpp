@@ -335,13 +335,9 @@ bool eval_fft(N, Ins in, Outs out, int kind) {
                     for (size_t d = 0; d < full.size(); ++d) src += id[d] * si[d];
                     ext[(size_t)o] = data[(size_t)src];
                 } else {
-                    // X[k] = conj(X[len - k]) with all other transformed indices mirrored as well
-                    for (size_t d = 0; d < full.size(); ++d) {
-                        int64_t i = id[d];
-                        if (d == ax) i = len - k;
-                        else if (std::find(axes.begin(), axes.end(), (int64_t)d) != axes.end()) i = (cur[d] - i) % cur[d];
-                        src += i * si[d];
-                    }
+                    // X[k] = conj(X[len - k]); the other transformed axes are back in the signal domain already (this axis is
+                    // the last one to be inverted), so their indices stay as they are
+                    for (size_t d = 0; d < full.size(); ++d) src += (d == ax ? len - k : id[d]) * si[d];
                     ext[(size_t)o] = (len - k) < cur[ax] ? std::conj(data[(size_t)src]) : std::complex<double>(0, 0);
                 }
             }
@@ -1462,8 +1458,11 @@ void register_ext_ops() {
                 for (int64_t y = 0; y < Ho; ++y)
                     for (int64_t xx = 0; xx < Wo; ++xx) {
                         float gx = unnorm(g[(size_t)(((b * Ho + y) * Wo + xx) * 2)], W), gy = unnorm(g[(size_t)(((b * Ho + y) * Wo + xx) * 2 + 1)], H);
-                        if (pad == "border") { gx = std::min(std::max(gx, 0.f), (float)(W - 1)); gy = std::min(std::max(gy, 0.f), (float)(H - 1)); }
-                        else if (pad == "reflection") { gx = reflect(gx, W); gy = reflect(gy, H); }
+                        // bilinear / nearest pad the sampling position itself; bicubic pads every neighbour it reads instead
+                        if (mode != "bicubic") {
+                            if (pad == "border") { gx = std::min(std::max(gx, 0.f), (float)(W - 1)); gy = std::min(std::max(gy, 0.f), (float)(H - 1)); }
+                            else if (pad == "reflection") { gx = reflect(gx, W); gy = reflect(gy, H); }
+                        }
                         for (int64_t c = 0; c < Cc; ++c) {
                             const float* img = v.data() + ((b * Cc + c) * H * W);
                             float r;

@@ -20,6 +20,55 @@ from ._graph import Model, Node, Output, as_output, constant, make_op, parameter
 from ._types import PartialShape, Type
 
 _SPEC = """
+identity Identity : data
+erfinv ErfInv : x
+bitwise_left_shift BitwiseLeftShift : a b | auto_broadcast=numpy
+bitwise_right_shift BitwiseRightShift : a b | auto_broadcast=numpy
+convert_promote_types ConvertPromoteTypes : left right | promote_unsafe=False pytorch_scalar_promotion=False u64_integer_promotion_target=f32
+space_to_depth SpaceToDepth : data | mode block_size=1
+space_to_batch SpaceToBatch : data block_shape pads_begin pads_end
+batch_to_space BatchToSpace : data block_shape crops_begin crops_end
+shuffle_channels ShuffleChannels : data | axis group=1
+reverse_sequence ReverseSequence : input seq_lengths | batch_axis seq_axis
+reorg_yolo ReorgYolo : input | stride
+bucketize Bucketize : data buckets | output_type=i64 with_right_bound=True
+search_sorted SearchSorted : sorted_sequence values | right_mode=False output_type=i64
+eye Eye : num_rows num_columns diagonal_index [batch_shape] | output_type
+random_uniform RandomUniform : output_shape min_val max_val | output_type global_seed=0 op_seed=0 alignment=TENSORFLOW
+multinomial Multinomial : probs num_samples | convert_type with_replacement log_probs global_seed=0 op_seed=0
+lrn LRN : data axes | alpha=1.0 beta=0.5 bias=1.0 size=5
+grn GRN : data | bias
+segment_max SegmentMax : data segment_ids [num_segments] | fill_mode=ZERO
+slice_scatter SliceScatter : data updates start stop step [axes]
+gather_tree GatherTree : step_ids parent_idx max_seq_len end_token
+unique Unique : data [axis] | sorted=True index_element_type=i64 count_element_type=i64
+inverse Inverse : data | adjoint=False
+grouped_matmul GroupedMatMul : mat_a mat_b [offsets]
+convolution_backprop_data ConvolutionBackpropData : data filters [output_shape] | strides pads_begin=[] pads_end=[] dilations=[] auto_pad=explicit output_padding=[]
+group_convolution_backprop_data GroupConvolutionBackpropData : data filters [output_shape] | strides pads_begin=[] pads_end=[] dilations=[] auto_pad=explicit output_padding=[]
+col2im Col2Im : data output_size kernel_size | strides=[1,1] dilations=[1,1] pads_begin=[0,0] pads_end=[0,0]
+adaptive_max_pool AdaptiveMaxPool : data output_shape | index_element_type=i64
+roi_align ROIAlign : data rois batch_indices | pooled_h pooled_w sampling_ratio spatial_scale mode aligned_mode=asymmetric
+roi_pooling ROIPooling : input coords | output_size spatial_scale method=max
+grid_sample GridSample : data grid | align_corners=False mode=bilinear padding_mode=zeros
+non_max_suppression NonMaxSuppression : boxes scores [max_output_boxes_per_class] [iou_threshold] [score_threshold] [soft_nms_sigma] | box_encoding=corner sort_result_descending=True output_type=i64
+dft DFT : data axes [signal_size]
+idft IDFT : data axes [signal_size]
+rdft RDFT : data axes [signal_size]
+irdft IRDFT : data axes [signal_size]
+lstm_cell LSTMCell : X initial_hidden_state initial_cell_state W R [B] | hidden_size activations=[] activations_alpha=[] activations_beta=[] clip=0.0
+gru_cell GRUCell : X initial_hidden_state W R [B] | hidden_size activations=[] activations_alpha=[] activations_beta=[] clip=0.0 linear_before_reset=False
+rnn_cell RNNCell : X initial_hidden_state W R [B] | hidden_size activations=[] activations_alpha=[] activations_beta=[] clip=0.0
+lstm_sequence LSTMSequence : X initial_hidden_state initial_cell_state sequence_lengths W R B | hidden_size direction activations=[] activations_alpha=[] activations_beta=[] clip=0.0
+gru_sequence GRUSequence : X initial_hidden_state sequence_lengths W R B | hidden_size direction activations=[] activations_alpha=[] activations_beta=[] clip=0.0 linear_before_reset=False
+rnn_sequence RNNSequence : X initial_hidden_state sequence_lengths W R B | hidden_size direction activations=[] activations_alpha=[] activations_beta=[] clip=0.0
+ctc_greedy_decoder CTCGreedyDecoder : data sequence_mask | merge_repeated>ctc_merge_repeated=True
+ctc_greedy_decoder_seq_len CTCGreedyDecoderSeqLen : data sequence_length [blank_index] | merge_repeated=True classes_index_type=i32 sequence_length_type=i32
+embedding_bag_offsets_sum EmbeddingBagOffsetsSum : emb_table indices offsets [default_index] [per_sample_weights]
+embedding_bag_packed_sum EmbeddingBagPackedSum : emb_table indices [per_sample_weights]
+embedding_bag_offsets EmbeddingBagOffsets : emb_table indices offsets [default_index] [per_sample_weights] | reduction=sum
+embedding_bag_packed EmbeddingBagPacked : emb_table indices [per_sample_weights] | reduction=sum
+embedding_segments_sum EmbeddingSegmentsSum : emb_table indices segment_ids num_segments [default_index] [per_sample_weights]
 abs Abs : x
 acos Acos : x
 acosh Acosh : x
@@ -150,6 +199,8 @@ def _parse_default(text):
     if text in _LITERALS:
         v = _LITERALS[text]
         return list(v) if isinstance(v, list) else v
+    if text.startswith("[") and text.endswith("]"):      # list literal: [1,1]
+        return [_parse_default(t) for t in text[1:-1].split(",") if t]
     try:
         return int(text)
     except ValueError:
@@ -161,7 +212,8 @@ def _parse_default(text):
 
 
 _REQUIRED = object()
-_TYPE_ATTRS = {"destination_type", "output_type", "index_element_type", "variable_type", "compute_type"}
+_TYPE_ATTRS = {"destination_type", "output_type", "index_element_type", "variable_type", "compute_type", "convert_type", "count_element_type",
+               "classes_index_type", "sequence_length_type", "u64_integer_promotion_target"}
 
 
 def _make_factory(py_name, op_type, version, inputs, attrs):
