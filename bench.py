@@ -98,6 +98,9 @@ def parse():
     ap.add_argument("--output-len", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (result is then marked invalid)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--direct", action="store_true",
+                    help="build the executor from an architecture description and packed random weights instead of going through "
+                         "graph -> SDPAToPagedAttention -> save_model / read_model -> Core.compile_model (same kernels, shorter start-up)")
     return ap.parse_args()
 
 
@@ -252,11 +255,50 @@ def main():
     bs = 16
     blocks_per_seq = (P + O + bs - 1) // bs + 1
     num_blocks = R * blocks_per_seq + 8
-    weights = LlmWeights.random(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
-    ex = CudaLlmExecutor(cfg, weights, num_kv_blocks=num_blocks, block_size=bs, max_batch_tokens=8192, max_seqs=R,
-                         max_blocks_per_seq=blocks_per_seq, device=dev, comm=comm)
-    sc = SchedulerConfig(max_num_batched_tokens=8192, max_num_seqs=R, num_kv_blocks=num_blocks, block_size=bs,
-                         max_blocks_per_seq=blocks_per_seq)
+    via_api = not args.direct and cfg.weight_format == "int4" and not cfg.num_experts
+    startup = {}
+    if via_api:
+        # The product path: a stateful decoder graph with int4-compressed weights (u4 constants, fp16 scales, u4 zero points,
+        # the decompression sub-graph exporters write) -> SDPAToPagedAttention -> IR on disk -> read_model ->
+        # Core.compile_model(model, "CUDA", {CUDA_SERVING_PROGRAM, MODEL_DISTRIBUTION_POLICY: TENSOR_PARALLEL}).
+        # The device analyses the graph by structure, takes this rank's slice of heads / MLP channels / vocabulary and builds
+        # the serving program; LLMPipeline wraps exactly these calls. Rank 0 writes the IR, every rank reads it.
+        import shutil
+        import openvino_b200 as ov
+        from openvino_b200 import passes
+        from openvino_b200.genai import LLMPipeline
+        from openvino_b200.models.ov_builders import build_llama_random_int4
+        ir_dir = os.path.join(tempfile.gettempdir(), "ovb_bench_%s_%s" % (cfg.name, os.environ.get("MASTER_PORT", str(os.getpid()))))
+        t0 = time.perf_counter()
+        if rank == 0:
+            os.makedirs(ir_dir, exist_ok=True)
+            graph = build_llama_random_int4(cfg, seed=0)
+            mgr = passes.Manager()
+            mgr.register_pass(passes.SDPAToPagedAttention())
+            mgr.run_passes(graph)
+            ov.save_model(graph, os.path.join(ir_dir, "openvino_model.xml"), compress_to_fp16=False)
+            del graph
+        if world > 1:
+            dist.barrier()
+        startup["build_and_save_s"] = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        llm = LLMPipeline(ir_dir, "CUDA.%d" % local_rank, comm=comm, tp_rank=rank, tp_size=world, max_num_seqs=R, max_num_batched_tokens=8192,
+                          max_model_len=P + O, block_size=bs, kv_cache_blocks=num_blocks)
+        startup["read_compile_s"] = time.perf_counter() - t0
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            shutil.rmtree(ir_dir, ignore_errors=True)
+        ex, sc = llm.executor, llm.scheduler_config
+        got = llm.config
+        assert (got.num_layers, got.num_heads, got.num_kv_heads, got.head_dim, got.ffn_size, got.hidden_size, got.vocab_size, got.weight_format) == \
+               (cfg.num_layers, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.ffn_size, cfg.hidden_size, cfg.vocab_size, "int4"), got
+    else:
+        weights = LlmWeights.random(cfg, dev, seed=0, tp_rank=rank, tp_size=world)
+        ex = CudaLlmExecutor(cfg, weights, num_kv_blocks=num_blocks, block_size=bs, max_batch_tokens=8192, max_seqs=R,
+                             max_blocks_per_seq=blocks_per_seq, device=dev, comm=comm)
+        sc = SchedulerConfig(max_num_batched_tokens=8192, max_num_seqs=R, num_kv_blocks=num_blocks, block_size=bs,
+                             max_blocks_per_seq=blocks_per_seq)
     g = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=g).tolist() for _ in range(R)]
     gen = GenerationConfig(max_new_tokens=O, ignore_eos=True)
@@ -333,7 +375,11 @@ def main():
                        "parallelism": ("tp%d" % world) if not cfg.num_experts else ("attention tp%d, experts ep%d" % (world, world)),
                        "kv_block_size": bs, "step": "one serving pass over all requests",
                        "l2": "working set (weights + KV cache) far larger than L2; no flush needed",
-                       "published_baseline": "OVMS Meta-Llama-3-8B-Instruct FP16 on Xeon 8580: 1151.94 tok/s"},
+                       "published_baseline": "OVMS Meta-Llama-3-8B-Instruct FP16 on Xeon 8580: 1151.94 tok/s",
+                       "path": ("graph with int4-compressed constants -> SDPAToPagedAttention -> save_model -> read_model -> "
+                                "Core.compile_model(CUDA, serving program%s) -> ContinuousBatchingPipeline" % (", TENSOR_PARALLEL" if world > 1 else ""))
+                               if via_api else "executor built directly from the architecture description (--direct)",
+                       "startup": startup},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
         if args.layers:

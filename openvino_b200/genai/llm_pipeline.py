@@ -44,19 +44,26 @@ class LLMPipeline:
             if os.path.isdir(path):
                 path = os.path.join(path, "openvino_model.xml")
             model = read_model(path)
-        from ..runtime import llm_import
-        from ..runtime.cuda_llm import CudaLlmExecutor
+        from .. import passes, properties as props
+        from ..runtime.core import Core
+        # the stateful form that exporters write becomes the PagedAttention form the serving program is compiled from
+        if not any(n.get_type_name() == "PagedAttentionExtension" for n in model.get_ops()):
+            model = model.clone()
+            mgr = passes.Manager()
+            mgr.register_pass(passes.SDPAToPagedAttention())
+            mgr.run_passes(model)
         dev_index = int(device.split(".")[1]) if "." in device else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
-        dev = torch.device("cuda", dev_index)
-        self.config, parts = llm_import.analyze(model)
-        weights = llm_import.build_weights(self.config, parts, dev, tp_rank, tp_size)
-        blocks_per_seq = (max_model_len + block_size - 1) // block_size + 1
-        num_blocks = kv_cache_blocks or max_num_seqs * blocks_per_seq + 8
-        self.executor = CudaLlmExecutor(self.config, weights, num_kv_blocks=num_blocks, block_size=block_size,
-                                        max_batch_tokens=max_num_batched_tokens, max_seqs=max_num_seqs, max_blocks_per_seq=blocks_per_seq,
-                                        device=dev, comm=comm)
-        self.scheduler_config = SchedulerConfig(max_num_batched_tokens=max_num_batched_tokens, max_num_seqs=max_num_seqs,
-                                                num_kv_blocks=num_blocks, block_size=block_size, max_blocks_per_seq=blocks_per_seq)
+        config = {props.cuda.serving_program: True}
+        if tp_size > 1:
+            config[props.hint.model_distribution_policy] = "TENSOR_PARALLEL"
+        self.compiled_model = Core().compile_model(model, "CUDA.%d" % dev_index, config)
+        if tp_size > 1 and (self.compiled_model.tp_rank, self.compiled_model.tp_size) != (tp_rank, tp_size):
+            raise RuntimeError("tensor-parallel rank / size (%d / %d) differ from the process group's (%d / %d)"
+                               % (tp_rank, tp_size, self.compiled_model.tp_rank, self.compiled_model.tp_size))
+        self.config = self.compiled_model.llm_config
+        self.executor, self.scheduler_config = self.compiled_model.create_llm_executor(
+            max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens, max_model_len=max_model_len, block_size=block_size,
+            kv_cache_blocks=kv_cache_blocks, comm=comm)
         self.pipeline = ContinuousBatchingPipeline(self.executor, self.scheduler_config)
         self.tokenizer = tokenizer
 

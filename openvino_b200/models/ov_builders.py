@@ -38,6 +38,8 @@ def _linear_weight(name: str, w: torch.Tensor, cfg: LlmConfig, compress: Optiona
     if compress is None:
         return constant(_f32(w), name=name).output(0)
     N, Kd = w.shape
+    if not isinstance(w, torch.Tensor):         # a placeholder of build_llama_random_int4: draw the compressed constants directly
+        return _random_compressed_weight(name, N, Kd, cfg, _linear_weight.rng)
     g = cfg.group_size
     G = Kd // g
     if compress == "int4":
@@ -59,6 +61,58 @@ def _linear_weight(name: str, w: torch.Tensor, cfg: LlmConfig, compress: Optiona
     return ops.convert(x, "f32", name=name + "/decompressed").output(0)
 
 
+def _random_compressed_weight(name: str, N: int, Kd: int, cfg: LlmConfig, rng: np.random.Generator, std: float = 0.02) -> Output:
+    """A random int4 (u4, asymmetric, group-wise) weight written straight into its compressed constants: no float copy of
+    the weight ever exists, which keeps the construction of multi-billion-parameter benchmark graphs to seconds. Nibbles
+    are uniform, zero points 8, one fp16 scale per group chosen so that the de-quantised weights have about ``std``."""
+    g = cfg.group_size
+    G = Kd // g
+    packed = np.frombuffer(rng.bytes(N * Kd // 2), dtype=np.uint8)
+    wq = constant(Tensor(packed, shape=[N, G, g], type=Type.u4, shared_memory=True), name=name + "/compressed")
+    zp = constant(Tensor(np.full(max(N * G // 2, 1), 0x88, dtype=np.uint8), shape=[N, G, 1], type=Type.u4, shared_memory=True), name=name + "/zero_point")
+    # uniform nibbles minus 8 have a standard deviation of about 4.6
+    sc = constant(((std / 4.6) * (0.75 + 0.5 * rng.random((N, G, 1)))).astype(np.float16), name=name + "/scale")
+    x = ops.subtract(ops.convert(wq, "f16"), ops.convert(zp, "f16"))
+    x = ops.multiply(x, sc)
+    x = ops.reshape(x, _i64([N, Kd]), False)
+    return ops.convert(x, "f32", name=name + "/decompressed").output(0)
+
+
+class _RandomState(dict):
+    """Stands in for the float state dict of ``build_llama`` when the weights are drawn directly in compressed form: norm
+    scales are ones, the embedding a small fp16 table; projections are made by ``_random_compressed_weight``."""
+
+
+def build_llama_random_int4(cfg: LlmConfig, seed: int = 0) -> Model:
+    """The stateful decoder of ``build_llama`` with random int4-compressed projections, for benchmarks of architectures too
+    large to quantise from float on the host in reasonable time. Same graph, same node names, same compression sub-graphs."""
+    rng = np.random.default_rng(seed)
+    shapes = {"q_proj": (cfg.num_heads * cfg.head_dim, cfg.hidden_size), "k_proj": (cfg.num_kv_heads * cfg.head_dim, cfg.hidden_size),
+              "v_proj": (cfg.num_kv_heads * cfg.head_dim, cfg.hidden_size), "o_proj": (cfg.hidden_size, cfg.num_heads * cfg.head_dim),
+              "gate_proj": (cfg.ffn_size, cfg.hidden_size), "up_proj": (cfg.ffn_size, cfg.hidden_size), "down_proj": (cfg.hidden_size, cfg.ffn_size),
+              "lm_head": (cfg.vocab_size, cfg.hidden_size)}
+
+    class _Lazy:                # a weight that is generated when the builder asks for it
+        def __init__(self, key):
+            self.shape = shapes[key]
+
+    state = _RandomState()
+    ones = torch.ones(cfg.hidden_size)
+    for l in range(cfg.num_layers):
+        p = "layers.%d." % l
+        state[p + "input_layernorm"] = ones
+        state[p + "post_attention_layernorm"] = ones
+        for key in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"):
+            state[p + key] = _Lazy(key)
+    state["norm"] = ones
+    state["lm_head"] = _Lazy("lm_head")
+    # fp16 values with random sign and mantissa and the exponent of 2^-6: magnitudes in [0.0156, 0.0313)
+    bits = np.frombuffer(rng.bytes(cfg.vocab_size * cfg.hidden_size * 2), dtype=np.uint16)
+    state["embed_tokens"] = torch.from_numpy(((bits & np.uint16(0x83FF)) | np.uint16(0x2400)).view(np.float16).reshape(cfg.vocab_size, cfg.hidden_size))
+    state["_rng"] = rng
+    return build_llama(cfg, state, compress="int4")
+
+
 def _rms(x: Output, gamma: np.ndarray, eps: float, name: str) -> Output:
     sq = ops.power(x, np.float32(2.0))
     var = ops.reduce_mean(sq, _i64([-1]), True)
@@ -77,6 +131,7 @@ def _rope(x: Output, cos: Output, sin: Output, D: int) -> Output:
 def build_llama(cfg: LlmConfig, state: Dict[str, torch.Tensor], compress: Optional[str] = None, stateful: bool = True) -> Model:
     """Stateful decoder ``Model`` with fp32 activations. ``compress``: None | "int4" | "int8" (group-wise, asymmetric)."""
     H, D, Hq, Hkv = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+    _linear_weight.rng = state.get("_rng")
     input_ids = parameter(PartialShape([-1, -1]), "i64", "input_ids")
     attention_mask = parameter(PartialShape([-1, -1]), "i64", "attention_mask")
     position_ids = parameter(PartialShape([-1, -1]), "i64", "position_ids")
@@ -84,7 +139,10 @@ def build_llama(cfg: LlmConfig, state: Dict[str, torch.Tensor], compress: Option
     for p in (input_ids, attention_mask, position_ids, beam_idx):
         p.output(0).set_names({p.get_friendly_name()})
 
-    embed = constant(_f32(state["embed_tokens"]), name="model.embed_tokens.weight")
+    if state["embed_tokens"].dtype == torch.float16:     # fp16 table + Convert, as exporters of compressed models write it
+        embed = ops.convert(constant(state["embed_tokens"].numpy(), name="model.embed_tokens.weight"), "f32")
+    else:
+        embed = constant(_f32(state["embed_tokens"]), name="model.embed_tokens.weight")
     h = ops.gather(embed, input_ids, _i64(0), name="embed").output(0)             # [B, L, H]
 
     # rotary tables from position ids: [B, L] -> cos/sin [B, 1, L, D]

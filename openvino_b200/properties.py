@@ -166,6 +166,10 @@ cuda = _Namespace(
     tensor_parallel_size=_Prop("CUDA_TENSOR_PARALLEL_SIZE"),
     memory_fraction=_Prop("CUDA_MEMORY_FRACTION"),
     weight_layout=_Prop("CUDA_WEIGHT_LAYOUT"),
+    # compile a decoder-only LLM graph into the serving program (paged KV cache, ragged batches, CUDA graphs, fused
+    # tensor-parallel collectives) instead of the general graph program; the compiled model then hands out the executor
+    # that a continuous-batching pipeline drives
+    serving_program=_Prop("CUDA_SERVING_PROGRAM"),
 )
 
 

@@ -1239,6 +1239,62 @@ class CudaCompiledModel(CompiledModel):
 _PRECISIONS = {"f32": None, "f16": torch.float16, "bf16": torch.bfloat16}
 
 
+class CudaServingCompiledModel(CompiledModel):
+    """A decoder-only LLM compiled for serving. The graph (stateful SDPA form or PagedAttention form, dense or
+    weight-compressed) is analysed by structure (runtime/llm_import.py); the compiled model keeps the architecture and the
+    weights found in the graph and builds this rank's executor on request. The partition over the GPUs follows the graph:
+    with ``MODEL_DISTRIBUTION_POLICY = TENSOR_PARALLEL`` and ``torch.distributed`` initialised, rank r takes its slice of
+    the attention heads (rows of the q / k / v projections, columns of the output projection), of the MLP channels (rows of
+    gate / up, columns of down) and of the vocabulary; the row-parallel projections then run with the all-reduce fused into
+    their epilogue. Reference flow: the PagedAttention model compiled by the device plugin for openvino.genai's continuous
+    batching (src/core/src/pass/sdpa_to_paged_attention.cpp, src/plugins/intel_gpu/src/plugin/transformations_pipeline.cpp)."""
+
+    def __init__(self, plugin, model, config, device: torch.device):
+        super().__init__(plugin, model, config, model)
+        from . import llm_import
+        self.device = device
+        self.llm_config, self._parts = llm_import.analyze(model)
+        policy = str(config.get(props.hint.model_distribution_policy, "") or "")
+        self.tp_rank, self.tp_size = 0, 1
+        if "TENSOR_PARALLEL" in policy and torch.distributed.is_available() and torch.distributed.is_initialized():
+            self.tp_rank, self.tp_size = torch.distributed.get_rank(), torch.distributed.get_world_size()
+        self._weights = None
+        self._comm = None
+
+    def weights(self):
+        """This rank's shard in the kernels' layouts (built once)."""
+        if self._weights is None:
+            from . import llm_import
+            with torch.cuda.device(self.device):
+                self._weights = llm_import.build_weights(self.llm_config, self._parts, self.device, self.tp_rank, self.tp_size)
+            self._parts = None      # the host copies of the constants are not needed any more
+        return self._weights
+
+    def create_llm_executor(self, max_num_seqs: int = 64, max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 16,
+                            kv_cache_blocks: int = 0, comm=None):
+        """The executor of this rank plus the scheduler limits that fit it: ``(executor, SchedulerConfig)``."""
+        from ..genai.scheduler import SchedulerConfig
+        from .cuda_llm import CudaLlmExecutor
+        if self.tp_size > 1 and comm is None:
+            if self._comm is None:
+                from ..parallel.comm import PeerCommunicator
+                self._comm = PeerCommunicator(self.tp_rank, self.tp_size, self.device)
+            comm = self._comm
+        blocks_per_seq = (max_model_len + block_size - 1) // block_size + 1
+        num_blocks = kv_cache_blocks or max_num_seqs * blocks_per_seq + 8
+        with torch.cuda.device(self.device):
+            ex = CudaLlmExecutor(self.llm_config, self.weights(), num_kv_blocks=num_blocks, block_size=block_size,
+                                 max_batch_tokens=max_num_batched_tokens, max_seqs=max_num_seqs, max_blocks_per_seq=blocks_per_seq,
+                                 device=self.device, comm=comm, use_cuda_graphs=bool(self.config.get(props.cuda.use_cuda_graphs, True)))
+        sc = SchedulerConfig(max_num_batched_tokens=max_num_batched_tokens, max_num_seqs=max_num_seqs, num_kv_blocks=num_blocks,
+                             block_size=block_size, max_blocks_per_seq=blocks_per_seq)
+        return ex, sc
+
+    def _make_runner(self, request):
+        raise RuntimeError("[CUDA] a model compiled with CUDA_SERVING_PROGRAM is driven by a generation pipeline "
+                           "(openvino_b200.genai.LLMPipeline / ContinuousBatchingPipeline), not by infer requests")
+
+
 class CudaPlugin(Plugin):
     device_name = "CUDA"
     description = "NVIDIA B200 (sm_100a)"
@@ -1250,7 +1306,7 @@ class CudaPlugin(Plugin):
         self._contexts: Dict[int, RemoteContext] = {}
 
     def supported_properties(self):
-        return super().supported_properties() + [props.cuda.use_cuda_graphs, props.cuda.tensor_parallel_size, props.device.uuid,
+        return super().supported_properties() + [props.cuda.use_cuda_graphs, props.cuda.tensor_parallel_size, props.cuda.serving_program, props.device.uuid,
                                                  props.device.architecture, props.device.type, props.optimal_batch_size,
                                                  props.hint.kv_cache_precision, props.hint.model_distribution_policy]
 
@@ -1304,6 +1360,8 @@ class CudaPlugin(Plugin):
         if str(cfg.get(props.hint.performance_mode)) == "THROUGHPUT" and props.num_streams not in config and props.num_streams not in self.config:
             cfg[props.num_streams] = 2
         dev = self._device(cfg)
+        if str(cfg.get(props.cuda.serving_program, "")).upper() in ("TRUE", "YES", "1"):
+            return CudaServingCompiledModel(self, model, cfg, dev)
         rm = self.transform(model)
         policy = str(cfg.get(props.hint.model_distribution_policy, "") or "")
         if "TENSOR_PARALLEL" in policy and torch.distributed.is_available() and torch.distributed.is_initialized() \

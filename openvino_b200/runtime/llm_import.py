@@ -3,8 +3,8 @@
 The CUDA device runs any graph through its graph program; a Llama-family decoder additionally gets the serving
 program (``CudaLlmExecutor``: paged KV cache, ragged batches, CUDA graphs, tensor parallelism). This module reads the
 architecture (hidden size, heads, head size, RoPE base, norm epsilon, vocabulary) and the weights out of the graph
-after the device's fusion passes: RMS / RoPE / FullyConnected / FullyConnectedCompressed nodes named by the usual
-exporter convention (``...layers.<i>.self_attn.q_proj`` and so on). Compressed weights are taken in their IR form
+after the device's fusion passes, following the data flow around every attention operation (node names play no part):
+RMS / RoPE / FullyConnected / FullyConnectedCompressed nodes. Compressed weights are taken in their IR form
 (u4/u8 Constant + fp16 scales + zero points) and re-packed for the kernels without ever being expanded to float.
 
 This is the step the reference performs inside its device plugins when a PagedAttention model is compiled
@@ -13,7 +13,6 @@ the one the reference's own LLM builders emit (src/frontends/gguf/src/builder/ar
 """
 from __future__ import annotations
 
-import re
 from typing import Dict, Optional, Tuple
 
 import numpy as np
@@ -23,9 +22,6 @@ from .. import _ovcore as _c
 from .._graph import Model, Node
 from .._types import Type
 from ..models.llm_config import LlmConfig
-
-_PROJ = re.compile(r"layers\.(\d+)\.(self_attn\.(?:q|k|v|o)_proj|mlp\.(?:gate|up|down)_proj)$")
-_NORM = re.compile(r"layers\.(\d+)\.(input_layernorm|post_attention_layernorm)$")
 
 
 class NotAnLlm(RuntimeError):
@@ -116,52 +112,134 @@ class _Linear:
         return K.PackedWeight.from_ir_u8(q.reshape(self.N, self.K), s, z, self.N, self.K, g)
 
 
+_FC = ("FullyConnected", "FullyConnectedCompressed")
+_DEAD_ENDS = ("Parameter", "Constant", "ReadValue", "Result", "Assign")
+
+
+def _nearest_fc_ancestor(out_port) -> Optional[Node]:
+    """Closest FullyConnected node that feeds ``out_port`` (breadth first over all data inputs; shape plumbing, RoPE, the
+    KV-state Concat and the grouped-query broadcast are walked through, parameters / constants / states end a path)."""
+    seen, frontier = set(), [out_port.get_node()]
+    while frontier:
+        nxt = []
+        for n in frontier:
+            if n in seen:
+                continue
+            seen.add(n)
+            t = n.get_type_name()
+            if t in _FC:
+                return n
+            if t in _DEAD_ENDS or t in ("ScaledDotProductAttention", "PagedAttentionExtension", "RMS"):
+                continue
+            for i in range(n.get_input_size()):
+                nxt.append(n.input_value(i).get_node())
+        frontier = nxt
+    return None
+
+
+def _consumers(node: Node, port: int = 0):
+    return [inp.get_node() for inp in node.output(port).get_target_inputs()]
+
+
+def _nearest_fc_descendant(node: Node) -> Optional[Node]:
+    """Closest FullyConnected node fed (through reshapes / transposes / converts) by ``node``."""
+    seen, frontier = set(), [node]
+    while frontier:
+        nxt = []
+        for n in frontier:
+            for c in _consumers(n):
+                if c in seen:
+                    continue
+                seen.add(c)
+                t = c.get_type_name()
+                if t in _FC:
+                    return c
+                if t in ("Reshape", "Transpose", "Convert", "Squeeze", "Unsqueeze"):
+                    nxt.append(c)
+        frontier = nxt
+    return None
+
+
+def _one(nodes, what: str) -> Node:
+    if len(nodes) != 1:
+        raise NotAnLlm("expected exactly one %s, found %d" % (what, len(nodes)))
+    return nodes[0]
+
+
+def _gamma(rms: Node) -> torch.Tensor:
+    g = rms.input_value(1).get_node()
+    if g.get_type_name() == "Convert":
+        g = g.input_value(0).get_node()
+    if g.get_type_name() != "Constant":
+        raise NotAnLlm("the scale of %s is not a constant" % rms.get_friendly_name())
+    return _const_f32(g).reshape(-1)
+
+
 def analyze(model: Model) -> Tuple[LlmConfig, Dict]:
-    """Fused graph -> (architecture, {name: _Linear | tensor}). Raises ``NotAnLlm`` when the graph does not look like one."""
+    """Fused graph -> (architecture, {name: _Linear | tensor}). The decoder is recognised by its STRUCTURE, whatever the
+    nodes are called: every attention operation (ScaledDotProductAttention or PagedAttentionExtension) is one layer; its
+    query / key / value inputs lead back to three projections that share one RMS input; its output leads on to the output
+    projection, the residual Add, the second RMS, the gate (the projection that feeds Swish) and up projections, their
+    product, the down projection and the second residual Add. After the last layer come the final RMS and the projection
+    onto the vocabulary; before the first one the embedding Gather. Raises ``NotAnLlm`` when the graph is not of this form."""
     m = model.clone()
     _c.run_moc_transformations(m._m, True)
     _c.run_llm_fusions(m._m)
     ops = m.get_ops()
-    lin: Dict[Tuple[int, str], _Linear] = {}
-    norms: Dict[Tuple[int, str], torch.Tensor] = {}
-    lm_head = final_norm = embed = None
-    eps = 1e-6
-    for n in ops:
-        t = n.get_type_name()
-        name = n.get_friendly_name()
-        if t in ("FullyConnected", "FullyConnectedCompressed"):
-            mm = _PROJ.search(name)
-            if mm:
-                lin[(int(mm.group(1)), mm.group(2).split(".")[1])] = _Linear(n)
-            elif name.endswith("lm_head"):
-                lm_head = _Linear(n)
-        elif t == "RMS":
-            gamma = n.input_value(1).get_node()
-            if gamma.get_type_name() == "Convert":
-                gamma = gamma.input_value(0).get_node()
-            mm = _NORM.search(name)
-            eps = float(n.get_attribute("epsilon"))
-            if mm:
-                norms[(int(mm.group(1)), mm.group(2))] = _const_f32(gamma).reshape(-1)
-            elif name.endswith("model.norm") or name.endswith("norm"):
-                final_norm = _const_f32(gamma).reshape(-1)
-        elif t == "Gather" and embed is None:
-            src = n.input_value(0).get_node()
-            if src.get_type_name() == "Convert":
-                src = src.input_value(0).get_node()
-            if src.get_type_name() == "Constant" and len(src.get_output_shape(0)) == 2 and src.get_output_shape(0)[0] > 16:
-                embed = _const_f32(src)
-    layers = sorted({k[0] for k in lin})
-    if not layers or lm_head is None or embed is None or final_norm is None:
-        raise NotAnLlm("the graph has no decoder layers / embedding / final norm / lm_head with the expected names")
-    for l in layers:
-        for p in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"):
-            if (l, p) not in lin:
-                raise NotAnLlm("layer %d lacks %s" % (l, p))
-    # head geometry from the attention op: query [B, Hq, L, D]
     att = [n for n in ops if n.get_type_name() in ("ScaledDotProductAttention", "PagedAttentionExtension")]
     if not att:
         raise NotAnLlm("no attention operation found")
+    lin: Dict[Tuple[int, str], _Linear] = {}
+    norms: Dict[Tuple[int, str], torch.Tensor] = {}
+    eps = 1e-6
+    last_add = first_norm = None
+    for l, a in enumerate(att):
+        q, k, v = (_nearest_fc_ancestor(a.input_value(i)) for i in range(3))
+        if q is None or k is None or v is None:
+            raise NotAnLlm("attention %d is not fed by three projections" % l)
+        n1 = q.input_value(0).get_node()
+        if n1.get_type_name() != "RMS" or any(x.input_value(0).get_node() != n1 for x in (k, v)):
+            raise NotAnLlm("the projections of attention %d do not share one RMS input" % l)
+        o = _nearest_fc_descendant(a)
+        if o is None:
+            raise NotAnLlm("attention %d has no output projection" % l)
+        add1 = _one([c for c in _consumers(o) if c.get_type_name() == "Add"], "residual Add after the attention output projection")
+        n2 = _one([c for c in _consumers(add1) if c.get_type_name() == "RMS"], "RMS after the attention residual")
+        mlp = [c for c in _consumers(n2) if c.get_type_name() in _FC]
+        gates = [c for c in mlp if any(x.get_type_name() == "Swish" for x in _consumers(c))]
+        ups = [c for c in mlp if c not in gates]
+        if len(gates) != 1 or len(ups) != 1:
+            raise NotAnLlm("layer %d: expected one gate (followed by Swish) and one up projection, found %d / %d" % (l, len(gates), len(ups)))
+        act = _one([x for x in _consumers(gates[0]) if x.get_type_name() == "Swish"], "Swish")
+        prod = _one([x for x in _consumers(act) if x.get_type_name() == "Multiply"], "gate x up product")
+        down = _nearest_fc_descendant(prod)
+        if down is None:
+            raise NotAnLlm("layer %d has no down projection" % l)
+        add2 = _one([c for c in _consumers(down) if c.get_type_name() == "Add"], "residual Add after the MLP")
+        for key, node in (("q_proj", q), ("k_proj", k), ("v_proj", v), ("o_proj", o), ("gate_proj", gates[0]), ("up_proj", ups[0]), ("down_proj", down)):
+            lin[(l, key)] = _Linear(node)
+        norms[(l, "input_layernorm")] = _gamma(n1)
+        norms[(l, "post_attention_layernorm")] = _gamma(n2)
+        eps = float(n1.get_attribute("epsilon"))
+        if l == 0:
+            first_norm = n1
+        last_add = add2
+    fn = _one([c for c in _consumers(last_add) if c.get_type_name() == "RMS"], "final RMS")
+    final_norm = _gamma(fn)
+    lm_head = _Linear(_one([c for c in _consumers(fn) if c.get_type_name() in _FC], "projection onto the vocabulary"))
+    emb = first_norm.input_value(0).get_node()
+    while emb.get_type_name() in ("Convert", "Reshape", "Squeeze", "Unsqueeze"):
+        emb = emb.input_value(0).get_node()
+    if emb.get_type_name() != "Gather":
+        raise NotAnLlm("the first layer is not fed by an embedding Gather")
+    src = emb.input_value(0).get_node()
+    if src.get_type_name() == "Convert":
+        src = src.input_value(0).get_node()
+    if src.get_type_name() != "Constant" or len(src.get_output_shape(0)) != 2:
+        raise NotAnLlm("the embedding table is not a 2-D constant")
+    embed = _const_f32(src)
+    layers = list(range(len(att)))
+    # head geometry from the attention op: query [B, Hq, L, D]
     H = embed.shape[1]
     if att[0].get_type_name() == "ScaledDotProductAttention":
         qs = att[0].input_value(0).get_partial_shape()

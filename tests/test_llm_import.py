@@ -1,0 +1,73 @@
+"""Structural recognition of decoder-only LLM graphs (runtime/llm_import.py): node names play no part."""
+import numpy as np
+import pytest
+import torch
+
+import openvino_b200 as ov
+from openvino_b200 import passes
+from openvino_b200.models import llama
+from openvino_b200.models.llm_config import TINY_LLAMA
+from openvino_b200.models.ov_builders import build_llama, build_llama_random_int4
+from openvino_b200.runtime import llm_import
+
+
+def _cfg(layers=2):
+    return TINY_LLAMA.with_(vocab_size=320, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=128, ffn_size=512, group_size=128, num_layers=layers)
+
+
+def _to_paged(m):
+    mgr = passes.Manager()
+    mgr.register_pass(passes.SDPAToPagedAttention())
+    mgr.run_passes(m)
+    return m
+
+
+@pytest.mark.parametrize("compress", [None, "int4", "int8"])
+@pytest.mark.parametrize("paged", [False, True])
+def test_renamed_graph_is_still_recognised(compress, paged, tmp_path):
+    cfg = _cfg()
+    state = llama.random_float_state(cfg, seed=7, std=0.05)
+    m = build_llama(cfg, state, compress=compress)
+    if paged:
+        _to_paged(m)
+    for i, n in enumerate(m.get_ops()):
+        if n.get_type_name() not in ("Parameter", "Result"):
+            n.set_friendly_name("op_%d" % i)                 # nothing is called q_proj / layers.N / lm_head any more
+    ov.save_model(m, str(tmp_path / "m.xml"), compress_to_fp16=False)
+    back = ov.Core().read_model(str(tmp_path / "m.xml"))
+    got, parts = llm_import.analyze(back)
+    assert (got.num_layers, got.num_heads, got.num_kv_heads, got.head_dim, got.ffn_size, got.hidden_size, got.vocab_size) == (2, 4, 2, 128, 512, 256, 320)
+    assert got.weight_format == {None: "bf16", "int4": "int4", "int8": "int8"}[compress]
+    assert abs(got.rope_theta - cfg.rope_theta) / cfg.rope_theta < 1e-3 and abs(got.rms_eps - cfg.rms_eps) < 1e-9
+    # the right constants ended up in the right roles
+    if compress is None:
+        for l in range(2):
+            for key in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"):
+                assert torch.allclose(parts["lin"][(l, key)].w, state["layers.%d.%s" % (l, key)].float(), atol=1e-6), (l, key)
+            assert torch.allclose(parts["norms"][(l, "input_layernorm")], state["layers.%d.input_layernorm" % l].float())
+            assert torch.allclose(parts["norms"][(l, "post_attention_layernorm")], state["layers.%d.post_attention_layernorm" % l].float())
+        assert torch.allclose(parts["lm_head"].w, state["lm_head"].float(), atol=1e-6)
+        assert torch.allclose(parts["final_norm"], state["norm"].float()) and torch.allclose(parts["embed"], state["embed_tokens"].float(), atol=1e-6)
+    else:
+        assert parts["lin"][(0, "q_proj")].compressed and parts["lin"][(1, "down_proj")].G == 512 // 128
+
+
+def test_graphs_that_are_not_decoders_are_refused():
+    from openvino_b200 import opset as ops
+    x = ops.parameter([1, 8], "f32", "x")
+    m = ov.Model([ops.result(ops.relu(x))], [x], "m")
+    with pytest.raises(llm_import.NotAnLlm):
+        llm_import.analyze(m)
+
+
+def test_random_int4_builder_writes_compressed_constants_directly():
+    cfg = _cfg(layers=1)
+    m = _to_paged(build_llama_random_int4(cfg, seed=3))
+    got, parts = llm_import.analyze(m)
+    assert got.weight_format == "int4" and got.num_layers == 1 and got.group_size == 128
+    q = parts["lin"][(0, "q_proj")]
+    assert q.q.shape == (512, 256 // 2) and q.q.dtype == torch.uint8 and int(q.zp.min()) == 8 and int(q.zp.max()) == 8
+    w = (torch.stack([q.q & 0xF, q.q >> 4], -1).reshape(512, 256).float() - 8.0) * q.scales.repeat_interleave(128, 1)
+    assert 0.012 < float(w.std()) < 0.03                    # about the 0.02 that float initialisation would give
+    emb = parts["embed"]
+    assert emb.shape == (320, 256) and 0.015 < float(emb.abs().min()) and float(emb.abs().max()) < 0.032
