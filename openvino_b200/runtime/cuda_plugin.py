@@ -29,6 +29,7 @@ from .. import properties as props
 from .._graph import Model, Node, Output
 from .._tensor import Tensor, torch_dtype
 from .._types import Type
+from .plugin_config import ConfigOption, OptionVisibility, PluginConfig
 from .core import CompiledModel, InferRequest, Plugin, ProfilingInfo, VariableState
 
 _FLOAT = ("f32", "f16", "bf16", "f64")
@@ -1239,6 +1240,33 @@ class CudaCompiledModel(CompiledModel):
 _PRECISIONS = {"f32": None, "f16": torch.float16, "bf16": torch.bfloat16}
 
 
+class CudaConfig(PluginConfig):
+    """Option table of the CUDA device (validated types, visibility, ``OV_<NAME>`` environment and config-file overrides)."""
+
+    def declare_options(self) -> None:
+        R, RI, D = OptionVisibility.RELEASE, OptionVisibility.RELEASE_INTERNAL, OptionVisibility.DEBUG
+        self.register(ConfigOption(props.hint.inference_precision, "f32", "compute precision of graph programs", lambda v: str(v).lower() in _PRECISIONS, R))
+        self.register(ConfigOption(props.hint.performance_mode, "LATENCY", "LATENCY | THROUGHPUT | CUMULATIVE_THROUGHPUT",
+                                   lambda v: v in ("LATENCY", "THROUGHPUT", "CUMULATIVE_THROUGHPUT"), R))
+        self.register(ConfigOption(props.num_streams, 1, "streams (infer requests that run concurrently); -1 = automatic", lambda v: v >= -1, R))
+        self.register(ConfigOption(props.hint.model_distribution_policy, "", "'' | TENSOR_PARALLEL | PIPELINE_PARALLEL",
+                                   lambda v: all(p in ("", "TENSOR_PARALLEL", "PIPELINE_PARALLEL") for p in str(v).replace(" ", "").split(",")), R))
+        self.register(ConfigOption(props.hint.kv_cache_precision, "bf16", "element type of the paged KV cache: bf16 | f16 | u8",
+                                   lambda v: str(v).lower() in ("bf16", "f16", "u8", "dynamic"), R))
+        self.register(ConfigOption(props.cuda.use_cuda_graphs, True, "capture decode steps of the serving program in CUDA graphs", None, R))
+        self.register(ConfigOption(props.cuda.serving_program, False, "compile a decoder-only LLM graph into the serving program", None, R))
+        self.register(ConfigOption(props.cuda.tensor_parallel_size, 0, "ranks of the tensor-parallel group (0 = the process group's size)", lambda v: 0 <= v <= 8, R))
+        self.register(ConfigOption(props.cuda.memory_fraction, 0.9, "share of the free device memory the KV cache may take", lambda v: 0.0 < v <= 1.0, RI))
+        self.register(ConfigOption(props.enable_profiling, False, "per-node timing of graph programs (PERF_COUNT)", None, R))
+        self.register(ConfigOption("CUDA_PDL", True, "programmatic dependent launch of the serving kernels", None, RI))
+        self.register(ConfigOption("CUDA_DUMP_GRAPH_PROGRAM", "", "write the node list of compiled graph programs to this file", None, D, str))
+
+    def finalize_impl(self) -> None:
+        # a throughput hint without an explicit stream count asks for two streams
+        if self[props.hint.performance_mode] == "THROUGHPUT" and not self.is_set_by_user(props.num_streams):
+            self.set_property({props.num_streams: 2})
+
+
 class CudaServingCompiledModel(CompiledModel):
     """A decoder-only LLM compiled for serving. The graph (stateful SDPA form or PagedAttention form, dense or
     weight-compressed) is analysed by structure (runtime/llm_import.py); the compiled model keeps the architecture and the
@@ -1352,13 +1380,27 @@ class CudaPlugin(Plugin):
         cuda_fusions.run(rm)
         return rm
 
+    def make_config(self, config: dict, model: Optional[Model] = None, device_name: str = "CUDA") -> CudaConfig:
+        """The validated option table of one compile call: public properties (RELEASE options only), then the derived
+        options, the configuration file and the environment. Unknown names are left to the generic property handling."""
+        pc = CudaConfig()
+        known = {k: v for k, v in config.items() if k in pc._options}
+        pc.set_user_property(known, OptionVisibility.RELEASE)
+        return pc.finalize(model, device_name)
+
     def compile_model(self, model: Model, config: dict) -> CompiledModel:
         cfg = self.merged_config(config)
+        try:
+            pc = self.make_config(cfg, model, "CUDA")
+        except (ValueError, PermissionError) as e:
+            raise RuntimeError("[CUDA] %s" % e)
+        cfg.update({k: v for k, v in pc.to_dict().items() if k in cfg or pc._options[k].value != pc._options[k].default})
+        if not pc["CUDA_PDL"]:
+            from ..ops import cuda as K
+            K.lib().ovb_set_pdl(0)
         prec = str(cfg.get(props.hint.inference_precision, "f32")).lower()
         if prec not in _PRECISIONS:
             raise RuntimeError("[CUDA] unsupported inference precision %s" % prec)
-        if str(cfg.get(props.hint.performance_mode)) == "THROUGHPUT" and props.num_streams not in config and props.num_streams not in self.config:
-            cfg[props.num_streams] = 2
         dev = self._device(cfg)
         if str(cfg.get(props.cuda.serving_program, "")).upper() in ("TRUE", "YES", "1"):
             return CudaServingCompiledModel(self, model, cfg, dev)
