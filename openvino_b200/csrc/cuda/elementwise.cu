@@ -158,8 +158,10 @@ layernorm_kernel(const E* __restrict__ x, const E* __restrict__ residual, const 
 }
 
 // ------------------------------------------------------------------------------------ SwiGLU gate
-__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int F) {
+// `nrows` (optional, device memory, written by an earlier kernel): only the first min(*nrows, rows) rows are valid.
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows, int F, const int* __restrict__ nrows) {
     pdl_enter();
+    if (nrows != nullptr) rows = min(rows, *nrows);
     const int fv = F >> 3;
     const size_t total = (size_t)rows * fv;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -462,6 +464,100 @@ __global__ void moe_group_kernel(const float* __restrict__ route, int T, int E, 
 }
 
 // act[i, f] = silu(gu[i, f]) * gu[i, F + f] * route[idx[i], e]  for the gathered rows of one expert
+// ---- single-launch expert path: rows of all local experts sorted by expert, no host round trip
+// Per local expert (one block each, like moe_group_kernel): the position of every token inside the expert's row list
+// (pos[t * nloc + e], -1 when the token is not routed to the expert) and the number of rows (counts[e]).
+__global__ void moe_positions_kernel(const float* __restrict__ route, int T, int E, int e0, int nloc, int* __restrict__ pos, int* __restrict__ counts) {
+    pdl_enter();
+    const int e = blockIdx.x;
+    __shared__ int warp_sums[32];
+    __shared__ int base_s;
+    if (threadIdx.x == 0) base_s = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int t0 = 0; t0 < T; t0 += blockDim.x) {
+        const int t = t0 + threadIdx.x;
+        const bool hit = t < T && route[(size_t)t * E + e0 + e] != 0.f;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_sums[warp] = __popc(m);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_sums[w];
+        if (t < T) pos[(size_t)t * nloc + e] = hit ? base_s + before + __popc(m & ((1u << lane) - 1u)) : -1;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < nwarps; ++w) tot += warp_sums[w];
+            base_s += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = base_s;
+}
+
+// Row offsets of the experts (offsets[nloc + 1], written by block 0) and the gathered activations: row offsets[e] + pos of
+// the sorted buffer is a copy of token t's row. One block per token.
+__global__ void moe_gather_sorted_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pos, const int* __restrict__ counts,
+                                         int* __restrict__ offsets, __nv_bfloat16* __restrict__ xg, int T, int H, int nloc, int cap) {
+    pdl_enter();
+    __shared__ int off_s[65];
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < nloc; ++e) { off_s[e] = acc; acc += counts[e]; }
+        off_s[nloc] = acc;
+        if (blockIdx.x == 0) for (int e = 0; e <= nloc; ++e) offsets[e] = min(off_s[e], cap);
+    }
+    __syncthreads();
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int hv = H >> 3;
+    for (int e = 0; e < nloc; ++e) {
+        const int p_ = pos[(size_t)t * nloc + e];
+        if (p_ < 0) continue;
+        const int r = off_s[e] + p_;
+        if (r >= cap) continue;
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * H);
+        uint4* dst = reinterpret_cast<uint4*>(xg + (size_t)r * H);
+        for (int c = threadIdx.x; c < hv; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+// dst[t] = (accumulate ? dst[t] : 0) + sum over the local experts of route[t, e0 + e] * y[offsets[e] + pos[t, e]], experts in
+// index order (deterministic, no atomics: a token's row is written by one block only).
+__global__ void moe_combine_sorted_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ route, const int* __restrict__ pos,
+                                          const int* __restrict__ offsets, __nv_bfloat16* __restrict__ dst, int T, int H, int E, int e0, int nloc,
+                                          int ld_dst, int accumulate, int cap) {
+    pdl_enter();
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int hv = H >> 3;
+    for (int c = threadIdx.x; c < hv; c += blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4* d = reinterpret_cast<uint4*>(dst + (size_t)t * ld_dst) + c;
+        if (accumulate) {
+            Pack8 a;
+            a.u = *d;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __bfloat162float(a.b[j]);
+        }
+        for (int e = 0; e < nloc; ++e) {
+            const int p_ = pos[(size_t)t * nloc + e];
+            if (p_ < 0) continue;
+            const int r = offsets[e] + p_;
+            if (r >= cap) continue;
+            const float w = route[(size_t)t * E + e0 + e];
+            Pack8 v;
+            v.u = reinterpret_cast<const uint4*>(y + (size_t)r * H)[c];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += w * __bfloat162float(v.b[j]);
+        }
+        Pack8 o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.b[j] = __float2bfloat16_rn(acc[j]);
+        *d = o.u;
+    }
+}
+
 __global__ void moe_silu_mul_rows_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ route, const int* __restrict__ idx,
                                          __nv_bfloat16* __restrict__ out, int rows, int F, int E, int e) {
     pdl_enter();
@@ -692,11 +788,13 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
     return 0;
 }
 
-int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream_) {
+int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream_) { return ovb_silu_mul_counted(gu, out, rows, F, nullptr, stream_); }
+
+int ovb_silu_mul_counted(const void* gu, void* out, int rows, int F, const int* nrows, ovb_stream_t stream_) {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     OVB_REQUIRE(gu && out && rows > 0 && F % 8 == 0, "ovb_silu_mul: bad arguments");
     const size_t total = (size_t)rows * (F / 8);
-    OVB_CHECK_CUDA(launch_pdl(silu_mul_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F));
+    OVB_CHECK_CUDA(launch_pdl(silu_mul_kernel, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, F, nrows));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }
@@ -723,6 +821,29 @@ int ovb_moe_group(const float* route, int T, int E, int e0, int nloc, int* idx, 
     OVB_REQUIRE(route && idx && counts && T > 0 && nloc > 0 && e0 >= 0 && e0 + nloc <= E && idx_stride >= T, "ovb_moe_group: bad arguments");
     OVB_CHECK_CUDA(launch_pdl(moe_group_kernel, dim3(nloc), dim3(1024), 0, stream, route, T, E, e0, idx, counts, idx_stride));
     OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_moe_positions(const float* route, int T, int E, int e0, int nloc, int* pos, int* counts, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(route && pos && counts && T > 0 && nloc > 0 && nloc <= 64 && e0 >= 0 && e0 + nloc <= E, "ovb_moe_positions: bad arguments");
+    OVB_CHECK_CUDA(launch_pdl(moe_positions_kernel, dim3(nloc), dim3(1024), 0, stream, route, T, E, e0, nloc, pos, counts));
+    return 0;
+}
+
+int ovb_moe_gather_sorted(const void* x, const int* pos, const int* counts, int* offsets, void* xg, int T, int H, int nloc, int cap, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(x && pos && counts && offsets && xg && T > 0 && H % 8 == 0 && nloc > 0 && nloc <= 64 && cap > 0, "ovb_moe_gather_sorted: bad arguments");
+    OVB_CHECK_CUDA(launch_pdl(moe_gather_sorted_kernel, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)x, pos, counts, offsets, (__nv_bfloat16*)xg, T, H, nloc, cap));
+    return 0;
+}
+
+int ovb_moe_combine_sorted(const void* y, const float* route, const int* pos, const int* offsets, void* dst, int T, int H, int E, int e0, int nloc,
+                           int ld_dst, int accumulate, int cap, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(y && route && pos && offsets && dst && T > 0 && H % 8 == 0 && ld_dst % 8 == 0 && nloc > 0 && nloc <= 64, "ovb_moe_combine_sorted: bad arguments");
+    OVB_CHECK_CUDA(launch_pdl(moe_combine_sorted_kernel, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)y, route, pos, offsets, (__nv_bfloat16*)dst, T, H, E, e0,
+                              nloc, ld_dst, accumulate, cap));
     return 0;
 }
 

@@ -83,6 +83,12 @@ struct GemmKParams {
     // call site's barrier words, [tile][kNvlsFlagStride] int32, as an offset in the heap
     uint8_t* mc;
     long long nvls_flags_off;
+    // Grouped GEMM (mixture of experts): the rows of X / out are grouped, group g owns rows [group_off[g], group_off[g + 1])
+    // (device array, written by an earlier kernel of the stream) and uses weight g of a stack: group_mode 1 = the weights are
+    // stacked along N (tile index g * tiles_n + n_tile), 2 = stacked along K (k-block offset g * K / 64). T is the row capacity.
+    const int* group_off;
+    int num_groups;
+    int group_mode;
 };
 
 constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 us apart
@@ -222,7 +228,29 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // Tile order: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so the
     // CTAs that are resident together share a few weight tiles and a few token tiles in L2.
     int n_tile, t_tile;
-    {
+    int w_tile, w_kb0 = 0;          // weight tile and first k-block inside the (possibly stacked) weight
+    int t0, T_end = p.T;            // first row of the tile, one past the last valid row
+    if (p.group_off != nullptr) {
+        // the offsets come from an earlier kernel of the stream: nothing of this CTA may run before that kernel is done
+        pdl_wait();
+        const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
+        n_tile = blockIdx.x % tiles_n;
+        const int tt = blockIdx.x / tiles_n;
+        int g = 0, acc = 0, begin = 0, end = 0;
+        for (; g < p.num_groups; ++g) {
+            begin = __ldg(p.group_off + g);
+            end = __ldg(p.group_off + g + 1);
+            const int nt = (end - begin + BT - 1) / BT;
+            if (tt < acc + nt) break;
+            acc += nt;
+        }
+        if (g == p.num_groups) return;      // more CTAs than row tiles (the grid is sized for the worst case); uniform over the CTA
+        t_tile = tt - acc;
+        t0 = begin + t_tile * BT;
+        T_end = min(end, p.T);
+        w_tile = p.group_mode == 1 ? g * tiles_n + n_tile : n_tile;
+        w_kb0 = p.group_mode == 2 ? g * ((p.K + TILE_K - 1) / TILE_K) : 0;
+    } else {
         const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
         const int tiles_t = (p.T + BT - 1) / BT;
         const int band_sz = kBandN * tiles_t;
@@ -231,9 +259,10 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int in_band = min(kBandN, tiles_n - band * kBandN);
         t_tile = r / in_band;
         n_tile = band * kBandN + (r - t_tile * in_band);
+        w_tile = n_tile;
+        t0 = t_tile * BT;
     }
     const int n0 = n_tile * TILE_N;
-    const int t0 = t_tile * BT;
     const int split = p.splits > 1 ? (int)cluster_ctarank() : 0;   // the splits of a tile are one cluster along z
     const int total_kb = (p.K + TILE_K - 1) / TILE_K;
     const int kb_begin = split * p.kblocks_per_split;
@@ -277,7 +306,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 // running pointers only. The token tiles have a producer lane of their own in warp X_PRODUCER_WARP.)
                 int wslot = 0;
                 uint32_t wpar = 1;                    // parity to wait for on the "empty" barriers
-                const uint8_t* wsrc = p.w_tiled + ((size_t)n_tile * p.w_kb_stride + kb_begin) * (WMODE == OVB_W_U4 ? WQ_SLOT : WQ_BYTES);
+                const uint8_t* wsrc = p.w_tiled + ((size_t)w_tile * p.w_kb_stride + w_kb0 + kb_begin) * (WMODE == OVB_W_U4 ? WQ_SLOT : WQ_BYTES);
                 uint32_t wdst = smem_u32(pring);
                 // u8: pairs come from the [group][N] table with a second copy
                 const int kpg = p.group_size / TILE_K;
@@ -309,7 +338,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 auto load_w = [&](int s, int kb) {
                     uint8_t* st = smem + s * STAGE_BYTES;
                     if (p.w_tiled != nullptr)
-                        bulk_load_1d(st + X_BYTES, p.w_tiled + ((size_t)n_tile * p.w_kb_stride + kb) * W_BYTES, W_BYTES, &full_x[s]);
+                        bulk_load_1d(st + X_BYTES, p.w_tiled + ((size_t)w_tile * p.w_kb_stride + w_kb0 + kb) * W_BYTES, W_BYTES, &full_x[s]);
                     else
                         tma_load_2d(st + X_BYTES, &tmW, &full_x[s], kb * TILE_K, n0);
                 };
@@ -515,7 +544,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // ---- tensor-parallel: the fp32 partial tile in stage_out is summed over the ranks (see GemmKParams)
         const bool comm = p.world > 1;
         auto comm_epilogue = [&](bool tile_ok) {
-            const int ntok = min(BT, p.T - t0);
+            const int ntok = min(BT, T_end - t0);
             const int epoch = __ldcg(p.epoch);
             constexpr int PIECES = BT * (TILE_N / 8);               // 16-byte pieces of the bf16 tile
             constexpr size_t SLOT = (size_t)BT * TILE_N * 2;        // bytes of one bf16 tile
@@ -929,7 +958,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
         auto finish = [&](int col, float v) {
             const int tok = t0 + col;
-            if (tok < p.T && oc < p.N) {
+            if (tok < T_end && oc < p.N) {
                 v += bias_v;
                 v = apply_act(v, p.act);
                 if (p.residual) v += to_float(reinterpret_cast<const E*>(p.residual)[(size_t)tok * p.ldr + oc]);
@@ -980,7 +1009,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
             if (acc_ok) {
                 constexpr int PIECES = BT * (TILE_N / 16);    // 16-byte pieces of the 64 output channels
-                const int ntok = min(BT, p.T - t0);
+                const int ntok = min(BT, T_end - t0);
                 for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
                     const int col = i >> 3, pc = i & 7;
                     if (col < ntok) {
@@ -998,7 +1027,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
             if (acc_ok) {
                 constexpr int PIECES = BT * (TILE_N / 8);     // 16-byte pieces in the tile
-                const int ntok = min(BT, p.T - t0);
+                const int ntok = min(BT, T_end - t0);
                 for (int i = dq_tid; i < PIECES; i += DQ_THREADS) {
                     const int col = i >> 4, pc = i & 15;
                     if (col < ntok) {
@@ -1057,7 +1086,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     const int e = i4 * 4;
                     const int col = e / TILE_N, r4 = e % TILE_N;
                     const int tok = t0 + col, oc4 = n0 + r4;
-                    if (tok < p.T) {
+                    if (tok < T_end) {
                         float vv[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
@@ -1263,6 +1292,8 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     if (p.splits > kMaxSplits) p.splits = kMaxSplits;
     p.kblocks_per_split = ceil_div(total_kb, p.splits);
     cfg.gridDim = dim3(ceil_div(a->N, TILE_N) * ceil_div(a->T, BT), 1, p.splits);
+    if (p.group_off != nullptr)     // every group may end with a partial row tile: num_groups extra tiles cover the worst case
+        cfg.gridDim = dim3(ceil_div(a->N, TILE_N) * (ceil_div(a->T, BT) + p.num_groups), 1, 1);
     attr[0].val.clusterDim.z = p.splits;
     // programmatic dependent launch: set-up, tensor-memory allocation and the first weight fetches run under the tail of
     // the kernel before this one (the kernel waits before it reads activations or writes anything)
@@ -1314,9 +1345,13 @@ static int comm_twohop(int world) {
     static const int env = env_int("OVB_COMM_TWOHOP", -1);
     return env >= 0 ? env : (world > 2);
 }
-static int comm_nvls_modes() {
-    static const int env = env_int("OVB_COMM_NVLS_MODES", 0);
-    return env;
+// Bit (mode - 1) set: the all-reduce of that mode runs inside the switch (multimem.ld_reduce / multimem.st) when the heap has a
+// multicast mapping. Measured (T=8192, N=4096, per-rank K=512/1792): with 8 ranks in-switch takes 378/423 us against 475/531 us
+// for the two-shot packets and 425/474 us for GEMM then NCCL; with 2 ranks the packets win (362/533 us against 499/683 us).
+// At T=64 the two-hop packets (28.7/31.7 us with 8 ranks) beat in-switch (37.8/43.0 us) at every world size.
+static int comm_nvls_modes(int world) {
+    static const int env = env_int("OVB_COMM_NVLS_MODES", -1);
+    return env >= 0 ? env : (world >= 4 ? 2 : 0);
 }
 
 static int comm_packets(int world, int mode) {
@@ -1355,8 +1390,14 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
                     "ovb_gemm: the SWIGLU epilogue needs a 16-byte aligned output with a row pitch that is a multiple of 8");
     }
 
+    const bool grouped = a->group_offsets != nullptr;
+    if (grouped) {
+        OVB_REQUIRE(a->num_groups >= 1 && a->num_groups <= 256 && (a->group_mode == 1 || a->group_mode == 2), "ovb_gemm: grouped GEMM needs 1..256 groups and group_mode 1 or 2");
+        OVB_REQUIRE((a->wmode == OVB_W_U4 || (a->w_tiled && !quant)) && a->comm == nullptr && a->N % TILE_N == 0 && a->K % TILE_K == 0,
+                    "ovb_gemm: grouped GEMM needs tile-packed weights (u4 or 16-bit), N %% 128 == 0, K %% 64 == 0 and no communicator");
+    }
     const int bt = a->block_t ? a->block_t : pick_block_t(a->T);
-    const int splits = swiglu ? 1 : a->splits;   // 0: chosen at launch, where the kernel variant and its cluster occupancy are known
+    const int splits = (swiglu || grouped) ? 1 : a->splits;   // 0: chosen at launch, where the kernel variant and its cluster occupancy are known
     const int64_t tiles = (int64_t)ceil_div(a->N, TILE_N) * ceil_div(a->T, bt);
 
     GemmKParams p;
@@ -1375,7 +1416,10 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.act = a->act;
     p.out_f32 = a->out_f32;
     p.splits = splits;
-    p.w_kb_stride = a->w_kb_stride > 0 ? a->w_kb_stride : ceil_div(a->K, TILE_K);
+    p.w_kb_stride = a->w_kb_stride > 0 ? a->w_kb_stride : ceil_div(a->K, TILE_K) * (grouped && a->group_mode == 2 ? a->num_groups : 1);
+    p.group_off = a->group_offsets;
+    p.num_groups = a->num_groups;
+    p.group_mode = a->group_mode;
     if (a->comm != nullptr && static_cast<const ovb_comm*>(a->comm)->world > 1) {
         const ovb_comm* c = static_cast<const ovb_comm*>(a->comm);
         OVB_REQUIRE(c->world <= 8 && c->rank >= 0 && c->rank < c->world, "ovb_gemm: bad communicator (rank %d of %d)", c->rank, c->world);
@@ -1418,7 +1462,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
         if (mode == 1 && comm_twohop(c->world) && (bt * 16) % c->world == 0 && 2 * tiles * bt * 16 * 32 <= c->stage1_bytes) {
             p.twohop = 1;
             p.mc = static_cast<uint8_t*>(c->mc_base);   // NULL: hop 2 stores to every rank in turn
-        } else if (c->mc_base != nullptr && ((comm_nvls_modes() >> (mode - 1)) & 1) && out_in_heap && (c->world == 2 || c->world == 4 || c->world == 8) &&
+        } else if (c->mc_base != nullptr && ((comm_nvls_modes(c->world) >> (mode - 1)) & 1) && out_in_heap && (c->world == 2 || c->world == 4 || c->world == 8) &&
             tiles * kNvlsFlagStride <= c->nvls_flags_per_site && tiles * slot <= (mode == 1 ? c->stage1_bytes : c->stage2_bytes)) {
             p.mc = static_cast<uint8_t*>(c->mc_base);
             p.nvls = 1;

@@ -69,6 +69,14 @@ typedef struct {
     // Window into a larger tile-contiguous weight (experts stacked along N or K): chunks of one 128-row weight tile are
     // w_kb_stride apart from the next tile's (0 = K / 64, the weight is exactly [N, K]); `w` points at the window's first chunk.
     int w_kb_stride;
+    // Grouped GEMM (mixture of experts, one launch for all experts of a rank). The rows of x / out are sorted by group: group
+    // g owns rows [group_offsets[g], group_offsets[g + 1]) (int32 device array of num_groups + 1 entries that an earlier
+    // kernel of the stream wrote; no host copy is needed) and multiplies them with weight g of a tile-packed stack:
+    // group_mode 1 = stacked along N (w is [num_groups * N, K]), 2 = stacked along K (w is [N, num_groups * K]); N and K
+    // describe ONE group's weight. T is the row capacity of x / out. NULL: ordinary GEMM.
+    const int* group_offsets;
+    int num_groups;
+    int group_mode;
 } ovb_gemm_args;
 
 int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream);
@@ -98,11 +106,21 @@ int ovb_layernorm(const void* x, const void* residual, const void* gamma, const 
                   int cols, float eps, int is_f16, ovb_stream_t stream);
 // out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
 int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
+/* The same over the first min(*nrows, rows) rows; nrows is device memory written by an earlier kernel of the stream. */
+int ovb_silu_mul_counted(const void* gu, void* out, int rows, int F, const int* nrows, ovb_stream_t stream);
 /* MoE prefill: token lists per local expert (idx[e * idx_stride + i], counts[e]) from the dense routing matrix route [T, E];
    SwiGLU of an expert's gathered rows scaled by the routing weight; dst[idx[i]] += src[i]. */
 int ovb_moe_group(const float* route, int T, int E, int e0, int nloc, int* idx, int idx_stride, int* counts, ovb_stream_t stream);
 int ovb_moe_silu_mul_rows(const void* gu, const float* route, const int* idx, void* out, int rows, int F, int E, int e, ovb_stream_t stream);
 int ovb_moe_scatter_add(const void* src, const int* idx, void* dst, int rows, int H, int ld_dst, ovb_stream_t stream);
+/* Single-launch expert path (no host round trip). ovb_moe_positions: pos[t * nloc + e] = position of token t in local expert
+   e's row list or -1, counts[e] rows. ovb_moe_gather_sorted: offsets[nloc + 1] = row offsets of the experts in the sorted
+   buffer (capped at cap rows) and xg[offsets[e] + pos] = x[t]. ovb_moe_combine_sorted: dst[t] (+)= sum over the local
+   experts, in index order, of route[t, e0 + e] * y[offsets[e] + pos[t, e]]. The grouped ovb_gemm runs in between. */
+int ovb_moe_positions(const float* route, int T, int E, int e0, int nloc, int* pos, int* counts, ovb_stream_t stream);
+int ovb_moe_gather_sorted(const void* x, const int* pos, const int* counts, int* offsets, void* xg, int T, int H, int nloc, int cap, ovb_stream_t stream);
+int ovb_moe_combine_sorted(const void* y, const float* route, const int* pos, const int* offsets, void* dst, int T, int H, int E, int e0, int nloc,
+                           int ld_dst, int accumulate, int cap, ovb_stream_t stream);
 /* bf16 [rows, cols] -> fp8 e4m3 bytes with one fp32 scale per row and group of 128 channels (scales [rows, cols/128]). */
 int ovb_act_quant_fp8(const void* x, void* q, float* scales, int rows, int cols, ovb_stream_t stream);
 /* Copy cache blocks src_blocks[i] -> dst_blocks[i] in the key and the value cache (block_bytes per block and cache). */

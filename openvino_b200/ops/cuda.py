@@ -36,6 +36,7 @@ class GemmArgs(C.Structure):
         ("group_size", C.c_int), ("wmode", C.c_int), ("act", C.c_int), ("out_f32", C.c_int),
         ("splits", C.c_int), ("block_t", C.c_int), ("w_tiled", C.c_int),
         ("comm", C.c_void_p), ("w_kb_stride", C.c_int),
+        ("group_offsets", C.c_void_p), ("num_groups", C.c_int), ("group_mode", C.c_int),
     ]
 
 
@@ -275,14 +276,23 @@ def layernorm(x, gamma, beta, eps, residual=None, out=None):
     return out
 
 
-def silu_mul(gu, out=None):
+def silu_mul(gu, out=None, nrows: Optional[torch.Tensor] = None):
+    """silu(gate) * up over [rows, 2F] -> [rows, F]; ``nrows`` (int32 device tensor) limits the rows without a host read."""
     rows, F2 = gu.shape
     F = F2 // 2
     if out is None:
         out = torch.empty((rows, F), dtype=gu.dtype, device=gu.device)
-    _check(lib().ovb_silu_mul(C.c_void_p(gu.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(rows), C.c_int(F),
-                              C.c_void_p(_stream())), "ovb_silu_mul")
+    _check(lib().ovb_silu_mul_counted(C.c_void_p(gu.data_ptr()), C.c_void_p(out.data_ptr()), C.c_int(rows), C.c_int(F),
+                                      C.c_void_p(nrows.data_ptr() if nrows is not None else None), C.c_void_p(_stream())), "ovb_silu_mul")
     return out
+
+
+def pick_block_t(T: int) -> int:
+    """Row-tile height the GEMM picks for T rows (16 .. 256)."""
+    for bt in (16, 32, 64, 128):
+        if T <= bt:
+            return bt
+    return 256
 
 
 def act_quant_fp8(x: torch.Tensor):
@@ -407,6 +417,60 @@ def moe_group(route: torch.Tensor, e0: int, nloc: int, idx: torch.Tensor, counts
     T, E = route.shape
     _check(lib().ovb_moe_group(C.c_void_p(route.data_ptr()), C.c_int(T), C.c_int(E), C.c_int(e0), C.c_int(nloc), C.c_void_p(idx.data_ptr()),
                                C.c_int(idx.stride(0)), C.c_void_p(counts.data_ptr()), C.c_void_p(_stream())), "ovb_moe_group")
+
+
+def moe_positions(route: torch.Tensor, e0: int, nloc: int, pos: torch.Tensor, counts: torch.Tensor) -> None:
+    """pos [T, nloc] int32: position of every token in the row list of each local expert (-1: not routed there); counts [nloc]."""
+    T, E = route.shape
+    _check(lib().ovb_moe_positions(C.c_void_p(route.data_ptr()), C.c_int(T), C.c_int(E), C.c_int(e0), C.c_int(nloc), C.c_void_p(pos.data_ptr()),
+                                   C.c_void_p(counts.data_ptr()), C.c_void_p(_stream())), "ovb_moe_positions")
+
+
+def moe_gather_sorted(x: torch.Tensor, pos: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, xg: torch.Tensor) -> None:
+    """Rows of ``x`` copied into ``xg`` sorted by expert; ``offsets`` [nloc + 1] receives the experts' row ranges."""
+    T, H = x.shape
+    _check(lib().ovb_moe_gather_sorted(C.c_void_p(x.data_ptr()), C.c_void_p(pos.data_ptr()), C.c_void_p(counts.data_ptr()), C.c_void_p(offsets.data_ptr()),
+                                       C.c_void_p(xg.data_ptr()), C.c_int(T), C.c_int(H), C.c_int(pos.shape[1]), C.c_int(xg.shape[0]),
+                                       C.c_void_p(_stream())), "ovb_moe_gather_sorted")
+
+
+def moe_combine_sorted(y: torch.Tensor, route: torch.Tensor, pos: torch.Tensor, offsets: torch.Tensor, dst: torch.Tensor, e0: int, accumulate: bool) -> None:
+    """dst[t] (+)= sum over local experts of route[t, e] * y[row of (t, e)] (expert order, deterministic)."""
+    T, E = route.shape
+    _check(lib().ovb_moe_combine_sorted(C.c_void_p(y.data_ptr()), C.c_void_p(route.data_ptr()), C.c_void_p(pos.data_ptr()), C.c_void_p(offsets.data_ptr()),
+                                        C.c_void_p(dst.data_ptr()), C.c_int(T), C.c_int(y.shape[1]), C.c_int(E), C.c_int(e0), C.c_int(pos.shape[1]),
+                                        C.c_int(dst.stride(0)), C.c_int(1 if accumulate else 0), C.c_int(y.shape[0]), C.c_void_p(_stream())),
+           "ovb_moe_combine_sorted")
+
+
+def gemm_grouped(x: torch.Tensor, w: PackedWeight, offsets: torch.Tensor, num_groups: int, mode: int, out: torch.Tensor, act: int = ACT_NONE,
+                 ws: Optional[Workspace] = None, block_t: int = 0) -> torch.Tensor:
+    """One launch for all groups (experts): rows [offsets[g], offsets[g + 1]) of ``x`` times weight g of the stack ``w``.
+    mode 1: ``w`` is [num_groups * N, K] (stacked along N); mode 2: ``w`` is [N, num_groups * K] (stacked along K).
+    ``offsets`` is an int32 device tensor written by an earlier kernel; nothing is read back to the host."""
+    assert x.dim() == 2 and x.stride(1) == 1 and offsets.dtype == torch.int32 and offsets.numel() >= num_groups + 1
+    cap, K = x.shape
+    N = w.N // num_groups if mode == 1 else w.N
+    assert (K == w.K if mode == 1 else K * num_groups == w.K), (K, w.K, mode)
+    if ws is None:
+        ws = default_workspace(x.device)
+    a = GemmArgs()
+    a.x, a.w, a.out = x.data_ptr(), w.w.data_ptr(), out.data_ptr()
+    a.bias = None
+    a.residual = None
+    a.scales, a.zps = _ptr(w.scales), _ptr(w.zps)
+    a.ws, a.counters, a.ws_bytes = ws.gemm_ws.data_ptr(), ws.counters.data_ptr(), ws.gemm_ws.numel() * 4
+    a.T, a.N, a.K = cap, N, K
+    a.ldx, a.ldo, a.ldr = x.stride(0), out.stride(0), 0
+    a.group_size = w.group_size
+    a.wmode, a.act, a.out_f32 = w.mode, act, 0
+    a.splits, a.block_t = 1, block_t
+    a.w_kb_stride = 0
+    a.w_tiled = 1 if (w.tiled and w.mode in (W_BF16, W_F16)) else 0
+    a.comm = None
+    a.group_offsets, a.num_groups, a.group_mode = offsets.data_ptr(), num_groups, mode
+    _check(lib().ovb_gemm(C.byref(a), C.c_void_p(_stream())), "ovb_gemm (grouped)")
+    return out
 
 
 def moe_silu_mul_rows(gu: torch.Tensor, route: torch.Tensor, idx: torch.Tensor, e: int, out: torch.Tensor) -> torch.Tensor:

