@@ -86,6 +86,7 @@ struct GemmKParams {
     // Grouped GEMM (mixture of experts): the rows of X / out are grouped, group g owns rows [group_off[g], group_off[g + 1])
     // (device array, written by an earlier kernel of the stream) and uses weight g of a stack: group_mode 1 = the weights are
     // stacked along N (tile index g * tiles_n + n_tile), 2 = stacked along K (k-block offset g * K / 64). T is the row capacity.
+    int nvls_lag;             // in-switch all-reduce: a CTA reduces the tile posted this many CTAs earlier (one wave of resident CTAs)
     const int* group_off;
     int num_groups;
     int group_mode;
@@ -169,6 +170,19 @@ __device__ __forceinline__ void dequant_f8x4(uint32_t w, __nv_bfloat162 ss, uint
     hi = *reinterpret_cast<uint32_t*>(&v1);
 }
 
+// Tile order of the (non-grouped) kernel: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so
+// the CTAs that are resident together share a few weight tiles and a few token tiles in L2.
+__device__ __forceinline__ void tile_coords(int idx, int N, int T, int bt, int& n_tile, int& t_tile) {
+    const int tiles_n = (N + TILE_N - 1) / TILE_N;
+    const int tiles_t = (T + bt - 1) / bt;
+    const int band_sz = kBandN * tiles_t;
+    const int band = idx / band_sz;
+    const int r = idx - band * band_sz;
+    const int in_band = min(kBandN, tiles_n - band * kBandN);
+    t_tile = r / in_band;
+    n_tile = band * kBandN + (r - t_tile * in_band);
+}
+
 // Quantised stages cover two k-blocks (128 elements of K) except for 256-token tiles, whose token tile alone is 32 KB
 // per k-block: every barrier round trip between the producers, the dequant warps and the MMA issuer then moves twice
 // the data, which halves the per-byte cost of the control chain.
@@ -225,8 +239,6 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // Tile order: bands of kBandN weight tiles; inside a band the token tiles advance slowest, so the
-    // CTAs that are resident together share a few weight tiles and a few token tiles in L2.
     int n_tile, t_tile;
     int w_tile, w_kb0 = 0;          // weight tile and first k-block inside the (possibly stacked) weight
     int t0, T_end = p.T;            // first row of the tile, one past the last valid row
@@ -251,14 +263,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         w_tile = p.group_mode == 1 ? g * tiles_n + n_tile : n_tile;
         w_kb0 = p.group_mode == 2 ? g * ((p.K + TILE_K - 1) / TILE_K) : 0;
     } else {
-        const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
-        const int tiles_t = (p.T + BT - 1) / BT;
-        const int band_sz = kBandN * tiles_t;
-        const int band = blockIdx.x / band_sz;
-        const int r = blockIdx.x - band * band_sz;
-        const int in_band = min(kBandN, tiles_n - band * kBandN);
-        t_tile = r / in_band;
-        n_tile = band * kBandN + (r - t_tile * in_band);
+        tile_coords(blockIdx.x, p.N, p.T, BT, n_tile, t_tile);
         w_tile = n_tile;
         t0 = t_tile * BT;
     }
@@ -584,37 +589,80 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     *reinterpret_cast<uint4*>(my_heap + slot_off + (size_t)i * 16) =
                         make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
                 }
-                // (no fence here: the CTA barrier orders these stores before thread 0's release fence inside nvls_barrier)
+                // Post: tell every rank that this rank's partial of the tile is in place (release: CTA barrier, then fence + flag).
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride;
-                int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride;
-                if (dq_tid == 0 && !nvls_barrier(bar_local, bar_mc, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) {
-                    report_status(p.status, STATUS_PEER_TIMEOUT);
-                    *abort_flag = 1;
+                if (dq_tid == 0) {
+                    fence_sys();
+                    multimem_st_u32(reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride + p.rank, (uint32_t)epoch);
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (*abort_flag) return;
+                // Reduce, deferred: waiting here for the other ranks' copies of THIS tile would hold the SM idle for a trip
+                // through the switch per tile. Instead the CTA reduces this rank's share of the tile that was posted
+                // `nvls_lag` CTAs earlier (one wave of resident CTAs: its partials have long arrived), and only the CTAs of the
+                // last wave also wait for their own tile. Rank r fetches the sum over all ranks of its 1/W share of a tile with
+                // multimem.ld_reduce and writes it to `out` on every rank with multimem.st: each piece is reduced exactly
+                // once, so all ranks hold the same bits. Traffic per rank and tile: one tile out (pulled by the switch), one in.
                 const int per = PIECES / W;                             // PIECES is a multiple of 256, W of 2, 4 or 8
-                // all reducing loads of a thread are in flight together, then the stores (a load is a round trip to the switch)
                 constexpr int MAXP = (PIECES / 2 + DQ_THREADS - 1) / DQ_THREADS;
-                uint4 v[MAXP];
+                const int lag = p.nvls_lag;
+#pragma unroll 1
+                for (int pass = 0; pass < 2; ++pass) {
+                    const int rt = pass == 0 ? tile_id - lag : tile_id;                 // tile to reduce in this pass
+                    if (rt < 0 || (pass == 1 && tile_id + lag < tiles)) continue;       // pass 1: a later CTA takes this tile
+                    const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + (size_t)rt * kNvlsFlagStride;
+                    if (dq_tid == 0) {
+                        bool ok = false;
+                        for (uint32_t it = 0; it < kPeerSpinLimit && !ok; ++it) {
+                            const uint4 a = ld_relaxed_sys_v4(bar_local), b = ld_relaxed_sys_v4(bar_local + 4);
+                            const int w[8] = {(int)a.x, (int)a.y, (int)a.z, (int)a.w, (int)b.x, (int)b.y, (int)b.z, (int)b.w};
+                            ok = true;
 #pragma unroll
-                for (int j = 0; j < MAXP; ++j) {
-                    const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
-                    if (k < per && (i >> 4) < ntok) v[j] = multimem_ld_reduce_bf16x8(p.mc + slot_off + (size_t)i * 16);
-                }
+                            for (int r = 0; r < 8; ++r) ok = ok && (r >= W || w[r] >= epoch);
+                            if (!ok) {
+                                if ((it & 255u) == 255u && *abort_flag) break;
+                                if (it > 32) __nanosleep(100);
+                            }
+                        }
+                        if (ok) {
+                            fence_sys();
+                        } else {
+                            report_status(p.status, STATUS_PEER_TIMEOUT);
+                            *abort_flag = 1;
+                        }
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                    if (*abort_flag) return;
+                    int rn, rtt;
+                    tile_coords(rt, p.N, p.T, BT, rn, rtt);
+                    const int r_t0 = rtt * BT, r_n0 = rn * TILE_N, r_ntok = min(BT, p.T - r_t0);
+                    const size_t r_slot = (size_t)p.stage_off + (size_t)rt * SLOT;
+                    // all reducing loads of a thread are in flight together, then the stores (a load is a round trip to the switch)
+                    uint4 v[MAXP];
 #pragma unroll
-                for (int j = 0; j < MAXP; ++j) {
-                    const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
-                    const int col = i >> 4, pc = i & 15;
-                    if (k < per && col < ntok) multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(t0 + col) * p.ldo + n0 + pc * 8) * 2, v[j]);
+                    for (int j = 0; j < MAXP; ++j) {
+                        const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
+                        if (k < per && (i >> 4) < r_ntok) v[j] = multimem_ld_reduce_bf16x8(p.mc + r_slot + (size_t)i * 16);
+                    }
+#pragma unroll
+                    for (int j = 0; j < MAXP; ++j) {
+                        const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
+                        const int col = i >> 4, pc = i & 15;
+                        if (k < per && col < r_ntok) multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(r_t0 + col) * p.ldo + r_n0 + pc * 8) * 2, v[j]);
+                    }
                 }
+                // Completion: the last CTA of this rank to get here meets the other ranks' last CTAs (words 8..15 of tile 0's
+                // flags), so when the kernel ends on a rank every share of every tile has landed in its `out`, and every
+                // rank is done reading the staging slots.
+                fence_sys();
                 asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                if (dq_tid == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) {
-                    report_status(p.status, STATUS_PEER_TIMEOUT);
-                    *abort_flag = 1;
+                if (dq_tid == 0) {
+                    const int done = atomicAdd(p.counters, 1);
+                    if (done == tiles - 1) {
+                        *p.counters = 0;
+                        const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + 8;
+                        int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + 8;
+                        if (!nvls_barrier(bar_local, bar_mc, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) report_status(p.status, STATUS_PEER_TIMEOUT);
+                    }
                 }
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
                 return;
             }
             auto flags_of = [&](int r) { return reinterpret_cast<int*>(p.heap[r] + p.flags_off) + (size_t)tile_id * (W + 1); };
@@ -1286,6 +1334,7 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
             resident[0] = 0;
         }
     }
+    p.nvls_lag = resident[1];
     if (p.splits == 0) p.splits = pick_splits(a->T, a->N, a->K, BT, WMODE, resident);
     const int total_kb = ceil_div(a->K, TILE_K);
     if (p.splits > total_kb) p.splits = total_kb;

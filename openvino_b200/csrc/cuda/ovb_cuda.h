@@ -121,6 +121,37 @@ int ovb_moe_positions(const float* route, int T, int E, int e0, int nloc, int* p
 int ovb_moe_gather_sorted(const void* x, const int* pos, const int* counts, int* offsets, void* xg, int T, int H, int nloc, int cap, ovb_stream_t stream);
 int ovb_moe_combine_sorted(const void* y, const float* route, const int* pos, const int* offsets, void* dst, int T, int H, int E, int e0, int nloc,
                            int ld_dst, int accumulate, int cap, ovb_stream_t stream);
+/* ---- generic primitives of the graph executor (fp32 / fp16 / bf16 storage, fp32 arithmetic) ---- */
+enum { OVB_DT_F32 = 0, OVB_DT_F16 = 1, OVB_DT_BF16 = 2 };
+enum {
+    OVB_UN_RELU = 0, OVB_UN_SIGMOID, OVB_UN_TANH, OVB_UN_GELU_ERF, OVB_UN_GELU_TANH, OVB_UN_SWISH /* a = beta */, OVB_UN_EXP, OVB_UN_LOG,
+    OVB_UN_SQRT, OVB_UN_ABS, OVB_UN_NEG, OVB_UN_HSWISH, OVB_UN_HSIGMOID, OVB_UN_MISH, OVB_UN_SOFTPLUS, OVB_UN_ERF, OVB_UN_FLOOR, OVB_UN_CEIL,
+    OVB_UN_SIGN, OVB_UN_CLAMP /* a = min, b = max */, OVB_UN_ELU /* a = alpha */, OVB_UN_SIN, OVB_UN_COS, OVB_UN_RSQRT, OVB_UN_SOFTSIGN,
+    OVB_UN_ROUND_EVEN, OVB_UN_ROUND_AWAY, OVB_UN_SCALE_SHIFT /* x * a + b */, OVB_UN_COUNT
+};
+enum { OVB_BIN_ADD = 0, OVB_BIN_SUB, OVB_BIN_MUL, OVB_BIN_DIV, OVB_BIN_MAX, OVB_BIN_MIN, OVB_BIN_POW, OVB_BIN_SQDIFF, OVB_BIN_PRELU, OVB_BIN_COUNT };
+enum { OVB_RED_SUM = 0, OVB_RED_MEAN, OVB_RED_MAX, OVB_RED_MIN, OVB_RED_PROD, OVB_RED_L2, OVB_RED_L1, OVB_RED_COUNT };
+#define OVB_MAX_DIMS 6
+int ovb_unary(int op, const void* x, void* y, int64_t n, int dtype, float a, float b, ovb_stream_t stream);
+/* y (contiguous, `shape`) = op(a, b); sa / sb are element strides of the operands (0 on a broadcast axis); same != 0: both
+   operands are contiguous and of the output's shape (16-byte vector path). */
+int ovb_binary(int op, const void* a, const void* b, void* y, int nd, const int64_t* shape, const int64_t* sa, const int64_t* sb, int same, int dtype,
+               ovb_stream_t stream);
+/* y[sum c_k * sy_k] = x[sum c_k * sx_k] over `shape`: transposes, slices, broadcasts, pieces of a concat. */
+int ovb_strided_copy(const void* x, void* y, int nd, const int64_t* shape, const int64_t* sx, const int64_t* sy, int elem_bytes, ovb_stream_t stream);
+/* [batch, R, C] -> [batch, C, R] through shared memory (2- and 4-byte elements). */
+int ovb_transpose2d(const void* x, void* y, int64_t batch, int R, int C, int elem_bytes, ovb_stream_t stream);
+/* softmax / log-softmax over the middle axis of [outer, dim, inner]. */
+int ovb_softmax(const void* x, void* y, int64_t outer, int dim, int64_t inner, int dtype, int log_out, ovb_stream_t stream);
+/* y[outer, inner] = reduction over the middle axis of x[outer, dim, inner]. */
+int ovb_reduce(int op, const void* x, void* y, int64_t outer, int dim, int64_t inner, int dtype, ovb_stream_t stream);
+typedef struct ovb_pool_args {
+    int64_t NC;               /* batch * channels */
+    int H, W, OH, OW, kh, kw, sh, sw, ph, pw, ph_end, pw_end, dh, dw;
+    int is_max, exclude_pad;
+} ovb_pool_args;
+int ovb_pool2d(const void* x, void* y, const ovb_pool_args* a, int dtype, ovb_stream_t stream);
+
 /* bf16 [rows, cols] -> fp8 e4m3 bytes with one fp32 scale per row and group of 128 channels (scales [rows, cols/128]). */
 int ovb_act_quant_fp8(const void* x, void* q, float* scales, int rows, int cols, ovb_stream_t stream);
 /* Copy cache blocks src_blocks[i] -> dst_blocks[i] in the key and the value cache (block_bytes per block and cache). */

@@ -29,6 +29,7 @@ from .. import properties as props
 from .._graph import Model, Node, Output
 from .._tensor import Tensor, torch_dtype
 from .._types import Type
+from ..ops import generic as G
 from .plugin_config import ConfigOption, OptionVisibility, PluginConfig
 from .core import CompiledModel, InferRequest, Plugin, ProfilingInfo, VariableState
 
@@ -85,12 +86,29 @@ def _same_device(ctx: Ctx, ins: Sequence[torch.Tensor]) -> List[torch.Tensor]:
     return [t if t.is_cuda else t.to(ctx.device, non_blocking=True) for t in ins]
 
 
-def _binary(fn, bool_out=False):
+def _native(*ts) -> bool:
+    """Floating-point device tensors go to the package's own generic kernels (ops/generic.py); integer / boolean tensors
+    and host-side values keep the torch expression."""
+    return G.enabled() and all(G.supported(t) for t in ts)
+
+
+_NATIVE_BINARY = {"Add": "add", "Subtract": "sub", "Multiply": "mul", "Maximum": "max", "Minimum": "min", "Power": "pow",
+                  "SquaredDifference": "sqdiff"}
+
+
+def _binary(fn, bool_out=False, name=None):
+    native = _NATIVE_BINARY.get(name)
+
     def impl(n, ins, ctx):
         a, b = _same_device(ctx, ins[:2])
         if a.dtype != b.dtype:
             dt = torch.promote_types(a.dtype, b.dtype)
             a, b = a.to(dt), b.to(dt)
+        if native and _native(a, b):
+            try:
+                return [G.binary(native, a, b)]
+            except NotImplementedError:
+                pass
         return [fn(a, b)]
     return impl
 
@@ -100,19 +118,35 @@ for _name, _fn in (("Add", torch.add), ("Subtract", torch.sub), ("Multiply", tor
                    ("Greater", torch.gt), ("GreaterEqual", torch.ge), ("LogicalAnd", torch.logical_and), ("LogicalOr", torch.logical_or),
                    ("LogicalXor", torch.logical_xor), ("FloorMod", torch.remainder), ("Mod", torch.fmod),
                    ("SquaredDifference", lambda a, b: (a - b) * (a - b))):
-    _OPS[_name] = _binary(_fn)
+    _OPS[_name] = _binary(_fn, name=_name)
 
 
 @op("Divide")
 def _divide(n, ins, ctx):
     a, b = _same_device(ctx, ins[:2])
     if a.dtype.is_floating_point:
+        if a.dtype == b.dtype and _native(a, b):
+            try:
+                return [G.binary("div", a, b)]
+            except NotImplementedError:
+                pass
         return [a / b]
     return [torch.div(a, b, rounding_mode="floor" if n.get_attribute("m_pythondiv") else "trunc")]
 
 
-def _unary(fn):
-    return lambda n, ins, ctx: [fn(ins[0])]
+_NATIVE_UNARY = {"Abs": "abs", "Negative": "neg", "Exp": "exp", "Log": "log", "Sqrt": "sqrt", "Relu": "relu", "Sigmoid": "sigmoid", "Tanh": "tanh",
+                 "Floor": "floor", "Ceiling": "ceil", "Sign": "sign", "Sin": "sin", "Cos": "cos", "Erf": "erf", "HSwish": "hswish",
+                 "HSigmoid": "hsigmoid", "Mish": "mish", "SoftPlus": "softplus", "SoftSign": "softsign"}
+
+
+def _unary(fn, name=None):
+    native = _NATIVE_UNARY.get(name)
+
+    def impl(n, ins, ctx):
+        if native and _native(ins[0]):
+            return [G.unary(native, ins[0])]
+        return [fn(ins[0])]
+    return impl
 
 
 for _name, _fn in (("Abs", torch.abs), ("Negative", torch.neg), ("Exp", torch.exp), ("Log", torch.log), ("Sqrt", torch.sqrt), ("Relu", torch.relu),
@@ -122,7 +156,7 @@ for _name, _fn in (("Abs", torch.abs), ("Negative", torch.neg), ("Exp", torch.ex
                    ("Acos", torch.acos), ("Atan", torch.atan), ("Sinh", torch.sinh), ("Cosh", torch.cosh), ("Asinh", torch.asinh),
                    ("Acosh", torch.acosh), ("Atanh", torch.atanh), ("IsNaN", torch.isnan), ("IsFinite", torch.isfinite),
                    ("SoftSign", F.softsign), ("BitwiseNot", torch.bitwise_not)):
-    _OPS[_name] = _unary(_fn)
+    _OPS[_name] = _unary(_fn, name=_name)
 
 
 @op("Parameter", "Constant")
@@ -150,8 +184,10 @@ def _convert_like(n, ins, ctx):
 
 @op("Swish")
 def _swish(n, ins, ctx):
+    b = _scalar(ins[1]) if len(ins) > 1 else 1.0
+    if _native(ins[0]):
+        return [G.unary("swish", ins[0], b)]
     if len(ins) > 1:
-        b = _scalar(ins[1])
         return [ins[0] * torch.sigmoid(ins[0] * b)]
     return [F.silu(ins[0])]
 
@@ -159,16 +195,22 @@ def _swish(n, ins, ctx):
 @op("Gelu")
 def _gelu(n, ins, ctx):
     mode = str(n.get_attributes().get("approximation_mode", "ERF")).lower()
+    if _native(ins[0]):
+        return [G.unary("gelu_tanh" if mode == "tanh" else "gelu_erf", ins[0])]
     return [F.gelu(ins[0], approximate="tanh" if mode == "tanh" else "none")]
 
 
 @op("Elu")
 def _elu(n, ins, ctx):
+    if _native(ins[0]):
+        return [G.unary("elu", ins[0], float(n.get_attribute("alpha")))]
     return [F.elu(ins[0], n.get_attribute("alpha"))]
 
 
 @op("Clamp")
 def _clamp(n, ins, ctx):
+    if _native(ins[0]):
+        return [G.unary("clamp", ins[0], float(n.get_attribute("min")), float(n.get_attribute("max")))]
     return [torch.clamp(ins[0], n.get_attribute("min"), n.get_attribute("max"))]
 
 
@@ -177,6 +219,11 @@ def _prelu(n, ins, ctx):
     x, s = _same_device(ctx, ins)
     if s.dim() == 1 and x.dim() > 1 and s.numel() == x.shape[1] and s.numel() > 1:
         s = s.reshape([1, -1] + [1] * (x.dim() - 2))
+    if x.dtype == s.dtype and _native(x, s):
+        try:
+            return [G.binary("prelu", x, s)]
+        except NotImplementedError:
+            pass
     return [torch.where(x >= 0, x, x * s)]
 
 
@@ -191,6 +238,8 @@ def _select(n, ins, ctx):
 
 @op("Round")
 def _round(n, ins, ctx):
+    if _native(ins[0]):
+        return [G.unary("round_even" if n.get_attribute("mode") == "half_to_even" else "round_away", ins[0])]
     if n.get_attribute("mode") == "half_to_even":
         return [torch.round(ins[0])]
     x = ins[0]
@@ -240,14 +289,26 @@ def _transpose(n, ins, ctx):
     order = _ints(ins[1])
     if not order:
         order = list(range(ins[0].dim() - 1, -1, -1))
-    return [ins[0].permute(order)]
+    v = ins[0].permute(order)
+    if _native(v):
+        try:
+            return [G.contiguous(v)]        # materialised by the tile-transpose / strided-copy kernels
+        except NotImplementedError:
+            pass
+    return [v]
 
 
 @op("Concat")
 def _concat(n, ins, ctx):
     ins = _same_device(ctx, ins)
     dt = ins[0].dtype
-    return [torch.cat([t.to(dt) for t in ins], dim=n.get_attribute("axis"))]
+    ts = [t.to(dt) for t in ins]
+    if ts[0].is_cuda and G.enabled() and ts[0].dim() > 0 and all(t.dim() == ts[0].dim() for t in ts):
+        try:
+            return [G.concat(ts, n.get_attribute("axis"))]
+        except NotImplementedError:
+            pass
+    return [torch.cat(ts, dim=n.get_attribute("axis"))]
 
 
 @op("Split")
@@ -503,13 +564,21 @@ def _topk(n, ins, ctx):
     return [v, i.to(torch_dtype(at["index_element_type"]))]
 
 
-def _reduce(fn):
+_NATIVE_REDUCE = {"ReduceSum": "sum", "ReduceMean": "mean", "ReduceMax": "max", "ReduceMin": "min", "ReduceProd": "prod", "ReduceL1": "l1",
+                  "ReduceL2": "l2"}
+
+
+def _reduce(fn, name=None):
+    native = _NATIVE_REDUCE.get(name)
+
     def impl(n, ins, ctx):
         axes = sorted({a % max(ins[0].dim(), 1) for a in _ints(ins[1])})
         keep = n.get_attribute("keep_dims")
         x = ins[0]
         if not axes:
             return [x]
+        if native and _native(x):
+            return [G.reduce(native, x, axes, bool(keep))]
         return [fn(x, axes, keep)]
     return impl
 
@@ -526,17 +595,21 @@ for _name, _fn in (("ReduceSum", lambda x, a, k: torch.sum(x, a, keepdim=k)), ("
                    ("ReduceL2", lambda x, a, k: torch.sqrt(torch.sum(x * x, a, keepdim=k))),
                    ("ReduceLogicalAnd", lambda x, a, k: torch.all(x, a[0], keepdim=k) if len(a) == 1 else torch.amin(x.to(torch.uint8), a, keepdim=k).bool()),
                    ("ReduceLogicalOr", lambda x, a, k: torch.any(x, a[0], keepdim=k) if len(a) == 1 else torch.amax(x.to(torch.uint8), a, keepdim=k).bool())):
-    _OPS[_name] = _reduce(_fn)
+    _OPS[_name] = _reduce(_fn, name=_name)
 
 
 # ---- neural network layers
 @op("Softmax")
 def _softmax(n, ins, ctx):
+    if _native(ins[0]) and ins[0].dim() > 0:
+        return [G.softmax(ins[0], n.get_attribute("axis"))]
     return [torch.softmax(ins[0], n.get_attribute("axis"))]
 
 
 @op("LogSoftmax")
 def _log_softmax(n, ins, ctx):
+    if _native(ins[0]) and ins[0].dim() > 0:
+        return [G.softmax(ins[0], n.get_attribute("axis"), log=True)]
     return [torch.log_softmax(ins[0], n.get_attribute("axis"))]
 
 
@@ -614,6 +687,19 @@ def _group_convolution(n, ins, ctx):
     return [_conv(x, w.reshape([g * w.shape[1]] + list(w.shape[2:])), n.get_attributes(), g)]
 
 
+def _pool_out_hw(x, kernel, strides, dil, pb, pe, ceil):
+    """Output extent of a pooling window walk: floor or ceil rounding; with ceil the last window must start inside the
+    input or its left padding (the rule of the reference's shape inference, src/core/shape_inference/include/pooling_shape_inference_util.hpp)."""
+    out = []
+    for i in range(2):
+        span = x.shape[2 + i] + pb[i] + pe[i] - (dil[i] * (kernel[i] - 1) + 1)
+        o = (-(-span // strides[i]) if ceil else span // strides[i]) + 1
+        if ceil and (o - 1) * strides[i] >= x.shape[2 + i] + pb[i]:
+            o -= 1
+        out.append(max(o, 0))
+    return out
+
+
 @op("MaxPool")
 def _max_pool(n, ins, ctx):
     x, at = ins[0], n.get_attributes()
@@ -621,6 +707,8 @@ def _max_pool(n, ins, ctx):
     dil = at.get("dilations") or [1] * nd
     pb, pe = _auto_pad(x, at["kernel"], at["strides"], dil, at["pads_begin"], at["pads_end"], at["auto_pad"])
     ceil = at["rounding_type"] == "ceil"
+    if nd == 2 and n.get_output_size() == 1 and _native(x):
+        return [G.pool2d(x, at["kernel"], at["strides"], pb, pe, dil, _pool_out_hw(x, at["kernel"], at["strides"], dil, pb, pe, ceil), True, False)]
     if list(pb) != list(pe):
         pads = []
         for b, e in zip(reversed(pb), reversed(pe)):
@@ -640,6 +728,9 @@ def _avg_pool(n, ins, ctx):
     nd = x.dim() - 2
     pb, pe = _auto_pad(x, at["kernel"], at["strides"], [1] * nd, at["pads_begin"], at["pads_end"], at["auto_pad"])
     ceil = at["rounding_type"] == "ceil"
+    if nd == 2 and _native(x):
+        return [G.pool2d(x, at["kernel"], at["strides"], pb, pe, [1, 1], _pool_out_hw(x, at["kernel"], at["strides"], [1, 1], pb, pe, ceil), False,
+                         bool(at["exclude-pad"]))]
     fn = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nd]
     if list(pb) != list(pe):
         raise NotImplementedError("AvgPool with asymmetric padding")
