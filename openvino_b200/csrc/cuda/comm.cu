@@ -95,7 +95,40 @@ __global__ void argmax_combine_kernel(CommK c, int* ids, const float* max_vals, 
 }
 
 // Small-tensor all-reduce (one-shot): CTA b owns pieces b, b + grid, ...; flags: one per (CTA, source rank).
-__global__ void allreduce_bf16_kernel(CommK c, long long data_off, long long npieces, long long rank_stride) {
+// DT: 0 = fp32 (4 values per 16-byte piece), 1 = fp16, 2 = bf16 (8 values); sums in fp32, ranks in index order.
+template <int DT>
+__device__ __forceinline__ void piece_add(float* f, const uint4& v) {
+    if (DT == OVB_DT_F32) {
+        f[0] += __uint_as_float(v.x); f[1] += __uint_as_float(v.y); f[2] += __uint_as_float(v.z); f[3] += __uint_as_float(v.w);
+    } else if (DT == OVB_DT_F16) {
+        const __half* e = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += __half2float(e[j]);
+    } else {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += __bfloat162float(e[j]);
+    }
+}
+template <int DT>
+__device__ __forceinline__ uint4 piece_pack(const float* f) {
+    uint4 o;
+    if (DT == OVB_DT_F32) {
+        o = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    } else if (DT == OVB_DT_F16) {
+        __half* oe = reinterpret_cast<__half*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) oe[j] = __float2half_rn(f[j]);
+    } else {
+        __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16_rn(f[j]);
+    }
+    return o;
+}
+
+template <int DT>
+__global__ void allreduce_kernel(CommK c, long long data_off, long long npieces, long long rank_stride) {
     pdl_enter();
     const int epoch = __ldcg(c.epoch);
     const int W = c.world;
@@ -122,15 +155,9 @@ __global__ void allreduce_bf16_kernel(CommK c, long long data_off, long long npi
         float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int r = 0; r < W; ++r) {
             const uint4 v = __ldcg(reinterpret_cast<const uint4*>(c.heap[c.rank] + c.stage_off + (size_t)r * rank_stride) + i);
-            const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] += __bfloat162float(e[j]);
+            piece_add<DT>(f, v);
         }
-        uint4 o;
-        __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&o);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) oe[j] = __float2bfloat16_rn(f[j]);
-        out[i] = o;
+        out[i] = piece_pack<DT>(f);
     }
 }
 
@@ -138,6 +165,7 @@ __global__ void allreduce_bf16_kernel(CommK c, long long data_off, long long npi
 // fetches the sum over the ranks of its 1/W share of the 16-byte pieces (multimem.ld_reduce, fp32 accumulation) and writes
 // it back to every rank (multimem.st), and a second barrier tells every rank that all shares have landed. No staging: a
 // piece is read and rewritten by its one owner only. CTA b uses barrier b of the call site.
+template <int DT>
 __global__ void allreduce_nvls_kernel(CommK c, long long data_off, long long npieces) {
     pdl_enter();
     const int epoch = __ldcg(c.epoch);
@@ -156,7 +184,8 @@ __global__ void allreduce_nvls_kernel(CommK c, long long data_off, long long npi
     const long long end = begin + per < npieces ? begin + per : npieces;
     uint8_t* base = c.mc + data_off;
     for (long long i = begin + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < end; i += (long long)gridDim.x * blockDim.x)
-        multimem_st_b128(base + i * 16, multimem_ld_reduce_bf16x8(base + i * 16));
+        multimem_st_b128(base + i * 16, DT == OVB_DT_F32 ? multimem_ld_reduce_f32x4(base + i * 16)
+                                                           : (DT == OVB_DT_F16 ? multimem_ld_reduce_f16x8(base + i * 16) : multimem_ld_reduce_bf16x8(base + i * 16)));
     fence_sys();
     __syncthreads();
     if (threadIdx.x == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, c.rank, W, epoch, kSpinLimit, nullptr)) report_status(c.status, STATUS_PEER_TIMEOUT);
@@ -247,29 +276,41 @@ int ovb_comm_argmax_combine(const ovb_comm* c, int* ids, const float* max_vals, 
     return 0;
 }
 
-int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream_t stream) {
-    OVB_REQUIRE(data != nullptr && n > 0 && n % 8 == 0, "ovb_comm_allreduce_bf16: n must be a positive multiple of 8");
+int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream_t stream) { return ovb_comm_allreduce(c, data, n, OVB_DT_BF16, stream); }
+
+#define OVB_COMM_DISPATCH(dtype, CALL)                          \
+    switch (dtype) {                                            \
+        case OVB_DT_F32: { constexpr int DT = OVB_DT_F32; CALL; break; }   \
+        case OVB_DT_F16: { constexpr int DT = OVB_DT_F16; CALL; break; }   \
+        default: { constexpr int DT = OVB_DT_BF16; CALL; break; }          \
+    }
+
+int ovb_comm_allreduce(const ovb_comm* c, void* data, int64_t n, int dtype, ovb_stream_t stream) {
+    OVB_REQUIRE(dtype == OVB_DT_F32 || dtype == OVB_DT_F16 || dtype == OVB_DT_BF16, "ovb_comm_allreduce: fp32, fp16 or bf16");
+    const int esz = dtype == OVB_DT_F32 ? 4 : 2, per_piece = 16 / esz;
+    OVB_REQUIRE(data != nullptr && n > 0 && n % per_piece == 0, "ovb_comm_allreduce: the size must be a positive multiple of 16 bytes");
     CommK k;
     if (int rc = fill(c, &k, c ? c->site : 0)) return rc;
     const int64_t off = static_cast<uint8_t*>(data) - k.heap[c->rank];
-    OVB_REQUIRE(off >= 0 && off + n * 2 <= c->heap_bytes && off % 16 == 0, "ovb_comm_allreduce_bf16: the tensor must live in the symmetric heap, 16-byte aligned");
+    OVB_REQUIRE(off >= 0 && off + n * esz <= c->heap_bytes && off % 16 == 0, "ovb_comm_allreduce: the tensor must live in the symmetric heap, 16-byte aligned");
+    const int64_t npieces = n / per_piece;
     if (k.mc != nullptr && (c->world == 2 || c->world == 4 || c->world == 8)) {
-        const int64_t npieces = n / 8;
         int grid = (int)((npieces / c->world + 255) / 256);
         if (grid < 1) grid = 1;
         if (grid > 148) grid = 148;
         if ((int64_t)grid * kNvlsFlagStride > c->nvls_flags_per_site) grid = (int)(c->nvls_flags_per_site / kNvlsFlagStride);
-        OVB_REQUIRE(grid >= 1, "ovb_comm_allreduce_bf16: no barrier words for the call site");
-        OVB_CHECK_CUDA(launch_pdl(allreduce_nvls_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), k, (long long)off, (long long)npieces));
+        OVB_REQUIRE(grid >= 1, "ovb_comm_allreduce: no barrier words for the call site");
+        OVB_COMM_DISPATCH(dtype, OVB_CHECK_CUDA(launch_pdl(allreduce_nvls_kernel<DT>, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), k, (long long)off,
+                                                           (long long)npieces)));
         return 0;
     }
     const int64_t rank_stride = ((c->stage3_bytes > 0 ? c->stage3_bytes : c->stage1_bytes) / c->world) & ~int64_t(15);
-    OVB_REQUIRE(n * 2 <= rank_stride, "ovb_comm_allreduce_bf16: %lld bytes exceed the staging share of a rank (%lld)", (long long)(n * 2), (long long)rank_stride);
-    const int64_t npieces = n / 8;
+    OVB_REQUIRE(n * esz <= rank_stride, "ovb_comm_allreduce: %lld bytes exceed the staging share of a rank (%lld)", (long long)(n * esz), (long long)rank_stride);
     int grid = (int)((npieces + 255) / 256);
     if (grid > 148) grid = 148;
-    OVB_REQUIRE((int64_t)grid * c->world <= c->flags_per_site, "ovb_comm_allreduce_bf16: flag area of a site is too small");
-    OVB_CHECK_CUDA(launch_pdl(allreduce_bf16_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), k, off, npieces, rank_stride));
+    OVB_REQUIRE((int64_t)grid * c->world <= c->flags_per_site, "ovb_comm_allreduce: flag area of a site is too small");
+    OVB_COMM_DISPATCH(dtype, OVB_CHECK_CUDA(launch_pdl(allreduce_kernel<DT>, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), k, (long long)off,
+                                                       (long long)npieces, (long long)rank_stride)));
     OVB_CHECK_CUDA(cudaGetLastError());
     return 0;
 }

@@ -652,9 +652,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 // Completion: the last CTA of this rank to get here meets the other ranks' last CTAs (words 8..15 of tile 0's
                 // flags), so when the kernel ends on a rank every share of every tile has landed in its `out`, and every
                 // rank is done reading the staging slots.
-                fence_sys();
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
+                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));     // orders the CTA's stores before thread 0's release fence
                 if (dq_tid == 0) {
+                    fence_sys();
                     const int done = atomicAdd(p.counters, 1);
                     if (done == tiles - 1) {
                         *p.counters = 0;

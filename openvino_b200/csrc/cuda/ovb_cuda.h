@@ -274,6 +274,8 @@ int ovb_comm_wait_flag(const int* flag, int value, unsigned max_polls, int* resu
 int ovb_comm_argmax_combine(const ovb_comm* c, int* ids, const float* max_vals, int rows, int shard_size, ovb_stream_t stream);
 // In-place sum of a bf16 tensor of n elements that lives at the same heap offset on every rank (n % 8 == 0).
 int ovb_comm_allreduce_bf16(const ovb_comm* c, void* data, int64_t n, ovb_stream_t stream);
+/* The same for fp32 / fp16 / bf16 tensors (dtype: OVB_DT_*); n elements, a multiple of 16 bytes. */
+int ovb_comm_allreduce(const ovb_comm* c, void* data, int64_t n, int dtype, ovb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -382,6 +382,18 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
     return v;
 }
+// The same for eight fp16 values and for four fp32 values.
+__device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc) {
+    float a, b, c, d;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "l"(mc) : "memory");
+    return make_uint4(__float_as_uint(a), __float_as_uint(b), __float_as_uint(c), __float_as_uint(d));
+}
 // 16 bytes to the same offset of every rank's heap.
 __device__ __forceinline__ void multimem_st_b128(void* mc, uint4 v) {
     asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");

@@ -83,7 +83,7 @@ class PyTorchFrontEnd(FrontEnd):
             import torch
         except ImportError:
             return False
-        return isinstance(model, torch.nn.Module) or (hasattr(model, "graph_signature") and hasattr(model, "graph"))
+        return isinstance(model, (torch.nn.Module, torch.jit.ScriptFunction)) or (hasattr(model, "graph_signature") and hasattr(model, "graph"))
 
     def convert(self, input_model) -> Model:
         from . import pytorch

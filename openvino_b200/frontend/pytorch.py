@@ -1021,6 +1021,68 @@ def from_exported_program(ep, share_weights: bool = True, input_names: Optional[
     raise ConversionError("the exported graph has no output node")
 
 
+def from_fx(gm, example_inputs: Sequence[Any], share_weights: bool = True) -> Model:
+    """A ``torch.fx.GraphModule`` whose call_function nodes are aten operators (what ``make_fx`` and the partitioner of the
+    ``torch.compile`` backend produce) -> ``Model``. Placeholders become Parameters shaped like ``example_inputs``
+    (fake or real tensors; python scalars are inlined), ``get_attr`` tensors become Constants."""
+    import torch
+    ctx = Ctx()
+    params: List[Node] = []
+    idx = 0
+    for node in gm.graph.nodes:
+        if node.op == "placeholder":
+            ex = example_inputs[idx] if idx < len(example_inputs) else node.meta.get("val")
+            idx += 1
+            if isinstance(ex, (int, float, bool)):
+                ctx.values[node] = ex
+                continue
+            if ex is None or not hasattr(ex, "shape"):
+                raise ConversionError("input %s is not a tensor" % node.name)
+            dims = [int(d) if isinstance(d, int) else -1 for d in ex.shape]
+            p = parameter(PartialShape(dims), _ov_type(ex.dtype), node.name)
+            p.output(0).set_names({node.name})
+            params.append(p)
+            ctx.values[node] = p.output(0)
+        elif node.op == "get_attr":
+            t = gm
+            for part in str(node.target).split("."):
+                t = getattr(t, part)
+            ctx.values[node] = constant(Tensor(t.detach().contiguous(), shared_memory=share_weights), name=str(node.target), shared_memory=share_weights).output(0)
+        elif node.op == "call_function":
+            name = _target_name(node.target)
+            plain_args = [ctx.get(a) for a in node.args] if name in ("add", "sub", "mul", "truediv", "floordiv", "mod", "eq", "ne", "lt", "le", "gt", "ge") else None
+            if plain_args is not None and all(isinstance(a, (int, float, bool)) for a in plain_args):
+                ctx.values[node] = _python_scalar_op(name, plain_args)
+                continue
+            fn = _TABLE.get(name)
+            if fn is None:
+                raise ConversionError("no translator for %s (node %s)" % (name, node.name))
+            out = fn(ctx, node)
+            if isinstance(out, Node):
+                out = out.output(0)
+            ctx.values[node] = out
+        elif node.op == "output":
+            flat = []
+
+            def walk(a):
+                if isinstance(a, (list, tuple)):
+                    for x in a:
+                        walk(x)
+                elif a is not None:
+                    flat.append(a)
+            walk(node.args[0])
+            results = []
+            for i, a in enumerate(flat):
+                o = ctx.out(a)
+                if not o.get_names():
+                    o.set_names({"output_%d" % i})
+                results.append(result(o))
+            return Model(results, params, "Model")
+        else:
+            raise ConversionError("fx node kind %s is not supported" % node.op)
+    raise ConversionError("the fx graph has no output node")
+
+
 def convert(module, example_input=None, input=None, dynamic_shapes=None, share_weights: bool = True, strict: bool = False) -> Model:
     """``torch.nn.Module`` (or ``ExportedProgram``) -> ``Model``.
 
@@ -1030,8 +1092,12 @@ def convert(module, example_input=None, input=None, dynamic_shapes=None, share_w
     import torch
     if hasattr(module, "graph_signature") and hasattr(module, "graph"):
         return from_exported_program(module, share_weights)
+    if isinstance(module, (torch.jit.ScriptModule, torch.jit.ScriptFunction)):
+        # traced / scripted models keep their TorchScript graph: decoded by the TorchScript front end
+        from .torchscript import from_script
+        return from_script(module, example_input=example_input, input=input, share_weights=share_weights)
     if not isinstance(module, torch.nn.Module):
-        raise ConversionError("expected a torch.nn.Module or an ExportedProgram, got %r" % type(module))
+        raise ConversionError("expected a torch.nn.Module, a ScriptModule or an ExportedProgram, got %r" % type(module))
     if example_input is None:
         if input is None:
             raise ConversionError("convert_model of a torch module needs example_input (or static input shapes)")

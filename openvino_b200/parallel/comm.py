@@ -81,6 +81,7 @@ class PeerCommunicator:
         self._bump = 0
         self._structs = {}
         self._keep = []
+        self._any_bufs = {}
         self.mc_ptr = 0           # multicast mapping of the heap (NVLS), 0 = none
         self._symm = None
 
@@ -166,6 +167,7 @@ class PeerCommunicator:
         lib.ovb_comm_step_begin.argtypes = [C.POINTER(CommStruct), C.c_void_p]
         lib.ovb_comm_argmax_combine.argtypes = [C.POINTER(CommStruct), C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         lib.ovb_comm_allreduce_bf16.argtypes = [C.POINTER(CommStruct), C.c_void_p, C.c_int64, C.c_void_p]
+        lib.ovb_comm_allreduce.argtypes = [C.POINTER(CommStruct), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
 
     def close(self) -> None:
         if not self._base:
@@ -231,34 +233,54 @@ class PeerCommunicator:
         K._check(K.lib().ovb_comm_argmax_combine(C.byref(self.struct(site)), C.c_void_p(ids.data_ptr()), C.c_void_p(max_vals.data_ptr()),
                                                  C.c_int(ids.numel()), C.c_int(shard_size), C.c_void_p(K._stream())), "ovb_comm_argmax_combine")
 
-    def all_reduce(self, t: torch.Tensor) -> None:
-        assert t.dtype == torch.bfloat16 and t.is_contiguous() and self.in_heap(t)
-        site = self.layout.num_sites - 1
-        K._check(K.lib().ovb_comm_allreduce_bf16(C.byref(self.struct(site)), C.c_void_p(t.data_ptr()), C.c_int64(t.numel()),
-                                                 C.c_void_p(K._stream())), "ovb_comm_allreduce_bf16")
+    _DTYPES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+    def all_reduce(self, t: torch.Tensor, site: Optional[int] = None) -> None:
+        """In-place sum over the ranks of a heap tensor (fp32, fp16 or bf16; a multiple of 16 bytes)."""
+        assert t.dtype in self._DTYPES and t.is_contiguous() and self.in_heap(t)
+        site = self.layout.num_sites - 1 if site is None else site
+        K._check(K.lib().ovb_comm_allreduce(C.byref(self.struct(site)), C.c_void_p(t.data_ptr()), C.c_int64(t.numel()), C.c_int(self._DTYPES[t.dtype]),
+                                            C.c_void_p(K._stream())), "ovb_comm_allreduce")
+
+    def all_reduce_any(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over the ranks of any device tensor (fp32 / fp16 / bf16): staged through a heap tensor that grows on demand
+        (every rank calls with the same sizes in the same order, so the heap offsets agree). Returns a new tensor."""
+        assert x.dtype in self._DTYPES
+        per = 16 // x.element_size()
+        n = x.numel()
+        padded = (n + per - 1) // per * per
+        key = x.dtype
+        buf = self._any_bufs.get(key)
+        if buf is None or buf.numel() < padded:
+            buf = self.alloc((max(padded, 1 << 20),), x.dtype)
+            self._any_bufs[key] = buf
+        stage = buf[:padded]
+        if padded != n:
+            stage[n:].zero_()
+        stage[:n].copy_(x.reshape(-1))
+        self.all_reduce_large(stage)
+        return stage[:n].clone().reshape(x.shape)
 
     def all_reduce_large(self, t: torch.Tensor) -> int:
         """Sum a heap tensor of any size over the ranks, in pieces that fit the one-shot staging area. Every piece gets
         a step number of its own (the flags of a call site hold step numbers) and the pieces alternate between two call
         sites, i.e. between the two staging buffers: a rank that runs ahead writes into the buffer its peers are not
         reading. A last bump keeps later users of the step number apart from these flags. Returns the launches made."""
-        assert t.dtype == torch.bfloat16 and t.is_contiguous() and self.in_heap(t)
+        assert t.dtype in self._DTYPES and t.is_contiguous() and self.in_heap(t)
         L = self.layout
         if self.mc_ptr:
             # in-switch reduction works in place on the heap tensor: no staging, so no pieces
             self.step_begin()
             self.all_reduce(t)
             return 2
-        max_elems = (((L.stage3_bytes // self.world) & ~15) // 2) & ~7
+        per = 16 // t.element_size()
+        max_elems = (((L.stage3_bytes // self.world) & ~15) // t.element_size()) & ~(per - 1)
         flat = t.view(-1)
         n, i, k = flat.numel(), 0, 0
-        lib = K.lib()
         while i < n:
             m = min(max_elems, n - i)
             self.step_begin()
-            site = L.num_sites - 1 - (k & 1)
-            K._check(lib.ovb_comm_allreduce_bf16(C.byref(self.struct(site)), C.c_void_p(flat[i:i + m].data_ptr()), C.c_int64(m),
-                                                 C.c_void_p(K._stream())), "ovb_comm_allreduce_bf16")
+            self.all_reduce(flat[i:i + m], site=L.num_sites - 1 - (k & 1))
             i += m
             k += 1
         self.step_begin()

@@ -938,10 +938,32 @@ def _layer_norm_fused(n, ins, ctx):
 @op("AllReduce")
 def _all_reduce(n, ins, ctx):
     x = ins[0]
-    if torch.distributed.is_available() and torch.distributed.is_initialized() and torch.distributed.get_world_size() > 1:
+    dist = torch.distributed
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        if ctx.on_gpu and x.is_cuda and x.dtype in (torch.float32, torch.float16, torch.bfloat16) and os.environ.get("OVB_GRAPH_TP_NCCL", "0") != "1":
+            # the package's own peer-memory all-reduce (in-switch reduction when the heap has a multicast mapping)
+            return [_graph_comm(ctx).all_reduce_any(x.contiguous())]
         x = x.contiguous().clone() if not ctx.on_gpu else x.contiguous()
-        torch.distributed.all_reduce(x)
+        dist.all_reduce(x)
     return [x]
+
+
+_GRAPH_COMMS: Dict[int, object] = {}
+
+
+def _graph_comm(ctx: Ctx):
+    """One peer-memory communicator per device for the AllReduce nodes of tensor-parallel graphs (created on first use by
+    all ranks together; sized by OVB_GRAPH_TP_HEAP_MB, 256 MB by default)."""
+    key = ctx.device.index or 0
+    c = _GRAPH_COMMS.get(key)
+    if c is None:
+        from ..parallel.comm import PeerCommunicator
+        dist = torch.distributed
+        mb = int(os.environ.get("OVB_GRAPH_TP_HEAP_MB", "256"))
+        c = PeerCommunicator(dist.get_rank(), dist.get_world_size(), ctx.device)
+        c.setup(hidden=1024, max_tokens=1024, num_layers=1, tensor_bytes=mb << 20)
+        _GRAPH_COMMS[key] = c
+    return c
 
 
 @op("Einsum")

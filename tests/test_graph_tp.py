@@ -15,3 +15,15 @@ def test_bert_shards_reproduce_the_full_model(world):
            "--master-port", str(29800 + world), os.path.join(HERE, "graph_tp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "GRAPH_TP_OK world=%d" % world in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])
+
+
+@pytest.mark.gpu
+def test_bert_shards_on_two_gpus_use_the_peer_memory_all_reduce():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="2", OVB_GRAPH_TP_DEVICE="CUDA")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29811", os.path.join(HERE, "graph_tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "GRAPH_TP_OK world=2" in r.stdout, (r.stdout[-2000:], r.stderr[-3000:])
