@@ -287,6 +287,16 @@ class HeteroCompiledModel(CompiledModel):
             return sorted({s.device for s in self.subs})
         return super().get_property(name)
 
+    def export_model(self, stream=None) -> bytes:
+        from .core import ModelBlob, __version__
+        xml, weights = _c.serialize(self.model._m)
+        header = {"device": self.plugin.device_name, "runtime": __version__, "affinity": dict(getattr(self, "affinity", {}) or {}),
+                  "config": {k: v for k, v in self.config.items() if isinstance(v, (str, int, float, bool))}}
+        data = ModelBlob(header, xml.decode(), weights).to_bytes()
+        if stream is not None:
+            stream.write(data)
+        return data
+
     def _make_runner(self, request):
         inner = [s.compiled.create_infer_request() for s in self.subs]
 
@@ -311,12 +321,83 @@ class HeteroPlugin(Plugin):
     description = "Heterogeneous execution across devices"
 
     def supported_properties(self):
-        return super().supported_properties() + [props.device.priorities, props.device.properties]
+        return super().supported_properties() + [props.device.priorities, props.device.properties, props.hint.model_distribution_policy]
+
+    def _device_memory(self, dev: str, cfg: dict) -> float:
+        """Memory a device offers to the pipeline split: its DEVICE_PROPERTIES entry "PIPELINE_MEMORY_BYTES" when given,
+        else what the device reports (GPU_DEVICE_TOTAL_MEM_SIZE), else an equal share."""
+        sub = (cfg.get(props.device.properties) or {}).get(dev.split(".")[0].split("(")[0], {})
+        if "PIPELINE_MEMORY_BYTES" in sub:
+            return float(sub["PIPELINE_MEMORY_BYTES"])
+        for key in ("GPU_DEVICE_TOTAL_MEM_SIZE", "DEVICE_TOTAL_MEM_SIZE"):
+            try:
+                v = self.core.get_property(dev, key)
+                if v:
+                    return float(v)
+            except Exception:   # noqa: BLE001 - the device has no such property
+                pass
+        return 1.0
+
+    def _assign_pipeline(self, model: Model, cfg: dict, devs: List[str], supported: Dict[str, set]) -> Dict[str, str]:
+        """``MODEL_DISTRIBUTION_POLICY = PIPELINE_PARALLEL``: the operations, in topological order, are cut into one
+        contiguous run per device so that every device receives a share of the constant (weight) bytes in proportion to
+        its memory; an operation that its device cannot run goes to the first device of the list that can. The activations
+        cross a device border once per cut (src/plugins/hetero/src/plugin.cpp, get_model_distribution_policy and the
+        memory-ratio walk of query_model_update)."""
+        mem = [self._device_memory(d, cfg) for d in devs]
+        if all(m == 1.0 for m in mem):
+            mem = [1.0] * len(devs)
+        ops_ = [n for n in model.get_ordered_ops() if n.get_type_name() not in ("Parameter", "Constant", "Result")]
+        weight = []
+        for n in ops_:
+            w = 0
+            for src in n.input_values():
+                p = src.get_node()
+                if p.get_type_name() == "Convert" and p.input_value(0).get_node().get_type_name() == "Constant":
+                    p = p.input_value(0).get_node()
+                if p.get_type_name() == "Constant":
+                    ps = src.get_partial_shape() if p is src.get_node() else p.output(0).get_partial_shape()
+                    cnt = 1
+                    for d in ps:
+                        cnt *= int(d.get_length())
+                    w += cnt * max(1, p.output(0).get_element_type().bitwidth) // 8
+            weight.append(max(w, 1))
+        total, acc, di = float(sum(weight)), 0.0, 0
+        bounds = []
+        run = 0.0
+        for m_ in mem:
+            run += m_ / sum(mem)
+            bounds.append(run * total)
+        affinity: Dict[str, str] = {}
+        for n, w in zip(ops_, weight):
+            while di < len(devs) - 1 and acc + w / 2.0 > bounds[di]:
+                di += 1
+            acc += w
+            name = n.get_friendly_name()
+            a = n.rt_info.get("affinity")
+            if a:
+                affinity[name] = str(a)
+            elif name in supported[devs[di]]:
+                affinity[name] = devs[di]
+            else:
+                for d in devs:
+                    if name in supported[d]:
+                        affinity[name] = d
+                        break
+        return affinity
 
     def _assign(self, model: Model, cfg: dict) -> Dict[str, str]:
         devs = _split_devices(cfg.get(props.device.priorities, ""))
         if not devs:
             raise RuntimeError("[HETERO] needs a device list: HETERO:CUDA,CPU")
+        if "PIPELINE_PARALLEL" in str(cfg.get(props.hint.model_distribution_policy, "") or ""):
+            supported = {}
+            for dev in devs:
+                try:
+                    supported[dev] = set(self.core.query_model(model, dev, _device_config(cfg, dev)))
+                except Exception:   # noqa: BLE001 - a device that cannot answer supports nothing
+                    supported[dev] = set()
+            return self._assign_pipeline(model, cfg, devs, supported)
         # a user-given per-node "affinity" rt_info wins over the automatic assignment
         affinity: Dict[str, str] = {}
         for n in model.get_ops():
@@ -335,14 +416,25 @@ class HeteroPlugin(Plugin):
     def query_model(self, model, config):
         return self._assign(model, self.merged_config(config))
 
-    def compile_model(self, model, config):
+    def compile_model(self, model, config, affinity: Optional[Dict[str, str]] = None):
         cfg = self.merged_config(config)
         work = model.clone()
-        affinity = self._assign(work, cfg)
+        affinity = dict(affinity) if affinity is not None else self._assign(work, cfg)
         subs = split_by_affinity(work, affinity)
         for s in subs:
             s.compiled = self.core.compile_model(s.model, s.device, _device_config(cfg, s.device))
-        return HeteroCompiledModel(self, model, cfg, subs, work)
+        cm = HeteroCompiledModel(self, model, cfg, subs, work)
+        cm.affinity = affinity
+        return cm
+
+    def import_model(self, blob, config):
+        """The exported blob carries the partition (operation -> device): the import compiles the same sub-models on the
+        same devices without asking the devices again (src/plugins/hetero/src/compiled_model.cpp, the constructor
+        from a stream)."""
+        model = Model._wrap(_c.deserialize(blob.xml, np.frombuffer(blob.weights, dtype=np.uint8)))
+        cfg = dict(blob.header.get("config", {}))
+        cfg.update(config)
+        return self.compile_model(model, cfg, affinity=blob.header.get("affinity"))
 
 
 # ---------------------------------------------------------------------------------------------- BATCH

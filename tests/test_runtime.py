@@ -394,6 +394,45 @@ def test_hetero_splits_by_supported_ops(core):
     assert {s.device for s in cm2.subs} == {"CPU"}
 
 
+def test_hetero_pipeline_parallel_splits_by_memory_and_round_trips_the_partition(core):
+    """MODEL_DISTRIBUTION_POLICY = PIPELINE_PARALLEL: contiguous runs of operations per device, sized by the devices'
+    memory; the exported blob restores the same partition without querying the devices."""
+    class Stage(CpuPlugin):
+        device_name = "STAGE_A"
+    class StageB(CpuPlugin):
+        device_name = "STAGE_B"
+    core.register_plugin(Stage, "STAGE_A")
+    core.register_plugin(StageB, "STAGE_B")
+    rng = np.random.default_rng(5)
+    x = ops.parameter([2, 32], "f32", "x")
+    h = x
+    ws = []
+    for i in range(8):
+        w = rng.standard_normal((32, 32)).astype(np.float32) * 0.2
+        ws.append(w)
+        h = ops.relu(ops.matmul(h, w, False, True, name="fc%d" % i), name="act%d" % i)
+    m = Model([h], [x], "deep")
+    xin = rng.standard_normal((2, 32)).astype(np.float32)
+    want = xin
+    for w in ws:
+        want = np.maximum(want @ w.T, 0)
+    cfg = {props.hint.model_distribution_policy: "PIPELINE_PARALLEL",
+           props.device.properties: {"STAGE_A": {"PIPELINE_MEMORY_BYTES": 3}, "STAGE_B": {"PIPELINE_MEMORY_BYTES": 1}}}
+    cm = core.compile_model(m, "HETERO:STAGE_A,STAGE_B", cfg)
+    assert [s.device for s in cm.subs] == ["STAGE_A", "STAGE_B"]          # one cut, devices in list order
+    on_a = sum(1 for k, v in cm.affinity.items() if v == "STAGE_A" and k.startswith("fc"))
+    assert on_a == 6                                                     # 3 : 1 of the eight equal layers
+    np.testing.assert_allclose(cm(xin)[0], want, rtol=1e-4, atol=1e-5)
+    # equal memory: an even split
+    cm_eq = core.compile_model(m, "HETERO:STAGE_A,STAGE_B", {props.hint.model_distribution_policy: "PIPELINE_PARALLEL"})
+    assert sum(1 for k, v in cm_eq.affinity.items() if v == "STAGE_A" and k.startswith("fc")) == 4
+    # export / import keeps the partition
+    blob = cm.export_model()
+    cm2 = core.import_model(blob, "HETERO:STAGE_A,STAGE_B")
+    assert cm2.affinity == cm.affinity and [s.device for s in cm2.subs] == ["STAGE_A", "STAGE_B"]
+    np.testing.assert_allclose(cm2(xin)[0], want, rtol=1e-4, atol=1e-5)
+
+
 def test_auto_batching(core):
     m = mlp()
     cm = core.compile_model(m, "BATCH:CPU(4)", {props.auto_batch_timeout: 200})
