@@ -12,6 +12,7 @@
 // Math: flash-style online softmax in the exp2 domain, bf16/fp16 tensor-core MMAs with fp32
 // accumulation. All the query heads of one KV group are stacked on the M side of the MMA, so K/V
 // pages are fetched once per group.
+#include <cuda_fp16.h>
 #include <math_constants.h>
 #include <stdlib.h>
 
@@ -27,6 +28,10 @@ namespace ovb {
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
     const int sz = valid ? 16 : 0;   // src-size 0 => 16 zero bytes are written
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc, bool valid) {
+    const int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -81,18 +86,59 @@ __device__ __forceinline__ const uint8_t* kv_row_ptr(const PaKParams& p, const v
     return reinterpret_cast<const uint8_t*>(base) + (((size_t)b * p.dense_S + j) * p.ld_kv + (size_t)h * D) * 2;
 }
 
+// u8 cache: address of the bytes of key/value row j, and of its (scale, zero point) pair.
+template <int D>
+__device__ __forceinline__ const uint8_t* kv_row_ptr_u8(const PaKParams& p, const void* base, int h, int j, int blk_begin) {
+    const int blk = p.block_indices[blk_begin + j / p.block_size];
+    const int off = j % p.block_size;
+    return reinterpret_cast<const uint8_t*>(base) + (((size_t)blk * p.Hkv + h) * p.block_size + off) * D;
+}
+__device__ __forceinline__ const uint8_t* kv_meta_ptr(const PaKParams& p, const void* meta, int h, int j, int blk_begin) {
+    const int blk = p.block_indices[blk_begin + j / p.block_size];
+    const int off = j % p.block_size;
+    return reinterpret_cast<const uint8_t*>(meta) + (((size_t)blk * p.Hkv + h) * p.block_size + off) * 4;
+}
+// Eight cache bytes -> eight bf16 values (byte - zero point) * scale.
+__device__ __forceinline__ uint4 dequant_u8x8(uint2 raw, float scale, float zp) {
+    const float nz = -zp * scale;
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t w = i < 2 ? raw.x : raw.y;
+        const int sh = (i & 1) * 16;
+        o[i] = pack_bf16x2(fmaf((float)((w >> sh) & 0xFFu), scale, nz), fmaf((float)((w >> (sh + 8)) & 0xFFu), scale, nz));
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+// A staged u8 tile ([rows][D] bytes, then one (scale, zero point) fp16 pair per row) -> the swizzled bf16 tile that the
+// ldmatrix reads. `tid` / `nthreads`: the threads that share the work (a warp, or the CTA).
+template <int D>
+__device__ __forceinline__ void expand_u8_tile(const uint8_t* stage, const uint8_t* meta, uint8_t* tile, int rows, int tid, int nthreads) {
+    constexpr int CH = D / 8;
+    for (int i = tid; i < rows * CH; i += nthreads) {
+        const int r = i / CH, c = i % CH;
+        const __half2 sz = *reinterpret_cast<const __half2*>(meta + r * 4);
+        const uint2 raw = *reinterpret_cast<const uint2*>(stage + r * D + c * 8);
+        *reinterpret_cast<uint4*>(tile + tile_off<D>(r, c)) = dequant_u8x8(raw, __low2float(sz), __high2float(sz));
+    }
+}
+
 // ------------------------------------------------------------------------------ prefill / mixed
 // CTA = 8 warps x 16 rows = 128 stacked rows (row = token_in_tile * G + head_in_group) of one
 // (sequence, kv head); K/V tiles of 64 keys double-buffered with cp.async.
-template <int D, int G, bool PAGED, bool F16>
+// KVU8: the cache holds bytes with a (scale, zero point) pair per row; the tiles are staged as bytes (double-buffered) and
+// expanded into one bf16 tile pair before the MMAs.
+template <int D, int G, bool PAGED, bool F16, bool KVU8 = false>
 __global__ void __launch_bounds__(256, 1) pa_prefill_kernel(PaKParams p) {
     pdl_enter_attn();
     constexpr int BM = 128, BN = 64, TOK = BM / G, CH = D / 8;   // CH = 16-byte chunks per row
+    constexpr int U8_STAGE = BN * D + BN * 4;                    // bytes of one staged u8 tile (rows, then the pairs)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t* sQ = smem;
-    uint8_t* sK[2] = {sQ + BM * D * 2, sQ + BM * D * 2 + 2 * BN * D * 2};
+    uint8_t* sK[2] = {sQ + BM * D * 2, KVU8 ? sQ + BM * D * 2 : sQ + BM * D * 2 + 2 * BN * D * 2};
     uint8_t* sV[2] = {sK[0] + BN * D * 2, sK[1] + BN * D * 2};
+    uint8_t* sU = sQ + BM * D * 2 + 2 * BN * D * 2;              // KVU8: [buf][K | V] staged byte tiles
     __shared__ int s_work[4];
 
     const int h = blockIdx.y;   // kv head
@@ -143,6 +189,19 @@ __global__ void __launch_bounds__(256, 1) pa_prefill_kernel(PaKParams p) {
             const int j = j0 + r;
             const bool valid = j < kv_end;
             const int jj = valid ? j : 0;
+            if (KVU8) {
+                // a row is D bytes = CH / 2 chunks of 16; chunk index CH / 2 of a row carries its (scale, zero point) pair
+                uint8_t* uk = sU + buf * (2 * U8_STAGE);
+                uint8_t* uv = uk + U8_STAGE;
+                if (c < CH / 2) {
+                    cp_async16(uk + r * D + c * 16, kv_row_ptr_u8<D>(p, p.k_cache, h, jj, blk_begin) + c * 16, valid);
+                    cp_async16(uv + r * D + c * 16, kv_row_ptr_u8<D>(p, p.v_cache, h, jj, blk_begin) + c * 16, valid);
+                } else if (c == CH / 2) {
+                    cp_async4(uk + BN * D + r * 4, kv_meta_ptr(p, p.k_meta, h, jj, blk_begin), valid);
+                    cp_async4(uv + BN * D + r * 4, kv_meta_ptr(p, p.v_meta, h, jj, blk_begin), valid);
+                }
+                continue;
+            }
             cp_async16(sK[buf] + tile_off<D>(r, c), kv_row_ptr<D, PAGED>(p, p.k_cache, b, h, jj, blk_begin) + c * 16, valid);
             cp_async16(sV[buf] + tile_off<D>(r, c), kv_row_ptr<D, PAGED>(p, p.v_cache, b, h, jj, blk_begin) + c * 16, valid);
         }
@@ -167,6 +226,13 @@ __global__ void __launch_bounds__(256, 1) pa_prefill_kernel(PaKParams p) {
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
+        if (KVU8) {
+            // (the barrier at the end of the previous iteration released the bf16 tiles)
+            const uint8_t* uk = sU + buf * (2 * U8_STAGE);
+            expand_u8_tile<D>(uk, uk + BN * D, sK[0], BN, threadIdx.x, 256);
+            expand_u8_tile<D>(uk + U8_STAGE, uk + U8_STAGE + BN * D, sV[0], BN, threadIdx.x, 256);
+            __syncthreads();
+        }
         if (t == 0) {
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
@@ -286,18 +352,24 @@ __global__ void __launch_bounds__(256, 1) pa_prefill_kernel(PaKParams p) {
 // online-softmax state for the G query heads (padded to the 16-row MMA tile); the 4 warps merge
 // through shared memory. With nsplit > 1 the partial (m, l, O) goes to scratch and
 // pa_decode_combine_kernel finishes.
-template <int D, int G, int PAGE>
+// KVU8: the cache holds bytes with a (scale, zero point) pair per row (half the traffic of a 16-bit cache): a page is staged
+// as bytes and the warp expands it into its one bf16 page pair right before the MMAs.
+template <int D, int G, int PAGE, bool KVU8 = false>
 __global__ void __launch_bounds__(128) pa_decode_kernel(PaKParams p) {
     pdl_enter_attn();
     constexpr int CH = D / 8;
     constexpr int NST = 3;   // page stages per warp
+    constexpr int U8_PAGE = PAGE * D + PAGE * 4;                       // bytes of one staged u8 page (rows, then the pairs)
+    constexpr int STAGE = KVU8 ? 2 * U8_PAGE : 2 * PAGE * D * 2;       // K and V of one stage
+    constexpr int WARP_BYTES = NST * STAGE + (KVU8 ? 2 * PAGE * D * 2 : 0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
     uint8_t* sQ = smem;                                   // 16 x D
-    uint8_t* sKV = smem + 16 * D * 2 + warp * (NST * 2 * PAGE * D * 2);
-    float* sMerge = reinterpret_cast<float*>(smem + 16 * D * 2 + 4 * (NST * 2 * PAGE * D * 2));   // [4][G][D+2]
+    uint8_t* sKV = smem + 16 * D * 2 + warp * WARP_BYTES;
+    uint8_t* sExp = sKV + NST * STAGE;                    // KVU8: the warp's expanded bf16 K and V pages
+    float* sMerge = reinterpret_cast<float*>(smem + 16 * D * 2 + 4 * WARP_BYTES);   // [4][G][D+2]
 
     const int tok = p.subsequence_begins[b];
     const int ctx = p.past_lens[b] + 1;
@@ -321,6 +393,23 @@ __global__ void __launch_bounds__(128) pa_decode_kernel(PaKParams p) {
     auto load_page = [&](int page, int st) {
         const bool pv = page < page_hi;
         const int blk = pv ? p.block_indices[blk_begin + page] : 0;
+        if (KVU8) {
+            // the page's bytes are contiguous (PAGE * D), so are its pairs (PAGE * 4)
+            const size_t pg = (size_t)blk * p.Hkv + h;
+            const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k_cache) + pg * PAGE * D;
+            const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.v_cache) + pg * PAGE * D;
+            uint8_t* dk = sKV + st * STAGE;
+            uint8_t* dv = dk + U8_PAGE;
+            for (int i = lane; i < PAGE * D / 16; i += 32) {
+                cp_async16(dk + i * 16, kb + i * 16, pv);
+                cp_async16(dv + i * 16, vb + i * 16, pv);
+            }
+            if (lane < PAGE * 4 / 16) {
+                cp_async16(dk + PAGE * D + lane * 16, reinterpret_cast<const uint8_t*>(p.k_meta) + pg * PAGE * 4 + lane * 16, pv);
+                cp_async16(dv + PAGE * D + lane * 16, reinterpret_cast<const uint8_t*>(p.v_meta) + pg * PAGE * 4 + lane * 16, pv);
+            }
+            return;
+        }
         const uint8_t* kb = reinterpret_cast<const uint8_t*>(p.k_cache) + (((size_t)blk * p.Hkv + h) * PAGE * D) * 2;
         const uint8_t* vb = reinterpret_cast<const uint8_t*>(p.v_cache) + (((size_t)blk * p.Hkv + h) * PAGE * D) * 2;
         uint8_t* dk = sKV + st * (2 * PAGE * D * 2);
@@ -361,6 +450,14 @@ __global__ void __launch_bounds__(128) pa_decode_kernel(PaKParams p) {
         __syncwarp();
         const uint8_t* kS = sKV + st * (2 * PAGE * D * 2);
         const uint8_t* vS = kS + PAGE * D * 2;
+        if (KVU8) {
+            const uint8_t* uk = sKV + st * STAGE;
+            expand_u8_tile<D>(uk, uk + PAGE * D, sExp, PAGE, lane, 32);
+            expand_u8_tile<D>(uk + U8_PAGE, uk + U8_PAGE + PAGE * D, sExp + PAGE * D * 2, PAGE, lane, 32);
+            __syncwarp();
+            kS = sExp;
+            vS = sExp + PAGE * D * 2;
+        }
         float s[PAGE / 8][4];
 #pragma unroll
         for (int i = 0; i < PAGE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -497,10 +594,10 @@ static int set_smem_once(std::atomic<uint64_t>& configured, const void* kern, in
     return 0;
 }
 
-template <int D, int G, bool PAGED, bool F16>
+template <int D, int G, bool PAGED, bool F16, bool KVU8 = false>
 static int launch_prefill(const PaKParams& p, int num_q_tiles, cudaStream_t stream) {
-    const int smem = 128 * D * 2 + 4 * 64 * D * 2 + 128;
-    auto kern = pa_prefill_kernel<D, G, PAGED, F16>;
+    const int smem = KVU8 ? 128 * D * 2 + 2 * 64 * D * 2 + 4 * (64 * D + 64 * 4) + 128 : 128 * D * 2 + 4 * 64 * D * 2 + 128;
+    auto kern = pa_prefill_kernel<D, G, PAGED, F16, KVU8>;
     static std::atomic<uint64_t> configured{0};   // one bit per device: the attribute is set on first use only
     if (int rc = set_smem_once(configured, reinterpret_cast<const void*>(kern), smem)) return rc;
     dim3 grid(num_q_tiles, p.Hkv);
@@ -509,11 +606,12 @@ static int launch_prefill(const PaKParams& p, int num_q_tiles, cudaStream_t stre
     return 0;
 }
 
-template <int D, int G>
+template <int D, int G, bool KVU8 = false>
 static int launch_decode(const PaKParams& p, cudaStream_t stream) {
     constexpr int PAGE = 16;
-    const int smem = 16 * D * 2 + 4 * (3 * 2 * PAGE * D * 2) + 4 * G * (D + 2) * 4 + 128;
-    auto kern = pa_decode_kernel<D, G, PAGE>;
+    const int warp_bytes = KVU8 ? 3 * 2 * (PAGE * D + PAGE * 4) + 2 * PAGE * D * 2 : 3 * 2 * PAGE * D * 2;
+    const int smem = 16 * D * 2 + 4 * warp_bytes + 4 * G * (D + 2) * 4 + 128;
+    auto kern = pa_decode_kernel<D, G, PAGE, KVU8>;
     static std::atomic<uint64_t> configured{0};
     if (int rc = set_smem_once(configured, reinterpret_cast<const void*>(kern), smem)) return rc;
     dim3 grid(p.B, p.Hkv, p.nsplit);
@@ -574,6 +672,14 @@ int ovb_paged_attention(const ovb_pa_args* a, ovb_stream_t stream_) {
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.causal = 1;
     p.nsplit = 1;
+    p.kv_u8 = a->kv_u8;
+    p.k_meta = a->k_meta;
+    p.v_meta = a->v_meta;
+    if (a->kv_u8) {
+        OVB_REQUIRE(a->k_meta && a->v_meta, "ovb_paged_attention: the u8 cache needs its (scale, zero point) tables");
+        OVB_REQUIRE(a->D == 128 && a->block_size == 16 && (G == 1 || G == 2 || G == 4 || G == 8),
+                    "ovb_paged_attention: the u8 cache is served for head size 128, 16-token blocks and 1, 2, 4 or 8 query heads per KV head");
+    }
 
     if (a->max_q_len == 1 && a->D == 128 && a->block_size == 16 && (G == 1 || G == 2 || G == 4 || G == 8)) {
         OVB_REQUIRE(a->T == a->B, "ovb_paged_attention: decode batch needs one token per sequence");
@@ -582,6 +688,14 @@ int ovb_paged_attention(const ovb_pa_args* a, ovb_stream_t stream_) {
         p.nsplit = ns;
         int kps = (a->max_context_len + ns - 1) / ns;
         p.keys_per_split = ((kps + 63) / 64) * 64;   // whole pages, and page index % 4 == warp stays aligned
+        if (a->kv_u8) {
+            switch (G) {
+                case 1: return launch_decode<128, 1, true>(p, stream);
+                case 2: return launch_decode<128, 2, true>(p, stream);
+                case 4: return launch_decode<128, 4, true>(p, stream);
+                case 8: return launch_decode<128, 8, true>(p, stream);
+            }
+        }
         switch (G) {
             case 1: return launch_decode<128, 1>(p, stream);
             case 2: return launch_decode<128, 2>(p, stream);
@@ -592,6 +706,14 @@ int ovb_paged_attention(const ovb_pa_args* a, ovb_stream_t stream_) {
     // ragged prefill / mixed: tiles of 128/G tokens per (sequence, kv head)
     const int tok_per_tile = 128 / G;
     const int num_q_tiles = a->T / tok_per_tile + a->B;   // upper bound of sum_b ceil(q_len_b / tok_per_tile)
+    if (a->kv_u8) {      // byte pages are expanded in shared memory: the mma.sync kernel (the tcgen05 kernel reads 16-bit pages by TMA)
+        switch (G) {
+            case 1: return launch_prefill<128, 1, true, false, true>(p, num_q_tiles, stream);
+            case 2: return launch_prefill<128, 2, true, false, true>(p, num_q_tiles, stream);
+            case 4: return launch_prefill<128, 4, true, false, true>(p, num_q_tiles, stream);
+            case 8: return launch_prefill<128, 8, true, false, true>(p, num_q_tiles, stream);
+        }
+    }
     // the tcgen05 kernel serves the common shapes; everything else (and OVB_ATTN_TC=0) runs on the mma.sync kernel below
     if (use_tc_attention() && (G == 1 || G == 2 || G == 4 || G == 8)) {
         const int rc = launch_prefill_tc(p, a->D, G, /*paged=*/true, /*f16=*/false, num_q_tiles, stream);

@@ -26,6 +26,11 @@ struct PaKParams {
     int dense_S;
     int ld_kv;
     int causal;
+    // u8 KV cache (kv_u8 != 0): k_cache / v_cache hold bytes [block, kv head, slot, D]; k_meta / v_meta hold one fp16 pair
+    // (scale, zero point) per (block, kv head, slot): value = (byte - zero point) * scale
+    int kv_u8;
+    const void* k_meta;
+    const void* v_meta;
 };
 
 // tcgen05 / TMA prefill and dense attention (attention_sm100.cu). Returns a negative code when the shape is not one it

@@ -432,6 +432,62 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
     }
 }
 
+// The same with a u8 KV cache (head size 128): a warp owns one (token, head), a lane four values. Key and value rows are
+// quantised per row: scale = (max - min) / 255, zero point = -min / scale, byte = round(x / scale + zero point), and the
+// (scale, zero point) pair is stored as fp16 beside the bytes; value = (byte - zero point) * scale. Query heads are rotated in
+// place as before. Role in the reference: the by-token quantisation of the KV cache,
+// src/plugins/intel_gpu/src/kernel_selector/cl_kernels/pa_kv_cache_update_ref.cl and dynamic_quantize_gpu_kv_cache.cl.
+__global__ void rope_kv_write_u8_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slot_map,
+                                        uint8_t* __restrict__ k_cache, uint8_t* __restrict__ v_cache, __half2* __restrict__ k_meta,
+                                        __half2* __restrict__ v_meta, int Hq, int Hkv, float log2_theta, int block_size) {
+    pdl_enter();
+    constexpr int D = 128, half = 64;
+    const int t = blockIdx.x;
+    const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (h >= Hq + 2 * Hkv) return;
+    const int slot = slot_map[t];
+    const int blk = slot / block_size, off = slot - blk * block_size;
+    __nv_bfloat16* p = qkv + ((size_t)t * (Hq + 2 * Hkv) + h) * D;
+    const int d = lane * 2;
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + d));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + d + half));
+    float v[4] = {a.x, a.y, b.x, b.y};
+    const bool is_v = h >= Hq + Hkv;
+    if (!is_v) {
+        const float pos = float(positions[t]);
+        float s0, c0, s1, c1;
+        sincosf(pos * exp2f(-log2_theta * (2.0f * float(d) / float(D))), &s0, &c0);
+        sincosf(pos * exp2f(-log2_theta * (2.0f * float(d + 1) / float(D))), &s1, &c1);
+        v[0] = a.x * c0 - b.x * s0; v[1] = a.y * c1 - b.y * s1;
+        v[2] = b.x * c0 + a.x * s0; v[3] = b.y * c1 + a.y * s1;
+        if (h < Hq) {
+            *reinterpret_cast<__nv_bfloat162*>(p + d) = __floats2bfloat162_rn(v[0], v[1]);
+            *reinterpret_cast<__nv_bfloat162*>(p + d + half) = __floats2bfloat162_rn(v[2], v[3]);
+            return;
+        }
+    }
+    if (slot < 0) return;                      // uniform over the warp
+    float mn = fminf(fminf(v[0], v[1]), fminf(v[2], v[3])), mx = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+    for (int o = 16; o; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    // the pair is stored as fp16: quantise with the values the reader will see
+    float scale = __half2float(__float2half_rn((mx - mn) * (1.0f / 255.0f)));
+    if (!(scale > 0.f)) scale = 1.0f;
+    const float zp = __half2float(__float2half_rn(-mn / scale));
+    uint32_t q[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = (uint32_t)fminf(fmaxf(rintf(v[i] / scale + zp), 0.f), 255.f);
+    const int hk = is_v ? h - Hq - Hkv : h - Hq;
+    const size_t row = ((size_t)blk * Hkv + hk) * block_size + off;
+    uint8_t* dst = (is_v ? v_cache : k_cache) + row * D;
+    *reinterpret_cast<uint16_t*>(dst + d) = (uint16_t)(q[0] | (q[1] << 8));
+    *reinterpret_cast<uint16_t*>(dst + d + half) = (uint16_t)(q[2] | (q[3] << 8));
+    if (lane == 0) (is_v ? v_meta : k_meta)[row] = __floats2half2_rn(scale, zp);
+}
+
 // ------------------------------------------------------------------------------------ MoE token grouping (prefill)
 // For every local expert: the indices of the tokens routed to it, in token order, and their number. One CTA per expert
 // walks the tokens in chunks of its size; positions come from a ballot / prefix sum, so the order is deterministic.
@@ -928,6 +984,19 @@ int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void
                                                     (__nv_bfloat16*)v_cache, Hq, Hkv, D, log2f(theta), block_size));
     }
     OVB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int ovb_rope_kv_write_u8(void* qkv, const int* positions, const int* slot_map, void* k_cache, void* v_cache, void* k_meta, void* v_meta, int T,
+                         int Hq, int Hkv, int D, float theta, int block_size, ovb_stream_t stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    OVB_REQUIRE(qkv && positions && slot_map && k_cache && v_cache && k_meta && v_meta && T > 0, "ovb_rope_kv_write_u8: null operand");
+    OVB_REQUIRE(D == 128, "ovb_rope_kv_write_u8: the u8 cache is served for head size 128");
+    OVB_REQUIRE(((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                  reinterpret_cast<uintptr_t>(k_meta) | reinterpret_cast<uintptr_t>(v_meta)) & 3) == 0, "ovb_rope_kv_write_u8: 4-byte aligned tensors expected");
+    const int heads = Hq + 2 * Hkv;
+    OVB_CHECK_CUDA(launch_pdl(rope_kv_write_u8_kernel, dim3(T, (heads + 3) / 4), dim3(128), 0, stream, (__nv_bfloat16*)qkv, positions, slot_map, (uint8_t*)k_cache,
+                              (uint8_t*)v_cache, (__half2*)k_meta, (__half2*)v_meta, Hq, Hkv, log2f(theta), block_size));
     return 0;
 }
 

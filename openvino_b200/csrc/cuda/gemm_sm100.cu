@@ -86,7 +86,7 @@ struct GemmKParams {
     // Grouped GEMM (mixture of experts): the rows of X / out are grouped, group g owns rows [group_off[g], group_off[g + 1])
     // (device array, written by an earlier kernel of the stream) and uses weight g of a stack: group_mode 1 = the weights are
     // stacked along N (tile index g * tiles_n + n_tile), 2 = stacked along K (k-block offset g * K / 64). T is the row capacity.
-    int nvls_lag;             // in-switch all-reduce: a CTA reduces the tile posted this many CTAs earlier (one wave of resident CTAs)
+    int nvls_reducers;        // in-switch all-reduce: the first CTAs of the grid only reduce (0: every tile CTA reduces its own tile)
     const int* group_off;
     int num_groups;
     int group_mode;
@@ -183,6 +183,65 @@ __device__ __forceinline__ void tile_coords(int idx, int N, int T, int bt, int& 
     n_tile = band * kBandN + (r - t_tile * in_band);
 }
 
+// In-switch all-reduce, the reducing half: wait until every rank has posted its partial of tile `rt` (flag words of the tile
+// >= epoch), then fetch the sum over the ranks of this rank's 1/W share of the tile (multimem.ld_reduce, fp32 accumulation in
+// the switch) and write it to `out` on every rank (multimem.st). Called by `nthreads` threads (thread `tid`) that meet at
+// named barrier `bar_id`; `wait_s` is one shared int. Returns false when the wait ran out (status already reported).
+template <int BT>
+__device__ __forceinline__ bool nvls_reduce_tile(const GemmKParams& p, int rt, int epoch, int tid, int nthreads, int bar_id, volatile int* wait_s,
+                                                 volatile int* abort_flag) {
+    constexpr int PIECES = BT * (TILE_N / 8);
+    constexpr size_t SLOT = (size_t)BT * TILE_N * 2;
+    const int W = p.world;
+    const int* bar_local = reinterpret_cast<const int*>(p.heap[p.rank] + p.nvls_flags_off) + (size_t)rt * kNvlsFlagStride;
+    if (tid == 0) {
+        bool ok = false;
+        for (uint32_t it = 0; it < kPeerSpinLimit && !ok; ++it) {
+            const uint4 a = ld_relaxed_sys_v4(bar_local), b = ld_relaxed_sys_v4(bar_local + 4);
+            const int w[8] = {(int)a.x, (int)a.y, (int)a.z, (int)a.w, (int)b.x, (int)b.y, (int)b.z, (int)b.w};
+            ok = true;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) ok = ok && (r >= W || w[r] >= epoch);
+            if (!ok) {
+                if (abort_flag != nullptr && (it & 255u) == 255u && *abort_flag) break;
+                if (it > 32) __nanosleep(100);
+            }
+        }
+        if (ok) {
+            fence_sys();
+        } else {
+            report_status(p.status, STATUS_PEER_TIMEOUT);
+        }
+        *wait_s = ok ? 1 : 0;
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads));
+    const bool ok = *wait_s != 0;
+    if (ok) {
+        int rn, rtt;
+        tile_coords(rt, p.N, p.T, BT, rn, rtt);
+        const int r_t0 = rtt * BT, r_n0 = rn * TILE_N, r_ntok = min(BT, p.T - r_t0);
+        const size_t r_slot = (size_t)p.stage_off + (size_t)rt * SLOT;
+        const int per = PIECES / W;                             // PIECES is a multiple of 256, W of 2, 4 or 8
+        // batches of four reducing loads in flight per thread, then their stores (a load is a round trip to the switch)
+        for (int k0 = tid; k0 < per; k0 += 4 * nthreads) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = k0 + j * nthreads, i = p.rank * per + k;
+                if (k < per && (i >> 4) < r_ntok) v[j] = multimem_ld_reduce_bf16x8(p.mc + r_slot + (size_t)i * 16);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int k = k0 + j * nthreads, i = p.rank * per + k;
+                const int col = i >> 4, pc = i & 15;
+                if (k < per && col < r_ntok) multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(r_t0 + col) * p.ldo + r_n0 + pc * 8) * 2, v[j]);
+            }
+        }
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads));   // wait_s may be rewritten after this point
+    return ok;
+}
+
 // Quantised stages cover two k-blocks (128 elements of K) except for 256-token tiles, whose token tile alone is 32 KB
 // per k-block: every barrier round trip between the producers, the dequant warps and the MMA issuer then moves twice
 // the data, which halves the per-byte cost of the control chain.
@@ -239,6 +298,33 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // In-switch all-reduce with reducer CTAs: the first `nvls_reducers` CTAs of the grid (dispatched first, small enough to sit
+    // beside a tile CTA on an SM) do nothing but reduce: reducer r takes tiles r, r + R, ... in the order in which the tile
+    // CTAs post them. The tile CTAs store their partial, post and leave, so the tensor pipe never waits for the switch.
+    const int cta = (int)blockIdx.x - p.nvls_reducers;   // tile index of this CTA (negative: a reducer)
+    if (cta < 0) {
+        __shared__ int red_wait_s;
+        pdl_wait();
+        const int epoch = __ldcg(p.epoch);
+        const int R = p.nvls_reducers, tiles = (int)gridDim.x - R;
+        bool ok = true;
+        for (int rt = (int)blockIdx.x; rt < tiles && ok; rt += R)
+            ok = nvls_reduce_tile<BT>(p, rt, epoch, (int)threadIdx.x, (int)blockDim.x, 2, &red_wait_s, nullptr);
+        // completion: the last reducer of this rank meets the other ranks' last reducers (words 8..15 of tile 0's flags), so
+        // when the kernel ends on a rank every share of every tile has landed in its `out`
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            fence_sys();
+            const int done = atomicAdd(p.counters, 1);
+            if (done == R - 1) {
+                *p.counters = 0;
+                const int* bar_local = reinterpret_cast<const int*>(p.heap[p.rank] + p.nvls_flags_off) + 8;
+                int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + 8;
+                if (!nvls_barrier(bar_local, bar_mc, p.rank, p.world, epoch, kPeerSpinLimit, nullptr)) report_status(p.status, STATUS_PEER_TIMEOUT);
+            }
+        }
+        return;
+    }
     int n_tile, t_tile;
     int w_tile, w_kb0 = 0;          // weight tile and first k-block inside the (possibly stacked) weight
     int t0, T_end = p.T;            // first row of the tile, one past the last valid row
@@ -246,8 +332,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // the offsets come from an earlier kernel of the stream: nothing of this CTA may run before that kernel is done
         pdl_wait();
         const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
-        n_tile = blockIdx.x % tiles_n;
-        const int tt = blockIdx.x / tiles_n;
+        n_tile = cta % tiles_n;
+        const int tt = cta / tiles_n;
         int g = 0, acc = 0, begin = 0, end = 0;
         for (; g < p.num_groups; ++g) {
             begin = __ldg(p.group_off + g);
@@ -263,7 +349,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         w_tile = p.group_mode == 1 ? g * tiles_n + n_tile : n_tile;
         w_kb0 = p.group_mode == 2 ? g * ((p.K + TILE_K - 1) / TILE_K) : 0;
     } else {
-        tile_coords(blockIdx.x, p.N, p.T, BT, n_tile, t_tile);
+        tile_coords(cta, p.N, p.T, BT, n_tile, t_tile);
         w_tile = n_tile;
         t0 = t_tile * BT;
     }
@@ -536,7 +622,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         pdl_wait();   // the epilogue reads the residual and writes the output: both belong to the stream's earlier kernels until now
 
         const float bias_v = (p.bias != nullptr && oc < p.N) ? to_float(reinterpret_cast<const E*>(p.bias)[oc]) : 0.f;
-        const int tile_id = blockIdx.x;
+        const int tile_id = cta;
         // Fast path: whole 128-row tile inside N, 16-bit output with 16-byte aligned rows. The tile is staged
         // in shared memory as [token][128] (the pipeline stages are free by now) and written with 16-byte
         // stores that cover 256 contiguous bytes per token row.
@@ -553,7 +639,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int epoch = __ldcg(p.epoch);
             constexpr int PIECES = BT * (TILE_N / 8);               // 16-byte pieces of the bf16 tile
             constexpr size_t SLOT = (size_t)BT * TILE_N * 2;        // bytes of one bf16 tile
-            const int tiles = gridDim.x;
+            const int tiles = (int)gridDim.x - p.nvls_reducers;
             const int W = p.world;
             if (p.nvls) {
                 // In-switch all-reduce (NVLS). Every rank stores its bf16 partial tile in its OWN staging slot (rank 0 adds
@@ -595,64 +681,16 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     fence_sys();
                     multimem_st_u32(reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + (size_t)tile_id * kNvlsFlagStride + p.rank, (uint32_t)epoch);
                 }
-                // Reduce, deferred: waiting here for the other ranks' copies of THIS tile would hold the SM idle for a trip
-                // through the switch per tile. Instead the CTA reduces this rank's share of the tile that was posted
-                // `nvls_lag` CTAs earlier (one wave of resident CTAs: its partials have long arrived), and only the CTAs of the
-                // last wave also wait for their own tile. Rank r fetches the sum over all ranks of its 1/W share of a tile with
-                // multimem.ld_reduce and writes it to `out` on every rank with multimem.st: each piece is reduced exactly
-                // once, so all ranks hold the same bits. Traffic per rank and tile: one tile out (pulled by the switch), one in.
-                const int per = PIECES / W;                             // PIECES is a multiple of 256, W of 2, 4 or 8
-                constexpr int MAXP = (PIECES / 2 + DQ_THREADS - 1) / DQ_THREADS;
-                const int lag = p.nvls_lag;
-#pragma unroll 1
-                for (int pass = 0; pass < 2; ++pass) {
-                    const int rt = pass == 0 ? tile_id - lag : tile_id;                 // tile to reduce in this pass
-                    if (rt < 0 || (pass == 1 && tile_id + lag < tiles)) continue;       // pass 1: a later CTA takes this tile
-                    const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + (size_t)rt * kNvlsFlagStride;
-                    if (dq_tid == 0) {
-                        bool ok = false;
-                        for (uint32_t it = 0; it < kPeerSpinLimit && !ok; ++it) {
-                            const uint4 a = ld_relaxed_sys_v4(bar_local), b = ld_relaxed_sys_v4(bar_local + 4);
-                            const int w[8] = {(int)a.x, (int)a.y, (int)a.z, (int)a.w, (int)b.x, (int)b.y, (int)b.z, (int)b.w};
-                            ok = true;
-#pragma unroll
-                            for (int r = 0; r < 8; ++r) ok = ok && (r >= W || w[r] >= epoch);
-                            if (!ok) {
-                                if ((it & 255u) == 255u && *abort_flag) break;
-                                if (it > 32) __nanosleep(100);
-                            }
-                        }
-                        if (ok) {
-                            fence_sys();
-                        } else {
-                            report_status(p.status, STATUS_PEER_TIMEOUT);
-                            *abort_flag = 1;
-                        }
-                    }
-                    asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));
-                    if (*abort_flag) return;
-                    int rn, rtt;
-                    tile_coords(rt, p.N, p.T, BT, rn, rtt);
-                    const int r_t0 = rtt * BT, r_n0 = rn * TILE_N, r_ntok = min(BT, p.T - r_t0);
-                    const size_t r_slot = (size_t)p.stage_off + (size_t)rt * SLOT;
-                    // all reducing loads of a thread are in flight together, then the stores (a load is a round trip to the switch)
-                    uint4 v[MAXP];
-#pragma unroll
-                    for (int j = 0; j < MAXP; ++j) {
-                        const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
-                        if (k < per && (i >> 4) < r_ntok) v[j] = multimem_ld_reduce_bf16x8(p.mc + r_slot + (size_t)i * 16);
-                    }
-#pragma unroll
-                    for (int j = 0; j < MAXP; ++j) {
-                        const int k = dq_tid + j * DQ_THREADS, i = p.rank * per + k;
-                        const int col = i >> 4, pc = i & 15;
-                        if (k < per && col < r_ntok) multimem_st_b128(p.mc + (size_t)p.out_off + ((size_t)(r_t0 + col) * p.ldo + r_n0 + pc * 8) * 2, v[j]);
-                    }
+                if (p.nvls_reducers > 0) return;      // the reducer CTAs take it from here
+                // No reducer CTAs (a launch of a single wave, e.g. a decode step): this CTA waits for the other ranks' copies of
+                // its own tile and reduces its share.
+                if (!nvls_reduce_tile<BT>(p, tile_id, epoch, dq_tid, DQ_THREADS, 1, last_flag, abort_flag)) {
+                    if (dq_tid == 0) *abort_flag = 1;
+                    return;
                 }
                 // Completion: the last CTA of this rank to get here meets the other ranks' last CTAs (words 8..15 of tile 0's
                 // flags), so when the kernel ends on a rank every share of every tile has landed in its `out`, and every
                 // rank is done reading the staging slots.
-                asm volatile("bar.sync 1, %0;" ::"n"(DQ_THREADS));     // orders the CTA's stores before thread 0's release fence
                 if (dq_tid == 0) {
                     fence_sys();
                     const int done = atomicAdd(p.counters, 1);
@@ -1212,6 +1250,11 @@ static int pick_block_t(int T) {
     return 256;
 }
 
+static int env_int(const char* name, int dflt) {
+    const char* e = getenv(name);
+    return e ? atoi(e) : dflt;
+}
+
 constexpr int kMaxSplits = 8;   // portable cluster size
 static std::mutex g_launch_mu;   // first-use set-up of a kernel variant (function attributes, occupancy table)
 
@@ -1334,7 +1377,7 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
             resident[0] = 0;
         }
     }
-    p.nvls_lag = resident[1];
+    // reducer CTAs when the tiles take more than one wave (set below with the grid)
     if (p.splits == 0) p.splits = pick_splits(a->T, a->N, a->K, BT, WMODE, resident);
     const int total_kb = ceil_div(a->K, TILE_K);
     if (p.splits > total_kb) p.splits = total_kb;
@@ -1343,6 +1386,12 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     cfg.gridDim = dim3(ceil_div(a->N, TILE_N) * ceil_div(a->T, BT), 1, p.splits);
     if (p.group_off != nullptr)     // every group may end with a partial row tile: num_groups extra tiles cover the worst case
         cfg.gridDim = dim3(ceil_div(a->N, TILE_N) * (ceil_div(a->T, BT) + p.num_groups), 1, 1);
+    p.nvls_reducers = 0;
+    if (p.nvls && p.splits == 1 && p.group_off == nullptr && (int)cfg.gridDim.x > resident[1]) {
+        static const int want = env_int("OVB_NVLS_REDUCERS", 32);
+        p.nvls_reducers = want < 0 ? 0 : (want > 128 ? 128 : want);
+        cfg.gridDim.x += p.nvls_reducers;
+    }
     attr[0].val.clusterDim.z = p.splits;
     // programmatic dependent launch: set-up, tensor-memory allocation and the first weight fetches run under the tail of
     // the kernel before this one (the kernel waits before it reads activations or writes anything)
@@ -1386,12 +1435,8 @@ int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act) {
 // Environment overrides for measurements (every rank must set them alike): OVB_COMM_TWOHOP = 0 / 1 forces the two-hop packet
 // protocol of the one-shot sizes off / on; OVB_COMM_NVLS_MODES is a bit mask of the modes (bit 0: T <= 128, bit 1: larger) that
 // reduce inside the switch when the heap has a multicast mapping.
-static int env_int(const char* name, int dflt) {
-    const char* e = getenv(name);
-    return e ? atoi(e) : dflt;
-}
 static int comm_twohop(int world) {
-    static const int env = env_int("OVB_COMM_TWOHOP", -1);
+    static const int env = ovb::env_int("OVB_COMM_TWOHOP", -1);
     return env >= 0 ? env : (world > 2);
 }
 // Bit (mode - 1) set: the all-reduce of that mode runs inside the switch (multimem.ld_reduce / multimem.st) when the heap has a
@@ -1399,7 +1444,7 @@ static int comm_twohop(int world) {
 // for the two-shot packets and 425/474 us for GEMM then NCCL; with 2 ranks the packets win (362/533 us against 499/683 us).
 // At T=64 the two-hop packets (28.7/31.7 us with 8 ranks) beat in-switch (37.8/43.0 us) at every world size.
 static int comm_nvls_modes(int world) {
-    static const int env = env_int("OVB_COMM_NVLS_MODES", -1);
+    static const int env = ovb::env_int("OVB_COMM_NVLS_MODES", -1);
     return env >= 0 ? env : (world >= 4 ? 2 : 0);
 }
 

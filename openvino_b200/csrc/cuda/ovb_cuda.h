@@ -195,6 +195,10 @@ int ovb_scatter_tokens(const int* tokens, const int* tok_dst, int* last_token, i
 //   k_cache/v_cache : [num_blocks, Hkv, block_size, D] bf16
 int ovb_rope_kv_write(void* qkv, const int* positions, const int* slot_map, void* k_cache, void* v_cache, int T,
                       int Hq, int Hkv, int D, float theta, int block_size, ovb_stream_t stream);
+/* The same into a u8 cache: key / value rows are quantised per (token, head) row and their (scale, zero point) pairs go
+   to k_meta / v_meta (see ovb_pa_args). */
+int ovb_rope_kv_write_u8(void* qkv, const int* positions, const int* slot_map, void* k_cache, void* v_cache, void* k_meta, void* v_meta, int T,
+                         int Hq, int Hkv, int D, float theta, int block_size, ovb_stream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // Paged attention. Cache layout [num_blocks, Hkv, block_size, D]; ragged batch described like the
@@ -217,6 +221,11 @@ typedef struct {
     int max_q_len;            // longest subsequence in the batch (1 = pure decode)
     int sliding_window;       // 0 = off
     float scale;
+    /* u8 KV cache (kv_u8 != 0): the caches hold bytes [num_blocks, Hkv, block_size, D], k_meta / v_meta one fp16 pair
+       (scale, zero point) per (block, kv head, slot): value = (byte - zero point) * scale. Head size 128, 16-token blocks. */
+    int kv_u8;
+    const void* k_meta;
+    const void* v_meta;
 } ovb_pa_args;
 int ovb_paged_attention(const ovb_pa_args* a, ovb_stream_t stream);
 int64_t ovb_pa_scratch_bytes(int B, int Hq, int D, int max_context_len);

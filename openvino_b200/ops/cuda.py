@@ -48,6 +48,7 @@ class PaArgs(C.Structure):
         ("B", C.c_int), ("T", C.c_int), ("Hq", C.c_int), ("Hkv", C.c_int), ("D", C.c_int),
         ("ldq", C.c_int), ("block_size", C.c_int), ("max_context_len", C.c_int), ("max_q_len", C.c_int),
         ("sliding_window", C.c_int), ("scale", C.c_float),
+        ("kv_u8", C.c_int), ("k_meta", C.c_void_p), ("v_meta", C.c_void_p),
     ]
 
 
@@ -535,9 +536,21 @@ def rope_kv_write(qkv, positions, slot_map, k_cache, v_cache, Hq, Hkv, D, theta,
                                    C.c_float(theta), C.c_int(block_size), C.c_void_p(_stream())), "ovb_rope_kv_write")
 
 
+def rope_kv_write_u8(qkv, positions, slot_map, k_cache, v_cache, k_meta, v_meta, Hq, Hkv, D, theta, block_size):
+    """RoPE on the query / key heads of ``qkv`` and the write of the new key / value rows into a u8 cache: rows are
+    quantised per (token, head); ``k_meta`` / ``v_meta`` [num_blocks, Hkv, block_size, 2] fp16 receive (scale, zero point)."""
+    T = qkv.shape[0]
+    assert k_cache.dtype == torch.uint8 and k_meta.dtype == torch.float16
+    _check(lib().ovb_rope_kv_write_u8(C.c_void_p(qkv.data_ptr()), C.c_void_p(positions.data_ptr()), C.c_void_p(slot_map.data_ptr()),
+                                      C.c_void_p(k_cache.data_ptr()), C.c_void_p(v_cache.data_ptr()), C.c_void_p(k_meta.data_ptr()),
+                                      C.c_void_p(v_meta.data_ptr()), C.c_int(T), C.c_int(Hq), C.c_int(Hkv), C.c_int(D), C.c_float(theta),
+                                      C.c_int(block_size), C.c_void_p(_stream())), "ovb_rope_kv_write_u8")
+
+
 def paged_attention(q, k_cache, v_cache, past_lens, subsequence_begins, block_indices, block_indices_begins, Hq, Hkv, D,
-                    scale=None, max_context_len=0, max_q_len=0, sliding_window=0, block_size=16, out=None, ws=None):
-    """q: [T, >=Hq*D] (row pitch = q.stride(0)); caches [num_blocks, Hkv, block_size, D]."""
+                    scale=None, max_context_len=0, max_q_len=0, sliding_window=0, block_size=16, out=None, ws=None, k_meta=None, v_meta=None):
+    """q: [T, >=Hq*D] (row pitch = q.stride(0)); caches [num_blocks, Hkv, block_size, D] (16-bit, or uint8 with the
+    (scale, zero point) tables ``k_meta`` / ``v_meta``)."""
     T = q.shape[0]
     B = past_lens.numel()
     if out is None:
@@ -555,6 +568,9 @@ def paged_attention(q, k_cache, v_cache, past_lens, subsequence_begins, block_in
     a.block_size, a.max_context_len, a.max_q_len = block_size, max_context_len, max_q_len
     a.sliding_window = sliding_window
     a.scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if k_cache.dtype == torch.uint8:
+        assert k_meta is not None and v_meta is not None
+        a.kv_u8, a.k_meta, a.v_meta = 1, k_meta.data_ptr(), v_meta.data_ptr()
     _check(lib().ovb_paged_attention(C.byref(a), C.c_void_p(_stream())), "ovb_paged_attention")
     return out
 

@@ -246,8 +246,11 @@ class CudaLlmExecutor:
 
     def __init__(self, cfg: LlmConfig, weights: LlmWeights, num_kv_blocks: int, block_size: int = 16,
                  max_batch_tokens: int = 8192, max_seqs: int = 64, max_blocks_per_seq: int = 0, device="cuda",
-                 comm=None, use_cuda_graphs: bool = True):
+                 comm=None, use_cuda_graphs: bool = True, kv_cache_precision: str = "bf16"):
         self.cfg, self.w = cfg, weights
+        self.kv_u8 = str(kv_cache_precision).lower() == "u8"
+        if self.kv_u8 and (cfg.head_dim != 128 or block_size != 16):
+            raise ValueError("the u8 KV cache is served for head size 128 and 16-token blocks")
         self.device = torch.device(device)
         self.block_size = block_size
         self.num_kv_blocks = num_kv_blocks
@@ -260,9 +263,14 @@ class CudaLlmExecutor:
         if max_blocks_per_seq <= 0:
             max_blocks_per_seq = max(1, num_kv_blocks // max(1, max_seqs)) + 1
         self.max_blocks_per_seq = max_blocks_per_seq
-        self.k_cache = [torch.zeros((num_kv_blocks, self.hkv, block_size, cfg.head_dim), dtype=torch.bfloat16, device=self.device)
-                        for _ in range(cfg.num_layers)]
+        # KV_CACHE_PRECISION = u8: rows are stored as bytes with one fp16 (scale, zero point) pair per (block, head, slot):
+        # half the cache memory and half the decode traffic of the 16-bit cache
+        self.k_cache = [torch.zeros((num_kv_blocks, self.hkv, block_size, cfg.head_dim), dtype=torch.uint8 if self.kv_u8 else torch.bfloat16,
+                                    device=self.device) for _ in range(cfg.num_layers)]
         self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+        self.k_meta = [torch.zeros((num_kv_blocks, self.hkv, block_size, 2), dtype=torch.float16, device=self.device) if self.kv_u8 else None
+                       for _ in range(cfg.num_layers)]
+        self.v_meta = [torch.zeros_like(m) if m is not None else None for m in self.k_meta]
         self.ws = K.Workspace(self.device)
         if self.tp_size > 1:
             if comm is None:
@@ -312,13 +320,17 @@ class CudaLlmExecutor:
         for l, lw in enumerate(w.layers):
             K.rmsnorm(h, lw.norm1, cfg.rms_eps, out=x)
             K.gemm(x, lw.qkv, out=qkv, ws=ws)
-            K.rope_kv_write(qkv, positions, slot_map, self.k_cache[l], self.v_cache[l], self.hq, self.hkv, D,
-                            cfg.rope_theta, self.block_size)
+            if self.kv_u8:
+                K.rope_kv_write_u8(qkv, positions, slot_map, self.k_cache[l], self.v_cache[l], self.k_meta[l], self.v_meta[l], self.hq, self.hkv, D,
+                                   cfg.rope_theta, self.block_size)
+            else:
+                K.rope_kv_write(qkv, positions, slot_map, self.k_cache[l], self.v_cache[l], self.hq, self.hkv, D,
+                                cfg.rope_theta, self.block_size)
             K.paged_attention(qkv, self.k_cache[l], self.v_cache[l], sb.view("past_lens")[:B],
                               sb.view("subsequence_begins")[:B + 1], sb.view("block_indices"),
                               sb.view("block_indices_begins")[:B + 1], self.hq, self.hkv, D,
                               max_context_len=shp.max_ctx, max_q_len=shp.max_q_len, sliding_window=cfg.sliding_window,
-                              block_size=self.block_size, out=attn, ws=ws)
+                              block_size=self.block_size, out=attn, ws=ws, k_meta=self.k_meta[l], v_meta=self.v_meta[l])
             self._row_parallel(attn, lw.o, h, 2 * l)
             K.rmsnorm(h, lw.norm2, cfg.rms_eps, out=x)
             if cfg.num_experts:
@@ -479,4 +491,4 @@ class CudaLlmExecutor:
         return sb.tokens_host[mirror][:B]
 
     def kv_cache_bytes(self) -> int:
-        return sum(k.numel() * 2 * 2 for k in self.k_cache)
+        return sum(2 * k.numel() * k.element_size() + (2 * m.numel() * 2 if m is not None else 0) for k, m in zip(self.k_cache, self.k_meta))

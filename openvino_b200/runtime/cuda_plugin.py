@@ -1426,7 +1426,8 @@ class CudaServingCompiledModel(CompiledModel):
         with torch.cuda.device(self.device):
             ex = CudaLlmExecutor(self.llm_config, self.weights(), num_kv_blocks=num_blocks, block_size=block_size,
                                  max_batch_tokens=max_num_batched_tokens, max_seqs=max_num_seqs, max_blocks_per_seq=blocks_per_seq,
-                                 device=self.device, comm=comm, use_cuda_graphs=bool(self.config.get(props.cuda.use_cuda_graphs, True)))
+                                 device=self.device, comm=comm, use_cuda_graphs=bool(self.config.get(props.cuda.use_cuda_graphs, True)),
+                                 kv_cache_precision=str(self.config.get(props.hint.kv_cache_precision, "bf16") or "bf16"))
         sc = SchedulerConfig(max_num_batched_tokens=max_num_batched_tokens, max_num_seqs=max_num_seqs, num_kv_blocks=num_blocks,
                              block_size=block_size, max_blocks_per_seq=blocks_per_seq)
         return ex, sc

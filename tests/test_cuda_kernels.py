@@ -460,6 +460,74 @@ def test_rope_kv_write_and_paged_attention(ops, q_lens, past_lens, Hq, Hkv):
     assert _rel_err(out.reshape(T, Hq, D), ref) < 1e-2
 
 
+@pytest.mark.parametrize("q_lens,past_lens,Hq,Hkv", [
+    ([1, 1, 1, 1], [0, 15, 16, 300], 8, 2),             # decode
+    ([1] * 5, [5, 1000, 77, 256, 511], 32, 8),          # decode, split over the keys
+    ([40, 17, 128], [0, 3, 70], 8, 2),                  # prefill with history
+    ([200, 1], [56, 9], 32, 8),                         # mixed
+    ([90], [300], 4, 4),
+])
+def test_u8_kv_cache_write_and_attention(ops, q_lens, past_lens, Hq, Hkv):
+    """KV_CACHE_PRECISION = u8: rows are quantised per (token, head) by the write kernel; decode and prefill attention read
+    the bytes. Reference: fp32 attention over the dequantised cache ((byte - zero point) * scale)."""
+    torch.manual_seed(16)
+    D, bs, theta, dev = 128, 16, 10000.0, "cuda"
+    pl_t, sb_t, bi_t, bib_t, total_blocks = _make_paged_batch(q_lens, past_lens, bs, dev)
+    B = len(q_lens)
+    k_cache = torch.zeros(total_blocks, Hkv, bs, D, device=dev, dtype=torch.uint8)
+    v_cache = torch.zeros_like(k_cache)
+    k_meta = torch.zeros(total_blocks, Hkv, bs, 2, device=dev, dtype=torch.float16)
+    v_meta = torch.zeros_like(k_meta)
+
+    def write(n_tok_per_seq, start_per_seq):
+        """Runs the write kernel for tokens [start, start + n) of every sequence; returns (qkv after RoPE, raw qkv, positions)."""
+        pos, slots = [], []
+        for b in range(B):
+            blocks = bi_t[bib_t[b]:bib_t[b + 1]].long().tolist()
+            for j in range(start_per_seq[b], start_per_seq[b] + n_tok_per_seq[b]):
+                pos.append(j)
+                slots.append(blocks[j // bs] * bs + j % bs)
+        T = len(pos)
+        if T == 0:
+            return None, None, None, None
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device=dev).to(torch.bfloat16)
+        raw = qkv.clone()
+        pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
+        slots_t = torch.tensor(slots, dtype=torch.int32, device=dev)
+        ops.rope_kv_write_u8(qkv, pos_t, slots_t, k_cache, v_cache, k_meta, v_meta, Hq, Hkv, D, theta, bs)
+        return qkv, raw, pos_t, slots_t
+
+    write(past_lens, [0] * B)                                        # history
+    qkv, raw, pos_t, slots_t = write(q_lens, past_lens)              # the step's tokens
+    T = sum(q_lens)
+    # the write: queries rotated in place, rows quantised within half a step of the fp32 value
+    q_ref = _rope_ref(raw[:, : Hq * D].float().reshape(T, Hq, D), pos_t, theta)
+    assert _rel_err(qkv[:, : Hq * D].reshape(T, Hq, D), q_ref) < 5e-3
+    k_new = _rope_ref(raw[:, Hq * D:(Hq + Hkv) * D].float().reshape(T, Hkv, D), pos_t, theta)
+    v_new = raw[:, (Hq + Hkv) * D:].float().reshape(T, Hkv, D)
+
+    def deq(cache, meta):
+        return (cache.float() - meta[..., 1:2].float()) * meta[..., 0:1].float()
+    kd, vd = deq(k_cache, k_meta), deq(v_cache, v_meta)
+    kc = kd.permute(0, 2, 1, 3).reshape(-1, Hkv, D)[slots_t.long()]
+    vc = vd.permute(0, 2, 1, 3).reshape(-1, Hkv, D)[slots_t.long()]
+    for got, want in ((kc, k_new), (vc, v_new)):
+        step = (want.amax(-1) - want.amin(-1)) / 255.0
+        assert ((got - want).abs() <= 0.75 * step.unsqueeze(-1) + 1e-3).all()
+
+    out = ops.paged_attention(qkv, k_cache, v_cache, pl_t, sb_t, bi_t, bib_t, Hq, Hkv, D, scale=1.0 / math.sqrt(D),
+                              max_context_len=max(p + q for p, q in zip(past_lens, q_lens)), max_q_len=max(q_lens), k_meta=k_meta, v_meta=v_meta)
+    ops.check_status("paged_attention u8")
+    k_all, v_all = [], []
+    for b in range(B):
+        blocks = bi_t[bib_t[b]:bib_t[b + 1]].long()
+        ctx = past_lens[b] + q_lens[b]
+        k_all.append(kd[blocks].permute(0, 2, 1, 3).reshape(-1, Hkv, D)[:ctx])
+        v_all.append(vd[blocks].permute(0, 2, 1, 3).reshape(-1, Hkv, D)[:ctx])
+    ref = _attn_ref(qkv[:, : Hq * D].float().reshape(T, Hq, D), k_all, v_all, q_lens, past_lens, Hq, Hkv, D, 1 / math.sqrt(D))
+    assert _rel_err(out.reshape(T, Hq, D), ref) < 1e-2
+
+
 def test_paged_attention_sliding_window(ops):
     torch.manual_seed(7)
     Hq, Hkv, D, bs = 8, 2, 128, 16

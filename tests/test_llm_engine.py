@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("fmt", ["bf16", "int4", "moe", "moe-gather"])
+@pytest.mark.parametrize("fmt", ["bf16", "int4", "moe", "moe-gather", "bf16-u8kv"])
 def test_tiny_llama_generate_matches_reference(fmt, monkeypatch):
     from openvino_b200.genai.pipeline import ContinuousBatchingPipeline, GenerationConfig
     from openvino_b200.genai.scheduler import SchedulerConfig
@@ -18,11 +18,12 @@ def test_tiny_llama_generate_matches_reference(fmt, monkeypatch):
         # prefill batches take the path that runs every expert on its own (gathered) tokens only
         from openvino_b200.runtime import cuda_llm
         monkeypatch.setattr(cuda_llm, "MOE_GATHER_MIN_TOKENS", 8)
-    cfg = TINY_MOE if fmt.startswith("moe") else TINY_LLAMA.with_(weight_format=fmt)
+    cfg = TINY_MOE if fmt.startswith("moe") else TINY_LLAMA.with_(weight_format=fmt.split("-")[0])
     state = llama.random_float_state(cfg, seed=3, std=0.05)
     eff = {k: v.cuda() for k, v in llama.effective_state(cfg, state).items()}
     w = LlmWeights.from_float(cfg, state, "cuda")
-    ex = CudaLlmExecutor(cfg, w, num_kv_blocks=64, max_batch_tokens=256, max_seqs=4)
+    # "-u8kv": KV_CACHE_PRECISION = u8 (rows quantised per token and head by the cache-write kernel)
+    ex = CudaLlmExecutor(cfg, w, num_kv_blocks=64, max_batch_tokens=256, max_seqs=4, kv_cache_precision="u8" if fmt.endswith("u8kv") else "bf16")
     sc = SchedulerConfig(max_num_batched_tokens=48, max_num_seqs=4, num_kv_blocks=64)   # forces chunked prefill
     pipe = ContinuousBatchingPipeline(ex, sc)
     g = torch.Generator().manual_seed(0)
