@@ -26,11 +26,12 @@ from .preprocess import Layout, layout_helpers   # noqa: F401
 from .frontend import FrontEndManager, convert_model, read_model, save_model, serialize   # noqa: F401
 from .runtime.core import (AsyncInferQueue, CompiledModel, Core, InferRequest, OVDict, ProfilingInfo, VariableState, Version,   # noqa: F401
                            __version__, compile_model)
+from .utils.shutdown import register_shutdown_callback, shutdown, unregister_shutdown_callback   # noqa: F401
 
 __all__ = ["AsyncInferQueue", "CompiledModel", "Core", "Dimension", "FrontEndManager", "InferRequest", "Input", "Layout", "Model", "Node",
            "OVDict", "Output", "PartialShape", "ProfilingInfo", "RTMap", "Shape", "Tensor", "Type", "VariableState", "Version", "compile_model",
-           "convert_model", "get_element_type", "layout_helpers", "opset", "passes", "preprocess", "properties", "read_model", "save_model",
-           "serialize"]
+           "convert_model", "get_element_type", "layout_helpers", "opset", "passes", "preprocess", "properties", "read_model", "register_shutdown_callback",
+           "save_model", "serialize", "shutdown", "unregister_shutdown_callback"]
 
 
 def get_version() -> str:

@@ -201,7 +201,7 @@ def build_native_test(test_source: Path, sanitize: str = "", force: bool = False
 
 def kernel_resources(stem: str) -> dict:
     """Per-kernel resource usage parsed from the ptxas report of ``csrc/cuda/<stem>.cu``:
-    ``{mangled name: {"registers", "stack", "spill_stores", "spill_loads"}}`` (empty when no report exists)."""
+    ``{mangled name: {"registers", "stack", "spill_stores", "spill_loads", "static_smem"}}`` (empty when no report exists)."""
     import re
     path = OBJ / (stem + ".ptxas.txt")
     if not path.exists():
@@ -209,8 +209,13 @@ def kernel_resources(stem: str) -> dict:
     out = {}
     pat = re.compile(r"Compiling entry function '(\S+)' for 'sm_100a'.*?(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads"
                      r".*?Used (\d+) registers", re.S)
-    for m in pat.finditer(path.read_text()):
-        out[m.group(1)] = {"stack": int(m.group(2)), "spill_stores": int(m.group(3)), "spill_loads": int(m.group(4)), "registers": int(m.group(5))}
+    text = path.read_text()
+    for m in pat.finditer(text):
+        line_end = text.find("\n", m.end())
+        used = text[m.end():line_end if line_end >= 0 else len(text)]
+        smem = re.search(r"(\d+) bytes smem", used)
+        out[m.group(1)] = {"stack": int(m.group(2)), "spill_stores": int(m.group(3)), "spill_loads": int(m.group(4)), "registers": int(m.group(5)),
+                           "static_smem": int(smem.group(1)) if smem else 0}
     return out
 
 

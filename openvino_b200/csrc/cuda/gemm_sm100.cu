@@ -303,13 +303,13 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // CTAs post them. The tile CTAs store their partial, post and leave, so the tensor pipe never waits for the switch.
     const int cta = (int)blockIdx.x - p.nvls_reducers;   // tile index of this CTA (negative: a reducer)
     if (cta < 0) {
-        __shared__ int red_wait_s;
+        volatile int* red_wait_s = last_flag;     // a word of the dynamic shared memory (no static shared memory in this kernel: it uses the whole opt-in limit)
         pdl_wait();
         const int epoch = __ldcg(p.epoch);
         const int R = p.nvls_reducers, tiles = (int)gridDim.x - R;
         bool ok = true;
         for (int rt = (int)blockIdx.x; rt < tiles && ok; rt += R)
-            ok = nvls_reduce_tile<BT>(p, rt, epoch, (int)threadIdx.x, (int)blockDim.x, 2, &red_wait_s, nullptr);
+            ok = nvls_reduce_tile<BT>(p, rt, epoch, (int)threadIdx.x, (int)blockDim.x, 2, red_wait_s, nullptr);
         // completion: the last reducer of this rank meets the other ranks' last reducers (words 8..15 of tile 0's flags), so
         // when the kernel ends on a rank every share of every tile has landed in its `out`
         __syncthreads();

@@ -120,6 +120,11 @@ class PeerCommunicator:
             self._setup_ipc(lib)
         self._bump = self.layout.tensors_off
         dist.barrier(group=self.group)
+        # peer mappings are released before the CUDA context goes away at interpreter exit (or at openvino_b200.shutdown())
+        import weakref
+        from ..utils.shutdown import register_shutdown_callback
+        ref = weakref.ref(self)
+        register_shutdown_callback(lambda: ref() and ref().close(), "PeerCommunicator.close")
 
     def _setup_symmetric(self) -> None:
         import torch.distributed as dist

@@ -451,6 +451,13 @@ class _BatchCollector:
         self.num_batched_runs = 0
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
+        self._register_shutdown()
+
+    def _register_shutdown(self) -> None:
+        import weakref
+        from ..utils.shutdown import register_shutdown_callback
+        ref = weakref.ref(self)
+        register_shutdown_callback(lambda: ref() and ref().close(), "BATCH collector thread")
 
     def submit(self, ins: List[Tensor]) -> List[Tensor]:
         item = {"ins": ins, "done": threading.Event(), "outs": None, "err": None}

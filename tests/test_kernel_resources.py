@@ -30,3 +30,8 @@ def test_decode_variants_fit_two_ctas_per_sm(gemm):
     # decode-sized quantised tiles run two CTAs of 352 threads per SM: at most 65536 / 704 = 93 registers per thread
     small = [r for n, r in gemm.items() if r["registers"] <= 93]
     assert len(small) >= 9                     # u4 / u8 / fp8 at 16, 32 and 64 tokens
+
+
+def test_gemm_uses_no_static_shared_memory(gemm):
+    # the kernel opts in to the whole dynamic shared-memory limit of the SM: one static __shared__ word makes the opt-in fail
+    assert all(r["static_smem"] == 0 for r in gemm.values()), {n: r["static_smem"] for n, r in gemm.items() if r["static_smem"]}

@@ -448,3 +448,20 @@ def test_auto_batching(core):
     # a lone request is served after the timeout
     np.testing.assert_allclose(cm(xs[0])[0], ref(xs[0]), rtol=1e-4, atol=1e-4)
     assert cm.collector.num_batched_runs == 2
+
+
+def test_shutdown_runs_callbacks_in_reverse_order_once(core):
+    order = []
+    h1 = ov.register_shutdown_callback(lambda: order.append("first"), "first")
+    ov.register_shutdown_callback(lambda: (_ for _ in ()).throw(RuntimeError("boom")), "failing")
+    ov.register_shutdown_callback(lambda: order.append("last"), "last")
+    h4 = ov.register_shutdown_callback(lambda: order.append("removed"), "removed")
+    assert ov.unregister_shutdown_callback(h4) and not ov.unregister_shutdown_callback(h4)
+    cm = core.compile_model(mlp(), "BATCH:CPU(2)", {props.auto_batch_timeout: 50})     # owns a collector thread
+    thread = cm.collector.thread
+    assert thread.is_alive()
+    ran = ov.shutdown()
+    assert order == ["last", "first"] and "failing" in ran and "BATCH collector thread" in ran
+    thread.join(timeout=5)
+    assert not thread.is_alive()
+    assert ov.shutdown() == [] and h1 > 0
