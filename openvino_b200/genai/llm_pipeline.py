@@ -36,7 +36,8 @@ class ByteTokenizer:
 class LLMPipeline:
     def __init__(self, model: Union[str, Model], device: str = "CUDA", tokenizer=None, comm=None, tp_rank: int = 0, tp_size: int = 1,
                  max_num_seqs: int = 64, max_num_batched_tokens: int = 8192, max_model_len: int = 4096, block_size: int = 16,
-                 kv_cache_blocks: int = 0):
+                 kv_cache_blocks: int = 0, **properties):
+        """``properties``: further device properties for ``compile_model`` (e.g. ``KV_CACHE_PRECISION="u8"``)."""
         if device.split(".")[0] not in ("CUDA", "GPU"):
             raise RuntimeError("LLMPipeline runs on the CUDA device; use compile_model for '%s'" % device)
         if not isinstance(model, Model):
@@ -54,6 +55,7 @@ class LLMPipeline:
             mgr.run_passes(model)
         dev_index = int(device.split(".")[1]) if "." in device else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
         config = {props.cuda.serving_program: True}
+        config.update(properties)
         if tp_size > 1:
             config[props.hint.model_distribution_policy] = "TENSOR_PARALLEL"
         self.compiled_model = Core().compile_model(model, "CUDA.%d" % dev_index, config)

@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from .. import opset as ops
-from .._graph import Model, Node, Output, constant, parameter, result
+from .._graph import make_op, Model, Node, Output, constant, parameter, result
 from .._tensor import Tensor
 from .._types import PartialShape, Type
 from ..utils import quant
@@ -211,6 +211,22 @@ def build_llama(cfg: LlmConfig, state: Dict[str, torch.Tensor], compress: Option
         h = ops.add(h, proj("self_attn.o_proj", a, "o_proj")).output(0)
 
         x = _rms(h, _f32(state[p + "post_attention_layernorm"]), cfg.rms_eps, n + "post_attention_layernorm")
+        if cfg.num_experts:
+            # mixture of experts: router -> softmax -> top-k -> renormalise -> MOE (batched expert weights [E, F, H] / [E, H, F])
+            E, k = cfg.num_experts, cfg.experts_top_k
+            router = ops.matmul(x, constant(_f32(state[p + "router"]), name=n + "block_sparse_moe.gate.weight"), False, True,
+                                name=n + "block_sparse_moe.gate")
+            probs = ops.softmax(router, -1)
+            top = ops.topk(probs, _i64(k), -1, "max", "value", "i32")
+            wsum = ops.reduce_sum(top.output(0), _i64([-1]), True)
+            rw = ops.divide(top.output(0), wsum)
+
+            def stack(key):
+                return constant(np.stack([_f32(state[p + "experts.%d.%s" % (e, key)]) for e in range(E)]), name=n + "block_sparse_moe.experts." + key)
+            moe = make_op("MOE", [x, rw.output(0), top.output(1), stack("gate_proj").output(0), stack("up_proj").output(0), stack("down_proj").output(0)],
+                          {"expert_type": "GEMM3_SWIGLU", "activation_type": "SWISH"}, "internal", n + "block_sparse_moe")
+            h = ops.add(h, moe.output(0)).output(0)
+            continue
         gate = ops.swish(proj("mlp.gate_proj", x, "gate_proj"))
         up = proj("mlp.up_proj", x, "up_proj")
         h = ops.add(h, proj("mlp.down_proj", ops.multiply(gate, up), "down_proj")).output(0)

@@ -1276,12 +1276,56 @@ class CudaCompiledModel(CompiledModel):
                 x = x.to(self.precision)
             return x
 
+        # CUDA graphs for static graphs: the second inference of a request with the same input shapes captures the whole
+        # program (every kernel launch of the interpreter walk) into one graph; later inferences copy the inputs into the
+        # captured buffers and replay it, so the per-node host work (dispatch, tensor-map encoding, allocation) is paid once.
+        # Not for models with states or cross-rank collectives, nor while profiling; a program that reads a device value on
+        # the host (data-dependent shapes) cannot be captured and stays in eager mode.
+        graphs_on = (stream is not None and not profile_on and bool(self.config.get(props.cuda.use_cuda_graphs, True))
+                     and not any(n.get_type_name() in ("ReadValue", "Assign", "AllReduce", "PagedAttentionExtension") for n in self.runtime_model.get_ops()))
+        graph_cache: Dict[tuple, object] = {}
+        request._cuda_graphs = graph_cache
+
+        def run_graphed(xs: List[torch.Tensor]):
+            key = tuple((tuple(x.shape), x.dtype) for x in xs)
+            entry = graph_cache.get(key)
+            if entry is None:                       # first call: eager (warms up workspaces and one-time kernel set-up)
+                graph_cache[key] = "warm"
+                return program.run(xs, None)
+            if entry == "eager":
+                return program.run(xs, None)
+            if entry == "warm":
+                static_in = [torch.empty_like(x) for x in xs]
+                for s_, x in zip(static_in, xs):
+                    s_.copy_(x)
+                g = torch.cuda.CUDAGraph()
+                try:
+                    stream.synchronize()
+                    with torch.cuda.graph(g, stream=stream):
+                        static_out = program.run(static_in, None)
+                    entry = (g, static_in, static_out)
+                except Exception as e:   # noqa: BLE001 - a host read inside the walk: this shape stays eager
+                    from ..utils import log
+                    log.debug("cuda", "graph capture failed, staying eager: %s" % str(e)[:200])
+                    torch.cuda.synchronize(dev)
+                    graph_cache[key] = "eager"
+                    return program.run(xs, None)
+                graph_cache[key] = entry
+                g.replay()
+                return list(entry[2])
+            g, static_in, static_out = entry
+            for s_, x in zip(static_in, xs):
+                s_.copy_(x, non_blocking=True)
+            g.replay()
+            return list(static_out)
+
         def run(req: InferRequest, ins: List[Tensor]) -> List[Tensor]:
             prof = [] if profile_on else None
             program.ctx.variables = ctx_vars
             if stream is not None:
                 with torch.cuda.stream(stream):
-                    outs = program.run([to_device(t) for t in ins], prof)
+                    xs = [to_device(t) for t in ins]
+                    outs = run_graphed(xs) if graphs_on else program.run(xs, prof)
                     res = self._finish(outs, req)
                 stream.synchronize()
             else:

@@ -204,6 +204,7 @@ def analyze(model: Model) -> Tuple[LlmConfig, Dict]:
         raise NotAnLlm("no attention operation found")
     lin: Dict[Tuple[int, str], _Linear] = {}
     norms: Dict[Tuple[int, str], torch.Tensor] = {}
+    experts: Dict[int, Dict] = {}
     eps = 1e-6
     last_add = first_norm = None
     for l, a in enumerate(att):
@@ -219,6 +220,36 @@ def analyze(model: Model) -> Tuple[LlmConfig, Dict]:
         add1 = _one([c for c in _consumers(o) if c.get_type_name() == "Add"], "residual Add after the attention output projection")
         n2 = _one([c for c in _consumers(add1) if c.get_type_name() == "RMS"], "RMS after the attention residual")
         mlp = [c for c in _consumers(n2) if c.get_type_name() in _FC]
+        moe = [c for c in _consumers(n2) if c.get_type_name() == "MOE"]
+        if moe:
+            # mixture of experts: the RMS output feeds the router projection (as many rows as experts) and the MOE operation,
+            # whose routing weights / expert indices come from the router through softmax and top-k
+            mo = _one(moe, "MOE operation")
+            if mo.get_attribute("expert_type") != "GEMM3_SWIGLU":
+                raise NotAnLlm("layer %d: expert type %s is not served" % (l, mo.get_attribute("expert_type")))
+            ew = []
+            for i in (3, 4, 5):
+                c = mo.input_value(i).get_node()
+                if c.get_type_name() == "Convert":
+                    c = c.input_value(0).get_node()
+                if c.get_type_name() != "Constant":
+                    raise NotAnLlm("layer %d: the expert weights are not constants" % l)
+                ew.append(_const_f32(c))
+            n_exp = ew[0].shape[0]
+            router = _one([c for c in mlp if _Linear(c).N == n_exp], "router projection")
+            idx_shape = mo.input_value(2).get_partial_shape()
+            top_k = int(idx_shape[idx_shape.rank.get_length() - 1].get_length())
+            add2 = _one([c for c in _consumers(mo) if c.get_type_name() == "Add"], "residual Add after the experts")
+            for key, node in (("q_proj", q), ("k_proj", k), ("v_proj", v), ("o_proj", o), ("router", router)):
+                lin[(l, key)] = _Linear(node)
+            experts[l] = {"gate": ew[0], "up": ew[1], "down": ew[2], "top_k": top_k}
+            norms[(l, "input_layernorm")] = _gamma(n1)
+            norms[(l, "post_attention_layernorm")] = _gamma(n2)
+            eps = float(n1.get_attribute("epsilon"))
+            if l == 0:
+                first_norm = n1
+            last_add = add2
+            continue
         gates = [c for c in mlp if any(x.get_type_name() == "Swish" for x in _consumers(c))]
         ups = [c for c in mlp if c not in gates]
         if len(gates) != 1 or len(ups) != 1:
@@ -274,9 +305,12 @@ def analyze(model: Model) -> Tuple[LlmConfig, Dict]:
     first = lin[(layers[0], "q_proj")]
     fmt = {"u4": "int4", "u8": "int8"}[first.kind] if first.compressed else "bf16"
     cfg = LlmConfig(name=model.get_friendly_name() or "llm", vocab_size=embed.shape[0], hidden_size=H, num_layers=len(layers), num_heads=Hq,
-                    num_kv_heads=Hkv, head_dim=D, ffn_size=lin[(layers[0], "gate_proj")].N, rope_theta=theta, rms_eps=eps,
-                    weight_format=fmt, group_size=(first.K // first.G) if first.compressed else 128)
-    return cfg, {"lin": lin, "norms": norms, "lm_head": lm_head, "final_norm": final_norm, "embed": embed, "layers": layers}
+                    num_kv_heads=Hkv, head_dim=D, ffn_size=experts[0]["gate"].shape[1] if experts else lin[(layers[0], "gate_proj")].N,
+                    rope_theta=theta, rms_eps=eps, weight_format=fmt, group_size=(first.K // first.G) if first.compressed else 128,
+                    num_experts=experts[0]["gate"].shape[0] if experts else 0, experts_top_k=experts[0]["top_k"] if experts else 0)
+    if experts and len(experts) != len(layers):
+        raise NotAnLlm("dense and expert layers in one model are not served")
+    return cfg, {"lin": lin, "norms": norms, "lm_head": lm_head, "final_norm": final_norm, "embed": embed, "layers": layers, "experts": experts}
 
 
 def build_weights(cfg: LlmConfig, parts: Dict, device, tp_rank: int = 0, tp_size: int = 1):
@@ -292,6 +326,21 @@ def build_weights(cfg: LlmConfig, parts: Dict, device, tp_rank: int = 0, tp_size
         q = lin[(l, "q_proj")].rows(r * hq * D, (r + 1) * hq * D)
         k = lin[(l, "k_proj")].rows(r * hkv * D, (r + 1) * hkv * D)
         v = lin[(l, "v_proj")].rows(r * hkv * D, (r + 1) * hkv * D)
+        if parts.get("experts"):
+            # expert parallel: rank r holds experts [r * nloc, (r + 1) * nloc) whole; gate and up of an expert are stacked
+            # ([nloc * 2F, H]), the down projections side by side along K ([H, nloc * F]); the router is replicated
+            from ..ops import cuda as K
+            ex = parts["experts"][l]
+            nloc = cfg.num_experts // tp_size
+            local = range(r * nloc, (r + 1) * nloc)
+            gu = torch.cat([torch.cat([ex["gate"][e], ex["up"][e]], 0) for e in local], 0)
+            down = torch.cat([ex["down"][e] for e in local], 1)
+            pack16 = lambda t: K.PackedWeight.from_dense(t.to(device).to(torch.bfloat16).contiguous())
+            layers.append(LayerWeights(norm1=bf(norms[(l, "input_layernorm")]), qkv=_Linear.stack([q, k, v]).pack(device),
+                                       o=lin[(l, "o_proj")].cols(r * hq * D, (r + 1) * hq * D).pack(device),
+                                       norm2=bf(norms[(l, "post_attention_layernorm")]), gate_up=pack16(gu), down=pack16(down),
+                                       router=lin[(l, "router")].pack(device)))
+            continue
         gate = lin[(l, "gate_proj")].rows(r * ffn, (r + 1) * ffn)
         up = lin[(l, "up_proj")].rows(r * ffn, (r + 1) * ffn)
         fused_gate = ffn % 64 == 0          # silu(gate) * up in the GEMM epilogue needs the interleaved row order

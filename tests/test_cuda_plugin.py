@@ -63,6 +63,35 @@ def test_bert_fp16_uses_own_kernels(core):
     assert any(p.node_type == "FullyConnected" for p in prof) and all(p.exec_type == "cuda" for p in prof)
 
 
+def test_static_graphs_replay_a_cuda_graph(core):
+    """The third inference of a request with unchanged shapes replays a captured CUDA graph; results equal the eager walk,
+    new input values are picked up, and another batch size gets a graph of its own."""
+    torch.manual_seed(1)
+    net = ResNet18(num_classes=10, width=16).eval()
+    x1, x2 = torch.randn(2, 3, 64, 64), torch.randn(2, 3, 64, 64)
+    with torch.no_grad():
+        want1, want2 = net(x1).numpy(), net(x2).numpy()
+    m = ov.convert_model(net, example_input=(x1,), input=[[-1, 3, 64, 64]])
+    req = core.compile_model(m, "CUDA").create_infer_request()
+    eager = req.infer([x1.numpy()])[0].copy()                          # first call: eager warm-up
+    captured = req.infer([x1.numpy()])[0].copy()                       # second: capture + replay
+    replayed = req.infer([x2.numpy()])[0].copy()                       # third: replay with new data
+    assert rel(eager, want1) < 1e-3 and np.array_equal(eager, captured) and rel(replayed, want2) < 1e-3
+    entries = list(req._cuda_graphs.values())
+    assert len(entries) == 1 and isinstance(entries[0], tuple), entries
+    x3 = torch.randn(5, 3, 64, 64)
+    for _ in range(3):
+        out3 = req.infer([x3.numpy()])[0]
+    with torch.no_grad():
+        assert rel(out3, net(x3).numpy()) < 1e-3
+    assert sum(isinstance(e, tuple) for e in req._cuda_graphs.values()) == 2
+    # switched off by the property
+    req_off = core.compile_model(m, "CUDA", {props.cuda.use_cuda_graphs: False}).create_infer_request()
+    for _ in range(3):
+        out_off = req_off.infer([x1.numpy()])[0]
+    assert not req_off._cuda_graphs and rel(out_off, want1) < 1e-3
+
+
 def test_stateful_llm_int4_on_device(core):
     cfg = TINY_LLAMA.with_(vocab_size=256, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=128, ffn_size=512, group_size=128)
     state = llama.random_float_state(cfg, seed=2, std=0.05)
@@ -149,3 +178,25 @@ def test_llm_pipeline_from_ir_directory(tmp_path):
             assert row[tok] >= row.max() - 0.05 * row.abs().max()
     text = pipe.generate("hi", max_new_tokens=3)
     assert isinstance(text, str)
+
+
+def test_mixture_of_experts_ir_runs_on_the_serving_program(tmp_path):
+    """A decoder with MOE layers, saved as IR: recognised by structure, experts run through the grouped GEMM; the
+    KV_CACHE_PRECISION property selects the u8 cache of the serving program."""
+    from openvino_b200.genai import ByteTokenizer, GenerationConfig, LLMPipeline
+    from openvino_b200.models.llm_config import TINY_MOE
+    cfg = TINY_MOE.with_(vocab_size=320)
+    state = llama.random_float_state(cfg, seed=11, std=0.05)
+    ov.save_model(build_llama(cfg, state), str(tmp_path / "openvino_model.xml"), compress_to_fp16=False)
+    eff = llama.effective_state(cfg, state)
+    prompts = [[5, 17, 200, 31, 8, 9, 1, 44, 90], [300, 2, 2, 9]]
+    for extra in ({}, {props.hint.kv_cache_precision: "u8"}):
+        pipe = LLMPipeline(str(tmp_path), "CUDA", tokenizer=ByteTokenizer(), max_num_seqs=4, max_num_batched_tokens=256, max_model_len=128, **extra)
+        assert (pipe.config.num_experts, pipe.config.experts_top_k) == (cfg.num_experts, cfg.experts_top_k)
+        outs = pipe.generate(prompts, GenerationConfig(max_new_tokens=5))
+        for p, o in zip(prompts, outs):
+            seq = p + o
+            logits = llama.reference_logits(cfg, eff, torch.tensor(seq[:-1]))
+            for i, tok in enumerate(o):
+                row = logits[len(p) - 1 + i]
+                assert row[tok] >= row.max() - 0.05 * row.abs().max()

@@ -6,7 +6,7 @@ import torch
 import openvino_b200 as ov
 from openvino_b200 import passes
 from openvino_b200.models import llama
-from openvino_b200.models.llm_config import TINY_LLAMA
+from openvino_b200.models.llm_config import TINY_LLAMA, TINY_MOE
 from openvino_b200.models.ov_builders import build_llama, build_llama_random_int4
 from openvino_b200.runtime import llm_import
 
@@ -50,6 +50,35 @@ def test_renamed_graph_is_still_recognised(compress, paged, tmp_path):
         assert torch.allclose(parts["final_norm"], state["norm"].float()) and torch.allclose(parts["embed"], state["embed_tokens"].float(), atol=1e-6)
     else:
         assert parts["lin"][(0, "q_proj")].compressed and parts["lin"][(1, "down_proj")].G == 512 // 128
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_mixture_of_experts_decoder_is_recognised_by_structure(paged, tmp_path):
+    """Router projection -> softmax -> top-k -> MOE: the experts, their number and the top-k come from the graph."""
+    cfg = TINY_MOE.with_(vocab_size=320)
+    state = llama.random_float_state(cfg, seed=9, std=0.05)
+    m = build_llama(cfg, state)
+    assert sum(1 for n in m.get_ops() if n.get_type_name() == "MOE") == cfg.num_layers
+    # the graph computes what the reference model computes
+    ids = np.array([[5, 9, 200, 17, 3]], dtype=np.int64)
+    feed = {"input_ids": ids, "attention_mask": np.ones_like(ids), "position_ids": np.arange(5, dtype=np.int64)[None], "beam_idx": np.zeros(1, np.int32)}
+    logits = ov.Core().compile_model(m, "CPU")(feed)[0]
+    eff = llama.effective_state(cfg, state)
+    want = llama.reference_logits(cfg, eff, torch.tensor(ids[0])).numpy()
+    assert np.abs(logits[0] - want).max() < 1e-2 * np.abs(want).max()      # the reference model rounds its weights to bf16
+    if paged:
+        _to_paged(m)
+    for i, n in enumerate(m.get_ops()):
+        if n.get_type_name() not in ("Parameter", "Result"):
+            n.set_friendly_name("op_%d" % i)
+    ov.save_model(m, str(tmp_path / "moe.xml"), compress_to_fp16=False)
+    got, parts = llm_import.analyze(ov.Core().read_model(str(tmp_path / "moe.xml")))
+    assert (got.num_experts, got.experts_top_k, got.ffn_size, got.num_layers) == (cfg.num_experts, cfg.experts_top_k, cfg.ffn_size, cfg.num_layers)
+    for l in range(cfg.num_layers):
+        assert torch.allclose(parts["lin"][(l, "router")].w, state["layers.%d.router" % l].float(), atol=1e-6)
+        for e in range(cfg.num_experts):
+            for key, role in (("gate_proj", "gate"), ("up_proj", "up"), ("down_proj", "down")):
+                assert torch.allclose(parts["experts"][l][role][e], state["layers.%d.experts.%d.%s" % (l, e, key)].float(), atol=1e-6)
 
 
 def test_graphs_that_are_not_decoders_are_refused():
