@@ -14,6 +14,7 @@ namespace ovc {
 void register_eval_functions();
 // More operations, registered together with their reference evaluation (ops_ext.cpp)
 void register_ext_ops();
+void register_internal_ops();
 
 namespace {
 
@@ -1127,6 +1128,7 @@ void register_all_ops() {
 
         register_eval_functions();
         register_ext_ops();
+        register_internal_ops();
     });
 }
 

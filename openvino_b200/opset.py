@@ -21,6 +21,10 @@ from ._types import PartialShape, Type
 
 _SPEC = """
 identity Identity : data
+extract_image_patches ExtractImagePatches : image | sizes strides rates auto_pad=valid
+region_yolo RegionYolo : input | coords classes num>num do_softmax mask axis end_axis anchors=[]
+ctc_loss CTCLoss : logits logit_length labels label_length [blank_index] | preprocess_collapse_repeated=False ctc_merge_repeated=True unique=False
+stft STFT : data window frame_size frame_step | transpose_frames=False
 erfinv ErfInv : x
 bitwise_left_shift BitwiseLeftShift : a b | auto_broadcast=numpy
 bitwise_right_shift BitwiseRightShift : a b | auto_broadcast=numpy

@@ -46,6 +46,7 @@ def main() -> int:
     link_gbs = 770.0
 
     calls = [0]
+    failures = []
 
     def timed(fn):
         for _ in range(a.warmup):
@@ -92,6 +93,22 @@ def main() -> int:
             hv.add_(tmp)
         nccl_ms = timed(unfused)
         gemm_ms = timed(lambda: K.gemm(x, pw, out=tmp, ws=ws))
+        # numerics of the fused launch (it also covers the multi-wave paths that only large T reaches): the sum over the ranks
+        # against GEMM + fp32 all-reduce, and the same bits on every rank
+        hv.zero_()
+        comm.step_begin()
+        fused()
+        K.check_status("fused gemm + all-reduce, verification")
+        ref = K.gemm(x, pw, out_f32=True, ws=ws)
+        dist.all_reduce(ref)
+        got = hv.float()
+        err = float((got - ref).norm() / ref.norm().clamp_min(1e-20))
+        digest = torch.stack([got.double().sum(), got.double().abs().sum(), (got.double() * torch.arange(got.numel(), device=dev, dtype=torch.float64).reshape(got.shape) % 7).sum()])
+        digests = [torch.empty_like(digest) for _ in range(world)]
+        dist.all_gather(digests, digest)
+        identical = all(bool(torch.equal(d, digests[0])) for d in digests)
+        if err > 2e-2 or not identical:
+            failures.append((T, Kd, err, identical))
         flops = 2.0 * T * H * Kd
         wbytes = H * Kd // 2 + (H * Kd // 128) * 4
         tile_bytes = T * H * 2
@@ -108,12 +125,15 @@ def main() -> int:
             print(json.dumps({"kernel": "gemm_u4 + all-reduce (fused epilogue)", "n_gpus": world, "T": T, "N": H, "K_per_rank": Kd,
                               "mode": "in-switch (NVLS)" if comm.mc_ptr else ("one-shot" if T <= 128 else "two-shot"), "fused_ms": fused_ms, "gemm_then_nccl_ms": nccl_ms, "gemm_only_ms": gemm_ms,
                               "roofline_ms": roof, "bound": ["compute", "hbm", "nvlink"][[t_compute, t_hbm, t_link].index(roof)],
-                              "fraction_of_roofline": roof / fused_ms, "peaks": pk["source"],
+                              "fraction_of_roofline": roof / fused_ms, "peaks": pk["source"], "rel_err_vs_fp32_allreduce": err, "ranks_identical": identical,
                               "nvlink_gbs_achieved": sent / fused_ms / 1e6}), flush=True)
     torch.cuda.synchronize()
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
+    if failures:
+        print("FUSED_ALLREDUCE_MISMATCH", failures, flush=True)
+        return 1
     return 0
 
 

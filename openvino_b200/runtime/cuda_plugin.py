@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import math
 import os
+import threading
 from typing import Callable, Dict, List, Optional, Sequence
 
 import numpy as np
@@ -1240,6 +1241,9 @@ class RemoteContext:
         return {"CONTEXT_TYPE": "CUDA", "DEVICE_ID": str(self.device.index or 0)}
 
 
+_CAPTURE_LOCK = threading.Lock()
+
+
 class CudaCompiledModel(CompiledModel):
     def __init__(self, plugin, model, config, runtime_model, device: torch.device, precision):
         super().__init__(plugin, model, config, runtime_model)
@@ -1301,13 +1305,18 @@ class CudaCompiledModel(CompiledModel):
                 g = torch.cuda.CUDAGraph()
                 try:
                     stream.synchronize()
-                    with torch.cuda.graph(g, stream=stream):
+                    # one capture at a time in the process; "thread_local" keeps the calls of other requests' threads
+                    # (allocations, launches on their own streams) legal while this thread captures
+                    with _CAPTURE_LOCK, torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
                         static_out = program.run(static_in, None)
                     entry = (g, static_in, static_out)
                 except Exception as e:   # noqa: BLE001 - a host read inside the walk: this shape stays eager
                     from ..utils import log
                     log.debug("cuda", "graph capture failed, staying eager: %s" % str(e)[:200])
-                    torch.cuda.synchronize(dev)
+                    try:
+                        stream.synchronize()
+                    except Exception:   # noqa: BLE001 - the failed capture may surface once more here
+                        pass
                     graph_cache[key] = "eager"
                     return program.run(xs, None)
                 graph_cache[key] = entry

@@ -72,3 +72,20 @@ def test_tensor_parallel_in_switch_reduction(world):
 @pytest.mark.parametrize("world", [4, 8])
 def test_tensor_parallel_peer_stores_beyond_two_gpus(world):
     _run_tp_worker(world, False, 29682 + world)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,env", [(2, {"OVB_NVLS": "0", "NCCL_NVLS_ENABLE": "0"}), (2, {"OVB_COMM_NVLS_MODES": "3"}), (8, {})])
+def test_fused_gemm_all_reduce_at_serving_shapes(world, env):
+    """The fused GEMM + all-reduce at the shapes of an 8B model (T = 64 and T = 8192, more tiles than one wave of CTAs, so
+    the reducer CTAs and the two-shot owners take part): sum over the ranks against GEMM + fp32 all-reduce, and the same
+    bits on every rank. The benchmark module verifies every shape it times and exits non-zero on a mismatch."""
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+                        "--master-port", str(29690 + world), "-m", "openvino_b200.parallel.bench_fused", "--iters", "3", "--warmup", "1"],
+                       capture_output=True, text=True, timeout=900, env=dict(os.environ, **env))
+    assert r.returncode == 0 and "FUSED_ALLREDUCE_MISMATCH" not in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
+    import json
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(rows) >= 3 and all(x["ranks_identical"] and x["rel_err_vs_fp32_allreduce"] < 2e-2 for x in rows)
