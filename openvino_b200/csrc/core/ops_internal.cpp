@@ -232,6 +232,34 @@ void register_internal_ops() {
             return moe->eval(n, ins, out, ctx);
         }, 12, 12);
 
+    // ---- LoraSubgraph (flat form): main_flow + ((x @ A^T) * alpha) @ B^T; A [r, in], alpha [1, r] or scalar, B [out, r]
+    reg("LoraSubgraph", "ie_internal_opset", {},
+        [](Node& n) { n.set_output(0, n.in_et(0), n.in_shape(0)); },
+        [](N n, Ins in, Outs out, C) {
+            const Tensor &M = in[0], &X = in[1], &Aw = in[2], &Al = in[3], &Bw = in[4];
+            OVC_CHECK(Aw.shape.size() == 2 && Bw.shape.size() == 2, n.description() << ": the adapter matrices are 2-D");
+            const int64_t r = Aw.shape[0], din = Aw.shape[1], dout = Bw.shape[0];
+            OVC_CHECK(X.shape.back() == din && Bw.shape[1] == r && M.shape.back() == dout, n.description() << ": adapter shapes do not fit the projection");
+            const int64_t rows = X.numel() / std::max<int64_t>(din, 1);
+            auto o = to_f32(M);
+            const auto x = to_f32(X), a = to_f32(Aw), al = to_f32(Al), b = to_f32(Bw);
+            std::vector<float> t((size_t)r);
+            for (int64_t i = 0; i < rows; ++i) {
+                for (int64_t k = 0; k < r; ++k) {
+                    float acc = 0;
+                    for (int64_t d = 0; d < din; ++d) acc += x[(size_t)(i * din + d)] * a[(size_t)(k * din + d)];
+                    t[(size_t)k] = acc * (al.size() == 1 ? al[0] : al[(size_t)(k % (int64_t)al.size())]);
+                }
+                for (int64_t j = 0; j < dout; ++j) {
+                    float acc = 0;
+                    for (int64_t k = 0; k < r; ++k) acc += t[(size_t)k] * b[(size_t)(j * r + k)];
+                    o[(size_t)(i * dout + j)] += acc;
+                }
+            }
+            out[0] = from_f32(M.et, M.shape, o);
+            return true;
+        }, 5, 5);
+
     // ---- ExtractImagePatches: [B, C, H, W] -> [B, C * kh * kw, OH, OW], channel = (kh * KW + kw) * C + c
     reg("ExtractImagePatches", "opset3", {Ais("sizes"), Ais("strides"), Ais("rates"), As("auto_pad", "valid")},
         [](Node& n) {

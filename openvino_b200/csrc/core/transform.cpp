@@ -435,6 +435,9 @@ static bool convert_precision(const ModelPtr& m, ET from, ET to) {
 // forward declarations of the LLM passes (transform_llm.cpp)
 std::shared_ptr<MatcherPass> make_rms_fusion();
 std::shared_ptr<MatcherPass> make_rope_fusion();
+std::shared_ptr<MatcherPass> make_rope_fusion_interleaved();
+std::shared_ptr<MatcherPass> make_rope_fusion_partial();
+std::shared_ptr<MatcherPass> make_lora_fusion();
 std::shared_ptr<MatcherPass> make_matmul_to_fc();
 std::shared_ptr<MatcherPass> make_fc_to_compressed();
 std::shared_ptr<MatcherPass> make_swiglu_fusion();
@@ -459,7 +462,15 @@ std::shared_ptr<ModelPass> make_pass(const std::string& name, const AttrMap& opt
     if (name == "CompressWeights") { const std::string mode = opt_s("mode", "int4_asym"); const int64_t gs = opt_i("group_size", 128); const bool all = opt_i("all_layers", 0) != 0;
         return lam([mode, gs, all](const ModelPtr& m) { return compress_weights(m, mode, gs, 1.0, all); }); }
     if (name == "RMSFusion") return wrap(make_rms_fusion());
-    if (name == "RoPEFusion") return wrap(make_rope_fusion());
+    if (name == "RoPEFusion") {     // half-rotate, interleaved, then the partial-rotary wrapper around either
+        auto g = std::make_shared<GraphRewrite>();
+        g->name = name;
+        g->add(make_rope_fusion());
+        g->add(make_rope_fusion_interleaved());
+        g->add(make_rope_fusion_partial());
+        return g;
+    }
+    if (name == "LoraSubgraphFusion") return wrap(make_lora_fusion());
     if (name == "ConvertMatMulToFullyConnected") return wrap(make_matmul_to_fc());
     if (name == "ConvertFullyConnectedToFullyConnectedCompressed") return wrap(make_fc_to_compressed());
     if (name == "GLUFusion") return wrap(make_swiglu_fusion());
@@ -474,7 +485,7 @@ std::vector<std::string> available_passes() {
     return {"ConstantFolding", "NopElimination", "BatchNormDecomposition", "Validate", "InitNodeInfo", "FusedNamesCleanup", "CompressFloatConstants",
             "ConvertFP32ToFP16", "ConvertPrecision", "StatefulToStateless", "CompressWeights", "RMSFusion", "RoPEFusion",
             "ConvertMatMulToFullyConnected", "ConvertFullyConnectedToFullyConnectedCompressed", "GLUFusion", "SDPAFusion", "FuseMOEExperts",
-            "SDPAToPagedAttention", "MOCTransformations"};
+            "SDPAToPagedAttention", "MOCTransformations", "LoraSubgraphFusion"};
 }
 
 void run_moc_transformations(const ModelPtr& m, bool cf) {

@@ -129,6 +129,110 @@ std::shared_ptr<MatcherPass> make_rope_fusion() {
     });
 }
 
+// RoPE, interleaved (GPT-J "rotate every two") form:
+//   x * cos + reshape(concat(unsqueeze(-x[..., 1::2]), unsqueeze(x[..., 0::2]), -1), shape(x)) * sin  ->  RoPE(x, cos, sin), is_interleaved
+// (fuse_rotary_positional_embeddings.cpp, RoPEFusionGPTJ, in the reference).
+std::shared_ptr<MatcherPass> make_rope_fusion_interleaved() {
+    auto x = any_input(rank_equals(4));
+    auto cos = any_input();
+    auto sin = any_input();
+    auto odd = wrap_type({"Slice"}, {x, any_input(), any_input(), any_input(), any_input()});
+    auto even = wrap_type({"Slice"}, {x, any_input(), any_input(), any_input(), any_input()});
+    auto neg = any_of({wrap_type({"Negative"}, {odd}), wrap_type({"Multiply"}, {odd, wrap_const(scalar_eq(-1.0))})});
+    auto u_neg = wrap_type({"Unsqueeze"}, {neg, any_input()});
+    auto u_even = wrap_type({"Unsqueeze"}, {even, any_input()});
+    auto cat = wrap_type({"Concat"}, {u_neg, u_even});
+    auto flat = wrap_type({"Reshape"}, {cat, any_input()});
+    auto mul_cos = wrap_type({"Multiply"}, {x, cos});
+    auto mul_sin = wrap_type({"Multiply"}, {flat, sin});
+    auto add = wrap_type({"Add"}, {mul_cos, mul_sin});
+    return std::make_shared<MatcherPass>("RoPEFusionInterleaved", add, [=](Matcher& m) {
+        const Output xin = m.at(x);
+        const PShape& xs = xin.shape();
+        if (!xs.dims[3].is_static() || xs.dims[3].lo % 2) return false;
+        const int64_t S = xs.dims[3].lo;
+        auto strided = [&](const NodePtr& sl, int64_t start) {
+            std::vector<int64_t> vb, ve, vs, va;
+            if (!get_constant_ints(sl->input(1), vb) || !get_constant_ints(sl->input(2), ve) || !get_constant_ints(sl->input(3), vs) ||
+                !get_constant_ints(sl->input(4), va)) return false;
+            return vb.size() == 1 && vb[0] == start && vs[0] == 2 && ve[0] >= S - 1 + start && (va[0] == 3 || va[0] == -1);
+        };
+        if (!strided(m.node(odd), 1) || !strided(m.node(even), 0)) return false;
+        const int64_t cat_axis = m.node(cat)->attr_int("axis");
+        if (cat_axis != -1 && cat_axis != 4) return false;
+        if (!(m.node(flat)->output(0).shape() == xs)) return false;
+        auto rope = op("RoPE", {xin, m.at(cos), m.at(sin)}, {{"is_interleaved", Attr::Bool(true)}, {"rotary_ndims", Attr::Int(S)}, {"head_size", Attr::Int(S)},
+                                                             {"head_cnt", Attr::Int(xs.dims[1].is_static() ? xs.dims[1].lo : 0)}});
+        copy_runtime_info(m.matched_nodes(), {rope});
+        replace_node(m.match_root(), rope);
+        return true;
+    });
+}
+
+// Partial rotary embedding (GPT-NeoX / Phi: only the first rotary_ndims of the head are rotated):
+//   concat(RoPE(x[..., :r], cos, sin), x[..., r:], -1)  ->  RoPE(x, cos, sin) with rotary_ndims = r
+std::shared_ptr<MatcherPass> make_rope_fusion_partial() {
+    auto x = any_input(rank_equals(4));
+    auto head = wrap_type({"Slice"}, {x, any_input(), any_input(), any_input(), any_input()});
+    auto tail = wrap_type({"Slice"}, {x, any_input(), any_input(), any_input(), any_input()});
+    auto rope_in = wrap_type({"RoPE"}, {head, any_input(), any_input()});
+    auto cat = wrap_type({"Concat"}, {rope_in, tail});
+    return std::make_shared<MatcherPass>("RoPEFusionPartial", cat, [=](Matcher& m) {
+        const Output xin = m.at(x);
+        const PShape& xs = xin.shape();
+        if (!xs.dims[3].is_static()) return false;
+        const int64_t S = xs.dims[3].lo;
+        NodePtr r = m.node(rope_in);
+        if (r->attr_bool("input_trans0213") || r->attr_bool("output_trans0213") || r->attr_int("slice_stop") > r->attr_int("slice_start")) return false;
+        const int64_t rot = r->attr_int("rotary_ndims");
+        auto range = [&](const NodePtr& sl, int64_t b, int64_t e) {
+            std::vector<int64_t> vb, ve, vs, va;
+            if (!get_constant_ints(sl->input(1), vb) || !get_constant_ints(sl->input(2), ve) || !get_constant_ints(sl->input(3), vs) ||
+                !get_constant_ints(sl->input(4), va)) return false;
+            return vb.size() == 1 && vb[0] == b && (ve[0] == e || (e == S && ve[0] >= S)) && vs[0] == 1 && (va[0] == 3 || va[0] == -1);
+        };
+        if (rot <= 0 || rot >= S || !range(m.node(head), 0, rot) || !range(m.node(tail), rot, S)) return false;
+        const int64_t cat_axis = m.node(cat)->attr_int("axis");
+        if (cat_axis != -1 && cat_axis != 3) return false;
+        auto rope = op("RoPE", {xin, r->input(1), r->input(2)}, {{"is_interleaved", Attr::Bool(r->attr_bool("is_interleaved"))}, {"rotary_ndims", Attr::Int(rot)},
+                                                                {"head_size", Attr::Int(S)}, {"head_cnt", Attr::Int(r->attr_int("head_cnt"))}});
+        copy_runtime_info(m.matched_nodes(), {rope});
+        replace_node(m.match_root(), rope);
+        return true;
+    });
+}
+
+// ------------------------------------------------------------------------------------ LoRA
+//   main(x) + ((x @ A^T) * alpha) @ B^T   with A, alpha, B read from variables (adapters switched by set_state at run time)
+//   ->  LoraSubgraph(main(x), x, A, alpha, B)
+// One operation per adapted projection lets a device run the low-rank path as two small GEMMs whose second epilogue adds
+// into the main result (src/common/transformations/src/transformations/common_optimizations/lora_subgraph_fusion.cpp).
+std::shared_ptr<MatcherPass> make_lora_fusion() {
+    auto x = any_input();
+    auto main = wrap_type({"MatMul", "FullyConnected", "FullyConnectedCompressed", "Convolution"});
+    auto rv = [] { return optional({"Convert"}, wrap_type({"ReadValue"})); };
+    auto a = rv(), alpha = rv(), b = rv();
+    auto mm_a = wrap_type({"MatMul"}, {x, a});
+    auto scaled = wrap_type({"Multiply"}, {mm_a, alpha});
+    auto mm_b = wrap_type({"MatMul"}, {scaled, b});
+    auto add = wrap_type({"Add"}, {main, mm_b});
+    return std::make_shared<MatcherPass>("LoraSubgraphFusion", add, [=](Matcher& m) {
+        NodePtr mn = m.node(main);
+        // the adapter reads the projection's own input
+        if (!(mn->input(0) == m.at(x))) return false;
+        if (!m.node(mm_a)->attr_bool("transpose_b") || !m.node(mm_b)->attr_bool("transpose_b") || m.node(mm_a)->attr_bool("transpose_a") ||
+            m.node(mm_b)->attr_bool("transpose_a")) return false;
+        // (the optional Convert may be absent: take the operands from the matched nodes themselves)
+        NodePtr sc = m.node(scaled);
+        const Output a_in = m.node(mm_a)->input(1), b_in = m.node(mm_b)->input(1);
+        const Output alpha_in = sc->input(0).node == m.node(mm_a) ? sc->input(1) : sc->input(0);
+        auto lora = op("LoraSubgraph", {mn->output(0), m.at(x), a_in, alpha_in, b_in}, {}, "ie_internal_opset");
+        copy_runtime_info({m.node(mm_a), m.node(scaled), m.node(mm_b), m.match_root()}, {lora});
+        replace_node(m.match_root(), lora);
+        return true;
+    });
+}
+
 // ------------------------------------------------------------------------------------ compressed weights helpers
 struct CompressedWeight {
     NodePtr weights;     // low-precision Constant

@@ -17,12 +17,11 @@
 
 namespace ovb {
 
-constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kArgmaxRowsCap = 1024;
 constexpr int kArgmaxDataOff = 64;   // ints: flags first, then two (value, index) buffers
 
-__device__ __forceinline__ bool wait_flag_ge(const int* f, int epoch, int* status) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool wait_flag_ge(const int* f, int epoch, int* status, uint32_t spin_limit) {
+    for (uint32_t i = 0; i < spin_limit; ++i) {
         if (ld_acquire_sys(f) >= epoch) return true;
         __nanosleep(200);
     }
@@ -56,6 +55,7 @@ struct CommK {
     int* status;
     uint8_t* mc;             // multicast mapping of the heap (NVLS) or NULL
     long long nvls_flags_off;   // of the call site
+    uint32_t spin_limit;        // polls before a wait on a peer gives up (peer_spin_limit())
 };
 
 // One CTA; thread = row. Every rank pushes (max value, global index) of its shard to every rank, then picks.
@@ -78,7 +78,7 @@ __global__ void argmax_combine_kernel(CommK c, int* ids, const float* max_vals, 
     __syncthreads();
     if (threadIdx.x < W) {
         st_release_sys(reinterpret_cast<int*>(c.heap[threadIdx.x] + c.flags_off) + c.rank, epoch);
-        if (!wait_flag_ge(reinterpret_cast<const int*>(c.heap[c.rank] + c.flags_off) + threadIdx.x, epoch, c.status)) ok_s = 0;
+        if (!wait_flag_ge(reinterpret_cast<const int*>(c.heap[c.rank] + c.flags_off) + threadIdx.x, epoch, c.status, c.spin_limit)) ok_s = 0;
     }
     __syncthreads();
     if (ok_s && row < rows) {
@@ -145,7 +145,7 @@ __global__ void allreduce_kernel(CommK c, long long data_off, long long npieces,
     __syncthreads();
     if (threadIdx.x < W) {
         st_release_sys(reinterpret_cast<int*>(c.heap[threadIdx.x] + c.flags_off) + (size_t)blockIdx.x * W + c.rank, epoch);
-        if (!wait_flag_ge(reinterpret_cast<const int*>(c.heap[c.rank] + c.flags_off) + (size_t)blockIdx.x * W + threadIdx.x, epoch, c.status))
+        if (!wait_flag_ge(reinterpret_cast<const int*>(c.heap[c.rank] + c.flags_off) + (size_t)blockIdx.x * W + threadIdx.x, epoch, c.status, c.spin_limit))
             ok_s = 0;
     }
     __syncthreads();
@@ -173,7 +173,7 @@ __global__ void allreduce_nvls_kernel(CommK c, long long data_off, long long npi
     const int* bar_local = reinterpret_cast<const int*>(c.heap[c.rank] + c.nvls_flags_off) + (size_t)blockIdx.x * kNvlsFlagStride;
     int* bar_mc = reinterpret_cast<int*>(c.mc + c.nvls_flags_off) + (size_t)blockIdx.x * kNvlsFlagStride;
     __shared__ int ok_s;
-    if (threadIdx.x == 0) ok_s = nvls_barrier(bar_local, bar_mc, c.rank, W, epoch, kSpinLimit, nullptr) ? 1 : 0;
+    if (threadIdx.x == 0) ok_s = nvls_barrier(bar_local, bar_mc, c.rank, W, epoch, c.spin_limit, nullptr) ? 1 : 0;
     __syncthreads();
     if (!ok_s) {
         if (threadIdx.x == 0) report_status(c.status, STATUS_PEER_TIMEOUT);
@@ -188,7 +188,7 @@ __global__ void allreduce_nvls_kernel(CommK c, long long data_off, long long npi
                                                            : (DT == OVB_DT_F16 ? multimem_ld_reduce_f16x8(base + i * 16) : multimem_ld_reduce_bf16x8(base + i * 16)));
     fence_sys();
     __syncthreads();
-    if (threadIdx.x == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, c.rank, W, epoch, kSpinLimit, nullptr)) report_status(c.status, STATUS_PEER_TIMEOUT);
+    if (threadIdx.x == 0 && !nvls_barrier(bar_local + 8, bar_mc + 8, c.rank, W, epoch, c.spin_limit, nullptr)) report_status(c.status, STATUS_PEER_TIMEOUT);
 }
 
 static int fill(const ovb_comm* c, CommK* k, int site) {
@@ -207,6 +207,7 @@ static int fill(const ovb_comm* c, CommK* k, int site) {
     k->status = status_word();
     k->mc = static_cast<uint8_t*>(c->mc_base);
     k->nvls_flags_off = c->nvls_flags_off + (int64_t)site * c->nvls_flags_per_site * 4;
+    k->spin_limit = peer_spin_limit();
     return 0;
 }
 

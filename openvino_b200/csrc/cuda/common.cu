@@ -4,6 +4,8 @@
 
 #include <mutex>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace ovb {
@@ -41,6 +43,18 @@ bool pdl_enabled() {
         g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
     return g_pdl != 0;
+}
+
+static std::atomic<uint32_t> g_spin_limit{0};
+uint32_t peer_spin_limit() {
+    uint32_t v = g_spin_limit.load(std::memory_order_relaxed);
+    if (v == 0) {
+        const char* e = getenv("OVB_PEER_SPIN_LIMIT");
+        const long long want = e ? atoll(e) : 0;
+        v = want > 0 && want < (1ll << 31) ? (uint32_t)want : (1u << 22);
+        g_spin_limit.store(v, std::memory_order_relaxed);
+    }
+    return v;
 }
 
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
@@ -91,6 +105,12 @@ int ovb_version(void) { return 100; }
 int ovb_set_pdl(int on) {
     const int before = ovb::pdl_enabled() ? 1 : 0;
     ovb::g_pdl = on ? 1 : 0;
+    return before;
+}
+
+unsigned ovb_set_peer_spin_limit(unsigned polls) {
+    const unsigned before = ovb::peer_spin_limit();
+    ovb::g_spin_limit.store(polls ? polls : (1u << 22), std::memory_order_relaxed);
     return before;
 }
 

@@ -53,6 +53,11 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // programmatic dependency of the graph). OVB_PDL=0 in the environment, or ovb_set_pdl(0), turns the attribute off.
 bool pdl_enabled();
 
+// Polls (about 0.25 us apart) that a kernel spends waiting for a peer GPU before it gives up, records STATUS_PEER_TIMEOUT in
+// the status word and returns. About one second by default; OVB_PEER_SPIN_LIMIT in the environment or
+// ovb_set_peer_spin_limit() change it (failure-detection tests use a few milliseconds).
+uint32_t peer_spin_limit();
+
 // Launch `kern` with the attribute (when enabled). Only for kernels whose every thread passes pdl_wait() before it touches
 // memory that an earlier kernel of the stream may write or still read.
 template <class... P, class... A>

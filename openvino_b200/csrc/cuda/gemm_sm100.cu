@@ -86,13 +86,14 @@ struct GemmKParams {
     // Grouped GEMM (mixture of experts): the rows of X / out are grouped, group g owns rows [group_off[g], group_off[g + 1])
     // (device array, written by an earlier kernel of the stream) and uses weight g of a stack: group_mode 1 = the weights are
     // stacked along N (tile index g * tiles_n + n_tile), 2 = stacked along K (k-block offset g * K / 64). T is the row capacity.
+    uint32_t spin_limit;      // polls before a wait on a peer gives up and reports STATUS_PEER_TIMEOUT
     int nvls_reducers;        // in-switch all-reduce: the first CTAs of the grid only reduce (0: every tile CTA reduces its own tile)
     const int* group_off;
     int num_groups;
     int group_mode;
 };
 
-constexpr uint32_t kPeerSpinLimit = 1u << 22;   // polls of a peer flag, ~0.25 us apart
+// polls of a peer flag (~0.25 us apart) before a wait gives up: GemmKParams::spin_limit, set per launch from peer_spin_limit()
 
 template <bool F16>
 struct Elem {
@@ -196,7 +197,7 @@ __device__ __forceinline__ bool nvls_reduce_tile(const GemmKParams& p, int rt, i
     const int* bar_local = reinterpret_cast<const int*>(p.heap[p.rank] + p.nvls_flags_off) + (size_t)rt * kNvlsFlagStride;
     if (tid == 0) {
         bool ok = false;
-        for (uint32_t it = 0; it < kPeerSpinLimit && !ok; ++it) {
+        for (uint32_t it = 0; it < p.spin_limit && !ok; ++it) {
             const uint4 a = ld_relaxed_sys_v4(bar_local), b = ld_relaxed_sys_v4(bar_local + 4);
             const int w[8] = {(int)a.x, (int)a.y, (int)a.z, (int)a.w, (int)b.x, (int)b.y, (int)b.z, (int)b.w};
             ok = true;
@@ -320,7 +321,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 *p.counters = 0;
                 const int* bar_local = reinterpret_cast<const int*>(p.heap[p.rank] + p.nvls_flags_off) + 8;
                 int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + 8;
-                if (!nvls_barrier(bar_local, bar_mc, p.rank, p.world, epoch, kPeerSpinLimit, nullptr)) report_status(p.status, STATUS_PEER_TIMEOUT);
+                if (!nvls_barrier(bar_local, bar_mc, p.rank, p.world, epoch, p.spin_limit, nullptr)) report_status(p.status, STATUS_PEER_TIMEOUT);
             }
         }
         return;
@@ -698,7 +699,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         *p.counters = 0;
                         const int* bar_local = reinterpret_cast<const int*>(my_heap + p.nvls_flags_off) + 8;
                         int* bar_mc = reinterpret_cast<int*>(p.mc + p.nvls_flags_off) + 8;
-                        if (!nvls_barrier(bar_local, bar_mc, p.rank, W, epoch, kPeerSpinLimit, abort_flag)) report_status(p.status, STATUS_PEER_TIMEOUT);
+                        if (!nvls_barrier(bar_local, bar_mc, p.rank, W, epoch, p.spin_limit, abort_flag)) report_status(p.status, STATUS_PEER_TIMEOUT);
                     }
                 }
                 return;
@@ -706,7 +707,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             auto flags_of = [&](int r) { return reinterpret_cast<int*>(p.heap[r] + p.flags_off) + (size_t)tile_id * (W + 1); };
             int* my_flags = flags_of(p.rank);
             auto wait_flag = [&](const int* f) {
-                for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+                for (uint32_t i = 0; i < p.spin_limit; ++i) {
                     if (ld_acquire_sys(f) >= epoch) return;
                     if ((i & 255u) == 255u && *abort_flag) return;
                     __nanosleep(200);
@@ -775,7 +776,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                 const uint8_t* src = slots + (size_t)r * slot_stride + poff;
                                 uint32_t spins = 0;
                                 while (!(a[j].y == tag && a[j].w == tag && b[j].y == tag && b[j].w == tag)) {
-                                    if (++spins > kPeerSpinLimit || ((spins & 1023u) == 0 && *abort_flag)) return false;
+                                    if (++spins > p.spin_limit || ((spins & 1023u) == 0 && *abort_flag)) return false;
                                     if (spins > 64) __nanosleep(100);
                                     a[j] = ld_volatile_v4(src);
                                     b[j] = ld_volatile_v4(src + 16);
@@ -873,7 +874,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         if (i >= PIECES || (i >> 4) >= ntok) continue;
                         uint32_t spins = 0;
                         while (!(a[j].y == tag && a[j].w == tag && b[j].y == tag && b[j].w == tag)) {
-                            if (++spins > kPeerSpinLimit || ((spins & 1023u) == 0 && *abort_flag)) { ok_ll = false; break; }
+                            if (++spins > p.spin_limit || ((spins & 1023u) == 0 && *abort_flag)) { ok_ll = false; break; }
                             if (spins > 64) __nanosleep(100);
                             a[j] = ld_volatile_v4(done + (size_t)i * 32);
                             b[j] = ld_volatile_v4(done + (size_t)i * 32 + 16);
@@ -1511,6 +1512,7 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream_) {
     p.out_f32 = a->out_f32;
     p.splits = splits;
     p.w_kb_stride = a->w_kb_stride > 0 ? a->w_kb_stride : ceil_div(a->K, TILE_K) * (grouped && a->group_mode == 2 ? a->num_groups : 1);
+    p.spin_limit = peer_spin_limit();
     p.group_off = a->group_offsets;
     p.num_groups = a->num_groups;
     p.group_mode = a->group_mode;

@@ -22,6 +22,9 @@ const char* ovb_last_error(void);
 // Programmatic dependent launch of the library's kernels (on by default; OVB_PDL=0 in the environment turns it off):
 // a kernel's preamble overlaps the tail of the kernel before it in the stream. Returns the previous setting.
 int ovb_set_pdl(int on);
+/* Polls (about 0.25 us apart) that a kernel waits for a peer GPU before it records OVB status 2 (peer timeout) and returns;
+   0 restores the default (about one second). Returns the previous value. */
+unsigned ovb_set_peer_spin_limit(unsigned polls);
 
 // ---------------------------------------------------------------------------------------------
 // GEMM family:  out[T, N] = epilogue( X[T, K] * dequant(W[N, K])^T )

@@ -117,6 +117,20 @@ class TensorFlowFrontEnd(FrontEnd):
         return tensorflow.convert(model)
 
 
+class TFLiteFrontEnd(FrontEnd):
+    name = "tflite"
+
+    def supported(self, model) -> bool:
+        if isinstance(model, (str, os.PathLike)):
+            return str(model).lower().endswith(".tflite")
+        return isinstance(model, (bytes, bytearray)) and len(model) >= 8 and bytes(model[4:8]) == b"TFL3"
+
+    def convert(self, input_model) -> Model:
+        from . import tflite
+        model, _ = input_model
+        return tflite.load(model)
+
+
 class GgufFrontEnd(FrontEnd):
     name = "gguf"
 
@@ -133,7 +147,8 @@ class GgufFrontEnd(FrontEnd):
 
 class FrontEndManager:
     def __init__(self):
-        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "tf": TensorFlowFrontEnd(), "gguf": GgufFrontEnd()}
+        self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "tf": TensorFlowFrontEnd(), "tflite": TFLiteFrontEnd(),
+                           "gguf": GgufFrontEnd()}
 
     def get_available_front_ends(self) -> List[str]:
         return list(self._frontends)
@@ -157,7 +172,7 @@ _manager = FrontEndManager()
 
 
 def read_model(model, weights=None, extensions=None) -> Model:
-    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor), an ``.onnx``, a frozen TensorFlow ``.pb`` or a ``.gguf`` file."""
+    """Read an IR (``.xml`` path, xml text or bytes; weights as path, bytes or a u8 Tensor), an ``.onnx``, a frozen TensorFlow ``.pb``, a ``.tflite`` or a ``.gguf`` file."""
     if isinstance(model, Model):
         return model
     if hasattr(model, "read"):

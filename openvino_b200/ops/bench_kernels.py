@@ -87,11 +87,20 @@ def bench_attention(a) -> dict:
     past, sb = i32([ctx - q_len] * B), i32([i * q_len for i in range(B + 1)])
     bi, bib = torch.randperm(total).to(torch.int32).cuda(), i32([i * nblk for i in range(B + 1)])
     out = torch.empty(T, Hq * D, device="cuda", dtype=torch.bfloat16)
-    ms = timeit(lambda: K.paged_attention(q, kc, vc, past, sb, bi, bib, Hq, Hkv, D, max_context_len=ctx, max_q_len=q_len, out=out), a.iters, a.warmup)
+    km = vm = None
+    kv_elem = 2.0
+    if getattr(a, "kv_u8", False):          # byte cache with one fp16 (scale, zero point) pair per (block, head, slot)
+        kc = torch.randint(0, 256, (total, Hkv, bs, D), device="cuda", dtype=torch.uint8)
+        vc = torch.randint(0, 256, (total, Hkv, bs, D), device="cuda", dtype=torch.uint8)
+        km = torch.stack([torch.full((total, Hkv, bs), 0.02, device="cuda"), torch.full((total, Hkv, bs), 128.0, device="cuda")], -1).to(torch.float16)
+        vm = km.clone()
+        kv_elem = 1.0 + 4.0 / D
+    ms = timeit(lambda: K.paged_attention(q, kc, vc, past, sb, bi, bib, Hq, Hkv, D, max_context_len=ctx, max_q_len=q_len, out=out, k_meta=km, v_meta=vm),
+                a.iters, a.warmup)
     K.check_status("attention")
-    kv_bytes = 2 * B * ctx * Hkv * D * 2
+    kv_bytes = 2 * B * ctx * Hkv * D * kv_elem
     flops = 4.0 * B * Hq * D * (q_len * (ctx - q_len) + q_len * (q_len + 1) / 2)
-    return {"kernel": "paged_attention", "B": B, "ctx": ctx, "q_len": q_len, "Hq": Hq, "Hkv": Hkv, "ms": ms, "gbs": (kv_bytes + 2 * T * Hq * D * 2) / ms / 1e6,
+    return {"kernel": "paged_attention" + (" (u8 cache)" if km is not None else ""), "B": B, "ctx": ctx, "q_len": q_len, "Hq": Hq, "Hkv": Hkv, "ms": ms, "gbs": (kv_bytes + 2 * T * Hq * D * 2) / ms / 1e6,
             "tflops": flops / ms / 1e9}
 
 
@@ -165,6 +174,7 @@ def main() -> int:
     ap.add_argument("--q-len", dest="q_len", type=int, default=1)
     ap.add_argument("--Hq", type=int, default=32)
     ap.add_argument("--Hkv", type=int, default=8)
+    ap.add_argument("--kv-u8", dest="kv_u8", action="store_true", help="attention: u8 KV cache with per-row scale / zero point")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()

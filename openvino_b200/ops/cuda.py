@@ -107,6 +107,14 @@ def read_status() -> int:
     return int(lib().ovb_status_read(C.c_void_p(_stream())))
 
 
+def set_peer_spin_limit(polls: int) -> int:
+    """Polls (about 0.25 us apart) a kernel waits for a peer GPU before it gives up with status 2; 0 = default (about 1 s).
+    Returns the previous value."""
+    fn = lib().ovb_set_peer_spin_limit
+    fn.restype = C.c_uint
+    return int(fn(C.c_uint(int(polls))))
+
+
 def check_status(what: str = "kernel") -> None:
     s = read_status()
     if s != 0:

@@ -229,6 +229,26 @@ class PeerCommunicator:
     def step_begin(self) -> None:
         K._check(K.lib().ovb_comm_step_begin(C.byref(self.struct(0)), C.c_void_p(K._stream())), "ovb_comm_step_begin")
 
+    def recover(self) -> int:
+        """After a step in which a rank reported a peer time-out (or did not take part): bring the ranks' step numbers back
+        together. Every rank calls this between steps, with nothing of its own in flight: the step numbers are compared on
+        the host and every rank moves to one past the largest, so that flags and packet tags of the abandoned step can never
+        satisfy a later wait; the local completion counter of the fused kernels and the device status word are cleared.
+        Returns the new step number. (The reference's sub-memory manager has no recovery: a lost rank ends the process
+        group, src/plugins/intel_cpu/src/sub_memory_manager.hpp.)"""
+        import torch.distributed as dist
+        torch.cuda.synchronize(self.device)
+        epoch = _wrap_device_memory(self._base + self.layout.epoch_off, 4, self.device).view(torch.int32)
+        mine = torch.tensor([int(epoch.item())], dtype=torch.int64, device=self.device if dist.get_backend(self.group) == "nccl" else "cpu")
+        dist.all_reduce(mine, op=dist.ReduceOp.MAX, group=self.group)
+        new = int(mine.item()) + 1
+        epoch.fill_(new)
+        K.default_workspace(self.device).counters.zero_()
+        K.read_status()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        return new
+
     def gemm_allreduce(self, x: torch.Tensor, w: "K.PackedWeight", h: torch.Tensor, ws, site: int, mode: int = 0) -> None:
         """h += sum over ranks of x @ W_shard^T (h replicated, must live in the heap)."""
         K.gemm(x, w, out=h, residual=h, ws=ws, comm=self.struct(site, mode))

@@ -97,6 +97,10 @@ class RoPEFusion(_NamedPass):
     native_name = "RoPEFusion"
 
 
+class LoraSubgraphFusion(_NamedPass):
+    """main(x) + ((x @ A^T) * alpha) @ B^T with A / alpha / B read from variables -> one LoraSubgraph operation."""
+
+
 class GLUFusion(_NamedPass):
     native_name = "GLUFusion"
 

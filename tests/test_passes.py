@@ -297,3 +297,91 @@ def test_low_latency2_makes_recurrent_state_persistent():
     req.reset_state()
     np.testing.assert_allclose(req.infer([data])[0], 10.0 + data.sum(1))
     assert not LowLatency2().run_on_model(m)                              # idempotent
+
+
+def _run_pass(m, p):
+    mgr = passes.Manager()
+    mgr.register_pass(p)
+    mgr.run_passes(m)
+    return m
+
+
+def _rope_tables(L, D, repeat):
+    inv = 10000.0 ** (-np.arange(0, D, 2, dtype=np.float32) / D)
+    ang = np.arange(L, dtype=np.float32)[:, None] * inv[None]
+    ang = np.repeat(ang, 2, axis=1) if repeat == "interleave" else np.concatenate([ang, ang], 1)
+    return np.cos(ang)[None, None].astype(np.float32), np.sin(ang)[None, None].astype(np.float32)
+
+
+def test_rope_fusion_interleaved_form():
+    """GPT-J "rotate every two": pairs (2i, 2i + 1) are rotated; the tables repeat every angle twice."""
+    B, H, L, D = 2, 3, 5, 8
+    i64 = lambda v: ops.constant(np.array(v, dtype=np.int64))
+    x = ops.parameter([B, H, L, D], "f32", "x")
+    cos, sin = _rope_tables(L, D, "interleave")
+    odd = ops.slice(x, i64([1]), i64([D]), i64([2]), i64([3]))
+    even = ops.slice(x, i64([0]), i64([D]), i64([2]), i64([3]))
+    stacked = ops.concat([ops.unsqueeze(ops.negative(odd), i64([4])).output(0), ops.unsqueeze(even, i64([4])).output(0)], 4)
+    rot = ops.reshape(stacked, i64([B, H, L, D]), False)
+    y = ops.add(ops.multiply(x, ops.constant(cos)), ops.multiply(rot, ops.constant(sin)))
+    m = ov.Model([y], [x], "gptj")
+    xin = np.random.default_rng(0).standard_normal((B, H, L, D)).astype(np.float32)
+    want = ov.compile_model(m, "CPU")([xin])[0]
+    _run_pass(m, passes.RoPEFusion())
+    rope = [n for n in m.get_ops() if n.get_type_name() == "RoPE"]
+    assert len(rope) == 1 and rope[0].get_attribute("is_interleaved") and rope[0].get_attribute("rotary_ndims") == D
+    assert not any(n.get_type_name() in ("Slice", "Concat", "Negative") for n in m.get_ops())
+    np.testing.assert_allclose(ov.compile_model(m, "CPU")([xin])[0], want, rtol=1e-5, atol=1e-6)
+
+
+def test_rope_fusion_partial_rotary():
+    """Only the first `rot` channels of every head are rotated (GPT-NeoX / Phi); the rest passes through."""
+    B, H, L, D, rot = 1, 2, 6, 16, 8
+    i64 = lambda v: ops.constant(np.array(v, dtype=np.int64))
+    x = ops.parameter([B, H, L, D], "f32", "x")
+    cos, sin = _rope_tables(L, rot, "halves")
+    head = ops.slice(x, i64([0]), i64([rot]), i64([1]), i64([3]))
+    tail = ops.slice(x, i64([rot]), i64([D]), i64([1]), i64([3]))
+    lo = ops.slice(head, i64([0]), i64([rot // 2]), i64([1]), i64([3]))
+    hi = ops.slice(head, i64([rot // 2]), i64([rot]), i64([1]), i64([3]))
+    rotated = ops.concat([ops.negative(hi).output(0), lo.output(0)], 3)
+    emb = ops.add(ops.multiply(head, ops.constant(cos)), ops.multiply(rotated, ops.constant(sin)))
+    y = ops.concat([emb.output(0), tail.output(0)], 3)
+    m = ov.Model([y], [x], "neox")
+    xin = np.random.default_rng(1).standard_normal((B, H, L, D)).astype(np.float32)
+    want = ov.compile_model(m, "CPU")([xin])[0]
+    _run_pass(m, passes.RoPEFusion())
+    rope = [n for n in m.get_ops() if n.get_type_name() == "RoPE"]
+    assert len(rope) == 1 and rope[0].get_attribute("rotary_ndims") == rot and rope[0].get_attribute("head_size") == D
+    assert rope[0].input_value(0).get_node().get_type_name() == "Parameter"           # the slices are gone: RoPE reads the whole head
+    np.testing.assert_allclose(ov.compile_model(m, "CPU")([xin])[0], want, rtol=1e-5, atol=1e-6)
+
+
+def test_lora_subgraph_fusion_keeps_adapters_switchable():
+    rng = np.random.default_rng(2)
+    din, dout, r = 16, 12, 4
+    x = ops.parameter([3, din], "f32", "x")
+    w = rng.standard_normal((dout, din)).astype(np.float32)
+    a0, b0 = rng.standard_normal((r, din)).astype(np.float32), rng.standard_normal((dout, r)).astype(np.float32)
+    al0 = np.full((1, r), 0.5, np.float32)
+    main = ops.matmul(x, w, False, True, name="proj")
+    A = ops.read_value(ops.constant(a0), "lora_A", "f32", ov.PartialShape([-1, din]))
+    AL = ops.read_value(ops.constant(al0), "lora_alpha", "f32", ov.PartialShape([1, -1]))
+    Bm = ops.read_value(ops.constant(b0), "lora_B", "f32", ov.PartialShape([dout, -1]))
+    low = ops.matmul(ops.multiply(ops.matmul(x, A, False, True), AL), Bm, False, True)
+    y = ops.add(main, low)
+    m = ov.Model([y], [x], "lora")
+    xin = rng.standard_normal((3, din)).astype(np.float32)
+    want = xin @ w.T + ((xin @ a0.T) * al0) @ b0.T
+    np.testing.assert_allclose(ov.compile_model(m, "CPU")([xin])[0], want, rtol=1e-4, atol=1e-5)
+    _run_pass(m, passes.LoraSubgraphFusion())
+    fused = [n for n in m.get_ops() if n.get_type_name() == "LoraSubgraph"]
+    assert len(fused) == 1 and sum(1 for n in m.get_ops() if n.get_type_name() == "MatMul") == 1
+    cm = ov.compile_model(m, "CPU")
+    req = cm.create_infer_request()
+    np.testing.assert_allclose(req.infer([xin])[0], want, rtol=1e-4, atol=1e-5)
+    # another adapter (another rank) through the states
+    a1, b1 = rng.standard_normal((2, din)).astype(np.float32), rng.standard_normal((dout, 2)).astype(np.float32)
+    for st in req.query_state():
+        st.state = ov.Tensor({"lora_A": a1, "lora_alpha": np.ones((1, 2), np.float32), "lora_B": b1}[st.name])
+    np.testing.assert_allclose(req.infer([xin])[0], xin @ w.T + (xin @ a1.T) @ b1.T, rtol=1e-4, atol=1e-5)

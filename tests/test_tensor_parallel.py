@@ -89,3 +89,16 @@ def test_fused_gemm_all_reduce_at_serving_shapes(world, env):
     import json
     rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
     assert len(rows) >= 3 and all(x["ranks_identical"] and x["rel_err_vs_fp32_allreduce"] < 2e-2 for x in rows)
+
+
+@pytest.mark.gpu
+def test_peer_that_never_posts_times_out_and_the_ranks_recover():
+    """Failure detection without a GPU fault: a rank skips one fused step, the other rank's kernel reports
+    STATUS_PEER_TIMEOUT after a short bounded wait, both keep their contexts, resynchronise on the host and run on."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, OVB_NVLS="0", NCCL_NVLS_ENABLE="0")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tp_timeout_worker.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29699", worker], capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "TP_TIMEOUT_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-3000:])
