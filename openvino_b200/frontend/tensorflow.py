@@ -16,6 +16,7 @@ import numpy as np
 from .. import opset as ops
 from .._graph import Model, Node, Output, as_output, constant, parameter, result
 from .._types import PartialShape
+from . import common_translators as CT
 from .onnx import _fields, _packed_ints, _sint
 
 
@@ -224,7 +225,6 @@ def _bias_add(n, i):
 @_op("Conv2D")
 def _conv2d(n, i):
     nhwc = _is_nhwc(n)
-    x = _nchw(i[0]) if nhwc else i[0]
     w = ops.transpose(i[1], _i64([3, 2, 0, 1])).output(0)          # HWIO -> OIHW
     strides, dil = _spatial(n.attrs.get("strides", [1, 1, 1, 1]), nhwc), _spatial(n.attrs.get("dilations", [1, 1, 1, 1]), nhwc)
     pad = _auto_pad(n)
@@ -233,40 +233,28 @@ def _conv2d(n, i):
         ep = n.attrs.get("explicit_paddings", [0] * 8)
         hw = (ep[2:6] if nhwc else ep[4:8])
         pb, pe = [int(hw[0]), int(hw[2])], [int(hw[1]), int(hw[3])]
-    y = ops.convolution(x, w, strides, pb, pe, dil, pad).output(0)
-    return _nhwc(y) if nhwc else y
+    return CT.conv2d(i[0], w, strides, dil, pad, pb, pe, nhwc=nhwc)
 
 
 @_op("DepthwiseConv2dNative")
 def _depthwise(n, i):
     nhwc = _is_nhwc(n)
-    x = _nchw(i[0]) if nhwc else i[0]
     kh, kw, cin, mult = i[1].get_shape()
     w = ops.transpose(i[1], _i64([2, 3, 0, 1]))                       # HWIM -> IMHW
     w = ops.reshape(w, _i64([cin, mult, 1, kh, kw]), False).output(0)  # groups = I, out per group = M, in per group = 1
     strides, dil = _spatial(n.attrs.get("strides", [1, 1, 1, 1]), nhwc), _spatial(n.attrs.get("dilations", [1, 1, 1, 1]), nhwc)
-    y = ops.group_convolution(x, w, strides, [0, 0], [0, 0], dil, _auto_pad(n)).output(0)
-    return _nhwc(y) if nhwc else y
+    return CT.depthwise_conv2d(i[0], w, strides, dil, _auto_pad(n), nhwc=nhwc)
 
 
 @_op("MaxPool", "AvgPool")
 def _pool(n, i):
     nhwc = _is_nhwc(n)
-    x = _nchw(i[0]) if nhwc else i[0]
-    k, s = _spatial(n.attrs["ksize"], nhwc), _spatial(n.attrs["strides"], nhwc)
-    if n.op == "MaxPool":
-        y = ops.max_pool(x, s, [1, 1], [0, 0], [0, 0], k, "floor", _auto_pad(n)).output(0)
-    else:
-        y = ops.avg_pool(x, s, [0, 0], [0, 0], k, True, "floor", _auto_pad(n)).output(0)
-    return _nhwc(y) if nhwc else y
+    return CT.pool2d(i[0], _spatial(n.attrs["ksize"], nhwc), _spatial(n.attrs["strides"], nhwc), _auto_pad(n), n.op == "MaxPool", nhwc=nhwc)
 
 
 @_op("FusedBatchNorm", "FusedBatchNormV2", "FusedBatchNormV3")
 def _fused_bn(n, i):
-    nhwc = _is_nhwc(n)
-    x = _nchw(i[0]) if nhwc else i[0]
-    y = ops.batch_norm_inference(x, i[1], i[2], i[3], i[4], float(n.attrs.get("epsilon", 1e-3))).output(0)
-    return _nhwc(y) if nhwc else y
+    return CT.batch_norm(i[0], i[1], i[2], i[3], i[4], float(n.attrs.get("epsilon", 1e-3)), nhwc=_is_nhwc(n))
 
 
 @_op("MatMul")

@@ -21,6 +21,7 @@ import numpy as np
 from .. import opset as ops
 from .._graph import Model, Output, constant, parameter, result
 from .._types import PartialShape
+from . import common_translators as CT
 
 
 class TFLiteError(RuntimeError):
@@ -124,30 +125,17 @@ def _op(*names):
 
 
 def _i64(v):
-    return constant(np.asarray(v, dtype=np.int64))
+    return CT.i64(v)
+
+
+_ACT = {0: "none", 1: "relu", 2: "relu_n1_to_1", 3: "relu6", 4: "tanh"}
 
 
 def _act(y: Output, code: int) -> Output:
     """Fused activation of the option tables: NONE, RELU, RELU_N1_TO_1, RELU6, TANH."""
-    if code == 0:
-        return y
-    if code == 1:
-        return ops.relu(y).output(0)
-    if code == 2:
-        return ops.clamp(y, -1.0, 1.0).output(0)
-    if code == 3:
-        return ops.clamp(y, 0.0, 6.0).output(0)
-    if code == 4:
-        return ops.tanh(y).output(0)
-    raise TFLiteError("fused activation %d is not supported" % code)
-
-
-def _nchw(x: Output) -> Output:
-    return ops.transpose(x, _i64([0, 3, 1, 2])).output(0)
-
-
-def _nhwc(x: Output) -> Output:
-    return ops.transpose(x, _i64([0, 2, 3, 1])).output(0)
+    if code not in _ACT:
+        raise TFLiteError("fused activation %d is not supported" % code)
+    return CT.fused_activation(y, _ACT[code])
 
 
 def _pad_mode(code: int) -> str:
@@ -159,11 +147,9 @@ def _conv(op: _Op, ins, g):
     x, w = ins[0], ins[1]                                    # NHWC, filters [O, kh, kw, I]
     pad, sw, sh, act = op.opt(0, "b"), op.opt(1), op.opt(2), op.opt(3, "b")
     dw, dh = op.opt(4, "i", 1), op.opt(5, "i", 1)
-    wt = ops.transpose(w, _i64([0, 3, 1, 2]))
-    y = ops.convolution(_nchw(x), wt, [sh, sw], [0, 0], [0, 0], [dh, dw], _pad_mode(pad)).output(0)
-    if len(ins) > 2 and ins[2] is not None:
-        y = ops.add(y, ops.reshape(ins[2], _i64([1, -1, 1, 1]), False)).output(0)
-    return [_act(_nhwc(y), act)]
+    wt = ops.transpose(w, _i64([0, 3, 1, 2])).output(0)
+    y = CT.conv2d(x, wt, [sh, sw], [dh, dw], _pad_mode(pad), bias=ins[2] if len(ins) > 2 else None)
+    return [_act(y, act)]
 
 
 @_op("DEPTHWISE_CONV_2D")
@@ -174,23 +160,15 @@ def _dwconv(op: _Op, ins, g):
     ws = w.get_partial_shape()
     kh, kw, cm = (int(ws[i].get_length()) for i in (1, 2, 3))
     mult = max(mult, 1)
-    c = cm // mult
     # [1, kh, kw, C * m] -> [C, m, 1, kh, kw]
-    wt = ops.reshape(ops.transpose(w, _i64([3, 0, 1, 2])), _i64([c, mult, 1, kh, kw]), False)
-    y = ops.group_convolution(_nchw(x), wt, [sh, sw], [0, 0], [0, 0], [dh, dw], _pad_mode(pad)).output(0)
-    if len(ins) > 2 and ins[2] is not None:
-        y = ops.add(y, ops.reshape(ins[2], _i64([1, -1, 1, 1]), False)).output(0)
-    return [_act(_nhwc(y), act)]
+    wt = ops.reshape(ops.transpose(w, _i64([3, 0, 1, 2])), _i64([cm // mult, mult, 1, kh, kw]), False).output(0)
+    y = CT.depthwise_conv2d(x, wt, [sh, sw], [dh, dw], _pad_mode(pad), bias=ins[2] if len(ins) > 2 else None)
+    return [_act(y, act)]
 
 
 def _pool(op: _Op, ins, is_max: bool):
     pad, sw, sh, fw, fh, act = op.opt(0, "b"), op.opt(1), op.opt(2), op.opt(3), op.opt(4), op.opt(5, "b")
-    x = _nchw(ins[0])
-    if is_max:
-        y = ops.max_pool(x, [sh, sw], [1, 1], [0, 0], [0, 0], [fh, fw], "floor", _pad_mode(pad)).output(0)
-    else:
-        y = ops.avg_pool(x, [sh, sw], [0, 0], [0, 0], [fh, fw], True, "floor", _pad_mode(pad)).output(0)
-    return [_act(_nhwc(y), act)]
+    return [_act(CT.pool2d(ins[0], [fh, fw], [sh, sw], _pad_mode(pad), is_max), act)]
 
 
 @_op("MAX_POOL_2D")
