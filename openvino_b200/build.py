@@ -219,6 +219,47 @@ def kernel_resources(stem: str) -> dict:
     return out
 
 
+def build_selective(stats_csv, out_dir, stems=None, link: bool = True) -> Path:
+    """Conditional compilation, the selective build: compile the kernel library with only the variants that an analysing
+    run recorded (``utils/cc.py`` writes the statistics; lines ``gemm,<token tile>,<weight format>,<fp16>``). The library
+    goes to ``out_dir/libovb_cuda.so`` (load it with ``OVB_CUDA_LIB``); variants that were left out are never instantiated.
+    Role in the reference: the SELECTIVE_BUILD=ON stage driven by the collected statistics
+    (src/common/conditional_compilation, cmake/developer_package/features.cmake)."""
+    out_dir = Path(out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    keep = set()
+    for line in Path(stats_csv).read_text().splitlines():
+        parts = [p.strip() for p in line.split(",")]
+        if len(parts) >= 4 and parts[0] == "gemm":
+            keep.add((int(parts[1]), int(parts[2]), int(parts[3])))
+    cond = " || ".join("(bt == %d && wmode == %d && f16 == %s)" % (bt, wm, "true" if f else "false") for bt, wm, f in sorted(keep)) or "false"
+    (out_dir / "cc_selected.h").write_text(
+        "// generated from %s: the GEMM variants of this selective build\n"
+        "constexpr bool cc_gemm_selected(int bt, int wmode, bool f16) { return %s; }\n" % (Path(stats_csv).name, cond))
+    nvcc = _nvcc()
+    objs = []
+
+    def compile_one(src: Path) -> Path:
+        obj = out_dir / (src.stem + ".o")
+        cmd = [nvcc, "-Xptxas", "-v", *NVCC_FLAGS, "-DOVB_CC_SELECTIVE", "-I", str(out_dir), "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout[-4000:], r.stderr[-8000:]))
+        (out_dir / (src.stem + ".ptxas.txt")).write_text(r.stderr)
+        return obj
+
+    srcs = [s_ for s_ in cuda_sources() if stems is None or s_.stem in stems]
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+        objs = list(ex.map(compile_one, srcs))
+    if not link:
+        return out_dir
+    vers = out_dir / "ovb_cuda.map"
+    vers.write_text("{ global: ovb_*; local: *; };\n")
+    target = out_dir / "libovb_cuda.so"
+    _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-cudart", "static", "-Xlinker", "--version-script=%s" % vers])
+    return target
+
+
 def build_all(force: bool = False) -> None:
     build_cuda(force)
     build_core(force)
@@ -226,6 +267,11 @@ def build_all(force: bool = False) -> None:
 
 
 if __name__ == "__main__":
+    cc = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--cc-stats=")]
+    if cc:
+        out = ([a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--cc-out=")] or [str(PKG / "lib_selective")])[0]
+        print("built:", build_selective(cc[0], out))
+        sys.exit(0)
     san = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--sanitize=")]
     if san:
         for src in [a for a in sys.argv[1:] if a.endswith(".cpp")]:

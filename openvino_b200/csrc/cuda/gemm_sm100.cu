@@ -26,6 +26,7 @@
 //    16-byte stores (residual added on the way out).
 #include <stdlib.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -1404,15 +1405,41 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
     return 0;
 }
 
+// ---- conditional compilation (selective build). The analysing run records which (token tile, weight format) variants
+// were launched (ovb_cc_used_gemm); a selective build is compiled with -DOVB_CC_SELECTIVE and a generated "cc_selected.h"
+// whose cc_gemm_selected(bt, wmode, f16) names the variants to keep. A variant that is not selected is never instantiated,
+// so it costs neither build time nor binary size; launching it reports an error. Role in the reference:
+// src/common/conditional_compilation (OV_CC_COLLECT / OV_CC_SELECTIVE scopes around kernels and passes).
+#ifdef OVB_CC_SELECTIVE
+#include "cc_selected.h"
+#else
+constexpr bool cc_gemm_selected(int, int, bool) { return true; }
+#endif
+
+static std::atomic<uint32_t> g_cc_gemm_used[16];      // [wmode * 2 + f16]: bit log2(bt) - 4
+
+static int bt_bit(int bt) { return bt == 16 ? 0 : bt == 32 ? 1 : bt == 64 ? 2 : bt == 128 ? 3 : 4; }
+
+template <int BT, int WMODE, bool F16>
+static int launch_selected(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensorMap& tmX, GemmKParams& p, cudaStream_t stream) {
+    if constexpr (cc_gemm_selected(BT, WMODE, F16)) {
+        g_cc_gemm_used[(WMODE * 2 + (F16 ? 1 : 0)) & 15].fetch_or(1u << bt_bit(BT), std::memory_order_relaxed);
+        return launch<BT, WMODE, F16>(a, tmW, tmX, p, stream);
+    } else {
+        set_error("ovb_gemm: the variant (token tile %d, weight format %d%s) was left out of this selective build", BT, WMODE, F16 ? ", fp16" : "");
+        return ERR_UNSUPPORTED;
+    }
+}
+
 template <int WMODE, bool F16>
 static int dispatch_bt(int bt, const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensorMap& tmX, GemmKParams& p,
                        cudaStream_t stream) {
     switch (bt) {
-        case 16: return launch<16, WMODE, F16>(a, tmW, tmX, p, stream);
-        case 32: return launch<32, WMODE, F16>(a, tmW, tmX, p, stream);
-        case 64: return launch<64, WMODE, F16>(a, tmW, tmX, p, stream);
-        case 128: return launch<128, WMODE, F16>(a, tmW, tmX, p, stream);
-        case 256: return launch<256, WMODE, F16>(a, tmW, tmX, p, stream);
+        case 16: return launch_selected<16, WMODE, F16>(a, tmW, tmX, p, stream);
+        case 32: return launch_selected<32, WMODE, F16>(a, tmW, tmX, p, stream);
+        case 64: return launch_selected<64, WMODE, F16>(a, tmW, tmX, p, stream);
+        case 128: return launch_selected<128, WMODE, F16>(a, tmW, tmX, p, stream);
+        case 256: return launch_selected<256, WMODE, F16>(a, tmW, tmX, p, stream);
     }
     set_error("unsupported block_t %d", bt);
     return ERR_BAD_ARG;
@@ -1423,6 +1450,16 @@ static int dispatch_bt(int bt, const ovb_gemm_args* a, const CUtensorMap& tmW, c
 extern "C" {
 
 int ovb_gemm_num_counters(void) { return ovb::kNumCounters; }
+
+unsigned ovb_cc_used_gemm(int wmode, int is_f16) { return ovb::g_cc_gemm_used[(wmode * 2 + (is_f16 ? 1 : 0)) & 15].load(std::memory_order_relaxed); }
+
+int ovb_cc_is_selective(void) {
+#ifdef OVB_CC_SELECTIVE
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act) {
     // split-K partials stay in shared memory (cluster reduction): no global workspace is needed any more

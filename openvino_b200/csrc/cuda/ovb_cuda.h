@@ -86,6 +86,10 @@ int ovb_gemm(const ovb_gemm_args* a, ovb_stream_t stream);
 // Bytes of split-K workspace / number of counters that ovb_gemm may need for the given problem.
 int64_t ovb_gemm_ws_bytes(int T, int N, int K, int act);
 int ovb_gemm_num_counters(void);
+/* Conditional compilation: bit (log2(token tile) - 4) of the result is set when the GEMM variant (tile, wmode, fp16) has been
+   launched in this process; ovb_cc_is_selective tells whether the library is a selective build. */
+unsigned ovb_cc_used_gemm(int wmode, int is_f16);
+int ovb_cc_is_selective(void);
 
 // Re-pack IR-layout u4 weights (LSB-first nibbles, [N, K]) into the plugin layout read by the
 // dequantising GEMM, and build the transposed table of (bf16 scale, bf16 16+zero point) pairs.

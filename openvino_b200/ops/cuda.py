@@ -82,6 +82,8 @@ def lib():
         l.ovb_paged_attention.argtypes = [C.POINTER(PaArgs), C.c_void_p]
         l.ovb_status_read.argtypes = [C.c_void_p]
         _lib = l
+        if os.environ.get("OVB_CC_COLLECT"):       # conditional compilation, analysing stage: statistics at shutdown
+            from ..utils import cc as _cc   # noqa: F401
     return _lib
 
 
