@@ -131,6 +131,18 @@ class TFLiteFrontEnd(FrontEnd):
         return tflite.load(model)
 
 
+class PaddleFrontEnd(FrontEnd):
+    name = "paddle"
+
+    def supported(self, model) -> bool:
+        return isinstance(model, (str, os.PathLike)) and str(model).lower().endswith(".pdmodel")
+
+    def convert(self, input_model) -> Model:
+        from . import paddle
+        model, weights = input_model
+        return paddle.load(str(model), str(weights) if isinstance(weights, (str, os.PathLike)) else None)
+
+
 class GgufFrontEnd(FrontEnd):
     name = "gguf"
 
@@ -148,7 +160,7 @@ class GgufFrontEnd(FrontEnd):
 class FrontEndManager:
     def __init__(self):
         self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "tf": TensorFlowFrontEnd(), "tflite": TFLiteFrontEnd(),
-                           "gguf": GgufFrontEnd()}
+                           "paddle": PaddleFrontEnd(), "gguf": GgufFrontEnd()}
 
     def get_available_front_ends(self) -> List[str]:
         return list(self._frontends)
