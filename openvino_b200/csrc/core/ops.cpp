@@ -15,6 +15,7 @@ void register_eval_functions();
 // More operations, registered together with their reference evaluation (ops_ext.cpp)
 void register_ext_ops();
 void register_internal_ops();
+void register_vision_ops();
 
 namespace {
 
@@ -1129,6 +1130,7 @@ void register_all_ops() {
         register_eval_functions();
         register_ext_ops();
         register_internal_ops();
+        register_vision_ops();
     });
 }
 

@@ -21,6 +21,14 @@ from ._types import PartialShape, Type
 
 _SPEC = """
 identity Identity : data
+nv12_to_rgb NV12toRGB : arg [arg_uv]
+nv12_to_bgr NV12toBGR : arg [arg_uv]
+i420_to_rgb I420toRGB : arg [arg_u] [arg_v]
+i420_to_bgr I420toBGR : arg [arg_u] [arg_v]
+prior_box_clustered PriorBoxClustered : output_size image_size | width height step=0.0 step_w=0.0 step_h=0.0 clip=True offset=0.0 variance=[]
+psroi_pooling PSROIPooling : input coords | output_dim group_size spatial_scale spatial_bins_x=1 spatial_bins_y=1 mode=average
+fake_convert FakeConvert : data scale [shift] | destination_type=f8e4m3
+sparse_fill_empty_rows SparseFillEmptyRows : values dense_shape indices default_value
 extract_image_patches ExtractImagePatches : image | sizes strides rates auto_pad=valid
 region_yolo RegionYolo : input | coords classes num>num do_softmax mask axis end_axis anchors=[]
 ctc_loss CTCLoss : logits logit_length labels label_length [blank_index] | preprocess_collapse_repeated=False ctc_merge_repeated=True unique=False

@@ -153,3 +153,83 @@ def test_moe_compressed_equals_moe_on_dequantised_weights():
     a = run([mc], [px, pr, pi], [x, rw, idx])[0]
     b = ov.compile_model(ov.Model([mf], [px, pr, pi], "f"), "CPU")([x, rw, idx])[0]
     np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-5)
+
+
+def _yuv_ref(y, u, v):
+    c, d, e = y - 16.0, u - 128.0, v - 128.0
+    clip = lambda a: np.clip(np.round(a), 0, 255)
+    return clip(1.164 * c + 1.596 * e), clip(1.164 * c - 0.391 * d - 0.813 * e), clip(1.164 * c + 2.018 * d)
+
+
+def test_colour_conversions_from_nv12_and_i420():
+    rng = np.random.default_rng(6)
+    H, W = 4, 6
+    y = rng.integers(16, 235, (1, H, W, 1), dtype=np.uint8)
+    u = rng.integers(16, 240, (1, H // 2, W // 2, 1), dtype=np.uint8)
+    v = rng.integers(16, 240, (1, H // 2, W // 2, 1), dtype=np.uint8)
+    uu, vv = np.repeat(np.repeat(u, 2, 1), 2, 2).astype(np.float32), np.repeat(np.repeat(v, 2, 1), 2, 2).astype(np.float32)
+    r, g, b = _yuv_ref(y.astype(np.float32), uu, vv)
+    rgb = np.concatenate([r, g, b], -1).astype(np.uint8)
+    py, pu, pv = ops.parameter([1, H, W, 1], "u8"), ops.parameter([1, H // 2, W // 2, 1], "u8"), ops.parameter([1, H // 2, W // 2, 1], "u8")
+    np.testing.assert_array_equal(run([ops.i420_to_rgb(py, pu, pv)], [py, pu, pv], [y, u, v])[0], rgb)
+    np.testing.assert_array_equal(run([ops.i420_to_bgr(py, pu, pv)], [py, pu, pv], [y, u, v])[0], rgb[..., ::-1])
+    puv = ops.parameter([1, H // 2, W // 2, 2], "u8")
+    uv = np.concatenate([u, v], -1)
+    np.testing.assert_array_equal(run([ops.nv12_to_rgb(py, puv)], [py, puv], [y, uv])[0], rgb)
+    # one plane holding the whole frame: Y rows, then the interleaved UV rows
+    frame = np.concatenate([y.reshape(1, H, W), uv.reshape(1, H // 2, W)], 1)[..., None]
+    pf = ops.parameter([1, H * 3 // 2, W, 1], "u8")
+    n = ops.nv12_to_bgr(pf)
+    assert list(n.get_output_shape(0)) == [1, H, W, 3]
+    np.testing.assert_array_equal(run([n], [pf], [frame])[0], rgb[..., ::-1])
+
+
+def test_prior_box_clustered():
+    n = ops.prior_box_clustered(np.array([2, 3], np.int64), np.array([20, 30], np.int64), [4.0, 8.0], [6.0, 2.0], offset=0.5, variance=[0.1, 0.1, 0.2, 0.2])
+    assert list(n.get_output_shape(0)) == [2, 2 * 3 * 2 * 4]
+    out = run([n], [], [])[0].reshape(2, 2, 3, 2, 4)
+    # cell (h=1, w=2), second prior: centre (2.5 * 10, 1.5 * 10) in a 30 x 20 image
+    np.testing.assert_allclose(out[0, 1, 2, 1], [(25 - 4) / 30, (15 - 1) / 20, (25 + 4) / 30, (15 + 1) / 20], rtol=1e-6)
+    np.testing.assert_allclose(out[1, 0, 0, 0], [0.1, 0.1, 0.2, 0.2], rtol=1e-6)
+    assert out[0].min() >= 0 and out[0].max() <= 1
+
+
+def test_psroi_pooling_average():
+    rng = np.random.default_rng(7)
+    G, Cout = 2, 3
+    x = rng.standard_normal((1, Cout * G * G, 8, 8)).astype(np.float32)
+    rois = np.array([[0, 0, 0, 7, 7], [0, 2, 2, 5, 5]], np.float32)
+    px, pr = ops.parameter(list(x.shape), "f32"), ops.parameter([2, 5], "f32")
+    n = ops.psroi_pooling(px, pr, Cout, G, 1.0)
+    out = run([n], [px, pr], [x, rois])[0]
+    assert out.shape == (2, Cout, G, G)
+    # first ROI covers the whole map: bin (ph, pw) of output channel c averages a 4 x 4 quadrant of input channel (c * G + ph) * G + pw
+    for c in range(Cout):
+        for ph in range(G):
+            for pw in range(G):
+                want = x[0, (c * G + ph) * G + pw, ph * 4:(ph + 1) * 4, pw * 4:(pw + 1) * 4].mean()
+                assert abs(out[0, c, ph, pw] - want) < 1e-5
+    want = x[0, (1 * G + 1) * G + 0, 4:6, 2:4].mean()          # second ROI (2..5 -> 4 cells per side), channel 1, bin (1, 0)
+    assert abs(out[1, 1, 1, 0] - want) < 1e-5
+
+
+def test_fake_convert_is_an_fp8_round_trip():
+    x = np.array([[0.3, -1.7, 100.0, 1e-3], [5.5, 7.3, -0.02, 200.0]], np.float32)
+    p = ops.parameter([2, 4], "f32")
+    out = run([ops.fake_convert(p, np.array([2.0], np.float32))], [p], [x])[0]
+    want = torch.from_numpy(x * 2).to(torch.float8_e4m3fn).float().numpy() / 2
+    np.testing.assert_allclose(out, want, rtol=1e-6)
+    out5 = run([ops.fake_convert(p, np.array([1.0], np.float32), np.array([0.0], np.float32), "f8e5m2")], [p], [x])[0]
+    np.testing.assert_allclose(out5, torch.from_numpy(x).to(torch.float8_e5m2).float().numpy(), rtol=1e-6)
+
+
+def test_sparse_fill_empty_rows():
+    vals = np.array([1.0, 2.0, 3.0], np.float32)
+    idx = np.array([[0, 1], [3, 0], [0, 3]], np.int64)
+    pv, pi = ops.parameter([3], "f32"), ops.parameter([3, 2], "i64")
+    n = ops.sparse_fill_empty_rows(pv, np.array([5, 4], np.int64), pi, np.float32(-1))
+    res = run([n.output(0), n.output(1), n.output(2)], [pv, pi], [vals, idx])
+    oi, ov_, empty = res[0], res[1], res[2]
+    np.testing.assert_array_equal(oi, [[0, 1], [0, 3], [1, 0], [2, 0], [3, 0], [4, 0]])
+    np.testing.assert_array_equal(ov_, [1, 3, -1, -1, 2, -1])
+    np.testing.assert_array_equal(empty, [False, True, True, False, True])
