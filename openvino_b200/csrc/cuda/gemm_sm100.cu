@@ -334,18 +334,17 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // the offsets come from an earlier kernel of the stream: nothing of this CTA may run before that kernel is done
         pdl_wait();
         const int tiles_n = (p.N + TILE_N - 1) / TILE_N;
-        n_tile = cta % tiles_n;
-        const int tt = cta / tiles_n;
         int g = 0, acc = 0, begin = 0, end = 0;
         for (; g < p.num_groups; ++g) {
             begin = __ldg(p.group_off + g);
             end = __ldg(p.group_off + g + 1);
-            const int nt = (end - begin + BT - 1) / BT;
-            if (tt < acc + nt) break;
-            acc += nt;
+            const int cnt = ((end - begin + BT - 1) / BT) * tiles_n;
+            if (cta < acc + cnt) break;
+            acc += cnt;
         }
-        if (g == p.num_groups) return;      // more CTAs than row tiles (the grid is sized for the worst case); uniform over the CTA
-        t_tile = tt - acc;
+        if (g == p.num_groups) return;      // more CTAs than tiles (the grid is sized for the worst case); uniform over the CTA
+        // inside a group the same banded order as the plain GEMM: resident CTAs share a few weight tiles and a few row tiles
+        tile_coords(cta - acc, p.N, end - begin, BT, n_tile, t_tile);
         t0 = begin + t_tile * BT;
         T_end = min(end, p.T);
         w_tile = p.group_mode == 1 ? g * tiles_n + n_tile : n_tile;

@@ -96,6 +96,37 @@ struct Dims {
     int64_t sb[OVB_MAX_DIMS];
 };
 
+// Offsets of flat index i in both operands. 32-bit index arithmetic when the element count allows it (64-bit division is
+// an order of magnitude slower and would bound the copy).
+__device__ __forceinline__ void offsets_of(size_t i, bool small, const Dims& d, int64_t& oa, int64_t& ob) {
+    oa = 0;
+    ob = 0;
+    if (small) {
+        uint32_t r = (uint32_t)i;
+#pragma unroll
+        for (int k = OVB_MAX_DIMS - 1; k >= 0; --k) {
+            if (k < d.nd) {
+                const uint32_t q = r / (uint32_t)d.shape[k];
+                const uint32_t c = r - q * (uint32_t)d.shape[k];
+                r = q;
+                oa += (int64_t)c * d.sa[k];
+                ob += (int64_t)c * d.sb[k];
+            }
+        }
+    } else {
+        size_t r = i;
+#pragma unroll
+        for (int k = OVB_MAX_DIMS - 1; k >= 0; --k) {
+            if (k < d.nd) {
+                const int c = int(r % d.shape[k]);
+                r /= d.shape[k];
+                oa += c * d.sa[k];
+                ob += c * d.sb[k];
+            }
+        }
+    }
+}
+
 template <class T>
 __global__ void binary_same_kernel(int op, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, size_t n) {
     pdl_enter();
@@ -118,18 +149,10 @@ template <class T>
 __global__ void binary_bcast_kernel(int op, const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, size_t n, Dims d) {
     pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const bool small = n <= 0xFFFFFFFFull;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += stride) {
-        size_t r = i;
-        int64_t oa = 0, ob = 0;
-#pragma unroll
-        for (int k = OVB_MAX_DIMS - 1; k >= 0; --k) {
-            if (k < d.nd) {
-                const int c = int(r % d.shape[k]);
-                r /= d.shape[k];
-                oa += c * d.sa[k];
-                ob += c * d.sb[k];
-            }
-        }
+        int64_t oa, ob;
+        offsets_of(i, small, d, oa, ob);
         y[i] = from_f<T>(binary_apply(op, to_f(a[oa]), to_f(b[ob])));
     }
 }
@@ -142,18 +165,10 @@ template <class T>
 __global__ void strided_copy_kernel(const T* __restrict__ x, T* __restrict__ y, size_t n, Dims d) {
     pdl_enter();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const bool small = n <= 0xFFFFFFFFull;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += stride) {
-        size_t r = i;
-        int64_t oa = 0, ob = 0;
-#pragma unroll
-        for (int k = OVB_MAX_DIMS - 1; k >= 0; --k) {
-            if (k < d.nd) {
-                const int c = int(r % d.shape[k]);
-                r /= d.shape[k];
-                oa += c * d.sa[k];
-                ob += c * d.sb[k];
-            }
-        }
+        int64_t oa, ob;
+        offsets_of(i, small, d, oa, ob);
         y[ob] = x[oa];
     }
 }
@@ -413,6 +428,10 @@ int ovb_strided_copy(const void* x, void* y, int nd, const int64_t* shape, const
         case 2: OVB_CHECK_CUDA(launch_pdl(strided_copy_kernel<uint16_t>, g, b, 0, stream, (const uint16_t*)x, (uint16_t*)y, n, d)); break;
         case 4: OVB_CHECK_CUDA(launch_pdl(strided_copy_kernel<uint32_t>, g, b, 0, stream, (const uint32_t*)x, (uint32_t*)y, n, d)); break;
         case 8: OVB_CHECK_CUDA(launch_pdl(strided_copy_kernel<uint64_t>, g, b, 0, stream, (const uint64_t*)x, (uint64_t*)y, n, d)); break;
+        case 16:
+            OVB_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0, "ovb_strided_copy: 16-byte units need 16-byte aligned tensors");
+            OVB_CHECK_CUDA(launch_pdl(strided_copy_kernel<uint4>, g, b, 0, stream, (const uint4*)x, (uint4*)y, n, d));
+            break;
         default: OVB_REQUIRE(false, "ovb_strided_copy: element size %d", elem_bytes);
     }
     return 0;

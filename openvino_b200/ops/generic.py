@@ -108,7 +108,19 @@ def strided_copy(src: torch.Tensor, dst: torch.Tensor) -> None:
     cs, (sx, sy) = _collapse(shape, [list(src.stride()) or [0], list(dst.stride()) or [0]])
     if len(cs) > MAX_DIMS:
         _too_many_dims()
-    K._check(K.lib().ovb_strided_copy(_p(src), _p(dst), C.c_int(len(cs)), _i64(cs), _i64(sx), _i64(sy), C.c_int(src.element_size()),
+    es = src.element_size()
+    # rows that are contiguous on both sides move as 16-byte (or 8- / 4-byte) units: the innermost run is re-expressed in
+    # wider elements when its length, the other strides and both base addresses allow it
+    if sx[-1] == 1 and sy[-1] == 1:
+        for unit in (16, 8, 4):
+            k = unit // es
+            if k > 1 and cs[-1] % k == 0 and all(v % k == 0 for v in sx[:-1] + sy[:-1]) and src.data_ptr() % unit == 0 and dst.data_ptr() % unit == 0:
+                cs = cs[:-1] + [cs[-1] // k]
+                sx = [v // k for v in sx[:-1]] + [1]
+                sy = [v // k for v in sy[:-1]] + [1]
+                es = unit
+                break
+    K._check(K.lib().ovb_strided_copy(_p(src), _p(dst), C.c_int(len(cs)), _i64(cs), _i64(sx), _i64(sy), C.c_int(es),
                                       C.c_void_p(K._stream())), "ovb_strided_copy")
 
 

@@ -87,6 +87,19 @@ def _same_device(ctx: Ctx, ins: Sequence[torch.Tensor]) -> List[torch.Tensor]:
     return [t if t.is_cuda else t.to(ctx.device, non_blocking=True) for t in ins]
 
 
+def _dense(t: torch.Tensor) -> torch.Tensor:
+    """``t`` laid out densely: the package's tile-transpose / strided-copy kernels for device tensors of the types they
+    serve, the library's copy otherwise."""
+    if t.is_contiguous():
+        return t
+    if G.enabled() and t.is_cuda and t.numel() > 0 and t.element_size() in (1, 2, 4, 8):
+        try:
+            return G.contiguous(t)
+        except NotImplementedError:
+            pass
+    return t.contiguous()
+
+
 def _native(*ts) -> bool:
     """Floating-point device tensors go to the package's own generic kernels (ops/generic.py); integer / boolean tensors
     and host-side values keep the torch expression."""
@@ -260,6 +273,11 @@ def _reshape(n, ins, ctx):
     pattern = _ints(ins[1])
     if n.get_attribute("special_zero"):
         pattern = [x.shape[i] if d == 0 else d for i, d in enumerate(pattern)]
+    if not x.is_contiguous():
+        try:
+            return [x.view(pattern)]            # a permuted tensor whose new shape is still a view
+        except RuntimeError:
+            x = _dense(x)
     return [x.reshape(pattern)]
 
 
@@ -290,13 +308,9 @@ def _transpose(n, ins, ctx):
     order = _ints(ins[1])
     if not order:
         order = list(range(ins[0].dim() - 1, -1, -1))
-    v = ins[0].permute(order)
-    if _native(v):
-        try:
-            return [G.contiguous(v)]        # materialised by the tile-transpose / strided-copy kernels
-        except NotImplementedError:
-            pass
-    return [v]
+    # a view: the consumer decides whether the permuted order is ever materialised (the attention and FullyConnected
+    # operations read strided rows; element-wise, softmax and reduction kernels call _dense)
+    return [ins[0].permute(order)]
 
 
 @op("Concat")
@@ -788,7 +802,7 @@ def _rms(n, ins, ctx):
     gamma = ins[1].to(x.device) if len(ins) > 1 else None
     eps = n.get_attribute("epsilon")
     if ctx.K is not None and x.dtype == torch.bfloat16 and gamma is not None and gamma.dim() == 1 and x.shape[-1] == gamma.numel() and x.shape[-1] % 8 == 0:
-        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        x2 = _dense(x.reshape(-1, x.shape[-1]))
         return [ctx.K.rmsnorm(x2, gamma.to(torch.bfloat16).contiguous(), eps).reshape(x.shape)]
     xf = x.float()
     y = xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps)
@@ -822,7 +836,7 @@ def _sdpa(n, ins, ctx):
             and q.shape == k.shape == v.shape and len(ins) <= 5):
         B, H, S, D = q.shape
         # kernel layout: [B*S, H*D] rows with head h at column h*D
-        pack = lambda t: t.transpose(1, 2).reshape(B * S, H * D).contiguous()
+        pack = lambda t: _dense(t.transpose(1, 2)).reshape(B * S, H * D)
         out = K.sdpa_dense(pack(q), pack(k), pack(v), B, S, H, D, H * D, scale=scale, causal=bool(causal))
         return [out.reshape(B, S, H, D).transpose(1, 2)]
     return [F.scaled_dot_product_attention(q, k.to(q.dtype), v.to(q.dtype), attn_mask=None if causal else mask, is_causal=bool(causal) and mask is None, scale=scale)]
@@ -901,7 +915,7 @@ def _fc(n, ins, ctx):
     if pw is not None and x.dtype in (torch.float16, torch.bfloat16) and (pw.mode != ctx.K.W_F16) == (x.dtype == torch.bfloat16):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
-            x2 = x2.contiguous()
+            x2 = _dense(x2)
         act = st.get("act")
         fused = act is not None and not (has_bias and pw.bias is None)      # the epilogue order is bias, then activation
         out = ctx.K.gemm(x2, pw, act=_GEMM_ACTS[act] if fused else 0)
@@ -930,7 +944,7 @@ def _layer_norm_fused(n, ins, ctx):
     if ctx.K is not None and x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.shape[-1] % 8 == 0:
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
-            x2 = x2.contiguous()
+            x2 = _dense(x2)
         out = ctx.K.layernorm(x2, g.to(x.device, x.dtype).contiguous(), b.to(x.device, x.dtype).contiguous(), eps)
         return [out.reshape(x.shape)]
     return [F.layer_norm(x, [x.shape[-1]], g.to(x.device, x.dtype), b.to(x.device, x.dtype), eps)]
@@ -1368,7 +1382,7 @@ class CudaCompiledModel(CompiledModel):
                     pinned[i] = host
                 host.copy_(o, non_blocking=True)
             else:
-                host = o.contiguous()
+                host = _dense(o)
             if host.dtype == torch.bfloat16:
                 res.append(Tensor(host))
             else:
