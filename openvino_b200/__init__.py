@@ -11,7 +11,8 @@ except ImportError:   # first import of a fresh checkout: compile the native cor
     _build_core()
     from . import _ovcore   # noqa: F401
 
-from ._types import Dimension, PartialShape, Shape, Type, get_element_type   # noqa: F401
+from ._types import Dimension, PartialShape, Shape, Symbol, Type, get_element_type   # noqa: F401
+from . import symbol   # noqa: F401
 from ._tensor import Tensor   # noqa: F401
 from ._graph import Input, Model, Node, Output, RTMap   # noqa: F401
 from ._op_base import DiscreteTypeInfo, Op, register_op   # noqa: F401
@@ -29,7 +30,7 @@ from .runtime.core import (AsyncInferQueue, CompiledModel, Core, InferRequest, O
 from .utils.shutdown import register_shutdown_callback, shutdown, unregister_shutdown_callback   # noqa: F401
 
 __all__ = ["AsyncInferQueue", "CompiledModel", "Core", "Dimension", "FrontEndManager", "InferRequest", "Input", "Layout", "Model", "Node",
-           "OVDict", "Output", "PartialShape", "ProfilingInfo", "RTMap", "Shape", "Tensor", "Type", "VariableState", "Version", "compile_model",
+           "OVDict", "Output", "PartialShape", "ProfilingInfo", "RTMap", "Shape", "Symbol", "Tensor", "Type", "VariableState", "Version", "compile_model",
            "convert_model", "get_element_type", "layout_helpers", "opset", "passes", "preprocess", "properties", "read_model", "register_shutdown_callback",
            "save_model", "serialize", "shutdown", "unregister_shutdown_callback"]
 

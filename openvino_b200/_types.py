@@ -109,14 +109,49 @@ def get_element_type(x) -> Type:
     return Type(x)
 
 
+class Symbol:
+    """Identity of a dynamic dimension's run-time value: dimensions whose symbols compare equal are known to be the same
+    size. ``Symbol()`` makes a fresh one; shape inference makes symbols equal where operands must agree
+    (``ov::Symbol``, src/core/include/openvino/core/symbol.hpp)."""
+
+    __slots__ = ("id",)
+
+    def __init__(self, _id: int = 0):
+        from . import _ovcore as _c
+        self.id = int(_id) if _id else int(_c.new_symbol())
+
+    def root(self) -> int:
+        from . import _ovcore as _c
+        return int(_c.symbol_root(self.id))
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, Symbol) and self.root() == other.root()
+
+    def __hash__(self) -> int:
+        return hash(("Symbol", self.id))
+
+    def __repr__(self) -> str:
+        return "<Symbol %d>" % self.root()
+
+
 class Dimension:
     """A dimension: static value, interval, or fully dynamic (``Dimension()`` / ``Dimension(-1)``)."""
 
-    __slots__ = ("lo", "hi")
+    __slots__ = ("lo", "hi", "sym")
+
+    def has_symbol(self) -> bool:
+        return bool(self.sym) and self.is_dynamic
+
+    def get_symbol(self):
+        return Symbol(self.sym) if self.has_symbol() else None
+
+    def set_symbol(self, symbol) -> None:
+        self.sym = symbol.id if symbol is not None else 0
 
     def __init__(self, a=None, b=None):
+        self.sym = 0
         if isinstance(a, Dimension):
-            self.lo, self.hi = a.lo, a.hi
+            self.lo, self.hi, self.sym = a.lo, a.hi, a.sym
         elif isinstance(a, str):
             s = a.strip()
             if s in ("?", "-1"):
@@ -235,10 +270,16 @@ class PartialShape:
     def _from_core(raw) -> "PartialShape":
         if raw is None:
             return PartialShape.dynamic()
-        return PartialShape([Dimension(l, h) for l, h in raw])
+        dims = []
+        for item in raw:
+            d = Dimension(item[0], item[1])
+            if len(item) > 2:
+                d.sym = int(item[2])
+            dims.append(d)
+        return PartialShape(dims)
 
     def _to_core(self):
-        return None if self._rank_dynamic else [(d.lo, d.hi) for d in self._dims]
+        return None if self._rank_dynamic else [(d.lo, d.hi, d.sym) if d.sym else (d.lo, d.hi) for d in self._dims]
 
     @property
     def rank(self) -> Dimension:

@@ -50,6 +50,7 @@ PShape pshape_from_py(const py::handle& h) {
         if (py::isinstance<py::tuple>(item) || py::isinstance<py::list>(item)) {
             auto t = py::cast<std::vector<int64_t>>(item);
             p.dims.emplace_back(t.at(0), t.at(1));
+            if (t.size() > 2 && p.dims.back().is_dynamic()) p.dims.back().sym = t[2];
         } else {
             p.dims.emplace_back(py::cast<int64_t>(item));
         }
@@ -59,7 +60,10 @@ PShape pshape_from_py(const py::handle& h) {
 py::object pshape_to_py(const PShape& s) {
     if (s.rank_dynamic) return py::none();
     py::list l;
-    for (auto& d : s.dims) l.append(py::make_tuple(d.lo, d.hi));
+    for (auto& d : s.dims) {
+        if (d.sym) l.append(py::make_tuple(d.lo, d.hi, d.sym));
+        else l.append(py::make_tuple(d.lo, d.hi));
+    }
     return std::move(l);
 }
 
@@ -225,6 +229,9 @@ PYBIND11_MODULE(_ovcore, mod) {
         return PyTensor::pack(convert_tensor(t, et_from_name(to)));
     });
     mod.def("pshape_to_string", [](const py::object& s) { return pshape_from_py(s).str(); });
+    mod.def("new_symbol", &new_symbol);
+    mod.def("symbol_root", &symbol_root);
+    mod.def("symbols_set_equal", &symbols_set_equal);
     mod.def("pshape_parse", [](const std::string& s) { return pshape_to_py(PShape::parse(s)); });
 
     // ------------------------------------------------------------------ Node

@@ -77,7 +77,8 @@ PShape broadcast_numpy(const PShape& a, const PShape& b, const Node& n) {
         } else {
             // both dynamic: the result is at least the larger lower bound; 1 may broadcast
             Dim m;
-            if (Dim::merge(m, da, db) && da.lo > 1 && db.lo > 1) d = m;
+            if (symbols_equal(da.sym, db.sym)) d = da;       // known to be the same value: nothing broadcasts
+            else if (Dim::merge(m, da, db) && da.lo > 1 && db.lo > 1) d = m;
             else d = Dim(std::max<int64_t>(std::min(da.lo, db.lo), 0), (da.hi < 0 || db.hi < 0) ? -1 : std::max(da.hi, db.hi));
         }
         out.dims[i] = d;

@@ -1,5 +1,7 @@
 #include "types.hpp"
 
+#include <mutex>
+
 #include <cstdio>
 
 namespace ovc {
@@ -298,6 +300,36 @@ Attr Attr::from_string(Kind k, const std::string& v) {
         case PSHAPE: return Shape_(PShape::parse(v));
         default: return Str(v);
     }
+}
+
+// ---- symbol table: union-find over symbol ids (1-based; id 0 = no symbol)
+namespace {
+std::mutex g_sym_mu;
+std::vector<int64_t> g_sym_parent{0};
+int64_t sym_find(int64_t s) {
+    while (g_sym_parent[(size_t)s] != s) {
+        g_sym_parent[(size_t)s] = g_sym_parent[(size_t)g_sym_parent[(size_t)s]];
+        s = g_sym_parent[(size_t)s];
+    }
+    return s;
+}
+}  // namespace
+
+int64_t new_symbol() {
+    std::lock_guard<std::mutex> lk(g_sym_mu);
+    g_sym_parent.push_back((int64_t)g_sym_parent.size());
+    return (int64_t)g_sym_parent.size() - 1;
+}
+int64_t symbol_root(int64_t sym) {
+    std::lock_guard<std::mutex> lk(g_sym_mu);
+    if (sym <= 0 || sym >= (int64_t)g_sym_parent.size()) return 0;
+    return sym_find(sym);
+}
+void symbols_set_equal(int64_t a, int64_t b) {
+    std::lock_guard<std::mutex> lk(g_sym_mu);
+    if (a <= 0 || b <= 0 || a >= (int64_t)g_sym_parent.size() || b >= (int64_t)g_sym_parent.size()) return;
+    const int64_t ra = sym_find(a), rb = sym_find(b);
+    if (ra != rb) g_sym_parent[(size_t)std::max(ra, rb)] = std::min(ra, rb);
 }
 
 }  // namespace ovc

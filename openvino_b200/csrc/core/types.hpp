@@ -110,9 +110,19 @@ inline int64_t shape_size(const Shape& s) {
     return n;
 }
 
+// Symbols: a dynamic dimension may carry a symbol; dimensions whose symbols are equal (same class of the table below) are
+// known to have the same run-time value. Shape inference copies dimensions, so a symbol travels with its dimension; merging
+// two dimensions (Concat / element-wise operands that must agree) makes their symbols equal. Role in the reference:
+// ov::Symbol and ov::symbol::set_equal / are_equal, src/core/include/openvino/core/symbol.hpp.
+int64_t new_symbol();
+int64_t symbol_root(int64_t sym);
+void symbols_set_equal(int64_t a, int64_t b);
+inline bool symbols_equal(int64_t a, int64_t b) { return a != 0 && b != 0 && symbol_root(a) == symbol_root(b); }
+
 struct Dim {
     int64_t lo = 0;
     int64_t hi = -1;   // -1: unbounded
+    int64_t sym = 0;   // 0: no symbol
     Dim() = default;
     Dim(int64_t v) : lo(v < 0 ? 0 : v), hi(v < 0 ? -1 : v) {}
     Dim(int64_t l, int64_t h) : lo(l), hi(h) {}
@@ -132,7 +142,12 @@ struct Dim {
         const int64_t l = std::max(a.lo, b.lo);
         const int64_t h = (a.hi < 0) ? b.hi : (b.hi < 0 ? a.hi : std::min(a.hi, b.hi));
         if (h >= 0 && l > h) return false;
+        const int64_t sa = a.sym, sb = b.sym;
         dst = Dim(l, h);
+        if (dst.is_dynamic()) {
+            dst.sym = sa ? sa : sb;
+            if (sa && sb && sa != sb) symbols_set_equal(sa, sb);      // the two dimensions must agree: one class from now on
+        }
         return true;
     }
     std::string str() const;   // "3", "-1" / "?" handled by callers, "1..8", "..8", "2.."

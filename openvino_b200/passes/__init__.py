@@ -151,6 +151,31 @@ class CompressWeights(_NamedPass):
         super().__init__(mode=mode, group_size=group_size, ratio=ratio, all_layers=all_layers)
 
 
+class SymbolicPropagation(ModelPass):
+    """Gives every dynamic dimension of the model's Parameters a fresh symbol (dimensions that already carry one keep
+    it) and re-runs shape inference, so that the symbols travel to every value that inherits the dimension; where
+    operands must agree (Concat, element-wise with equal dimensions) their symbols become one class
+    (src/common/transformations/src/transformations/symbolic_transformations/symbolic_optimizations.cpp, SymbolicPropagation)."""
+
+    def run_on_model(self, model) -> bool:
+        from .._types import Symbol
+        shapes = {}
+        for i, p in enumerate(model.get_parameters()):
+            ps = p.get_output_partial_shape(0)
+            if ps.rank.is_dynamic:
+                continue
+            touched = False
+            for d in ps:
+                if d.is_dynamic and not d.has_symbol():
+                    d.set_symbol(Symbol())
+                    touched = True
+            if touched:
+                shapes[i] = ps
+        if shapes:
+            model.reshape(shapes)            # re-runs shape inference: the symbols travel with the dimensions
+        return bool(shapes)
+
+
 class MakeStateful(ModelPass):
     """Turn (Parameter, Result) pairs into ReadValue/Assign. Pairs are tensor names or nodes."""
 

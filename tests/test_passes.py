@@ -385,3 +385,33 @@ def test_lora_subgraph_fusion_keeps_adapters_switchable():
     for st in req.query_state():
         st.state = ov.Tensor({"lora_A": a1, "lora_alpha": np.ones((1, 2), np.float32), "lora_B": b1}[st.name])
     np.testing.assert_allclose(req.infer([xin])[0], xin @ w.T + (xin @ a1.T) @ b1.T, rtol=1e-4, atol=1e-5)
+
+
+def test_symbols_travel_with_dynamic_dimensions():
+    """Dynamic dimensions carry symbols through shape inference; where operands must agree their symbols become one."""
+    a = ops.parameter(ov.PartialShape([-1, 16]), "f32", "a")
+    b = ops.parameter(ov.PartialShape([-1, 16]), "f32", "b")
+    w = np.ones((8, 16), np.float32)
+    ya = ops.matmul(ops.relu(a), w, False, True)                       # [?, 8]: keeps a's batch symbol
+    yb = ops.reshape(b, np.array([0, 4, 4], np.int64), True)           # [?, 4, 4]: keeps b's batch symbol
+    cat = ops.concat([a.output(0), b.output(0)], 1)                    # rows must agree: a's and b's symbols become equal
+    m = ov.Model([ya, yb, cat], [a, b], "sym")
+    assert not m.input(0).get_partial_shape()[0].has_symbol()
+    _run_pass(m, passes.SymbolicPropagation())
+    sa, sb = m.input(0).get_partial_shape()[0].get_symbol(), m.input(1).get_partial_shape()[0].get_symbol()
+    assert sa is not None and sb is not None
+    assert m.output(0).get_partial_shape()[0].get_symbol() == sa and not m.output(0).get_partial_shape()[1].has_symbol()
+    assert m.output(1).get_partial_shape()[0].get_symbol() == sb
+    assert ov.symbol.are_equal(sa, sb)                                  # through the Concat
+    assert m.output(2).get_partial_shape()[0].get_symbol() == sa
+    # fresh symbols are unrelated until they are declared equal
+    s1, s2 = ov.Symbol(), ov.Symbol()
+    assert s1 != s2 and not ov.symbol.are_equal(s1, s2)
+    ov.symbol.set_equal(s1, s2)
+    assert s1 == s2 and ov.symbol.ancestor_of(s2) == s1
+    # static dimensions never carry one; serialisation ignores symbols
+    d = ov.Dimension(4)
+    d.set_symbol(s1)
+    assert not d.has_symbol()
+    xml, _ = ov._ovcore.serialize(m._m)
+    assert b"Symbol" not in xml
