@@ -57,11 +57,19 @@ def cuda_sources() -> list[Path]:
     return sorted((CSRC / "cuda").glob("*.cu"))
 
 
-def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+def build_cuda_debug(force: bool = False) -> Path:
+    """The bounds-checking debug build of the kernels: ``lib/libovb_cuda_dbg.so`` (compiled with -DOVB_DEBUG_BOUNDS, objects
+    under ``build/dbg``). Load it with ``OVB_CUDA_LIB``; see csrc/cuda/debug_bounds.cuh."""
+    return build_cuda(force, False, ("-DOVB_DEBUG_BOUNDS",), "_dbg")
+
+
+def build_cuda(force: bool = False, verbose: bool = False, extra_flags=(), suffix: str = "") -> Path:
     """Compile every .cu under csrc/cuda for sm_100a and link libovb_cuda.so."""
     LIB.mkdir(exist_ok=True)
     OBJ.mkdir(exist_ok=True)
-    target = LIB / "libovb_cuda.so"
+    target = LIB / ("libovb_cuda%s.so" % suffix)
+    obj_dir = OBJ / suffix.strip("_") if suffix else OBJ
+    obj_dir.mkdir(exist_ok=True)
     srcs = cuda_sources()
     hdrs = sorted((CSRC / "cuda").glob("*.cuh")) + sorted((CSRC / "cuda").glob("*.h"))
     if not force and not _stale(target, srcs + hdrs):
@@ -69,15 +77,15 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _nvcc()
 
     def compile_one(src: Path) -> Path:
-        obj = OBJ / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         if force or _stale(obj, [src] + hdrs):
             # ptxas reports registers, stack frame and spills of every kernel; the report is kept next to the object
             # (build/<name>.ptxas.txt) so that a resource regression of a hot kernel shows up without a GPU
-            cmd = [nvcc, "-Xptxas", "-v", *NVCC_FLAGS, "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, "-Xptxas", "-v", *NVCC_FLAGS, *extra_flags, "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
             r = subprocess.run(cmd, capture_output=True, text=True)
             if r.returncode != 0:
                 raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout[-4000:], r.stderr[-8000:]))
-            (OBJ / (src.stem + ".ptxas.txt")).write_text(r.stderr)
+            (obj_dir / (src.stem + ".ptxas.txt")).write_text(r.stderr)
             if verbose:
                 print(r.stderr)
         return obj
@@ -85,7 +93,7 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
     # only the C ABI is exported; everything else (C++ runtime templates, the static CUDA runtime) stays local
-    vers = OBJ / "ovb_cuda.map"
+    vers = obj_dir / "ovb_cuda.map"
     vers.write_text("{ global: ovb_*; local: *; };\n")
     _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-cudart", "static", "-Xlinker", "--version-script=%s" % vers])
     return target
@@ -271,6 +279,9 @@ if __name__ == "__main__":
     if cc:
         out = ([a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--cc-out=")] or [str(PKG / "lib_selective")])[0]
         print("built:", build_selective(cc[0], out))
+        sys.exit(0)
+    if "--debug-bounds" in sys.argv:
+        print("built:", build_cuda_debug(force="--force" in sys.argv))
         sys.exit(0)
     san = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--sanitize=")]
     if san:

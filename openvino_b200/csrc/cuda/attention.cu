@@ -20,9 +20,12 @@
 
 #include "attention.cuh"
 #include "common.cuh"
+#include "debug_bounds.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ovb {
+
+OVB_DEBUG_LIMITS_DEFINE
 
 // ------------------------------------------------------------------------------ small PTX helpers
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
@@ -79,7 +82,7 @@ template <int D, bool PAGED>
 __device__ __forceinline__ const uint8_t* kv_row_ptr(const PaKParams& p, const void* base, int b, int h, int j,
                                                      int blk_begin) {
     if (PAGED) {
-        const int blk = p.block_indices[blk_begin + j / p.block_size];
+        const int blk = OVB_DBG_BLOCK(p.block_indices[blk_begin + j / p.block_size]);
         const int off = j % p.block_size;
         return reinterpret_cast<const uint8_t*>(base) + ((((size_t)blk * p.Hkv + h) * p.block_size + off) * D) * 2;
     }
@@ -89,12 +92,12 @@ __device__ __forceinline__ const uint8_t* kv_row_ptr(const PaKParams& p, const v
 // u8 cache: address of the bytes of key/value row j, and of its (scale, zero point) pair.
 template <int D>
 __device__ __forceinline__ const uint8_t* kv_row_ptr_u8(const PaKParams& p, const void* base, int h, int j, int blk_begin) {
-    const int blk = p.block_indices[blk_begin + j / p.block_size];
+    const int blk = OVB_DBG_BLOCK(p.block_indices[blk_begin + j / p.block_size]);
     const int off = j % p.block_size;
     return reinterpret_cast<const uint8_t*>(base) + (((size_t)blk * p.Hkv + h) * p.block_size + off) * D;
 }
 __device__ __forceinline__ const uint8_t* kv_meta_ptr(const PaKParams& p, const void* meta, int h, int j, int blk_begin) {
-    const int blk = p.block_indices[blk_begin + j / p.block_size];
+    const int blk = OVB_DBG_BLOCK(p.block_indices[blk_begin + j / p.block_size]);
     const int off = j % p.block_size;
     return reinterpret_cast<const uint8_t*>(meta) + (((size_t)blk * p.Hkv + h) * p.block_size + off) * 4;
 }
@@ -392,7 +395,7 @@ __global__ void __launch_bounds__(128) pa_decode_kernel(PaKParams p) {
 
     auto load_page = [&](int page, int st) {
         const bool pv = page < page_hi;
-        const int blk = pv ? p.block_indices[blk_begin + page] : 0;
+        const int blk = pv ? OVB_DBG_BLOCK(p.block_indices[blk_begin + page]) : 0;
         if (KVU8) {
             // the page's bytes are contiguous (PAGE * D), so are its pairs (PAGE * 4)
             const size_t pg = (size_t)blk * p.Hkv + h;
@@ -644,6 +647,13 @@ static int decode_nsplit(int B, int Hkv, int max_ctx) {
 }
 
 }  // namespace ovb
+
+#ifdef OVB_DEBUG_BOUNDS
+extern "C" int ovb_debug_set_limits_attention(const ovb::DebugLimits* l) {
+    OVB_CHECK_CUDA(cudaMemcpyToSymbol(ovb::g_dbg_limits, l, sizeof(*l)));
+    return 0;
+}
+#endif
 
 extern "C" {
 using namespace ovb;

@@ -7,6 +7,7 @@
 #include <atomic>
 
 #include "common.cuh"
+#include "debug_bounds.cuh"
 
 namespace ovb {
 
@@ -112,6 +113,33 @@ unsigned ovb_set_peer_spin_limit(unsigned polls) {
     const unsigned before = ovb::peer_spin_limit();
     ovb::g_spin_limit.store(polls ? polls : (1u << 22), std::memory_order_relaxed);
     return before;
+}
+
+#ifdef OVB_DEBUG_BOUNDS
+int ovb_debug_set_limits_attention(const ovb::DebugLimits* l);
+int ovb_debug_set_limits_elementwise(const ovb::DebugLimits* l);
+#endif
+
+int ovb_debug_bounds_enabled(void) {
+#ifdef OVB_DEBUG_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+int ovb_debug_set_limits(int kv_blocks, int vocab) {
+#ifdef OVB_DEBUG_BOUNDS
+    ovb::DebugLimits l;
+    l.kv_blocks = kv_blocks;
+    l.vocab = vocab;
+    l.status = ovb::status_word();
+    if (int rc = ovb_debug_set_limits_attention(&l)) return rc;
+    return ovb_debug_set_limits_elementwise(&l);
+#else
+    (void)kv_blocks; (void)vocab;
+    return 0;
+#endif
 }
 
 const char* ovb_last_error(void) { return ovb::g_err; }

@@ -10,9 +10,12 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "debug_bounds.cuh"
 #include "sm100_ptx.cuh"
 
 namespace ovb {
+
+OVB_DEBUG_LIMITS_DEFINE
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -259,7 +262,10 @@ __global__ void embedding_kernel(const IdT* __restrict__ ids, const uint4* __res
         const size_t r = i / vec_per_row;
         const int c = int(i - r * vec_per_row);
         int64_t id = ids[r];
-        if (id < 0 || id >= vocab) id = 0;   // out-of-range ids read row 0 instead of faulting
+        if (id < 0 || id >= vocab) {         // out-of-range ids read row 0 instead of faulting (the debug build also reports them)
+            (void)OVB_DBG_ROW(-1, 1);
+            id = 0;
+        }
         out[i] = table[(size_t)id * vec_per_row + c];
     }
 }
@@ -360,7 +366,7 @@ __global__ void rope_kv_write_kernel(__nv_bfloat16* __restrict__ qkv, const int*
     const int t = blockIdx.x;
     const int half = D >> 1;
     const float pos = float(positions[t]);
-    const int slot = slot_map[t];
+    const int slot = OVB_DBG_SLOT(slot_map[t], block_size);
     const int blk = slot / block_size, off = slot - blk * block_size;
     __nv_bfloat16* row = qkv + (size_t)t * (Hq + 2 * Hkv) * D;
     const int pairs_q = Hq * half, pairs_k = Hkv * half;
@@ -408,7 +414,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
     const int lane = threadIdx.x & 31;
     if (h >= Hq + 2 * Hkv) return;
     const int half = D >> 1;
-    const int slot = slot_map[t];
+    const int slot = OVB_DBG_SLOT(slot_map[t], block_size);
     const int blk = slot / block_size, off = slot - blk * block_size;
     __nv_bfloat16* p = qkv + ((size_t)t * (Hq + 2 * Hkv) + h) * D;
     if (h >= Hq + Hkv) {                       // value head: copy to the cache
@@ -446,7 +452,7 @@ __global__ void rope_kv_write_u8_kernel(__nv_bfloat16* __restrict__ qkv, const i
     const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (h >= Hq + 2 * Hkv) return;
-    const int slot = slot_map[t];
+    const int slot = OVB_DBG_SLOT(slot_map[t], block_size);
     const int blk = slot / block_size, off = slot - blk * block_size;
     __nv_bfloat16* p = qkv + ((size_t)t * (Hq + 2 * Hkv) + h) * D;
     const int d = lane * 2;
@@ -691,7 +697,7 @@ __global__ void kv_block_copy_kernel(uint4* __restrict__ k_cache, uint4* __restr
                                      const int* __restrict__ dst, size_t pieces_per_block) {
     pdl_enter();
     uint4* cache = blockIdx.y == 0 ? k_cache : v_cache;
-    const size_t s = (size_t)src[blockIdx.x] * pieces_per_block, d = (size_t)dst[blockIdx.x] * pieces_per_block;
+    const size_t s = (size_t)OVB_DBG_BLOCK(src[blockIdx.x]) * pieces_per_block, d = (size_t)OVB_DBG_BLOCK(dst[blockIdx.x]) * pieces_per_block;
     if (s == d) return;
     for (size_t i = threadIdx.x; i < pieces_per_block; i += blockDim.x) cache[d + i] = cache[s + i];
 }
@@ -804,6 +810,13 @@ static inline int grid_for(size_t n, int threads) {
 }
 
 }  // namespace ovb
+
+#ifdef OVB_DEBUG_BOUNDS
+extern "C" int ovb_debug_set_limits_elementwise(const ovb::DebugLimits* l) {
+    OVB_CHECK_CUDA(cudaMemcpyToSymbol(ovb::g_dbg_limits, l, sizeof(*l)));
+    return 0;
+}
+#endif
 
 extern "C" {
 using namespace ovb;

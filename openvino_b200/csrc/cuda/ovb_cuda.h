@@ -25,6 +25,11 @@ int ovb_set_pdl(int on);
 /* Polls (about 0.25 us apart) that a kernel waits for a peer GPU before it records OVB status 2 (peer timeout) and returns;
    0 restores the default (about one second). Returns the previous value. */
 unsigned ovb_set_peer_spin_limit(unsigned polls);
+/* Debug build of the kernels (compiled with -DOVB_DEBUG_BOUNDS, libovb_cuda_dbg.so): block ids, cache slots and token ids
+   that kernels read from device memory are checked against these limits; an index out of range records status 5 and the
+   access is skipped. In the release build ovb_debug_bounds_enabled() returns 0 and the limits are ignored. */
+int ovb_debug_bounds_enabled(void);
+int ovb_debug_set_limits(int kv_blocks, int vocab);
 
 // ---------------------------------------------------------------------------------------------
 // GEMM family:  out[T, N] = epilogue( X[T, K] * dequant(W[N, K])^T )

@@ -22,6 +22,7 @@ enum : int {
     STATUS_PEER_TIMEOUT = 2,   // a wait on a peer GPU's flag ran out
     STATUS_BAD_ARG = 3,        // a shape/alignment check inside a kernel failed
     STATUS_FLAG_TIMEOUT = 4,   // a wait on a local flag (split-K counter, test flag) ran out
+    STATUS_BAD_INDEX = 5,      // debug build: an index read from device memory was out of range (the access was skipped)
 };
 
 constexpr uint32_t kMbarSpinLimit = 1u << 24;   // try_wait calls; each blocks for a HW time slice

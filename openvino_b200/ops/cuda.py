@@ -23,7 +23,7 @@ W_BF16, W_U4, W_U8, W_F16, W_F8 = 0, 1, 2, 3, 4
 ACT_NONE, ACT_GELU_ERF, ACT_RELU, ACT_SILU, ACT_SWIGLU, ACT_GELU_TANH = 0, 1, 2, 3, 4, 5
 
 STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "bad argument seen on device",
-                4: "local flag wait timed out"}
+                4: "local flag wait timed out", 5: "index out of range (debug build; the access was skipped)"}
 
 
 class GemmArgs(C.Structure):
@@ -115,6 +115,16 @@ def set_peer_spin_limit(polls: int) -> int:
     fn = lib().ovb_set_peer_spin_limit
     fn.restype = C.c_uint
     return int(fn(C.c_uint(int(polls))))
+
+
+def debug_bounds_enabled() -> bool:
+    """True when the loaded kernel library is the bounds-checking debug build (``OVB_CUDA_LIB=.../libovb_cuda_dbg.so``)."""
+    return bool(lib().ovb_debug_bounds_enabled())
+
+
+def debug_set_limits(kv_blocks: int = 0, vocab: int = 0) -> None:
+    """Debug build: the limits that block ids / cache slots / token ids read by kernels are checked against (0 = unknown)."""
+    _check(lib().ovb_debug_set_limits(C.c_int(int(kv_blocks)), C.c_int(int(vocab))), "ovb_debug_set_limits")
 
 
 def check_status(what: str = "kernel") -> None:
