@@ -637,6 +637,8 @@ static bool use_tc_attention() {
 }
 
 static int decode_nsplit(int B, int Hkv, int max_ctx) {
+    static const int forced = [] { const char* e = getenv("OVB_PA_NSPLIT"); return e ? atoi(e) : 0; }();   // measurements only
+    if (forced > 0) return forced > 32 ? 32 : forced;
     // enough CTAs to fill the machine a few times over, at least 256 keys per split
     int by_len = (max_ctx + 255) / 256;
     int want = (148 * 6 + B * Hkv - 1) / (B * Hkv);

@@ -143,6 +143,19 @@ class PaddleFrontEnd(FrontEnd):
         return paddle.load(str(model), str(weights) if isinstance(weights, (str, os.PathLike)) else None)
 
 
+class JaxFrontEnd(FrontEnd):
+    name = "jax"
+
+    def supported(self, model) -> bool:
+        # a ClosedJaxpr: an open jaxpr with its constants
+        return hasattr(model, "jaxpr") and hasattr(model, "consts") and hasattr(getattr(model, "jaxpr"), "eqns")
+
+    def convert(self, input_model) -> Model:
+        from . import jax
+        model, _ = input_model
+        return jax.convert(model)
+
+
 class GgufFrontEnd(FrontEnd):
     name = "gguf"
 
@@ -160,7 +173,7 @@ class GgufFrontEnd(FrontEnd):
 class FrontEndManager:
     def __init__(self):
         self._frontends = {"ir": IRFrontEnd(), "pytorch": PyTorchFrontEnd(), "onnx": OnnxFrontEnd(), "tf": TensorFlowFrontEnd(), "tflite": TFLiteFrontEnd(),
-                           "paddle": PaddleFrontEnd(), "gguf": GgufFrontEnd()}
+                           "paddle": PaddleFrontEnd(), "jax": JaxFrontEnd(), "gguf": GgufFrontEnd()}
 
     def get_available_front_ends(self) -> List[str]:
         return list(self._frontends)
@@ -204,6 +217,8 @@ def convert_model(input_model, input=None, output=None, example_input=None, exte
     """
     if isinstance(input_model, Model):
         model = input_model
+    elif _manager._frontends["jax"].supported(input_model):
+        model = _manager._frontends["jax"].convert((input_model, None))
     elif _manager._frontends["pytorch"].supported(input_model):
         model = _manager._frontends["pytorch"].convert((input_model, dict(example_input=example_input, input=input, share_weights=share_weights, **kwargs)))
     else:
