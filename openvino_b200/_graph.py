@@ -86,6 +86,13 @@ class RTMap:
     def values(self):
         return self._d().values()
 
+    def pop(self, k, default=None):
+        if k in self:
+            v = self[k]
+            del self[k]
+            return v
+        return default
+
     def get(self, k, default=None):
         return self._d().get(k, default)
 

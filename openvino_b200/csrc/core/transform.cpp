@@ -420,6 +420,8 @@ static bool fused_names_cleanup(const ModelPtr& m) {
 static bool convert_precision(const ModelPtr& m, ET from, ET to) {
     bool changed = false;
     for (auto& n : m->ordered_ops()) {
+        // nodes of a precision-sensitive island (marked by MarkSugraphsToKeepInMixedPrecision or by hand) keep their type
+        if (n->rt_info.count("disable_fp16_compression_0") && !n->is_parameter()) continue;
         if (n->is_parameter() && n->attr("element_type").et == from) { n->set_attr("element_type", Attr::Type(to)); changed = true; }
         else if (n->is_constant() && n->constant.et == from) { n->constant = convert_tensor(n->constant, to); changed = true; }
         else if (n->type == "Convert" && n->attr("destination_type").et == from) { n->set_attr("destination_type", Attr::Type(to)); changed = true; }

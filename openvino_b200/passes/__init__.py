@@ -135,13 +135,40 @@ class SDPAToPagedAttention(_NamedPass):
                          allow_xattention=allow_xattention, allow_adaptive_rkv=allow_adaptive_rkv, allow_qq_bias=allow_qq_bias)
 
 
-class ConvertPrecision(_NamedPass):
-    """``ConvertPrecision(from_type, to_type)``: re-types parameters, constants and operations."""
-
-    native_name = "ConvertPrecision"
+class ConvertPrecision(ModelPass):
+    """``ConvertPrecision(from_type, to_type)``: re-types parameters, constants and operations. Converting f32 to f16 with
+    ``keep_precision_sensitive_in_fp32`` (the default) leaves the nodes marked ``disable_fp16_compression`` in fp32: a
+    Convert to f32 goes in front of every input of such an island and a Convert back behind its outputs
+    (transformations/convert_precision.cpp together with align_mixed_fp32_fp16_types.cpp in the reference)."""
 
     def __init__(self, from_type="f32", to_type="f16", keep_precision_sensitive_in_fp32: bool = True):
-        super().__init__(**{"from": str(from_type), "to": str(to_type), "keep_precision_sensitive_in_fp32": keep_precision_sensitive_in_fp32})
+        super().__init__("ConvertPrecision")
+        self._from, self._to, self._keep = str(from_type), str(to_type), bool(keep_precision_sensitive_in_fp32)
+
+    def run_on_model(self, model: Model) -> bool:
+        from .. import opset as ops
+        from .. import rt_info as rt
+        if self._keep and self._from == "f32" and self._to == "f16":
+            island = [n for n in model.get_ordered_ops() if rt.fp16_compression_is_disabled(n) and n.get_type_name() not in ("Parameter", "Result")]
+            members = set(island)
+            for n in island:
+                for k in range(n.get_input_size()):
+                    src = n.input_value(k)
+                    p = src.get_node()
+                    if p in members or src.get_element_type().name != "f32" or p.get_type_name() == "Constant":
+                        continue
+                    cvt = ops.convert(src, "f32")              # stays f32: the producer's output becomes f16 below
+                    rt.disable_fp16_compression(cvt)
+                    n.input(k).replace_source_output(cvt.output(0))
+                for o in n.outputs():
+                    if o.get_element_type().name != "f32":
+                        continue
+                    outside = [i for i in o.get_target_inputs() if i.get_node() not in members and not rt.fp16_compression_is_disabled(i.get_node())]
+                    if outside:
+                        back = ops.convert(o, "f32")           # unmarked: the native pass re-targets it to f16
+                        for i in outside:
+                            i.replace_source_output(back.output(0))
+        return bool(_c.make_pass("ConvertPrecision", {"from": self._from, "to": self._to}).run_on_model(model._m))
 
 
 class CompressWeights(_NamedPass):
@@ -149,6 +176,74 @@ class CompressWeights(_NamedPass):
 
     def __init__(self, mode: str = "int4_asym", group_size: int = 128, ratio: float = 1.0, all_layers: bool = False):
         super().__init__(mode=mode, group_size=group_size, ratio=ratio, all_layers=all_layers)
+
+
+class MarkSugraphsToKeepInMixedPrecision(ModelPass):
+    """Marks the operations whose fp16 evaluation loses too much (``disable_fp16_compression``), so that a later
+    ``ConvertPrecision`` f32 -> f16 leaves them in fp32 and puts Converts at the island's borders:
+
+    * exponent sums: ``Exp`` and everything between it and the ``ReduceSum`` / ``ReduceMean`` that accumulates it, the
+      reduction itself and the division / multiplication that normalises by it (soft-max written out, log-sum-exp);
+    * variance-style normalisations: ``ReduceMean`` / ``ReduceSum`` of squares up to the ``Sqrt`` / ``Power`` /
+      ``Divide`` that applies it (layer norm, RMS norm, L2 normalisation written out), and ``MVN`` / ``NormalizeL2``.
+
+    Role in the reference: transformations/fp16_compression/mark_subgraphs_to_keep_in_mixed_precision.cpp."""
+
+    _THROUGH = {"Add", "Subtract", "Multiply", "Divide", "Convert", "Reshape", "Squeeze", "Unsqueeze", "Transpose", "Broadcast", "Maximum", "Power", "Sqrt",
+                "Negative", "Abs", "Clamp"}
+    _REDUCE = {"ReduceSum", "ReduceMean"}
+
+    def run_on_model(self, model) -> bool:
+        from .. import rt_info as rt
+        marked = set()
+
+        def consumers(n):
+            return [i.get_node() for o in n.outputs() for i in o.get_target_inputs()]
+
+        def mark_down_to_reduce(start):
+            """start .. element-wise .. Reduce .. normalising consumer: mark the whole path when it reaches a reduction."""
+            path_marks, stack, seen = [], [(start, [start])], set()
+            while stack:
+                n, path = stack.pop()
+                if id(n) in seen or len(path) > 12:
+                    continue
+                seen.add(id(n))
+                for c in consumers(n):
+                    t = c.get_type_name()
+                    if t in self._REDUCE:
+                        path_marks.extend(path + [c])
+                        # the consumers that apply the reduced value (divide by the sum, multiply by 1 / sqrt(mean + eps) ...)
+                        frontier = [c]
+                        for _ in range(6):
+                            nxt = []
+                            for f in frontier:
+                                for cc in consumers(f):
+                                    if cc.get_type_name() in self._THROUGH and cc not in path_marks:
+                                        path_marks.append(cc)
+                                        nxt.append(cc)
+                            frontier = nxt
+                    elif t in self._THROUGH:
+                        stack.append((c, path + [c]))
+            return path_marks
+
+        for n in model.get_ordered_ops():
+            t = n.get_type_name()
+            if t in ("MVN", "NormalizeL2"):
+                marked.add(n)
+            elif t == "Exp":
+                marked.update(mark_down_to_reduce(n))
+            elif t in ("Multiply", "Power") and n.get_output_element_type(0).is_real():
+                # squares: x * x or x ^ 2 on the way to a mean / sum
+                ins = [n.input_value(i) for i in range(n.get_input_size())]
+                is_square = (t == "Multiply" and len(ins) == 2 and ins[0] == ins[1]) or \
+                            (t == "Power" and ins[1].get_node().get_type_name() == "Constant" and ins[1].get_node().get_tensor_view().size == 1
+                             and float(ins[1].get_node().get_tensor_view().to_float32().reshape(-1)[0]) == 2.0)
+                if is_square:
+                    marked.update(mark_down_to_reduce(n))
+        for n in marked:
+            if n.get_type_name() not in ("Parameter", "Result", "Constant"):
+                rt.disable_fp16_compression(n)
+        return bool(marked)
 
 
 class SymbolicPropagation(ModelPass):

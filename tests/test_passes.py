@@ -415,3 +415,44 @@ def test_symbols_travel_with_dynamic_dimensions():
     assert not d.has_symbol()
     xml, _ = ov._ovcore.serialize(m._m)
     assert b"Symbol" not in xml
+
+
+def test_precision_sensitive_islands_stay_in_fp32():
+    """Soft-max written out (exp / sum / divide) overflows in fp16 for large logits; the marking pass keeps that island in
+    fp32 while the projections around it are converted."""
+    from openvino_b200 import rt_info as rt
+    rng = np.random.default_rng(3)
+    x = ops.parameter([2, 8], "f32", "x")
+    w1 = rng.standard_normal((16, 8)).astype(np.float32)
+    w2 = rng.standard_normal((4, 16)).astype(np.float32) * 0.1
+    h = ops.matmul(x, w1, False, True, name="proj_in")
+    e = ops.exp(h, name="exp")
+    ssum = ops.reduce_sum(e, np.array([1], np.int64), True, name="sum")
+    p = ops.divide(e, ssum, name="normalise")
+    y = ops.matmul(p, w2, False, True, name="proj_out")
+    m = ov.Model([y], [x], "softmax_written_out")
+    xin = (rng.standard_normal((2, 8)) * 6).astype(np.float32)             # exp() of these sums leaves the fp16 range
+    want = ov.compile_model(m, "CPU")([xin])[0]
+    plain = m.clone()
+    _run_pass(plain, passes.ConvertPrecision("f32", "f16"))
+    lossy = ov.compile_model(plain, "CPU")([xin.astype(np.float16)])[0].astype(np.float32)
+    assert not np.isfinite(lossy).all() or np.abs(lossy - want).max() > 1e-2       # without the island the result is ruined
+    _run_pass(m, passes.MarkSugraphsToKeepInMixedPrecision())
+    by_name = {n.get_friendly_name(): n for n in m.get_ops()}
+    assert all(rt.fp16_compression_is_disabled(by_name[k]) for k in ("exp", "sum", "normalise"))
+    assert not rt.fp16_compression_is_disabled(by_name["proj_in"]) and not rt.fp16_compression_is_disabled(by_name["proj_out"])
+    _run_pass(m, passes.ConvertPrecision("f32", "f16"))
+    by_name = {n.get_friendly_name(): n for n in m.get_ops()}
+    assert by_name["proj_in"].get_output_element_type(0).name == "f16" and by_name["proj_out"].get_output_element_type(0).name == "f16"
+    assert all(by_name[k].get_output_element_type(0).name == "f32" for k in ("exp", "sum", "normalise"))
+    got = ov.compile_model(m, "CPU")([xin.astype(np.float16)])[0].astype(np.float32)
+    assert np.isfinite(got).all() and np.abs(got - want).max() < 2e-2 * max(1.0, np.abs(want).max())
+    # attribute helpers
+    c = ops.constant(np.ones(4, np.float32))
+    rt.enable_keep_const_precision(c)
+    assert rt.is_keep_const_precision(c)
+    rt.disable_keep_const_precision(c)
+    assert not rt.is_keep_const_precision(c)
+    cv = ops.convert(c, "f16")
+    rt.mark_as_decompression(cv)
+    assert rt.is_decompression(cv)
