@@ -20,16 +20,86 @@ from .._tensor import Tensor
 
 class FrontEnd:
     name = ""
+    # module and name of the translator table that ConversionExtension entries go to (None: the frontend has no table)
+    _table = None
+
+    def __init__(self):
+        self._extensions = []
+
+    def __init_subclass__(cls, **kw):
+        """``convert`` of every frontend also takes an ``InputModel`` (edited or not) besides the (source, weights) pair."""
+        super().__init_subclass__(**kw)
+        raw = cls.__dict__.get("convert")
+        if raw is None:
+            return
+
+        def convert(self, input_model):
+            from .input_model import InputModel
+            if isinstance(input_model, InputModel):
+                return input_model._m()
+            return raw(self, input_model)
+        convert.__doc__ = raw.__doc__
+        cls.convert = convert
+
+    def get_name(self) -> str:
+        return self.name
 
     def supported(self, model) -> bool:
         return False
 
     def load(self, model, weights=None):
-        """-> an input model handle that ``convert`` accepts."""
-        return (model, weights)
+        """-> an ``InputModel``: places can be renamed, re-shaped and cut before ``convert`` (input_model.py)."""
+        from .input_model import InputModel
+        return InputModel(self, model, weights)
+
+    def add_extension(self, extension) -> None:
+        """``ConversionExtension`` (a user translator for one source operation), ``TelemetryExtension``,
+        ``ProgressReporterExtension``."""
+        from .input_model import ConversionExtension
+        if isinstance(extension, ConversionExtension):
+            if self._table is None:
+                raise RuntimeError("frontend '%s' has no operation table to extend" % self.name)
+            import importlib
+            mod = importlib.import_module(self._table[0], __package__)
+            getattr(mod, self._table[1])[extension.op_type] = extension.converter
+        self._extensions.append(extension)
+
+    def _convert_source(self, model, weights) -> Model:
+        """Source + weights -> Model, reporting to the telemetry / progress extensions."""
+        from .input_model import ProgressReporterExtension, TelemetryExtension
+        progress = [e for e in self._extensions if isinstance(e, ProgressReporterExtension)]
+        telemetry = [e for e in self._extensions if isinstance(e, TelemetryExtension)]
+        for p in progress:
+            p.report_progress(0.0, 1, 0)
+        try:
+            m = self.convert((model, weights))
+        except Exception as e:   # noqa: BLE001 - reported, then re-raised
+            for t in telemetry:
+                t.send_error("%s: %s" % (type(e).__name__, str(e)[:200]))
+            raise
+        if telemetry:
+            counts = {}
+            for n in m.get_ops():
+                counts[n.get_type_name()] = counts.get(n.get_type_name(), 0) + 1
+            for t in telemetry:
+                t.send_event("conversion", self.name)
+                for k, v in sorted(counts.items()):
+                    t.send_event("op_count", "%s_%s" % (self.name, k), v)
+        for p in progress:
+            p.report_progress(1.0, 1, 1)
+        return m
 
     def convert(self, input_model) -> Model:
         raise NotImplementedError
+
+    def convert_partially(self, input_model) -> Model:
+        return self.convert(input_model)
+
+    def decode(self, input_model) -> Model:
+        return self.convert(input_model)
+
+    def normalize(self, model: Model) -> None:
+        model.validate_nodes_and_infer_types()
 
     def __repr__(self):
         return "<FrontEnd '%s'>" % self.name
@@ -77,6 +147,7 @@ class IRFrontEnd(FrontEnd):
 
 class PyTorchFrontEnd(FrontEnd):
     name = "pytorch"
+    _table = (".pytorch", "_TABLE")
 
     def supported(self, model) -> bool:
         try:
@@ -93,6 +164,7 @@ class PyTorchFrontEnd(FrontEnd):
 
 class OnnxFrontEnd(FrontEnd):
     name = "onnx"
+    _table = (".onnx", "_T")
 
     def supported(self, model) -> bool:
         if isinstance(model, (str, os.PathLike)):
@@ -107,6 +179,7 @@ class OnnxFrontEnd(FrontEnd):
 
 class TensorFlowFrontEnd(FrontEnd):
     name = "tf"
+    _table = (".tensorflow", "_T")
 
     def supported(self, model) -> bool:
         return isinstance(model, (str, os.PathLike)) and str(model).lower().endswith(".pb")
@@ -119,6 +192,7 @@ class TensorFlowFrontEnd(FrontEnd):
 
 class TFLiteFrontEnd(FrontEnd):
     name = "tflite"
+    _table = (".tflite", "_T")
 
     def supported(self, model) -> bool:
         if isinstance(model, (str, os.PathLike)):
@@ -133,6 +207,7 @@ class TFLiteFrontEnd(FrontEnd):
 
 class PaddleFrontEnd(FrontEnd):
     name = "paddle"
+    _table = (".paddle", "_T")
 
     def supported(self, model) -> bool:
         return isinstance(model, (str, os.PathLike)) and str(model).lower().endswith(".pdmodel")
@@ -145,6 +220,7 @@ class PaddleFrontEnd(FrontEnd):
 
 class JaxFrontEnd(FrontEnd):
     name = "jax"
+    _table = (".jax", "_T")
 
     def supported(self, model) -> bool:
         # a ClosedJaxpr: an open jaxpr with its constants

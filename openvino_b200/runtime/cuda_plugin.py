@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import math
 import os
+import contextlib
 import threading
 from typing import Callable, Dict, List, Optional, Sequence
 
@@ -1266,10 +1267,18 @@ class CudaCompiledModel(CompiledModel):
         self._out_types = [o.get_element_type() for o in model.outputs]
         # one stream per compiled-model stream: requests of different streams overlap on the GPU
         self._streams = [torch.cuda.Stream(device=device) for _ in range(self._n_streams)] if device.type == "cuda" else [None]
+        # requests that share a stream take turns on the host as well: one of them may be capturing a graph on that stream,
+        # and a launch or a synchronize from another thread on a capturing stream would end the capture with an error
+        self._stream_locks = [threading.Lock() for _ in self._streams]
+        # the interpreter keeps the running request's variables in its (shared) context: requests of a model with states
+        # walk the program one at a time
+        self._has_state = any(n.get_type_name() in ("ReadValue", "Assign") for n in runtime_model.get_ops())
+        self._state_lock = threading.Lock()
         self._next_stream = 0
 
     def _make_runner(self, request: InferRequest):
         stream = self._streams[self._next_stream % len(self._streams)]
+        stream_lock = self._stream_locks[self._next_stream % len(self._streams)]
         self._next_stream += 1
         program = self.program
         # variables (states) are per request; constants and packed weights are shared by all requests
@@ -1344,17 +1353,20 @@ class CudaCompiledModel(CompiledModel):
 
         def run(req: InferRequest, ins: List[Tensor]) -> List[Tensor]:
             prof = [] if profile_on else None
-            program.ctx.variables = ctx_vars
             if stream is not None:
-                with torch.cuda.stream(stream):
-                    xs = [to_device(t) for t in ins]
-                    outs = run_graphed(xs) if graphs_on else program.run(xs, prof)
-                    res = self._finish(outs, req)
-                stream.synchronize()
+                with (self._state_lock if self._has_state else contextlib.nullcontext()), stream_lock:
+                    program.ctx.variables = ctx_vars
+                    with torch.cuda.stream(stream):
+                        xs = [to_device(t) for t in ins]
+                        outs = run_graphed(xs) if graphs_on else program.run(xs, prof)
+                        res = self._finish(outs, req)
+                    stream.synchronize()
             else:
-                outs = program.run([to_device(t) for t in ins], prof)
-                res = self._finish(outs, req)
-                torch.cuda.current_stream(self.device).synchronize()
+                with self._state_lock:
+                    program.ctx.variables = ctx_vars
+                    outs = program.run([to_device(t) for t in ins], prof)
+                    res = self._finish(outs, req)
+                    torch.cuda.current_stream(self.device).synchronize()
             if prof is not None:
                 req._profile = [ProfilingInfo(name, typ, "cuda", (ev[0].elapsed_time(ev[1]) * 1e3) if ev else 0.0) for name, typ, ev in prof]
             return res
