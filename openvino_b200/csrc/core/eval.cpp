@@ -944,7 +944,8 @@ void register_eval_functions() {
 #undef COMPARE
     set_eval("LogicalAnd", [](N, Ins in, Outs out, C) { return compare(in, out, [](double x, double y) { return x != 0 && y != 0; }, [](int64_t x, int64_t y) { return x != 0 && y != 0; }); });
     set_eval("LogicalOr", [](N, Ins in, Outs out, C) { return compare(in, out, [](double x, double y) { return x != 0 || y != 0; }, [](int64_t x, int64_t y) { return x != 0 || y != 0; }); });
-    set_eval("LogicalXor", [](N, Ins in, Outs out, C) { return compare(in, out, [](double x, double y) { return (x != 0) != (y != 0); }, [](int64_t x, int64_t y) { return (x != 0) != (y != 0); }); });
+    for (const char* t : {"LogicalXor", "Xor"})
+        set_eval(t, [](N, Ins in, Outs out, C) { return compare(in, out, [](double x, double y) { return (x != 0) != (y != 0); }, [](int64_t x, int64_t y) { return (x != 0) != (y != 0); }); });
     set_eval("Select", [](N, Ins in, Outs out, C) {
         const Shape os = broadcast_shape(in[0].shape, broadcast_shape(in[1].shape, in[2].shape));
         const auto sc = bstrides(in[0].shape, os), sa = bstrides(in[1].shape, os), sb = bstrides(in[2].shape, os);

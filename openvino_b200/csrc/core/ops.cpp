@@ -16,6 +16,8 @@ void register_eval_functions();
 void register_ext_ops();
 void register_internal_ops();
 void register_vision_ops();
+void register_detection_ops();
+void register_rest_ops();
 
 namespace {
 
@@ -877,7 +879,7 @@ void register_all_ops() {
         reg("Divide", "opset1", {AB(), Ab("m_pythondiv", true)}, infer_binary_arith, 2, 2);
         for (const char* t : {"Equal", "NotEqual"}) reg(t, "opset1", {AB()}, infer_binary_cmp, 2, 2, true);
         for (const char* t : {"Less", "LessEqual", "Greater", "GreaterEqual"}) reg(t, "opset1", {AB()}, infer_binary_cmp, 2, 2);
-        for (const char* t : {"LogicalAnd", "LogicalOr", "LogicalXor"}) reg(t, "opset1", {AB()}, infer_binary_cmp, 2, 2, true);
+        for (const char* t : {"LogicalAnd", "LogicalOr", "LogicalXor", "Xor"}) reg(t, "opset1", {AB()}, infer_binary_cmp, 2, 2, true);
         for (const char* t : {"BitwiseAnd", "BitwiseOr", "BitwiseXor"}) reg(t, "opset13", {AB()}, infer_binary_arith, 2, 2, true);
         reg("BitwiseNot", "opset13", {}, infer_same, 1, 1);
         reg("Select", "opset1", {AB()},
@@ -1132,6 +1134,8 @@ void register_all_ops() {
         register_ext_ops();
         register_internal_ops();
         register_vision_ops();
+        register_detection_ops();
+        register_rest_ops();
     });
 }
 

@@ -1389,7 +1389,9 @@ static int launch(const ovb_gemm_args* a, const CUtensorMap& tmW, const CUtensor
         cfg.gridDim = dim3(ceil_div(a->N, TILE_N) * (ceil_div(a->T, BT) + p.num_groups), 1, 1);
     p.nvls_reducers = 0;
     if (p.nvls && p.splits == 1 && p.group_off == nullptr && (int)cfg.gridDim.x > resident[1]) {
-        static const int want = env_int("OVB_NVLS_REDUCERS", 32);
+        // dedicated reducer CTAs are an option, off by default: at 8 ranks (T 8192, N 4096) 32 / 64 of them gave 360 / 320 us
+        // against 334 us with every tile CTA reducing its own share after the last tile, and the serving pass was 4 % slower
+        static const int want = env_int("OVB_NVLS_REDUCERS", 0);
         p.nvls_reducers = want < 0 ? 0 : (want > 128 ? 128 : want);
         cfg.gridDim.x += p.nvls_reducers;
     }

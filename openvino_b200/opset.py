@@ -20,6 +20,29 @@ from ._graph import Model, Node, Output, as_output, constant, make_op, parameter
 from ._types import PartialShape, Type
 
 _SPEC = """
+prior_box PriorBox : layer_shape image_shape | min_size=[] max_size=[] aspect_ratio=[] density=[] fixed_ratio=[] fixed_size=[] clip=False flip=False step=0.0 offset=0.0 variance=[] scale_all_sizes=True min_max_aspect_ratios_order=True
+detection_output DetectionOutput : box_logits class_preds proposals [aux_class_preds] [aux_box_preds] | background_label_id=0 top_k=-1 variance_encoded_in_target=False keep_top_k=[1] code_type=caffe.PriorBoxParameter.CORNER share_location=True nms_threshold=0.0 confidence_threshold=0.0 clip_after_nms=False clip_before_nms=False decrease_label_id=False normalized=False input_height=1 input_width=1 objectness_score=0.0
+proposal Proposal : class_probs bbox_deltas image_shape | base_size pre_nms_topn post_nms_topn nms_thresh feat_stride min_size ratio scale clip_before_nms=True clip_after_nms=False normalize=False box_size_scale=1.0 box_coordinate_scale=1.0 framework=
+generate_proposals GenerateProposals : im_info anchors deltas scores | min_size nms_threshold pre_nms_count post_nms_count normalized=True nms_eta=1.0 roi_num_type=i64
+experimental_detectron_prior_grid_generator ExperimentalDetectronPriorGridGenerator : priors feature_map image | flatten=True h=0 w=0 stride_x=0.0 stride_y=0.0
+experimental_detectron_detection_output ExperimentalDetectronDetectionOutput : input_rois input_deltas input_scores input_im_info | score_threshold nms_threshold max_delta_log_wh num_classes post_nms_count max_detections_per_image class_agnostic_box_regression=False deltas_weights=[10.0,10.0,5.0,5.0]
+experimental_detectron_generate_proposals_single_image ExperimentalDetectronGenerateProposalsSingleImage : im_info anchors deltas scores | min_size nms_threshold post_nms_count pre_nms_count
+experimental_detectron_roi_feature_extractor ExperimentalDetectronROIFeatureExtractor : *inputs | output_size sampling_ratio pyramid_scales aligned=False
+experimental_detectron_topk_rois ExperimentalDetectronTopKROIs : input_rois rois_probs | max_rois=0
+deformable_convolution DeformableConvolution : data offsets filters [mask] | strides pads_begin pads_end dilations auto_pad=explicit group=1 deformable_group=1 bilinear_interpolation_pad=False
+deformable_psroi_pooling DeformablePSROIPooling : feature_maps coords [offsets] | output_dim spatial_scale group_size=1 mode=bilinear_deformable spatial_bins_x=1 spatial_bins_y=1 trans_std=1.0 part_size=1
+matrix_nms MatrixNms : boxes scores | sort_result_type=none sort_result_across_batch=False output_type=i64 score_threshold=0.0 nms_top_k=-1 keep_top_k=-1 background_class=-1 decay_function=linear gaussian_sigma=2.0 post_threshold=0.0 normalized=True
+multiclass_nms MulticlassNms : boxes scores [roisnum] | sort_result_type=none sort_result_across_batch=False output_type=i64 iou_threshold=0.0 score_threshold=0.0 nms_top_k=-1 keep_top_k=-1 background_class=-1 nms_eta=1.0 normalized=True
+nms_rotated NMSRotated : boxes scores max_output_boxes_per_class iou_threshold score_threshold | sort_result_descending=True output_type=i64 clockwise=True
+roi_align_rotated ROIAlignRotated : data rois batch_indices | pooled_h pooled_w sampling_ratio spatial_scale clockwise_mode=False
+binary_convolution BinaryConvolution : data filters | strides pads_begin pads_end dilations mode=xnor-popcount pad_value=0.0 auto_pad=explicit
+string_tensor_pack StringTensorPack : begins ends symbols
+string_tensor_unpack StringTensorUnpack : data
+reverse Reverse : data axis | mode=index
+istft ISTFT : data window frame_size frame_step [signal_length] | center=False normalized=False
+logical_xor_v0 Xor : a b | auto_broadcast=numpy
+rgb_to_nv12 RGBtoNV12 : arg | single_plane=True
+bgr_to_nv12 BGRtoNV12 : arg | single_plane=True
 identity Identity : data
 nv12_to_rgb NV12toRGB : arg [arg_uv]
 nv12_to_bgr NV12toBGR : arg [arg_uv]
@@ -264,6 +287,11 @@ def _make_factory(py_name, op_type, version, inputs, attrs):
                     args.pop(0)
                 elif args and not isinstance(args[0], (str, bool, Type)):
                     ins.append(args.pop(0))
+        # the detection factories of the reference take their attributes as one dict: ``prior_box(layer, image, attrs)``
+        if args and isinstance(args[0], dict):
+            kwargs.update(args.pop(0))
+        elif isinstance(kwargs.get("attrs"), dict):
+            kwargs.update(kwargs.pop("attrs"))
         values = {}
         for py, ir, default in attr_specs:
             if py in kwargs:
