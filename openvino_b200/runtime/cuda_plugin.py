@@ -71,6 +71,12 @@ def op(*names):
     return deco
 
 
+@op("Subgraph")
+def _snippet_subgraph(n, ins, ctx):
+    from ..snippets.runtime import run_subgraph
+    return run_subgraph(n, ins, ctx, _OPS)
+
+
 def _ints(t) -> List[int]:
     if isinstance(t, torch.Tensor):
         return [int(v) for v in t.reshape(-1).tolist()]
@@ -1450,6 +1456,8 @@ class CudaConfig(PluginConfig):
         self.register(ConfigOption(props.cuda.tensor_parallel_size, 0, "ranks of the tensor-parallel group (0 = the process group's size)", lambda v: 0 <= v <= 8, R))
         self.register(ConfigOption(props.cuda.memory_fraction, 0.9, "share of the free device memory the KV cache may take", lambda v: 0.0 < v <= 1.0, RI))
         self.register(ConfigOption(props.enable_profiling, False, "per-node timing of graph programs (PERF_COUNT)", None, R))
+        self.register(ConfigOption("SNIPPETS_MODE", "DISABLE", "ENABLE: groups of element-wise operations run as generated kernels (built with nvcc at compile time)",
+                                   lambda v: str(v).upper() in ("ENABLE", "DISABLE"), R, str))
         self.register(ConfigOption("CUDA_PDL", True, "programmatic dependent launch of the serving kernels", None, RI))
         self.register(ConfigOption("CUDA_DUMP_GRAPH_PROGRAM", "", "write the node list of compiled graph programs to this file", None, D, str))
 
@@ -1598,6 +1606,9 @@ class CudaPlugin(Plugin):
         if str(cfg.get(props.cuda.serving_program, "")).upper() in ("TRUE", "YES", "1"):
             return CudaServingCompiledModel(self, model, cfg, dev)
         rm = self.transform(model)
+        if str(pc["SNIPPETS_MODE"]).upper() == "ENABLE":
+            from ..snippets import tokenize
+            tokenize(rm)
         policy = str(cfg.get(props.hint.model_distribution_policy, "") or "")
         if "TENSOR_PARALLEL" in policy and torch.distributed.is_available() and torch.distributed.is_initialized() \
                 and torch.distributed.get_world_size() > 1:
