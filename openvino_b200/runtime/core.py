@@ -874,6 +874,8 @@ class Core:
         self.register_plugin_factory("CPU", CpuPlugin)
         from . import policy_plugins
         policy_plugins.register(self)
+        from . import npuw
+        npuw.register(self)
         self.register_plugin_factory("CUDA", _load_cuda_plugin)
 
     # ---- plugins

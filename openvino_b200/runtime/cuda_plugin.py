@@ -71,6 +71,22 @@ def op(*names):
     return deco
 
 
+@op("FunctionCall")
+def _npuw_function_call(n, ins, ctx):
+    """A folded block: the shared body runs as its own graph program (built once per device), with this block's weights."""
+    from .npuw import function_of
+    f = function_of(n)
+    progs = f.__dict__.setdefault("_cuda_programs", {})
+    key = (str(ctx.device), ctx.precision)
+    prog = progs.get(key)
+    if prog is None:
+        prog = progs[key] = GraphProgram(f.body, ctx.device, ctx.precision)
+        f.compiles += 1
+    f.calls += 1
+    prog.ctx.variables = ctx.variables
+    return prog.run([t if isinstance(t, torch.Tensor) else torch.as_tensor(np.asarray(t)).to(ctx.device) for t in ins], None)
+
+
 @op("Subgraph")
 def _snippet_subgraph(n, ins, ctx):
     from ..snippets.runtime import run_subgraph
