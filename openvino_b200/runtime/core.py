@@ -142,6 +142,38 @@ class Plugin:
         return cfg
 
 
+class _EntryLock:
+    """Advisory lock on a file next to a cache entry: processes (and threads) that want the same entry take turns."""
+    _thread_locks: Dict[str, threading.Lock] = {}
+    _guard = threading.Lock()
+
+    def __init__(self, path: str):
+        self.path = path
+        with self._guard:
+            self._tl = self._thread_locks.setdefault(path, threading.Lock())
+        self._f = None
+
+    def __enter__(self):
+        self._tl.acquire()
+        try:
+            import fcntl
+            self._f = open(self.path, "a+b")
+            fcntl.flock(self._f.fileno(), fcntl.LOCK_EX)
+        except (ImportError, OSError):
+            self._f = None        # no advisory locks on this file system: the thread lock still holds
+        return self
+
+    def __exit__(self, *exc):
+        if self._f is not None:
+            try:
+                import fcntl
+                fcntl.flock(self._f.fileno(), fcntl.LOCK_UN)
+            finally:
+                self._f.close()
+        self._tl.release()
+        return False
+
+
 class ModelBlob:
     """Exported compiled model: header (json) + IR xml + weights, with a fixed magic and version.
 
@@ -961,7 +993,7 @@ class Core:
             return
         name, dev_cfg = _parse_device(device_or_config)
         cfg = props.normalize(config)
-        core_keys = {props.cache_dir, props.enable_mmap, props.force_tbb_terminate}
+        core_keys = {props.cache_dir, props.enable_mmap, props.force_tbb_terminate, props.cache_encryption_callbacks}
         plugin_cfg = {k: v for k, v in cfg.items() if k not in core_keys or k == props.cache_dir}
         self._get_plugin(name).set_property(plugin_cfg)
 
@@ -1014,9 +1046,10 @@ class Core:
             model = self.read_model(model, weights)
         cache_dir = self._cache_dir(plugin, cfg)
         cfg.pop(props.cache_dir, None)
+        callbacks = cfg.pop(props.cache_encryption_callbacks, None) or self._core_config.get(props.cache_encryption_callbacks)
         with _trace.scope("ov::LoadTime", "Core::compile_model::%s" % dev):
             if cache_dir and "EXPORT_IMPORT" in plugin.capabilities():
-                cm = self._compile_with_cache(plugin, model, cfg, cache_dir)
+                cm = self._compile_with_cache(plugin, model, cfg, cache_dir, callbacks)
                 _log.info("core", "compiled '%s' for %s (%s)" % (model.get_friendly_name(), dev, "cache hit" if cm.loaded_from_cache else "cache miss"))
                 return cm
             cm = plugin.compile_model(model, cfg)
@@ -1034,29 +1067,46 @@ class Core:
                 h.update(("%s=%s;" % (k, merged[k])).encode())
         return h.hexdigest()[:32]
 
-    def _compile_with_cache(self, plugin: Plugin, model: Model, cfg: dict, cache_dir: str) -> CompiledModel:
+    def _compile_with_cache(self, plugin: Plugin, model: Model, cfg: dict, cache_dir: str, callbacks=None) -> CompiledModel:
+        """One cache entry per (model, device, compile configuration). The entry is read through a memory mapping when
+        ``ENABLE_MMAP`` is on; ``CACHE_ENCRYPTION_CALLBACKS`` = (encrypt, decrypt) are applied to the stored bytes; a lock file
+        per entry makes processes that want the same entry take turns, so that only the first one compiles
+        (src/inference/src/cache_manager.hpp, src/inference/src/cache_guard.cpp)."""
         os.makedirs(cache_dir, exist_ok=True)
         path = os.path.join(cache_dir, self._cache_key(plugin, model, cfg) + ".blob")
-        if os.path.exists(path):
-            try:
-                with open(path, "rb") as f:
-                    blob = ModelBlob.from_bytes(f.read())
-                if blob.header.get("runtime") != __version__ or blob.header.get("device") != plugin.device_name:
-                    raise RuntimeError("stale cache entry")
-                cm = plugin.import_model(blob, cfg)
-                cm.loaded_from_cache = True
-                return cm
-            except Exception:   # noqa: BLE001 - a broken entry is removed and the model compiled afresh
+        encrypt, decrypt = (callbacks if callbacks else (None, None))
+        use_mmap = bool(self._core_config.get(props.enable_mmap, True)) and decrypt is None
+        with _EntryLock(path + ".lock"):
+            if os.path.exists(path):
                 try:
-                    os.remove(path)
-                except OSError:
-                    pass
-        cm = plugin.compile_model(model, cfg)
-        tmp = path + ".%d.tmp" % os.getpid()
-        with open(tmp, "wb") as f:
-            f.write(cm.export_model())
-        os.replace(tmp, path)
-        return cm
+                    with open(path, "rb") as f:
+                        if use_mmap and os.path.getsize(path) > 0:
+                            import mmap
+                            data = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+                        else:
+                            data = f.read()
+                    if decrypt is not None:
+                        data = decrypt(bytes(data))
+                    blob = ModelBlob.from_bytes(data)
+                    if blob.header.get("runtime") != __version__ or blob.header.get("device") != plugin.device_name:
+                        raise RuntimeError("stale cache entry")
+                    cm = plugin.import_model(blob, cfg)
+                    cm.loaded_from_cache = True
+                    return cm
+                except Exception:   # noqa: BLE001 - a broken entry is removed and the model compiled afresh
+                    try:
+                        os.remove(path)
+                    except OSError:
+                        pass
+            cm = plugin.compile_model(model, cfg)
+            tmp = path + ".%d.tmp" % os.getpid()
+            payload = cm.export_model()
+            if encrypt is not None:
+                payload = encrypt(bytes(payload))
+            with open(tmp, "wb") as f:
+                f.write(payload)
+            os.replace(tmp, path)
+            return cm
 
     def import_model(self, model_stream, device_name: str, config=None) -> CompiledModel:
         data = model_stream.read() if hasattr(model_stream, "read") else model_stream

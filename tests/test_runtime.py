@@ -252,7 +252,7 @@ def test_export_import_and_cache(core, tmp_path):
     cache = str(tmp_path / "cache")
     core.set_property({props.cache_dir: cache})
     a = core.compile_model(m, "CPU")
-    assert a.get_property(props.loaded_from_cache) is False and len(os.listdir(cache)) == 1
+    assert a.get_property(props.loaded_from_cache) is False and len([f for f in os.listdir(cache) if f.endswith(".blob")]) == 1
     b = core.compile_model(m, "CPU")
     assert b.get_property(props.loaded_from_cache) is True
     np.testing.assert_array_equal(a(x)[0], b(x)[0])
@@ -465,3 +465,34 @@ def test_shutdown_runs_callbacks_in_reverse_order_once(core):
     thread.join(timeout=5)
     assert not thread.is_alive()
     assert ov.shutdown() == [] and h1 > 0
+
+
+def test_cache_encryption_lock_and_mmap(core, tmp_path):
+    """Entries pass through the user's (encrypt, decrypt) pair; a plain entry is read through a memory mapping; threads
+    that ask for the same entry take turns, so one of them compiles and the others import."""
+    import threading
+    x = ops.parameter([2, 4], "f32", "x")
+    m = Model([ops.relu(ops.add(x, np.float32(1)))], [x], "enc")
+    cache = str(tmp_path / "c1")
+    key = 0x5A
+    enc = (lambda b: bytes(v ^ key for v in b), lambda b: bytes(v ^ key for v in b))
+    a = core.compile_model(m, "CPU", {props.cache_dir: cache, props.cache_encryption_callbacks: enc})
+    entry = [f for f in os.listdir(cache) if f.endswith(".blob")]
+    assert len(entry) == 1 and not open(os.path.join(cache, entry[0]), "rb").read().startswith(b"OVB200BL")
+    b = core.compile_model(m, "CPU", {props.cache_dir: cache, props.cache_encryption_callbacks: enc})
+    assert a.get_property(props.loaded_from_cache) is False and b.get_property(props.loaded_from_cache) is True
+    xin = np.array([[-3, 0, 1, 2], [5, -1, -2, 0]], np.float32)
+    np.testing.assert_array_equal(b([xin])[0], np.maximum(xin + 1, 0))
+    # reading the encrypted entry without the callbacks cannot work: it is dropped and the model compiled again
+    c = core.compile_model(m, "CPU", {props.cache_dir: cache})
+    assert c.get_property(props.loaded_from_cache) is False
+    # plain entries, several threads at once
+    cache2 = str(tmp_path / "c2")
+    got = []
+    def worker():
+        got.append(core.compile_model(m, "CPU", {props.cache_dir: cache2}).get_property(props.loaded_from_cache))
+    ts = [threading.Thread(target=worker) for _ in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert sorted(got) == [False, True, True, True]
+    assert len([f for f in os.listdir(cache2) if f.endswith(".blob")]) == 1
