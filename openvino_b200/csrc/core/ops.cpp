@@ -18,6 +18,7 @@ void register_internal_ops();
 void register_vision_ops();
 void register_detection_ops();
 void register_rest_ops();
+void register_recurrent_ops();
 
 namespace {
 
@@ -1136,6 +1137,7 @@ void register_all_ops() {
         register_vision_ops();
         register_detection_ops();
         register_rest_ops();
+        register_recurrent_ops();
     });
 }
 

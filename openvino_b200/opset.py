@@ -20,6 +20,14 @@ from ._graph import Model, Node, Output, as_output, constant, make_op, parameter
 from ._types import PartialShape, Type
 
 _SPEC = """
+selective_ssm SelectiveSSM@ie_internal_opset : A dt B x C recurrent_state
+gated_delta_net GatedDeltaNet@ie_internal_opset : query key value recurrent_state gate beta | fuse_qk_l2norm=False q_l2_norm_eps=1e-6 k_l2_norm_eps=1e-6
+paged_selective_ssm PagedSelectiveSSM@ie_internal_opset : A dt B x C recurrent_state_table subsequence_begins la_block_indices la_block_indices_begins num_processed_tokens cache_interval
+paged_gated_delta_net PagedGatedDeltaNet@ie_internal_opset : query key value recurrent_state_table gate beta subsequence_begins la_block_indices la_block_indices_begins processed_tokens cache_interval | use_qk_l2norm=False q_l2_norm_eps=1e-6 k_l2_norm_eps=1e-6
+paged_causal_conv1d PagedCausalConv1D@ie_internal_opset : input_embeds conv_state_table conv_weight conv_bias subsequence_begins la_block_indices la_block_indices_begins processed_tokens cache_interval
+pa_kv_reorder PaKVReorder@ie_internal_opset : key_cache value_cache block_indices block_indices_begins block_update_indices block_update_indices_begins
+augru_cell AUGRUCell@ie_internal_opset : X initial_hidden_state W R B A | hidden_size activations=[] activations_alpha=[] activations_beta=[] clip=0.0 linear_before_reset=False
+augru_sequence AUGRUSequence@ie_internal_opset : X initial_hidden_state sequence_lengths W R B A | hidden_size direction=forward activations=[] activations_alpha=[] activations_beta=[] clip=0.0 linear_before_reset=False
 prior_box PriorBox : layer_shape image_shape | min_size=[] max_size=[] aspect_ratio=[] density=[] fixed_ratio=[] fixed_size=[] clip=False flip=False step=0.0 offset=0.0 variance=[] scale_all_sizes=True min_max_aspect_ratios_order=True
 detection_output DetectionOutput : box_logits class_preds proposals [aux_class_preds] [aux_box_preds] | background_label_id=0 top_k=-1 variance_encoded_in_target=False keep_top_k=[1] code_type=caffe.PriorBoxParameter.CORNER share_location=True nms_threshold=0.0 confidence_threshold=0.0 clip_after_nms=False clip_before_nms=False decrease_label_id=False normalized=False input_height=1 input_width=1 objectness_score=0.0
 proposal Proposal : class_probs bbox_deltas image_shape | base_size pre_nms_topn post_nms_topn nms_thresh feat_stride min_size ratio scale clip_before_nms=True clip_after_nms=False normalize=False box_size_scale=1.0 box_coordinate_scale=1.0 framework=
