@@ -467,6 +467,67 @@ KvTrace trace_kv(Output v) {
 }
 }  // namespace
 
+
+// What the attention mask of an SDPA encodes besides causality, read from the mask's own subgraph:
+// * a sliding window: a comparison one side of which is a position shifted by a scalar integer constant W
+//   (``k_pos > q_pos - W``, the form of the exported Mistral / Phi-3 / Gemma graphs): W keys stay visible
+//   (W + 1 for the non-strict comparisons);
+// * ALiBi: a per-head constant ([H, 1, 1] or [1, H, 1, 1]) multiplied into a position term that is added to the scores.
+struct MaskFeatures {
+    int64_t window = 0;
+    Output alibi;            // the slopes constant when found
+};
+
+Output skip_shape_ops(Output o) {
+    for (int i = 0; i < 4; ++i) {
+        const std::string& t = o.node->type;
+        if (t == "Convert" || t == "Unsqueeze" || t == "Squeeze" || t == "Reshape") o = o.node->input(0);
+        else break;
+    }
+    return o;
+}
+
+MaskFeatures mask_features(const Output& mask, int64_t heads) {
+    MaskFeatures f;
+    std::vector<NodePtr> stack = {mask.node};
+    std::set<Node*> seen;
+    size_t budget = 400;
+    while (!stack.empty() && budget--) {
+        NodePtr n = stack.back();
+        stack.pop_back();
+        if (!seen.insert(n.get()).second) continue;
+        if (n->is_parameter() || n->type == "ReadValue" || n->type == "Constant") continue;
+        const bool strict = n->type == "Greater" || n->type == "Less";
+        if (strict || n->type == "GreaterEqual" || n->type == "LessEqual") {
+            for (size_t k = 0; k < 2 && f.window == 0; ++k) {
+                Output side = skip_shape_ops(n->input(k));
+                if (side.node->type != "Subtract" && side.node->type != "Add") continue;
+                for (size_t j = 0; j < 2; ++j) {
+                    std::vector<int64_t> c;
+                    Output operand = skip_shape_ops(side.node->input(j));
+                    if (operand.node->type == "Constant" && get_constant_ints(operand, c) && c.size() == 1 && std::llabs(c[0]) >= 2) {
+                        f.window = std::llabs(c[0]) + (strict ? 0 : 1);
+                        break;
+                    }
+                }
+            }
+        }
+        if (n->type == "Multiply" && !f.alibi.node && heads > 1) {
+            for (size_t k = 0; k < 2; ++k) {
+                Output c = skip_shape_ops(n->input(k));
+                if (c.node->type != "Constant" || !et_is_real(c.et())) continue;
+                const PShape& cs = c.shape();
+                if (!cs.is_static()) continue;
+                int64_t total = 1, big = 0;
+                for (auto& d : cs.dims) { total *= d.lo; if (d.lo > 1) big = d.lo; }
+                if (total == heads && big == heads) { f.alibi = c; break; }
+            }
+        }
+        for (size_t k = 0; k < n->num_inputs(); ++k) stack.push_back(n->input(k).node);
+    }
+    return f;
+}
+
 bool sdpa_to_paged_attention(const ModelPtr& m, const AttrMap& options) {
     auto opt_b = [&](const char* k) { auto it = options.find(k); return it != options.end() && it->second.i != 0; };
     (void)opt_b;
@@ -541,8 +602,18 @@ bool sdpa_to_paged_attention(const ModelPtr& m, const AttrMap& options) {
         if (scale.shape().rank_is_static() && scale.shape().rank() > 0) scale = op("Squeeze", {scale})->output(0);
         auto empty_f = [&]() { return make_constant(Tensor(ET::f32, Shape{0}))->output(0); };
         auto empty_i = [&]() { return make_constant(Tensor(ET::i32, Shape{0}))->output(0); };
+        // sliding window and ALiBi slopes: from the options when given, else from the structure of the mask
+        MaskFeatures mf;
+        if (sdpa->num_inputs() > 3) mf = mask_features(sdpa->input(3), Hq);
+        if (auto it = options.find("sliding_window"); it != options.end() && it->second.i > 0) mf.window = it->second.i;
+        Output alibi = empty_f();
+        if (mf.alibi.node) {
+            auto flat_slopes = op("Reshape", {mf.alibi, c_i64({-1})}, {{"special_zero", Attr::Bool(false)}});
+            alibi = flat_slopes->output(0);
+            if (alibi.et() != ET::f32) alibi = op("Convert", {alibi}, {{"destination_type", Attr::Type(ET::f32)}})->output(0);
+        }
         std::vector<Output> ins = {q2, k2, v2, kc->output(0), vc->output(0), past_lens->output(0), subsequence_begins->output(0),
-                                   block_indices->output(0), block_indices_begins->output(0), scale, c_i32({0}, true), empty_f(),
+                                   block_indices->output(0), block_indices_begins->output(0), scale, c_i32({mf.window}, true), alibi,
                                    max_context_len->output(0)};
         // score_aggregation_window, rotated_block_indices, rotation_deltas, rotation_trig_lut, xattention_threshold,
         // xattention_block_size, xattention_stride, sinks, adaptive_rkv (4), token_type_ids, qq_bias, qq_bias_begins

@@ -161,6 +161,9 @@ def build_llama(cfg: LlmConfig, state: Dict[str, torch.Tensor], compress: Option
     q_pos = ops.add(ops.range(_i64(0), ops.squeeze(L), _i64(1), "i64"), ops.squeeze(past))
     k_pos = ops.range(_i64(0), ops.squeeze(S), _i64(1), "i64")
     causal = ops.less_equal(ops.unsqueeze(k_pos, _i64([0])), ops.unsqueeze(q_pos, _i64([1])))   # [L, S]
+    if cfg.sliding_window > 0:          # only the last `sliding_window` keys stay visible: k_pos > q_pos - W
+        near = ops.greater(ops.unsqueeze(k_pos, _i64([0])), ops.subtract(ops.unsqueeze(q_pos, _i64([1])), _i64(cfg.sliding_window)))
+        causal = ops.logical_and(causal, near)
     pad_ok = ops.unsqueeze(ops.not_equal(attention_mask, _i64(0)), _i64([1, 2]))                # [B, 1, 1, S]
     allowed = ops.logical_and(ops.unsqueeze(causal, _i64([0, 1])), pad_ok)
     mask = ops.select(allowed, np.float32(0.0), np.float32(-65504.0), name="attention_bias").output(0)

@@ -310,6 +310,16 @@ def analyze(model: Model) -> Tuple[LlmConfig, Dict]:
                     num_experts=experts[0]["gate"].shape[0] if experts else 0, experts_top_k=experts[0]["top_k"] if experts else 0)
     if experts and len(experts) != len(layers):
         raise NotAnLlm("dense and expert layers in one model are not served")
+    # the sliding window of the paged form is an input of the attention operation (0 = none); ALiBi has no kernel yet
+    for n in ops:
+        if n.get_type_name() == "PagedAttentionExtension" and n.get_input_size() > 11:
+            w = n.input_value(10).get_node()
+            if w.get_type_name() == "Constant":
+                cfg = cfg.with_(sliding_window=int(np.asarray(w.get_data()).reshape(-1)[0]))
+            a = n.input_value(11)
+            if a.get_partial_shape().is_static and int(np.prod(list(a.get_shape()) or [1])) > 0:
+                raise NotAnLlm("attention with ALiBi slopes is not served by the device program")
+            break
     return cfg, {"lin": lin, "norms": norms, "lm_head": lm_head, "final_norm": final_norm, "embed": embed, "layers": layers, "experts": experts}
 
 

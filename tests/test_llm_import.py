@@ -100,3 +100,14 @@ def test_random_int4_builder_writes_compressed_constants_directly():
     assert 0.012 < float(w.std()) < 0.03                    # about the 0.02 that float initialisation would give
     emb = parts["embed"]
     assert emb.shape == (320, 256) and 0.015 < float(emb.abs().min()) and float(emb.abs().max()) < 0.032
+
+
+def test_sliding_window_reaches_the_serving_configuration():
+    """A windowed mask in the SDPA form becomes the sliding_window input of the paged form and then a field of the
+    configuration that the serving program is built from."""
+    cfg = _cfg().with_(sliding_window=5)
+    m = _to_paged(build_llama(cfg, llama.random_float_state(cfg, seed=2, std=0.05)))
+    got, _ = llm_import.analyze(m)
+    assert got.sliding_window == 5
+    plain, _ = llm_import.analyze(_to_paged(build_llama(_cfg(), llama.random_float_state(_cfg(), seed=2, std=0.05))))
+    assert plain.sliding_window == 0

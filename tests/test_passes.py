@@ -254,6 +254,49 @@ def test_sdpa_to_paged_attention(llama_state):
     np.testing.assert_allclose(logits2[0], ref2[-1], rtol=1e-3, atol=1e-4)
 
 
+def test_sdpa_to_paged_attention_reads_sliding_window_and_alibi_from_the_mask():
+    cfg = CFG.with_(sliding_window=3)
+    state = llama.random_float_state(cfg, seed=3, std=0.05)
+    m = build_llama(cfg, state)
+    offline.paged_attention_transformation(m)
+    pas = [n for n in m.get_ops() if n.get_type_name() == "PagedAttentionExtension"]
+    assert all(int(p.input_value(10).get_node().get_data()) == 3 for p in pas)
+    # prefill of 6 tokens: every query sees itself and the two keys before it, like the dense reference with the same window
+    seq = [3, 7, 11, 19, 23, 5]
+    bs = 16
+    feed = {"input_ids": np.array(seq, np.int64), "position_ids": np.arange(6, dtype=np.int64), "past_lens": np.array([0], np.int32),
+            "subsequence_begins": np.array([0, 6], np.int32), "block_indices": np.array([1], np.int32), "block_indices_begins": np.array([0, 1], np.int32),
+            "max_context_len": np.array(6, np.int32)}
+    for l in range(cfg.num_layers):
+        feed["key_cache.%d" % l] = np.zeros((2, cfg.num_kv_heads, bs, cfg.head_dim), np.float32)
+        feed["value_cache.%d" % l] = np.zeros((2, cfg.num_kv_heads, bs, cfg.head_dim), np.float32)
+    logits = ov.compile_model(m, "CPU")(feed)["logits"].reshape(-1, cfg.vocab_size)
+    ref = llama.reference_logits(cfg, state, torch.tensor(seq)).numpy()
+    np.testing.assert_allclose(logits, ref, rtol=1e-3, atol=1e-4)
+    full = llama.reference_logits(CFG, state, torch.tensor(seq)).numpy()
+    assert np.abs(full[-1] - ref[-1]).max() > 1e-4                  # the window matters for the later tokens
+    # ALiBi: slopes [H, 1, 1] times a position term, added to a causal mask
+    H, D = 4, 8
+    q, k, v = (ops.parameter([1, H, -1, D], "f32", n) for n in "qkv")
+    past_k = ops.read_value(ops.constant(np.zeros((1, H, 0, D), np.float32)), "pk", "f32", [1, H, -1, D])
+    past_v = ops.read_value(ops.constant(np.zeros((1, H, 0, D), np.float32)), "pv", "f32", [1, H, -1, D])
+    kk, vv = ops.concat([past_k, k], 2), ops.concat([past_v, v], 2)
+    ids = ops.parameter([1, -1], "i64", "input_ids")
+    L = ops.gather(ops.shape_of(ids), np.array([1], np.int64), np.int64(0))
+    pos = ops.convert(ops.range(np.int64(0), ops.squeeze(L), np.int64(1), "i64"), "f32")
+    slopes = np.array([0.5, 0.25, 0.125, 0.0625], np.float32).reshape(H, 1, 1)
+    bias = ops.multiply(slopes, ops.unsqueeze(pos, np.array([0, 1], np.int64)))                       # [H, 1, L]
+    causal = ops.select(ops.less_equal(ops.unsqueeze(pos, np.array([0], np.int64)), ops.unsqueeze(pos, np.array([1], np.int64))), np.float32(0), np.float32(-65504))
+    mask = ops.add(ops.unsqueeze(bias, np.array([0], np.int64)), ops.unsqueeze(causal, np.array([0, 1], np.int64)))
+    att = ops.scaled_dot_product_attention(q, kk, vv, mask)
+    ma = Model([att], [q, k, v, ids], "alibi", [ops.assign(kk, "pk"), ops.assign(vv, "pv")])
+    offline.paged_attention_transformation(ma)
+    pa = next(n for n in ma.get_ops() if n.get_type_name() == "PagedAttentionExtension")
+    folded = ov.compile_model(Model([pa.input_value(11)], [], "s"), "CPU")([])[0]
+    np.testing.assert_allclose(folded, slopes.reshape(-1))
+    assert int(pa.input_value(10).get_node().get_data()) == 0
+
+
 def test_visualize_and_serialize_passes(tmp_path):
     x = ops.parameter([1], "f32")
     m = Model([ops.relu(x)], [x], "v")
