@@ -19,6 +19,7 @@ void register_vision_ops();
 void register_detection_ops();
 void register_rest_ops();
 void register_recurrent_ops();
+void register_private_ops();
 
 namespace {
 
@@ -1138,6 +1139,7 @@ void register_all_ops() {
         register_detection_ops();
         register_rest_ops();
         register_recurrent_ops();
+        register_private_ops();
     });
 }
 

@@ -20,6 +20,12 @@ from ._graph import Model, Node, Output, as_output, constant, make_op, parameter
 from ._types import PartialShape, Type
 
 _SPEC = """
+gather_matmul GatherMatmul@ie_internal_opset : A B indices [bias]
+gather_matmul_compressed GatherMatmulCompressed@ie_internal_opset : A B indices bias weight_scales [weight_zero_points]
+grouped_matmul_compressed GroupedMatMulCompressed@ie_internal_opset : *inputs
+fully_connected_quantized FullyConnectedQuantized@ie_internal_opset : X W bias weight_scales weight_zero_points input_scales input_zero_points output_scales output_zero_points | output_type=dynamic
+fully_connected_quantized_legacy FullyConnectedQuantizedLegacy@ie_internal_opset : X W bias deq_scales [deq_zero_points] | output_type=dynamic
+vl_sdpa VLSDPA@ie_internal_opset : q k v cu_seqlens | order_q=[] order_k=[] order_v=[] order_out=[]
 selective_ssm SelectiveSSM@ie_internal_opset : A dt B x C recurrent_state
 gated_delta_net GatedDeltaNet@ie_internal_opset : query key value recurrent_state gate beta | fuse_qk_l2norm=False q_l2_norm_eps=1e-6 k_l2_norm_eps=1e-6
 paged_selective_ssm PagedSelectiveSSM@ie_internal_opset : A dt B x C recurrent_state_table subsequence_begins la_block_indices la_block_indices_begins num_processed_tokens cache_interval
