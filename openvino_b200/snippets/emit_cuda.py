@@ -31,6 +31,7 @@ from .op_table import OPS, REDUCTIONS, _f
 _CTYPE = {"f32": "float", "f16": "__half", "bf16": "__nv_bfloat16", "boolean": "unsigned char", "u8": "unsigned char"}
 _ESIZE = {"f32": 4, "f16": 2, "bf16": 2, "boolean": 1, "u8": 1}
 MAX_IO = 12
+KEPT_ITERS = (1, 2, 4)
 
 _PRELUDE = r"""
 #include <cuda_runtime.h>
@@ -38,6 +39,7 @@ _PRELUDE = r"""
 #include <cuda_bf16.h>
 #include <math.h>
 struct Args { const void* in[%(max_io)d]; void* out[%(max_io)d]; long long rs[%(max_io)d]; long long cs[%(max_io)d]; long long rows; long long cols; };
+__device__ __forceinline__ float tanh_fast(float x) { float y; asm("tanh.approx.f32 %%0, %%1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float widen(float v) { return v; }
 __device__ __forceinline__ float widen(__half v) { return __half2float(v); }
 __device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -60,6 +62,36 @@ __device__ __forceinline__ void copy_bytes(void* d, const void* s) {
         for (int i = 0; i < BYTES; ++i) reinterpret_cast<unsigned char*>(d)[i] = reinterpret_cast<const unsigned char*>(s)[i];
     }
 }
+// conversions of a whole vector: two values per instruction for the 16-bit types
+template <class T, int VEC>
+__device__ __forceinline__ void widen_all(const T* src, float* dst) {
+    if constexpr (sizeof(T) == 2 && VEC %% 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) {
+            float2 f;
+            if constexpr (sizeof(T) == 2 && __is_same(T, __half)) f = __half22float2(reinterpret_cast<const __half2*>(src)[i]);
+            else f = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[i]);
+            dst[2 * i] = f.x;
+            dst[2 * i + 1] = f.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) dst[i] = widen(src[i]);
+    }
+}
+template <class T, int VEC>
+__device__ __forceinline__ void narrow_all(T* dst, const float* src) {
+    if constexpr (sizeof(T) == 2 && VEC %% 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) {
+            if constexpr (__is_same(T, __half)) reinterpret_cast<__half2*>(dst)[i] = __floats2half2_rn(src[2 * i], src[2 * i + 1]);
+            else reinterpret_cast<__nv_bfloat162*>(dst)[i] = __floats2bfloat162_rn(src[2 * i], src[2 * i + 1]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) narrow(dst[i], src[i]);
+    }
+}
 // VEC values of one input for columns c .. c+VEC-1 of row r: one 16-byte (or narrower) load when the input runs along
 // the row, one scalar load repeated when it is constant along the row
 template <class T, int VEC>
@@ -74,8 +106,7 @@ __device__ __forceinline__ void load_vec(const void* base, long long rs, long lo
     } else {
         alignas(16) T tmp[VEC];
         copy_bytes<VEC * (int)sizeof(T)>(tmp, p + c);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) dst[i] = widen(tmp[i]);
+        widen_all<T, VEC>(tmp, dst);
     }
 }
 template <class T, int VEC>
@@ -85,8 +116,7 @@ __device__ __forceinline__ void store_vec(void* base, long long r, long long col
         narrow(p[0], src[0]);
     } else {
         alignas(16) T tmp[VEC];
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) narrow(tmp[i], src[i]);
+        narrow_all<T, VEC>(tmp, src);
         copy_bytes<VEC * (int)sizeof(T)>(p, tmp);
     }
 }
@@ -135,20 +165,26 @@ def _col_stmt(lir: LinearIR, i: int) -> str:
     return "const float c%d = %s;" % (i, OPS[e.op].cuda(e.attrs, *["c%d" % a for a in e.args]))
 
 
-def _loop_body(lir: LinearIR, lp, indent: str) -> List[str]:
-    """Statements of one pass for VEC columns starting at c (registers are float[VEC] arrays)."""
+def _loop_body(lir: LinearIR, lp, indent: str, kept: bool = False) -> List[str]:
+    """Statements of one pass for VEC columns starting at c (registers are float[VEC] arrays). In ``kept`` mode values
+    of earlier passes are read back from the per-thread arrays k<id>[it] and values that later passes need are saved."""
     out = []
     nregs = 1 + max(lp.regs.values()) if lp.regs else 0
     for k in range(nregs):
         out.append("%sfloat r%d[VEC];" % (indent, k))
     for i in lp.body:
         e = lir.exprs[i]
+        if kept and i in lp.readback:
+            out.append("%s_Pragma(\"unroll\") for (int i = 0; i < VEC; ++i) r%d[i] = k%d[it][i];" % (indent, lp.regs[i], i))
+            continue
         if e.kind == "param":
             t = _CTYPE[lir.in_types[e.index]]
             out.append("%sload_vec<%s, VEC>(a.in[%d], a.rs[%d], a.cs[%d], r, c, r%d);" % (indent, t, e.index, e.index, e.index, lp.regs[i]))
         else:
             args = [_name(lir, lp, a_, "i") for a_ in e.args]
             out.append("%s_Pragma(\"unroll\") for (int i = 0; i < VEC; ++i) r%d[i] = %s;" % (indent, lp.regs[i], OPS[e.op].cuda(e.attrs, *args)))
+        if kept and i in lir.kept and e.stage == lp.index:
+            out.append("%s_Pragma(\"unroll\") for (int i = 0; i < VEC; ++i) k%d[it][i] = r%d[i];" % (indent, i, lp.regs[i]))
     for rd in lp.reduces:
         src = lir.exprs[rd].args[0]
         comb = REDUCTIONS[lir.exprs[rd].op][2]("acc%d" % rd, _name(lir, lp, src, "i"))
@@ -160,6 +196,11 @@ def _loop_body(lir: LinearIR, lp, indent: str) -> List[str]:
 
 
 def generate_source(lir: LinearIR) -> str:
+    # all streams 16 bits wide: approximate transcendentals are below the resolution of what is stored
+    fast = all(_ESIZE[t] <= 2 for t in lir.in_types + lir.out_types) and any(t in ("f16", "bf16") for t in lir.out_types)
+    for e in lir.exprs:
+        if e.kind == "op":
+            e.attrs = dict(e.attrs, _fast=fast)
     src = [_PRELUDE % {"max_io": MAX_IO}]
     src.append("template <int VEC> __device__ __forceinline__ void run(const Args& a) {")
     if not lir.has_reduce:
@@ -193,10 +234,50 @@ def generate_source(lir: LinearIR) -> str:
                 src.append("        if (threadIdx.x == 0) narrow(reinterpret_cast<%s*>(a.out[%d])[r], c%d);" % (t, s.output, s.value))
         src.append("    }")
     src.append("}")
+    use_kept = bool(lir.has_reduce and lir.kept and lir.loops_kept)
+    if use_kept:
+        # the same passes with the reused values held in registers: ITERS iterations of the CTA cover a row
+        src.append("template <int VEC, int ITERS> __device__ __forceinline__ void run_kept(const Args& a) {")
+        src.append("    __shared__ float sm[32];")
+        src.append("    for (long long r = blockIdx.x; r < a.rows; r += gridDim.x) {")
+        for i in lir.kept:
+            src.append("        float k%d[ITERS][VEC];" % i)
+        for lp in lir.loops_kept:
+            for i in lp.prologue:
+                src.append("        " + _col_stmt(lir, i))
+            for rd in lp.reduces:
+                src.append("        float acc%d = %s;" % (rd, _f(REDUCTIONS[lir.exprs[rd].op][0])))
+            if lp.body:
+                src.append("        _Pragma(\"unroll\") for (int it = 0; it < ITERS; ++it) {")
+                src.append("            const long long c = ((long long)it * blockDim.x + threadIdx.x) * VEC;")
+                src.append("            if (c < a.cols) {")
+                src.extend(_loop_body(lir, lp, "                ", kept=True))
+                src.append("            }")
+                src.append("        }")
+            for rd in lp.reduces:
+                src.append("        const float c%d = %s(acc%d, sm);" % (rd, REDUCTIONS[lir.exprs[rd].op][3], rd))
+        for i in lir.epilogue:
+            src.append("        " + _col_stmt(lir, i))
+        for s_ in lir.stores:
+            if s_.domain == COL:
+                t = _CTYPE[lir.out_types[s_.output]]
+                src.append("        if (threadIdx.x == 0) narrow(reinterpret_cast<%s*>(a.out[%d])[r], c%d);" % (t, s_.output, s_.value))
+        src.append("    }")
+        src.append("}")
+        for it in KEPT_ITERS:
+            src.append("extern \"C\" __global__ void __launch_bounds__(256) snippet_vec_k%d(Args a) { run_kept<%d, %d>(a); }" % (it, vec_width(lir), it))
     src.append("extern \"C\" __global__ void __launch_bounds__(256) snippet_vec(Args a) { run<%d>(a); }" % vec_width(lir))
     src.append("extern \"C\" __global__ void __launch_bounds__(256) snippet_scalar(Args a) { run<1>(a); }")
-    src.append("extern \"C\" int snippet_launch(const Args* a, int vec, int grid, int block, void* stream) {")
-    src.append("    if (vec) snippet_vec<<<grid, block, 0, (cudaStream_t)stream>>>(*a); else snippet_scalar<<<grid, block, 0, (cudaStream_t)stream>>>(*a);")
+    src.append("extern \"C\" int snippet_launch(const Args* a, int variant, int grid, int block, void* stream) {")
+    src.append("    // variant: 0 scalar, 1 vector, 2 + n vector with kept values and KEPT_ITERS[n] iterations per row")
+    src.append("    switch (variant) {")
+    src.append("        case 0: snippet_scalar<<<grid, block, 0, (cudaStream_t)stream>>>(*a); break;")
+    src.append("        case 1: snippet_vec<<<grid, block, 0, (cudaStream_t)stream>>>(*a); break;")
+    if use_kept:
+        for n_, it in enumerate(KEPT_ITERS):
+            src.append("        case %d: snippet_vec_k%d<<<grid, block, 0, (cudaStream_t)stream>>>(*a); break;" % (2 + n_, it))
+    src.append("        default: return (int)cudaErrorInvalidValue;")
+    src.append("    }")
     src.append("    return (int)cudaGetLastError();")
     src.append("}")
     return "\n".join(src) + "\n"
@@ -274,12 +355,19 @@ class CudaKernel:
             cs == 0 or (cs == 1 and p % 16 == 0 and (rs * e) % 16 == 0) for p, rs, cs, e in zip(in_ptrs, in_rs, in_cs, esz_in)) and \
             all((cols * _ESIZE[t]) % 16 == 0 for t in self.lir.out_types)
         width = v if vec_ok else 1
+        variant = 1 if vec_ok else 0
         if self.lir.has_reduce:
             block = 256 if cols >= 256 * width else max(32, ((cols // width + 31) // 32) * 32)
             grid = max(1, min(rows, sm_count * 8))
+            if vec_ok and self.lir.kept and self.lir.loops_kept:
+                need = -(-cols // (block * width))            # iterations of the CTA over one row
+                for n_, it in enumerate(KEPT_ITERS):
+                    if it >= need:
+                        variant = 2 + n_
+                        break
         else:
             block = 256
             grid = max(1, min((rows * (cols // width) + block - 1) // block, sm_count * 16))
-        rc = self._lib.snippet_launch(ctypes.byref(a), 1 if vec_ok else 0, int(grid), int(block), ctypes.c_void_p(stream))
+        rc = self._lib.snippet_launch(ctypes.byref(a), variant, int(grid), int(block), ctypes.c_void_p(stream))
         if rc != 0:
             raise RuntimeError("snippet kernel launch failed with CUDA error %d" % rc)

@@ -58,6 +58,7 @@ class Loop:
     reduces: List[int]             # reductions accumulated in this pass
     stores: List[Store]
     regs: Dict[int, int] = field(default_factory=dict)      # expression id -> virtual register inside the body
+    readback: List[int] = field(default_factory=list)       # kept values of earlier passes that this pass reads back
 
 
 @dataclass
@@ -69,6 +70,8 @@ class LinearIR:
     in_types: List[str]
     out_types: List[str]
     in_kinds: Tuple[str, ...]      # per input: full | row | col | scalar
+    loops_kept: List[Loop] = field(default_factory=list)   # the same passes when `kept` values stay in registers between them
+    kept: List[int] = field(default_factory=list)
 
     @property
     def has_reduce(self) -> bool:
@@ -90,8 +93,18 @@ class _Builder:
 
     def add(self, kind, **kw) -> int:
         e = Expr(len(self.exprs), kind, **kw)
+        if kind == "op":
+            e.domain = COL if all(self.exprs[a].domain == COL for a in e.args) else FULL
+        elif kind == "reduce":
+            e.domain = COL
         self.exprs.append(e)
         return e.id
+
+    def divide(self, x: int, d: int, attrs=None) -> int:
+        """x / d; with a per-row d (the sum of a Softmax) it becomes x * (1 / d): one division per row, not per element."""
+        if self.exprs[x].domain == FULL and self.exprs[d].domain == COL:
+            return self.add("op", op="Multiply", args=(x, self.add("op", op="Reciprocal", args=(d,))))
+        return self.add("op", op="Divide", args=(x, d), attrs=attrs or {})
 
 
 def _const_scalar(node) -> Optional[float]:
@@ -133,7 +146,7 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
             d = b.add("op", op="Subtract", args=(args[0], m))
             e = b.add("op", op="Exp", args=(d,))
             s = b.add("reduce", op="sum", args=(e,))
-            value_of[(n, 0)] = b.add("op", op="Divide", args=(e, s))
+            value_of[(n, 0)] = b.divide(e, s)
         elif t in REDUCE_OPS:
             r = b.add("reduce", op=REDUCE_OPS[t], args=(args[0],))     # args[1] is the axes constant, checked by the tokenizer
             if t == "ReduceMean":
@@ -145,7 +158,7 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
                 raise ValueError("operation %s cannot be part of a snippet" % t)
             if t == "Convert":
                 attrs = {"destination_type": str(n.get_output_element_type(0))}
-            value_of[(n, 0)] = b.add("op", op=t, args=tuple(args[:OPS[t].arity]), attrs=attrs)
+            value_of[(n, 0)] = b.divide(args[0], args[1], attrs) if t == "Divide" else b.add("op", op=t, args=tuple(args[:OPS[t].arity]), attrs=attrs)
     exprs = b.exprs
     # domains and stages
     for e in exprs:
@@ -162,6 +175,31 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
         src = r.input_value(0)
         vid = value_of[(src.get_node(), src.get_index())]
         stores.append(Store(k, vid, exprs[vid].domain, exprs[vid].avail))
+    loops, epilogue = _plan_loops(exprs, stores, set())
+    # values worth keeping in registers from the pass that computes them to the later passes that read them again
+    kept = _values_to_keep(exprs, stores)
+    loops_kept = _plan_loops(exprs, stores, kept)[0] if kept else []
+    return LinearIR(exprs, stores, loops, epilogue, [str(p.get_output_element_type(0)) for p in params],
+                    [str(r.get_input_element_type(0)) for r in body.get_results()], tuple(in_kinds), loops_kept, sorted(kept))
+
+
+def _values_to_keep(exprs: List[Expr], stores: List[Store], limit: int = 6) -> set:
+    """Full-domain results that a later pass reads: recomputing them costs their whole cone of operations again, keeping
+    them costs VEC registers per value and iteration. Inputs are not kept (a load is as cheap as a register move)."""
+    kept = set()
+    for e in exprs:
+        if e.kind != "op" or e.domain != FULL:
+            continue
+        later = any(x.kind in ("op", "reduce") and e.id in x.args and x.stage > e.stage for x in exprs) or any(s.value == e.id and s.stage > e.stage for s in stores)
+        if later:
+            kept.add(e.id)
+    if len(kept) > limit:
+        return set()
+    return kept
+
+
+def _plan_loops(exprs: List[Expr], stores: List[Store], kept: set):
+    """Passes over a row. With ``kept`` values a later pass reads them back instead of walking into their arguments."""
     n_loops = 1 + max([e.stage for e in exprs if e.kind == "reduce"] + [s.stage for s in stores if s.domain == FULL] + [0])
     loops: List[Loop] = []
     done_col: set = set()
@@ -170,6 +208,8 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
         lstores = [s for s in stores if s.domain == FULL and s.stage == k]
         need: set = set()
         stack = [exprs[r].args[0] for r in reduces] + [s.value for s in lstores]
+        # a kept value is written in the pass of its own stage even if nothing else of that pass reads it
+        stack += [i for i in kept if exprs[i].stage == k]
         col_need: set = set()
         while stack:
             i = stack.pop()
@@ -180,9 +220,10 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
             if i in need:
                 continue
             need.add(i)
+            if i in kept and e.stage < k:
+                continue                      # read back, not recomputed
             stack.extend(e.args)
         # col-domain values read by this loop (and whatever col-domain values they are computed from), once per row
-        prologue: List[int] = []
         stack = sorted(col_need)
         seen: set = set()
         while stack:
@@ -195,10 +236,10 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
         prologue = sorted(i for i in seen if exprs[i].kind in ("op", "scalar", "inv_cols", "param"))
         done_col |= set(prologue)
         lp = Loop(k, prologue, sorted(need), reduces, lstores)
+        lp.readback = sorted(i for i in need if i in kept and exprs[i].stage < k)
         _assign_registers(lp, exprs)
         loops.append(lp)
     # col-domain stores (a reduction result that leaves the snippet) and their inputs
-    epilogue: List[int] = []
     stack = [s.value for s in stores if s.domain == COL]
     seen = set()
     while stack:
@@ -209,8 +250,7 @@ def lower(body, in_kinds: Sequence[str]) -> LinearIR:
         if exprs[i].kind == "op":
             stack.extend(exprs[i].args)
     epilogue = sorted(i for i in seen if exprs[i].kind != "reduce")
-    return LinearIR(exprs, stores, loops, epilogue, [str(p.get_output_element_type(0)) for p in params],
-                    [str(r.get_input_element_type(0)) for r in body.get_results()], tuple(in_kinds))
+    return loops, epilogue
 
 
 def _assign_registers(lp: Loop, exprs: List[Expr]) -> None:

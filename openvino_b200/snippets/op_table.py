@@ -1,7 +1,9 @@
 """Operations a snippet may contain: how each is evaluated by the NumPy executor and how the CUDA emitter writes it.
 
 Every value inside a snippet is an fp32 scalar per element (16-bit inputs are widened on load, results narrowed on
-store; booleans are 0.0 / 1.0), so one table serves every element type. Role of the emitter tables of the reference
+store; booleans are 0.0 / 1.0), so one table serves every element type. When every input and output of a snippet is a 16-bit type the emitter sets
+``_fast`` in the attributes: sigmoid-shaped functions then cost one ``tanh.approx`` (relative error about 5e-4, below
+the resolution of the stored values) instead of an exponential and a reciprocal. Role of the emitter tables of the reference
 (src/common/snippets/include/snippets/target_machine.hpp, src/plugins/intel_cpu/src/emitters/snippets/x64/cpu_generator.cpp).
 """
 from __future__ import annotations
@@ -42,6 +44,8 @@ def _gelu_np(a, x):
 
 def _gelu_cu(a, x):
     if str(a.get("approximation_mode", "ERF")).upper() == "TANH":
+        if a.get("_fast"):
+            return "(0.5f * %s * (1.0f + tanh_fast(0.7978845608028654f * (%s + 0.044715f * %s * %s * %s))))" % (x, x, x, x, x)
         return "(0.5f * %s * (1.0f + tanhf(0.7978845608028654f * (%s + 0.044715f * %s * %s * %s))))" % (x, x, x, x, x)
     return "(0.5f * %s * (1.0f + erff(%s * 0.70710678118654752f)))" % (x, x)
 
@@ -76,8 +80,9 @@ def _cmp(sym):
 
 OPS: Dict[str, OpDef] = {
     "Relu": OpDef(1, lambda a, x: np.maximum(x, 0), lambda a, x: "fmaxf(%s, 0.0f)" % x),
-    "Sigmoid": OpDef(1, lambda a, x: 1 / (1 + np.exp(-x)), lambda a, x: "(1.0f / (1.0f + __expf(-%s)))" % x),
-    "Tanh": OpDef(1, lambda a, x: np.tanh(x), lambda a, x: "tanhf(%s)" % x),
+    "Sigmoid": OpDef(1, lambda a, x: 1 / (1 + np.exp(-x)),
+                     lambda a, x: ("(0.5f * tanh_fast(0.5f * %s) + 0.5f)" % x) if a.get("_fast") else ("__fdividef(1.0f, 1.0f + __expf(-%s))" % x)),
+    "Tanh": OpDef(1, lambda a, x: np.tanh(x), lambda a, x: ("tanh_fast(%s)" if a.get("_fast") else "tanhf(%s)") % x),
     "Exp": OpDef(1, lambda a, x: np.exp(x), lambda a, x: "__expf(%s)" % x),
     "Log": OpDef(1, lambda a, x: np.log(x), lambda a, x: "__logf(%s)" % x),
     "Sqrt": OpDef(1, lambda a, x: np.sqrt(x), lambda a, x: "sqrtf(%s)" % x),
@@ -89,7 +94,8 @@ OPS: Dict[str, OpDef] = {
     "Sin": OpDef(1, lambda a, x: np.sin(x), lambda a, x: "sinf(%s)" % x),
     "Cos": OpDef(1, lambda a, x: np.cos(x), lambda a, x: "cosf(%s)" % x),
     "Gelu": OpDef(1, _gelu_np, _gelu_cu),
-    "Swish": OpDef(1, lambda a, x: x / (1 + np.exp(-x)), lambda a, x: "(%s / (1.0f + __expf(-%s)))" % (x, x)),
+    "Swish": OpDef(1, lambda a, x: x / (1 + np.exp(-x)),
+                   lambda a, x: ("(%s * (0.5f * tanh_fast(0.5f * %s) + 0.5f))" % (x, x)) if a.get("_fast") else ("__fdividef(%s, 1.0f + __expf(-%s))" % (x, x))),
     "HSwish": OpDef(1, lambda a, x: x * np.clip(x + 3, 0, 6) / 6, lambda a, x: "(%s * fminf(fmaxf(%s + 3.0f, 0.0f), 6.0f) * (1.0f / 6.0f))" % (x, x)),
     "HSigmoid": OpDef(1, lambda a, x: np.clip(x + 3, 0, 6) / 6, lambda a, x: "(fminf(fmaxf(%s + 3.0f, 0.0f), 6.0f) * (1.0f / 6.0f))" % x),
     "Mish": OpDef(1, lambda a, x: x * np.tanh(np.log1p(np.exp(x))), lambda a, x: "(%s * tanhf(log1pf(__expf(%s))))" % (x, x)),
@@ -98,6 +104,7 @@ OPS: Dict[str, OpDef] = {
                  lambda a, x: "(%s > 0.0f ? %s : %s * (__expf(%s) - 1.0f))" % (x, x, _f(a.get("alpha", 1.0)), x)),
     "Clamp": OpDef(1, lambda a, x: np.clip(x, float(a["min"]), float(a["max"])), lambda a, x: "fminf(fmaxf(%s, %s), %s)" % (x, _f(a["min"]), _f(a["max"]))),
     "Convert": OpDef(1, _round_to, _round_to_cu),
+    "Reciprocal": OpDef(1, lambda a, x: 1.0 / x, lambda a, x: "(1.0f / %s)" % x),          # made by the lowering, never tokenised
     "LogicalNot": OpDef(1, lambda a, x: (x == 0).astype(np.float32), lambda a, x: "((%s) == 0.0f ? 1.0f : 0.0f)" % x, True),
     "Add": OpDef(2, lambda a, x, y: x + y, lambda a, x, y: "(%s + %s)" % (x, y)),
     "Subtract": OpDef(2, lambda a, x, y: x - y, lambda a, x, y: "(%s - %s)" % (x, y)),

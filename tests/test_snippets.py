@@ -43,6 +43,11 @@ def test_tokenizer_forms_one_subgraph_and_host_matches():
     assert max(lir.loops[2].regs.values()) <= 2                 # registers are reused along the chain
     src = generate_source(lir)
     assert "block_max" in src and "block_sum" in src and src.count("for (long long c =") == 3 and vec_width(lir) == 4
+    # the clamped value and the exponentials are held in registers between the passes of the second kernel form,
+    # and the division by the row sum became a multiplication by its reciprocal
+    assert len(lir.kept) == 2 and "run_kept" in src and "snippet_vec_k4" in src
+    assert [len(lp.readback) for lp in lir.loops_kept] == [0, 1, 1]
+    assert any(e.op == "Reciprocal" and e.domain == "col" for e in lir.exprs) and not any(e.op == "Divide" for e in lir.exprs)
 
 
 def test_independent_reductions_share_a_loop_and_col_outputs():
