@@ -40,6 +40,22 @@ bool eval_paged_attention(const Node& n, Ins in, Outs out, EvalContext&) {
     std::vector<float> sinks;
     if (in.size() > 20 && in[20].numel() > 0) sinks = to_f32(in[20]);
     const int64_t G = Hq / Hk;
+    // score aggregation (input 13): 0 = off, N > 0 = the last N new tokens of a sequence vote, N < 0 = all of them
+    std::vector<int64_t> score_win;
+    if (in.size() > 13 && in[13].numel() > 0) score_win = to_i64(in[13]);
+    // re-rotation of cached keys (inputs 14..16): physical blocks whose keys still carry the position they had before an
+    // eviction moved them; deltas name the row of the (cos | sin) table per block or per token of the block
+    std::vector<int64_t> rot_blocks, rot_deltas;
+    std::vector<float> rot_lut;
+    int64_t rot_per_block = 1;
+    if (in.size() > 16 && in[14].numel() > 0 && in[15].numel() > 0 && in[16].numel() > 0) {
+        rot_blocks = to_i64(in[14]);
+        rot_deltas = to_i64(in[15]);
+        rot_lut = to_f32(in[16]);
+        rot_per_block = std::max<int64_t>(1, (int64_t)rot_deltas.size() / (int64_t)rot_blocks.size());
+        OVC_CHECK(rot_per_block == 1 || rot_per_block == bs, n.description() << ": rotation_deltas holds one row per block or one per token of a block");
+        OVC_CHECK((int64_t)rot_lut.size() % S == 0, n.description() << ": rotation_trig_lut rows must be head_size wide");
+    }
     auto q = to_f32(Q), kn = to_f32(Kn), vn = to_f32(Vn);
     const bool write = n.attr_bool("write_kv_cache", true);
     auto slot = [&](int64_t b, int64_t pos) -> int64_t {
@@ -63,9 +79,17 @@ bool eval_paged_attention(const Node& n, Ins in, Outs out, EvalContext&) {
     // 2. attention
     std::vector<float> o((size_t)(T * Hq * Sv), 0.f);
     std::vector<float> s;
+    int64_t total_ctx = 0;
+    std::vector<int64_t> score_off((size_t)B, 0);
+    for (int64_t b = 0; b < B; ++b) { score_off[(size_t)b] = total_ctx; total_ctx += past[(size_t)b] + (sb[(size_t)b + 1] - sb[(size_t)b]); }
+    std::vector<float> scores((size_t)total_ctx, 0.f);
+    std::vector<float> krow((size_t)S);
     for (int64_t b = 0; b < B; ++b) {
+        const int64_t new_len = sb[(size_t)b + 1] - sb[(size_t)b];
+        const int64_t win = score_win.empty() ? 0 : score_win[score_win.size() == 1 ? 0 : (size_t)b];
         for (int64_t t = sb[(size_t)b]; t < sb[(size_t)b + 1]; ++t) {
             const int64_t qpos = past[(size_t)b] + (t - sb[(size_t)b]);
+            const bool votes = win != 0 && (win < 0 || (new_len - (t - sb[(size_t)b])) <= win);
             const int64_t lo = window > 0 ? std::max<int64_t>(0, qpos - window + 1) : 0;
             const int64_t cnt = qpos - lo + 1;
             s.resize((size_t)cnt);
@@ -76,8 +100,24 @@ bool eval_paged_attention(const Node& n, Ins in, Outs out, EvalContext&) {
                 for (int64_t j = 0; j < cnt; ++j) {
                     const int64_t sl = slot(b, lo + j), blk = sl / bs, off = sl % bs;
                     const int64_t base = ((blk * Hk + hk) * bs + off) * S;
+                    for (int64_t d = 0; d < S; ++d) krow[(size_t)d] = float(get_elem_f64(kc, base + d));
+                    if (!rot_blocks.empty() && lo + j < past[(size_t)b]) {
+                        const auto it = std::find(rot_blocks.begin(), rot_blocks.end(), blk);
+                        if (it != rot_blocks.end()) {
+                            const int64_t r = it - rot_blocks.begin();
+                            const int64_t row = rot_deltas[(size_t)(r * rot_per_block + (rot_per_block == 1 ? 0 : off))];
+                            OVC_CHECK(row >= 0 && (row + 1) * S <= (int64_t)rot_lut.size(), n.description() << ": rotation row " << row << " outside the table");
+                            const float* lut = rot_lut.data() + row * S;
+                            const int64_t half = S / 2;
+                            for (int64_t d = 0; d < half; ++d) {
+                                const float x0 = krow[(size_t)d], x1 = krow[(size_t)(d + half)];
+                                krow[(size_t)d] = x0 * lut[d] - x1 * lut[d + half];
+                                krow[(size_t)(d + half)] = x0 * lut[d + half] + x1 * lut[d];
+                            }
+                        }
+                    }
                     float acc = 0;
-                    for (int64_t d = 0; d < S; ++d) acc += qp[d] * float(get_elem_f64(kc, base + d));
+                    for (int64_t d = 0; d < S; ++d) acc += qp[d] * krow[(size_t)d];
                     acc *= scale;
                     if (!alibi.empty()) acc += alibi[(size_t)h] * float((lo + j) - qpos);
                     s[(size_t)j] = acc;
@@ -94,12 +134,15 @@ bool eval_paged_attention(const Node& n, Ins in, Outs out, EvalContext&) {
                     const int64_t base = ((blk * Hk + hk) * bs + off) * Sv;
                     const float p = s[(size_t)j] * inv;
                     for (int64_t d = 0; d < Sv; ++d) op[d] += p * float(get_elem_f64(vc, base + d));
+                    if (votes) scores[(size_t)(score_off[(size_t)b] + lo + j)] += p;
                 }
             }
         }
     }
     out[0] = from_f32(n.outs[0].et == ET::dynamic ? Q.et : n.outs[0].et, Shape{T, Hq * Sv}, o);
-    out[1] = Tensor(out[0].et, Shape{0});
+    // output 1: one region per sequence (past + new positions), the attention mass each cached position received from the
+    // voting queries, summed over the heads; all zeros when aggregation is off
+    out[1] = score_win.empty() ? Tensor(out[0].et, Shape{0}) : from_f32(out[0].et, Shape{total_ctx}, scores);
     out[2] = Tensor(out[0].et, Shape{0});
     return true;
 }

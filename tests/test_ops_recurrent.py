@@ -188,3 +188,75 @@ def test_augru_cell_and_sequence():
             np.testing.assert_allclose(y[bi, 0, t], h[0].numpy(), rtol=1e-4, atol=1e-5)
         np.testing.assert_allclose(hn[bi, 0], h[0].numpy(), rtol=1e-4, atol=1e-5)
         assert (y[bi, 0, int(lens[bi]):] == 0).all()
+
+
+def _pa(feeds, Hk, S):
+    """A PagedAttentionExtension node over Parameters for every given input (28 inputs, absent ones are empty constants)."""
+    from openvino_b200._graph import make_op
+    types = {np.dtype("float32"): "f32", np.dtype("int32"): "i32", np.dtype("uint8"): "u8"}
+    ps, ins = [], []
+    for i, f in enumerate(feeds):
+        p = ops.parameter(list(f.shape), types[f.dtype], "in%d" % i)
+        ps.append(p)
+        ins.append(p)
+    n = make_op("PagedAttentionExtension", ins, {}, version="extension")
+    n.get_rt_info()["num_k_heads"] = Hk
+    return n, ps
+
+
+def test_paged_attention_scores_and_key_rerotation():
+    rng = np.random.default_rng(11)
+    Hq, Hk, S, bs = 2, 1, 8, 4
+    past, new = 5, 3
+    T = new
+    q = rng.standard_normal((T, Hq * S)).astype(np.float32)
+    k = rng.standard_normal((T, Hk * S)).astype(np.float32)
+    v = rng.standard_normal((T, Hk * S)).astype(np.float32)
+    kc = rng.standard_normal((4, Hk, bs, S)).astype(np.float32)
+    vc = rng.standard_normal((4, Hk, bs, S)).astype(np.float32)
+    blocks = np.array([2, 0], np.int32)                       # logical block 0 -> physical 2, block 1 -> physical 0
+    e_f, e_i = np.zeros((0,), np.float32), np.zeros((0,), np.int32)
+    # table of (cos | sin) rows; row 1 turns every pair by 0.3 rad
+    half = S // 2
+    lut = np.stack([np.concatenate([np.ones(half), np.zeros(half)]), np.concatenate([np.full(half, np.cos(0.3)), np.full(half, np.sin(0.3))])]).astype(np.float32)
+
+    def feeds(score_win, rot):
+        f = [q, k, v, kc.copy(), vc.copy(), np.array([past], np.int32), np.array([0, new], np.int32), blocks, np.array([0, 2], np.int32),
+             np.array(1.0 / np.sqrt(S), np.float32), np.array(0, np.int32), e_f, np.array(past + new, np.int32),
+             np.array(score_win, np.int32)]
+        f += ([np.array([2], np.int32), np.array([1], np.int32), lut] if rot else [e_i, e_i, e_f])
+        f += [e_f, np.array(0, np.int32), np.array(0, np.int32), e_f, e_i, e_i, e_i, e_i, e_i, np.zeros((0,), np.uint8), e_i]
+        return f
+
+    def reference(score_win, rot):
+        kfull = np.concatenate([kc[2, 0], kc[0, 0]])[:past + new].copy()
+        vfull = np.concatenate([vc[2, 0], vc[0, 0]])[:past + new].copy()
+        kfull[past:], vfull[past:] = k, v
+        out = np.zeros((T, Hq * S), np.float32)
+        scores = np.zeros(past + new, np.float32)
+        for i in range(new):
+            qpos = past + i
+            keys = kfull[:qpos + 1].copy()
+            if rot:                                            # cached keys of physical block 2 (positions 0..3) are turned
+                x0, x1 = keys[:4, :half].copy(), keys[:4, half:].copy()
+                keys[:4, :half] = x0 * np.cos(0.3) - x1 * np.sin(0.3)
+                keys[:4, half:] = x0 * np.sin(0.3) + x1 * np.cos(0.3)
+            for h in range(Hq):
+                logit = keys @ q[i, h * S:(h + 1) * S] / np.sqrt(S)
+                w = np.exp(logit - logit.max())
+                w /= w.sum()
+                out[i, h * S:(h + 1) * S] = w @ vfull[:qpos + 1]
+                if score_win != 0 and (score_win < 0 or new - i <= score_win):
+                    scores[:qpos + 1] += w
+        return out, scores
+    for score_win, rot in ((2, False), (-1, True), (0, False)):
+        f = feeds(score_win, rot)
+        node, ps = _pa(f, Hk, S)
+        m = ov.Model([node.output(0), node.output(1)], ps, "pa")
+        res = ov.compile_model(m, "CPU")(f)
+        ro, rs = reference(score_win, rot)
+        np.testing.assert_allclose(res[0], ro, rtol=1e-4, atol=1e-5)
+        np.testing.assert_allclose(res[1], rs, rtol=1e-4, atol=1e-5)
+        assert res[1].shape == (past + new,)
+        if score_win == 2:
+            assert abs(res[1].sum() - 2 * Hq) < 1e-4           # two voting queries, every head's weights sum to one
