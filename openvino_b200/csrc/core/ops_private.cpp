@@ -143,6 +143,37 @@ bool eval_fc_quantized(N n, Ins in, Outs out, C) {
     return true;
 }
 
+
+// ---- static-shape forms of the suppression / proposal operations: the dynamic operation of the public set does the
+// work on a detached node with the same attributes; the rows are then padded to the upper bound that inference gave
+std::vector<Tensor> run_public(const char* type, const char* version, Ins in, const std::vector<std::pair<std::string, Attr>>& attrs, C ctx) {
+    std::vector<Output> ports;
+    for (const Tensor& t : in) ports.push_back(make_parameter(t.et, PShape(t.shape))->output(0));
+    NodePtr node = make_node(type, version, ports, attrs, false);
+    const OpSchema* schema = OpRegistry::get().find(type, version);
+    OVC_CHECK(schema && schema->eval, type << " has no evaluation");
+    node->set_num_outputs(3);
+    std::vector<Tensor> out(3);
+    OVC_CHECK(schema->eval(*node, in, out, ctx), type << ": evaluation refused the inputs");
+    return out;
+}
+
+Tensor pad_rows(const Tensor& t, int64_t rows, double fill) {
+    Shape s = t.shape;
+    const int64_t have = s.empty() ? 0 : s[0];
+    s[0] = rows;
+    Tensor o(t.et, s);
+    const int64_t width = have > 0 ? t.numel() / have : (rows > 0 ? o.numel() / rows : 0);
+    for (int64_t i = 0; i < o.numel(); ++i) {
+        if (i < std::min(have, rows) * width) {
+            if (et_is_real(t.et)) set_elem_f64(o, i, get_elem_f64(t, i)); else set_elem_i64(o, i, get_elem_i64(t, i));
+        } else {
+            if (et_is_real(t.et)) set_elem_f64(o, i, fill); else set_elem_i64(o, i, (int64_t)fill);
+        }
+    }
+    return o;
+}
+
 }  // namespace
 
 void register_private_ops() {
@@ -247,6 +278,103 @@ void register_private_ops() {
             Shape os = Q.shape;
             os[2] = Sv;
             out[0] = from_f32(Q.et, os, o);
+            return true;
+        }, 4, 4);
+
+    // ---- NonMaxSuppressionIEInternal: [B * C * min(boxes, max per class), 3] rows, unused rows filled with -1
+    reg("NonMaxSuppressionIEInternal", "ie_internal_opset", {A("center_point_box", K::INT, Attr::Int(0)), A("sort_result_descending", K::BOOL, Attr::Bool(true)),
+                                                             At("output_type", ET::i64), At("score_output_type", ET::f32), A("rotation", K::INT, Attr::Int(0))},
+        [](Node& n) {
+            n.set_num_outputs(3);
+            PShape o = PShape::dynamic(2);
+            o.dims[1] = Dim(3);
+            std::vector<int64_t> mx;
+            const PShape &b = n.in_shape(0), &s = n.in_shape(1);
+            if (n.num_inputs() > 2 && get_constant_ints(n.input(2), mx) && !mx.empty() && dim_of(b, 1).is_static() && dim_of(s, 0).is_static() && dim_of(s, 1).is_static())
+                o.dims[0] = Dim(std::min(dim_of(b, 1).lo, mx[0]) * dim_of(s, 0).lo * dim_of(s, 1).lo);
+            n.set_output(0, n.attr("output_type").et, o);
+            n.set_output(1, n.attr("score_output_type").et, o);
+            n.set_output(2, n.attr("output_type").et, PShape({Dim(1)}));
+        },
+        [](N n, Ins in, Outs out, C c) {
+            const int64_t rot = n.attr_int("rotation");
+            std::vector<Tensor> res;
+            if (rot == 0) {
+                res = run_public("NonMaxSuppression", "opset9", in, {{"box_encoding", Attr::Str(n.attr_int("center_point_box") ? "center" : "corner")},
+                                 {"sort_result_descending", Attr::Bool(n.attr_bool("sort_result_descending", true))}, {"output_type", Attr::Type(n.attr("output_type").et)}}, c);
+            } else {
+                std::vector<Tensor> five(in.begin(), in.begin() + std::min<size_t>(in.size(), 5));
+                res = run_public("NMSRotated", "opset13", five, {{"sort_result_descending", Attr::Bool(n.attr_bool("sort_result_descending", true))},
+                                 {"output_type", Attr::Type(n.attr("output_type").et)}, {"clockwise", Attr::Bool(rot == 1)}}, c);
+            }
+            const int64_t mx = in.size() > 2 ? get_elem_i64(in[2], 0) : 0;
+            const int64_t rows = std::min<int64_t>(in[0].shape[1], mx) * in[1].shape[0] * in[1].shape[1];
+            out[0] = pad_rows(res[0], rows, -1);
+            out[1] = pad_rows(convert_tensor(res[1], n.attr("score_output_type").et), rows, -1);
+            out[2] = res[2];
+            return true;
+        }, 2, 6);
+
+    // ---- MulticlassNmsIEInternal / MatrixNms static form: rows padded with -1 up to the bound per image
+    auto infer_static_nms = [](Node& n) {
+        n.set_num_outputs(3);
+        const ET it = n.attr("output_type").et;
+        const PShape &b = n.in_shape(0), &s = n.in_shape(1);
+        PShape sel = PShape::dynamic(2), idx = PShape::dynamic(2);
+        sel.dims[1] = Dim(6);
+        idx.dims[1] = Dim(1);
+        const Dim batch = dim_of(b, 0), classes = dim_of(s, 1), boxes = dim_of(b, 1);
+        if (batch.is_static() && classes.is_static() && boxes.is_static()) {
+            int64_t per_class = boxes.lo;
+            if (n.attr_int("nms_top_k", -1) >= 0) per_class = std::min(per_class, n.attr_int("nms_top_k", -1));
+            int64_t per_batch = per_class * classes.lo;
+            if (n.attr_int("keep_top_k", -1) >= 0) per_batch = std::min(per_batch, n.attr_int("keep_top_k", -1));
+            sel.dims[0] = idx.dims[0] = Dim(per_batch * batch.lo);
+        }
+        n.set_output(0, n.in_et(0), sel);
+        n.set_output(1, it, idx);
+        n.set_output(2, it, PShape({batch}));
+    };
+    auto static_nms_eval = [](const char* type, const char* version) {
+        return [type, version](N n, Ins in, Outs out, C c) {
+            auto res = run_public(type, version, in, n.attrs, c);
+            const int64_t rows = n.outs[0].shape.dims[0].is_static() ? n.outs[0].shape.dims[0].lo : res[0].shape[0];
+            out[0] = pad_rows(res[0], rows, -1);
+            out[1] = pad_rows(res[1], rows, -1);
+            out[2] = res[2];
+            return true;
+        };
+    };
+    const std::vector<AttrSpec> mc = {A("sort_result_type", K::STR, Attr::Str("none")), At("output_type", ET::i64), A("nms_top_k", K::INT, Attr::Int(-1)),
+                                      A("keep_top_k", K::INT, Attr::Int(-1)), A("sort_result_across_batch", K::BOOL, Attr::Bool(false)),
+                                      A("iou_threshold", K::FLOAT, Attr::Float(0)), A("score_threshold", K::FLOAT, Attr::Float(0)),
+                                      A("background_class", K::INT, Attr::Int(-1)), A("nms_eta", K::FLOAT, Attr::Float(1)), A("normalized", K::BOOL, Attr::Bool(true))};
+    reg("MulticlassNmsIEInternal", "ie_internal_opset", mc, infer_static_nms, static_nms_eval("MulticlassNms", "opset9"), 2, 3);
+    const std::vector<AttrSpec> mx = {A("sort_result_type", K::STR, Attr::Str("none")), At("output_type", ET::i64), A("nms_top_k", K::INT, Attr::Int(-1)),
+                                      A("keep_top_k", K::INT, Attr::Int(-1)), A("sort_result_across_batch", K::BOOL, Attr::Bool(false)),
+                                      A("score_threshold", K::FLOAT, Attr::Float(0)), A("background_class", K::INT, Attr::Int(-1)),
+                                      A("decay_function", K::STR, Attr::Str("linear")), A("gaussian_sigma", K::FLOAT, Attr::Float(2)),
+                                      A("post_threshold", K::FLOAT, Attr::Float(0)), A("normalized", K::BOOL, Attr::Bool(true))};
+    reg("NmsStaticShapeIE", "ie_internal_opset", mx, infer_static_nms, static_nms_eval("MatrixNms", "opset8"), 2, 2);
+
+    // ---- GenerateProposalsIEInternal: [B * post_nms_count] rows, zero filled
+    reg("GenerateProposalsIEInternal", "ie_internal_opset", {A("min_size", K::FLOAT, Attr::Float(0)), A("nms_threshold", K::FLOAT, Attr::Float(0)), A("post_nms_count", K::INT, Attr::Int(0)),
+                                                             A("pre_nms_count", K::INT, Attr::Int(0)), A("normalized", K::BOOL, Attr::Bool(true)), A("nms_eta", K::FLOAT, Attr::Float(1)),
+                                                             At("roi_num_type", ET::i64)},
+        [](Node& n) {
+            n.set_num_outputs(3);
+            const Dim batch = dim_of(n.in_shape(0), 0);
+            const Dim rows = batch.is_static() ? Dim(batch.lo * n.attr_int("post_nms_count")) : Dim::dynamic();
+            n.set_output(0, n.in_et(0), PShape({rows, Dim(4)}));
+            n.set_output(1, n.in_et(0), PShape({rows}));
+            n.set_output(2, n.attr("roi_num_type").et, PShape({batch}));
+        },
+        [](N n, Ins in, Outs out, C c) {
+            auto res = run_public("GenerateProposals", "opset9", in, n.attrs, c);
+            const int64_t rows = in[3].shape[0] * n.attr_int("post_nms_count");
+            out[0] = pad_rows(res[0], rows, 0);
+            out[1] = pad_rows(res[1], rows, 0);
+            out[2] = res[2];
             return true;
         }, 4, 4);
 }

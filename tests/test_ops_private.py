@@ -95,3 +95,34 @@ def test_vl_sdpa_attends_inside_segments():
         o = torch.nn.functional.scaled_dot_product_attention(q[b:e].transpose(0, 1), k[b:e].transpose(0, 1), v[b:e].transpose(0, 1))
         ref[b:e] = o.transpose(0, 1)
     np.testing.assert_allclose(got, ref.numpy(), rtol=1e-4, atol=1e-5)
+
+
+def test_static_shape_suppression_forms_pad_the_dynamic_ones():
+    from openvino_b200._graph import make_op
+    rng = np.random.default_rng(5)
+    B, M, Cn = 1, 6, 2
+    xy = rng.random((B, M, 2)).astype(np.float32) * 0.5
+    boxes = np.concatenate([xy, xy + 0.3], -1).astype(np.float32)
+    scores = rng.random((B, Cn, M)).astype(np.float32)
+    pb, ps = P(boxes.shape, "b"), P(scores.shape, "s")
+    dyn = ops.non_max_suppression(pb, ps, np.int64(3), np.float32(0.4), np.float32(0.1))
+    d_idx, d_sc, d_valid = run([dyn.output(0), dyn.output(1), dyn.output(2)], [pb, ps], [boxes, scores])
+    st = make_op("NonMaxSuppressionIEInternal", [pb, ps, ops.constant(np.int64(3)), ops.constant(np.float32(0.4)), ops.constant(np.float32(0.1))],
+                 {"center_point_box": 0, "sort_result_descending": True, "output_type": "i64", "score_output_type": "f32", "rotation": 0}, version="ie_internal_opset")
+    assert list(st.get_output_shape(0)) == [3 * Cn * B, 3]
+    s_idx, s_sc, s_valid = run([st.output(0), st.output(1), st.output(2)], [pb, ps], [boxes, scores])
+    k = int(d_valid[0])
+    assert int(s_valid[0]) == k and s_idx.shape == (6, 3)
+    np.testing.assert_array_equal(s_idx[:k], d_idx[:k])
+    np.testing.assert_allclose(s_sc[:k], d_sc[:k])
+    assert (s_idx[k:] == -1).all() and (s_sc[k:] == -1).all()
+    # multiclass form
+    mc_dyn = ops.multiclass_nms(pb, ps, iou_threshold=0.4, score_threshold=0.2, keep_top_k=4)
+    d_sel, d_i, d_n = run([mc_dyn.output(0), mc_dyn.output(1), mc_dyn.output(2)], [pb, ps], [boxes, scores])
+    mc_st = make_op("MulticlassNmsIEInternal", [pb, ps], {"iou_threshold": 0.4, "score_threshold": 0.2, "keep_top_k": 4}, version="ie_internal_opset")
+    assert list(mc_st.get_output_shape(0)) == [4, 6] and list(mc_st.get_output_shape(1)) == [4, 1]
+    s_sel, s_i, s_n = run([mc_st.output(0), mc_st.output(1), mc_st.output(2)], [pb, ps], [boxes, scores])
+    k = int(d_n[0])
+    np.testing.assert_allclose(s_sel[:k], d_sel, rtol=1e-6)
+    np.testing.assert_array_equal(s_i[:k], d_i)
+    assert (s_sel[k:] == -1).all() and int(s_n[0]) == k
