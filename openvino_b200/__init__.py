@@ -17,9 +17,8 @@ from ._tensor import Tensor   # noqa: F401
 from ._graph import Input, Model, Node, Output, RTMap   # noqa: F401
 from ._op_base import DiscreteTypeInfo, Op, register_op   # noqa: F401
 from . import opset   # noqa: F401
-from . import opset as opset1, opset as opset2, opset as opset3, opset as opset4, opset as opset5, opset as opset6   # noqa: F401,E401
-from . import opset as opset7, opset as opset8, opset as opset9, opset as opset10, opset as opset11, opset as opset12   # noqa: F401,E401
-from . import opset as opset13, opset as opset14, opset as opset15, opset as opset16   # noqa: F401,E401
+from . import (opset1, opset2, opset3, opset4, opset5, opset6, opset7, opset8, opset9, opset10, opset11, opset12, opset13, opset14,   # noqa: F401
+               opset15, opset16, opset17)
 from . import properties   # noqa: F401
 from . import passes   # noqa: F401
 from . import preprocess   # noqa: F401
@@ -27,6 +26,8 @@ from .preprocess import Layout, layout_helpers   # noqa: F401
 from .frontend import FrontEndManager, convert_model, read_model, save_model, serialize   # noqa: F401
 from .runtime.core import (AsyncInferQueue, CompiledModel, Core, InferRequest, OVDict, ProfilingInfo, VariableState, Version,   # noqa: F401
                            __version__, compile_model)
+from ._compat import (AxisSet, AxisVector, Coordinate, CoordinateDiff, Extension, OpExtension, OVAny, Strides, get_batch, set_batch,   # noqa: F401
+                      tensor_from_file)
 from .utils.shutdown import register_shutdown_callback, shutdown, unregister_shutdown_callback   # noqa: F401
 
 __all__ = ["AsyncInferQueue", "CompiledModel", "Core", "Dimension", "FrontEndManager", "InferRequest", "Input", "Layout", "Model", "Node",
@@ -37,3 +38,14 @@ __all__ = ["AsyncInferQueue", "CompiledModel", "Core", "Dimension", "FrontEndMan
 
 def get_version() -> str:
     return __version__
+
+
+Any = OVAny
+
+
+def __getattr__(name):
+    # device-side classes live with the CUDA device (importing them pulls in torch): resolved on first use
+    if name in ("RemoteContext", "RemoteTensor"):
+        from .runtime import cuda_plugin
+        return getattr(cuda_plugin, name)
+    raise AttributeError("module %r has no attribute %r" % (__name__, name))

@@ -678,6 +678,19 @@ class Model:
     def get_variables(self):
         return [_Variable(i, PartialShape._from_core(s), Type(t)) for i, s, t in self._m.variables()]
 
+    def add_variables(self, variables) -> None:
+        """Variables follow from the ReadValue / Assign pairs of the graph; adding one that no node uses changes nothing."""
+        known = {v.get_info().variable_id for v in self.get_variables()}
+        for v in variables:
+            if v.get_info().variable_id not in known:
+                self.__dict__.setdefault("_extra_variables", []).append(v)
+
+    def remove_variable(self, variable) -> None:
+        vid = variable.get_info().variable_id
+        if any(v.get_info().variable_id == vid for v in self.get_variables()):
+            raise RuntimeError("variable '%s' is used by ReadValue / Assign nodes of the model" % vid)
+        self.__dict__["_extra_variables"] = [v for v in self.__dict__.get("_extra_variables", []) if v.get_info().variable_id != vid]
+
     def get_variable_by_id(self, vid):
         for v in self.get_variables():
             if v.get_info().variable_id == vid:

@@ -55,7 +55,12 @@ class FrontEnd:
     def add_extension(self, extension) -> None:
         """``ConversionExtension`` (a user translator for one source operation), ``TelemetryExtension``,
         ``ProgressReporterExtension``."""
-        from .input_model import ConversionExtension
+        from .input_model import ConversionExtension, op_extension_translator
+        from .._compat import OpExtension
+        if isinstance(extension, OpExtension):
+            extension.register()
+            if extension.fw_type:
+                extension = ConversionExtension(extension.fw_type, op_extension_translator(extension, self.name))
         if isinstance(extension, ConversionExtension):
             if self._table is None:
                 raise RuntimeError("frontend '%s' has no operation table to extend" % self.name)
@@ -77,6 +82,10 @@ class FrontEnd:
             for t in telemetry:
                 t.send_error("%s: %s" % (type(e).__name__, str(e)[:200]))
             raise
+        from .input_model import DecoderTransformationExtension
+        for e in self._extensions:
+            if isinstance(e, DecoderTransformationExtension):
+                e.transformation(m)
         if telemetry:
             counts = {}
             for n in m.get_ops():
@@ -154,12 +163,23 @@ class PyTorchFrontEnd(FrontEnd):
             import torch
         except ImportError:
             return False
-        return isinstance(model, (torch.nn.Module, torch.jit.ScriptFunction)) or (hasattr(model, "graph_signature") and hasattr(model, "graph"))
+        return isinstance(model, (torch.nn.Module, torch.jit.ScriptFunction)) or (hasattr(model, "graph_signature") and hasattr(model, "graph")) \
+            or self.supported_decoder(model)
+
+    def supported_decoder(self, model) -> bool:
+        return hasattr(model, "convert") and type(model).__name__ in ("TorchScriptPythonDecoder", "TorchFXPythonDecoder")
 
     def convert(self, input_model) -> Model:
         from . import pytorch
         model, kwargs = input_model
-        return pytorch.convert(model, **(kwargs or {}))
+        if self.supported_decoder(model):
+            return model.convert()
+        module_exts = [e for e in self._extensions if isinstance(e, pytorch.ModuleExtension)]
+        undo = pytorch.apply_module_extensions(model, module_exts) if module_exts and hasattr(model, "named_modules") else []
+        try:
+            return pytorch.convert(model, **(kwargs or {}))
+        finally:
+            pytorch.restore_module_extensions(undo)
 
 
 class OnnxFrontEnd(FrontEnd):
@@ -270,6 +290,9 @@ class FrontEndManager:
 
 
 _manager = FrontEndManager()
+from .input_model import (ConversionExtension, DecoderTransformationExtension, InputModel, NodeContext, Place, ProgressReporterExtension,   # noqa: E402,F401
+                          TelemetryExtension)
+from .._compat import OpExtension   # noqa: E402,F401
 
 
 def read_model(model, weights=None, extensions=None) -> Model:

@@ -198,3 +198,52 @@ class ProgressReporterExtension:
         if not (0.0 <= progress <= 1.0) or completed_steps > total_steps:
             raise RuntimeError("bad progress report: %r of %r (%r)" % (completed_steps, total_steps, progress))
         self._cb(progress, total_steps, completed_steps)
+
+
+class NodeContext:
+    """What a user translator sees of one source operation: its inputs as graph outputs and its attributes.
+    ``get_input(i)``, ``get_input_size()``, ``get_attribute(name, default)``, ``get_op_type()``, ``get_name()``."""
+
+    def __init__(self, op_type: str, inputs, attrs: Optional[dict] = None, name: str = ""):
+        self._type, self._inputs, self._attrs, self._name = op_type, list(inputs), dict(attrs or {}), name
+
+    def get_input(self, index: int) -> Output:
+        return self._inputs[index]
+
+    def get_input_size(self) -> int:
+        return len(self._inputs)
+
+    def get_attribute(self, name: str, default=None):
+        return self._attrs.get(name, default)
+
+    def has_attribute(self, name: str) -> bool:
+        return name in self._attrs
+
+    def get_op_type(self) -> str:
+        return self._type
+
+    def get_name(self) -> str:
+        return self._name
+
+
+class DecoderTransformationExtension:
+    """A function applied to every model the frontend has converted (``fn(model)``; a true return value means changed)."""
+
+    def __init__(self, transformation: Callable):
+        self.transformation = transformation
+
+
+def op_extension_translator(ext, frontend_name: str) -> Callable:
+    """Translator for ``OpExtension(target, source, names_map, values_map)``: the source operation becomes one ``target``
+    node over all of its inputs; attributes are taken by the names map (target name -> source name), then the fixed values."""
+    from .._graph import make_op
+    target = ext.op if isinstance(ext.op, str) else ext.op._type_and_version()[0]
+    version = "" if isinstance(ext.op, str) else ext.op._type_and_version()[1]
+
+    def attrs_from(source: dict) -> dict:
+        out = {t: source[s] for t, s in ext.attr_names_map.items() if s in source}
+        out.update(ext.attr_values_map)
+        return out
+    if frontend_name == "onnx":
+        return lambda n, i: [o for o in make_op(target, list(i), attrs_from(n.attrs), version=version).outputs()]
+    raise RuntimeError("OpExtension with a source operation is served by the ONNX frontend; frontend '%s' takes ConversionExtension" % frontend_name)

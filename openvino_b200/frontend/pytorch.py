@@ -1151,3 +1151,90 @@ def _dynamic_spec(input, args, kwargs):
     for ai, s in enumerate(shapes):
         spec.append({i: torch.export.Dim.AUTO if hasattr(torch.export.Dim, "AUTO") else torch.export.Dim("d%d_%d" % (ai, i)) for i, d in enumerate(s) if d < 0} or None)
     return tuple(spec)
+
+
+# ---------------------------------------------------------------------------------------------- public decoder objects
+class TorchScriptPythonDecoder:
+    """What ``FrontEnd.load`` accepts for a PyTorch model: the module (traced or scripted when it is not yet a
+    ScriptModule) with its example input. ``FrontEnd.convert`` of the loaded model decodes the TorchScript graph
+    (torchscript.py). Reference: src/bindings/python/src/openvino/frontend/pytorch/ts_decoder.py."""
+
+    def __init__(self, pt_module, example_input=None, skip_freeze: bool = False, shared_memory: bool = True, trace_kwargs=None, module_extensions=None):
+        import torch
+        self.example_input, self.shared_memory = example_input, shared_memory
+        self.module_extensions = dict(module_extensions or {})
+        if isinstance(pt_module, (torch.jit.ScriptModule, torch.jit.ScriptFunction)):
+            self.pt_module = pt_module
+        else:
+            pt_module.eval()
+            if example_input is None:
+                self.pt_module = torch.jit.script(pt_module)
+            else:
+                args = example_input if isinstance(example_input, (tuple, list)) else (example_input,)
+                self.pt_module = torch.jit.trace(pt_module, tuple(args), strict=False, **(trace_kwargs or {}))
+
+    def convert(self) -> Model:
+        from .torchscript import from_script
+        return from_script(self.pt_module, example_input=self.example_input, share_weights=self.shared_memory)
+
+
+class TorchFXPythonDecoder:
+    """An ``fx.GraphModule`` (``torch.export`` / ``make_fx`` output) for ``FrontEnd.load``; ``from_fx`` does the work.
+    Reference: src/bindings/python/src/openvino/frontend/pytorch/fx_decoder.py."""
+
+    def __init__(self, pt_module, fx_gm=None, input_shapes=None, input_types=None, dynamic_shapes: bool = False):
+        self.pt_module = fx_gm if fx_gm is not None else pt_module
+        self.input_shapes, self.input_types = input_shapes, input_types
+
+    @classmethod
+    def from_exported_program(cls, exported_program):
+        d = cls(exported_program)
+        d._exported = True
+        return d
+
+    def convert(self) -> Model:
+        if getattr(self, "_exported", False) or (hasattr(self.pt_module, "graph_signature") and hasattr(self.pt_module, "graph")):
+            return from_exported_program(self.pt_module, True)
+        return from_fx(self.pt_module)
+
+
+class ModuleExtension:
+    """Replaces a sub-module during conversion: ``ModuleExtension(MyAttention, "MyAttentionOp", convert=...)``. With
+    ``convert(module, target_op, *args, **kwargs)`` the sub-module's forward is swapped for that callable while the model
+    is traced, so the traced graph holds what it returns. Reference: frontend/pytorch/module_extension.py."""
+
+    def __init__(self, module, target_op: str = None, evaluate=None, convert=None, condition=None):
+        self.module, self.target_op, self.evaluate, self.convert, self.condition = module, target_op, evaluate, convert, condition
+
+    def matches(self, name: str, sub) -> bool:
+        if self.condition is not None and not self.condition(sub):
+            return False
+        if isinstance(self.module, str):
+            return name == self.module
+        if isinstance(self.module, type):
+            return isinstance(sub, self.module)
+        return sub is self.module
+
+
+def apply_module_extensions(model, extensions):
+    """Patch the forwards named by ``extensions``; returns the undo list for ``restore_module_extensions``."""
+    undo = []
+    for name, sub in model.named_modules():
+        for ext in extensions:
+            if ext.matches(name, sub) and ext.convert is not None:
+                orig = sub.forward
+                target = ext.target_op
+
+                def patched(*a, _ext=ext, _sub=sub, _orig=orig, _t=target, **kw):
+                    return _ext.convert(_sub, (lambda *x, **y: _orig(*x, **y)) if _t is None else _t, *a, **kw)
+                sub.forward = patched
+                undo.append((sub, orig))
+    return undo
+
+
+def restore_module_extensions(undo) -> None:
+    for sub, orig in undo:
+        sub.forward = orig
+
+
+from .input_model import ConversionExtension   # noqa: E402,F401  (the PyTorch table takes (ctx, node) translators)

@@ -334,6 +334,7 @@ def _make_factory(py_name, op_type, version, inputs, attrs):
 
     factory.__name__ = py_name
     factory.__qualname__ = py_name
+    factory._spec = (py_name, op_type, version, list(inputs), list(attrs))
     sig = ", ".join(inputs + [a for a in attrs])
     factory.__doc__ = "Create a %s operation. Arguments: %s, name=None." % (op_type, sig)
     return factory
@@ -355,6 +356,37 @@ def _build():
 
 
 _build()
+
+
+def export_versioned(namespace: dict, number: int) -> None:
+    """Fill ``namespace`` with the factories of ``opset<number>``: an operation appears when some version of it is at most
+    that set, and the factory then creates the newest such version (``opset1.softmax`` makes Softmax-1, ``opset8.softmax``
+    Softmax-8). Hand-written builders and helpers are shared by all sets. Reference: src/bindings/python/src/openvino/opsetN/."""
+    from . import _ovcore as _c
+    versions: dict = {}
+    for sch in _c.op_schemas():
+        t, v = sch[0], sch[1]
+        if v.startswith("opset") and v[5:].isdigit():
+            versions.setdefault(t, []).append(int(v[5:]))
+    mod = sys.modules[__name__]
+    for name, obj in vars(mod).items():
+        if name.startswith("_"):
+            continue
+        spec = getattr(obj, "_spec", None)
+        if spec is None:
+            if callable(obj) or isinstance(obj, type):
+                namespace.setdefault(name, obj)
+            continue
+        py_name, op_type, version, inputs, attrs = spec
+        have = versions.get(op_type)
+        if version or not have:                      # pinned to a set (internal operations) or not versioned: as is
+            if not version.startswith("opset") or int(version[5:] or 0) <= number:
+                namespace[name] = obj
+            continue
+        best = max((v for v in have if v <= number), default=None)
+        if best is None:
+            continue
+        namespace[name] = _make_factory(py_name, op_type, "opset%d" % best, inputs, attrs)
 
 
 # ---------------------------------------------------------------------------- factories that need hand-written logic

@@ -611,3 +611,10 @@ class Manager:
 
 def available_passes() -> List[str]:
     return list(_c.available_passes())
+
+
+class Version:
+    """IR version selector of ``Serialize`` (``Version.UNSPECIFIED`` writes the newest the model needs)."""
+    UNSPECIFIED = "UNSPECIFIED"
+    IR_V10 = "IR_V10"
+    IR_V11 = "IR_V11"

@@ -160,6 +160,43 @@ intel_auto = _Namespace(
     schedule_policy=_Prop("SCHEDULE_POLICY"),
 )
 
+# Device-specific namespaces of the reference: accepted (and stored) by the CPU device and by AUTO; the CUDA device has its own
+intel_cpu = _Namespace(
+    denormals_optimization=_Prop("CPU_DENORMALS_OPTIMIZATION"),
+    sparse_weights_decompression_rate=_Prop("CPU_SPARSE_WEIGHTS_DECOMPRESSION_RATE"),
+    tbb_partitioner=_Prop("TBB_PARTITIONER"),
+)
+intel_gpu = _Namespace(
+    device_total_mem_size=_Prop("GPU_DEVICE_TOTAL_MEM_SIZE", "RO"),
+    uarch_version=_Prop("GPU_UARCH_VERSION", "RO"),
+    execution_units_count=_Prop("GPU_EXECUTION_UNITS_COUNT", "RO"),
+    memory_statistics=_Prop("GPU_MEMORY_STATISTICS", "RO"),
+    enable_loop_unrolling=_Prop("GPU_ENABLE_LOOP_UNROLLING"),
+    disable_winograd_convolution=_Prop("GPU_DISABLE_WINOGRAD_CONVOLUTION"),
+    enable_sdpa_optimization=_Prop("GPU_ENABLE_SDPA_OPTIMIZATION"),
+    enable_lora_operation=_Prop("GPU_ENABLE_LORA_OPERATION"),
+    enable_kernels_reuse=_Prop("GPU_ENABLE_KERNELS_REUSE"),
+    hint=_Namespace(
+        queue_throttle=_Prop("GPU_QUEUE_THROTTLE"),
+        queue_priority=_Prop("GPU_QUEUE_PRIORITY"),
+        host_task_priority=_Prop("GPU_HOST_TASK_PRIORITY"),
+        available_device_mem=_Prop("AVAILABLE_DEVICE_MEM_SIZE"),
+        dynamic_quantization_group_size_max=_Prop("GPU_DYNAMIC_QUANTIZATION_GROUP_SIZE_MAX"),
+    ),
+)
+intel_npu = _Namespace(
+    device_alloc_mem_size=_Prop("NPU_DEVICE_ALLOC_MEM_SIZE", "RO"),
+    device_total_mem_size=_Prop("NPU_DEVICE_TOTAL_MEM_SIZE", "RO"),
+    driver_version=_Prop("NPU_DRIVER_VERSION", "RO"),
+    compilation_mode_params=_Prop("NPU_COMPILATION_MODE_PARAMS"),
+    turbo=_Prop("NPU_TURBO"),
+    tiles=_Prop("NPU_TILES"),
+    max_tiles=_Prop("NPU_MAX_TILES"),
+    bypass_umd_caching=_Prop("NPU_BYPASS_UMD_CACHING"),
+    defer_weights_load=_Prop("NPU_DEFER_WEIGHTS_LOAD"),
+    use_npuw=_Prop("NPU_USE_NPUW"),
+)
+
 # Properties of the CUDA (B200) device
 cuda = _Namespace(
     use_cuda_graphs=_Prop("CUDA_USE_GRAPHS"),

@@ -417,6 +417,22 @@ class CompiledModel:
         return data
 
 
+def _compiled_get_context(self):
+    """The device context the model was compiled in (devices with device memory only)."""
+    try:
+        name = self.get_property(props.execution_devices)[0]
+    except Exception:   # noqa: BLE001 - the property is optional
+        name = self.plugin.device_name
+    if str(name) == self.plugin.device_name or not hasattr(self.plugin, "core"):
+        if not hasattr(self.plugin, "get_default_context"):
+            raise RuntimeError("device %s has no remote context" % self.plugin.device_name)
+        return self.plugin.get_default_context()
+    return self.plugin.core.get_default_context(str(name).split(".")[0])
+
+
+CompiledModel.get_context = _compiled_get_context
+
+
 class OVDict(dict):
     """Results of an inference: addressable by output port, tensor name or index (``ov.utils.data_helpers.OVDict``)."""
 
@@ -1017,7 +1033,38 @@ class Core:
             return _read(model, weights, self._extensions)
 
     def add_extension(self, ext) -> None:
+        """An ``ov.Op`` sub-class or ``OpExtension`` (the operation becomes readable from IR), a frontend extension
+        (handed to every frontend), or a list of those. Shared libraries of compiled extensions are not loaded."""
+        if isinstance(ext, (list, tuple)):
+            for e in ext:
+                self.add_extension(e)
+            return
+        from .._compat import OpExtension
+        from .._op_base import Op
+        from ..frontend import _manager
+        from ..frontend.input_model import ConversionExtension, DecoderTransformationExtension, ProgressReporterExtension, TelemetryExtension
+        if isinstance(ext, str):
+            raise RuntimeError("extension libraries (%s) are not loaded by this runtime: register the operation with ov.Op / OpExtension" % ext)
+        if isinstance(ext, type) and issubclass(ext, Op):
+            ext._ensure_registered()
+        elif isinstance(ext, OpExtension) and not ext.fw_type:
+            ext.register()
+        elif isinstance(ext, (OpExtension, ConversionExtension, DecoderTransformationExtension, ProgressReporterExtension, TelemetryExtension)):
+            for fe in _manager._frontends.values():
+                try:
+                    fe.add_extension(ext)
+                except RuntimeError:
+                    pass        # a frontend without an operation table, or another framework's operation
         self._extensions.append(ext)
+
+    def register_plugins(self, xml_config_file: str) -> None:
+        """Devices from a plugins file: ``<ie><plugins><plugin name="X" location="module:attr">`` with optional
+        ``<properties><property key= value=/>``."""
+        import xml.etree.ElementTree as ET
+        root = ET.parse(xml_config_file).getroot()
+        for pl in root.iter("plugin"):
+            cfg = {p.get("key"): p.get("value") for p in pl.iter("property")}
+            self.register_plugin(pl.get("location"), pl.get("name"), cfg)
 
     # ---- compile
     def _cache_dir(self, plugin: Plugin, cfg: dict) -> str:
