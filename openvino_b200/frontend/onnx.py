@@ -617,7 +617,7 @@ def convert(path_or_bytes) -> Model:
         params.append(p)
         values[name] = p.output(0)
     for n in nodes:
-        if n.domain not in ("", "ai.onnx"):
+        if n.domain not in ("", "ai.onnx", "com.microsoft"):
             raise OnnxError("operator %s of domain '%s' is not supported" % (n.op_type, n.domain))
         fn = _T.get(n.op_type)
         if fn is None:
@@ -626,9 +626,9 @@ def convert(path_or_bytes) -> Model:
         while ins and ins[-1] is None:
             ins.pop()
         out = fn(n, ins)
-        outs = out if isinstance(out, tuple) else (out,)
+        outs = tuple(out) if isinstance(out, (tuple, list)) else (out,)
         for k, (oname, o) in enumerate(zip(n.outputs, outs)):
-            if not oname:
+            if not oname or o is None:        # an optional output nobody reads, or one the translator does not produce
                 continue
             o = as_output(o)
             values[oname] = o
@@ -641,3 +641,6 @@ def convert(path_or_bytes) -> Model:
             raise OnnxError("graph output '%s' is not produced by any node" % name)
         results.append(result(values[name], name))
     return Model(results, params, gname)
+
+
+from . import onnx_more   # noqa: E402,F401  (second part of the translator table)

@@ -1,0 +1,159 @@
+"""Second part of the ONNX translator table (frontend/onnx_more.py) on models written by the test-side encoder of
+tests/test_frontend_onnx.py, against NumPy / PyTorch."""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import openvino_b200 as ov   # noqa: E402
+from openvino_b200.frontend import onnx as fe   # noqa: E402
+import test_frontend_onnx as W   # noqa: E402
+from test_frontend_onnx import model, node   # noqa: E402
+
+_ELEM = {np.dtype("float32"): 1, np.dtype("uint8"): 2, np.dtype("int8"): 3, np.dtype("int32"): 6, np.dtype("int64"): 7, np.dtype("bool"): 9}
+
+
+def _tensor(name, arr):
+    arr = np.ascontiguousarray(arr)
+    return b"".join(W._int(1, d) for d in arr.shape) + W._int(2, _ELEM[arr.dtype]) + W._ld(8, name.encode()) + W._ld(9, arr.tobytes())
+
+
+W.tensor = _tensor            # the encoder's initialisers may now be 8-bit as well
+
+
+def run(nodes, inits, inputs, outputs, feeds):
+    data = model(nodes, inits, inputs, outputs)
+    m = fe.convert(data)
+    res = ov.compile_model(m, "CPU")(feeds)
+    return [res[i] for i in range(len(outputs))]
+
+
+def test_activations_indexing_and_reductions():
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    nodes = [node("Selu", ["x"], ["a"]), node("HardSigmoid", ["a"], ["b"], alpha=0.25, beta=0.4), node("Celu", ["b"], ["c"], alpha=1.5),
+             node("ReduceLogSumExp", ["c"], ["d"], axes=[2], keepdims=1), node("Trilu", ["x", "k"], ["t"], upper=0),
+             node("ReduceSumSquare", ["t"], ["e"], axes=[1, 2], keepdims=0), node("Hardmax", ["x"], ["hm"], axis=-1),
+             node("Reciprocal", ["d"], ["rec"]), node("Round", ["x"], ["rnd"]), node("Size", ["x"], ["sz"])]
+    d, e, hm, rec, rnd, sz = run(nodes, {"k": np.array(1, np.int64)}, [("x", 1, [3, 4, 5])],
+                                 [("d", 1, [3, 4, 1]), ("e", 1, [3]), ("hm", 1, [3, 4, 5]), ("rec", 1, [3, 4, 1]), ("rnd", 1, [3, 4, 5]), ("sz", 7, [])], [x])
+    t = torch.tensor(x)
+    c = torch.nn.functional.celu(torch.clamp(0.25 * torch.selu(t) + 0.4, 0, 1), alpha=1.5)
+    np.testing.assert_allclose(d, torch.logsumexp(c, 2, keepdim=True).numpy(), rtol=1e-5)
+    np.testing.assert_allclose(e, (torch.tril(t, 1) ** 2).sum((1, 2)).numpy(), rtol=1e-5)
+    np.testing.assert_array_equal(hm, torch.nn.functional.one_hot(t.argmax(-1), 5).float().numpy())
+    np.testing.assert_allclose(rec, 1 / d, rtol=1e-6)
+    np.testing.assert_array_equal(rnd, np.round(x))
+    assert int(sz) == 60
+    # OneHot / GatherND / ScatterND(add) / Compress
+    idx = np.array([[0, 2], [3, 1]], np.int64)
+    data = rng.standard_normal((4, 3, 2)).astype(np.float32)
+    nodes = [node("OneHot", ["idx", "depth", "vals"], ["oh"], axis=-1), node("GatherND", ["data", "gidx"], ["g"]),
+             node("ScatterND", ["data", "sidx", "upd"], ["s"], reduction=b"add"), node("Compress", ["data", "cond"], ["cp"], axis=0)]
+    inits = {"depth": np.array(4, np.int64), "vals": np.array([-1.0, 2.0], np.float32), "gidx": np.array([[1, 2], [3, 0]], np.int64),
+             "sidx": np.array([[0], [0]], np.int64), "upd": np.ones((2, 3, 2), np.float32), "cond": np.array([True, False, False, True])}
+    oh, g, s, cp = run(nodes, inits, [("idx", 7, [2, 2]), ("data", 1, [4, 3, 2])], [("oh", 1, [2, 2, 4]), ("g", 1, [2, 2]), ("s", 1, [4, 3, 2]), ("cp", 1, [2, 3, 2])], [idx, data])
+    np.testing.assert_array_equal(oh, np.where(np.eye(4)[idx] > 0, 2.0, -1.0))
+    np.testing.assert_array_equal(g, np.stack([data[1, 2], data[3, 0]]))
+    ref = data.copy()
+    ref[0] += 2
+    np.testing.assert_allclose(s, ref, rtol=1e-6)
+    np.testing.assert_array_equal(cp, data[[0, 3]])
+
+
+def test_quantisation_family():
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((4, 6)).astype(np.float32) * 3
+    nodes = [node("QuantizeLinear", ["x", "s", "z"], ["q"]), node("DequantizeLinear", ["q", "s", "z"], ["dq"]),
+             node("DynamicQuantizeLinear", ["x"], ["y", "ys", "yz"]),
+             node("DequantizeLinear", ["w", "ws"], ["wd"], axis=0), node("MatMulInteger", ["q", "wq", "z", "wz"], ["mi"])]
+    w = rng.integers(-100, 100, (3, 6)).astype(np.int8)
+    wq = rng.integers(0, 255, (6, 2)).astype(np.uint8)
+    inits = {"s": np.array(0.05, np.float32), "z": np.array(120, np.uint8), "w": w, "ws": np.array([0.1, 0.2, 0.3], np.float32), "wq": wq, "wz": np.array(7, np.uint8)}
+    q, dq, y, ys, yz, wd, mi = run(nodes, inits, [("x", 1, [4, 6])], [("q", 2, [4, 6]), ("dq", 1, [4, 6]), ("y", 2, [4, 6]), ("ys", 1, []), ("yz", 2, []), ("wd", 1, [3, 6]), ("mi", 6, [4, 2])], [x])
+    qr = np.clip(np.round(x / 0.05) + 120, 0, 255)
+    np.testing.assert_array_equal(q, qr.astype(np.uint8))
+    np.testing.assert_allclose(dq, (qr - 120) * 0.05, rtol=1e-6)
+    scale = (max(x.max(), 0) - min(x.min(), 0)) / 255
+    zp = np.clip(np.round(-min(x.min(), 0) / scale), 0, 255)
+    np.testing.assert_allclose(ys, scale, rtol=1e-6)
+    assert int(yz) == int(zp)
+    np.testing.assert_array_equal(y, np.clip(np.round(x / scale) + zp, 0, 255).astype(np.uint8))
+    np.testing.assert_allclose(wd, w.astype(np.float32) * np.array([[0.1], [0.2], [0.3]], np.float32), rtol=1e-6)
+    np.testing.assert_array_equal(mi, (qr.astype(np.int32) - 120) @ (wq.astype(np.int32) - 7))
+
+
+def test_conv_transpose_and_lstm():
+    torch.manual_seed(2)
+    x = torch.randn(1, 4, 5, 5)
+    w = torch.randn(4, 3, 3, 3)
+    b = torch.randn(6)
+    wg = torch.randn(4, 3, 3, 3)                         # two groups: [C, O / G, k, k]
+    nodes = [node("ConvTranspose", ["x", "w"], ["y"], strides=[2, 2], pads=[1, 1, 1, 1], output_padding=[1, 1]),
+             node("ConvTranspose", ["x", "wg", "b"], ["yg"], strides=[1, 1], group=2)]
+    y, yg = run(nodes, {"w": w.numpy(), "wg": wg.numpy(), "b": b.numpy()}, [("x", 1, [1, 4, 5, 5])], [("y", 1, [1, 3, 10, 10]), ("yg", 1, [1, 6, 7, 7])], [x.numpy()])
+    np.testing.assert_allclose(y, torch.nn.functional.conv_transpose2d(x, w, stride=2, padding=1, output_padding=1).numpy(), rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(yg, torch.nn.functional.conv_transpose2d(x, wg, b, groups=2).numpy(), rtol=1e-4, atol=1e-4)
+    # LSTM: ONNX gate order i o f c, torch order i f g o
+    S, B, I, H = 5, 2, 3, 4
+    lstm = torch.nn.LSTM(I, H)
+    xs = torch.randn(S, B, I)
+    with torch.no_grad():
+        ref, (hn, cn) = lstm(xs)
+
+    def regate(t):
+        i_, f_, g_, o_ = t.chunk(4, 0)
+        return torch.cat([i_, o_, f_, g_], 0)
+    Wn, Rn = regate(lstm.weight_ih_l0.detach())[None].numpy(), regate(lstm.weight_hh_l0.detach())[None].numpy()
+    Bn = torch.cat([regate(lstm.bias_ih_l0.detach()), regate(lstm.bias_hh_l0.detach())])[None].numpy()
+    nodes = [node("LSTM", ["x", "W", "R", "B"], ["Y", "Yh", "Yc"], hidden_size=H)]
+    Y, Yh, Yc = run(nodes, {"W": Wn, "R": Rn, "B": Bn}, [("x", 1, [S, B, I])], [("Y", 1, [S, 1, B, H]), ("Yh", 1, [1, B, H]), ("Yc", 1, [1, B, H])], [xs.numpy()])
+    np.testing.assert_allclose(Y[:, 0], ref.numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(Yh, hn.numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(Yc, cn.numpy(), rtol=1e-4, atol=1e-5)
+
+
+def test_transformer_contrib_operations():
+    rng = np.random.default_rng(3)
+    B, S, H = 2, 4, 8
+    x, skip = rng.standard_normal((B, S, H)).astype(np.float32), rng.standard_normal((B, S, H)).astype(np.float32)
+    gamma, beta, bias = rng.random(H).astype(np.float32) + 0.5, rng.standard_normal(H).astype(np.float32), rng.standard_normal(H).astype(np.float32)
+    nodes = [node("SkipLayerNormalization", ["x", "skip", "gamma", "beta", "bias"], ["y", "", "", "sum"], epsilon=1e-5),
+             node("BiasGelu", ["y", "bias"], ["bg"]), node("FastGelu", ["y"], ["fg"]), node("SimplifiedLayerNormalization", ["sum", "gamma"], ["rms"], epsilon=1e-6),
+             node("FusedMatMul", ["x", "skip"], ["fm"], transB=1, alpha=0.5)]
+    y, s, bg, fg, rms, fm = run(nodes, {"gamma": gamma, "beta": beta, "bias": bias}, [("x", 1, [B, S, H]), ("skip", 1, [B, S, H])],
+                                [("y", 1, [B, S, H]), ("sum", 1, [B, S, H]), ("bg", 1, [B, S, H]), ("fg", 1, [B, S, H]), ("rms", 1, [B, S, H]), ("fm", 1, [B, S, S])], [x, skip])
+    st = torch.tensor(x + skip + bias)
+    ref = torch.nn.functional.layer_norm(st, [H], torch.tensor(gamma), torch.tensor(beta), 1e-5)
+    np.testing.assert_allclose(s, st.numpy(), rtol=1e-6)
+    np.testing.assert_allclose(y, ref.numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(bg, torch.nn.functional.gelu(ref + torch.tensor(bias)).numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(fg, torch.nn.functional.gelu(ref, approximate="tanh").numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(rms, (st / torch.sqrt((st ** 2).mean(-1, keepdim=True) + 1e-6) * torch.tensor(gamma)).numpy(), rtol=1e-4, atol=1e-5)
+    np.testing.assert_allclose(fm, 0.5 * (x @ skip.transpose(0, 2, 1)), rtol=1e-4, atol=1e-5)
+    # MatMulNBits: 4-bit blocks of 16 along K = 32, N = 5
+    K, N, bs = 32, 5, 16
+    qv = rng.integers(0, 16, (N, K)).astype(np.uint8)
+    scales = (rng.random((N, K // bs)) * 0.1 + 0.01).astype(np.float32)
+    zps = rng.integers(0, 16, (N, K // bs)).astype(np.uint8)
+    packed = (qv[:, 0::2] | (qv[:, 1::2] << 4)).reshape(N, K // bs, bs // 2)
+    zp_packed = (zps[:, 0::2] | (zps[:, 1::2] << 4)).reshape(N, -1)
+    a = rng.standard_normal((3, K)).astype(np.float32)
+    nodes = [node("MatMulNBits", ["a", "Bq", "sc", "zp"], ["y"], K=K, N=N, bits=4, block_size=bs)]
+    got = run(nodes, {"Bq": packed, "sc": scales.reshape(-1), "zp": zp_packed}, [("a", 1, [3, K])], [("y", 1, [3, N])], [a])[0]
+    wd = (qv.astype(np.float32) - np.repeat(zps, bs, 1)) * np.repeat(scales, bs, 1)
+    np.testing.assert_allclose(got, a @ wd.T, rtol=2e-3, atol=2e-3)
+    # RotaryEmbedding, half-rotate, [B, S, heads * D]
+    heads, D = 2, 4
+    xr = rng.standard_normal((B, S, heads * D)).astype(np.float32)
+    pos = np.tile(np.arange(S, dtype=np.int64), (B, 1))
+    ang = np.outer(np.arange(16), 1.0 / (10000 ** (np.arange(0, D, 2) / D))).astype(np.float32)
+    nodes = [node("RotaryEmbedding", ["x", "pos", "cos", "sin"], ["y"], num_heads=heads)]
+    got = run(nodes, {"cos": np.cos(ang), "sin": np.sin(ang)}, [("x", 1, [B, S, heads * D]), ("pos", 7, [B, S])], [("y", 1, [B, S, heads * D])], [xr, pos])[0]
+    x4 = xr.reshape(B, S, heads, D)
+    c, sn = np.cos(ang)[pos][:, :, None], np.sin(ang)[pos][:, :, None]
+    a_, b_ = x4[..., :D // 2], x4[..., D // 2:]
+    ref = np.concatenate([a_ * c - b_ * sn, a_ * sn + b_ * c], -1).reshape(B, S, heads * D)
+    np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
