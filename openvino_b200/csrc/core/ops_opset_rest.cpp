@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cmath>
 #include <limits>
+#include <map>
 
 #include "graph.hpp"
 
@@ -230,9 +231,111 @@ bool eval_to_nv12(N n, Ins in, Outs out, bool bgr) {
     return true;
 }
 
+
+// ---- Einsum: every output element is the sum over the contracted labels of the product of the operands
+bool eval_einsum(N n, Ins in, Outs out, C) {
+    std::string eq = n.attr_str("equation");
+    eq.erase(std::remove(eq.begin(), eq.end(), ' '), eq.end());
+    const size_t arrow = eq.find("->");
+    std::string lhs = arrow == std::string::npos ? eq : eq.substr(0, arrow);
+    std::vector<std::string> terms;
+    for (size_t p = 0;;) {
+        const size_t c = lhs.find(',', p);
+        terms.push_back(lhs.substr(p, c == std::string::npos ? std::string::npos : c - p));
+        if (c == std::string::npos) break;
+        p = c + 1;
+    }
+    OVC_CHECK(terms.size() == in.size(), n.description() << ": the equation names " << terms.size() << " operands, " << in.size() << " are given");
+    // labels: letters, plus one synthetic label per broadcast axis that an ellipsis stands for (aligned from the right)
+    size_t ell_rank = 0;
+    for (size_t t = 0; t < terms.size(); ++t) {
+        const size_t e = terms[t].find("...");
+        if (e != std::string::npos) ell_rank = std::max(ell_rank, in[t].shape.size() - (terms[t].size() - 3));
+    }
+    auto expand = [&](const std::string& term, size_t rank_of_operand, bool is_output) {
+        std::vector<int> labels;
+        const size_t e = term.find("...");
+        for (size_t k = 0; k < term.size(); ++k) {
+            if (e != std::string::npos && k == e) {
+                const size_t here = is_output ? ell_rank : rank_of_operand - (term.size() - 3);
+                for (size_t a = 0; a < here; ++a) labels.push_back(256 + (int)(ell_rank - here + a));
+                k += 2;
+                continue;
+            }
+            labels.push_back((int)(unsigned char)term[k]);
+        }
+        return labels;
+    };
+    std::vector<std::vector<int>> tl;
+    for (size_t t = 0; t < terms.size(); ++t) {
+        tl.push_back(expand(terms[t], in[t].shape.size(), false));
+        OVC_CHECK(tl.back().size() == in[t].shape.size(), n.description() << ": term '" << terms[t] << "' does not match an operand of rank " << in[t].shape.size());
+    }
+    std::map<int, int64_t> extent;
+    for (size_t t = 0; t < tl.size(); ++t)
+        for (size_t a = 0; a < tl[t].size(); ++a) {
+            const int64_t d = in[t].shape[a];
+            auto it = extent.find(tl[t][a]);
+            if (it == extent.end() || it->second == 1) extent[tl[t][a]] = d;
+            else OVC_CHECK(d == 1 || d == it->second, n.description() << ": label extents " << it->second << " and " << d << " do not agree");
+        }
+    std::vector<int> ol;
+    if (arrow != std::string::npos) {
+        ol = expand(eq.substr(arrow + 2), 0, true);
+    } else {                                     // implicit output: ellipsis axes, then the letters that occur once, sorted
+        for (size_t a = 0; a < ell_rank; ++a) ol.push_back(256 + (int)a);
+        std::map<int, int> count;
+        for (auto& t : tl) for (int l : t) if (l < 256) ++count[l];
+        for (auto& kv : count) if (kv.second == 1) ol.push_back(kv.first);
+    }
+    std::vector<int> all = ol;                    // output labels first, then the contracted ones
+    for (auto& kv : extent) if (std::find(all.begin(), all.end(), kv.first) == all.end()) all.push_back(kv.first);
+    std::vector<int64_t> ext;
+    for (int l : all) { OVC_CHECK(extent.count(l), n.description() << ": output label without an operand"); ext.push_back(extent[l]); }
+    Shape os(ext.begin(), ext.begin() + (long)ol.size());
+    int64_t out_total = 1, red_total = 1;
+    for (size_t k = 0; k < all.size(); ++k) (k < ol.size() ? out_total : red_total) *= ext[k];
+    std::vector<std::vector<float>> data;
+    for (auto& t : in) data.push_back(to_f32(t));
+    // stride of every label in every operand (0 where the operand lacks the label or broadcasts it)
+    std::vector<std::vector<int64_t>> stride(in.size(), std::vector<int64_t>(all.size(), 0));
+    for (size_t t = 0; t < in.size(); ++t) {
+        int64_t st = 1;
+        for (size_t a = tl[t].size(); a-- > 0;) {
+            if (in[t].shape[a] != 1) {
+                const size_t pos = std::find(all.begin(), all.end(), tl[t][a]) - all.begin();
+                stride[t][pos] += st;            // a label used twice in one term walks the diagonal
+            }
+            st *= in[t].shape[a];
+        }
+    }
+    std::vector<float> o((size_t)out_total);
+    std::vector<int64_t> idx(all.size(), 0);
+    for (int64_t oi = 0; oi < out_total; ++oi) {
+        int64_t rem = oi;
+        for (size_t k = ol.size(); k-- > 0;) { idx[k] = rem % ext[k]; rem /= ext[k]; }
+        double acc = 0;
+        for (int64_t ri = 0; ri < red_total; ++ri) {
+            int64_t r2 = ri;
+            for (size_t k = all.size(); k-- > ol.size();) { idx[k] = r2 % ext[k]; r2 /= ext[k]; }
+            double prod = 1;
+            for (size_t t = 0; t < in.size(); ++t) {
+                int64_t off = 0;
+                for (size_t k = 0; k < all.size(); ++k) off += idx[k] * stride[t][k];
+                prod *= data[t][(size_t)off];
+            }
+            acc += prod;
+        }
+        o[(size_t)oi] = (float)acc;
+    }
+    out[0] = from_f32(in[0].et, os, o);
+    return true;
+}
+
 }  // namespace
 
 void register_rest_ops() {
+    if (auto* es = const_cast<OpSchema*>(OpRegistry::get().find("Einsum", "opset7")); es && !es->eval) es->eval = eval_einsum;
     // ---- DeformableConvolution: every kernel tap reads the input at its own learned offset
     const std::vector<AttrSpec> dc1 = {Ais("strides"), Ais("dilations"), Ais("pads_begin"), Ais("pads_end"), As("auto_pad", "explicit"), Ai("group", 1), Ai("deformable_group", 1)};
     std::vector<AttrSpec> dc8 = {Ab("bilinear_interpolation_pad")};

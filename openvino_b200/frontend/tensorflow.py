@@ -402,3 +402,6 @@ def convert(path_or_bytes) -> Model:
     if not results:
         raise TensorFlowError("the graph has no output node")
     return Model(results, params, "tf_model")
+
+
+from . import tensorflow_more   # noqa: E402,F401  (second part of the translator table)

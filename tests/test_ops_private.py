@@ -126,3 +126,16 @@ def test_static_shape_suppression_forms_pad_the_dynamic_ones():
     np.testing.assert_allclose(s_sel[:k], d_sel, rtol=1e-6)
     np.testing.assert_array_equal(s_i[:k], d_i)
     assert (s_sel[k:] == -1).all() and int(s_n[0]) == k
+
+
+def test_einsum_reference_evaluation():
+    rng = np.random.default_rng(7)
+    a, b, c = rng.standard_normal((2, 3, 4)).astype(np.float32), rng.standard_normal((2, 4, 5)).astype(np.float32), rng.standard_normal((5,)).astype(np.float32)
+    pa, pb, pc = P(a.shape, "a"), P(b.shape, "b"), P(c.shape, "c")
+    for eq, ins, feeds in (("bij,bjk->bik", [pa, pb], [a, b]), ("...ij,...jk,k->...i", [pa, pb, pc], [a, b, c]), ("bij->jb", [pa], [a]), ("bij,bjk", [pa, pb], [a, b])):
+        n = ops.einsum(ins, eq)
+        got = run([n], ins, feeds)[0]
+        np.testing.assert_allclose(got, np.einsum(eq, *feeds), rtol=1e-4, atol=1e-5)
+    sq = rng.standard_normal((4, 4)).astype(np.float32)
+    ps = P(sq.shape, "s")
+    np.testing.assert_allclose(run([ops.einsum([ps], "ii->i")], [ps], [sq])[0], np.diag(sq), rtol=1e-6)
