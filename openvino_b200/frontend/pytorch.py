@@ -946,10 +946,62 @@ def _python_scalar_op(name, args):
     return fn(*args)
 
 
+def _untranslated(ep) -> list:
+    missing = []
+    for node in ep.graph.nodes:
+        if node.op != "call_function":
+            continue
+        name = _target_name(node.target)
+        if name.startswith("aten.") is False and not isinstance(node.target, str) and hasattr(node.target, "_schema"):
+            name = str(node.target)
+        if name not in _TABLE and node.target not in missing:
+            missing.append(node.target)
+    return missing
+
+
+def _decompose_untranslated(ep, rounds: int = 3):
+    import torch
+    try:
+        from torch._decomp import decomposition_table
+    except ImportError:
+        return ep
+    for _ in range(rounds):
+        missing = [t for t in _untranslated(ep) if hasattr(t, "_schema")]
+        table = {t: decomposition_table[t] for t in missing if t in decomposition_table}
+        if not table:
+            break
+        try:
+            ep = ep.run_decompositions(table)
+        except Exception:   # noqa: BLE001 - one of the decompositions does not apply here: take them one at a time
+            progressed = False
+            for t, fn in table.items():
+                try:
+                    ep = ep.run_decompositions({t: fn})
+                    progressed = True
+                except Exception:   # noqa: BLE001 - the conversion below then names the operation that has no translator
+                    pass
+            if not progressed:
+                break
+    left = _untranslated(ep)
+    if left:
+        # composite operations (var.dim, std.dim, ...) have no table entry of their own: the default decomposition to the
+        # core ATen set resolves them
+        try:
+            full = ep.run_decompositions()
+            if len(_untranslated(full)) < len(left):
+                ep = full
+        except Exception:   # noqa: BLE001
+            pass
+    return ep
+
+
 def from_exported_program(ep, share_weights: bool = True, input_names: Optional[Sequence[str]] = None) -> Model:
-    """``torch.export.ExportedProgram`` -> ``Model``."""
+    """``torch.export.ExportedProgram`` -> ``Model``. Operations without a translator are first rewritten by their ATen
+    decompositions (``ExportedProgram.run_decompositions`` with a table of just those operations), so the table above only
+    has to cover what the decompositions bottom out in."""
     import torch
     from torch.export.graph_signature import InputKind
+    ep = _decompose_untranslated(ep)
     ctx = Ctx()
     sig = ep.graph_signature
     spec_by_name = {s.arg.name: s for s in sig.input_specs if hasattr(s.arg, "name")}
@@ -1238,3 +1290,6 @@ def restore_module_extensions(undo) -> None:
 
 
 from .input_model import ConversionExtension   # noqa: E402,F401  (the PyTorch table takes (ctx, node) translators)
+
+
+from . import pytorch_more   # noqa: E402,F401  (second part of the translator table)
