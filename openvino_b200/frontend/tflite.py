@@ -382,3 +382,6 @@ def load(path_or_bytes) -> Model:
         o.set_names({g.tensor_name(int(i))})
         results.append(result(o))
     return Model(results, params, sub.string(4) or "tflite_model")
+
+
+from . import tflite_more   # noqa: E402,F401  (second part of the translator table)
