@@ -460,3 +460,6 @@ def load(model_path: str, params_path: Optional[str] = None) -> Model:
     if not results:
         raise PaddleError("the program has no fetch operator")
     return Model([results[k] for k in sorted(results)], [params[k] for k in sorted(params)], os.path.splitext(os.path.basename(model_path))[0])
+
+
+from . import paddle_more   # noqa: E402,F401  (second part of the translator table)
