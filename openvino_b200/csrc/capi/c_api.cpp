@@ -40,11 +40,36 @@ struct ov_infer_request {
     int threads = 0;
     bool started = false;
 };
+struct ov_layout { std::string desc; };
+// One step of an input's pre-processing, in the order the user asked for them
+struct PpStep {
+    enum Kind { RESIZE, SCALE, MEAN, CROP, CONVERT_LAYOUT, REVERSE_CHANNELS, CONVERT_ELEMENT_TYPE, CONVERT_COLOR, PAD } kind;
+    std::vector<float> values;
+    std::vector<int64_t> a, b;
+    std::string text;
+    int code = 0;
+    float fill = 0;
+};
+struct PpInput {
+    ET tensor_et = ET::dynamic;
+    std::string tensor_layout, model_layout;
+    int color = 0;                  // ov_color_format_e
+    int64_t height = -1, width = -1;
+    std::vector<PpStep> steps;
+};
 struct ov_preprocess_prepostprocessor {
     ModelPtr m;
     struct In { ET et = ET::dynamic; std::vector<float> mean, scale; int64_t axis = 1; bool nhwc = false; };
     std::map<size_t, In> ins;
+    std::map<size_t, std::shared_ptr<PpInput>> inputs;      // the object-by-object interface of the reference
+    std::map<size_t, ET> output_types;
 };
+struct ov_preprocess_input_info { std::shared_ptr<PpInput> in; };
+struct ov_preprocess_input_tensor_info { std::shared_ptr<PpInput> in; };
+struct ov_preprocess_preprocess_steps { std::shared_ptr<PpInput> in; };
+struct ov_preprocess_input_model_info { std::shared_ptr<PpInput> in; };
+struct ov_preprocess_output_info { ov_preprocess_prepostprocessor* pp; size_t index; };
+struct ov_preprocess_output_tensor_info { ov_preprocess_prepostprocessor* pp; size_t index; };
 
 namespace {
 
@@ -104,6 +129,134 @@ bool resolves_to_cpu(const std::string& device) {
         start = comma + 1;
     }
     return true;
+}
+
+// Position of an axis letter in a layout string ("NCHW" -> C at 1); -1 when absent
+int64_t layout_axis(const std::string& layout, char c) {
+    const size_t p = layout.find(c);
+    return p == std::string::npos ? -1 : (int64_t)p;
+}
+
+// Rebuild input `index` of `m` as: new Parameter (tensor type / layout / colour / spatial shape) -> the user's steps in
+// order -> conversion to the model's layout and element type. Mirrors what the reference's PrePostProcessor::build adds.
+void apply_input_preprocessing(const ModelPtr& m, size_t index, const PpInput& cfg) {
+    NodePtr old = m->params[index];
+    const ET model_et = old->outs[0].et;
+    const PShape model_shape = old->outs[0].shape;
+    OVC_CHECK(model_shape.rank_is_static(), "pre-processing needs an input of known rank");
+    const size_t rank = model_shape.rank();
+    std::string model_layout = cfg.model_layout, cur_layout = cfg.tensor_layout.empty() ? cfg.model_layout : cfg.tensor_layout;
+    // tensor shape: the model's dims permuted into the tensor's layout, spatial extents replaced when given
+    PShape tshape = model_shape;
+    if (!cur_layout.empty() && !model_layout.empty() && cur_layout != model_layout) {
+        OVC_CHECK(cur_layout.size() == rank && model_layout.size() == rank, "layouts must name every axis of the input");
+        for (size_t i = 0; i < rank; ++i) {
+            const int64_t src = layout_axis(model_layout, cur_layout[i]);
+            OVC_CHECK(src >= 0, "tensor layout " << cur_layout << " and model layout " << model_layout << " name different axes");
+            tshape.dims[i] = model_shape.dims[(size_t)src];
+        }
+    }
+    const int64_t hp = layout_axis(cur_layout, 'H'), wp = layout_axis(cur_layout, 'W'), cp = layout_axis(cur_layout, 'C');
+    if (cfg.height >= 0 && hp >= 0) tshape.dims[(size_t)hp] = Dim(cfg.height);
+    if (cfg.width >= 0 && wp >= 0) tshape.dims[(size_t)wp] = Dim(cfg.width);
+    const bool yuv = cfg.color == NV12_SINGLE_PLANE || cfg.color == I420_SINGLE_PLANE;
+    if (yuv) {
+        OVC_CHECK(hp >= 0 && cp >= 0, "a YUV input needs a tensor layout with H and C");
+        if (tshape.dims[(size_t)hp].is_static()) tshape.dims[(size_t)hp] = Dim(tshape.dims[(size_t)hp].lo * 3 / 2);
+        tshape.dims[(size_t)cp] = Dim(1);
+    }
+    NodePtr np = make_parameter(cfg.tensor_et == ET::dynamic ? model_et : cfg.tensor_et, tshape, old->name);
+    np->outs[0].names = old->outs[0].names;
+    Output cur = np->output(0);
+    int color = cfg.color;
+    auto to_float_first = [&] {
+        if (!et_is_real(cur.et())) cur = make_node("Convert", "opset1", {cur}, {{"destination_type", Attr::Type(et_is_real(model_et) ? model_et : ET::f32)}})->output(0);
+    };
+    auto per_channel = [&](const std::vector<float>& v) {
+        if (v.size() == 1) return make_constant_f32(v, Shape{}, cur.et())->output(0);
+        const int64_t c = layout_axis(cur_layout, 'C');
+        OVC_CHECK(c >= 0, "per-channel values need a layout with a C axis");
+        Shape s(rank, 1);
+        s[(size_t)c] = (int64_t)v.size();
+        return make_constant_f32(v, s, cur.et())->output(0);
+    };
+    for (const PpStep& st : cfg.steps) {
+        switch (st.kind) {
+            case PpStep::CONVERT_ELEMENT_TYPE:
+                cur = make_node("Convert", "opset1", {cur}, {{"destination_type", Attr::Type(static_cast<ET>(st.code))}})->output(0);
+                break;
+            case PpStep::CONVERT_COLOR: {
+                const bool to_bgr = st.code == BGR;
+                OVC_CHECK(st.code == RGB || st.code == BGR, "colour conversion targets RGB or BGR");
+                if (color == NV12_SINGLE_PLANE) cur = make_node(to_bgr ? "NV12toBGR" : "NV12toRGB", "opset8", {cur})->output(0);
+                else if (color == I420_SINGLE_PLANE) cur = make_node(to_bgr ? "I420toBGR" : "I420toRGB", "opset8", {cur})->output(0);
+                else if ((color == RGB && to_bgr) || (color == BGR && !to_bgr)) {
+                    const int64_t c = layout_axis(cur_layout, 'C');
+                    OVC_CHECK(c >= 0, "RGB <-> BGR needs a layout with a C axis");
+                    cur = make_node("Gather", "opset8", {cur, make_constant_i64({2, 1, 0})->output(0), make_constant_i64({c}, ET::i64, true)->output(0)})->output(0);
+                } else OVC_CHECK(color == st.code, "this colour conversion is not available");
+                color = st.code;
+                break;
+            }
+            case PpStep::RESIZE: {
+                const int64_t h = layout_axis(cur_layout, 'H'), w = layout_axis(cur_layout, 'W');
+                OVC_CHECK(h >= 0 && w >= 0 && !model_layout.empty(), "resize needs tensor and model layouts with H and W");
+                const Dim mh = model_shape.dims[(size_t)layout_axis(model_layout, 'H')], mw = model_shape.dims[(size_t)layout_axis(model_layout, 'W')];
+                OVC_CHECK(mh.is_static() && mw.is_static(), "resize needs static spatial extents of the model input");
+                to_float_first();
+                const char* mode = st.code == RESIZE_LINEAR ? "linear" : (st.code == RESIZE_CUBIC ? "cubic" : "nearest");
+                cur = make_node("Interpolate", "opset11", {cur, make_constant_i64({mh.lo, mw.lo})->output(0), make_constant_i64({h, w})->output(0)},
+                                {{"mode", Attr::Str(mode)}, {"shape_calculation_mode", Attr::Str("sizes")},
+                                 {"coordinate_transformation_mode", Attr::Str(st.code == RESIZE_NEAREST ? "asymmetric" : "half_pixel")},
+                                 {"nearest_mode", Attr::Str("floor")}})->output(0);
+                break;
+            }
+            case PpStep::CONVERT_LAYOUT: {
+                OVC_CHECK(st.text.size() == rank && cur_layout.size() == rank, "convert_layout needs layouts that name every axis");
+                std::vector<int64_t> order;
+                for (char c : st.text) { const int64_t a = layout_axis(cur_layout, c); OVC_CHECK(a >= 0, "layout " << st.text << " names an axis the tensor lacks"); order.push_back(a); }
+                cur = make_node("Transpose", "opset1", {cur, make_constant_i64(order)->output(0)})->output(0);
+                cur_layout = st.text;
+                break;
+            }
+            case PpStep::MEAN:
+                to_float_first();
+                cur = make_node("Subtract", "opset1", {cur, per_channel(st.values)})->output(0);
+                break;
+            case PpStep::SCALE:
+                to_float_first();
+                cur = make_node("Divide", "opset1", {cur, per_channel(st.values)})->output(0);
+                break;
+            case PpStep::REVERSE_CHANNELS: {
+                const int64_t c = layout_axis(cur_layout, 'C');
+                OVC_CHECK(c >= 0 && cur.shape().dims[(size_t)c].is_static(), "reverse_channels needs a static C axis");
+                std::vector<int64_t> idx;
+                for (int64_t k = cur.shape().dims[(size_t)c].lo; k-- > 0;) idx.push_back(k);
+                cur = make_node("Gather", "opset8", {cur, make_constant_i64(idx)->output(0), make_constant_i64({c}, ET::i64, true)->output(0)})->output(0);
+                break;
+            }
+            case PpStep::CROP: {
+                std::vector<int64_t> step(st.a.size(), 1);
+                cur = make_node("Slice", "opset8", {cur, make_constant_i64(st.a)->output(0), make_constant_i64(st.b)->output(0), make_constant_i64(step)->output(0)})->output(0);
+                break;
+            }
+            case PpStep::PAD: {
+                static const char* modes[] = {"constant", "edge", "reflect", "symmetric"};
+                cur = make_node("Pad", "opset12", {cur, make_constant_i64(st.a)->output(0), make_constant_i64(st.b)->output(0), make_constant_f32({st.fill}, Shape{}, cur.et())->output(0)},
+                                {{"pad_mode", Attr::Str(modes[st.code & 3])}})->output(0);
+                break;
+            }
+        }
+    }
+    // what is left to reach the model's own input: layout, then element type
+    if (!model_layout.empty() && !cur_layout.empty() && cur_layout != model_layout) {
+        std::vector<int64_t> order;
+        for (char c : model_layout) order.push_back(layout_axis(cur_layout, c));
+        cur = make_node("Transpose", "opset1", {cur, make_constant_i64(order)->output(0)})->output(0);
+    }
+    if (cur.et() != model_et) cur = make_node("Convert", "opset1", {cur}, {{"destination_type", Attr::Type(model_et)}})->output(0);
+    replace_output(old->output(0), cur);
+    m->params[index] = np;
 }
 
 std::string port_name(const Output& o) {
@@ -989,10 +1142,327 @@ ov_status_e ov_preprocess_prepostprocessor_build(const ov_preprocess_prepostproc
             replace_output(old->output(0), cur);
             m->params[kv.first] = np;
         }
+        for (auto& kv : pp->inputs) {
+            if (kv.first >= m->params.size()) { g_last_error = "no such input"; return NOT_FOUND; }
+            apply_input_preprocessing(m, kv.first, *kv.second);
+        }
+        for (auto& kv : pp->output_types) {
+            if (kv.first >= m->results.size()) { g_last_error = "no such output"; return NOT_FOUND; }
+            NodePtr r = m->results[kv.first];
+            Output src = r->input(0);
+            if (src.et() != kv.second) r->set_input(0, make_node("Convert", "opset1", {src}, {{"destination_type", Attr::Type(kv.second)}})->output(0));
+        }
         m->validate();
         *model = new ov_model{m};
         return OK;
     });
 }
+
+// ---- object-by-object interface: prepostprocessor -> input info -> tensor info / steps / model info; output info
+static std::shared_ptr<PpInput> pp_input(const ov_preprocess_prepostprocessor_t* pp, size_t idx) {
+    auto* p = const_cast<ov_preprocess_prepostprocessor_t*>(pp);
+    auto& slot = p->inputs[idx];
+    if (!slot) slot = std::make_shared<PpInput>();
+    return slot;
+}
+ov_status_e ov_preprocess_prepostprocessor_get_input_info_by_index(const ov_preprocess_prepostprocessor_t* pp, const size_t idx, ov_preprocess_input_info_t** info) {
+    REQUIRE_PTR(pp, info);
+    if (idx >= pp->m->params.size()) { g_last_error = "no such input"; return NOT_FOUND; }
+    *info = new ov_preprocess_input_info{pp_input(pp, idx)};
+    return OK;
+}
+ov_status_e ov_preprocess_prepostprocessor_get_input_info(const ov_preprocess_prepostprocessor_t* pp, ov_preprocess_input_info_t** info) {
+    REQUIRE_PTR(pp, info);
+    if (pp->m->params.size() != 1) { g_last_error = "the model has more than one input: name it or give its index"; return PARAMETER_MISMATCH; }
+    return ov_preprocess_prepostprocessor_get_input_info_by_index(pp, 0, info);
+}
+ov_status_e ov_preprocess_prepostprocessor_get_input_info_by_name(const ov_preprocess_prepostprocessor_t* pp, const char* name, ov_preprocess_input_info_t** info) {
+    REQUIRE_PTR(pp, name, info);
+    const int k = find_port(pp->m->params, name);
+    if (k < 0) { g_last_error = std::string("no input named ") + name; return NOT_FOUND; }
+    return ov_preprocess_prepostprocessor_get_input_info_by_index(pp, (size_t)k, info);
+}
+void ov_preprocess_input_info_free(ov_preprocess_input_info_t* p) { delete p; }
+ov_status_e ov_preprocess_input_info_get_tensor_info(const ov_preprocess_input_info_t* info, ov_preprocess_input_tensor_info_t** t) {
+    REQUIRE_PTR(info, t);
+    *t = new ov_preprocess_input_tensor_info{info->in};
+    return OK;
+}
+void ov_preprocess_input_tensor_info_free(ov_preprocess_input_tensor_info_t* p) { delete p; }
+ov_status_e ov_preprocess_input_info_get_preprocess_steps(const ov_preprocess_input_info_t* info, ov_preprocess_preprocess_steps_t** steps) {
+    REQUIRE_PTR(info, steps);
+    *steps = new ov_preprocess_preprocess_steps{info->in};
+    return OK;
+}
+void ov_preprocess_preprocess_steps_free(ov_preprocess_preprocess_steps_t* p) { delete p; }
+ov_status_e ov_preprocess_input_info_get_model_info(const ov_preprocess_input_info_t* info, ov_preprocess_input_model_info_t** mi) {
+    REQUIRE_PTR(info, mi);
+    *mi = new ov_preprocess_input_model_info{info->in};
+    return OK;
+}
+void ov_preprocess_input_model_info_free(ov_preprocess_input_model_info_t* p) { delete p; }
+ov_status_e ov_preprocess_input_model_info_set_layout(ov_preprocess_input_model_info_t* mi, ov_layout_t* layout) {
+    REQUIRE_PTR(mi, layout);
+    mi->in->model_layout = layout->desc;
+    return OK;
+}
+ov_status_e ov_preprocess_input_tensor_info_set_element_type(ov_preprocess_input_tensor_info_t* t, const ov_element_type_e type) {
+    REQUIRE_PTR(t);
+    t->in->tensor_et = static_cast<ET>(type);
+    return OK;
+}
+ov_status_e ov_preprocess_input_tensor_info_set_layout(ov_preprocess_input_tensor_info_t* t, ov_layout_t* layout) {
+    REQUIRE_PTR(t, layout);
+    t->in->tensor_layout = layout->desc;
+    return OK;
+}
+ov_status_e ov_preprocess_input_tensor_info_set_color_format(ov_preprocess_input_tensor_info_t* t, const ov_color_format_e fmt) {
+    REQUIRE_PTR(t);
+    if (fmt == NV12_TWO_PLANES || fmt == I420_THREE_PLANES) { g_last_error = "multi-plane colour formats are served through the single-plane forms here"; return NOT_IMPLEMENTED; }
+    t->in->color = (int)fmt;
+    return OK;
+}
+ov_status_e ov_preprocess_input_tensor_info_set_color_format_with_subname(ov_preprocess_input_tensor_info_t* t, const ov_color_format_e fmt, const size_t, ...) {
+    return ov_preprocess_input_tensor_info_set_color_format(t, fmt);
+}
+ov_status_e ov_preprocess_input_tensor_info_set_spatial_static_shape(ov_preprocess_input_tensor_info_t* t, const size_t h, const size_t w) {
+    REQUIRE_PTR(t);
+    t->in->height = (int64_t)h;
+    t->in->width = (int64_t)w;
+    return OK;
+}
+ov_status_e ov_preprocess_input_tensor_info_set_memory_type(ov_preprocess_input_tensor_info_t* t, const char* mem_type) {
+    REQUIRE_PTR(t, mem_type);
+    return OK;             // host memory is the only kind of this library
+}
+ov_status_e ov_preprocess_input_tensor_info_set_from(ov_preprocess_input_tensor_info_t* t, const ov_tensor_t* tensor) {
+    REQUIRE_PTR(t, tensor);
+    t->in->tensor_et = tensor->t.et;
+    // spatial extents follow the tensor's layout when one is set ('H' and 'W' positions), else NHWC is assumed for rank 4
+    const Shape& s = tensor->t.shape;
+    const std::string& lay = t->in->tensor_layout;
+    const size_t hp = lay.find('H'), wp = lay.find('W');
+    if (hp != std::string::npos && wp != std::string::npos && hp < s.size() && wp < s.size()) { t->in->height = s[hp]; t->in->width = s[wp]; }
+    else if (s.size() == 4) { t->in->height = s[1]; t->in->width = s[2]; }
+    return OK;
+}
+static ov_status_e add_step(ov_preprocess_preprocess_steps_t* st, PpStep step) {
+    if (!st) { g_last_error = "null argument"; return INVALID_C_PARAM; }
+    st->in->steps.push_back(std::move(step));
+    return OK;
+}
+ov_status_e ov_preprocess_preprocess_steps_resize(ov_preprocess_preprocess_steps_t* st, const ov_preprocess_resize_algorithm_e alg) {
+    PpStep s{PpStep::RESIZE};
+    s.code = (int)alg;
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_scale(ov_preprocess_preprocess_steps_t* st, float v) { PpStep s{PpStep::SCALE}; s.values = {v}; return add_step(st, s); }
+ov_status_e ov_preprocess_preprocess_steps_scale_multi_channels(ov_preprocess_preprocess_steps_t* st, const float* v, const int32_t n) {
+    REQUIRE_PTR(v);
+    PpStep s{PpStep::SCALE};
+    s.values.assign(v, v + n);
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_mean(ov_preprocess_preprocess_steps_t* st, float v) { PpStep s{PpStep::MEAN}; s.values = {v}; return add_step(st, s); }
+ov_status_e ov_preprocess_preprocess_steps_mean_multi_channels(ov_preprocess_preprocess_steps_t* st, const float* v, const int32_t n) {
+    REQUIRE_PTR(v);
+    PpStep s{PpStep::MEAN};
+    s.values.assign(v, v + n);
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_crop(ov_preprocess_preprocess_steps_t* st, int32_t* begin, int32_t bn, int32_t* end, int32_t en) {
+    REQUIRE_PTR(begin, end);
+    PpStep s{PpStep::CROP};
+    s.a.assign(begin, begin + bn);
+    s.b.assign(end, end + en);
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_convert_layout(ov_preprocess_preprocess_steps_t* st, ov_layout_t* layout) {
+    REQUIRE_PTR(layout);
+    PpStep s{PpStep::CONVERT_LAYOUT};
+    s.text = layout->desc;
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_reverse_channels(ov_preprocess_preprocess_steps_t* st) { return add_step(st, PpStep{PpStep::REVERSE_CHANNELS}); }
+ov_status_e ov_preprocess_preprocess_steps_convert_element_type(ov_preprocess_preprocess_steps_t* st, const ov_element_type_e type) {
+    PpStep s{PpStep::CONVERT_ELEMENT_TYPE};
+    s.code = (int)type;
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_convert_color(ov_preprocess_preprocess_steps_t* st, const ov_color_format_e fmt) {
+    PpStep s{PpStep::CONVERT_COLOR};
+    s.code = (int)fmt;
+    return add_step(st, s);
+}
+ov_status_e ov_preprocess_preprocess_steps_pad(const ov_preprocess_preprocess_steps_t* st, const int* const pb, size_t pbn, const int* const pe, size_t pen, float value,
+                                               ov_padding_mode_e mode) {
+    REQUIRE_PTR(pb, pe);
+    PpStep s{PpStep::PAD};
+    s.a.assign(pb, pb + pbn);
+    s.b.assign(pe, pe + pen);
+    s.fill = value;
+    s.code = (int)mode;
+    return add_step(const_cast<ov_preprocess_preprocess_steps_t*>(st), s);
+}
+ov_status_e ov_preprocess_prepostprocessor_get_output_info_by_index(const ov_preprocess_prepostprocessor_t* pp, const size_t idx, ov_preprocess_output_info_t** info) {
+    REQUIRE_PTR(pp, info);
+    if (idx >= pp->m->results.size()) { g_last_error = "no such output"; return NOT_FOUND; }
+    *info = new ov_preprocess_output_info{const_cast<ov_preprocess_prepostprocessor_t*>(pp), idx};
+    return OK;
+}
+ov_status_e ov_preprocess_prepostprocessor_get_output_info(const ov_preprocess_prepostprocessor_t* pp, ov_preprocess_output_info_t** info) {
+    REQUIRE_PTR(pp, info);
+    if (pp->m->results.size() != 1) { g_last_error = "the model has more than one output: name it or give its index"; return PARAMETER_MISMATCH; }
+    return ov_preprocess_prepostprocessor_get_output_info_by_index(pp, 0, info);
+}
+ov_status_e ov_preprocess_prepostprocessor_get_output_info_by_name(const ov_preprocess_prepostprocessor_t* pp, const char* name, ov_preprocess_output_info_t** info) {
+    REQUIRE_PTR(pp, name, info);
+    const int k = find_port(pp->m->results, name);
+    if (k < 0) { g_last_error = std::string("no output named ") + name; return NOT_FOUND; }
+    return ov_preprocess_prepostprocessor_get_output_info_by_index(pp, (size_t)k, info);
+}
+void ov_preprocess_output_info_free(ov_preprocess_output_info_t* p) { delete p; }
+ov_status_e ov_preprocess_output_info_get_tensor_info(const ov_preprocess_output_info_t* info, ov_preprocess_output_tensor_info_t** t) {
+    REQUIRE_PTR(info, t);
+    *t = new ov_preprocess_output_tensor_info{info->pp, info->index};
+    return OK;
+}
+void ov_preprocess_output_tensor_info_free(ov_preprocess_output_tensor_info_t* p) { delete p; }
+ov_status_e ov_preprocess_output_set_element_type(ov_preprocess_output_tensor_info_t* t, const ov_element_type_e type) {
+    REQUIRE_PTR(t);
+    t->pp->output_types[t->index] = static_cast<ET>(type);
+    return OK;
+}
+
+// ---- layouts
+ov_status_e ov_layout_create(const char* desc, ov_layout_t** layout) {
+    REQUIRE_PTR(desc, layout);
+    std::string d;
+    for (const char* c = desc; *c; ++c)
+        if (*c != '[' && *c != ']' && *c != ',' && *c != ' ') d.push_back((char)std::toupper((unsigned char)*c));
+    if (d.empty()) { g_last_error = "empty layout"; return INVALID_C_PARAM; }
+    *layout = new ov_layout{d};
+    return OK;
+}
+void ov_layout_free(ov_layout_t* layout) { delete layout; }
+const char* ov_layout_to_string(const ov_layout_t* layout) {
+    if (!layout) return nullptr;
+    std::string s = "[";
+    for (size_t i = 0; i < layout->desc.size(); ++i) { if (i) s += ","; s.push_back(layout->desc[i]); }
+    return dup_str(s + "]");
+}
+
+// ---- the remaining names of the reference headers
+ov_status_e ov_tensor_create_from_string_array(const char** strings, const size_t n, const ov_shape_t shape, ov_tensor_t** tensor) {
+    REQUIRE_PTR(strings, tensor);
+    return guarded([&] {
+        Shape s(shape.dims, shape.dims + shape.rank);
+        Tensor t(ET::string, s);
+        if ((size_t)t.numel() != n) { g_last_error = "the shape does not hold that many strings"; return PARAMETER_MISMATCH; }
+        for (size_t i = 0; i < n; ++i) t.strings[i] = strings[i] ? strings[i] : "";
+        *tensor = new ov_tensor{t};
+        return OK;
+    });
+}
+ov_status_e ov_tensor_set_string_data(ov_tensor_t* tensor, const char** strings, const size_t n) {
+    REQUIRE_PTR(tensor, strings);
+    if (tensor->t.et != ET::string || tensor->t.strings.size() != n) { g_last_error = "not a string tensor of that size"; return PARAMETER_MISMATCH; }
+    for (size_t i = 0; i < n; ++i) tensor->t.strings[i] = strings[i] ? strings[i] : "";
+    return OK;
+}
+ov_status_e ov_model_reshape_by_ports(const ov_model_t* model, const ov_output_port_t** ports, const ov_partial_shape_t* shapes, size_t size) {
+    REQUIRE_PTR(model, ports, shapes);
+    return guarded([&] {
+        std::map<size_t, PShape> m;
+        for (size_t i = 0; i < size; ++i) {
+            bool found = false;
+            for (size_t k = 0; k < model->m->params.size(); ++k)
+                if (ports[i] && model->m->params[k] == ports[i]->o.node) { m[k] = to_pshape(shapes[i]); found = true; }
+            if (!found) { g_last_error = "a port does not belong to the model's inputs"; return NOT_FOUND; }
+        }
+        model->m->reshape(m);
+        return OK;
+    });
+}
+ov_status_e ov_infer_request_set_tensor_by_port(ov_infer_request_t* r, const ov_output_port_t* port, const ov_tensor_t* t) {
+    REQUIRE_PTR(r, port, t);
+    // a port of the model the request was compiled from is matched by its tensor name, as the compiled copy has its own nodes
+    ov_output_const_port cp{port->o};
+    if (ov_infer_request_set_tensor_by_const_port(r, &cp, t) == OK) return OK;
+    return ov_infer_request_set_tensor(r, port_name(port->o).c_str(), t);
+}
+ov_status_e ov_infer_request_get_tensor_by_port(const ov_infer_request_t* r, const ov_output_port_t* port, ov_tensor_t** t) {
+    REQUIRE_PTR(r, port, t);
+    ov_output_const_port cp{port->o};
+    if (ov_infer_request_get_tensor_by_const_port(r, &cp, t) == OK) return OK;
+    return ov_infer_request_get_tensor(r, port_name(port->o).c_str(), t);
+}
+// wide-character paths: converted to UTF-8 and handed to the narrow entry points
+static std::string narrow(const wchar_t* w) {
+    std::string out;
+    for (; w && *w; ++w) {
+        uint32_t c = (uint32_t)*w;
+        if (c < 0x80) out.push_back((char)c);
+        else if (c < 0x800) { out.push_back((char)(0xC0 | (c >> 6))); out.push_back((char)(0x80 | (c & 0x3F))); }
+        else if (c < 0x10000) { out.push_back((char)(0xE0 | (c >> 12))); out.push_back((char)(0x80 | ((c >> 6) & 0x3F))); out.push_back((char)(0x80 | (c & 0x3F))); }
+        else { out.push_back((char)(0xF0 | (c >> 18))); out.push_back((char)(0x80 | ((c >> 12) & 0x3F))); out.push_back((char)(0x80 | ((c >> 6) & 0x3F))); out.push_back((char)(0x80 | (c & 0x3F))); }
+    }
+    return out;
+}
+ov_status_e ov_core_create_with_config_unicode(const wchar_t* xml_config_file, ov_core_t** core) {
+    return ov_core_create_with_config(xml_config_file ? narrow(xml_config_file).c_str() : nullptr, core);
+}
+ov_status_e ov_core_read_model_unicode(const ov_core_t* core, const wchar_t* model_path, const wchar_t* bin_path, ov_model_t** model) {
+    REQUIRE_PTR(core, model_path, model);
+    const std::string mp = narrow(model_path), bp = narrow(bin_path);
+    return ov_core_read_model(core, mp.c_str(), bin_path ? bp.c_str() : nullptr, model);
+}
+ov_status_e ov_core_compile_model_from_file_unicode(const ov_core_t* core, const wchar_t* model_path, const char* device_name, const size_t property_args_size,
+                                                    ov_compiled_model_t** compiled_model, ...) {
+    REQUIRE_PTR(core, model_path, device_name, compiled_model);
+    va_list ap;
+    va_start(ap, compiled_model);
+    auto props = read_props(property_args_size, ap);
+    va_end(ap);
+    return guarded([&] { return compile_impl(core, read_model_files(narrow(model_path), ""), device_name, props, compiled_model); });
+}
+ov_status_e ov_core_add_extension(const ov_core_t* core, const char* path) {
+    REQUIRE_PTR(core, path);
+    g_last_error = std::string("extension libraries are not loaded by this runtime: ") + path;
+    return NOT_IMPLEMENTED;
+}
+// device memory contexts belong to devices with their own memory; the host device of this library has none
+ov_status_e ov_core_create_context(const ov_core_t* core, const char* device, const size_t, ov_remote_context_t** ctx, ...) {
+    REQUIRE_PTR(core, device, ctx);
+    g_last_error = std::string("device ") + device + " has no remote context";
+    return NOT_IMPLEMENTED;
+}
+ov_status_e ov_core_get_default_context(const ov_core_t* core, const char* device, ov_remote_context_t** ctx) {
+    REQUIRE_PTR(core, device, ctx);
+    g_last_error = std::string("device ") + device + " has no remote context";
+    return NOT_IMPLEMENTED;
+}
+ov_status_e ov_compiled_model_get_context(const ov_compiled_model_t* cm, ov_remote_context_t** ctx) {
+    REQUIRE_PTR(cm, ctx);
+    g_last_error = "the host device has no remote context";
+    return NOT_IMPLEMENTED;
+}
+ov_status_e ov_core_compile_model_with_context(const ov_core_t* core, const ov_model_t* model, const ov_remote_context_t* ctx, const size_t, ov_compiled_model_t** cm, ...) {
+    REQUIRE_PTR(core, model, cm);
+    (void)ctx;
+    g_last_error = "the host device has no remote context";
+    return NOT_IMPLEMENTED;
+}
+void ov_remote_context_free(ov_remote_context_t*) {}
+static ov_status_e no_remote() { g_last_error = "the host device has no remote context"; return NOT_IMPLEMENTED; }
+ov_status_e ov_remote_context_get_device_name(const ov_remote_context_t*, char**) { return no_remote(); }
+ov_status_e ov_remote_context_get_params(const ov_remote_context_t*, size_t*, char**) { return no_remote(); }
+ov_status_e ov_remote_context_create_tensor(const ov_remote_context_t*, const ov_element_type_e, const ov_shape_t, const size_t, ov_tensor_t**, ...) { return no_remote(); }
+ov_status_e ov_remote_context_create_host_tensor(const ov_remote_context_t*, const ov_element_type_e, const ov_shape_t, ov_tensor_t**) { return no_remote(); }
+ov_status_e ov_remote_tensor_get_params(ov_tensor_t*, size_t*, char**) { return no_remote(); }
+ov_status_e ov_remote_tensor_get_device_name(ov_tensor_t*, char**) { return no_remote(); }
+static void (*g_log_callback)(const char*) = nullptr;
+void ov_util_set_log_callback(void (*callback)(const char*)) { g_log_callback = callback; }
+void ov_util_reset_log_callback() { g_log_callback = nullptr; }
 
 }  // extern "C"

@@ -13,6 +13,7 @@
 
 #include <stdbool.h>
 #include <stddef.h>
+#include <wchar.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -60,6 +61,20 @@ typedef struct ov_tensor ov_tensor_t;
 typedef struct ov_output_const_port ov_output_const_port_t;
 typedef struct ov_output_port ov_output_port_t;
 typedef struct ov_preprocess_prepostprocessor ov_preprocess_prepostprocessor_t;
+typedef struct ov_preprocess_input_info ov_preprocess_input_info_t;
+typedef struct ov_preprocess_input_tensor_info ov_preprocess_input_tensor_info_t;
+typedef struct ov_preprocess_preprocess_steps ov_preprocess_preprocess_steps_t;
+typedef struct ov_preprocess_input_model_info ov_preprocess_input_model_info_t;
+typedef struct ov_preprocess_output_info ov_preprocess_output_info_t;
+typedef struct ov_preprocess_output_tensor_info ov_preprocess_output_tensor_info_t;
+typedef struct ov_layout ov_layout_t;
+typedef struct ov_remote_context ov_remote_context_t;
+
+typedef enum {
+    UNDEFINE = 0U, NV12_SINGLE_PLANE, NV12_TWO_PLANES, I420_SINGLE_PLANE, I420_THREE_PLANES, RGB, BGR, GRAY, RGBX, BGRX,
+} ov_color_format_e;
+typedef enum { RESIZE_LINEAR, RESIZE_CUBIC, RESIZE_NEAREST } ov_preprocess_resize_algorithm_e;
+typedef enum { CONSTANT = 0, EDGE, REFLECT, SYMMETRIC } ov_padding_mode_e;
 
 typedef struct ov_version { const char* buildNumber; const char* description; } ov_version_t;
 typedef struct { const char* device_name; ov_version_t version; } ov_core_version_t;
@@ -210,6 +225,89 @@ OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_set_input_mean_scale(
                                                                                 const float* scale, size_t channels, int64_t channel_axis);
 OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_set_input_nhwc(ov_preprocess_prepostprocessor_t* preprocess, size_t input);
 OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_build(const ov_preprocess_prepostprocessor_t* preprocess, ov_model_t** model);
+
+/* ---- pre/post-processing, object by object: prepostprocessor -> input info -> tensor info / steps / model info */
+OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_get_input_info(const ov_preprocess_prepostprocessor_t* preprocess, ov_preprocess_input_info_t** info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_get_input_info_by_name(const ov_preprocess_prepostprocessor_t* preprocess, const char* tensor_name,
+                                                                                  ov_preprocess_input_info_t** info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_get_input_info_by_index(const ov_preprocess_prepostprocessor_t* preprocess, const size_t tensor_index,
+                                                                                   ov_preprocess_input_info_t** info);
+OPENVINO_C_API(void) ov_preprocess_input_info_free(ov_preprocess_input_info_t* info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_info_get_tensor_info(const ov_preprocess_input_info_t* info, ov_preprocess_input_tensor_info_t** tensor_info);
+OPENVINO_C_API(void) ov_preprocess_input_tensor_info_free(ov_preprocess_input_tensor_info_t* tensor_info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_info_get_preprocess_steps(const ov_preprocess_input_info_t* info, ov_preprocess_preprocess_steps_t** steps);
+OPENVINO_C_API(void) ov_preprocess_preprocess_steps_free(ov_preprocess_preprocess_steps_t* steps);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_info_get_model_info(const ov_preprocess_input_info_t* info, ov_preprocess_input_model_info_t** model_info);
+OPENVINO_C_API(void) ov_preprocess_input_model_info_free(ov_preprocess_input_model_info_t* model_info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_model_info_set_layout(ov_preprocess_input_model_info_t* model_info, ov_layout_t* layout);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_element_type(ov_preprocess_input_tensor_info_t* tensor_info, const ov_element_type_e type);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_layout(ov_preprocess_input_tensor_info_t* tensor_info, ov_layout_t* layout);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_color_format(ov_preprocess_input_tensor_info_t* tensor_info, const ov_color_format_e format);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_color_format_with_subname(ov_preprocess_input_tensor_info_t* tensor_info, const ov_color_format_e format,
+                                                                                          const size_t sub_names_size, ...);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_spatial_static_shape(ov_preprocess_input_tensor_info_t* tensor_info, const size_t height,
+                                                                                     const size_t width);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_memory_type(ov_preprocess_input_tensor_info_t* tensor_info, const char* mem_type);
+OPENVINO_C_API(ov_status_e) ov_preprocess_input_tensor_info_set_from(ov_preprocess_input_tensor_info_t* tensor_info, const ov_tensor_t* tensor);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_resize(ov_preprocess_preprocess_steps_t* steps, const ov_preprocess_resize_algorithm_e algorithm);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_scale(ov_preprocess_preprocess_steps_t* steps, float value);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_scale_multi_channels(ov_preprocess_preprocess_steps_t* steps, const float* values, const int32_t size);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_mean(ov_preprocess_preprocess_steps_t* steps, float value);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_mean_multi_channels(ov_preprocess_preprocess_steps_t* steps, const float* values, const int32_t size);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_crop(ov_preprocess_preprocess_steps_t* steps, int32_t* begin, int32_t begin_size, int32_t* end,
+                                                                int32_t end_size);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_convert_layout(ov_preprocess_preprocess_steps_t* steps, ov_layout_t* layout);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_reverse_channels(ov_preprocess_preprocess_steps_t* steps);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_convert_element_type(ov_preprocess_preprocess_steps_t* steps, const ov_element_type_e type);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_convert_color(ov_preprocess_preprocess_steps_t* steps, const ov_color_format_e format);
+OPENVINO_C_API(ov_status_e) ov_preprocess_preprocess_steps_pad(const ov_preprocess_preprocess_steps_t* steps, const int* const pads_begin, size_t pads_begin_size,
+                                                               const int* const pads_end, size_t pads_end_size, float value, ov_padding_mode_e mode);
+OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_get_output_info(const ov_preprocess_prepostprocessor_t* preprocess, ov_preprocess_output_info_t** info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_get_output_info_by_index(const ov_preprocess_prepostprocessor_t* preprocess, const size_t tensor_index,
+                                                                                    ov_preprocess_output_info_t** info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_prepostprocessor_get_output_info_by_name(const ov_preprocess_prepostprocessor_t* preprocess, const char* tensor_name,
+                                                                                   ov_preprocess_output_info_t** info);
+OPENVINO_C_API(void) ov_preprocess_output_info_free(ov_preprocess_output_info_t* info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_output_info_get_tensor_info(const ov_preprocess_output_info_t* info, ov_preprocess_output_tensor_info_t** tensor_info);
+OPENVINO_C_API(void) ov_preprocess_output_tensor_info_free(ov_preprocess_output_tensor_info_t* tensor_info);
+OPENVINO_C_API(ov_status_e) ov_preprocess_output_set_element_type(ov_preprocess_output_tensor_info_t* tensor_info, const ov_element_type_e type);
+
+/* ---- layouts ("NCHW", "[N,H,W,C]") */
+OPENVINO_C_API(ov_status_e) ov_layout_create(const char* layout_desc, ov_layout_t** layout);
+OPENVINO_C_API(void) ov_layout_free(ov_layout_t* layout);
+OPENVINO_C_API(const char*) ov_layout_to_string(const ov_layout_t* layout);
+
+/* ---- string tensors, ports of either constness, wide-character paths, log callback */
+OPENVINO_C_API(ov_status_e) ov_tensor_create_from_string_array(const char** string_array, const size_t array_size, const ov_shape_t shape, ov_tensor_t** tensor);
+OPENVINO_C_API(ov_status_e) ov_tensor_set_string_data(ov_tensor_t* tensor, const char** string_array, const size_t array_size);
+OPENVINO_C_API(ov_status_e) ov_model_reshape_by_ports(const ov_model_t* model, const ov_output_port_t** output_ports, const ov_partial_shape_t* partial_shapes,
+                                                      size_t size);
+OPENVINO_C_API(ov_status_e) ov_infer_request_set_tensor_by_port(ov_infer_request_t* infer_request, const ov_output_port_t* port, const ov_tensor_t* tensor);
+OPENVINO_C_API(ov_status_e) ov_infer_request_get_tensor_by_port(const ov_infer_request_t* infer_request, const ov_output_port_t* port, ov_tensor_t** tensor);
+OPENVINO_C_API(ov_status_e) ov_core_create_with_config_unicode(const wchar_t* xml_config_file, ov_core_t** core);
+OPENVINO_C_API(ov_status_e) ov_core_read_model_unicode(const ov_core_t* core, const wchar_t* model_path, const wchar_t* bin_path, ov_model_t** model);
+OPENVINO_C_API(ov_status_e) ov_core_compile_model_from_file_unicode(const ov_core_t* core, const wchar_t* model_path, const char* device_name,
+                                                                    const size_t property_args_size, ov_compiled_model_t** compiled_model, ...);
+OPENVINO_C_API(void) ov_util_set_log_callback(void (*callback)(const char*));
+OPENVINO_C_API(void) ov_util_reset_log_callback();
+
+/* ---- device memory contexts and extension libraries: the host device of this library has neither; the calls answer
+ *      NOT_IMPLEMENTED with a message (the CUDA device's remote tensors are reached through the Python and C++ APIs) */
+OPENVINO_C_API(ov_status_e) ov_core_add_extension(const ov_core_t* core, const char* path);
+OPENVINO_C_API(ov_status_e) ov_core_create_context(const ov_core_t* core, const char* device_name, const size_t context_args_size, ov_remote_context_t** context, ...);
+OPENVINO_C_API(ov_status_e) ov_core_get_default_context(const ov_core_t* core, const char* device_name, ov_remote_context_t** context);
+OPENVINO_C_API(ov_status_e) ov_core_compile_model_with_context(const ov_core_t* core, const ov_model_t* model, const ov_remote_context_t* context,
+                                                               const size_t property_args_size, ov_compiled_model_t** compiled_model, ...);
+OPENVINO_C_API(ov_status_e) ov_compiled_model_get_context(const ov_compiled_model_t* compiled_model, ov_remote_context_t** context);
+OPENVINO_C_API(void) ov_remote_context_free(ov_remote_context_t* context);
+OPENVINO_C_API(ov_status_e) ov_remote_context_get_device_name(const ov_remote_context_t* context, char** device_name);
+OPENVINO_C_API(ov_status_e) ov_remote_context_get_params(const ov_remote_context_t* context, size_t* size, char** params);
+OPENVINO_C_API(ov_status_e) ov_remote_context_create_tensor(const ov_remote_context_t* context, const ov_element_type_e type, const ov_shape_t shape,
+                                                            const size_t object_args_size, ov_tensor_t** remote_tensor, ...);
+OPENVINO_C_API(ov_status_e) ov_remote_context_create_host_tensor(const ov_remote_context_t* context, const ov_element_type_e type, const ov_shape_t shape,
+                                                                 ov_tensor_t** tensor);
+OPENVINO_C_API(ov_status_e) ov_remote_tensor_get_params(ov_tensor_t* tensor, size_t* size, char** params);
+OPENVINO_C_API(ov_status_e) ov_remote_tensor_get_device_name(ov_tensor_t* remote_tensor, char** device_name);
 
 #ifdef __cplusplus
 }
