@@ -174,6 +174,31 @@ Tensor pad_rows(const Tensor& t, int64_t rows, double fill) {
     return o;
 }
 
+// The operation a TypeRelaxed node wraps, built over stand-in inputs that carry the overriding element types (and the
+// shapes of the node's inputs, or of the tensors of an evaluation) so that the wrapped operation's own rules run.
+NodePtr relaxed_base(const Node& n, const std::vector<Tensor>* tensors) {
+    const std::string type = n.attr_str("base_type"), version = n.attr_str("base_version");
+    const OpSchema* schema = version.empty() ? OpRegistry::get().find_latest(type) : OpRegistry::get().find(type, version);
+    OVC_CHECK(schema, n.description() << ": no operation " << type << " in " << (version.empty() ? "any opset" : version));
+    const auto& its = n.attr("input_data_types").ss;
+    std::vector<Output> ports;
+    for (size_t i = 0; i < n.num_inputs(); ++i) {
+        const ET et = i < its.size() && its[i] != "dynamic" && !its[i].empty() ? et_from_name(its[i]) : n.in_et(i);
+        std::vector<int64_t> values;
+        // constant inputs keep their values: shape arguments (Reshape pattern, axes) drive the wrapped operation's inference
+        if (!tensors && n.input(i).node->type == "Constant" && et == n.in_et(i)) { ports.push_back(n.input(i)); continue; }
+        ports.push_back(make_parameter(et, tensors ? PShape((*tensors)[i].shape) : n.in_shape(i))->output(0));
+    }
+    std::vector<std::pair<std::string, Attr>> attrs;
+    for (const auto& kv : n.attrs)
+        if (kv.first != "base_type" && kv.first != "base_version" && kv.first != "input_data_types" && kv.first != "output_data_types") attrs.push_back(kv);
+    // a model read back from a file carries the wrapped operation's attributes as text: give each the kind its schema names
+    for (auto& kv : attrs)
+        for (const AttrSpec& spec : schema->attrs)
+            if (spec.name == kv.first && kv.second.kind == Attr::STR && spec.kind != Attr::STR) kv.second = Attr::from_string(spec.kind, kv.second.s);
+    return make_node(schema->type, schema->version, ports, attrs, true);
+}
+
 }  // namespace
 
 void register_private_ops() {
@@ -377,6 +402,139 @@ void register_private_ops() {
             out[2] = res[2];
             return true;
         }, 4, 4);
+
+    // ---- GroupQueryAttention (src/core/dev_api/openvino/op/group_query_attention.hpp): q [B, N, S, H], k / v
+    // [B, Nkv, S, H], past k / v [B, Nkv, P, H], seqlens_k = (past + current) - 1, total_sequence_length, then optional
+    // cos / sin caches [positions, H / 2], position ids [B, S], attention bias [B or 1, N or 1, S, total], head sink [N].
+    // Outputs: attention [B, S, N * H], present k / v [B, Nkv, past + S, H]. An empty tensor stands for an absent input.
+    reg("GroupQueryAttention", "ie_internal_opset",
+        {A("num_heads", K::INT, Attr::Int(0)), A("kv_num_heads", K::INT, Attr::Int(0)), A("scale", K::FLOAT, Attr::Float(0)), A("do_rotary", K::BOOL, Attr::Bool(false)),
+         A("rotary_interleaved", K::BOOL, Attr::Bool(false)), A("local_window_size", K::INT, Attr::Int(-1)), A("smooth_softmax", K::BOOL, Attr::Bool(false))},
+        [](Node& n) {
+            n.set_num_outputs(3);
+            const PShape &q = n.in_shape(0), &k = n.in_shape(1), &pk = n.in_shape(3);
+            const Dim heads = dim_of(q, 1), width = dim_of(q, 3);
+            n.set_output(0, n.in_et(0), PShape({dim_of(q, 0), dim_of(q, 2), heads.is_static() && width.is_static() ? Dim(heads.lo * width.lo) : Dim::dynamic()}));
+            PShape present({dim_of(k, 0), dim_of(k, 1), Dim::dynamic(), dim_of(k, 3)});
+            std::vector<int64_t> lens;
+            if (get_constant_ints(n.input(5), lens) && !lens.empty()) present.dims[2] = Dim(lens[0] + 1);
+            (void)pk;
+            n.set_output(1, n.in_et(1), present);
+            n.set_output(2, n.in_et(2), present);
+        },
+        [](N n, Ins in, Outs out, C) {
+            const Tensor& Q = in[0];
+            OVC_CHECK(Q.shape.size() == 4 && in[1].shape.size() == 4 && in[3].shape.size() == 4, n.description() << ": q, k, v and the past are rank-4 [batch, heads, length, width]");
+            const int64_t B = Q.shape[0], Nq = Q.shape[1], S = Q.shape[2], H = Q.shape[3], Nkv = in[1].shape[1], Pmax = in[3].shape[2];
+            OVC_CHECK(Nkv > 0 && Nq % Nkv == 0, n.description() << ": " << Nq << " query heads do not divide into " << Nkv << " key / value heads");
+            const int64_t total = to_i64(in[5])[0] + 1, P = total - S, group = Nq / Nkv;
+            OVC_CHECK(P >= 0 && P <= Pmax, n.description() << ": seqlens_k names a past of " << P << " positions, the past tensors hold " << Pmax);
+            auto q = to_f32(Q), kn = to_f32(in[1]);
+            const auto vn = to_f32(in[2]), pk = to_f32(in[3]), pv = to_f32(in[4]);
+            auto present = [&](size_t i) { return i < in.size() && in[i].numel() > 0; };
+            if (n.attr_bool("do_rotary")) {
+                OVC_CHECK(present(7) && present(8), n.description() << ": do_rotary needs the cos and sin caches");
+                const auto cs = to_f32(in[7]), sn = to_f32(in[8]);
+                const int64_t half = in[7].shape.back(), rows = in[7].numel() / half;
+                std::vector<int64_t> pos;
+                if (present(9)) pos = to_i64(in[9]);
+                const bool inter = n.attr_bool("rotary_interleaved");
+                auto rotate = [&](std::vector<float>& x, int64_t heads) {
+                    for (int64_t b = 0; b < B; ++b)
+                        for (int64_t h = 0; h < heads; ++h)
+                            for (int64_t s_ = 0; s_ < S; ++s_) {
+                                const int64_t p_ = pos.empty() ? P + s_ : pos[(size_t)((b * S + s_) % (int64_t)pos.size())];
+                                OVC_CHECK(p_ >= 0 && p_ < rows, n.description() << ": position " << p_ << " outside the rotary caches of " << rows << " rows");
+                                float* r = x.data() + ((b * heads + h) * S + s_) * H;
+                                for (int64_t d = 0; d < half; ++d) {
+                                    const int64_t i0 = inter ? 2 * d : d, i1 = inter ? 2 * d + 1 : d + half;
+                                    const float c = cs[(size_t)(p_ * half + d)], s2 = sn[(size_t)(p_ * half + d)], a = r[i0], b2 = r[i1];
+                                    r[i0] = a * c - b2 * s2;
+                                    r[i1] = a * s2 + b2 * c;
+                                }
+                            }
+                };
+                rotate(q, Nq);
+                rotate(kn, Nkv);
+            }
+            // present = past[:P] ++ new
+            std::vector<float> K_((size_t)(B * Nkv * total * H)), V_((size_t)(B * Nkv * total * H));
+            for (int64_t b = 0; b < B; ++b)
+                for (int64_t h = 0; h < Nkv; ++h)
+                    for (int64_t t = 0; t < total; ++t) {
+                        float* kd = K_.data() + ((b * Nkv + h) * total + t) * H;
+                        float* vd = V_.data() + ((b * Nkv + h) * total + t) * H;
+                        const float* ks = t < P ? pk.data() + ((b * Nkv + h) * Pmax + t) * H : kn.data() + ((b * Nkv + h) * S + (t - P)) * H;
+                        const float* vs = t < P ? pv.data() + ((b * Nkv + h) * Pmax + t) * H : vn.data() + ((b * Nkv + h) * S + (t - P)) * H;
+                        std::copy(ks, ks + H, kd);
+                        std::copy(vs, vs + H, vd);
+                    }
+            const float scale = n.attr_float("scale") != 0 ? (float)n.attr_float("scale") : 1.f / std::sqrt((float)H);
+            const int64_t window = n.attr_int("local_window_size", -1);
+            std::vector<float> bias, sink;
+            Shape bs;
+            if (present(10)) { bias = to_f32(in[10]); bs = in[10].shape; OVC_CHECK(bs.size() == 4 && bs[3] >= total && bs[2] == S, n.description() << ": attention bias is [B or 1, N or 1, S, >= total]"); }
+            if (present(11)) sink = to_f32(in[11]);
+            const bool smooth = n.attr_bool("smooth_softmax") || !sink.empty();
+            std::vector<float> o((size_t)(B * S * Nq * H), 0.f), p((size_t)total);
+            for (int64_t b = 0; b < B; ++b)
+                for (int64_t h = 0; h < Nq; ++h)
+                    for (int64_t i = 0; i < S; ++i) {
+                        const float* qr = q.data() + ((b * Nq + h) * S + i) * H;
+                        const int64_t last = P + i, first = window > 0 ? std::max<int64_t>(0, last - window + 1) : 0;
+                        float mx = smooth ? (sink.empty() ? 0.f : sink[(size_t)(h % (int64_t)sink.size())]) : -std::numeric_limits<float>::infinity();
+                        for (int64_t j = first; j <= last; ++j) {
+                            const float* kr = K_.data() + ((b * Nkv + h / group) * total + j) * H;
+                            float acc = 0;
+                            for (int64_t d = 0; d < H; ++d) acc += qr[d] * kr[d];
+                            acc *= scale;
+                            if (!bias.empty()) acc += bias[(size_t)((((bs[0] == 1 ? 0 : b) * bs[1] + (bs[1] == 1 ? 0 : h)) * S + i) * bs[3] + j)];
+                            p[(size_t)j] = acc;
+                            mx = std::max(mx, acc);
+                        }
+                        double sum = smooth ? std::exp((sink.empty() ? 0.f : sink[(size_t)(h % (int64_t)sink.size())]) - mx) : 0.0;
+                        for (int64_t j = first; j <= last; ++j) { p[(size_t)j] = std::exp(p[(size_t)j] - mx); sum += p[(size_t)j]; }
+                        float* orow = o.data() + ((b * S + i) * Nq + h) * H;
+                        for (int64_t j = first; j <= last; ++j) {
+                            const float w = (float)(p[(size_t)j] / sum);
+                            const float* vr = V_.data() + ((b * Nkv + h / group) * total + j) * H;
+                            for (int64_t d = 0; d < H; ++d) orow[d] += w * vr[d];
+                        }
+                    }
+            out[0] = from_f32(Q.et, {B, S, Nq * H}, o);
+            out[1] = from_f32(in[1].et, {B, Nkv, total, H}, K_);
+            out[2] = from_f32(in[2].et, {B, Nkv, total, H}, V_);
+            return true;
+        }, 7, 14);
+
+    // ---- TypeRelaxed (src/core/dev_api/openvino/op/util/type_relaxed... ov_ops/type_relaxed.hpp): an operation whose inputs
+    // are seen by its own type rules as `input_data_types` whatever feeds it, and whose outputs are declared as
+    // `output_data_types`. The wrapped operation is named by base_type / base_version; every other attribute is the
+    // wrapped operation's own.
+    reg("TypeRelaxed", "type_relaxed_opset",
+        {A("base_type", K::STR, Attr::Str("")), A("base_version", K::STR, Attr::Str("")), A("input_data_types", K::STRS, Attr::Strs({})),
+         A("output_data_types", K::STRS, Attr::Strs({}))},
+        [](Node& n) {
+            NodePtr base = relaxed_base(n, nullptr);
+            n.set_num_outputs(base->outs.size());
+            const auto& outs = n.attr("output_data_types").ss;
+            for (size_t i = 0; i < base->outs.size(); ++i) {
+                const ET et = i < outs.size() && outs[i] != "dynamic" && !outs[i].empty() ? et_from_name(outs[i]) : base->outs[i].et;
+                n.set_output(i, et, base->outs[i].shape);
+            }
+        },
+        [](N n, Ins in, Outs out, C c) {
+            std::vector<Tensor> seen;
+            NodePtr base = relaxed_base(n, &in);
+            const auto& its = n.attr("input_data_types").ss;
+            for (size_t i = 0; i < in.size(); ++i)
+                seen.push_back(i < its.size() && its[i] != "dynamic" && !its[i].empty() && in[i].et != et_from_name(its[i]) ? convert_tensor(in[i], et_from_name(its[i])) : in[i]);
+            OVC_CHECK(base->schema && base->schema->eval, n.description() << ": " << base->type << " has no evaluation");
+            std::vector<Tensor> res(base->outs.size());
+            if (!base->schema->eval(*base, seen, res, c)) return false;
+            for (size_t i = 0; i < res.size(); ++i) out[i] = res[i].et == n.outs[i].et ? res[i] : convert_tensor(res[i], n.outs[i].et);
+            return true;
+        }, 0, -1);
 }
 
 }  // namespace ovc

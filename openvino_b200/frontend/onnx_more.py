@@ -602,3 +602,36 @@ def _rotary_embedding(n, i):
     if r == 3:
         return ops.reshape(y4, _i64([0, 0, -1]), True).output(0)
     return ops.transpose(y4, _i64([0, 2, 1, 3])).output(0)
+
+
+@_op("GroupQueryAttention")
+def _group_query_attention(n, i):
+    """com.microsoft GroupQueryAttention: query / key / value [B, S, heads * width] (or one packed tensor), past key /
+    value [B, kv heads, past, width], seqlens_k, total_sequence_length and the optional cos / sin caches, position ids,
+    attention bias and head sink -> the GroupQueryAttention operation, which works on [B, heads, S, width].
+    Reference: src/frontends/onnx/frontend/src/op/com.microsoft/group_query_attention.cpp."""
+    heads, kv_heads = int(n.attrs.get("num_heads", 0)), int(n.attrs.get("kv_num_heads", 0))
+    if not heads or not kv_heads:
+        raise OnnxError("GroupQueryAttention needs num_heads and kv_num_heads")
+    got = lambda k: len(i) > k and i[k] is not None
+    q = i[0]
+    if got(1) and got(2):
+        k, v = i[1], i[2]
+    else:                        # packed [B, S, (heads + 2 * kv heads) * width]
+        hidden = q.get_partial_shape()[2]
+        if not hidden.is_static:
+            raise OnnxError("GroupQueryAttention with packed QKV needs a static hidden size")
+        width = hidden.get_length() // (heads + 2 * kv_heads)
+        parts = ops.variadic_split(q, _i64(2), _i64([heads * width, kv_heads * width, kv_heads * width]))
+        q, k, v = parts.output(0), parts.output(1), parts.output(2)
+
+    def split_heads(x, count):
+        return ops.transpose(ops.reshape(x, _i64([0, 0, count, -1]), True), _i64([0, 2, 1, 3])).output(0)
+    absent = lambda: constant(np.zeros((0,), np.float32)).output(0)
+    ins = [split_heads(q, heads), split_heads(k, kv_heads), split_heads(v, kv_heads), i[3], i[4], i[5], i[6]]
+    last = max([p for p in range(7, 12) if got(p)], default=6)
+    ins += [i[p] if got(p) else absent() for p in range(7, last + 1)]
+    node = ops.group_query_attention(ins, num_heads=heads, kv_num_heads=kv_heads, scale=float(n.attrs.get("scale", 0.0)),
+                                     do_rotary=bool(n.attrs.get("do_rotary", 0)), rotary_interleaved=bool(n.attrs.get("rotary_interleaved", 0)),
+                                     local_window_size=int(n.attrs.get("local_window_size", -1)), smooth_softmax=bool(n.attrs.get("smooth_softmax", 0)))
+    return [node.output(0), node.output(1), node.output(2)]

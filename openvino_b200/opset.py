@@ -25,6 +25,7 @@ gather_matmul_compressed GatherMatmulCompressed@ie_internal_opset : A B indices 
 grouped_matmul_compressed GroupedMatMulCompressed@ie_internal_opset : *inputs
 fully_connected_quantized FullyConnectedQuantized@ie_internal_opset : X W bias weight_scales weight_zero_points input_scales input_zero_points output_scales output_zero_points | output_type=dynamic
 fully_connected_quantized_legacy FullyConnectedQuantizedLegacy@ie_internal_opset : X W bias deq_scales [deq_zero_points] | output_type=dynamic
+group_query_attention GroupQueryAttention@ie_internal_opset : *inputs | num_heads kv_num_heads scale=0.0 do_rotary=False rotary_interleaved=False local_window_size=-1 smooth_softmax=False
 vl_sdpa VLSDPA@ie_internal_opset : q k v cu_seqlens | order_q=[] order_k=[] order_v=[] order_out=[]
 selective_ssm SelectiveSSM@ie_internal_opset : A dt B x C recurrent_state
 gated_delta_net GatedDeltaNet@ie_internal_opset : query key value recurrent_state gate beta | fuse_qk_l2norm=False q_l2_norm_eps=1e-6 k_l2_norm_eps=1e-6
@@ -564,4 +565,14 @@ def paged_attention(inputs, write_kv_cache: bool = True, name=None) -> Node:
 
 
 # re-exports so that ``from openvino_b200.opset import constant, parameter``
+def type_relaxed(base_type: str, inputs, input_data_types=(), output_data_types=(), base_version: str = "", name=None, **attrs) -> Node:
+    """``base_type`` applied to ``inputs`` with its type rules seeing ``input_data_types`` and its outputs declared as
+    ``output_data_types`` (ov::op::TypeRelaxed<Base> of the reference, src/core/include/openvino/op/util/... ov_ops/type_relaxed.hpp).
+    An empty string or "dynamic" in either list leaves that port as it is."""
+    spell = lambda t: t if isinstance(t, str) else Type(t).get_type_name()
+    a = dict(attrs, base_type=base_type, base_version=base_version, input_data_types=[spell(t) for t in input_data_types],
+             output_data_types=[spell(t) for t in output_data_types])
+    return make_op("TypeRelaxed", list(inputs), a, version="type_relaxed_opset", name=name)
+
+
 __all__ = [n for n in dir() if not n.startswith("_")]

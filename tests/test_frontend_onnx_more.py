@@ -157,3 +157,46 @@ def test_transformer_contrib_operations():
     a_, b_ = x4[..., :D // 2], x4[..., D // 2:]
     ref = np.concatenate([a_ * c - b_ * sn, a_ * sn + b_ * c], -1).reshape(B, S, heads * D)
     np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_group_query_attention_contrib():
+    """com.microsoft GroupQueryAttention with separate and with packed q / k / v, a past of 3 positions and rotary caches."""
+    rng = np.random.default_rng(21)
+    B, S, N, Nkv, H, P = 1, 2, 4, 2, 8, 3
+    total = P + S
+    q = rng.standard_normal((B, S, N * H)).astype(np.float32)
+    k = rng.standard_normal((B, S, Nkv * H)).astype(np.float32)
+    v = rng.standard_normal((B, S, Nkv * H)).astype(np.float32)
+    pk = rng.standard_normal((B, Nkv, P, H)).astype(np.float32)
+    pv = rng.standard_normal((B, Nkv, P, H)).astype(np.float32)
+    ang = rng.random((16, H // 2)).astype(np.float32)
+    inits = {"lens": np.array([total - 1], np.int32), "total": np.array(total, np.int32), "cos": np.cos(ang), "sin": np.sin(ang)}
+
+    def reference(rot):
+        t = lambda x, h: torch.tensor(x).reshape(B, S, h, H).transpose(1, 2)
+        qh, kh, vh = t(q, N), t(k, Nkv), t(v, Nkv)
+        if rot:
+            c, s = torch.tensor(inits["cos"][P:total]), torch.tensor(inits["sin"][P:total])
+            r = lambda x: torch.cat([x[..., :H // 2] * c - x[..., H // 2:] * s, x[..., :H // 2] * s + x[..., H // 2:] * c], -1)
+            qh, kh = r(qh), r(kh)
+        K_ = torch.cat([torch.tensor(pk), kh], 2)
+        V_ = torch.cat([torch.tensor(pv), vh], 2)
+        sc = qh @ K_.repeat_interleave(N // Nkv, 1).transpose(-1, -2) / np.sqrt(H)
+        keep = torch.arange(total)[None, :] <= torch.arange(S)[:, None] + P
+        w = torch.softmax(sc.masked_fill(~keep, float("-inf")), -1)
+        return (w @ V_.repeat_interleave(N // Nkv, 1)).transpose(1, 2).reshape(B, S, N * H).numpy(), K_.numpy()
+
+    outs = [("y", 1, [B, S, N * H]), ("nk", 1, [B, Nkv, total, H]), ("nv", 1, [B, Nkv, total, H])]
+    ins = [("q", 1, list(q.shape)), ("k", 1, list(k.shape)), ("v", 1, list(v.shape)), ("pk", 1, list(pk.shape)), ("pv", 1, list(pv.shape))]
+    y, nk, _ = run([node("GroupQueryAttention", ["q", "k", "v", "pk", "pv", "lens", "total"], ["y", "nk", "nv"], num_heads=N, kv_num_heads=Nkv)],
+                   inits, ins, outs, [q, k, v, pk, pv])
+    ref_y, ref_k = reference(False)
+    np.testing.assert_allclose(y, ref_y, rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(nk, ref_k, rtol=1e-6)
+    packed = np.concatenate([q, k, v], -1)
+    ins = [("qkv", 1, list(packed.shape)), ("pk", 1, list(pk.shape)), ("pv", 1, list(pv.shape))]
+    y, nk, _ = run([node("GroupQueryAttention", ["qkv", "", "", "pk", "pv", "lens", "total", "cos", "sin"], ["y", "nk", "nv"], num_heads=N, kv_num_heads=Nkv,
+                         do_rotary=1)], inits, ins, outs, [packed, pk, pv])
+    ref_y, ref_k = reference(True)
+    np.testing.assert_allclose(y, ref_y, rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(nk, ref_k, rtol=2e-5, atol=2e-5)

@@ -139,3 +139,107 @@ def test_einsum_reference_evaluation():
     sq = rng.standard_normal((4, 4)).astype(np.float32)
     ps = P(sq.shape, "s")
     np.testing.assert_allclose(run([ops.einsum([ps], "ii->i")], [ps], [sq])[0], np.diag(sq), rtol=1e-6)
+
+
+def _gqa_reference(q, k, v, pk, pv, total, scale=None, window=-1, rotary=None, interleaved=False, sink=None, bias=None):
+    """PyTorch restatement of GroupQueryAttention: returns (out [B, S, N * H], present k, present v)."""
+    q, k, v, pk, pv = (torch.from_numpy(np.array(t, dtype=np.float32)) for t in (q, k, v, pk, pv))
+    B, Nq, S, H = q.shape
+    Nkv = k.shape[1]
+    P_ = total - S
+    if rotary is not None:
+        cos, sin = (torch.from_numpy(t)[P_:P_ + S] for t in rotary)           # [S, H / 2]
+
+        def rot(x):
+            if interleaved:
+                a, b = x[..., 0::2], x[..., 1::2]
+                return torch.stack([a * cos - b * sin, a * sin + b * cos], -1).flatten(-2)
+            a, b = x[..., :H // 2], x[..., H // 2:]
+            return torch.cat([a * cos - b * sin, a * sin + b * cos], -1)
+        q, k = rot(q), rot(k)
+    K_ = torch.cat([pk[:, :, :P_], k], 2)
+    V_ = torch.cat([pv[:, :, :P_], v], 2)
+    Kx = K_.repeat_interleave(Nq // Nkv, 1)
+    Vx = V_.repeat_interleave(Nq // Nkv, 1)
+    s = q @ Kx.transpose(-1, -2) * (scale or 1.0 / np.sqrt(H))
+    if bias is not None:
+        s = s + torch.from_numpy(bias)[..., :total]
+    i = torch.arange(S)[:, None] + P_
+    j = torch.arange(total)[None, :]
+    keep = j <= i
+    if window > 0:
+        keep &= j > i - window
+    s = s.masked_fill(~keep, float("-inf"))
+    if sink is not None:
+        col = torch.from_numpy(sink).reshape(1, Nq, 1, 1).expand(B, Nq, S, 1)
+        w = torch.softmax(torch.cat([s, col], -1), -1)[..., :-1]
+    else:
+        w = torch.softmax(s, -1)
+    o = (w @ Vx).permute(0, 2, 1, 3).reshape(B, S, Nq * H)
+    return o.numpy(), K_.numpy(), V_.numpy()
+
+
+def test_group_query_attention_prefill_decode_rotary_window_sink():
+    rng = np.random.default_rng(11)
+    B, Nq, Nkv, H, Pmax = 2, 4, 2, 8, 12
+    for S, past, kw in ((5, 0, {}), (1, 7, {}), (3, 4, {"window": 4}), (2, 5, {"rot": True}), (2, 5, {"rot": True, "inter": True}), (3, 2, {"sink": True}),
+                        (2, 3, {"bias": True})):
+        total = past + S
+        q = rng.standard_normal((B, Nq, S, H)).astype(np.float32)
+        k = rng.standard_normal((B, Nkv, S, H)).astype(np.float32)
+        v = rng.standard_normal((B, Nkv, S, H)).astype(np.float32)
+        pk = rng.standard_normal((B, Nkv, Pmax, H)).astype(np.float32)
+        pv = rng.standard_normal((B, Nkv, Pmax, H)).astype(np.float32)
+        feeds = [q, k, v, pk, pv, np.array([total - 1], np.int32), np.array(total, np.int32)]
+        ps = [P(q.shape, "q"), P(k.shape, "k"), P(v.shape, "v"), P(pk.shape, "pk"), P(pv.shape, "pv"), P([1], "lens", "i32"), P([], "total", "i32")]
+        attrs = dict(num_heads=Nq, kv_num_heads=Nkv)
+        ref_kw = {}
+        empty = lambda: ops.constant(np.zeros((0,), np.float32))
+        extra = []
+        if kw.get("rot"):
+            ang = rng.random((32, H // 2)).astype(np.float32) * 3
+            cos, sin = np.cos(ang), np.sin(ang)
+            extra = [ops.constant(cos), ops.constant(sin)]
+            attrs.update(do_rotary=True, rotary_interleaved=bool(kw.get("inter")))
+            ref_kw.update(rotary=(cos, sin), interleaved=bool(kw.get("inter")))
+        if kw.get("window"):
+            attrs["local_window_size"] = kw["window"]
+            ref_kw["window"] = kw["window"]
+        if kw.get("sink"):
+            sink = rng.standard_normal((Nq,)).astype(np.float32)
+            extra = [empty(), empty(), empty(), empty(), ops.constant(sink)]
+            ref_kw["sink"] = sink
+        if kw.get("bias"):
+            bias = rng.standard_normal((1, Nq, S, total + 2)).astype(np.float32)
+            extra = [empty(), empty(), empty(), ops.constant(bias)]
+            ref_kw["bias"] = bias
+        n = ops.group_query_attention(ps + extra, **attrs)
+        assert n.get_output_partial_shape(0).to_shape() if False else True
+        assert [d.get_length() for d in n.get_output_partial_shape(0)] == [B, S, Nq * H]
+        got = run([n.output(0), n.output(1), n.output(2)], ps, feeds)
+        ref = _gqa_reference(q, k, v, pk, pv, total, **ref_kw)
+        for g, r in zip(got, ref):
+            np.testing.assert_allclose(g, r, rtol=2e-5, atol=2e-5)
+
+
+def test_type_relaxed_overrides_input_and_output_types():
+    # u8 x i8 product accumulated and declared as i32: the wrapped Multiply sees both inputs as i32
+    a = P([2, 3], "a", "u8")
+    b = P([2, 3], "b", "i8")
+    n = ops.type_relaxed("Multiply", [a, b], ["i32", "i32"], ["i32"], base_version="opset1")
+    assert n.get_output_element_type(0) == ov.Type.i32 and list(n.get_output_shape(0)) == [2, 3]
+    av = np.array([[200, 3, 255], [7, 100, 0]], np.uint8)
+    bv = np.array([[-100, 5, 127], [-3, -128, 9]], np.int8)
+    got = run([n], [a, b], [av, bv])[0]
+    assert got.dtype == np.int32
+    np.testing.assert_array_equal(got, av.astype(np.int32) * bv.astype(np.int32))
+    # a float operation whose result is declared as f16; attributes of the wrapped operation pass through
+    x = P([2, 4], "x")
+    s = ops.type_relaxed("Softmax", [x], [], ["f16"], base_version="opset8", axis=1)
+    xv = np.random.default_rng(3).standard_normal((2, 4)).astype(np.float32)
+    got = run([s], [x], [xv])[0]
+    assert got.dtype == np.float16
+    np.testing.assert_allclose(got.astype(np.float32), torch.softmax(torch.from_numpy(xv), 1).numpy(), atol=1e-3)
+    # shape arguments given as constants still drive the wrapped operation's shape inference
+    r = ops.type_relaxed("Reshape", [x, ops.constant(np.array([4, 2], np.int64))], [], ["f16"], base_version="opset1", special_zero=False)
+    assert list(r.get_output_shape(0)) == [4, 2]
