@@ -116,6 +116,14 @@ int ovb_rmsnorm(const void* x, const void* residual, const void* gamma, void* y,
                 int cols, float eps, ovb_stream_t stream);
 int ovb_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* y, int rows,
                   int cols, float eps, int is_f16, ovb_stream_t stream);
+// Linear recurrences (fp32, contiguous). `state` is read, advanced over the L tokens of every sequence and written back.
+// Selective state-space scan: A [H], dt [B, L, H], Bm / Cm [B, L, G, S], x / y [B, L, H, P], state [B, H, P, S]; S <= 256.
+int ovb_selective_ssm(const float* A, const float* dt, const float* Bm, const float* x, const float* Cm, float* state, float* y, int B, int L, int H, int P,
+                      int G, int S, ovb_stream_t stream);
+// Gated delta rule: q / k [B, L, Hq, Dk] (q scaled, both normalised by the caller where the layer asks for it), v / y [B, L, Hv, Dv],
+// gate / beta [B, L, Hv], state [B, Hv, Dk, Dv]; Dk <= 256.
+int ovb_gated_delta_rule(const float* q, const float* k, const float* v, const float* gate, const float* beta, float* state, float* y, int B, int L, int Hq,
+                         int Hv, int Dk, int Dv, ovb_stream_t stream);
 // out[t, :] = silu(gu[t, :F]) * gu[t, F:2F]
 int ovb_silu_mul(const void* gu, void* out, int rows, int F, ovb_stream_t stream);
 /* The same over the first min(*nrows, rows) rows; nrows is device memory written by an earlier kernel of the stream. */

@@ -159,9 +159,35 @@ def bench_im2col(a) -> dict:
             "gbs": (B * H * H * pw.K * 2 * 2 + x.numel() * 2) / ms / 1e6}
 
 
+def bench_ssm(a) -> dict:
+    """Selective state-space scan: --B sequences of --ctx tokens, --Hq heads of width --K (head_dim), state size --N, 8 groups."""
+    from . import cuda as K
+    B, L, H, P, S, G = a.B, a.ctx, a.Hq, a.K, a.N, min(8, a.Hq)
+    A = -torch.rand(H, device="cuda")
+    dt, x = torch.rand(B, L, H, device="cuda") * 0.1, torch.randn(B, L, H, P, device="cuda")
+    Bm, Cm, st = torch.randn(B, L, G, S, device="cuda"), torch.randn(B, L, G, S, device="cuda"), torch.randn(B, H, P, S, device="cuda")
+    ms = timeit(lambda: K.selective_ssm(A, dt, Bm, x, Cm, st), a.iters, a.warmup)
+    nbytes = 4 * (dt.numel() + 2 * x.numel() + Bm.numel() + Cm.numel() + 3 * st.numel())      # the wrapper clones the state: read, write, read / write
+    return {"kernel": "selective_ssm", "B": B, "L": L, "H": H, "P": P, "S": S, "ms": ms, "gbs": nbytes / ms / 1e6,
+            "tokens_per_s": B * L / ms * 1e3, "gflops": 6.0 * B * L * H * P * S / ms / 1e6}
+
+
+def bench_gdn(a) -> dict:
+    """Gated delta rule: --B sequences of --ctx tokens, --Hkv key heads and --Hq value heads, key width --K, value width --N."""
+    from . import cuda as K
+    B, L, Hq, Hv, Dk, Dv = a.B, a.ctx, a.Hkv, a.Hq, a.K, a.N
+    q, k = torch.randn(B, L, Hq, Dk, device="cuda") / Dk ** 0.5, torch.nn.functional.normalize(torch.randn(B, L, Hq, Dk, device="cuda"), dim=-1)
+    v, st = torch.randn(B, L, Hv, Dv, device="cuda"), torch.zeros(B, Hv, Dk, Dv, device="cuda")
+    g, beta = -torch.rand(B, L, Hv, device="cuda"), torch.rand(B, L, Hv, device="cuda")
+    ms = timeit(lambda: K.gated_delta_rule(q, k, v, g, beta, st), a.iters, a.warmup)
+    nbytes = 4 * (2 * q.numel() + 2 * v.numel() + 2 * g.numel() + 3 * st.numel())
+    return {"kernel": "gated_delta_rule", "B": B, "L": L, "Hq": Hq, "Hv": Hv, "Dk": Dk, "Dv": Dv, "ms": ms, "gbs": nbytes / ms / 1e6,
+            "tokens_per_s": B * L / ms * 1e3, "gflops": 7.0 * B * L * Hv * Dk * Dv / ms / 1e6}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "rope", "silu", "sample", "conv"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "rmsnorm", "rope", "silu", "sample", "conv", "ssm", "gdn"])
     ap.add_argument("--T", type=int, default=64)
     ap.add_argument("--N", type=int, default=4096)
     ap.add_argument("--K", type=int, default=4096)
@@ -179,7 +205,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
     r = {"gemm": bench_gemm, "attention": bench_attention, "rmsnorm": bench_rmsnorm, "rope": bench_rope, "silu": bench_silu,
-         "sample": bench_sample, "conv": bench_im2col}[a.kernel](a)
+         "sample": bench_sample, "conv": bench_im2col, "ssm": bench_ssm, "gdn": bench_gdn}[a.kernel](a)
     pk = _peaks()
     if pk["hbm_gbs"]:
         r["frac_of_%s_hbm" % pk["source"]] = r["gbs"] / pk["hbm_gbs"]

@@ -286,6 +286,32 @@ def rmsnorm(x, gamma, eps, residual=None, out=None, residual_out=None):
     return out
 
 
+def selective_ssm(A, dt, Bm, x, Cm, state):
+    """Selective state-space scan over fp32 tensors: A [H], dt [B, L, H], Bm / Cm [B, L, G, S], x [B, L, H, P], state [B, H, P, S].
+    Returns (y [B, L, H, P], new state); ``state`` itself is left as it was."""
+    B, L, H, P = x.shape
+    G, S = Bm.shape[2], Bm.shape[3]
+    args = [t.float().contiguous() for t in (A, dt, Bm, x, Cm)]
+    new_state = state.float().contiguous().clone()
+    y = torch.empty((B, L, H, P), dtype=torch.float32, device=x.device)
+    _check(lib().ovb_selective_ssm(*(C.c_void_p(t.data_ptr()) for t in args), C.c_void_p(new_state.data_ptr()), C.c_void_p(y.data_ptr()),
+                                   C.c_int(B), C.c_int(L), C.c_int(H), C.c_int(P), C.c_int(G), C.c_int(S), C.c_void_p(_stream())), "ovb_selective_ssm")
+    return y, new_state
+
+
+def gated_delta_rule(q, k, v, gate, beta, state):
+    """Gated delta rule over fp32 tensors: q / k [B, L, Hq, Dk] (already scaled / normalised), v [B, L, Hv, Dv], gate / beta [B, L, Hv],
+    state [B, Hv, Dk, Dv]. Returns (y [B, L, Hv, Dv], new state)."""
+    B, L, Hq, Dk = q.shape
+    Hv, Dv = v.shape[2], v.shape[3]
+    args = [t.float().contiguous() for t in (q, k, v, gate, beta)]
+    new_state = state.float().contiguous().clone()
+    y = torch.empty((B, L, Hv, Dv), dtype=torch.float32, device=q.device)
+    _check(lib().ovb_gated_delta_rule(*(C.c_void_p(t.data_ptr()) for t in args), C.c_void_p(new_state.data_ptr()), C.c_void_p(y.data_ptr()),
+                                      C.c_int(B), C.c_int(L), C.c_int(Hq), C.c_int(Hv), C.c_int(Dk), C.c_int(Dv), C.c_void_p(_stream())), "ovb_gated_delta_rule")
+    return y, new_state
+
+
 def layernorm(x, gamma, beta, eps, residual=None, out=None):
     rows, cols = x.shape
     if out is None:

@@ -1062,6 +1062,34 @@ def _rope(n, ins, ctx):
     return [torch.cat([out, rest], -1) if nd != D else out]
 
 
+@op("SelectiveSSM")
+def _selective_ssm(n, ins, ctx):
+    """A [H], dt [B, L, H], B [B, L, G, S], x [B, L, H, P], C [B, L, G, S], state [B, H, P, S] -> y, new state."""
+    if ctx.K is None or ins[2].shape[-1] > 256:
+        return NotImplemented
+    A, dt, Bm, x, Cm, state = _same_device(ctx, ins)
+    y, new_state = ctx.K.selective_ssm(A, dt, Bm, x, Cm, state)
+    return [y.to(x.dtype), new_state.to(state.dtype)]
+
+
+@op("GatedDeltaNet")
+def _gated_delta_net(n, ins, ctx):
+    """query / key [B, L, Hq, Dk], value [B, L, Hv, Dv], state [B, Hv, Dk, Dv], gate / beta [B, L, Hv] -> y, new state."""
+    if ctx.K is None or ins[0].shape[-1] > 256:
+        return NotImplemented
+    q, k, v, state, gate, beta = _same_device(ctx, ins)
+    at = n.get_attributes()
+    qf, kf = q.float(), k.float()
+    scale = float(q.shape[-1]) ** -0.5
+    if at.get("fuse_qk_l2norm"):
+        qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + float(at.get("q_l2_norm_eps", 1e-6))) * scale
+        kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + float(at.get("k_l2_norm_eps", 1e-6)))
+    else:
+        qf = qf * scale
+    y, new_state = ctx.K.gated_delta_rule(qf, kf, v, gate, beta, state)
+    return [y.to(v.dtype), new_state.to(state.dtype)]
+
+
 @op("ReadValue")
 def _read_value(n, ins, ctx):
     vid = n.get_attribute("variable_id")
@@ -1241,6 +1269,8 @@ class GraphProgram:
                 ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                 ev[0].record()
             values[i] = impl(n, ins, ctx) if impl is not None else self._host_eval(n, ins)
+            if values[i] is NotImplemented:      # a device implementation that does not serve these sizes
+                values[i] = self._host_eval(n, ins)
             if profile is not None:
                 if ctx.on_gpu:
                     ev[1].record()

@@ -1,6 +1,7 @@
 """Recurrent-state operations (selective SSM, gated delta rule, paged forms, paged causal conv, KV reorder, AUGRU) against
 PyTorch restatements of their specifications."""
 import numpy as np
+import pytest
 import torch
 
 import openvino_b200 as ov
@@ -260,3 +261,39 @@ def test_paged_attention_scores_and_key_rerotation():
         assert res[1].shape == (past + new,)
         if score_win == 2:
             assert abs(res[1].sum() - 2 * Hq) < 1e-4           # two voting queries, every head's weights sum to one
+
+
+@pytest.mark.gpu
+def test_recurrent_device_kernels_match_the_restatements():
+    """SelectiveSSM and GatedDeltaNet on the CUDA device run the register-resident scan kernels (csrc/cuda/recurrent.cu);
+    sizes are those of a Mamba-2 block (state 128) and a gated-delta layer (key width 128), plus ragged ones."""
+    from openvino_b200.ops import cuda as K
+    torch.manual_seed(5)
+    dev = "cuda:0"
+    for b, L, H, Pd, G, S in ((2, 33, 8, 64, 2, 128), (1, 7, 3, 5, 1, 40), (1, 4, 2, 3, 2, 200)):
+        A = -torch.rand(H)
+        dt, B, x, C, st = torch.rand(b, L, H) * 0.5, torch.randn(b, L, G, S), torch.randn(b, L, H, Pd), torch.randn(b, L, G, S), torch.randn(b, H, Pd, S)
+        ry, rs = torch_ssm(A, dt, B, x, C, st)
+        y, s2 = K.selective_ssm(*(t.to(dev) for t in (A, dt, B, x, C, st)))
+        torch.testing.assert_close(y.cpu(), ry, rtol=2e-4, atol=2e-4)
+        torch.testing.assert_close(s2.cpu(), rs, rtol=2e-4, atol=2e-4)
+        # through the device plugin's graph interpreter
+        ps = [P(t.shape, "i%d" % i) for i, t in enumerate((A, dt, B, x, C, st))]
+        n = ops.selective_ssm(*ps)
+        cm = ov.compile_model(ov.Model([n.output(0), n.output(1)], ps, "ssm"), "CUDA", {"INFERENCE_PRECISION_HINT": "f32"})
+        res = cm([t.numpy() for t in (A, dt, B, x, C, st)])
+        np.testing.assert_allclose(res[0], ry.numpy(), rtol=2e-4, atol=2e-4)
+        np.testing.assert_allclose(res[1], rs.numpy(), rtol=2e-4, atol=2e-4)
+    for b, L, Hq, Hv, Dk, Dv in ((2, 19, 4, 8, 128, 128), (1, 6, 2, 4, 24, 5), (1, 3, 1, 2, 160, 9)):
+        q, k, v = torch.randn(b, L, Hq, Dk), torch.randn(b, L, Hq, Dk), torch.randn(b, L, Hv, Dv)
+        st, g, beta = torch.randn(b, Hv, Dk, Dv) * 0.1, -torch.rand(b, L, Hv), torch.rand(b, L, Hv)
+        for norm in (True, False):
+            if not norm:
+                k = k / Dk ** 0.5            # keeps the un-normalised recurrence bounded
+            ry, rs = torch_gdn(q, k, v, st, g, beta, norm)
+            ps = [P(t.shape, "g%d" % i) for i, t in enumerate((q, k, v, st, g, beta))]
+            n = ops.gated_delta_net(*ps, fuse_qk_l2norm=norm)
+            cm = ov.compile_model(ov.Model([n.output(0), n.output(1)], ps, "gdn"), "CUDA", {"INFERENCE_PRECISION_HINT": "f32"})
+            res = cm([t.numpy() for t in (q, k, v, st, g, beta)])
+            np.testing.assert_allclose(res[0], ry.numpy(), rtol=5e-4, atol=5e-4)
+            np.testing.assert_allclose(res[1], rs.numpy(), rtol=5e-4, atol=5e-4)
