@@ -150,7 +150,61 @@ bool eval_paged_attention(const Node& n, Ins in, Outs out, EvalContext&) {
 // RoPE(x, cos, sin[, position ids]); half-rotate (LLaMA / GPT-NeoX) and interleaved (GPT-J) forms.
 // x is [B, H, L, S] ([B, L, H, S] with input_trans0213); cos/sin broadcast to [B, 1, L, rotary_ndims]
 // (tables of rotary_ndims or rotary_ndims/2 entries per position are both accepted).
+// Fused-QKV forms. X is [a, b, W]; the head block [slice_start, slice_stop) of the last axis holds head_cnt heads of head_size.
+// Qwen: a = batch, b = tokens; half rotation by tables [1, positions, 1, S] whose LAST b rows belong to these tokens (the
+// tables are cut to the present length) unless position ids (input 3) name the rows.
+// ChatGLM: a = tokens, b = batch; neighbouring pairs of the first rotary_ndims values rotate by a cache [a, b or 1, 1, rot / 2, 2].
+static bool eval_rope_fused_qkv(const Node& n, Ins in, Outs out) {
+    const Tensor& X = in[0];
+    OVC_CHECK(X.shape.size() == 3, n.description() << ": the fused QKV input must be 3-D");
+    const int64_t D0 = X.shape[0], D1 = X.shape[1], W = X.shape[2], H = n.attr_int("head_cnt"), S = n.attr_int("head_size"), s0 = n.attr_int("slice_start");
+    OVC_CHECK(H > 0 && S > 0 && s0 >= 0 && s0 + H * S <= W, n.description() << ": heads [" << s0 << ", " << s0 + H * S << ") do not fit the projection of width " << W);
+    int64_t rot = n.attr_int("rotary_ndims");
+    if (rot <= 0) rot = S;
+    const int64_t half = rot / 2;
+    const auto x = to_f32(X), c = to_f32(in[1]), s = to_f32(in[2]);
+    std::vector<float> o((size_t)(D0 * D1 * H * S));
+    if (n.attr_bool("is_qwen")) {
+        const int64_t cw = in[1].shape.back(), rows = in[1].numel() / std::max<int64_t>(cw, 1);
+        OVC_CHECK(cw == rot, n.description() << ": tables must hold " << rot << " values per position");
+        std::vector<int64_t> pos;
+        if (in.size() > 3 && in[3].numel() > 0) pos = to_i64(in[3]);
+        for (int64_t b = 0; b < D0; ++b) for (int64_t l = 0; l < D1; ++l) {
+            int64_t row = rows >= D1 ? rows - D1 + l : std::min(l, rows - 1);
+            if (!pos.empty()) row = pos[(size_t)((b * D1 + l) % (int64_t)pos.size())];
+            OVC_CHECK(row >= 0 && row < rows, n.description() << ": position " << row << " outside the tables of " << rows << " rows");
+            for (int64_t h = 0; h < H; ++h) {
+                const float* xp = x.data() + (b * D1 + l) * W + s0 + h * S;
+                float* op = o.data() + ((b * D1 + l) * H + h) * S;
+                for (int64_t i = 0; i < half; ++i) {
+                    op[i] = xp[i] * c[(size_t)(row * cw + i)] - xp[i + half] * s[(size_t)(row * cw + i)];
+                    op[i + half] = xp[i + half] * c[(size_t)(row * cw + i + half)] + xp[i] * s[(size_t)(row * cw + i + half)];
+                }
+                for (int64_t i = rot; i < S; ++i) op[i] = xp[i];
+            }
+        }
+    } else {
+        const Shape& cs = in[1].shape;
+        OVC_CHECK(cs.size() == 5 && cs[0] >= D0 && cs[3] == half && cs[4] == 2, n.description() << ": the cache must be [tokens, batch or 1, 1, " << half << ", 2]");
+        const int64_t Bc = cs[1];
+        for (int64_t l = 0; l < D0; ++l) for (int64_t b = 0; b < D1; ++b) for (int64_t h = 0; h < H; ++h) {
+            const float* xp = x.data() + (l * D1 + b) * W + s0 + h * S;
+            float* op = o.data() + ((l * D1 + b) * H + h) * S;
+            const float* cp = c.data() + ((l * Bc + (Bc == 1 ? 0 : b)) * half) * 2;
+            for (int64_t i = 0; i < half; ++i) {
+                const float x0 = xp[2 * i], x1 = xp[2 * i + 1], cc = cp[2 * i], ss = cp[2 * i + 1];
+                op[2 * i] = x0 * cc - x1 * ss;
+                op[2 * i + 1] = x1 * cc + x0 * ss;
+            }
+            for (int64_t i = rot; i < S; ++i) op[i] = xp[i];
+        }
+    }
+    out[0] = from_f32(X.et, Shape{D0, D1, H, S}, o);
+    return true;
+}
+
 bool eval_rope(const Node& n, Ins in, Outs out, EvalContext&) {
+    if (n.attr_bool("is_qwen") || n.attr_bool("is_chatglm")) return eval_rope_fused_qkv(n, in, out);
     const Tensor& X = in[0];
     OVC_CHECK(X.shape.size() == 4, n.description() << ": input must be 4-D");
     const bool it = n.attr_bool("input_trans0213"), ot = n.attr_bool("output_trans0213");

@@ -1092,6 +1092,11 @@ void register_all_ops() {
              Ab("use_rope_cache", false), Ab("is_ltx_video", false), Ai("head_cnt", 0), Ai("head_size", 0), Ai("gather_position_arg_id", 0)},
             [](Node& n) {
                 PShape s = n.in_shape(0);
+                if (n.attr_bool("is_qwen") || n.attr_bool("is_chatglm")) {      // fused QKV [a, b, W] -> [a, b, heads, head size]
+                    const bool r3 = !s.rank_dynamic && s.rank() == 3;
+                    n.set_output(0, n.in_et(0), PShape({r3 ? s.dims[0] : Dim::dynamic(), r3 ? s.dims[1] : Dim::dynamic(), Dim(n.attr_int("head_cnt")), Dim(n.attr_int("head_size"))}));
+                    return;
+                }
                 if (!s.rank_dynamic && s.rank() == 4 && (n.attr_bool("input_trans0213") != n.attr_bool("output_trans0213"))) std::swap(s.dims[1], s.dims[2]);
                 if (!s.rank_dynamic && n.attr_int("slice_stop") > n.attr_int("slice_start")) s.dims.back() = Dim(n.attr_int("slice_stop") - n.attr_int("slice_start"));
                 n.set_output(0, n.in_et(0), s);

@@ -439,6 +439,8 @@ std::shared_ptr<MatcherPass> make_rms_fusion();
 std::shared_ptr<MatcherPass> make_rope_fusion();
 std::shared_ptr<MatcherPass> make_rope_fusion_interleaved();
 std::shared_ptr<MatcherPass> make_rope_fusion_partial();
+std::shared_ptr<MatcherPass> make_rope_fusion_qwen();
+std::shared_ptr<MatcherPass> make_rope_fusion_chatglm();
 std::shared_ptr<MatcherPass> make_lora_fusion();
 std::shared_ptr<MatcherPass> make_matmul_to_fc();
 std::shared_ptr<MatcherPass> make_fc_to_compressed();
@@ -464,12 +466,14 @@ std::shared_ptr<ModelPass> make_pass(const std::string& name, const AttrMap& opt
     if (name == "CompressWeights") { const std::string mode = opt_s("mode", "int4_asym"); const int64_t gs = opt_i("group_size", 128); const bool all = opt_i("all_layers", 0) != 0;
         return lam([mode, gs, all](const ModelPtr& m) { return compress_weights(m, mode, gs, 1.0, all); }); }
     if (name == "RMSFusion") return wrap(make_rms_fusion());
-    if (name == "RoPEFusion") {     // half-rotate, interleaved, then the partial-rotary wrapper around either
+    if (name == "RoPEFusion") {     // half-rotate, interleaved, the partial-rotary wrapper around either, then the fused-QKV forms of Qwen and ChatGLM
         auto g = std::make_shared<GraphRewrite>();
         g->name = name;
         g->add(make_rope_fusion());
         g->add(make_rope_fusion_interleaved());
         g->add(make_rope_fusion_partial());
+        g->add(make_rope_fusion_qwen());
+        g->add(make_rope_fusion_chatglm());
         return g;
     }
     if (name == "LoraSubgraphFusion") return wrap(make_lora_fusion());

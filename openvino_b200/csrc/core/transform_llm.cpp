@@ -119,6 +119,9 @@ std::shared_ptr<MatcherPass> make_rope_fusion() {
             return false;
         };
         if (!check_slice(m.node(slice_hi), half, S) || !check_slice(m.node(slice_lo), 0, half)) return false;
+        // a table laid out [1, positions, 1, S] belongs to x in [B, L, H, S] order: RoPE reads x as [B, H, L, S], so leave that form alone
+        const PShape& cshape = m.at(cos).shape();
+        if (!cshape.rank_dynamic && cshape.rank() == 4 && cshape.dims[2].is_static() && cshape.dims[2].lo == 1 && !(cshape.dims[1].is_static() && cshape.dims[1].lo == 1)) return false;
         if (m.node(slice_lo)->input(2).node->is_constant()) { std::vector<int64_t> ve; get_constant_ints(m.node(slice_lo)->input(2), ve); if (ve[0] != half) return false; }
         if (m.node(cat)->attr_int("axis") != -1 && m.node(cat)->attr_int("axis") != 3) return false;
         auto rope = op("RoPE", {xin, m.at(cos), m.at(sin)}, {{"rotary_ndims", Attr::Int(S)}, {"head_size", Attr::Int(S)},
@@ -196,6 +199,118 @@ std::shared_ptr<MatcherPass> make_rope_fusion_partial() {
         if (cat_axis != -1 && cat_axis != 3) return false;
         auto rope = op("RoPE", {xin, r->input(1), r->input(2)}, {{"is_interleaved", Attr::Bool(r->attr_bool("is_interleaved"))}, {"rotary_ndims", Attr::Int(rot)},
                                                                 {"head_size", Attr::Int(S)}, {"head_cnt", Attr::Int(r->attr_int("head_cnt"))}});
+        copy_runtime_info(m.matched_nodes(), {rope});
+        replace_node(m.match_root(), rope);
+        return true;
+    });
+}
+
+// Where one output of a VariadicSplit over the last axis of a fused QKV projection starts and stops
+static bool split_range(const NodePtr& split, size_t index, int64_t& start, int64_t& stop) {
+    std::vector<int64_t> axis, lens;
+    if (!get_constant_ints(split->input(1), axis) || !get_constant_ints(split->input(2), lens) || axis.size() != 1 || index >= lens.size()) return false;
+    if (axis[0] != 2 && axis[0] != -1) return false;
+    start = 0;
+    for (size_t i = 0; i < index; ++i) { if (lens[i] < 0) return false; start += lens[i]; }
+    if (lens[index] < 0) return false;
+    stop = start + lens[index];
+    return true;
+}
+
+// RoPE over a fused QKV projection, Qwen form (RoPEFusionQwen of fuse_rotary_positional_embeddings.cpp in the reference):
+//   x = reshape(variadic_split(qkv [B, L, W], -1)[i], [B, L, H, S]);  h = split(reshape(x, [B, L, H, 2, S / 2]), -2)
+//   x * cos + concat(squeeze(-h[1]), squeeze(h[0]), -1) * sin,  cos / sin [1, positions, 1, S]
+//   ->  RoPE(qkv, cos, sin) {is_qwen, slice_start / stop, head_cnt, head_size}, output [B, L, H, S]
+std::shared_ptr<MatcherPass> make_rope_fusion_qwen() {
+    auto qkv = any_input(rank_equals(3));
+    auto split = wrap_type({"VariadicSplit"}, {qkv, wrap_const(), wrap_const()});
+    auto x = wrap_type({"Reshape"}, {split, any_input()}, rank_equals(4));
+    auto cos = any_input(rank_equals(4));
+    auto sin = any_input(rank_equals(4));
+    auto halves = wrap_type({"Reshape"}, {x, any_input()}, rank_equals(5));
+    auto hi = wrap_type({"Split"}, {halves, wrap_const()});
+    auto lo = wrap_type({"Split"}, {halves, wrap_const()});
+    auto neg = any_of({wrap_type({"Multiply"}, {hi, wrap_const(scalar_eq(-1.0))}), wrap_type({"Negative"}, {hi})});
+    auto sq_neg = wrap_type({"Squeeze", "Reshape"}, {neg, any_input()});
+    auto sq_lo = wrap_type({"Squeeze", "Reshape"}, {lo, any_input()});
+    auto cat = wrap_type({"Concat"}, {sq_neg, sq_lo});
+    auto add = wrap_type({"Add"}, {wrap_type({"Multiply"}, {x, cos}), wrap_type({"Multiply"}, {cat, sin})});
+    return std::make_shared<MatcherPass>("RoPEFusionQwen", add, [=](Matcher& m) {
+        const PShape& xs = m.at(x).shape();
+        if (!xs.dims[2].is_static() || !xs.dims[3].is_static() || xs.dims[3].lo % 2) return false;
+        const int64_t H = xs.dims[2].lo, S = xs.dims[3].lo;
+        int64_t start = 0, stop = 0;
+        if (!split_range(m.node(split), m.at(split).index, start, stop) || stop - start != H * S) return false;
+        if (m.node(hi) != m.node(lo) || m.at(hi).index != 1 || m.at(lo).index != 0 || m.node(hi)->attr_int("num_splits") != 2) return false;
+        std::vector<int64_t> ax;
+        if (!get_constant_ints(m.node(hi)->input(1), ax) || ax.size() != 1 || (ax[0] != -2 && ax[0] != 3)) return false;
+        const PShape& hs = m.at(halves).shape();
+        if (!hs.dims[3].is_static() || hs.dims[3].lo != 2 || !hs.dims[4].is_static() || hs.dims[4].lo != S / 2) return false;
+        const int64_t cat_axis = m.node(cat)->attr_int("axis");
+        if (cat_axis != -1 && cat_axis != 3) return false;
+        if (!(m.at(cat).shape().rank() == 4)) return false;
+        for (const PatternPtr& t : {cos, sin}) {
+            const PShape& ts = m.at(t).shape();
+            if (!(ts.dims[2].is_static() && ts.dims[2].lo == 1 && ts.dims[3].is_static() && ts.dims[3].lo == S)) return false;
+        }
+        auto rope = op("RoPE", {m.at(qkv), m.at(cos), m.at(sin)},
+                       {{"is_qwen", Attr::Bool(true)}, {"slice_start", Attr::Int(start)}, {"slice_stop", Attr::Int(stop)}, {"rotary_ndims", Attr::Int(S)},
+                        {"head_cnt", Attr::Int(H)}, {"head_size", Attr::Int(S)}});
+        copy_runtime_info(m.matched_nodes(), {rope});
+        replace_node(m.match_root(), rope);
+        return true;
+    });
+}
+
+// RoPE over a fused QKV projection, ChatGLM form (RoPEFusionChatGLM in the reference): pairs of neighbouring elements of the
+// first `rot` values of every head are rotated by a combined cache [L, B or 1, 1, rot / 2, 2] (cos, sin), the rest passes through:
+//   x = reshape(variadic_split(qkv [L, B, W], -1)[i], [L, B, H, S]);  p = reshape(x[..., :rot], [L, B, H, rot / 2, 2])
+//   concat(reshape(stack(p0 * c - p1 * s, p1 * c + p0 * s), [L, B, H, rot]), x[..., rot:], -1)
+//   ->  RoPE(qkv, cache, cache) {is_chatglm, rotary_ndims, slice_start / stop, head_cnt, head_size}, output [L, B, H, S]
+std::shared_ptr<MatcherPass> make_rope_fusion_chatglm() {
+    auto qkv = any_input(rank_equals(3));
+    auto split = wrap_type({"VariadicSplit"}, {qkv, wrap_const(), wrap_const()});
+    auto x = wrap_type({"Reshape"}, {split, any_input()}, rank_equals(4));
+    auto cache = any_input(rank_equals(5));
+    auto head = wrap_type({"Slice"}, {x, any_input(), any_input(), any_input(), any_input()});
+    auto tail = wrap_type({"Slice"}, {x, any_input(), any_input(), any_input(), any_input()});
+    auto pairs = wrap_type({"Reshape"}, {head, any_input()}, rank_equals(5));
+    auto p0 = wrap_type({"Gather"}, {pairs, wrap_const(scalar_eq(0.0)), wrap_const()});
+    auto p1 = wrap_type({"Gather"}, {pairs, wrap_const(scalar_eq(1.0)), wrap_const()});
+    auto c = wrap_type({"Gather"}, {cache, wrap_const(scalar_eq(0.0)), wrap_const()});
+    auto s = wrap_type({"Gather"}, {cache, wrap_const(scalar_eq(1.0)), wrap_const()});
+    auto o0 = wrap_type({"Subtract"}, {wrap_type({"Multiply"}, {p0, c}), wrap_type({"Multiply"}, {p1, s})});
+    auto o1 = wrap_type({"Add"}, {wrap_type({"Multiply"}, {p1, c}), wrap_type({"Multiply"}, {p0, s})});
+    auto stack = wrap_type({"Concat"}, {wrap_type({"Unsqueeze"}, {o0, any_input()}), wrap_type({"Unsqueeze"}, {o1, any_input()})});
+    auto flat = wrap_type({"Reshape"}, {stack, any_input()}, rank_equals(4));
+    auto root = wrap_type({"Concat"}, {flat, tail});
+    return std::make_shared<MatcherPass>("RoPEFusionChatGLM", root, [=](Matcher& m) {
+        const PShape& xs = m.at(x).shape();
+        if (!xs.dims[2].is_static() || !xs.dims[3].is_static()) return false;
+        const int64_t H = xs.dims[2].lo, S = xs.dims[3].lo;
+        int64_t start = 0, stop = 0;
+        if (!split_range(m.node(split), m.at(split).index, start, stop) || stop - start != H * S) return false;
+        const PShape& ps = m.at(pairs).shape();
+        if (!ps.dims[3].is_static() || !ps.dims[4].is_static() || ps.dims[4].lo != 2) return false;
+        const int64_t rot = 2 * ps.dims[3].lo;
+        auto range = [&](const NodePtr& sl, int64_t b, int64_t e) {
+            std::vector<int64_t> vb, ve, vs, va;
+            if (!get_constant_ints(sl->input(1), vb) || !get_constant_ints(sl->input(2), ve) || !get_constant_ints(sl->input(3), vs) ||
+                !get_constant_ints(sl->input(4), va)) return false;
+            return vb.size() == 1 && vb[0] == b && (ve[0] == e || (e == S && ve[0] >= S)) && vs[0] == 1 && (va[0] == 3 || va[0] == -1);
+        };
+        if (rot <= 0 || rot > S || !range(m.node(head), 0, rot) || (rot < S && !range(m.node(tail), rot, S))) return false;
+        for (const PatternPtr& g : {p0, p1, c, s}) {
+            std::vector<int64_t> ax;
+            if (!get_constant_ints(m.node(g)->input(2), ax) || ax.size() != 1 || (ax[0] != -1 && ax[0] != 4)) return false;
+        }
+        const PShape& cs = m.at(cache).shape();
+        if (!(cs.dims[3].is_static() && cs.dims[3].lo == rot / 2 && cs.dims[4].is_static() && cs.dims[4].lo == 2 && cs.dims[2].is_static() && cs.dims[2].lo == 1)) return false;
+        const int64_t a0 = m.node(stack)->attr_int("axis"), a1 = m.node(root)->attr_int("axis");
+        if ((a0 != -1 && a0 != 4) || (a1 != -1 && a1 != 3)) return false;
+        auto rope = op("RoPE", {m.at(qkv), m.at(cache), m.at(cache)},
+                       {{"is_chatglm", Attr::Bool(true)}, {"is_interleaved", Attr::Bool(true)}, {"slice_start", Attr::Int(start)}, {"slice_stop", Attr::Int(stop)},
+                        {"rotary_ndims", Attr::Int(rot)}, {"head_cnt", Attr::Int(H)}, {"head_size", Attr::Int(S)}});
         copy_runtime_info(m.matched_nodes(), {rope});
         replace_node(m.match_root(), rope);
         return true;

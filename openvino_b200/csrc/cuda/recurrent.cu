@@ -1,9 +1,9 @@
 // Linear-recurrence layers of hybrid LLMs: the selective state-space scan (Mamba-2 form) and the gated delta rule
 // (Gated DeltaNet / Qwen3-Next linear attention). Both walk the tokens of a sequence in order with the recurrent state
-// of one head resident in registers: one warp owns one row (state-space) or one column (delta rule) of the state matrix,
-// its 32 lanes hold the row's elements, and the two dot products of a token are warp shuffles. The state is read from
-// and written to HBM once per launch; per token only the token's own vectors are read and one output element per warp is
-// written.
+// of one head resident in registers: one warp owns four rows (state-space) or four columns (delta rule) of the state
+// matrix, its 32 lanes hold the rows' elements, and the dot products of a token are warp shuffles (four sums share six
+// shuffles). The state is read from and written to HBM once per launch; the token vectors every row of a head shares are
+// staged in shared memory sixteen tokens at a time.
 //
 // Reference counterparts: the SelectiveSSM and GatedDeltaNet internal operations
 // (src/common/transformations/include/ov_ops/, executed by the CPU plugin's recurrent kernels).
@@ -15,92 +15,165 @@ namespace ovb {
 
 namespace {
 
-constexpr int REC_WARPS = 8;     // warps (state rows / columns) per CTA
+constexpr int REC_WARPS = 8;     // warps per CTA
+constexpr int REC_PER_WARP = 4;  // state rows (state-space) / columns (delta rule) per warp
+constexpr int REC_TILE = REC_WARPS * REC_PER_WARP;   // rows / columns of one head per CTA
+constexpr int REC_CHUNK = 16;    // tokens staged in shared memory at a time
 constexpr int REC_MAXV = 8;      // state elements per lane: state widths up to 256
 
-__device__ __forceinline__ float rec_warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+// Sums four per-lane values over the warp with 6 shuffles instead of 20: after each exchange a lane keeps only the values
+// its half is responsible for. The total of v0 ends in lanes 0-7, v1 in 16-23, v2 in 8-15, v3 in 24-31.
+__device__ __forceinline__ float rec_reduce4(float v0, float v1, float v2, float v3, int lane) {
+    const bool up16 = lane & 16, up8 = lane & 8;
+    float a = (up16 ? v1 : v0) + __shfl_xor_sync(0xffffffffu, up16 ? v0 : v1, 16);
+    float b = (up16 ? v3 : v2) + __shfl_xor_sync(0xffffffffu, up16 ? v2 : v3, 16);
+    float c = (up8 ? b : a) + __shfl_xor_sync(0xffffffffu, up8 ? a : b, 8);
+    c += __shfl_xor_sync(0xffffffffu, c, 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
 }
+// Lane that holds the total of value r after rec_reduce4, and the value index a lane holds
+__device__ __forceinline__ int rec_owner_lane(int r) { return ((r & 1) << 4) | ((r >> 1) << 3); }
+__device__ __forceinline__ int rec_owned_value(int lane) { return ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1); }
 
 // state[b, h, p, :] <- state * exp(A[h] * dt) + dt * B[b, t, g, :] * x[b, t, h, p];  y[b, t, h, p] = <state, C[b, t, g, :]>
+// One CTA owns REC_TILE rows p of one (b, h); the token vectors B, C (shared by all rows and by the heads of a group) are
+// staged in shared memory REC_CHUNK tokens at a time, so that they cross L2 once per CTA and not once per row.
 template <int NV>
 __global__ void __launch_bounds__(REC_WARPS * 32)
 selective_ssm_kernel(const float* __restrict__ A, const float* __restrict__ dt, const float* __restrict__ Bm, const float* __restrict__ x,
-                     const float* __restrict__ Cm, float* __restrict__ state, float* __restrict__ y, int rows, int L, int H, int P, int G, int S) {
-    const int row = blockIdx.x * REC_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= rows) return;
-    const int p = row % P, h = (row / P) % H, b = row / (P * H), g = h / (H / G);
-    float st[NV];
-    float* srow = state + (size_t)row * S;
+                     const float* __restrict__ Cm, float* __restrict__ state, float* __restrict__ y, int L, int H, int P, int G, int S) {
+    __shared__ float sB[REC_CHUNK][NV * 32], sC[REC_CHUNK][NV * 32], sX[REC_CHUNK][REC_TILE], sD[REC_CHUNK], sDA[REC_CHUNK];
+    const int bh = blockIdx.y, b = bh / H, h = bh % H, g = h / (H / G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, p0 = blockIdx.x * REC_TILE, pw = p0 + warp * REC_PER_WARP;
+    float st[REC_PER_WARP][NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) st[i] = (lane + 32 * i < S) ? srow[lane + 32 * i] : 0.f;
+    for (int r = 0; r < REC_PER_WARP; ++r)
+#pragma unroll
+        for (int i = 0; i < NV; ++i) st[r][i] = (pw + r < P && lane + 32 * i < S) ? state[((size_t)bh * P + pw + r) * S + lane + 32 * i] : 0.f;
     const float a = A[h];
-    for (int t = 0; t < L; ++t) {
-        const size_t tok = (size_t)b * L + t;
-        const float d = dt[tok * H + h], xv = x[(tok * H + h) * P + p];
-        const float dA = expf(a * d), dx = d * xv;
-        const float* bv = Bm + (tok * G + g) * S;
-        const float* cv = Cm + (tok * G + g) * S;
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int s = lane + 32 * i;
-            if (s < S) {
-                st[i] = st[i] * dA + bv[s] * dx;
-                acc += st[i] * cv[s];
-            }
+    for (int t0 = 0; t0 < L; t0 += REC_CHUNK) {
+        const int nt = min(REC_CHUNK, L - t0);
+        const size_t tok0 = (size_t)b * L + t0;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * NV * 32; idx += REC_WARPS * 32) {
+            const int tt = idx / (NV * 32), s = idx % (NV * 32);
+            sB[tt][s] = s < S ? Bm[((tok0 + tt) * G + g) * S + s] : 0.f;
+            sC[tt][s] = s < S ? Cm[((tok0 + tt) * G + g) * S + s] : 0.f;
         }
-        acc = rec_warp_sum(acc);
-        if (lane == 0) y[(tok * H + h) * P + p] = acc;
+        for (int idx = threadIdx.x; idx < nt * REC_TILE; idx += REC_WARPS * 32) {
+            const int tt = idx / REC_TILE, r = idx % REC_TILE;
+            sX[tt][r] = p0 + r < P ? x[((tok0 + tt) * H + h) * P + p0 + r] : 0.f;
+        }
+        if (threadIdx.x < nt) {
+            const float d = dt[(tok0 + threadIdx.x) * H + h];
+            sD[threadIdx.x] = d;
+            sDA[threadIdx.x] = expf(a * d);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float d = sD[tt], dA = sDA[tt];
+            float bv[NV], cv[NV], acc[REC_PER_WARP];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                bv[i] = sB[tt][lane + 32 * i] * d;
+                cv[i] = sC[tt][lane + 32 * i];
+            }
+#pragma unroll
+            for (int r = 0; r < REC_PER_WARP; ++r) {
+                const float xv = sX[tt][warp * REC_PER_WARP + r];
+                acc[r] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    st[r][i] = st[r][i] * dA + bv[i] * xv;
+                    acc[r] += st[r][i] * cv[i];
+                }
+            }
+            const float total = rec_reduce4(acc[0], acc[1], acc[2], acc[3], lane);
+            const int r = rec_owned_value(lane);
+            if ((lane & 7) == 0 && pw + r < P) y[((tok0 + tt) * H + h) * P + pw + r] = total;
+        }
     }
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
-        if (lane + 32 * i < S) srow[lane + 32 * i] = st[i];
+    for (int r = 0; r < REC_PER_WARP; ++r)
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (pw + r < P && lane + 32 * i < S) state[((size_t)bh * P + pw + r) * S + lane + 32 * i] = st[r][i];
 }
 
-// One value column iv of the state [Dk, Dv] of (b, hv):  S *= exp(g);  delta = (v - <S, k>) * beta;  S += k * delta;  y = <S, q>.
-// q arrives scaled (and normalised where the layer asks for it), k normalised likewise.
+// Value columns iv of the state [Dk, Dv] of (b, hv):  S *= exp(g);  delta = (v - <S, k>) * beta;  S += k * delta;  y = <S, q>.
+// q arrives scaled (and normalised where the layer asks for it), k normalised likewise. One CTA owns REC_TILE columns of one
+// (b, hv); q and k of the head (shared by all its columns) are staged in shared memory REC_CHUNK tokens at a time.
 template <int NV>
 __global__ void __launch_bounds__(REC_WARPS * 32)
 gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ gate,
-                        const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ y, int cols, int L, int Hq, int Hv, int Dk, int Dv) {
-    const int col = blockIdx.x * REC_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (col >= cols) return;
-    const int iv = col % Dv, h = (col / Dv) % Hv, b = col / (Dv * Hv), hq = h / (Hv / Hq);
-    float st[NV];
-    float* sbase = state + ((size_t)(b * Hv + h) * Dk) * Dv + iv;
+                        const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ y, int L, int Hq, int Hv, int Dk, int Dv) {
+    __shared__ float sQ[REC_CHUNK][NV * 32], sK[REC_CHUNK][NV * 32], sV[REC_CHUNK][REC_TILE], sG[REC_CHUNK], sBt[REC_CHUNK];
+    const int bh = blockIdx.y, b = bh / Hv, h = bh % Hv, hq = h / (Hv / Hq);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c0 = blockIdx.x * REC_TILE, cw = c0 + warp * REC_PER_WARP;
+    float st[REC_PER_WARP][NV];
+    float* sbase = state + (size_t)bh * Dk * Dv;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) st[i] = (lane + 32 * i < Dk) ? sbase[(size_t)(lane + 32 * i) * Dv] : 0.f;
-    for (int t = 0; t < L; ++t) {
-        const size_t tok = (size_t)b * L + t;
-        const float* qv = q + (tok * Hq + hq) * Dk;
-        const float* kv = k + (tok * Hq + hq) * Dk;
-        const float decay = expf(gate[tok * Hv + h]), bt = beta[tok * Hv + h], vv = v[(tok * Hv + h) * Dv + iv];
-        float kr[NV], qr[NV], mem = 0.f;
+    for (int c = 0; c < REC_PER_WARP; ++c)
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int d = lane + 32 * i;
-            kr[i] = d < Dk ? kv[d] : 0.f;
-            qr[i] = d < Dk ? qv[d] : 0.f;
-            st[i] *= decay;
-            mem += st[i] * kr[i];
+        for (int i = 0; i < NV; ++i) st[c][i] = (cw + c < Dv && lane + 32 * i < Dk) ? sbase[(size_t)(lane + 32 * i) * Dv + cw + c] : 0.f;
+    for (int t0 = 0; t0 < L; t0 += REC_CHUNK) {
+        const int nt = min(REC_CHUNK, L - t0);
+        const size_t tok0 = (size_t)b * L + t0;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * NV * 32; idx += REC_WARPS * 32) {
+            const int tt = idx / (NV * 32), d = idx % (NV * 32);
+            sQ[tt][d] = d < Dk ? q[((tok0 + tt) * Hq + hq) * Dk + d] : 0.f;
+            sK[tt][d] = d < Dk ? k[((tok0 + tt) * Hq + hq) * Dk + d] : 0.f;
         }
-        mem = rec_warp_sum(mem);
-        const float delta = (vv - mem) * bt;
-        float o = 0.f;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            st[i] += kr[i] * delta;
-            o += st[i] * qr[i];
+        for (int idx = threadIdx.x; idx < nt * REC_TILE; idx += REC_WARPS * 32) {
+            const int tt = idx / REC_TILE, c = idx % REC_TILE;
+            sV[tt][c] = c0 + c < Dv ? v[((tok0 + tt) * Hv + h) * Dv + c0 + c] : 0.f;
         }
-        o = rec_warp_sum(o);
-        if (lane == 0) y[(tok * Hv + h) * Dv + iv] = o;
+        if (threadIdx.x < nt) {
+            sG[threadIdx.x] = expf(gate[(tok0 + threadIdx.x) * Hv + h]);
+            sBt[threadIdx.x] = beta[(tok0 + threadIdx.x) * Hv + h];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float decay = sG[tt], bt = sBt[tt];
+            float kr[NV], qr[NV], mem[REC_PER_WARP], o[REC_PER_WARP];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                kr[i] = sK[tt][lane + 32 * i];
+                qr[i] = sQ[tt][lane + 32 * i];
+            }
+#pragma unroll
+            for (int c = 0; c < REC_PER_WARP; ++c) {
+                mem[c] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    st[c][i] *= decay;
+                    mem[c] += st[c][i] * kr[i];
+                }
+            }
+            const float m = rec_reduce4(mem[0], mem[1], mem[2], mem[3], lane);
+#pragma unroll
+            for (int c = 0; c < REC_PER_WARP; ++c) {
+                const float delta = (sV[tt][warp * REC_PER_WARP + c] - __shfl_sync(0xffffffffu, m, rec_owner_lane(c))) * bt;
+                o[c] = 0.f;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    st[c][i] += kr[i] * delta;
+                    o[c] += st[c][i] * qr[i];
+                }
+            }
+            const float total = rec_reduce4(o[0], o[1], o[2], o[3], lane);
+            const int c = rec_owned_value(lane);
+            if ((lane & 7) == 0 && cw + c < Dv) y[((tok0 + tt) * Hv + h) * Dv + cw + c] = total;
+        }
     }
 #pragma unroll
-    for (int i = 0; i < NV; ++i)
-        if (lane + 32 * i < Dk) sbase[(size_t)(lane + 32 * i) * Dv] = st[i];
+    for (int c = 0; c < REC_PER_WARP; ++c)
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (cw + c < Dv && lane + 32 * i < Dk) sbase[(size_t)(lane + 32 * i) * Dv + cw + c] = st[c][i];
 }
 
 template <class Launch>
@@ -126,11 +199,10 @@ int ovb_selective_ssm(const float* A, const float* dt, const float* Bm, const fl
         set_error("ovb_selective_ssm: state size %d above %d", S, 32 * REC_MAXV);
         return ERR_UNSUPPORTED;
     }
-    OVB_REQUIRE((long long)B * H * P < (1ll << 31), "ovb_selective_ssm: too many state rows");
-    const int rows = B * H * P;
+    OVB_REQUIRE((long long)B * H <= 65535, "ovb_selective_ssm: batch x heads above 65535");
     cudaStream_t stream = (cudaStream_t)stream_;
     return dispatch_width(S, [&](auto nv) -> int {
-        selective_ssm_kernel<decltype(nv)::value><<<ceil_div(rows, REC_WARPS), REC_WARPS * 32, 0, stream>>>(A, dt, Bm, x, Cm, state, y, rows, L, H, P, G, S);
+        selective_ssm_kernel<decltype(nv)::value><<<dim3(ceil_div(P, REC_TILE), B * H), REC_WARPS * 32, 0, stream>>>(A, dt, Bm, x, Cm, state, y, L, H, P, G, S);
         OVB_CHECK_CUDA(cudaGetLastError());
         return 0;
     });
@@ -145,11 +217,10 @@ int ovb_gated_delta_rule(const float* q, const float* k, const float* v, const f
         set_error("ovb_gated_delta_rule: key width %d above %d", Dk, 32 * REC_MAXV);
         return ERR_UNSUPPORTED;
     }
-    OVB_REQUIRE((long long)B * Hv * Dv < (1ll << 31), "ovb_gated_delta_rule: too many state columns");
-    const int cols = B * Hv * Dv;
+    OVB_REQUIRE((long long)B * Hv <= 65535, "ovb_gated_delta_rule: batch x value heads above 65535");
     cudaStream_t stream = (cudaStream_t)stream_;
     return dispatch_width(Dk, [&](auto nv) -> int {
-        gated_delta_rule_kernel<decltype(nv)::value><<<ceil_div(cols, REC_WARPS), REC_WARPS * 32, 0, stream>>>(q, k, v, gate, beta, state, y, cols, L, Hq, Hv, Dk, Dv);
+        gated_delta_rule_kernel<decltype(nv)::value><<<dim3(ceil_div(Dv, REC_TILE), B * Hv), REC_WARPS * 32, 0, stream>>>(q, k, v, gate, beta, state, y, L, Hq, Hv, Dk, Dv);
         OVB_CHECK_CUDA(cudaGetLastError());
         return 0;
     });

@@ -1051,7 +1051,7 @@ def _rope(n, ins, ctx):
     at = n.get_attributes()
     flags = [k for k in ("is_interleaved", "is_chatglm", "is_qwen", "support_2d_rope", "support_3d_rope", "is_ltx_video", "use_rope_cache") if at.get(k)]
     if flags or at.get("input_trans0213") or at.get("output_trans0213") or at.get("slice_stop", 0) or len(ins) > 3:
-        raise NotImplementedError("RoPE variant %s" % flags)
+        return NotImplemented        # the fused-QKV, transposed and interleaved forms run through the reference evaluation
     x, cos, sin = _same_device(ctx, ins[:3])
     D = x.shape[-1]
     nd = at.get("rotary_ndims") or D

@@ -400,6 +400,88 @@ def test_rope_fusion_partial_rotary():
     np.testing.assert_allclose(ov.compile_model(m, "CPU")([xin])[0], want, rtol=1e-5, atol=1e-6)
 
 
+def test_rope_fusion_qwen_fused_qkv():
+    """Qwen: heads cut out of the fused QKV projection, [B, L, H, S] order, halves swapped through reshape / split, tables
+    [1, positions, 1, S] already cut to the tokens at hand -> RoPE {is_qwen} reading the projection itself."""
+    B, L, H, S = 2, 5, 3, 8
+    i64 = lambda v: ops.constant(np.array(v, dtype=np.int64))
+    qkv = ops.parameter([B, L, 3 * H * S], "f32", "qkv")
+    cos, sin = _rope_tables(L, S, "halves")
+    cos, sin = cos.reshape(1, L, 1, S), sin.reshape(1, L, 1, S)
+    parts = ops.variadic_split(qkv, i64(2), i64([H * S, H * S, H * S]))
+    outs = []
+    for k in (0, 1):
+        x = ops.reshape(parts.output(k), i64([0, 0, H, S]), True)
+        halves = ops.split(ops.reshape(x, i64([0, 0, 0, 2, S // 2]), True), i64(-2), 2)
+        rot = ops.concat([ops.squeeze(ops.multiply(halves.output(1), np.float32(-1.0)), i64(-2)).output(0), ops.squeeze(halves.output(0), i64(-2)).output(0)], -1)
+        outs.append(ops.add(ops.multiply(x, ops.constant(cos)), ops.multiply(rot, ops.constant(sin))))
+    m = ov.Model(outs, [qkv], "qwen")
+    xin = np.random.default_rng(3).standard_normal((B, L, 3 * H * S)).astype(np.float32)
+    want = ov.compile_model(m, "CPU")([xin])
+    want = [want[0], want[1]]
+    _run_pass(m, passes.RoPEFusion())
+    rope = [n for n in m.get_ops() if n.get_type_name() == "RoPE"]
+    assert len(rope) == 2 and all(r.get_attribute("is_qwen") and r.get_attribute("head_cnt") == H and r.get_attribute("head_size") == S for r in rope)
+    assert sorted(r.get_attribute("slice_start") for r in rope) == [0, H * S]
+    assert all(r.input_value(0).get_node().get_type_name() == "Parameter" for r in rope)
+    assert not any(n.get_type_name() in ("VariadicSplit", "Split", "Squeeze") for n in m.get_ops())
+    got = ov.compile_model(m, "CPU")([xin])
+    for k in (0, 1):
+        assert list(got[k].shape) == [B, L, H, S]
+        np.testing.assert_allclose(got[k], want[k], rtol=1e-5, atol=1e-6)
+
+
+def test_rope_fusion_chatglm_fused_qkv():
+    """ChatGLM: [L, B, W] projection, neighbouring pairs of the first `rot` values of each head rotated by a combined
+    (cos, sin) cache [L, 1, 1, rot / 2, 2], the rest of the head passes through -> RoPE {is_chatglm}."""
+    L, B, H, S, rot = 4, 2, 3, 16, 8
+    i64 = lambda v: ops.constant(np.array(v, dtype=np.int64))
+    qkv = ops.parameter([L, B, H * S + 2 * 2 * S], "f32", "qkv")          # multi-query: 3 query heads, 2 key and 2 value heads
+    ang = np.arange(L, dtype=np.float32)[:, None] * (10000.0 ** (-np.arange(0, rot, 2, dtype=np.float32) / rot))[None]
+    cache = np.stack([np.cos(ang), np.sin(ang)], -1).reshape(L, 1, 1, rot // 2, 2).astype(np.float32)
+    parts = ops.variadic_split(qkv, i64(-1), i64([H * S, 2 * S, 2 * S]))
+    x = ops.reshape(parts.output(0), i64([0, 0, H, S]), True)
+    head = ops.slice(x, i64([0]), i64([rot]), i64([1]), i64([3]))
+    tail = ops.slice(x, i64([rot]), i64([S]), i64([1]), i64([3]))
+    pairs = ops.reshape(head, i64([0, 0, H, rot // 2, 2]), True)
+    cc = ops.constant(cache)
+    p0, p1 = ops.gather(pairs, i64(0), i64(-1)), ops.gather(pairs, i64(1), i64(-1))
+    c, s_ = ops.gather(cc, i64(0), i64(-1)), ops.gather(cc, i64(1), i64(-1))
+    o0 = ops.subtract(ops.multiply(p0, c), ops.multiply(p1, s_))
+    o1 = ops.add(ops.multiply(p1, c), ops.multiply(p0, s_))
+    stack = ops.concat([ops.unsqueeze(o0, i64(-1)).output(0), ops.unsqueeze(o1, i64(-1)).output(0)], -1)
+    y = ops.concat([ops.reshape(stack, i64([0, 0, H, rot]), True).output(0), tail.output(0)], -1)
+    m = ov.Model([y], [qkv], "chatglm")
+    xin = np.random.default_rng(4).standard_normal((L, B, H * S + 4 * S)).astype(np.float32)
+    want = ov.compile_model(m, "CPU")([xin])[0]
+    _run_pass(m, passes.RoPEFusion())
+    rope = [n for n in m.get_ops() if n.get_type_name() == "RoPE"]
+    assert len(rope) == 1 and rope[0].get_attribute("is_chatglm") and rope[0].get_attribute("rotary_ndims") == rot
+    assert rope[0].get_attribute("slice_start") == 0 and rope[0].get_attribute("slice_stop") == H * S
+    assert not any(n.get_type_name() in ("Gather", "Slice", "VariadicSplit") for n in m.get_ops())
+    got = ov.compile_model(m, "CPU")([xin])[0]
+    assert list(got.shape) == [L, B, H, S]
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+
+
+def test_rope_fusion_leaves_blhs_tables_alone():
+    """x in [B, L, H, S] order with tables [1, L, 1, S] and slice-built halves is not the [B, H, L, S] form RoPE reads: no fusion."""
+    B, L, H, S = 1, 4, 2, 8
+    i64 = lambda v: ops.constant(np.array(v, dtype=np.int64))
+    x = ops.parameter([B, L, H, S], "f32", "x")
+    cos, sin = _rope_tables(L, S, "halves")
+    cos, sin = cos.reshape(1, L, 1, S), sin.reshape(1, L, 1, S)
+    lo = ops.slice(x, i64([0]), i64([S // 2]), i64([1]), i64([3]))
+    hi = ops.slice(x, i64([S // 2]), i64([S]), i64([1]), i64([3]))
+    y = ops.add(ops.multiply(x, ops.constant(cos)), ops.multiply(ops.concat([ops.negative(hi).output(0), lo.output(0)], 3), ops.constant(sin)))
+    m = ov.Model([y], [x], "blhs")
+    xin = np.random.default_rng(5).standard_normal((B, L, H, S)).astype(np.float32)
+    want = ov.compile_model(m, "CPU")([xin])[0]
+    _run_pass(m, passes.RoPEFusion())
+    assert not any(n.get_type_name() == "RoPE" for n in m.get_ops())
+    np.testing.assert_allclose(ov.compile_model(m, "CPU")([xin])[0], want, rtol=1e-6)
+
+
 def test_lora_subgraph_fusion_keeps_adapters_switchable():
     rng = np.random.default_rng(2)
     din, dout, r = 16, 12, 4
