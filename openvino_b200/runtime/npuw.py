@@ -416,18 +416,28 @@ class NpuwPlugin(Plugin):
     description = "Repeated-block folding and weights bank over another device"
 
     def supported_properties(self):
-        return super().supported_properties() + ["NPUW_DEVICES", "NPUW_FOLD", "NPUW_ONLINE_MIN_SIZE", "NPUW_ONLINE_KEEP_BLOCKS", "NPUW_WEIGHTS_BANK", props.device.priorities]
+        return super().supported_properties() + ["NPUW_DEVICES", "NPUW_FOLD", "NPUW_ONLINE_MIN_SIZE", "NPUW_ONLINE_KEEP_BLOCKS", "NPUW_WEIGHTS_BANK", props.device.priorities,
+                                                 "NPUW_LLM", "NPUW_LLM_MAX_PROMPT_LEN", "NPUW_LLM_MIN_RESPONSE_LEN", "NPUW_LLM_PREFILL_CHUNK_SIZE",
+                                                 "NPUW_LLM_GENERATE_VARIANTS", "NPUW_LLM_PREFIX_CACHING"]
 
     def default_config(self):
         d = super().default_config()
-        d.update({"NPUW_DEVICES": "CPU", "NPUW_FOLD": "YES", "NPUW_ONLINE_MIN_SIZE": 4, "NPUW_ONLINE_KEEP_BLOCKS": 2, "NPUW_WEIGHTS_BANK": "shared"})
+        d.update({"NPUW_DEVICES": "CPU", "NPUW_FOLD": "YES", "NPUW_ONLINE_MIN_SIZE": 4, "NPUW_ONLINE_KEEP_BLOCKS": 2, "NPUW_WEIGHTS_BANK": "shared",
+                  "NPUW_LLM": "NO", "NPUW_LLM_MAX_PROMPT_LEN": 1024, "NPUW_LLM_MIN_RESPONSE_LEN": 128, "NPUW_LLM_PREFILL_CHUNK_SIZE": 0,
+                  "NPUW_LLM_GENERATE_VARIANTS": "", "NPUW_LLM_PREFIX_CACHING": "NO"})
         return d
 
     def compile_model(self, model: Model, config: dict) -> CompiledModel:
         cfg = self.merged_config(config)
         dev = str(cfg.get(props.device.priorities) or cfg.get("NPUW_DEVICES") or "CPU").split(",")[0]
-        work = model.clone()
         bank = WeightsBank.for_device("%s/%s" % (dev, cfg.get("NPUW_WEIGHTS_BANK", "shared")))
+        if str(cfg.get("NPUW_LLM", "NO")).upper() in ("YES", "TRUE", "1"):
+            from .npuw_llm import NpuwLlmCompiledModel, is_llm
+            if not is_llm(model):
+                raise RuntimeError("[NPUW] NPUW_LLM needs a stateful decoder with input_ids / attention_mask / position_ids inputs")
+            inner_cfg = {k: v for k, v in cfg.items() if not str(k).startswith("NPUW_") and k != props.device.priorities and k in config}
+            return NpuwLlmCompiledModel(self, model, cfg, dev, inner_cfg, bank)
+        work = model.clone()
         removed = dedupe_constants(work, bank)
         f = None
         if str(cfg.get("NPUW_FOLD", "YES")).upper() in ("YES", "TRUE", "1"):

@@ -89,3 +89,65 @@ def test_folded_stack_on_cuda():
     assert cm.get_property("NPUW_FOLDED_BLOCKS") == 6
     np.testing.assert_allclose(cm([xv])[0], ref, rtol=2e-3, atol=2e-3)
     assert cm.function.compiles == 1 and cm.function.calls == 6
+
+
+def _tiny_llm():
+    import torch
+    from openvino_b200.models import llama
+    from openvino_b200.models.llm_config import TINY_LLAMA
+    from openvino_b200.models.ov_builders import build_llama
+    cfg = TINY_LLAMA.with_(vocab_size=96, hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, ffn_size=128, group_size=32, num_layers=2)
+    state = llama.random_float_state(cfg, seed=3, std=0.1)
+    return cfg, state, build_llama(cfg, state), llama, torch
+
+
+def test_llm_pipeline_static_prefill_and_generate_variants():
+    """The stateful decoder behind static sub-models: chunked prefill, KV rows copied between the prefill model and the
+    generate variants, the smallest variant that holds the sequence, reset_state, prefix caching."""
+    cfg, state, model, llama, torch = _tiny_llm()
+    core = ov.Core()
+    cm = core.compile_model(model, "NPUW", {"NPUW_LLM": "YES", "NPUW_LLM_MAX_PROMPT_LEN": 16, "NPUW_LLM_MIN_RESPONSE_LEN": 8, "NPUW_LLM_PREFILL_CHUNK_SIZE": 8,
+                                            "NPUW_LLM_GENERATE_VARIANTS": "12,16", "NPUW_LLM_PREFIX_CACHING": "YES"})
+    assert cm.get_property("NPUW_LLM_GENERATE_VARIANTS") == [12, 16, 24] and cm.get_property("NPUW_LLM_PREFILL_CHUNK_SIZE") == 8
+    assert [i.get_any_name() for i in cm.inputs] == ["input_ids", "attention_mask", "position_ids", "beam_idx"]
+    req = cm.create_infer_request()
+
+    def feed(ids, past):
+        n = len(ids)
+        return {"input_ids": np.asarray(ids, np.int64)[None], "attention_mask": np.ones((1, past + n), np.int64),
+                "position_ids": np.arange(past, past + n)[None], "beam_idx": np.zeros(1, np.int32)}
+    prompt = [5, 9, 1, 77, 30, 2, 41, 8, 63, 12, 7]                 # 11 tokens: one full chunk and a ragged one
+    seq = list(prompt)
+    logits = req.infer(feed(prompt, 0))[0]
+    ref = llama.reference_logits(cfg, state, torch.tensor(seq)).numpy()
+    np.testing.assert_allclose(logits[0], ref, rtol=2e-3, atol=2e-4)
+    for _ in range(8):                                              # rows 12 ... 19: variants 12, then 16, then the full 24
+        tok = int(logits[0, -1].argmax())
+        seq.append(tok)
+        logits = req.infer(feed([tok], len(seq) - 1))[0]
+        ref = llama.reference_logits(cfg, state, torch.tensor(seq)).numpy()
+        np.testing.assert_allclose(logits[0, -1], ref[-1], rtol=2e-3, atol=2e-4)
+    names = [t[0] for t in req.npuw_trace]
+    assert names[:2] == ["prefill", "prefill"] and names[2] == "generate/12" and "generate/16" in names and names[-1] == "generate/24"
+    kv = req.query_state()
+    assert len(kv) == 2 * cfg.num_layers and list(kv[0].state.shape) == [1, 2, len(seq), 16]
+
+    # a new prompt that repeats the first chunk of the conversation: that chunk is served from the cache
+    before = len(req.npuw_trace)
+    again = prompt[:8] + [3, 4, 6]
+    logits = req.infer(feed(again, 0))[0]
+    assert [t for t in req.npuw_trace[before:]] == [("prefill", 3)]
+    ref = llama.reference_logits(cfg, state, torch.tensor(again)).numpy()
+    np.testing.assert_allclose(logits[0, 8:], ref[8:], rtol=2e-3, atol=2e-4)
+
+    # reset_state starts over: the same prompt now runs both chunks
+    req.reset_state()
+    before = len(req.npuw_trace)
+    logits = req.infer(feed(again, 0))[0]
+    assert [t for t in req.npuw_trace[before:]] == [("prefill", 8), ("prefill", 3)]
+    np.testing.assert_allclose(logits[0], ref, rtol=2e-3, atol=2e-4)
+    with pytest.raises(RuntimeError, match="longer than"):
+        req.infer(feed(list(range(1, 19)), 0))
+    with pytest.raises(RuntimeError, match="stateful decoder"):
+        x = ops.parameter([1, 4], "f32", "x")
+        core.compile_model(ov.Model([ops.relu(x)], [x], "plain"), "NPUW", {"NPUW_LLM": "YES"})
