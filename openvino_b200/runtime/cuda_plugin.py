@@ -1048,18 +1048,72 @@ def _glu(n, ins, ctx):
 
 @op("RoPE")
 def _rope(n, ins, ctx):
+    """Half-rotate and interleaved forms over [B, H, L, S] (or [B, L, H, S] with the transposition flags), partial rotary
+    widths, and the fused-QKV forms of Qwen ([B, L, W], tables [1, positions, 1, S]) and ChatGLM ([L, B, W], cache
+    [L, B or 1, 1, rot / 2, 2]). Same arithmetic as the reference evaluation (csrc/core/eval_llm.cpp)."""
     at = n.get_attributes()
-    flags = [k for k in ("is_interleaved", "is_chatglm", "is_qwen", "support_2d_rope", "support_3d_rope", "is_ltx_video", "use_rope_cache") if at.get(k)]
-    if flags or at.get("input_trans0213") or at.get("output_trans0213") or at.get("slice_stop", 0) or len(ins) > 3:
-        return NotImplemented        # the fused-QKV, transposed and interleaved forms run through the reference evaluation
+    if at.get("support_2d_rope") or at.get("support_3d_rope") or at.get("is_ltx_video") or at.get("use_rope_cache"):
+        return NotImplemented
     x, cos, sin = _same_device(ctx, ins[:3])
-    D = x.shape[-1]
+    pos = ins[3].to(x.device).long() if len(ins) > 3 and ins[3].numel() > 0 else None
+    H, S = at.get("head_cnt", 0), at.get("head_size", 0)
+    if at.get("is_chatglm"):
+        L, B = x.shape[0], x.shape[1]
+        rot = at.get("rotary_ndims") or S
+        xh = x[..., at.get("slice_start", 0):at.get("slice_start", 0) + H * S].reshape(L, B, H, S)
+        pairs = xh[..., :rot].reshape(L, B, H, rot // 2, 2).float()
+        cache = cos[:L].float()                                              # [L, B or 1, 1, rot / 2, 2]
+        c, s_ = cache[..., 0], cache[..., 1]
+        out = torch.stack([pairs[..., 0] * c - pairs[..., 1] * s_, pairs[..., 1] * c + pairs[..., 0] * s_], -1).reshape(L, B, H, rot)
+        return [torch.cat([out.to(x.dtype), xh[..., rot:]], -1)]
+    if at.get("is_qwen"):
+        B, L = x.shape[0], x.shape[1]
+        xh = x[..., at.get("slice_start", 0):at.get("slice_start", 0) + H * S].reshape(B, L, H, S).float()
+        c2, s2 = cos.reshape(-1, S).float(), sin.reshape(-1, S).float()
+        rows = torch.arange(c2.shape[0] - L, c2.shape[0], device=x.device) if c2.shape[0] >= L else torch.arange(L, device=x.device).clamp(max=c2.shape[0] - 1)
+        if pos is not None:
+            rows = pos.reshape(-1, L) if pos.numel() == B * L else pos.reshape(1, -1)
+            c4, s4 = c2[rows].unsqueeze(2), s2[rows].unsqueeze(2)          # [B or 1, L, 1, S]
+        else:
+            c4, s4 = c2[rows].reshape(1, L, 1, S), s2[rows].reshape(1, L, 1, S)
+        half = S // 2
+        rotd = torch.cat([-xh[..., half:], xh[..., :half]], -1)
+        return [(xh * c4 + rotd * s4).to(x.dtype)]
+    if x.dim() != 4 or at.get("slice_stop", 0) > at.get("slice_start", 0):
+        return NotImplemented
+    it, ot = bool(at.get("input_trans0213")), bool(at.get("output_trans0213"))
+    xb = x.transpose(1, 2) if it else x                                      # [B, H, L, S]
+    B, Hh, L, D = xb.shape
     nd = at.get("rotary_ndims") or D
-    xr, rest = x[..., :nd], x[..., nd:]
-    lo, hi = xr[..., : nd // 2], xr[..., nd // 2:]
-    rot = torch.cat([-hi, lo], -1)
-    out = xr * cos.to(x.dtype) + rot * sin.to(x.dtype)
-    return [torch.cat([out, rest], -1) if nd != D else out]
+    half = nd // 2
+    # tables: last axis nd or nd / 2 wide, the axis before it (if any) runs over positions, an optional leading batch
+    cw = cos.shape[-1]
+    crow = cos.shape[-2] if cos.dim() >= 2 else 1
+    c3, s3 = cos.reshape(-1, crow, cw).float(), sin.reshape(-1, crow, cw).float()
+    rows = torch.arange(L, device=x.device)
+    if pos is not None:
+        rows = pos.reshape(1, L) if pos.numel() == L else pos.reshape(-1, L)
+    rows = torch.zeros_like(rows) if crow == 1 else rows.clamp(max=crow - 1)
+    if rows.dim() == 1:
+        ct, st_ = c3[:, rows], s3[:, rows]                                  # [cb, L, cw]
+    else:
+        bi = torch.arange(rows.shape[0], device=x.device).clamp(max=c3.shape[0] - 1).unsqueeze(1)
+        ct, st_ = c3[bi, rows], s3[bi, rows]                                # [B or 1, L, cw]
+    ct, st_ = ct.unsqueeze(1), st_.unsqueeze(1)                             # [., 1, L, cw]
+    xr = xb[..., :nd].float()
+    if at.get("is_interleaved"):
+        x0, x1 = xr[..., 0::2], xr[..., 1::2]
+        cc, ss = (ct[..., 0::2], st_[..., 0::2]) if cw == nd else (ct, st_)
+        out = torch.stack([x0 * cc - x1 * ss, x1 * cc + x0 * ss], -1).reshape(B, Hh, L, nd)
+    else:
+        x0, x1 = xr[..., :half], xr[..., half:]
+        c0, s0 = ct[..., :half], st_[..., :half]
+        c1, s1 = (ct[..., half:nd], st_[..., half:nd]) if cw == nd else (c0, s0)
+        out = torch.cat([x0 * c0 - x1 * s0, x1 * c1 + x0 * s1], -1)
+    out = out.to(x.dtype)
+    if nd != D:
+        out = torch.cat([out, xb[..., nd:]], -1)
+    return [out.transpose(1, 2) if ot else out]
 
 
 @op("SelectiveSSM")
@@ -1088,6 +1142,76 @@ def _gated_delta_net(n, ins, ctx):
         qf = qf * scale
     y, new_state = ctx.K.gated_delta_rule(qf, kf, v, gate, beta, state)
     return [y.to(v.dtype), new_state.to(state.dtype)]
+
+
+def _paged_segments(begins, blocks, bbeg, past, interval):
+    """Host walk of the paged-state bookkeeping: for every sequence the block to read, then (token begin, token end, block
+    to write) per stretch of tokens up to the next multiple of the cache interval."""
+    plan = []
+    for s in range(len(begins) - 1):
+        slots = blocks[bbeg[s]:bbeg[s + 1]]
+        tb, te, pst, iv = begins[s], begins[s + 1], past[s], interval[s]
+        if len(slots) == 0:
+            raise RuntimeError("a sequence needs at least one state block")
+        to_boundary = (iv - pst % iv if pst % iv else iv) if iv > 0 else te - tb
+        segs, slot, tok = [], 1, tb
+        while tok < te:
+            end = min(tok + to_boundary, te)
+            if slot >= len(slots):
+                raise RuntimeError("block slot %d is beyond the %d slots of the sequence" % (slot, len(slots)))
+            segs.append((tok, end, int(slots[slot])))
+            slot += 1
+            tok = end
+            to_boundary = iv if iv > 0 else te - tb
+        plan.append((int(slots[0]), segs))
+    return plan
+
+
+def _host_ints(t):
+    return [int(v) for v in t.detach().to("cpu").reshape(-1).tolist()]
+
+
+@op("PagedSelectiveSSM")
+def _paged_selective_ssm(n, ins, ctx):
+    """Token-major inputs (dt [T, H], B / C [T, G, S], x [T, H, P]) and a state table [blocks, H, P, S] updated in place:
+    the scan kernel runs once per stretch between cache-interval boundaries."""
+    if ctx.K is None or ins[2].shape[-1] > 256 or not ins[5].is_cuda:
+        return NotImplemented
+    A, dt, Bm, x, Cm, table = _same_device(ctx, ins[:6])
+    plan = _paged_segments(*(_host_ints(t) for t in ins[6:11]))
+    y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    for first, segs in plan:
+        state = table[first:first + 1].float()
+        for t0, t1, blk in segs:
+            ys, state = ctx.K.selective_ssm(A, dt[None, t0:t1], Bm[None, t0:t1], x[None, t0:t1], Cm[None, t0:t1], state)
+            y[t0:t1] = ys[0]
+            table[blk].copy_(state[0])
+    return [y.to(x.dtype)]
+
+
+@op("PagedGatedDeltaNet")
+def _paged_gated_delta_net(n, ins, ctx):
+    """Token-major q / k [T, Hq, Dk], v [T, Hv, Dv], gate / beta [T, Hv]; state table [blocks, Hv, Dv, Dk] updated in place."""
+    if ctx.K is None or ins[0].shape[-1] > 256 or not ins[3].is_cuda:
+        return NotImplemented
+    q, k, v, table, gate, beta = _same_device(ctx, ins[:6])
+    at = n.get_attributes()
+    qf, kf = q.float(), k.float()
+    scale = float(q.shape[-1]) ** -0.5
+    if at.get("use_qk_l2norm"):
+        qf = qf * torch.rsqrt((qf * qf).sum(-1, keepdim=True) + float(at.get("q_l2_norm_eps", 1e-6))) * scale
+        kf = kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + float(at.get("k_l2_norm_eps", 1e-6)))
+    else:
+        qf = qf * scale
+    plan = _paged_segments(*(_host_ints(t) for t in ins[6:11]))
+    y = torch.empty(v.shape, dtype=torch.float32, device=v.device)
+    for first, segs in plan:
+        state = table[first:first + 1].float().transpose(-1, -2).contiguous()          # the kernel keeps [Dk, Dv]
+        for t0, t1, blk in segs:
+            ys, state = ctx.K.gated_delta_rule(qf[None, t0:t1], kf[None, t0:t1], v[None, t0:t1], gate[None, t0:t1], beta[None, t0:t1], state)
+            y[t0:t1] = ys[0]
+            table[blk].copy_(state[0].transpose(-1, -2))
+    return [y.to(v.dtype)]
 
 
 @op("ReadValue")

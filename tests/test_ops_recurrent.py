@@ -297,3 +297,64 @@ def test_recurrent_device_kernels_match_the_restatements():
             res = cm([t.numpy() for t in (q, k, v, st, g, beta)])
             np.testing.assert_allclose(res[0], ry.numpy(), rtol=5e-4, atol=5e-4)
             np.testing.assert_allclose(res[1], rs.numpy(), rtol=5e-4, atol=5e-4)
+
+
+@pytest.mark.gpu
+def test_paged_recurrent_forms_on_the_device_update_the_table_in_place():
+    """PagedGatedDeltaNet / PagedSelectiveSSM on the CUDA device: the state table is a device tensor of the caller, the scan
+    kernels run per stretch between cache-interval boundaries, snapshots land in the blocks the bookkeeping names."""
+    torch.manual_seed(1)
+    core = ov.Core()
+    rctx = core.get_default_context("CUDA")
+    begins = np.array([0, 5, 7], np.int32)
+    blocks = np.array([2, 2, 4, 1, 1], np.int32)
+    bbeg = np.array([0, 3, 5], np.int32)
+    past, interval = np.array([3, 0], np.int32), np.array([4, 0], np.int32)
+    T, Hq, Hv, Dk, Dv = 7, 2, 4, 40, 9
+    q, k, v = torch.randn(T, Hq, Dk), torch.randn(T, Hq, Dk), torch.randn(T, Hv, Dv)
+    g, beta = -torch.rand(T, Hv), torch.rand(T, Hv)
+    table = torch.randn(5, Hv, Dv, Dk) * 0.1
+    ps = [P(q.shape, "q"), P(k.shape, "k"), P(v.shape, "v"), P(table.shape, "tab"), P(g.shape, "g"), P(beta.shape, "b"),
+          P([3], "sb", "i32"), P([5], "bi", "i32"), P([3], "bb", "i32"), P([2], "pt", "i32"), P([2], "ci", "i32")]
+    n = ops.paged_gated_delta_net(*ps, use_qk_l2norm=True)
+    cm = core.compile_model(ov.Model([n.output(0)], ps, "pgdn"), "CUDA", {"INFERENCE_PRECISION_HINT": "f32"})
+    remote = rctx.create_tensor(ov.Type.f32, list(table.shape))
+    remote.torch().copy_(table)
+    req = cm.create_infer_request()
+    for i, a in enumerate([q.numpy(), k.numpy(), v.numpy(), None, g.numpy(), beta.numpy(), begins, blocks, bbeg, past, interval]):
+        req.set_input_tensor(i, remote if a is None else ov.Tensor(a))
+    req.infer()
+    y = req.get_output_tensor(0).data
+    ref0, s_mid = torch_gdn(q[None, 0:1], k[None, 0:1], v[None, 0:1], table[2].transpose(-1, -2)[None], g[None, 0:1], beta[None, 0:1], True)
+    ref0b, s_end = torch_gdn(q[None, 1:5], k[None, 1:5], v[None, 1:5], s_mid, g[None, 1:5], beta[None, 1:5], True)
+    ref1, s1 = torch_gdn(q[None, 5:7], k[None, 5:7], v[None, 5:7], table[1].transpose(-1, -2)[None], g[None, 5:7], beta[None, 5:7], True)
+    np.testing.assert_allclose(y, torch.cat([ref0[0], ref0b[0], ref1[0]]).numpy(), rtol=5e-4, atol=5e-5)
+    tab = remote.torch().cpu()
+    torch.testing.assert_close(tab[2], s_mid[0].transpose(-1, -2), rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(tab[4], s_end[0].transpose(-1, -2), rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(tab[1], s1[0].transpose(-1, -2), rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(tab[0], table[0])
+
+    H, Pd, G, S = 4, 6, 2, 48
+    A = -torch.rand(H)
+    dt, B, x, C = torch.rand(3, H), torch.randn(3, G, S), torch.randn(3, H, Pd), torch.randn(3, G, S)
+    tab0 = torch.randn(4, H, Pd, S)
+    ps = [P([H], "A"), P(dt.shape, "dt"), P(B.shape, "B"), P(x.shape, "x"), P(C.shape, "C"), P(tab0.shape, "t"),
+          P([2], "sb", "i64"), P([3], "bi", "i64"), P([2], "bb", "i64"), P([1], "pt", "i64"), P([1], "ci", "i64")]
+    n = ops.paged_selective_ssm(*ps)
+    cm = core.compile_model(ov.Model([n.output(0)], ps, "pssm"), "CUDA", {"INFERENCE_PRECISION_HINT": "f32"})
+    remote = rctx.create_tensor(ov.Type.f32, list(tab0.shape))
+    remote.torch().copy_(tab0)
+    req = cm.create_infer_request()
+    # 3 new tokens after 5 processed, interval 3: one token reaches the boundary (block 1), the other two go to block 3
+    for i, a in enumerate([A.numpy(), dt.numpy(), B.numpy(), x.numpy(), C.numpy(), None, np.array([0, 3]), np.array([0, 1, 3]), np.array([0, 3]), np.array([5]), np.array([3])]):
+        req.set_input_tensor(i, remote if a is None else ov.Tensor(a))
+    req.infer()
+    y = req.get_output_tensor(0).data
+    ry1, rs1 = torch_ssm(A, dt[None, :1], B[None, :1], x[None, :1], C[None, :1], tab0[0][None])
+    ry2, rs2 = torch_ssm(A, dt[None, 1:], B[None, 1:], x[None, 1:], C[None, 1:], rs1)
+    np.testing.assert_allclose(y, torch.cat([ry1[0], ry2[0]]).numpy(), rtol=5e-4, atol=5e-5)
+    tab = remote.torch().cpu()
+    torch.testing.assert_close(tab[1], rs1[0], rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(tab[3], rs2[0], rtol=5e-4, atol=5e-5)
+    torch.testing.assert_close(tab[2], tab0[2])

@@ -581,3 +581,44 @@ def test_precision_sensitive_islands_stay_in_fp32():
     cv = ops.convert(c, "f16")
     rt.mark_as_decompression(cv)
     assert rt.is_decompression(cv)
+
+
+def test_device_rope_expression_matches_the_reference_evaluation():
+    """The CUDA device's RoPE (tensor expressions in runtime/cuda_plugin.py) against the native reference evaluation, on
+    host tensors: plain, partial, interleaved, transposed, position ids, and the fused-QKV forms."""
+    import types as _types
+    import torch
+    from openvino_b200.runtime import cuda_plugin
+    rng = np.random.default_rng(9)
+    ctx = _types.SimpleNamespace(on_gpu=False, device="cpu", K=None)
+    B, H, L, S = 2, 3, 5, 8
+
+    def check(x, cos, sin, pos=None, **cfg):
+        ps = [ops.parameter(list(a.shape), "f32" if a.dtype == np.float32 else "i64", "p%d" % i) for i, a in enumerate([x, cos, sin] + ([pos] if pos is not None else []))]
+        node = ops.rope(ps[0], ps[1], ps[2], ps[3] if pos is not None else None, **cfg)
+        feeds = [x, cos, sin] + ([pos] if pos is not None else [])
+        want = ov.compile_model(ov.Model([node], ps, "rope"), "CPU")(feeds)[0]
+        got = cuda_plugin._OPS["RoPE"](node, [torch.from_numpy(a) for a in feeds], ctx)
+        assert got is not NotImplemented, cfg
+        np.testing.assert_allclose(got[0].numpy(), want, rtol=1e-5, atol=1e-6, err_msg=str(cfg))
+
+    x = rng.standard_normal((B, H, L, S)).astype(np.float32)
+    cos, sin = _rope_tables(L, S, "halves")
+    check(x, cos, sin, rotary_ndims=S)
+    check(x, cos[..., :S // 2].copy(), sin[..., :S // 2].copy(), rotary_ndims=S)                     # half-width tables
+    cos4, sin4 = _rope_tables(L, 4, "halves")
+    check(x, cos4, sin4, rotary_ndims=4)                                                              # partial rotary
+    ci, si = _rope_tables(L, S, "interleave")
+    check(x, ci, si, rotary_ndims=S, is_interleaved=True)
+    check(x.transpose(0, 2, 1, 3).copy(), cos, sin, rotary_ndims=S, input_trans0213=True)
+    check(x, cos, sin, rotary_ndims=S, output_trans0213=True)
+    big_c, big_s = _rope_tables(16, S, "halves")
+    check(x, big_c, big_s, pos=np.array([[3, 4, 9, 1, 0], [2, 2, 15, 7, 5]], np.int64), rotary_ndims=S)
+    # fused QKV forms
+    qkv = rng.standard_normal((B, L, 3 * H * S)).astype(np.float32)
+    tc, ts = _rope_tables(L + 3, S, "halves")
+    check(qkv, tc.reshape(1, L + 3, 1, S), ts.reshape(1, L + 3, 1, S), is_qwen=True, slice_start=H * S, slice_stop=2 * H * S, head_cnt=H, head_size=S, rotary_ndims=S)
+    glm = rng.standard_normal((L, B, H * S + 16)).astype(np.float32)
+    ang = rng.random((L, 1, 1, 2, 1)).astype(np.float32)
+    cache = np.concatenate([np.cos(ang), np.sin(ang)], -1)
+    check(glm, cache, cache, is_chatglm=True, is_interleaved=True, slice_start=0, slice_stop=H * S, head_cnt=H, head_size=S, rotary_ndims=4)
