@@ -1214,6 +1214,46 @@ def _paged_gated_delta_net(n, ins, ctx):
     return [y.to(v.dtype)]
 
 
+@op("PagedCausalConv1D")
+def _paged_causal_conv1d(n, ins, ctx):
+    """x [T, hidden], window table [blocks, hidden, kernel] updated in place, weights [hidden, hidden / groups, kernel], bias [hidden] or empty:
+    per stretch between cache-interval boundaries one grouped convolution over (window ++ new tokens)."""
+    if not ins[1].is_cuda:
+        return NotImplemented
+    x, table, w, bias = _same_device(ctx, ins[:4])
+    Kk, groups = table.shape[2], x.shape[1] // w.shape[1]
+    plan = _paged_segments(*(_host_ints(t) for t in ins[4:9]))
+    y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    wf, bf = w.float(), (bias.float() if bias.numel() else None)
+    for first, segs in plan:
+        window = table[first].float()                                              # [hidden, kernel]
+        for t0, t1, blk in segs:
+            seq = torch.cat([window, x[t0:t1].float().t()], 1)                     # [hidden, kernel + n]
+            y[t0:t1] = torch.nn.functional.conv1d(seq[None], wf, bf, groups=groups)[0, :, 1:].t()
+            window = seq[:, -Kk:]
+            table[blk].copy_(window)
+    return [y.to(x.dtype)]
+
+
+@op("PaKVReorder")
+def _pa_kv_reorder(n, ins, ctx):
+    """Rows of the key / value caches [blocks, heads, block_size, head_size] move (source token, destination token) pair by pair,
+    in the order given, inside the blocks of their sequence."""
+    if not (ins[0].is_cuda and ins[1].is_cuda):
+        return NotImplemented
+    blocks, bbeg, upd, ubeg = (_host_ints(t) for t in ins[2:6])
+    BS = ins[0].shape[2]
+    for s in range(len(ubeg) - 1):
+        mine = blocks[bbeg[s]:bbeg[s + 1]]
+        for o in range(ubeg[s], ubeg[s + 1]):
+            src, dst = upd[2 * o], upd[2 * o + 1]
+            if src < 0 or dst < 0 or src // BS >= len(mine) or dst // BS >= len(mine):
+                raise RuntimeError("PaKVReorder: token %d -> %d is outside the blocks of sequence %d" % (src, dst, s))
+            for cache in ins[:2]:
+                cache[mine[dst // BS], :, dst % BS] = cache[mine[src // BS], :, src % BS].clone()
+    return [torch.zeros(1, dtype=torch.uint8)]
+
+
 @op("ReadValue")
 def _read_value(n, ins, ctx):
     vid = n.get_attribute("variable_id")

@@ -358,3 +358,44 @@ def test_paged_recurrent_forms_on_the_device_update_the_table_in_place():
     torch.testing.assert_close(tab[1], rs1[0], rtol=5e-4, atol=5e-5)
     torch.testing.assert_close(tab[3], rs2[0], rtol=5e-4, atol=5e-5)
     torch.testing.assert_close(tab[2], tab0[2])
+
+
+@pytest.mark.gpu
+def test_paged_causal_conv_and_kv_reorder_on_the_device():
+    torch.manual_seed(2)
+    core = ov.Core()
+    rctx = core.get_default_context("CUDA")
+
+    def remote_of(t):
+        r = rctx.create_tensor(ov.Type.f32, list(t.shape))
+        r.torch().copy_(t)
+        return r
+    Hd, Kk, T = 6, 4, 5
+    x, w, bias = torch.randn(T, Hd), torch.randn(Hd, 2, Kk), torch.randn(Hd)
+    ps = [P(x.shape, "x"), P([3, Hd, Kk], "t"), P(w.shape, "w"), P(bias.shape, "b"), P([2], "sb", "i32"), P([3], "bi", "i32"), P([2], "bb", "i32"), P([1], "pt", "i32"), P([1], "ci", "i32")]
+    cm = core.compile_model(ov.Model([ops.paged_causal_conv1d(*ps).output(0)], ps, "pcc"), "CUDA", {"INFERENCE_PRECISION_HINT": "f32"})
+    table = remote_of(torch.zeros(3, Hd, Kk))
+    req = cm.create_infer_request()
+    # 5 tokens after 1 processed with interval 3: two tokens reach the boundary (block 2), the other three go to block 1
+    feeds = [x.numpy(), None, w.numpy(), bias.numpy(), np.array([0, T], np.int32), np.array([0, 2, 1], np.int32), np.array([0, 3], np.int32), np.array([1], np.int32), np.array([3], np.int32)]
+    for i, a in enumerate(feeds):
+        req.set_input_tensor(i, table if a is None else ov.Tensor(a))
+    req.infer()
+    ref = torch.nn.functional.conv1d(torch.nn.functional.pad(x.t()[None], (Kk - 1, 0)), w, bias, groups=3)[0].t()
+    np.testing.assert_allclose(req.get_output_tensor(0).data, ref.numpy(), rtol=1e-4, atol=1e-5)
+    tab = table.torch().cpu()
+    torch.testing.assert_close(tab[1], x[-Kk:].t().contiguous())
+    torch.testing.assert_close(tab[2][:, -2:], x[:2].t().contiguous())
+
+    kc, vc = torch.randn(4, 2, 4, 8), torch.randn(4, 2, 4, 8)
+    ps = [P(kc.shape, "k"), P(vc.shape, "v"), P([3], "bi", "i32"), P([2], "bb", "i32"), P([4], "u", "i32"), P([2], "ub", "i32")]
+    cm = core.compile_model(ov.Model([ops.pa_kv_reorder(*ps).output(0)], ps, "reorder"), "CUDA", {"INFERENCE_PRECISION_HINT": "f32"})
+    rk, rv = remote_of(kc), remote_of(vc)
+    req = cm.create_infer_request()
+    for i, a in enumerate([rk, rv, np.array([3, 0, 2], np.int32), np.array([0, 3], np.int32), np.array([5, 2, 9, 4], np.int32), np.array([0, 2], np.int32)]):
+        req.set_input_tensor(i, a if not isinstance(a, np.ndarray) else ov.Tensor(a))
+    req.infer()
+    k1, v1 = rk.torch().cpu(), rv.torch().cpu()
+    torch.testing.assert_close(k1[3, :, 2], kc[0, :, 1])
+    torch.testing.assert_close(v1[0, :, 0], vc[2, :, 1])
+    assert (k1 != kc).sum() == 2 * 8 * 2 and (v1 != vc).sum() == 2 * 8 * 2
