@@ -7,6 +7,8 @@
 //
 // Reference counterparts: the SelectiveSSM and GatedDeltaNet internal operations
 // (src/common/transformations/include/ov_ops/, executed by the CPU plugin's recurrent kernels).
+#include <stdlib.h>
+
 #include <type_traits>
 
 #include "common.cuh"
@@ -37,22 +39,42 @@ __device__ __forceinline__ float rec_reduce4(float v0, float v1, float v2, float
 __device__ __forceinline__ int rec_owner_lane(int r) { return ((r & 1) << 4) | ((r >> 1) << 3); }
 __device__ __forceinline__ int rec_owned_value(int lane) { return ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1); }
 
+// Sums eight per-lane values over the warp with 9 shuffles. The total of value r ends in the four lanes whose bits 4, 3, 2
+// spell r & 1, (r >> 1) & 1, (r >> 2) & 1.
+__device__ __forceinline__ float rec_reduce8(const float (&v)[8], int lane) {
+    const bool up16 = lane & 16, up8 = lane & 8, up4 = lane & 4;
+    float a[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = (up16 ? v[2 * i + 1] : v[2 * i]) + __shfl_xor_sync(0xffffffffu, up16 ? v[2 * i] : v[2 * i + 1], 16);
+    float b0 = (up8 ? a[1] : a[0]) + __shfl_xor_sync(0xffffffffu, up8 ? a[0] : a[1], 8);
+    float b1 = (up8 ? a[3] : a[2]) + __shfl_xor_sync(0xffffffffu, up8 ? a[2] : a[3], 8);
+    float c = (up4 ? b1 : b0) + __shfl_xor_sync(0xffffffffu, up4 ? b0 : b1, 4);
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
+}
+__device__ __forceinline__ int rec_owned_value8(int lane) { return ((lane >> 4) & 1) | (((lane >> 3) & 1) << 1) | (((lane >> 2) & 1) << 2); }
+
 // state[b, h, p, :] <- state * exp(A[h] * dt) + dt * B[b, t, g, :] * x[b, t, h, p];  y[b, t, h, p] = <state, C[b, t, g, :]>
-// One CTA owns REC_TILE rows p of one (b, h); the token vectors B, C (shared by all rows and by the heads of a group) are
-// staged in shared memory REC_CHUNK tokens at a time, so that they cross L2 once per CTA and not once per row.
-template <int NV>
+// One CTA owns RW * 8 rows p of one (b, h), each warp RW of them; the token vectors B, C (shared by all rows and by the
+// heads of a group) are staged in shared memory REC_CHUNK tokens at a time, so that they cross L2 once per CTA and not
+// once per row, and the outputs of a chunk leave through shared memory as whole rows of y.
+template <int NV, int RW>
 __global__ void __launch_bounds__(REC_WARPS * 32)
 selective_ssm_kernel(const float* __restrict__ A, const float* __restrict__ dt, const float* __restrict__ Bm, const float* __restrict__ x,
                      const float* __restrict__ Cm, float* __restrict__ state, float* __restrict__ y, int L, int H, int P, int G, int S) {
-    __shared__ float sB[REC_CHUNK][NV * 32], sC[REC_CHUNK][NV * 32], sX[REC_CHUNK][REC_TILE], sD[REC_CHUNK], sDA[REC_CHUNK];
+    constexpr int TILE = REC_WARPS * RW;
+    __shared__ float sB[REC_CHUNK][NV * 32], sC[REC_CHUNK][NV * 32], sX[REC_CHUNK][TILE], sY[REC_CHUNK][TILE], sD[REC_CHUNK], sDA[REC_CHUNK];
     const int bh = blockIdx.y, b = bh / H, h = bh % H, g = h / (H / G);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, p0 = blockIdx.x * REC_TILE, pw = p0 + warp * REC_PER_WARP;
-    float st[REC_PER_WARP][NV];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, p0 = blockIdx.x * TILE, pw = p0 + warp * RW;
+    float st[RW][NV];
 #pragma unroll
-    for (int r = 0; r < REC_PER_WARP; ++r)
+    for (int r = 0; r < RW; ++r)
 #pragma unroll
         for (int i = 0; i < NV; ++i) st[r][i] = (pw + r < P && lane + 32 * i < S) ? state[((size_t)bh * P + pw + r) * S + lane + 32 * i] : 0.f;
     const float a = A[h];
+    const int mine = RW == 8 ? rec_owned_value8(lane) : rec_owned_value(lane);
+    const bool writer = RW == 8 ? (lane & 3) == 0 : (lane & 7) == 0;
     for (int t0 = 0; t0 < L; t0 += REC_CHUNK) {
         const int nt = min(REC_CHUNK, L - t0);
         const size_t tok0 = (size_t)b * L + t0;
@@ -62,8 +84,8 @@ selective_ssm_kernel(const float* __restrict__ A, const float* __restrict__ dt, 
             sB[tt][s] = s < S ? Bm[((tok0 + tt) * G + g) * S + s] : 0.f;
             sC[tt][s] = s < S ? Cm[((tok0 + tt) * G + g) * S + s] : 0.f;
         }
-        for (int idx = threadIdx.x; idx < nt * REC_TILE; idx += REC_WARPS * 32) {
-            const int tt = idx / REC_TILE, r = idx % REC_TILE;
+        for (int idx = threadIdx.x; idx < nt * TILE; idx += REC_WARPS * 32) {
+            const int tt = idx / TILE, r = idx % TILE;
             sX[tt][r] = p0 + r < P ? x[((tok0 + tt) * H + h) * P + p0 + r] : 0.f;
         }
         if (threadIdx.x < nt) {
@@ -72,17 +94,18 @@ selective_ssm_kernel(const float* __restrict__ A, const float* __restrict__ dt, 
             sDA[threadIdx.x] = expf(a * d);
         }
         __syncthreads();
+#pragma unroll 2
         for (int tt = 0; tt < nt; ++tt) {
             const float d = sD[tt], dA = sDA[tt];
-            float bv[NV], cv[NV], acc[REC_PER_WARP];
+            float bv[NV], cv[NV], acc[RW];
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 bv[i] = sB[tt][lane + 32 * i] * d;
                 cv[i] = sC[tt][lane + 32 * i];
             }
 #pragma unroll
-            for (int r = 0; r < REC_PER_WARP; ++r) {
-                const float xv = sX[tt][warp * REC_PER_WARP + r];
+            for (int r = 0; r < RW; ++r) {
+                const float xv = sX[tt][warp * RW + r];
                 acc[r] = 0.f;
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
@@ -90,13 +113,19 @@ selective_ssm_kernel(const float* __restrict__ A, const float* __restrict__ dt, 
                     acc[r] += st[r][i] * cv[i];
                 }
             }
-            const float total = rec_reduce4(acc[0], acc[1], acc[2], acc[3], lane);
-            const int r = rec_owned_value(lane);
-            if ((lane & 7) == 0 && pw + r < P) y[((tok0 + tt) * H + h) * P + pw + r] = total;
+            float total;
+            if constexpr (RW == 8) total = rec_reduce8(acc, lane);
+            else total = rec_reduce4(acc[0], acc[1], acc[2], acc[3], lane);
+            if (writer) sY[tt][warp * RW + mine] = total;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * TILE; idx += REC_WARPS * 32) {
+            const int tt = idx / TILE, r = idx % TILE;
+            if (p0 + r < P) y[((tok0 + tt) * H + h) * P + p0 + r] = sY[tt][r];
         }
     }
 #pragma unroll
-    for (int r = 0; r < REC_PER_WARP; ++r)
+    for (int r = 0; r < RW; ++r)
 #pragma unroll
         for (int i = 0; i < NV; ++i)
             if (pw + r < P && lane + 32 * i < S) state[((size_t)bh * P + pw + r) * S + lane + 32 * i] = st[r][i];
@@ -176,6 +205,12 @@ gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k
             if (cw + c < Dv && lane + 32 * i < Dk) sbase[(size_t)(lane + 32 * i) * Dv + cw + c] = st[c][i];
 }
 
+// OVB_SSM_ROWS_PER_WARP = 4 keeps the four-row form for every shape (8 by default where it applies)
+int env_rows_per_warp() {
+    const char* e = getenv("OVB_SSM_ROWS_PER_WARP");
+    return e && atoi(e) == 4 ? 4 : 8;
+}
+
 template <class Launch>
 int dispatch_width(int width, Launch launch) {
     if (width <= 32) return launch(std::integral_constant<int, 1>());
@@ -201,8 +236,14 @@ int ovb_selective_ssm(const float* A, const float* dt, const float* Bm, const fl
     }
     OVB_REQUIRE((long long)B * H <= 65535, "ovb_selective_ssm: batch x heads above 65535");
     cudaStream_t stream = (cudaStream_t)stream_;
+    static const int rows_per_warp = env_rows_per_warp();
     return dispatch_width(S, [&](auto nv) -> int {
-        selective_ssm_kernel<decltype(nv)::value><<<dim3(ceil_div(P, REC_TILE), B * H), REC_WARPS * 32, 0, stream>>>(A, dt, Bm, x, Cm, state, y, L, H, P, G, S);
+        constexpr int NV = decltype(nv)::value;
+        // eight rows per warp halve the shared-memory reads and shuffles per row; they need 8 * NV state registers per lane
+        if (NV <= 4 && P >= 64 && rows_per_warp == 8)
+            selective_ssm_kernel<NV, 8><<<dim3(ceil_div(P, REC_WARPS * 8), B * H), REC_WARPS * 32, 0, stream>>>(A, dt, Bm, x, Cm, state, y, L, H, P, G, S);
+        else
+            selective_ssm_kernel<NV, 4><<<dim3(ceil_div(P, REC_WARPS * 4), B * H), REC_WARPS * 32, 0, stream>>>(A, dt, Bm, x, Cm, state, y, L, H, P, G, S);
         OVB_CHECK_CUDA(cudaGetLastError());
         return 0;
     });
