@@ -635,3 +635,198 @@ def _group_query_attention(n, i):
                                      do_rotary=bool(n.attrs.get("do_rotary", 0)), rotary_interleaved=bool(n.attrs.get("rotary_interleaved", 0)),
                                      local_window_size=int(n.attrs.get("local_window_size", -1)), smooth_softmax=bool(n.attrs.get("smooth_softmax", 0)))
     return [node.output(0), node.output(1), node.output(2)]
+
+
+# ------------------------------------------------------------------------------------------------ more com.microsoft
+def _activation(name: str, x: Output, n) -> Output:
+    name = (name.decode() if isinstance(name, bytes) else str(name))
+    params = list(n.attrs.get("activation_params", []))
+    if name in ("", "None"):
+        return x
+    if name == "Relu":
+        return ops.relu(x).output(0)
+    if name == "Sigmoid":
+        return ops.sigmoid(x).output(0)
+    if name == "Tanh":
+        return ops.tanh(x).output(0)
+    if name == "LeakyRelu":
+        return ops.prelu(x, _f(params[0] if params else 0.01, x)).output(0)
+    if name == "Clip":
+        return ops.clamp(x, float(params[0]), float(params[1])).output(0)
+    if name == "HardSigmoid":
+        a, b = (params + [0.2, 0.5])[:2] if len(params) >= 2 else (0.2, 0.5)
+        return ops.clamp(ops.add(ops.multiply(x, _f(a, x)), _f(b, x)), 0.0, 1.0).output(0)
+    raise OnnxError("fused activation %s is not supported" % name)
+
+
+@_op("BiasAdd")
+def _bias_add(n, i):
+    """x [N, S, C] + bias [C] + skip [N, S, C]."""
+    return ops.add(ops.add(i[0], i[1]), i[2]).output(0)
+
+
+@_op("FusedGemm")
+def _fused_gemm(n, i):
+    return _activation(n.attrs.get("activation", b"Relu"), _T["Gemm"](n, i), n)
+
+
+@_op("FusedConv")
+def _fused_conv(n, i):
+    """Conv(x, w, b) [+ z] followed by the named activation."""
+    y = _T["Conv"](n, i[:3])
+    y = y[0] if isinstance(y, (list, tuple)) else y
+    if len(i) > 3 and i[3] is not None:
+        y = ops.add(y, i[3]).output(0)
+    return _activation(n.attrs.get("activation", b""), y, n)
+
+
+@_op("GroupNorm")
+def _group_norm_contrib(n, i):
+    """Channels-last (or channels-first) group normalisation with an optional Swish: x [N, H, W, C], gamma / beta [C]."""
+    x = i[0]
+    last = bool(n.attrs.get("channels_last", 1))
+    r = _rank(x)
+    if last:
+        x = ops.transpose(x, _i64([0, r - 1] + list(range(1, r - 1)))).output(0)
+    y = make_op("GroupNormalization", [x, i[1], i[2]], {"num_groups": int(n.attrs["groups"]), "epsilon": float(n.attrs.get("epsilon", 1e-5))}).output(0)
+    if int(n.attrs.get("activation", 0)) == 1:
+        y = ops.swish(y).output(0)
+    if last:
+        y = ops.transpose(y, _i64([0] + list(range(2, r)) + [1])).output(0)
+    return y
+
+
+def _dq(x: Output, scale: Output, zp) -> Output:
+    y = ops.convert(x, "f32").output(0)
+    if zp is not None:
+        y = ops.subtract(y, ops.convert(zp, "f32")).output(0)
+    return ops.multiply(y, ops.convert(scale, "f32")).output(0)
+
+
+def _q(y: Output, scale: Output, zp, like: Output) -> Output:
+    et = zp.get_element_type() if zp is not None else like.get_element_type()
+    lo, hi = (-128.0, 127.0) if str(et) == "i8" else (0.0, 255.0)
+    v = ops.round(ops.divide(y, ops.convert(scale, "f32")), "half_to_even")
+    if zp is not None:
+        v = ops.add(v, ops.convert(zp, "f32"))
+    return ops.convert(ops.clamp(v, lo, hi), et).output(0)
+
+
+def _opt(i, k):
+    return i[k] if len(i) > k and i[k] is not None else None
+
+
+@_op("QLinearAdd", "QLinearMul")
+def _qlinear_binary(n, i):
+    """(A, A_scale, A_zp, B, B_scale, B_zp, C_scale, C_zp): the operation on dequantised values, quantised again."""
+    a, b = _dq(i[0], i[1], _opt(i, 2)), _dq(i[3], i[4], _opt(i, 5))
+    y = (ops.add if n.op_type == "QLinearAdd" else ops.multiply)(a, b).output(0)
+    return _q(y, i[6], _opt(i, 7), i[0])
+
+
+@_op("QLinearSigmoid", "QLinearLeakyRelu")
+def _qlinear_unary(n, i):
+    x = _dq(i[0], i[1], _opt(i, 2))
+    y = ops.sigmoid(x).output(0) if n.op_type == "QLinearSigmoid" else ops.prelu(x, _f(float(n.attrs.get("alpha", 0.01)), x)).output(0)
+    return _q(y, i[3], _opt(i, 4), i[0])
+
+
+@_op("QLinearConcat")
+def _qlinear_concat(n, i):
+    """(Y_scale, Y_zp, then x, x_scale, x_zp per input)."""
+    parts = [_dq(i[k], i[k + 1], _opt(i, k + 2)) for k in range(2, len(i), 3)]
+    return _q(ops.concat(parts, int(n.attrs["axis"])).output(0), i[0], i[1], i[2])
+
+
+@_op("QLinearWhere")
+def _qlinear_where(n, i):
+    """(condition, X, x_scale, x_zp, Y, y_scale, y_zp, z_scale, z_zp)."""
+    y = ops.select(i[0], _dq(i[1], i[2], _opt(i, 3)), _dq(i[4], i[5], _opt(i, 6))).output(0)
+    return _q(y, i[7], _opt(i, 8), i[1])
+
+
+@_op("MatMulIntegerToFloat")
+def _matmul_integer_to_float(n, i):
+    """(A, B, a_scale, b_scale, a_zp, b_zp, bias): the product of the dequantised operands, in float."""
+    y = ops.matmul(_dq(i[0], i[2], _opt(i, 4)), _dq(i[1], i[3], _opt(i, 5)), False, False).output(0)
+    return ops.add(y, i[6]).output(0) if _opt(i, 6) is not None else y
+
+
+@_op("DynamicQuantizeMatMul")
+def _dynamic_quantize_matmul(n, i):
+    """(A float, B quantised, b_scale, b_zp, bias): A is quantised to u8 with the range of the whole tensor first."""
+    q = _T["DynamicQuantizeLinear"](n, [i[0]])
+    a = _dq(q[0], q[1], q[2])
+    y = ops.matmul(a, _dq(i[1], i[2], _opt(i, 3)), False, False).output(0)
+    return ops.add(y, i[4]).output(0) if _opt(i, 4) is not None else y
+
+
+def _split_heads(x: Output, heads: int) -> Output:
+    return ops.transpose(ops.reshape(x, _i64([0, 0, heads, -1]), True), _i64([0, 2, 1, 3])).output(0)
+
+
+def _merge_heads(x: Output) -> Output:
+    return ops.reshape(ops.transpose(x, _i64([0, 2, 1, 3])), _i64([0, 0, -1]), True).output(0)
+
+
+def _key_padding_bias(mask: Output, like: Output) -> Output:
+    """mask [B, S_kv] of 0 / 1 -> additive [B, 1, 1, S_kv]."""
+    keep = ops.convert(ops.unsqueeze(mask, _i64([1, 2])), "f32")
+    return ops.multiply(ops.subtract(_f(1.0, like), keep), _f(-10000.0, like)).output(0)
+
+
+@_op("MultiHeadAttention")
+def _multi_head_attention(n, i):
+    """query / key / value [B, S, hidden] (+ bias [3 * hidden], key padding mask [B, S_kv], attention bias [B or 1, N or 1, S, S_kv])."""
+    heads = int(n.attrs["num_heads"])
+    q, k, v = i[0], _opt(i, 1), _opt(i, 2)
+    if k is None or v is None or _rank(q) != 3 or _rank(k) != 3:
+        raise OnnxError("MultiHeadAttention: packed QKV / KV layouts are not supported")
+    bias = _opt(i, 3)
+    if bias is not None:
+        b3 = ops.split(bias, _i64(0), 3)
+        q, k, v = ops.add(q, b3.output(0)).output(0), ops.add(k, b3.output(1)).output(0), ops.add(v, b3.output(2)).output(0)
+    qh, kh, vh = _split_heads(q, heads), _split_heads(k, heads), _split_heads(v, heads)
+    extra = None
+    if _opt(i, 4) is not None:
+        if _rank(i[4]) != 2:
+            raise OnnxError("MultiHeadAttention: only [batch, kv length] key padding masks are supported")
+        extra = _key_padding_bias(i[4], qh)
+    if _opt(i, 5) is not None:
+        extra = i[5] if extra is None else ops.add(extra, i[5]).output(0)
+    args = [qh, kh, vh] + ([extra] if extra is not None else [])
+    if "scale" in n.attrs and float(n.attrs["scale"]) != 0.0:
+        if extra is None:
+            args.append(_f(0.0, qh))
+        args.append(_f(float(n.attrs["scale"]), qh))
+    y = ops.scaled_dot_product_attention(*args, causal=bool(n.attrs.get("unidirectional", 0)) and extra is None).output(0)
+    return [_merge_heads(y), None, None]
+
+
+@_op("Attention")
+def _attention(n, i):
+    """input [B, S, hidden_in] x weights [hidden_in, 3 * hidden] + bias [3 * hidden], optional mask [B, S] -> [B, S, hidden]."""
+    heads = int(n.attrs["num_heads"])
+    if _opt(i, 4) is not None:
+        raise OnnxError("Attention: a past state input is not supported")
+    qkv = ops.matmul(i[0], i[1], False, False).output(0)
+    if _opt(i, 2) is not None:
+        qkv = ops.add(qkv, i[2]).output(0)
+    sizes = n.attrs.get("qkv_hidden_sizes")
+    parts = ops.variadic_split(qkv, _i64(2), _i64(list(sizes))) if sizes else ops.split(qkv, _i64(2), 3)
+    qh, kh, vh = (_split_heads(parts.output(k), heads) for k in range(3))
+    uni = bool(n.attrs.get("unidirectional", 0))
+    args = [qh, kh, vh]
+    if _opt(i, 3) is not None:
+        if _rank(i[3]) != 2:
+            raise OnnxError("Attention: only [batch, length] masks are supported")
+        bias = _key_padding_bias(i[3], qh)
+        if uni:
+            raise OnnxError("Attention: a mask together with unidirectional is not supported")
+        args.append(bias)
+    if "scale" in n.attrs and float(n.attrs["scale"]) != 0.0:
+        if len(args) == 3:
+            args.append(_f(0.0, qh))
+        args.append(_f(float(n.attrs["scale"]), qh))
+    y = ops.scaled_dot_product_attention(*args, causal=uni and len(args) == 3).output(0)
+    return [_merge_heads(y), None]

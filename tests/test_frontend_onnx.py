@@ -48,6 +48,8 @@ def attr(name, v):
         return b + _ld(5, tensor("", v)) + _int(20, 4)
     if isinstance(v, list) and all(isinstance(x, int) for x in v):
         return b + b"".join(_int(8, x) for x in v) + _int(20, 7)
+    if isinstance(v, list) and all(isinstance(x, float) for x in v):
+        return b + _ld(7, struct.pack("<%df" % len(v), *v)) + _int(20, 6)
     raise TypeError(v)
 
 

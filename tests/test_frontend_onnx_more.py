@@ -200,3 +200,72 @@ def test_group_query_attention_contrib():
     ref_y, ref_k = reference(True)
     np.testing.assert_allclose(y, ref_y, rtol=2e-5, atol=2e-5)
     np.testing.assert_allclose(nk, ref_k, rtol=2e-5, atol=2e-5)
+
+
+def test_contrib_attention_qlinear_and_fused_ops():
+    rng = np.random.default_rng(31)
+    B, S, Hd, N = 2, 5, 16, 4
+    x = rng.standard_normal((B, S, Hd)).astype(np.float32)
+    w = (rng.standard_normal((Hd, 3 * Hd)) * 0.3).astype(np.float32)
+    bias = rng.standard_normal((3 * Hd,)).astype(np.float32)
+    mask = np.array([[1, 1, 1, 0, 0], [1, 1, 1, 1, 1]], np.int32)
+    t = torch.tensor
+
+    def sdpa(q, k, v, add=None, causal=False):
+        sp = lambda a: a.reshape(B, -1, N, Hd // N).transpose(1, 2)
+        o = torch.nn.functional.scaled_dot_product_attention(sp(q), sp(k), sp(v), attn_mask=add, is_causal=causal)
+        return o.transpose(1, 2).reshape(B, -1, Hd).numpy()
+    qkv = t(x) @ t(w) + t(bias)
+    q, k, v = qkv.split(Hd, -1)
+    add = ((1 - t(mask).float()) * -10000.0)[:, None, None, :]
+    y, = run([node("Attention", ["x", "w", "b", "m"], ["y"], num_heads=N)], {"w": w, "b": bias}, [("x", 1, [B, S, Hd]), ("m", 6, [B, S])], [("y", 1, [B, S, Hd])], [x, mask])
+    np.testing.assert_allclose(y, sdpa(q, k, v, add), rtol=1e-4, atol=1e-5)
+    y, = run([node("Attention", ["x", "w", "b"], ["y"], num_heads=N, unidirectional=1)], {"w": w, "b": bias}, [("x", 1, [B, S, Hd])], [("y", 1, [B, S, Hd])], [x])
+    np.testing.assert_allclose(y, sdpa(q, k, v, None, True), rtol=1e-4, atol=1e-5)
+
+    kx = rng.standard_normal((B, 7, Hd)).astype(np.float32)
+    vx = rng.standard_normal((B, 7, Hd)).astype(np.float32)
+    rel = rng.standard_normal((1, N, S, 7)).astype(np.float32)
+    y, = run([node("MultiHeadAttention", ["q", "k", "v", "b", "", "rel"], ["y"], num_heads=N)], {"b": bias, "rel": rel},
+             [("q", 1, [B, S, Hd]), ("k", 1, [B, 7, Hd]), ("v", 1, [B, 7, Hd])], [("y", 1, [B, S, Hd])], [x, kx, vx])
+    bq, bk, bv = t(bias).split(Hd)
+    np.testing.assert_allclose(y, sdpa(t(x) + bq, t(kx) + bk, t(vx) + bv, t(rel)), rtol=1e-4, atol=1e-5)
+
+    # quantised element-wise family
+    a = rng.integers(0, 255, (3, 4)).astype(np.uint8)
+    b = rng.integers(0, 255, (3, 4)).astype(np.uint8)
+    inits = {"as": np.array(0.02, np.float32), "az": np.array(128, np.uint8), "bs": np.array(0.03, np.float32), "bz": np.array(120, np.uint8),
+             "cs": np.array(0.05, np.float32), "cz": np.array(100, np.uint8)}
+    nodes = [node("QLinearAdd", ["a", "as", "az", "b", "bs", "bz", "cs", "cz"], ["s"]), node("QLinearMul", ["a", "as", "az", "b", "bs", "bz", "cs", "cz"], ["p"]),
+             node("QLinearSigmoid", ["a", "as", "az", "cs", "cz"], ["g"]), node("QLinearLeakyRelu", ["a", "as", "az", "cs", "cz"], ["l"], alpha=0.1),
+             node("QLinearConcat", ["cs", "cz", "a", "as", "az", "b", "bs", "bz"], ["c"], axis=1)]
+    s, p, g, l, c = run(nodes, inits, [("a", 2, [3, 4]), ("b", 2, [3, 4])], [("s", 2, [3, 4]), ("p", 2, [3, 4]), ("g", 2, [3, 4]), ("l", 2, [3, 4]), ("c", 2, [3, 8])], [a, b])
+    fa, fb = (a.astype(np.float32) - 128) * 0.02, (b.astype(np.float32) - 120) * 0.03
+    quant = lambda v: np.clip(np.round(v / 0.05) + 100, 0, 255).astype(np.uint8)
+    for got, ref in ((s, fa + fb), (p, fa * fb), (g, 1 / (1 + np.exp(-fa))), (l, np.where(fa >= 0, fa, 0.1 * fa)), (c, np.concatenate([fa, fb], 1))):
+        assert got.dtype == np.uint8 and np.abs(got.astype(np.int32) - quant(ref).astype(np.int32)).max() <= 1
+
+    # fused float ops and the integer products with float scales
+    gx = rng.standard_normal((3, 6)).astype(np.float32)
+    gw = rng.standard_normal((6, 5)).astype(np.float32)
+    gb = rng.standard_normal((5,)).astype(np.float32)
+    skip = rng.standard_normal((B, S, Hd)).astype(np.float32)
+    bi = rng.integers(-100, 100, (6, 5)).astype(np.int8)
+    nodes = [node("FusedGemm", ["gx", "gw", "gb"], ["fg"], activation=b"LeakyRelu", activation_params=[0.2]), node("BiasAdd", ["x", "hb", "skip"], ["ba"]),
+             node("MatMulIntegerToFloat", ["ai", "bi", "sa", "sb", "za", "", "gb"], ["mf"]), node("DynamicQuantizeMatMul", ["gx", "bi", "sb", "", "gb"], ["dq"])]
+    ai = rng.integers(0, 255, (3, 6)).astype(np.uint8)
+    inits = {"gw": gw, "gb": gb, "hb": bias[:Hd].copy(), "bi": bi, "sa": np.array(0.01, np.float32), "sb": np.array(0.02, np.float32), "za": np.array(127, np.uint8)}
+    fg, ba, mf, dq = run(nodes, inits, [("gx", 1, [3, 6]), ("x", 1, [B, S, Hd]), ("skip", 1, [B, S, Hd]), ("ai", 2, [3, 6])],
+                         [("fg", 1, [3, 5]), ("ba", 1, [B, S, Hd]), ("mf", 1, [3, 5]), ("dq", 1, [3, 5])], [gx, x, skip, ai])
+    np.testing.assert_allclose(fg, torch.nn.functional.leaky_relu(t(gx) @ t(gw) + t(gb), 0.2).numpy(), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(ba, x + bias[:Hd] + skip, rtol=1e-6)
+    np.testing.assert_allclose(mf, ((ai.astype(np.float32) - 127) * 0.01) @ (bi.astype(np.float32) * 0.02) + gb, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(dq, gx @ (bi.astype(np.float32) * 0.02) + gb, atol=0.15)          # A goes through 8 bits first
+
+    # channels-last group normalisation with Swish
+    im = rng.standard_normal((2, 3, 3, 8)).astype(np.float32)
+    gamma, beta = rng.standard_normal(8).astype(np.float32), rng.standard_normal(8).astype(np.float32)
+    gn, = run([node("GroupNorm", ["im", "gamma", "beta"], ["gn"], groups=2, activation=1, epsilon=1e-5)], {"gamma": gamma, "beta": beta}, [("im", 1, [2, 3, 3, 8])],
+              [("gn", 1, [2, 3, 3, 8])], [im])
+    ref = torch.nn.functional.silu(torch.nn.functional.group_norm(t(im).permute(0, 3, 1, 2), 2, t(gamma), t(beta), 1e-5)).permute(0, 2, 3, 1).numpy()
+    np.testing.assert_allclose(gn, ref, rtol=1e-4, atol=1e-5)
