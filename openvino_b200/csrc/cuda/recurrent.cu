@@ -132,21 +132,25 @@ selective_ssm_kernel(const float* __restrict__ A, const float* __restrict__ dt, 
 }
 
 // Value columns iv of the state [Dk, Dv] of (b, hv):  S *= exp(g);  delta = (v - <S, k>) * beta;  S += k * delta;  y = <S, q>.
-// q arrives scaled (and normalised where the layer asks for it), k normalised likewise. One CTA owns REC_TILE columns of one
-// (b, hv); q and k of the head (shared by all its columns) are staged in shared memory REC_CHUNK tokens at a time.
-template <int NV>
+// q arrives scaled (and normalised where the layer asks for it), k normalised likewise. One CTA owns CW * 8 columns of one
+// (b, hv), each warp CW of them; q and k of the head (shared by all its columns) are staged in shared memory REC_CHUNK
+// tokens at a time, and the outputs of a chunk leave through shared memory as whole rows of y.
+template <int NV, int CW>
 __global__ void __launch_bounds__(REC_WARPS * 32)
 gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ gate,
                         const float* __restrict__ beta, float* __restrict__ state, float* __restrict__ y, int L, int Hq, int Hv, int Dk, int Dv) {
-    __shared__ float sQ[REC_CHUNK][NV * 32], sK[REC_CHUNK][NV * 32], sV[REC_CHUNK][REC_TILE], sG[REC_CHUNK], sBt[REC_CHUNK];
+    constexpr int TILE = REC_WARPS * CW;
+    __shared__ float sQ[REC_CHUNK][NV * 32], sK[REC_CHUNK][NV * 32], sV[REC_CHUNK][TILE], sY[REC_CHUNK][TILE], sG[REC_CHUNK], sBt[REC_CHUNK];
     const int bh = blockIdx.y, b = bh / Hv, h = bh % Hv, hq = h / (Hv / Hq);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c0 = blockIdx.x * REC_TILE, cw = c0 + warp * REC_PER_WARP;
-    float st[REC_PER_WARP][NV];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, c0 = blockIdx.x * TILE, cw = c0 + warp * CW;
+    float st[CW][NV];
     float* sbase = state + (size_t)bh * Dk * Dv;
 #pragma unroll
-    for (int c = 0; c < REC_PER_WARP; ++c)
+    for (int c = 0; c < CW; ++c)
 #pragma unroll
         for (int i = 0; i < NV; ++i) st[c][i] = (cw + c < Dv && lane + 32 * i < Dk) ? sbase[(size_t)(lane + 32 * i) * Dv + cw + c] : 0.f;
+    const int mine = CW == 8 ? rec_owned_value8(lane) : rec_owned_value(lane);
+    const bool writer = CW == 8 ? (lane & 3) == 0 : (lane & 7) == 0;
     for (int t0 = 0; t0 < L; t0 += REC_CHUNK) {
         const int nt = min(REC_CHUNK, L - t0);
         const size_t tok0 = (size_t)b * L + t0;
@@ -156,8 +160,8 @@ gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k
             sQ[tt][d] = d < Dk ? q[((tok0 + tt) * Hq + hq) * Dk + d] : 0.f;
             sK[tt][d] = d < Dk ? k[((tok0 + tt) * Hq + hq) * Dk + d] : 0.f;
         }
-        for (int idx = threadIdx.x; idx < nt * REC_TILE; idx += REC_WARPS * 32) {
-            const int tt = idx / REC_TILE, c = idx % REC_TILE;
+        for (int idx = threadIdx.x; idx < nt * TILE; idx += REC_WARPS * 32) {
+            const int tt = idx / TILE, c = idx % TILE;
             sV[tt][c] = c0 + c < Dv ? v[((tok0 + tt) * Hv + h) * Dv + c0 + c] : 0.f;
         }
         if (threadIdx.x < nt) {
@@ -167,14 +171,14 @@ gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const float decay = sG[tt], bt = sBt[tt];
-            float kr[NV], qr[NV], mem[REC_PER_WARP], o[REC_PER_WARP];
+            float kr[NV], qr[NV], mem[CW], o[CW];
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 kr[i] = sK[tt][lane + 32 * i];
                 qr[i] = sQ[tt][lane + 32 * i];
             }
 #pragma unroll
-            for (int c = 0; c < REC_PER_WARP; ++c) {
+            for (int c = 0; c < CW; ++c) {
                 mem[c] = 0.f;
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
@@ -182,10 +186,13 @@ gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k
                     mem[c] += st[c][i] * kr[i];
                 }
             }
-            const float m = rec_reduce4(mem[0], mem[1], mem[2], mem[3], lane);
+            float m;
+            if constexpr (CW == 8) m = rec_reduce8(mem, lane);
+            else m = rec_reduce4(mem[0], mem[1], mem[2], mem[3], lane);
 #pragma unroll
-            for (int c = 0; c < REC_PER_WARP; ++c) {
-                const float delta = (sV[tt][warp * REC_PER_WARP + c] - __shfl_sync(0xffffffffu, m, rec_owner_lane(c))) * bt;
+            for (int c = 0; c < CW; ++c) {
+                const int owner = CW == 8 ? (((c & 1) << 4) | (((c >> 1) & 1) << 3) | (((c >> 2) & 1) << 2)) : rec_owner_lane(c);
+                const float delta = (sV[tt][warp * CW + c] - __shfl_sync(0xffffffffu, m, owner)) * bt;
                 o[c] = 0.f;
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
@@ -193,19 +200,25 @@ gated_delta_rule_kernel(const float* __restrict__ q, const float* __restrict__ k
                     o[c] += st[c][i] * qr[i];
                 }
             }
-            const float total = rec_reduce4(o[0], o[1], o[2], o[3], lane);
-            const int c = rec_owned_value(lane);
-            if ((lane & 7) == 0 && cw + c < Dv) y[((tok0 + tt) * Hv + h) * Dv + cw + c] = total;
+            float total;
+            if constexpr (CW == 8) total = rec_reduce8(o, lane);
+            else total = rec_reduce4(o[0], o[1], o[2], o[3], lane);
+            if (writer) sY[tt][warp * CW + mine] = total;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * TILE; idx += REC_WARPS * 32) {
+            const int tt = idx / TILE, c = idx % TILE;
+            if (c0 + c < Dv) y[((tok0 + tt) * Hv + h) * Dv + c0 + c] = sY[tt][c];
         }
     }
 #pragma unroll
-    for (int c = 0; c < REC_PER_WARP; ++c)
+    for (int c = 0; c < CW; ++c)
 #pragma unroll
         for (int i = 0; i < NV; ++i)
             if (cw + c < Dv && lane + 32 * i < Dk) sbase[(size_t)(lane + 32 * i) * Dv + cw + c] = st[c][i];
 }
 
-// OVB_SSM_ROWS_PER_WARP = 4 keeps the four-row form for every shape (8 by default where it applies)
+// OVB_SSM_ROWS_PER_WARP = 4 keeps the four-row (four-column) form of both kernels for every shape (8 by default where it applies)
 int env_rows_per_warp() {
     const char* e = getenv("OVB_SSM_ROWS_PER_WARP");
     return e && atoi(e) == 4 ? 4 : 8;
@@ -260,8 +273,13 @@ int ovb_gated_delta_rule(const float* q, const float* k, const float* v, const f
     }
     OVB_REQUIRE((long long)B * Hv <= 65535, "ovb_gated_delta_rule: batch x value heads above 65535");
     cudaStream_t stream = (cudaStream_t)stream_;
+    static const int cols_per_warp = env_rows_per_warp();
     return dispatch_width(Dk, [&](auto nv) -> int {
-        gated_delta_rule_kernel<decltype(nv)::value><<<dim3(ceil_div(Dv, REC_TILE), B * Hv), REC_WARPS * 32, 0, stream>>>(q, k, v, gate, beta, state, y, L, Hq, Hv, Dk, Dv);
+        constexpr int NV = decltype(nv)::value;
+        if (NV <= 4 && Dv >= 64 && cols_per_warp == 8)
+            gated_delta_rule_kernel<NV, 8><<<dim3(ceil_div(Dv, REC_WARPS * 8), B * Hv), REC_WARPS * 32, 0, stream>>>(q, k, v, gate, beta, state, y, L, Hq, Hv, Dk, Dv);
+        else
+            gated_delta_rule_kernel<NV, 4><<<dim3(ceil_div(Dv, REC_WARPS * 4), B * Hv), REC_WARPS * 32, 0, stream>>>(q, k, v, gate, beta, state, y, L, Hq, Hv, Dk, Dv);
         OVB_CHECK_CUDA(cudaGetLastError());
         return 0;
     });
