@@ -1254,6 +1254,68 @@ def _pa_kv_reorder(n, ins, ctx):
     return [torch.zeros(1, dtype=torch.uint8)]
 
 
+@op("GroupQueryAttention")
+def _group_query_attention(n, ins, ctx):
+    """q [B, N, S, H], k / v [B, Nkv, S, H], past k / v [B, Nkv, P, H], seqlens_k, total length, then optional rotary caches,
+    position ids, attention bias, head sink -> (attention [B, S, N * H], present k, present v). The key / value rows are
+    laid out on the device, the attention itself runs on the package's dense kernel when its layout is served (no bias,
+    no sink, no window, one of its head sizes, 16-bit) and on the library expression otherwise."""
+    ins = _same_device(ctx, ins)
+    at = n.get_attributes()
+    q, k, v, pk, pv = ins[:5]
+    have = lambda i: len(ins) > i and ins[i].numel() > 0
+    B, N, S, H = q.shape
+    Nkv = k.shape[1]
+    total = int(_host_ints(ins[5])[0]) + 1
+    P = total - S
+    if P < 0 or P > pk.shape[2]:
+        raise RuntimeError("GroupQueryAttention: seqlens_k names a past of %d rows, the past tensors hold %d" % (P, pk.shape[2]))
+    if at.get("do_rotary"):
+        cos, sin = ins[7].float(), ins[8].float()
+        half = cos.shape[-1]
+        rows = ins[9].to(q.device).long().reshape(-1, S) if have(9) else torch.arange(P, P + S, device=q.device).reshape(1, S)
+        c, s_ = cos[rows].unsqueeze(1), sin[rows].unsqueeze(1)                 # [B or 1, 1, S, half]
+
+        def rotate(x):
+            xf = x.float()
+            if at.get("rotary_interleaved"):
+                a, b = xf[..., 0:2 * half:2], xf[..., 1:2 * half:2]
+                r = torch.stack([a * c - b * s_, a * s_ + b * c], -1).flatten(-2)
+            else:
+                a, b = xf[..., :half], xf[..., half:2 * half]
+                r = torch.cat([a * c - b * s_, a * s_ + b * c], -1)
+            return torch.cat([r, xf[..., 2 * half:]], -1).to(x.dtype)
+        q, k = rotate(q), rotate(k)
+    K_ = torch.cat([pk[:, :, :P].to(k.dtype), k], 2)
+    V_ = torch.cat([pv[:, :, :P].to(v.dtype), v], 2)
+    scale = float(at.get("scale") or 0.0) or float(H) ** -0.5
+    window = int(at.get("local_window_size", -1))
+    sink = ins[11].float() if have(11) else None
+    smooth = bool(at.get("smooth_softmax")) or sink is not None
+    group = N // Nkv
+    Kx, Vx = K_.repeat_interleave(group, 1), V_.repeat_interleave(group, 1)
+    if (ctx.K is not None and P == 0 and not have(10) and not smooth and window <= 0 and q.dtype in (torch.float16, torch.bfloat16) and H in (64, 128)):
+        pack = lambda t: _dense(t.transpose(1, 2)).reshape(B * S, N * H)
+        out = ctx.K.sdpa_dense(pack(q), pack(Kx), pack(Vx), B, S, N, H, N * H, scale=scale, causal=True).reshape(B, S, N * H)
+        return [out, K_, V_]
+    sc = torch.matmul(q.float(), Kx.float().transpose(-1, -2)) * scale
+    if have(10):
+        sc = sc + ins[10].float()[..., :total]
+    i = torch.arange(S, device=q.device).unsqueeze(1) + P
+    j = torch.arange(total, device=q.device).unsqueeze(0)
+    keep = j <= i
+    if window > 0:
+        keep = keep & (j > i - window)
+    sc = sc.masked_fill(~keep, float("-inf"))
+    if smooth:
+        col = (sink if sink is not None else torch.zeros(N, device=q.device)).reshape(1, N, 1, 1).expand(B, N, S, 1)
+        w = torch.softmax(torch.cat([sc, col], -1), -1)[..., :-1]
+    else:
+        w = torch.softmax(sc, -1)
+    out = torch.matmul(w, Vx.float()).to(q.dtype).transpose(1, 2).reshape(B, S, N * H)
+    return [out, K_, V_]
+
+
 @op("ReadValue")
 def _read_value(n, ins, ctx):
     vid = n.get_attribute("variable_id")

@@ -1,6 +1,7 @@
 """Transformation-private operations: expert-gathered products, compressed grouped product, quantised fully-connected
 forms and segment-wise attention, against NumPy / PyTorch restatements."""
 import numpy as np
+import pytest
 import torch
 
 import openvino_b200 as ov
@@ -243,3 +244,61 @@ def test_type_relaxed_overrides_input_and_output_types():
     # shape arguments given as constants still drive the wrapped operation's shape inference
     r = ops.type_relaxed("Reshape", [x, ops.constant(np.array([4, 2], np.int64))], [], ["f16"], base_version="opset1", special_zero=False)
     assert list(r.get_output_shape(0)) == [4, 2]
+
+
+def test_group_query_attention_device_expression_matches_the_reference_evaluation():
+    """The CUDA device's GroupQueryAttention (runtime/cuda_plugin.py) on host tensors against the restatement above."""
+    import types as _types
+    from openvino_b200.runtime import cuda_plugin
+    rng = np.random.default_rng(12)
+    ctx = _types.SimpleNamespace(on_gpu=False, device="cpu", K=None)
+    B, Nq, Nkv, H, Pmax = 2, 4, 2, 8, 12
+    for S, past, kw in ((5, 0, {}), (1, 7, {}), (3, 4, {"window": 4}), (2, 5, {"rot": True}), (2, 5, {"rot": True, "inter": True}), (3, 2, {"sink": True}), (2, 3, {"bias": True})):
+        total = past + S
+        q, k, v = (rng.standard_normal((B, h, S, H)).astype(np.float32) for h in (Nq, Nkv, Nkv))
+        pk, pv = (rng.standard_normal((B, Nkv, Pmax, H)).astype(np.float32) for _ in range(2))
+        feeds = [q, k, v, pk, pv, np.array([total - 1], np.int32), np.array(total, np.int32)]
+        attrs, ref_kw = dict(num_heads=Nq, kv_num_heads=Nkv), {}
+        empty = np.zeros((0,), np.float32)
+        if kw.get("rot"):
+            ang = rng.random((32, H // 2)).astype(np.float32) * 3
+            feeds += [np.cos(ang), np.sin(ang)]
+            attrs.update(do_rotary=True, rotary_interleaved=bool(kw.get("inter")))
+            ref_kw.update(rotary=(np.cos(ang), np.sin(ang)), interleaved=bool(kw.get("inter")))
+        if kw.get("window"):
+            attrs["local_window_size"] = ref_kw["window"] = kw["window"]
+        if kw.get("sink"):
+            sink = rng.standard_normal((Nq,)).astype(np.float32)
+            feeds += [empty, empty, empty, empty, sink]
+            ref_kw["sink"] = sink
+        if kw.get("bias"):
+            bias = rng.standard_normal((1, Nq, S, total + 2)).astype(np.float32)
+            feeds += [empty, empty, empty, bias]
+            ref_kw["bias"] = bias
+        ps = [P(a.shape, "p%d" % i, "f32" if a.dtype == np.float32 else "i32") for i, a in enumerate(feeds)]
+        node = ops.group_query_attention(ps, **attrs)
+        got = cuda_plugin._OPS["GroupQueryAttention"](node, [torch.from_numpy(a) for a in feeds], ctx)
+        ref = _gqa_reference(q, k, v, pk, pv, total, **ref_kw)
+        for g, r in zip(got, ref):
+            np.testing.assert_allclose(g.numpy(), r, rtol=2e-5, atol=2e-5, err_msg=str(kw))
+
+
+@pytest.mark.gpu
+def test_group_query_attention_on_the_device():
+    """Prefill in f16 with head size 64 runs the package's dense attention kernel; a decode step with a past runs the
+    expression path; both against the fp32 restatement."""
+    rng = np.random.default_rng(13)
+    B, Nq, Nkv, H, Pmax = 2, 4, 2, 64, 40
+    core = ov.Core()
+    for S, past, tol in ((33, 0, 2e-2), (1, 20, 2e-2)):
+        total = past + S
+        q, k, v = (rng.standard_normal((B, h, S, H)).astype(np.float32) * 0.5 for h in (Nq, Nkv, Nkv))
+        pk, pv = (rng.standard_normal((B, Nkv, Pmax, H)).astype(np.float32) * 0.5 for _ in range(2))
+        feeds = [q, k, v, pk, pv, np.array([total - 1], np.int32), np.array(total, np.int32)]
+        ps = [P(a.shape, "p%d" % i, "f32" if a.dtype == np.float32 else "i32") for i, a in enumerate(feeds)]
+        node = ops.group_query_attention(ps, num_heads=Nq, kv_num_heads=Nkv)
+        cm = core.compile_model(ov.Model([node.output(0), node.output(1)], ps, "gqa"), "CUDA", {"INFERENCE_PRECISION_HINT": "f16"})
+        res = cm(feeds)
+        ref = _gqa_reference(q, k, v, pk, pv, total)
+        np.testing.assert_allclose(np.asarray(res[0], np.float32), ref[0], rtol=tol, atol=tol)
+        np.testing.assert_allclose(np.asarray(res[1], np.float32), ref[1], rtol=2e-3, atol=2e-3)
